@@ -1,0 +1,49 @@
+"""Engine options, with the names and meanings of the reference's ``ServeOptions``
+(models/qwen3/src/service.rs:43-140) and of its ``dinfer serve`` flags
+(bins/dinfer/src/main.rs:30-131) where it has them."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+
+@dataclass
+class EngineConfig:
+    # longest sequence (prompt + generated) a request may reach
+    max_model_len: int = 4096
+    # most requests running at the same time
+    max_num_seqs: int = 16
+    # token budget of one step; a longer prompt is cut into portions of at most this many
+    max_num_batched_tokens: int = 2048
+    # pages of the cache pool; None = from the free device memory
+    num_blocks: Optional[int] = None
+    # tokens per page
+    block_size: int = 16
+    # share of the device memory that weights, scratch and cache may take together
+    gpu_memory_utilization: float = 0.9
+    # decoded tokens do not count against the token budget (so every running request decodes
+    # in every step and prompts fill what is left)
+    decode_exempt_from_budget: bool = True
+    # one prompt gets at most this many tokens a step (0 = no limit)
+    long_prefill_token_threshold: int = 0
+    # decode-only steps replay a captured CUDA graph
+    enable_cuda_graph: bool = True
+    # "bfloat16" = what serving uses; "float32" = everything in true 32-bit
+    dtype: str = "bfloat16"
+    device: int = 0
+
+    def check(self) -> None:
+        if self.dtype not in ("bfloat16", "float32"):
+            raise ValueError(f"dtype must be bfloat16 or float32, got {self.dtype!r}")
+        if self.block_size <= 0:
+            raise ValueError(f"block_size must be positive, got {self.block_size}")
+        if self.max_num_seqs <= 0:
+            raise ValueError(f"max_num_seqs must be positive, got {self.max_num_seqs}")
+        if self.max_num_batched_tokens <= 0:
+            raise ValueError("max_num_batched_tokens must be positive")
+        if self.max_model_len <= 1:
+            raise ValueError("max_model_len must be at least 2")
+        if not (0.0 < self.gpu_memory_utilization <= 1.0):
+            raise ValueError("gpu_memory_utilization must be in (0, 1]")
+        if self.num_blocks is not None and self.num_blocks <= 0:
+            raise ValueError("num_blocks must be positive")

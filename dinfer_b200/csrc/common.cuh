@@ -1,0 +1,110 @@
+// Shared helpers of the kernel libraries.  Every library is one .cu file built into its own
+// shared object with a C ABI: `extern "C" int dinfer_<op>(pointers..., sizes..., cudaStream_t)`.
+// A call returns 0, a positive cudaError_t, or a negative refusal code; the text of the last
+// refusal or CUDA error of the calling thread is read with dinfer_last_error().
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#define DINFER_API extern "C" __attribute__((visibility("default")))
+
+enum DinferDtype : int { DINFER_F32 = 0, DINFER_BF16 = 1 };
+
+enum DinferStatus : int {
+  DINFER_OK = 0,
+  DINFER_BAD_ARGUMENT = -1,   // a size or option the kernel does not take
+  DINFER_BAD_DTYPE = -2,
+  DINFER_DEVICE_STATUS = -3,  // a kernel recorded a fault in its status word
+};
+
+namespace dinfer {
+
+inline char* error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+inline int refuse(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+inline int cuda_status(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    snprintf(error_buffer(), 512, "%s: %s", what, cudaGetErrorString(e));
+    return (int)e;
+  }
+  return 0;
+}
+
+// ---- element types: storage in T, arithmetic in float ----
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarp ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarp ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+}  // namespace dinfer
+
+// One of these per library gives Python the text of the last refusal.
+#define DINFER_DEFINE_LAST_ERROR() \
+  DINFER_API const char* dinfer_last_error() { return dinfer::error_buffer(); }
+
+// Call `expr` with T bound to the element type that `code` names.
+#define DINFER_DISPATCH_DTYPE(code, T, ...)                                  \
+  do {                                                                       \
+    if ((code) == DINFER_F32) { using T = float; __VA_ARGS__; }              \
+    else if ((code) == DINFER_BF16) { using T = __nv_bfloat16; __VA_ARGS__; }\
+    else return dinfer::refuse(DINFER_BAD_DTYPE, "unknown dtype code %d", (int)(code)); \
+  } while (0)

@@ -1,0 +1,88 @@
+// Embedding gather into the 32-bit residual stream, and the SwiGLU gate.
+// Counterparts in the reference: crates/kernels/cuda/activation.cu:121-129 (embedding, an id out of
+// range reads row 0) and :80-99 (silu_and_mul).
+#include "common.cuh"
+
+using namespace dinfer;
+
+namespace {
+
+template <typename TW>
+__global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
+                                 float* __restrict__ out, int h, int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  const TW* row = table + (int64_t)id * h;
+  float* o = out + (int64_t)t * h;
+  for (int i = threadIdx.x; i < h; i += blockDim.x) o[i] = to_f32<TW>(row[i]);
+}
+
+// out[t, i] = silu(x[t, i]) * x[t, I + i]; silu(g) = g / (1 + exp(-g)) in 32-bit, one rounding.
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int inter, int64_t ldx) {
+  const int t = blockIdx.x;
+  const T* g = x + (int64_t)t * ldx;
+  const T* u = g + inter;
+  T* o = out + (int64_t)t * inter;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x) {
+    const float a = to_f32<T>(g[i]);
+    const float b = to_f32<T>(u[i]);
+    o[i] = from_f32<T>(a / (1.f + expf(-a)) * b);
+  }
+}
+
+template <typename TS, typename TD>
+__global__ void cast_kernel(const TS* __restrict__ src, TD* __restrict__ dst, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    dst[i] = from_f32<TD>(to_f32<TS>(src[i]));
+}
+
+}  // namespace
+
+DINFER_DEFINE_LAST_ERROR()
+
+// ids [T] int32; table [vocab, h]; out [T, h] f32.
+DINFER_API int dinfer_embedding(const int* ids, const void* table, float* out, int T, int h, int vocab,
+                                int table_dtype, cudaStream_t stream) {
+  if (T < 0 || h <= 0 || vocab <= 0) return refuse(DINFER_BAD_ARGUMENT, "embedding: bad sizes T=%d h=%d vocab=%d", T, h, vocab);
+  if (T == 0) return 0;
+  int threads = (h + 31) / 32 * 32;
+  if (threads > 256) threads = 256;
+  DINFER_DISPATCH_DTYPE(table_dtype, TW, {
+    embedding_kernel<TW><<<T, threads, 0, stream>>>(ids, (const TW*)table, out, h, vocab);
+    return cuda_status("embedding");
+  });
+  return 0;
+}
+
+// x [T, 2*inter] with row stride ldx (gate first, then up); out [T, inter].
+DINFER_API int dinfer_silu_mul(const void* x, void* out, int T, int inter, int64_t ldx, int dtype,
+                               cudaStream_t stream) {
+  if (T < 0 || inter <= 0 || ldx < 2 * (int64_t)inter)
+    return refuse(DINFER_BAD_ARGUMENT, "silu_mul: bad sizes T=%d inter=%d ldx=%lld", T, inter, (long long)ldx);
+  if (T == 0) return 0;
+  const int threads = 256;
+  int bx = (inter + threads - 1) / threads;
+  if (bx > 64) bx = 64;
+  DINFER_DISPATCH_DTYPE(dtype, T_, {
+    silu_mul_kernel<T_><<<dim3(T, bx), threads, 0, stream>>>((const T_*)x, (T_*)out, inter, ldx);
+    return cuda_status("silu_mul");
+  });
+  return 0;
+}
+
+// dst[i] = (dst type) src[i]
+DINFER_API int dinfer_cast(const void* src, void* dst, int64_t n, int src_dtype, int dst_dtype,
+                           cudaStream_t stream) {
+  if (n < 0) return refuse(DINFER_BAD_ARGUMENT, "cast: negative length");
+  if (n == 0) return 0;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  DINFER_DISPATCH_DTYPE(src_dtype, TS,
+    DINFER_DISPATCH_DTYPE(dst_dtype, TD, {
+      cast_kernel<TS, TD><<<(int)blocks, 256, 0, stream>>>((const TS*)src, (TD*)dst, n);
+      return cuda_status("cast");
+    }));
+  return 0;
+}

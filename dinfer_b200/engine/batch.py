@@ -1,0 +1,143 @@
+"""A step's batch, from the host's description to the tensors the parts read.
+
+The host side is a list of ``StepEntry`` (request, its next tokens, the places whose logits are
+wanted).  ``PlanBuilder`` flattens them request-major into one packed int32 buffer in pinned
+memory, copied to the device in one transfer, and hands out views: ids, positions, cu_seqlens,
+seq_lens, and per cache group the block table and the slot of every new token.  The fields follow
+the reference's ``BatchPlan`` (crates/core/src/runner.rs:46-89, built at runner.rs:745-876).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..parts.base import CacheGroupView, StepContext
+
+
+@dataclass
+class StepEntry:
+    req_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()          # indices into ``tokens`` whose logits are returned
+
+
+class OutOfPages(RuntimeError):
+    """The cache pool cannot hold the tokens of this step."""
+
+
+def _align(n: int, a: int = 4) -> int:
+    return (n + a - 1) // a * a
+
+
+class PlanBuilder:
+    """Owns the pinned staging buffers (a small ring, so that a buffer is not rewritten while its
+    copy may still be in flight) and the device buffer the views point into."""
+
+    RING = 4
+
+    def __init__(self, manager: CacheManager, device, max_tokens: int, max_reqs: int, max_blocks: int):
+        self.manager = manager
+        self.device = device
+        self.max_blocks = max_blocks
+        ng = len(manager.groups)
+        cap = (3 * _align(max_tokens) + 6 * _align(max_reqs + 1) + ng * (_align(max_tokens) +
+               _align(max_reqs * max_blocks)) + 64)
+        self.capacity = cap
+        self.max_tokens, self.max_reqs = max_tokens, max_reqs
+        on_gpu = torch.device(device).type == "cuda"
+        self._host = [torch.empty(cap, dtype=torch.int32, pin_memory=on_gpu) for _ in range(self.RING)]
+        self._events = [None] * self.RING
+        self._dev = [torch.empty(cap, dtype=torch.int32, device=device) for _ in range(self.RING)]
+        self._turn = 0
+
+    def build(self, entries: Sequence[StepEntry], starts: Sequence[int], table_width: Optional[int] = None):
+        """``starts[i]`` = tokens of entry i already in the cache.  Pages must be allocated already.
+        Returns (ids, logits_rows, ctx)."""
+        m = self.manager
+        bs = m.block_size
+        B = len(entries)
+        lens = [len(e.tokens) for e in entries]
+        T = sum(lens)
+        if T > self.max_tokens or B > self.max_reqs:
+            raise ValueError(f"step of {T} tokens / {B} requests exceeds the plan buffers "
+                             f"({self.max_tokens} / {self.max_reqs})")
+        cu = np.zeros(B + 1, dtype=np.int32)
+        np.cumsum(lens, out=cu[1:])
+        seq = np.asarray([s + n for s, n in zip(starts, lens)], dtype=np.int32)
+        ids = np.empty(T, dtype=np.int32)
+        pos = np.empty(T, dtype=np.int32)
+        rows: List[int] = []
+        for i, e in enumerate(entries):
+            a, b = cu[i], cu[i + 1]
+            ids[a:b] = np.asarray(e.tokens, dtype=np.int64)
+            pos[a:b] = np.arange(starts[i], starts[i] + lens[i], dtype=np.int32)
+            for w in e.want:
+                if not (0 <= w < lens[i]):
+                    raise ValueError(f"request {e.req_id!r}: wanted place {w} is outside its {lens[i]} tokens")
+                rows.append(int(a) + int(w))
+        width = table_width or max(1, max((int(s) + bs - 1) // bs for s in seq)) if B else 1
+        if width > self.max_blocks:
+            raise ValueError(f"a request needs {width} pages, the plan buffers hold {self.max_blocks}")
+        tables, slots = [], []
+        for g in range(len(m.groups)):
+            tab = np.full((B, width), -1, dtype=np.int32)
+            sl = np.empty(T, dtype=np.int32)
+            for i, e in enumerate(entries):
+                t = m.block_table(e.req_id, g)
+                n = min(len(t), width)
+                tab[i, :n] = t[:n]
+                p = pos[cu[i]:cu[i + 1]]
+                blk = tab[i, p // bs]
+                sl[cu[i]:cu[i + 1]] = np.where(blk >= 0, blk * bs + p % bs, -1)
+            tables.append(tab)
+            slots.append(sl)
+        sslots = np.asarray([m.state_slots.slot(e.req_id) for e in entries], dtype=np.int32)
+        fresh = np.asarray([1 if m.state_slots.take_fresh(e.req_id) else 0 for e in entries], dtype=np.int32)
+        rows_np = np.asarray(rows, dtype=np.int32)
+
+        # pack
+        k = self._turn
+        self._turn = (k + 1) % self.RING
+        if self._events[k] is not None:
+            self._events[k].synchronize()
+        host = self._host[k].numpy()
+        off = 0
+        views = {}
+
+        def put(name, arr):
+            nonlocal off
+            n = arr.size
+            host[off:off + n] = arr.reshape(-1)
+            views[name] = (off, n)
+            off = _align(off + n)
+
+        put("ids", ids); put("pos", pos); put("cu", cu); put("seq", seq)
+        put("rows", rows_np); put("sslots", sslots); put("fresh", fresh)
+        for g in range(len(m.groups)):
+            put(f"tab{g}", tables[g]); put(f"slot{g}", slots[g])
+        dev = self._dev[k]
+        dev[:off].copy_(self._host[k][:off], non_blocking=True)
+        if dev.is_cuda:
+            ev = torch.cuda.Event()
+            ev.record()
+            self._events[k] = ev
+
+        def view(name):
+            o, n = views[name]
+            return dev[o:o + n]
+
+        groups = [CacheGroupView(bs, view(f"tab{g}").view(B, width), view(f"slot{g}"), m.groups[g].window)
+                  for g in range(len(m.groups))]
+        ctx = StepContext(
+            num_tokens=T, num_reqs=B, positions=view("pos"), cu_seqlens=view("cu"), seq_lens=view("seq"),
+            groups=groups, state_slots=view("sslots"), state_fresh=view("fresh"),
+            max_q_len=max(lens) if lens else 0, max_seq_len=int(seq.max()) if B else 0,
+            all_decode=all(n == 1 for n in lens),
+            cu_seqlens_host=cu.tolist(), seq_lens_host=seq.tolist(),
+            state_slots_host=sslots.tolist(), state_fresh_host=fresh.tolist())
+        self.h2d_bytes = off * 4
+        return view("ids"), view("rows"), ctx

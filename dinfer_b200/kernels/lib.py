@@ -1,0 +1,70 @@
+"""Loads the kernel libraries (ctypes) and turns their return codes into exceptions.
+
+There is no fallback: if a library cannot be built or loaded the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict
+
+import torch
+
+from ..csrc import build as _build
+
+
+class KernelError(RuntimeError):
+    """A kernel library refused its arguments or CUDA reported an error."""
+
+
+_LIBS: Dict[str, ctypes.CDLL] = {}
+
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return DTYPE_CODE[dt]
+    except KeyError:
+        raise KernelError(f"dtype {dt} is not one the kernels take (float32, bfloat16)") from None
+
+
+def library(name: str) -> ctypes.CDLL:
+    lib = _LIBS.get(name)
+    if lib is None:
+        path = _build.ensure_built([name])[name]
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load kernel library {path}: {e}") from e
+        lib.dinfer_last_error.restype = ctypes.c_char_p
+        _LIBS[name] = lib
+    return lib
+
+
+def preload(names) -> None:
+    """Build (in parallel) and load several libraries at once."""
+    names = [n for n in names if n not in _LIBS]
+    if names:
+        _build.ensure_built(names)
+        for n in names:
+            library(n)
+
+
+def check(lib: ctypes.CDLL, code: int, what: str) -> None:
+    if code != 0:
+        msg = lib.dinfer_last_error()
+        raise KernelError(f"{what} failed (code {code}): {msg.decode('utf-8', 'replace') if msg else ''}")
+
+
+def stream_handle() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def require_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the kernels run on CUDA tensors only (there is no CPU path)")

@@ -1,0 +1,198 @@
+"""Interfaces of the parts and the registries that map a ``PartSpec.kind`` to its class.
+
+A part is built from ``(spec.params, env)``, declares the tensors it takes, receives them in
+``bind`` and then only sees activations, the step's ``StepContext`` and (a mixer) its cache.
+No part knows which model it is in.
+
+    Mixer           forward(x [T, h], ctx, cache) -> [T, h];  cache_need() says what it keeps
+    FeedForward     forward(x [T, h], ctx) -> [T, h]
+    Norm            forward(residual f32 [T, h], delta | None, rows | None) -> normed [R, h]
+    PositionEncoding  a mixer's helper; see parts/rope.py
+    Block           forward(stream: ResidualStream, ctx, cache) -> None   (arranges the four)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+
+from .spec import PartSpec, TensorDecl
+
+
+# ---------------------------------------------------------------- what a mixer keeps
+
+@dataclass(frozen=True)
+class KvCacheNeed:
+    """Keys and values of every token (``window`` None) or of the last ``window`` tokens."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+    def group_key(self):
+        # layers whose pages live and die together: same span of tokens
+        return ("kv", self.window)
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A per-request state of fixed size (``shape`` elements of ``dtype``), zeroed for a new request."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+# ---------------------------------------------------------------- what a part sees of a step
+
+@dataclass
+class CacheGroupView:
+    """One cache group's view of the step: pages of the requests and the slot of each new token."""
+    block_size: int
+    block_table: torch.Tensor          # [B, max_blocks] int32, -1 where no page is held
+    slot_mapping: torch.Tensor         # [T] int32, block*block_size + offset (-1: not stored)
+    window: Optional[int] = None
+
+
+@dataclass
+class StepContext:
+    """The batch of one step, on the device (and the few numbers the host needs to launch)."""
+    num_tokens: int
+    num_reqs: int
+    positions: torch.Tensor            # [T] int32, absolute position of each token
+    cu_seqlens: torch.Tensor           # [B+1] int32, offsets of the requests' tokens
+    seq_lens: torch.Tensor             # [B] int32, length of each request after this step
+    groups: List[CacheGroupView]
+    state_slots: torch.Tensor          # [B] int32, slot of each request's fixed-size state
+    state_fresh: torch.Tensor          # [B] int32, 1 where the request starts (state must be zeroed)
+    max_q_len: int                     # longest portion in the batch
+    max_seq_len: int                   # longest request after the step
+    all_decode: bool                   # every request brings exactly one token
+    # host copies for parts written in plain torch (tests, toy parts)
+    cu_seqlens_host: Sequence[int] = ()
+    seq_lens_host: Sequence[int] = ()
+    state_slots_host: Sequence[int] = ()
+    state_fresh_host: Sequence[int] = ()
+
+
+@dataclass
+class CacheBinding:
+    """The cache a mixer works on in one schedule entry."""
+    kv: Optional[torch.Tensor] = None      # [num_blocks, 2, Hkv, block_size, D] of this entry
+    group: int = -1                        # index into StepContext.groups
+    write: bool = True                     # False when the entry reads another entry's cache
+    state: Optional[torch.Tensor] = None   # [num_slots, *shape] of this entry
+
+
+@dataclass
+class BuildEnv:
+    """What a part needs to know about the engine it is built into."""
+    device: torch.device
+    act_dtype: torch.dtype             # torch.bfloat16 or torch.float32
+    hidden_size: int
+    max_positions: int
+
+
+# ---------------------------------------------------------------- base classes
+
+class Part:
+    def __init__(self, params: Mapping[str, Any], env: BuildEnv, prefix: str = ""):
+        self.params = dict(params)
+        self.env = env
+        self.prefix = prefix
+
+    def declare(self) -> List[TensorDecl]:
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        pass
+
+    def kernel_libraries(self) -> List[str]:
+        """Names of the kernel libraries the part launches (built before the first step)."""
+        return []
+
+
+class Mixer(Part):
+    def cache_need(self):
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor] = None,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    # True: the q/k post-processing kernel does the whole encoding (a table rotation or nothing);
+    # False: the mixer calls apply(q, k, ctx) between the head norm and the cache write.
+    fused = False
+
+    def fused_table(self) -> Optional[torch.Tensor]:
+        return None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, ctx: "StepContext") -> None:
+        raise NotImplementedError
+
+
+@dataclass
+class ResidualStream:
+    """The 32-bit residual ``x`` and a part's output that has not been added to it yet."""
+    x: torch.Tensor
+    pending: Optional[torch.Tensor] = None
+
+
+class Block:
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, feed_forward: FeedForward, feed_forward_norm: Norm):
+        self.mixer, self.mixer_norm = mixer, mixer_norm
+        self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
+
+    def parts(self) -> List[Part]:
+        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache: CacheBinding) -> None:
+        raise NotImplementedError
+
+
+# ---------------------------------------------------------------- registries
+
+class Registry:
+    def __init__(self, what: str):
+        self.what = what
+        self._items: Dict[str, Any] = {}
+
+    def register(self, kind: str, cls=None, *, replace: bool = False):
+        def put(c):
+            if kind in self._items and not replace:
+                raise ValueError(f"{self.what} {kind!r} is already registered")
+            self._items[kind] = c
+            return c
+        return put if cls is None else put(cls)
+
+    def unregister(self, kind: str) -> None:
+        self._items.pop(kind, None)
+
+    def get(self, kind: str):
+        if kind not in self._items:
+            raise KeyError(f"unknown {self.what} {kind!r} (registered: {', '.join(sorted(self._items))})")
+        return self._items[kind]
+
+    def kinds(self):
+        return sorted(self._items)
+
+
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+BLOCKS = Registry("block")
+
+
+def build_part(registry: Registry, spec: PartSpec, env: BuildEnv, prefix: str) -> Part:
+    return registry.get(spec.kind)(spec.params, env, prefix)

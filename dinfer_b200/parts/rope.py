@@ -1,0 +1,68 @@
+"""Rotary position encoding, neox pairing ``(i, i + rot/2)``.
+
+A position encoding is a helper of a mixer.  Interface:
+  ``fused_table()`` -> the ``[max_positions, rot]`` f32 table ``cos | sin`` when the rotation can be
+                      done inside the q/k post-processing kernel, else None;
+  ``apply(q, k, ctx)`` -> for encodings that are not a table rotation: change the ``[T, heads, D]``
+                      views of q and k in place (called between the head norm and the cache write).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .base import POSITION_ENCODINGS, PositionEncoding
+
+_TABLES: Dict[Tuple, torch.Tensor] = {}
+
+
+def rope_table(rotary_dim: int, theta: float, max_positions: int, device) -> torch.Tensor:
+    """``[p, i] = cos(p f_i)``, ``[p, rot/2 + i] = sin(p f_i)``, ``f_i = theta^(-2i/rot)``: angles in
+    64-bit, stored in 32-bit (crates/layers/src/nn.rs:157-173)."""
+    key = (rotary_dim, float(theta), max_positions, str(device))
+    t = _TABLES.get(key)
+    if t is None:
+        half = rotary_dim // 2
+        i = torch.arange(half, dtype=torch.float64)
+        inv_freq = 1.0 / (float(theta) ** (2.0 * i / rotary_dim))
+        ang = torch.arange(max_positions, dtype=torch.float64)[:, None] * inv_freq[None, :]
+        t = torch.cat([ang.cos(), ang.sin()], dim=1).to(torch.float32).to(device).contiguous()
+        _TABLES[key] = t
+    return t
+
+
+@POSITION_ENCODINGS.register("rope_neox")
+class RotaryNeox(PositionEncoding):
+    """params: ``head_dim``, ``theta``, ``max_positions``, optional ``rotary_dim`` (default: the whole head)."""
+
+    def __init__(self, params, env, prefix=""):
+        super().__init__(params, env, prefix)
+        self.head_dim = int(params["head_dim"])
+        self.rotary_dim = int(params.get("rotary_dim", self.head_dim))
+        self.theta = float(params["theta"])
+        self.max_positions = int(params["max_positions"])
+        if self.rotary_dim % 2 or not (0 < self.rotary_dim <= self.head_dim):
+            raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
+        self._table: Optional[torch.Tensor] = None
+
+    fused = True
+
+    def fused_table(self) -> Optional[torch.Tensor]:
+        if self._table is None:
+            self._table = rope_table(self.rotary_dim, self.theta, self.max_positions, self.env.device)
+        return self._table
+
+    def apply(self, q, k, ctx) -> None:       # the rotation is always fused
+        raise NotImplementedError
+
+
+@POSITION_ENCODINGS.register("none")
+class NoPositionEncoding(PositionEncoding):
+    fused = True
+
+    def fused_table(self):
+        return None
+
+    def apply(self, q, k, ctx) -> None:
+        return None

@@ -1,0 +1,192 @@
+"""Shared pieces of the tests: tiny configurations, model folders in a temporary place, the plain
+oracle's logits, a driver of ``bin/trace_run`` and the ways a set of requests is cut into steps."""
+from __future__ import annotations
+
+import json
+import os
+import random
+import subprocess
+import sys
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(__file__))
+
+import plain_model  # noqa: E402
+
+# Two (and a third) tiny configurations that differ in every size and option.
+TINY_A = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=256, hidden_size=64,
+              intermediate_size=160, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1,
+              head_dim=16, rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=128,
+              tie_word_embeddings=True, attention_bias=False, hidden_act="silu", eos_token_id=7)
+TINY_B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=517, hidden_size=96,
+              intermediate_size=224, num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=2,
+              head_dim=32, rms_norm_eps=1e-5, rope_theta=1000000.0, max_position_embeddings=256,
+              tie_word_embeddings=False, eos_token_id=[3, 5])
+TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=331, hidden_size=120,
+              intermediate_size=200, num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5,
+              head_dim=48, rms_norm_eps=3e-6, rope_theta=50000.0, max_position_embeddings=512,
+              tie_word_embeddings=False)
+# init rules of the tiny models: (seed, std, norm jitter)
+INIT = {"A": (0, 0.05, 0.1), "B": (1, 0.03, 0.2), "C": (2, 0.04, 0.15)}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+
+
+def make_model_dir(path: str, cfg: dict, seed: int, std: float, jitter: float,
+                   dtype: torch.dtype = torch.bfloat16) -> str:
+    from dinfer_b200.weights.random_init import write_random_model
+    return write_random_model(path, cfg, seed, std, jitter, dtype)
+
+
+def load_plain_weights(model_dir: str) -> Dict[str, torch.Tensor]:
+    """Read with the ``safetensors`` package, not with the engine's reader."""
+    from safetensors.torch import load_file
+    return load_file(os.path.join(model_dir, "model.safetensors"))
+
+
+def random_tokens(rng: random.Random, n: int, vocab: int) -> List[int]:
+    return [rng.randrange(vocab) for _ in range(n)]
+
+
+class PlainOracle:
+    """Logits of whole sequences by the plain implementation (64-bit), cached per sequence."""
+
+    def __init__(self, model_dir: str):
+        self.cfg = json.load(open(os.path.join(model_dir, "config.json")))
+        self.W = {k: v.to(torch.float64) for k, v in load_plain_weights(model_dir).items()}
+        self._cache: Dict[Tuple[int, ...], np.ndarray] = {}
+
+    def logits(self, ids: Sequence[int]) -> np.ndarray:
+        key = tuple(ids)
+        if key not in self._cache:
+            self._cache[key] = plain_model.qwen3_logits(self.W, self.cfg, list(ids)).numpy()
+        return self._cache[key]
+
+
+class Replay:
+    """One ``bin/trace_run`` process; ``step`` sends a line, waits for ``done`` and reads the file."""
+
+    def __init__(self, model_dir: str, dtype: str, out_dir: str, max_tokens: int, extra: Sequence[str] = ()):
+        self.out_dir = out_dir
+        os.makedirs(out_dir, exist_ok=True)
+        self.vocab = json.load(open(os.path.join(model_dir, "config.json")))["vocab_size"]
+        self.proc = subprocess.Popen(
+            [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
+             "--out", out_dir, "--max-tokens", str(max_tokens), *extra],
+            stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+        self.n = 0
+
+    def step(self, entries: List[dict], end: Sequence[str] = ()) -> Optional[np.ndarray]:
+        step = self.n
+        self.n += 1
+        self.proc.stdin.write(json.dumps({"step": step, "entries": entries, "end": list(end)}) + "\n")
+        self.proc.stdin.flush()
+        line = self.proc.stdout.readline()
+        if line.strip() != f"done {step}":
+            raise RuntimeError(f"trace_run answered {line!r} to step {step} (exit {self.proc.poll()})")
+        wanted = sum(len(e.get("want", [])) for e in entries)
+        if not wanted:
+            return None
+        a = np.fromfile(os.path.join(self.out_dir, f"{step}.f32"), dtype="<f4")
+        return a.reshape(wanted, self.vocab)
+
+    def close(self) -> int:
+        self.proc.stdin.close()
+        return self.proc.wait(timeout=120)
+
+
+# ---------------------------------------------------------------- cutting requests into steps
+# A schedule is a list of steps; a step is (entries, end) with entries = [(req, lo, hi)] meaning the
+# tokens [lo, hi) of request ``req``.  Every position's logits are asked for.
+
+def schedule_whole(lengths: Dict[str, int]):
+    return [([(r, 0, n)], [r]) for r, n in lengths.items()]
+
+
+def schedule_tail(lengths: Dict[str, int], tail: int = 32):
+    steps = []
+    for r, n in lengths.items():
+        head = max(1, n - tail)
+        steps.append(([(r, 0, head)], [r] if head == n else []))
+        for p in range(head, n):
+            steps.append(([(r, p, p + 1)], [r] if p == n - 1 else []))
+    return steps
+
+
+def schedule_chunks(lengths: Dict[str, int], rng: random.Random, sizes=(2, 3, 5, 8, 13, 2, 17, 4)):
+    steps = []
+    for r, n in lengths.items():
+        p, i = 0, rng.randrange(len(sizes))
+        while p < n:
+            c = min(sizes[i % len(sizes)], n - p)
+            i += 1
+            steps.append(([(r, p, p + c)], [r] if p + c == n else []))
+            p += c
+    return steps
+
+
+def schedule_mixed(lengths: Dict[str, int], rng: random.Random, max_live: int = 4, decode_tail: int = 12):
+    """Up to ``max_live`` requests at a time: prompts in portions of 2..11 tokens beside single
+    decoded tokens of others; a request may sit a step out; a finished one is replaced at once."""
+    waiting = list(lengths)
+    live: Dict[str, int] = {}
+    steps = []
+    while waiting or live:
+        while waiting and len(live) < max_live:
+            live[waiting.pop(0)] = 0
+        entries, end = [], []
+        for r in list(live):
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                      # left out of this step, goes on later
+            p, n = live[r], lengths[r]
+            c = 1 if n - p <= decode_tail else min(rng.randrange(2, 12), n - p - decode_tail)
+            entries.append((r, p, p + c))
+            live[r] = p + c
+            if p + c == n:
+                end.append(r)
+                del live[r]
+        if entries:
+            steps.append((entries, end))
+    return steps
+
+
+def max_live_tokens(steps, round_to: int = 64) -> int:
+    """Most tokens live requests hold at any time, each rounded up to ``round_to``."""
+    held: Dict[str, int] = {}
+    worst = 0
+    for entries, end in steps:
+        for r, lo, hi in entries:
+            held[r] = hi
+        worst = max(worst, sum((v + round_to - 1) // round_to * round_to for v in held.values()))
+        for r in end:
+            held.pop(r, None)
+    return worst
+
+
+def run_schedule(replay: Replay, steps, tokens: Dict[str, List[int]], tag: str = ""):
+    """Replays the steps; returns {req: [n, V] logits} assembled from the steps' outputs."""
+    got = {r: np.full((len(t), replay.vocab), np.nan, dtype=np.float32) for r, t in tokens.items()}
+    for entries, end in steps:
+        ents = [{"id": tag + r, "tokens": tokens[r][lo:hi], "want": list(range(hi - lo))} for r, lo, hi in entries]
+        out = replay.step(ents, [tag + r for r in end])
+        o = 0
+        for r, lo, hi in entries:
+            got[r][lo:hi] = out[o:o + hi - lo]
+            o += hi - lo
+    return got
+
+
+def rel_err(got: np.ndarray, want: np.ndarray) -> float:
+    """Largest difference over the largest magnitude of the expected logits."""
+    if not np.isfinite(got).all():
+        return float("inf")
+    return float(np.abs(got.astype(np.float64) - want).max() / np.abs(want).max())
+
+
+# one tolerance per dtype, fixed before the first run
+TOLERANCE = {"float32": 1e-4, "bfloat16": 2e-2}

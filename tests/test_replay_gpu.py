@@ -1,0 +1,63 @@
+"""Trace replay against the plain implementation: each request whole; most of it in one step and
+the last 32 tokens one by one; in portions of changing size down to two tokens; and mixed, up to
+four live requests with so few pages that they are used again.  In 32-bit and in bfloat16, on
+tiny configurations that differ in every size."""
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {
+    "A": {"a": 1, "b": 7, "c": 19, "d": 64, "e": 97, "f": 128},
+    "B": {"a": 3, "b": 16, "c": 17, "d": 40, "e": 63, "f": 150, "g": 255},
+    "C": {"a": 2, "b": 33, "c": 129, "d": 200},
+}
+
+
+@pytest.fixture(scope="module")
+def model_dirs(tmp_path_factory):
+    out = {}
+    for name, cfg in H.CONFIGS.items():
+        seed, std, jit = H.INIT[name]
+        for dt, tdt in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
+            d = tmp_path_factory.mktemp(f"tiny{name}_{dt}")
+            out[(name, dt)] = H.make_model_dir(str(d), cfg, seed, std, jit, tdt)
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_replay_all_ways(model_dirs, tmp_path, name, dtype):
+    model_dir = model_dirs[(name, dtype)]
+    cfg = H.CONFIGS[name]
+    rng = random.Random(1234 + ord(name))
+    tokens = {r: H.random_tokens(rng, n, cfg["vocab_size"]) for r, n in LENGTHS[name].items()}
+    oracle = H.PlainOracle(model_dir)
+    want = {r: oracle.logits(t) for r, t in tokens.items()}
+    lengths = LENGTHS[name]
+    schedules = {
+        "whole": H.schedule_whole(lengths),
+        "tail32": H.schedule_tail(lengths, 32),
+        "chunks": H.schedule_chunks(lengths, rng),
+        "mixed": H.schedule_mixed(lengths, rng),
+        "mixed2": H.schedule_mixed(dict(reversed(list(lengths.items()))), rng, max_live=3, decode_tail=33),
+    }
+    # the pool holds just what the most demanding schedule needs, so pages are used again
+    max_tokens = max(H.max_live_tokens(s) for s in schedules.values())
+    rp = H.Replay(model_dir, dtype, str(tmp_path / "out"), max_tokens)
+    worst = {}
+    try:
+        for sname, steps in schedules.items():
+            got = H.run_schedule(rp, steps, tokens, tag=sname + "/")
+            worst[sname] = max(H.rel_err(got[r], want[r]) for r in tokens)
+    finally:
+        assert rp.close() == 0
+    print(name, dtype, worst)
+    tol = H.TOLERANCE[dtype]
+    bad = {k: v for k, v in worst.items() if not v <= tol}
+    assert not bad, f"{name} {dtype}: relative error above {tol}: {bad} (all: {worst})"
