@@ -32,6 +32,7 @@ LIBRARIES: Dict[str, tuple] = {
     "qk_post": ("qk_post.cu", []),
     "attention_generic": ("attention_generic.cu", []),
     "gemm_f32": ("gemm_f32.cu", []),
+    "sampling": ("sampling.cu", []),
 }
 
 

@@ -1,0 +1,133 @@
+"""Command line, in the manner of the reference's ``dinfer`` binary (bins/dinfer/src/main.rs:28-151):
+sub-commands, and for the engine options the reference's own flag names and defaults
+(``--model --max-model-len --max-num-seqs --max-num-batched-tokens --num-blocks --block-size
+--gpu-memory-utilization --no-cuda-graph --no-decode-exempt --long-prefill-token-threshold
+--device``).  The reference serves HTTP; this engine starts at token ids, so ``generate`` takes the
+place of ``serve``:
+
+    dinfer generate --model DIR --prompt-ids 1,2,3 --prompt-ids 4,5 --max-tokens 16 --temperature 0
+    dinfer random-model --config config.json --out DIR --seed 0
+    dinfer device-info
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from typing import List
+
+
+def _engine_flags(p: argparse.ArgumentParser) -> None:
+    p.add_argument("--model", required=True, help="model folder (config.json + safetensors)")
+    p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    p.add_argument("--max-model-len", type=int, default=4096)
+    p.add_argument("--max-num-seqs", type=int, default=16)
+    p.add_argument("--max-num-batched-tokens", type=int, default=2048)
+    p.add_argument("--num-blocks", type=int, default=None, help="cache pages; default: from free device memory")
+    p.add_argument("--block-size", type=int, default=16)
+    p.add_argument("--gpu-memory-utilization", type=float, default=0.9)
+    p.add_argument("--no-decode-exempt", action="store_true",
+                   help="decoded tokens count against the token budget")
+    p.add_argument("--long-prefill-token-threshold", type=int, default=0)
+    p.add_argument("--no-cuda-graph", action="store_true")
+    p.add_argument("--device", type=int, default=0)
+
+
+def _ids(text: str) -> List[int]:
+    return [int(x) for x in text.replace(",", " ").split()]
+
+
+def cmd_generate(a) -> int:
+    from .. import LLM, SamplingParams
+    prompts = [_ids(t) for t in (a.prompt_ids or [])]
+    if a.prompt_file:
+        with open(a.prompt_file) as f:
+            for line in f:
+                line = line.strip()
+                if line:
+                    prompts.append(json.loads(line) if line.startswith("[") else _ids(line))
+    if not prompts:
+        print("no prompt given (--prompt-ids or --prompt-file)", file=sys.stderr)
+        return 2
+    llm = LLM(a.model, dtype=a.dtype, max_model_len=a.max_model_len, max_num_seqs=a.max_num_seqs,
+              max_num_batched_tokens=a.max_num_batched_tokens, num_blocks=a.num_blocks,
+              block_size=a.block_size, gpu_memory_utilization=a.gpu_memory_utilization,
+              decode_exempt_from_budget=not a.no_decode_exempt,
+              long_prefill_token_threshold=a.long_prefill_token_threshold,
+              enable_cuda_graph=not a.no_cuda_graph, device=a.device)
+    sp = SamplingParams(max_tokens=a.max_tokens, min_tokens=a.min_tokens, temperature=a.temperature,
+                        top_p=a.top_p, top_k=a.top_k, min_p=a.min_p,
+                        repetition_penalty=a.repetition_penalty, frequency_penalty=a.frequency_penalty,
+                        presence_penalty=a.presence_penalty, seed=a.seed,
+                        stop_token_ids=_ids(a.stop_token_ids) if a.stop_token_ids else [],
+                        ignore_eos=a.ignore_eos)
+    for o in llm.generate(prompts, sp):
+        print(json.dumps({"id": o.req_id, "output_ids": o.output_ids, "finish_reason": o.finish_reason}))
+    s = llm.stats
+    print(f"steps {s.steps}  prompt tokens {s.prompt_tokens}  generated {s.generated_tokens}  "
+          f"preemptions {s.preemptions}", file=sys.stderr)
+    return 0
+
+
+def cmd_random_model(a) -> int:
+    import torch
+    from ..weights.random_init import write_random_model
+    with open(a.config) as f:
+        cfg = json.load(f)
+    dt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[a.dtype]
+    write_random_model(a.out, cfg, a.seed, a.std, a.norm_jitter, dt)
+    print(a.out)
+    return 0
+
+
+def cmd_device_info(a) -> int:
+    import torch
+    if not torch.cuda.is_available():
+        print("no CUDA device")
+        return 1
+    for i in range(torch.cuda.device_count()):
+        p = torch.cuda.get_device_properties(i)
+        free, total = torch.cuda.mem_get_info(i)
+        print(json.dumps({"index": i, "name": p.name, "compute_capability": f"{p.major}.{p.minor}",
+                          "multiprocessors": p.multi_processor_count, "memory_total": total,
+                          "memory_free": free}))
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="dinfer", description=__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("generate", help="generate tokens for prompts given as token ids")
+    _engine_flags(g)
+    g.add_argument("--prompt-ids", action="append", help="comma separated token ids; may repeat")
+    g.add_argument("--prompt-file", help="one prompt a line: JSON list or separated ids")
+    g.add_argument("--max-tokens", type=int, default=256)
+    g.add_argument("--min-tokens", type=int, default=0)
+    g.add_argument("--temperature", type=float, default=1.0)
+    g.add_argument("--top-p", type=float, default=1.0)
+    g.add_argument("--top-k", type=int, default=-1)
+    g.add_argument("--min-p", type=float, default=0.0)
+    g.add_argument("--repetition-penalty", type=float, default=1.0)
+    g.add_argument("--frequency-penalty", type=float, default=0.0)
+    g.add_argument("--presence-penalty", type=float, default=0.0)
+    g.add_argument("--seed", type=int, default=None)
+    g.add_argument("--stop-token-ids", default="")
+    g.add_argument("--ignore-eos", action="store_true")
+    g.set_defaults(fn=cmd_generate)
+    r = sub.add_parser("random-model", help="write a model folder with random weights")
+    r.add_argument("--config", required=True, help="a config.json")
+    r.add_argument("--out", required=True)
+    r.add_argument("--seed", type=int, default=0)
+    r.add_argument("--std", type=float, default=0.02)
+    r.add_argument("--norm-jitter", type=float, default=0.0)
+    r.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    r.set_defaults(fn=cmd_random_model)
+    d = sub.add_parser("device-info", help="list the CUDA devices")
+    d.set_defaults(fn=cmd_device_info)
+    a = ap.parse_args(argv)
+    return a.fn(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

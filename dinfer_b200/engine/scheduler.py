@@ -1,0 +1,189 @@
+"""Continuous batching above the step function.
+
+Every step: running requests first, then waiting ones while the token budget, ``max_num_seqs`` and
+the pages last.  A prompt longer than the budget is cut into portions; a request whose known tokens
+are all in the cache decodes one token a step.  When pages run out the LAST running request is
+preempted: its pages go back, it returns to the FRONT of the waiting queue and is recomputed from
+token 0 later; a request never preempts itself while others run (it sits the step out), and a
+request that alone does not fit is finished with ``length``.  Nothing is admitted in a step that
+preempted.  This is the policy of the reference's scheduler (crates/core/src/sched/mod.rs:318-644
+for schedule, :646-680 for the bookkeeping after it and preemption, :687-828 for the update and
+the stop check), without its asynchronous placeholders, speculative tokens and prefix cache.
+
+Pure host code: it owns the queues and asks the cache manager for pages; it never touches the GPU.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+
+from ..cache.manager import CacheManager
+from ..config.engine_config import EngineConfig
+from .request import FinishReason, Request, RequestStatus
+
+
+@dataclass
+class ScheduledRequest:
+    request: Request
+    start: int            # tokens already in the cache
+    num_tokens: int       # tokens run in this step
+    samples: bool         # the step's last row yields the request's next token
+
+
+@dataclass
+class SchedulerOutput:
+    scheduled: List[ScheduledRequest] = field(default_factory=list)
+    preempted: List[Request] = field(default_factory=list)
+    finished: List[Request] = field(default_factory=list)     # finished by the scheduler itself (no fit)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(s.num_tokens for s in self.scheduled)
+
+
+class Scheduler:
+    def __init__(self, config: EngineConfig, manager: CacheManager, eos_token_ids: Sequence[int] = ()):
+        self.config = config
+        self.manager = manager
+        self.eos = set(int(x) for x in eos_token_ids)
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []
+        self.num_preemptions = 0
+
+    # ---- queue
+    def add_request(self, req: Request) -> None:
+        req.params.validate()
+        if not req.prompt_ids:
+            raise ValueError(f"request {req.req_id!r}: empty prompt")
+        if len(req.prompt_ids) >= self.config.max_model_len:
+            raise ValueError(f"request {req.req_id!r}: prompt of {len(req.prompt_ids)} tokens leaves no room "
+                             f"under max_model_len {self.config.max_model_len}")
+        bs = self.manager.block_size
+        need = (len(req.prompt_ids) + 1 + bs - 1) // bs
+        if any(need > p.num_blocks for p in self.manager.pools):
+            raise ValueError(f"request {req.req_id!r}: needs {need} pages, the pool has "
+                             f"{min(p.num_blocks for p in self.manager.pools)}")
+        req.status = RequestStatus.WAITING
+        self.waiting.append(req)
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def abort(self, req_id: Hashable) -> Optional[Request]:
+        for q in (self.running, self.waiting):
+            for r in list(q):
+                if r.req_id == req_id:
+                    q.remove(r)
+                    self._finish(r, FinishReason.ABORT)
+                    return r
+        return None
+
+    # ---- one step's decisions
+    def schedule(self) -> SchedulerOutput:
+        cfg = self.config
+        out = SchedulerOutput()
+        budget = cfg.max_num_batched_tokens
+        threshold = cfg.long_prefill_token_threshold
+        i = 0
+        while i < len(self.running):
+            req = self.running[i]
+            num_new = req.num_tokens - req.num_computed
+            is_decode = num_new == 1 and req.num_computed > 0
+            if threshold > 0:
+                num_new = min(num_new, threshold)
+            if not (is_decode and cfg.decode_exempt_from_budget):
+                num_new = min(num_new, budget)
+            num_new = min(num_new, cfg.max_model_len - req.num_computed)
+            if num_new <= 0:
+                i += 1
+                continue
+            placed = True
+            while not self.manager.allocate(req.req_id, req.num_computed + num_new):
+                victim = self.running[-1]
+                if victim is req:
+                    if len(self.running) > 1:
+                        placed = False          # others run: sit this step out, keep the pages
+                    else:
+                        self.running.pop()      # alone and still no fit: it can never finish
+                        self._finish(req, FinishReason.LENGTH)
+                        out.finished.append(req)
+                        placed = False
+                    break
+                self.running.pop()
+                self._preempt(victim)
+                out.preempted.append(victim)
+            if not placed:
+                if req.finished:
+                    continue
+                i += 1
+                continue
+            out.scheduled.append(ScheduledRequest(req, req.num_computed, num_new,
+                                                  req.num_computed + num_new == req.num_tokens))
+            if not (is_decode and cfg.decode_exempt_from_budget):
+                budget -= num_new
+            i += 1
+
+        if not out.preempted:
+            while self.waiting and budget > 0 and len(self.running) < cfg.max_num_seqs:
+                req = self.waiting[0]
+                num_new = req.num_tokens - req.num_computed
+                if threshold > 0:
+                    num_new = min(num_new, threshold)
+                num_new = min(num_new, budget, cfg.max_model_len - req.num_computed)
+                if num_new <= 0 or not self.manager.allocate(req.req_id, req.num_computed + num_new):
+                    break
+                self.waiting.popleft()
+                req.status = RequestStatus.RUNNING
+                self.running.append(req)
+                out.scheduled.append(ScheduledRequest(req, req.num_computed, num_new,
+                                                      req.num_computed + num_new == req.num_tokens))
+                budget -= num_new
+
+        for s in out.scheduled:                 # the cache will hold these once the step has run
+            s.request.num_computed += s.num_tokens
+        return out
+
+    def _preempt(self, req: Request) -> None:
+        if req.req_id in self.manager:
+            self.manager.free(req.req_id)
+        req.num_computed = 0
+        req.status = RequestStatus.WAITING
+        req.num_preemptions += 1
+        self.num_preemptions += 1
+        self.waiting.appendleft(req)
+
+    def _finish(self, req: Request, reason: FinishReason) -> None:
+        req.status = RequestStatus.FINISHED
+        req.finish_reason = reason
+        if req.req_id in self.manager:
+            self.manager.free(req.req_id)
+
+    # ---- after the step
+    def update(self, step: SchedulerOutput, sampled: Dict[Hashable, int]) -> List[Request]:
+        """Append the sampled tokens, check the stop conditions, free what has finished."""
+        done = []
+        for s in step.scheduled:
+            req = s.request
+            if not s.samples or req.finished or req.status != RequestStatus.RUNNING:
+                continue
+            tok = int(sampled[req.req_id])
+            req.output_ids.append(tok)
+            reason = self._check_stop(req, tok)
+            if reason is not None:
+                self.running.remove(req)
+                self._finish(req, reason)
+                done.append(req)
+        return done
+
+    def _check_stop(self, req: Request, tok: int) -> Optional[FinishReason]:
+        p = req.params
+        n_out = len(req.output_ids)
+        if n_out >= p.min_tokens:
+            if not p.ignore_eos and tok in self.eos:
+                return FinishReason.STOP
+            if tok in p.stop_token_ids:
+                return FinishReason.STOP
+        if n_out >= p.max_tokens or req.num_tokens >= self.config.max_model_len:
+            return FinishReason.LENGTH
+        return None

@@ -50,7 +50,23 @@ def preload(names) -> None:
             library(n)
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernel launches so far: calls into the kernel libraries, library matrix products, and for a
+    replayed CUDA graph the launches it captured."""
+    return _launches
+
+
+def add_launches(n: int = 1) -> None:
+    global _launches
+    _launches += n
+
+
 def check(lib: ctypes.CDLL, code: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if code != 0:
         msg = lib.dinfer_last_error()
         raise KernelError(f"{what} failed (code {code}): {msg.decode('utf-8', 'replace') if msg else ''}")

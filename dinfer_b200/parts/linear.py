@@ -15,6 +15,7 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
+from ..kernels.lib import add_launches
 
 
 class Linear:
@@ -36,6 +37,7 @@ class Linear:
         if x.dtype == torch.float32 or w.dtype == torch.float32:
             return ops.gemm_f32(x, w, out)
         # bfloat16 x bfloat16, f32 accumulation
+        add_launches(1)
         if out.dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)
         else:

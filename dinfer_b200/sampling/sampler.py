@@ -1,0 +1,108 @@
+"""From logits rows to token ids, on the device.
+
+One row per request that samples in this step.  All-greedy batches take the argmax kernel; anything
+else goes through penalties (if any row has them) and the fused temperature / min_p / top-k / top-p
+/ Philox inverse-CDF kernel (order as in models/qwen3/src/executor.rs:534-605).  The random number of
+a row depends only on the request's seed and on how many tokens it has produced
+(crates/core/src/sampler.rs:84,183-191), never on its place in the batch.
+"""
+from __future__ import annotations
+
+from ctypes import c_int, c_int64, c_void_p
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..kernels.lib import check, ptr, stream_handle
+from ..kernels.ops import _fn
+from .params import SamplingParams
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise ValueError("argmax: logits must be float32 with a contiguous last axis")
+    if out is None:
+        out = torch.empty(R, dtype=torch.int32, device=logits.device)
+    lib, f = _fn("sampling", "dinfer_argmax", [c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p])
+    check(lib, f(ptr(logits), logits.stride(0), ptr(out), R, V, stream_handle()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor, offsets: torch.Tensor,
+           top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
+           min_p: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """temperature/top_p/min_p float32 [R], top_k int32 [R], seeds/offsets int64 [R] (bit patterns of uint64)."""
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise ValueError("sample: logits must be float32 with a contiguous last axis")
+    if out is None:
+        out = torch.empty(R, dtype=torch.int32, device=logits.device)
+    lib, f = _fn("sampling", "dinfer_sample",
+                 [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_int, c_int, c_void_p])
+    check(lib, f(ptr(logits), logits.stride(0), ptr(temperature), ptr(top_k), ptr(top_p), ptr(min_p),
+                 ptr(seeds), ptr(offsets), ptr(out), R, V, stream_handle()), "sample")
+    return out
+
+
+def apply_penalties(logits: torch.Tensor, ids: torch.Tensor, offsets: torch.Tensor, prompt_len: torch.Tensor,
+                    rep: torch.Tensor, freq: torch.Tensor, pres: torch.Tensor) -> torch.Tensor:
+    """In place on ``logits``; history of row b is ids[offsets[b]:offsets[b+1]], prompt first."""
+    R, V = logits.shape
+    lib, f = _fn("sampling", "dinfer_penalties",
+                 [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                  c_void_p])
+    check(lib, f(ptr(logits), logits.stride(0), ptr(ids), ptr(offsets), ptr(prompt_len), ptr(rep), ptr(freq),
+                 ptr(pres), R, V, stream_handle()), "penalties")
+    return logits
+
+
+def _u64(x: int) -> int:
+    x &= 0xFFFFFFFFFFFFFFFF
+    return x - (1 << 64) if x >= (1 << 63) else x
+
+
+class Sampler:
+    """Builds the per-row columns on the host, uploads them in one copy and launches the kernels."""
+
+    def __init__(self, device):
+        self.device = device
+
+    def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+                 num_generated: Sequence[int], histories: Optional[Sequence[tuple]] = None) -> torch.Tensor:
+        """``histories[i] = (prompt_ids, output_ids)`` is needed only for rows with penalties.
+        Returns int32 [R] on the device."""
+        R = logits.shape[0]
+        if all(p.is_greedy and not p.has_penalties for p in params):
+            return argmax(logits)
+        if any(p.has_penalties for p in params):
+            logits = logits.clone()
+            flat: List[int] = []
+            offs, plen = [0], []
+            for i, p in enumerate(params):
+                pr, ou = histories[i] if (histories and p.has_penalties) else ((), ())
+                flat.extend(pr)
+                flat.extend(ou)
+                offs.append(len(flat))
+                plen.append(len(pr))
+            dev = self.device
+            apply_penalties(
+                logits, torch.tensor(flat or [0], dtype=torch.int32, device=dev),
+                torch.tensor(offs, dtype=torch.int32, device=dev), torch.tensor(plen, dtype=torch.int32, device=dev),
+                torch.tensor([p.repetition_penalty for p in params], dtype=torch.float32, device=dev),
+                torch.tensor([p.frequency_penalty for p in params], dtype=torch.float32, device=dev),
+                torch.tensor([p.presence_penalty for p in params], dtype=torch.float32, device=dev))
+        f32 = np.empty((3, R), dtype=np.float32)
+        i64 = np.empty((2, R), dtype=np.int64)
+        i32 = np.empty(R, dtype=np.int32)
+        for i, p in enumerate(params):
+            f32[0, i], f32[1, i], f32[2, i] = p.temperature, p.top_p, p.min_p
+            i32[i] = p.top_k
+            i64[0, i], i64[1, i] = _u64(seeds[i]), _u64(num_generated[i])
+        dev = self.device
+        f32d = torch.from_numpy(f32).to(dev, non_blocking=True)
+        i64d = torch.from_numpy(i64).to(dev, non_blocking=True)
+        i32d = torch.from_numpy(i32).to(dev, non_blocking=True)
+        return sample(logits, f32d[0], i64d[0], i64d[1], top_k=i32d, top_p=f32d[1], min_p=f32d[2])

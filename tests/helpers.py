@@ -190,3 +190,31 @@ def rel_err(got: np.ndarray, want: np.ndarray) -> float:
 
 # one tolerance per dtype, fixed before the first run
 TOLERANCE = {"float32": 1e-4, "bfloat16": 2e-2}
+
+
+class LocalReplay:
+    """The same ``step`` interface as ``Replay`` on a ModelRunner of this process (for architectures
+    that exist only in the test that registers them)."""
+
+    def __init__(self, model_dir: str, dtype: str, max_tokens: int, block_size: int = 16):
+        from dinfer_b200.config.engine_config import EngineConfig
+        from dinfer_b200.engine.runner import ModelRunner
+        cfg = json.load(open(os.path.join(model_dir, "config.json")))
+        self.vocab = cfg["vocab_size"]
+        n = (max_tokens + 63) // 64 * 64
+        self.runner = ModelRunner.from_dir(model_dir, EngineConfig(
+            max_model_len=min(n, cfg.get("max_position_embeddings", cfg.get("max_positions", n))), max_num_seqs=16,
+            max_num_batched_tokens=n, num_blocks=n // block_size, block_size=block_size, dtype=dtype,
+            enable_cuda_graph=False))
+
+    def step(self, entries: List[dict], end: Sequence[str] = ()) -> Optional[np.ndarray]:
+        from dinfer_b200.engine.batch import StepEntry
+        out = self.runner.step([StepEntry(e["id"], e["tokens"], e.get("want", [])) for e in entries])
+        for r in end:
+            self.runner.finish(r)
+        return out.cpu().numpy() if out.shape[0] else None
+
+    def close(self) -> int:
+        self.runner.manager.check_invariants()
+        assert not self.runner.manager.requests()
+        return 0

@@ -186,21 +186,21 @@ def sample_token(logits: torch.Tensor, temperature: float, seed: int, offset: in
     if temperature <= 1e-5:
         return int(torch.argmax(x))
     x = x / temperature
-    probs = torch.softmax(x, dim=-1)
-    keep = torch.ones_like(probs, dtype=torch.bool)
+    neg = torch.full_like(x, float("-inf"))
     if min_p > 0.0:
-        keep &= probs >= min_p * probs.max()
-    if top_k > 0:
-        kth = torch.topk(x, min(top_k, x.numel())).values[-1]
-        keep &= x >= kth
+        probs = torch.softmax(x, dim=-1)
+        x = torch.where(probs >= min_p * probs.max(), x, neg)
+    if 0 < top_k < x.numel():
+        kth = torch.topk(x, top_k).values[-1]
+        x = torch.where(x >= kth, x, neg)
     if top_p < 1.0:
+        probs = torch.softmax(x, dim=-1)          # over what min_p and top-k left
         sp, si = torch.sort(probs, descending=True)
         before = torch.cumsum(sp, 0) - sp
-        kept_sorted = before < top_p
-        m = torch.zeros_like(keep)
-        m[si[kept_sorted]] = True
-        keep &= m
-    w = torch.where(keep, torch.exp(x - x.max()), torch.zeros_like(x))
+        keep = torch.zeros_like(x, dtype=torch.bool)
+        keep[si[before < top_p]] = True
+        x = torch.where(keep, x, neg)
+    w = torch.exp(x - x.max())
     target = philox_uniform(seed, offset) * float(w.sum())
     cum = torch.cumsum(w, 0)
     hit = torch.nonzero((cum >= target) & (w > 0))

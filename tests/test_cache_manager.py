@@ -1,0 +1,120 @@
+"""The cache manager: no page lost, held twice or freed twice, under random orders of requests;
+windows give pages back; state slots (no GPU)."""
+import random
+
+import pytest
+
+from dinfer_b200.cache.block_pool import BlockPool, PoolError, StateSlots
+from dinfer_b200.cache.manager import CacheManager, GroupSpec
+
+
+def test_pool_reuses_freed_pages_first():
+    p = BlockPool(4)
+    a = p.allocate(3)
+    assert a == [0, 1, 2] and p.num_free == 1
+    p.free([1])
+    assert p.allocate(1) == [1]                 # the page just freed is used again at once
+    with pytest.raises(PoolError):
+        p.allocate(2)
+    p.free([0])
+    with pytest.raises(PoolError, match="not held"):
+        p.free([0])
+    with pytest.raises(PoolError, match="not of this pool"):
+        p.free([9])
+
+
+def test_allocate_is_incremental_and_all_or_nothing():
+    m = CacheManager([GroupSpec()], block_size=4, num_blocks=5, max_num_seqs=4)
+    assert m.allocate("a", 5) and m.block_table("a", 0) == [0, 1]
+    assert m.allocate("a", 8) and m.block_table("a", 0) == [0, 1]        # still covered: nothing new
+    assert m.allocate("a", 9) and len(m.block_table("a", 0)) == 3
+    assert not m.allocate("b", 12)                                       # needs 3, 2 free
+    assert "b" not in m and m.num_free_blocks() == 2                     # state untouched
+    m.check_invariants()
+    assert m.allocate("b", 8)
+    m.free("a")
+    assert m.num_free_blocks() == 3
+    with pytest.raises(PoolError):
+        m.free("a")
+    m.check_invariants()
+
+
+def test_window_group_gives_pages_back():
+    m = CacheManager([GroupSpec(), GroupSpec(window=6)], block_size=4, num_blocks=[16, 16], max_num_seqs=2)
+    assert m.allocate("a", 20)
+    assert len(m.block_table("a", 0)) == 5 and len(m.block_table("a", 1)) == 5
+    m.advance("a", 20)           # next query at 20 sees keys >= 15: blocks 0..2 (positions < 12) are passed
+    assert m.block_table("a", 1)[:3] == [-1, -1, -1] and all(b >= 0 for b in m.block_table("a", 1)[3:])
+    assert all(b >= 0 for b in m.block_table("a", 0))
+    assert m.num_free_blocks(1) == 16 - 2
+    m.check_invariants()
+    assert m.allocate("a", 21)
+    assert len(m.block_table("a", 1)) == 6
+    m.advance("a", 21)
+    m.free("a")
+    assert m.num_free_blocks(0) == 16 and m.num_free_blocks(1) == 16
+    m.check_invariants()
+
+
+def test_groups_fail_together():
+    m = CacheManager([GroupSpec(), GroupSpec(window=4)], block_size=4, num_blocks=[8, 2], max_num_seqs=2)
+    assert not m.allocate("a", 12)              # the window group has only 2 pages
+    assert m.num_free_blocks(0) == 8 and m.num_free_blocks(1) == 2 and "a" not in m
+    assert m.state_slots.num_free == 2
+
+
+def test_state_slots():
+    s = StateSlots(2)
+    assert s.acquire("a") == 0 and s.acquire("a") == 0
+    assert s.take_fresh("a") is True and s.take_fresh("a") is False
+    assert s.acquire("b") == 1 and s.acquire("c") is None
+    s.release("a")
+    assert s.acquire("c") == 0 and s.take_fresh("c") is True     # a reused slot is fresh again
+    m = CacheManager([GroupSpec()], 4, 8, max_num_seqs=1)
+    assert m.allocate("a", 1) and not m.allocate("b", 1)         # no slot for a second request
+    m.free("a")
+    assert m.allocate("b", 1)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders(seed):
+    rng = random.Random(seed)
+    groups = [GroupSpec(), GroupSpec(window=rng.choice([3, 7, 16]))] if seed % 2 else [GroupSpec()]
+    bs = rng.choice([1, 4, 16])
+    m = CacheManager(groups, bs, [rng.randrange(8, 40) for _ in groups], max_num_seqs=5)
+    live = {}
+    next_id = 0
+    for _ in range(600):
+        op = rng.random()
+        if op < 0.25 and len(live) < 7:
+            live[next_id] = 0
+            next_id += 1
+        elif op < 0.85 and live:
+            r = rng.choice(list(live))
+            grow = rng.choice([1, 1, 1, 2, 5, 17])
+            before = [m.num_free_blocks(g) for g in range(len(groups))]
+            ok = m.allocate(r, live[r] + grow)
+            if ok:
+                live[r] += grow
+                m.advance(r, live[r])
+                for g in range(len(groups)):          # every position a query may still see has a page
+                    t = m.block_table(r, g)
+                    w = groups[g].window
+                    first = 0 if w is None else max(0, live[r] - w + 1)
+                    assert all(t[p // bs] >= 0 for p in range(first, live[r]))
+            else:
+                assert [m.num_free_blocks(g) for g in range(len(groups))] == before
+                if r not in m:
+                    del live[r]
+        elif live:
+            r = rng.choice(list(live))
+            if r in m:
+                m.free(r)
+            del live[r]
+        m.check_invariants()
+    for r in list(live):
+        if r in m:
+            m.free(r)
+    m.check_invariants()
+    assert all(m.num_free_blocks(g) == m.pools[g].num_blocks for g in range(len(groups)))
+    assert m.state_slots.num_free == 5

@@ -1,0 +1,157 @@
+"""The engine through its Python entry point: greedy and sampled generation against the plain
+implementation, long decoding, the first tokens, preemption under a small pool, and the BASELINE
+workloads of the two tiny configurations."""
+import random
+
+import pytest
+import torch
+
+import helpers as H
+import plain_model as P
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dirs(tmp_path_factory):
+    out = {}
+    for name in ("A", "B"):
+        d = tmp_path_factory.mktemp(f"gen{name}")
+        out[name] = H.make_model_dir(str(d), H.CONFIGS[name], *H.INIT[name], torch.float32)
+    return out
+
+
+def plain_sampled(W, cfg, prompt, n, temperature, seed, **kw):
+    seq, out = list(prompt), []
+    for i in range(n):
+        logits = P.qwen3_logits(W, cfg, seq)[-1]
+        tok = P.sample_token(logits, temperature, seed, i, **kw)
+        out.append(tok)
+        seq.append(tok)
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_tiny_a(dirs, dtype):
+    """Tiny A's workload: prompts of 1, 7 and 19 tokens, greedy, 12 tokens each, pages of 4 tokens."""
+    from dinfer_b200 import LLM, SamplingParams
+    cfg = H.TINY_A
+    rng = random.Random(0)
+    prompts = [H.random_tokens(rng, n, cfg["vocab_size"]) for n in (1, 7, 19)]
+    W = H.load_plain_weights(dirs["A"])
+    llm = LLM(dirs["A"], dtype=dtype, max_model_len=64, max_num_seqs=4, max_num_batched_tokens=16,
+              num_blocks=40, block_size=4, enable_cuda_graph=False)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        want = P.greedy_generate(W, cfg, p, 12)
+        assert o.finish_reason == "length" and len(o.output_ids) == 12
+        if dtype == "float32":
+            assert o.output_ids == want
+        else:   # bfloat16 may leave the path at a near-tie; up to there the tokens are the same
+            same = sum(1 for a, b in zip(o.output_ids, want) if a == b)
+            first_diff = next((i for i, (a, b) in enumerate(zip(o.output_ids, want)) if a != b), 12)
+            if first_diff < 12:
+                lg = P.qwen3_logits(W, cfg, p + want[:first_diff])[-1]
+                top = torch.topk(lg, 2).values
+                assert float(top[0] - top[1]) < 0.05 * float(lg.abs().max()), (first_diff, same)
+    assert llm.runner.manager.num_free_blocks() == 40
+
+
+def test_sampled_generation_tiny_b(dirs):
+    """Tiny B's workload: prompts of 3, 16, 17, 40, 63 tokens, portions of 8 mixed with decodes,
+    20 tokens each at temperature 0.8 with sampling seed 7; 32-bit so that the draws are the same."""
+    from dinfer_b200 import LLM, SamplingParams
+    cfg = H.TINY_B
+    rng = random.Random(1)
+    prompts = [H.random_tokens(rng, n, cfg["vocab_size"]) for n in (3, 16, 17, 40, 63)]
+    W = H.load_plain_weights(dirs["B"])
+    llm = LLM(dirs["B"], dtype="float32", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=8,
+              num_blocks=24, block_size=16, enable_cuda_graph=False)
+    sp = SamplingParams(temperature=0.8, seed=7, max_tokens=20, ignore_eos=True)
+    outs = llm.generate(prompts, sp)
+    agree = 0
+    for p, o in zip(prompts, outs):
+        want = plain_sampled(W, cfg, p, 20, 0.8, 7)
+        assert len(o.output_ids) == 20
+        agree += o.output_ids == want
+    assert agree >= 4          # a draw within rounding of a boundary may differ in at most one request
+    assert llm.runner.manager.num_free_blocks() == 24
+    # the same request gives the same tokens alone and with top-k / top-p set
+    solo = llm.generate([prompts[2]], sp)[0].output_ids
+    assert solo == outs[2].output_ids
+    sp2 = SamplingParams(temperature=1.0, seed=3, max_tokens=10, top_k=5, top_p=0.9, ignore_eos=True)
+    got = llm.generate([prompts[1]], sp2)[0].output_ids
+    assert got == plain_sampled(W, cfg, prompts[1], 10, 1.0, 3, top_k=5, top_p=0.9)
+
+
+def test_preemption_gives_the_same_tokens(dirs):
+    """A pool too small for all requests at once: some are preempted and recomputed; every request
+    still gets the tokens it gets alone."""
+    from dinfer_b200 import LLM, SamplingParams
+    cfg = H.TINY_B
+    rng = random.Random(5)
+    prompts = [H.random_tokens(rng, n, cfg["vocab_size"]) for n in (30, 28, 33, 25)]
+    sp = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
+    big = LLM(dirs["B"], dtype="float32", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32,
+              num_blocks=64, block_size=4, enable_cuda_graph=False)
+    want = [o.output_ids for o in big.generate(prompts, sp)]
+    assert big.stats.preemptions == 0
+    del big
+    small = LLM(dirs["B"], dtype="float32", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32,
+                num_blocks=40, block_size=4, enable_cuda_graph=False)        # 160 tokens for 4 x ~70
+    outs = small.generate(prompts, sp)
+    assert small.stats.preemptions > 0
+    assert [o.output_ids for o in outs] == want
+    assert small.runner.manager.num_free_blocks() == 40
+    small.runner.manager.check_invariants()
+
+
+def test_stop_token_and_eos(dirs):
+    from dinfer_b200 import LLM, SamplingParams
+    cfg = H.TINY_A
+    W = H.load_plain_weights(dirs["A"])
+    prompt = [9, 8, 7, 6]
+    path = P.greedy_generate(W, cfg, prompt, 10)
+    llm = LLM(dirs["A"], dtype="float32", max_model_len=64, max_num_seqs=2, max_num_batched_tokens=16,
+              num_blocks=32, block_size=4, enable_cuda_graph=False)
+    o = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=10, stop_token_ids=[path[3]],
+                                              ignore_eos=True))[0]
+    cut = path.index(path[3]) + 1
+    assert o.output_ids == path[:cut] and o.finish_reason == "stop"
+
+
+def test_long_decoding_and_first_tokens(dirs):
+    """Decode one token at a time up to the model's longest sequence; every position's logits are
+    compared, the first ones included."""
+    from dinfer_b200.config.engine_config import EngineConfig
+    from dinfer_b200.engine.batch import StepEntry
+    from dinfer_b200.engine.runner import ModelRunner
+    cfg = H.TINY_B
+    ids = H.random_tokens(random.Random(3), 256, cfg["vocab_size"])
+    want = H.PlainOracle(dirs["B"]).logits(ids)
+    for dtype in ("float32", "bfloat16"):
+        r = ModelRunner.from_dir(dirs["B"], EngineConfig(max_model_len=256, max_num_seqs=2,
+                                                         max_num_batched_tokens=64, num_blocks=17, block_size=16,
+                                                         dtype=dtype, enable_cuda_graph=False))
+        got = torch.cat([r.step([StepEntry("x", [t], [0])]) for t in ids]).cpu().numpy()
+        r.finish("x")
+        assert H.rel_err(got, want) <= H.TOLERANCE[dtype], dtype
+        assert H.rel_err(got[:4], want[:4]) <= H.TOLERANCE[dtype]
+        with pytest.raises(ValueError, match="max_model_len"):
+            r.step([StepEntry("y", ids + [1], [])])
+        with pytest.raises(ValueError, match="vocabulary"):
+            r.step([StepEntry("z", [cfg["vocab_size"]], [0])])
+
+
+def test_out_of_pages_is_an_error_at_the_step_function(dirs):
+    from dinfer_b200.config.engine_config import EngineConfig
+    from dinfer_b200.engine.batch import OutOfPages, StepEntry
+    from dinfer_b200.engine.runner import ModelRunner
+    r = ModelRunner.from_dir(dirs["A"], EngineConfig(max_model_len=64, max_num_seqs=4, max_num_batched_tokens=64,
+                                                     num_blocks=4, block_size=4, dtype="float32",
+                                                     enable_cuda_graph=False))
+    r.step([StepEntry("a", list(range(12)), [])])
+    with pytest.raises(OutOfPages):
+        r.step([StepEntry("b", list(range(8)), [])])
+    r.finish("a")
+    assert r.step([StepEntry("b", list(range(8)), [7])]).shape == (1, 256)

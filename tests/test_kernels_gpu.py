@@ -1,0 +1,272 @@
+"""Each kernel alone against a plain torch reference of the same operation, at sizes other than the
+engine's tiny models (widths and vocabularies that are no power of two, head sizes in steps of 16,
+odd head and group counts)."""
+import math
+import random
+
+import pytest
+import torch
+
+import plain_model as P
+
+pytestmark = pytest.mark.gpu
+
+DT = [torch.float32, torch.bfloat16]
+
+
+def tol(dt):
+    return dict(atol=2e-5, rtol=2e-5) if dt == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def dev(t, dt=None):
+    return t.to("cuda", dtype=dt) if dt else t.to("cuda")
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("T,h", [(1, 24), (7, 1000), (33, 4100), (3, 20000)])
+def test_rmsnorm_add_and_gather(dt, T, h):
+    from dinfer_b200.kernels import ops
+    g = torch.Generator().manual_seed(T * h)
+    res = torch.randn(T, h, generator=g) * 3
+    delta = (torch.randn(T, h, generator=g)).to(dt)
+    w = (1 + 0.3 * torch.randn(h, generator=g)).to(dt)
+    eps = 1e-5
+    # plain norm of the residual
+    r = dev(res.clone())
+    out = torch.empty(T, h, dtype=dt, device="cuda")
+    ops.rmsnorm(r, dev(w), eps, out)
+    want = P.rms_norm(res.double(), w.double(), eps)
+    assert torch.allclose(out.double().cpu(), want, **tol(dt))
+    assert torch.equal(r.cpu(), res)
+    # fused add: residual updated in place, in 32-bit
+    ops.rmsnorm(r, dev(w), eps, out, delta=dev(delta))
+    summed = res + delta.float()
+    assert torch.equal(r.cpu(), summed)
+    assert torch.allclose(out.double().cpu(), P.rms_norm(summed.double(), w.double(), eps), **tol(dt))
+    # gather of rows (+ pending delta), residual untouched
+    rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32)
+    r2 = dev(res.clone())
+    out2 = torch.empty(3, h, dtype=dt, device="cuda")
+    ops.rmsnorm(r2, dev(w), eps, out2, delta=dev(delta), rows=dev(rows))
+    assert torch.equal(r2.cpu(), res)
+    assert torch.allclose(out2.double().cpu(), P.rms_norm(summed.double(), w.double(), eps)[rows.long()], **tol(dt))
+
+
+@pytest.mark.parametrize("dt", DT)
+def test_embedding_and_silu(dt):
+    from dinfer_b200.kernels import ops
+    g = torch.Generator().manual_seed(5)
+    table = torch.randn(301, 72, generator=g).to(dt)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32)
+    out = torch.empty(5, 72, dtype=torch.float32, device="cuda")
+    ops.embedding(dev(ids), dev(table), out)
+    assert torch.equal(out.cpu(), table.float()[ids.long()])
+    x = (torch.randn(9, 2 * 250, generator=g) * 4).to(dt)
+    o = torch.empty(9, 250, dtype=dt, device="cuda")
+    ops.silu_mul(dev(x), o)
+    xd = x.double()
+    want = P.silu(xd[:, :250]) * xd[:, 250:]
+    assert torch.allclose(o.double().cpu(), want, **tol(dt))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 37, 50), (8, 130, 999), (9, 260, 70), (130, 129, 1031), (300, 17, 8)])
+@pytest.mark.parametrize("adt,wdt,cdt", [(torch.float32,) * 3, (torch.bfloat16, torch.float32, torch.bfloat16),
+                                         (torch.float32, torch.bfloat16, torch.float32)])
+def test_gemm_f32(M, N, K, adt, wdt, cdt):
+    from dinfer_b200.kernels import ops
+    g = torch.Generator().manual_seed(M * N + K)
+    a = torch.randn(M, K, generator=g).to(adt)
+    w = torch.randn(N, K, generator=g).to(wdt)
+    out = torch.empty(M, N, dtype=cdt, device="cuda")
+    ops.gemm_f32(dev(a), dev(w), out)
+    want = a.double() @ w.double().T
+    t = dict(atol=1e-4 * math.sqrt(K), rtol=1e-5) if cdt == torch.float32 else dict(atol=5e-2 * math.sqrt(K) / 8, rtol=1e-2)
+    assert torch.allclose(out.double().cpu(), want, **t)
+
+
+def test_gemm_f32_strided_operands():
+    from dinfer_b200.kernels import ops
+    g = torch.Generator().manual_seed(3)
+    big = dev(torch.randn(20, 100, generator=g))
+    a = big[:, 10:60]                       # row stride 100, 50 columns
+    w = dev(torch.randn(31, 50, generator=g))
+    outbig = torch.zeros(20, 64, device="cuda")
+    ops.gemm_f32(a, w, outbig[:, 3:34])
+    assert torch.allclose(outbig[:, 3:34], a @ w.T, atol=1e-4)
+    assert float(outbig[:, :3].abs().max()) == 0 and float(outbig[:, 34:].abs().max()) == 0
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("H,Hkv,D,rot,bs", [(4, 1, 16, 16, 4), (6, 2, 32, 32, 16), (5, 5, 48, 48, 8),
+                                             (8, 2, 128, 64, 16), (3, 3, 256, 256, 32), (2, 1, 80, 80, 16)])
+def test_qk_post(dt, H, Hkv, D, rot, bs):
+    from dinfer_b200.kernels import ops
+    from dinfer_b200.parts.rope import rope_table
+    g = torch.Generator().manual_seed(H * D)
+    T, nb, eps, theta, maxpos = 11, 9, 1e-5, 12345.0, 300
+    width = (H + 2 * Hkv) * D
+    qkv = torch.randn(T, width + 8, generator=g).to(dt)           # padded rows: stride != width
+    pos = torch.tensor(random.Random(1).sample(range(maxpos), T), dtype=torch.int32)
+    wq = (1 + 0.2 * torch.randn(D, generator=g)).to(dt)
+    wk = (1 + 0.2 * torch.randn(D, generator=g)).to(dt)
+    slots = torch.tensor(random.Random(2).sample(range(nb * bs), T), dtype=torch.int32)
+    slots[3] = -1
+    cache = torch.zeros(nb, 2, Hkv, bs, D, dtype=dt, device="cuda")
+    table = rope_table(rot, theta, maxpos, "cuda")
+    x = dev(qkv)
+    ops.qk_post(x[:, :width], dev(pos), H, Hkv, D, eps, dev(wq), dev(wk), table, cache, dev(slots), bs)
+    # plain
+    q = qkv[:, :H * D].double().reshape(T, H, D)
+    k = qkv[:, H * D:(H + Hkv) * D].double().reshape(T, Hkv, D)
+    v = qkv[:, (H + Hkv) * D:width].double().reshape(T, Hkv, D)
+    cos, sin = P.rope_cos_sin(pos, rot, theta)
+    qn, kn = P.rms_norm(q, wq.double(), eps), P.rms_norm(k, wk.double(), eps)
+    qn = torch.cat([P.rope_neox(qn[..., :rot], cos, sin), qn[..., rot:]], -1)
+    kn = torch.cat([P.rope_neox(kn[..., :rot], cos, sin), kn[..., rot:]], -1)
+    got = x.double().cpu()
+    assert torch.allclose(got[:, :H * D].reshape(T, H, D), qn, **tol(dt))
+    assert torch.allclose(got[:, H * D:(H + Hkv) * D].reshape(T, Hkv, D), kn, **tol(dt))
+    assert torch.equal(got[:, (H + Hkv) * D:], qkv[:, (H + Hkv) * D:].double())      # v and the padding untouched
+    c = cache.double().cpu()
+    want_c = torch.zeros_like(c)
+    for t in range(T):
+        s = int(slots[t])
+        if s >= 0:
+            want_c[s // bs, 0, :, s % bs] = kn[t]
+            want_c[s // bs, 1, :, s % bs] = v[t]
+    assert torch.allclose(c, want_c, **tol(dt))
+
+
+def paged_case(rng, reqs, H, Hkv, D, bs, dt, extra_blocks=3):
+    """reqs = [(history, new)].  Returns the kernel's inputs and the plain answer [T, H, D]."""
+    g = torch.Generator().manual_seed(rng.randrange(1 << 30))
+    total_blocks = sum((h + n + bs - 1) // bs for h, n in reqs) + extra_blocks
+    perm = list(range(total_blocks))
+    rng.shuffle(perm)
+    cache = (torch.randn(total_blocks, 2, Hkv, bs, D, generator=g) * 50).to(dt)   # garbage where nothing is stored
+    max_blocks = max((h + n + bs - 1) // bs for h, n in reqs) + 1
+    table = torch.full((len(reqs), max_blocks), -1, dtype=torch.int32)
+    qs, ks, vs, pos, cu = [], [], [], [], [0]
+    for b, (hist, new) in enumerate(reqs):
+        L = hist + new
+        k = torch.randn(L, Hkv, D, generator=g).to(dt)
+        v = torch.randn(L, Hkv, D, generator=g).to(dt)
+        q = torch.randn(new, H, D, generator=g).to(dt)
+        for i in range((L + bs - 1) // bs):
+            blk = perm.pop()
+            table[b, i] = blk
+            n = min(bs, L - i * bs)
+            cache[blk, 0, :, :n] = k[i * bs:i * bs + n].transpose(0, 1)
+            cache[blk, 1, :, :n] = v[i * bs:i * bs + n].transpose(0, 1)
+        qs.append(q); ks.append(k); vs.append(v)
+        pos += list(range(hist, L))
+        cu.append(cu[-1] + new)
+    return (torch.cat(qs), cache, table, torch.tensor(cu, dtype=torch.int32), torch.tensor(pos, dtype=torch.int32),
+            qs, ks, vs)
+
+
+def plain_paged(reqs, qs, ks, vs, scale, window=None):
+    outs = []
+    for (hist, new), q, k, v in zip(reqs, qs, ks, vs):
+        qfull = torch.cat([torch.zeros(hist, *q.shape[1:], dtype=torch.float64), q.double()])
+        outs.append(P.causal_gqa_attention(qfull, k.double(), v.double(), scale, window)[hist:])
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("H,Hkv,D,bs,window", [(4, 1, 16, 4, None), (6, 2, 32, 16, None), (5, 5, 48, 8, 7),
+                                                (8, 2, 128, 16, None), (3, 1, 80, 16, 33), (2, 2, 256, 32, None)])
+def test_attention_generic(dt, H, Hkv, D, bs, window):
+    from dinfer_b200.kernels import ops
+    rng = random.Random(H * 1000 + D)
+    reqs = [(40, 5), (70, 1), (0, 33), (130, 64), (0, 1), (7, 1)]        # portions with history beside decodes
+    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, dt)
+    scale = D ** -0.5
+    out = torch.empty(q.shape[0], H * D, dtype=dt, device="cuda")
+    ops.attention_generic(dev(q).reshape(-1, H * D), out, dev(cache), dev(table), dev(cu), dev(pos), H, Hkv, D,
+                          scale, window or 0)
+    want = plain_paged(reqs, qs, ks, vs, scale, window).reshape(-1, H * D)
+    assert torch.allclose(out.double().cpu(), want, **tol(dt))
+
+
+def test_attention_finds_a_far_key():
+    """One key among hundreds, on another page, is made to dominate: the output must be its value."""
+    from dinfer_b200.kernels import ops
+    rng = random.Random(9)
+    H, Hkv, D, bs = 4, 2, 64, 16
+    reqs = [(600, 1), (300, 2)]
+    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, torch.float32)
+    far = 37                                                  # position of the key that must win, request 0
+    q[0] = 0
+    q[0, :, 0] = 100.0
+    blk = int(table[0, far // bs])
+    cache[:, 0, :, :, 0] = 0                                  # no other key has weight along dim 0
+    cache[blk, 0, :, far % bs, 0] = 10.0
+    out = torch.empty(q.shape[0], H * D, device="cuda")
+    ops.attention_generic(dev(q).reshape(-1, H * D), out, dev(cache), dev(table), dev(cu), dev(pos), H, Hkv, D, 1.0, 0)
+    got = out[0].reshape(H, D).cpu()
+    want = cache[blk, 1, :, far % bs].repeat_interleave(H // Hkv, 0)
+    assert torch.allclose(got, want, atol=1e-5)
+
+
+@pytest.mark.parametrize("V", [517, 4099, 151936])
+def test_argmax_and_sampling(V):
+    from dinfer_b200.sampling import sampler as S
+    g = torch.Generator().manual_seed(V)
+    R = 6
+    logits = torch.randn(R, V, generator=g) * 3
+    logits[2, 11] = logits[2, 400] = 50.0                     # a tie: the lower index wins
+    d = dev(logits)
+    assert S.argmax(d).cpu().tolist() == [int(torch.argmax(logits[i])) if i != 2 else 11 for i in range(R)]
+    temps = torch.tensor([0.0, 0.7, 1.0, 1.3, 0.8, 1.0])
+    topk = torch.tensor([-1, -1, 5, -1, 40, 3], dtype=torch.int32)
+    topp = torch.tensor([1.0, 1.0, 1.0, 0.6, 0.9, 0.5])
+    minp = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.02, 0.0])
+    agree = total = 0
+    for off in range(25):
+        seeds = torch.tensor([7, 8, 9, 10, 11, 12], dtype=torch.int64)
+        offs = torch.full((R,), off, dtype=torch.int64)
+        got = S.sample(d, dev(temps), dev(seeds), dev(offs), top_k=dev(topk), top_p=dev(topp), min_p=dev(minp)).cpu()
+        for i in range(R):
+            want = P.sample_token(logits[i], float(temps[i]), int(seeds[i]), off, int(topk[i]), float(topp[i]),
+                                  float(minp[i]))
+            total += 1
+            agree += int(got[i]) == want
+    # f32 sums against f64: a draw that lands within rounding of a boundary may pick the neighbour
+    assert agree >= total - 2, f"{agree}/{total}"
+
+
+def test_sampling_distribution_and_batch_independence():
+    from dinfer_b200.sampling import sampler as S
+    logits = torch.tensor([[2.0, 1.0, 0.5, -1.0, 3.0, 0.0, -30.0]])
+    n = 3000
+    d = dev(logits.repeat(n, 1))
+    temps = dev(torch.full((n,), 0.8))
+    seeds = dev(torch.full((n,), 123, dtype=torch.int64))
+    offs = dev(torch.arange(n, dtype=torch.int64))
+    got = S.sample(d, temps, seeds, offs).cpu()
+    freq = torch.bincount(got.long(), minlength=7).double() / n
+    want = torch.softmax(logits[0].double() / 0.8, 0)
+    assert float((freq - want).abs().max()) < 0.03
+    # the same (seed, offset) gives the same token wherever the row stands in the batch
+    perm = torch.randperm(n)
+    got2 = S.sample(d, temps, seeds, dev(torch.arange(n, dtype=torch.int64)[perm])).cpu()
+    assert torch.equal(got2, got[perm])
+
+
+def test_penalties():
+    from dinfer_b200.sampling import sampler as S
+    V = 50
+    logits = torch.linspace(-2, 2, V).repeat(2, 1)
+    ids = torch.tensor([3, 40, 40, 7, 40, 3,   1, 2], dtype=torch.int32)     # row 0: prompt [3, 40], output [40, 7, 40, 3]
+    offsets = torch.tensor([0, 6, 8], dtype=torch.int32)
+    plen = torch.tensor([2, 2], dtype=torch.int32)
+    rep, freq, pres = torch.tensor([1.5, 1.0]), torch.tensor([0.3, 0.0]), torch.tensor([0.2, 0.0])
+    d = dev(logits.clone())
+    S.apply_penalties(d, dev(ids), dev(offsets), dev(plen), dev(rep), dev(freq), dev(pres))
+    want = logits.clone()
+    for tok, cnt in ((3, 1), (40, 2), (7, 1)):
+        v = want[0, tok]
+        v = v / 1.5 if v > 0 else v * 1.5
+        want[0, tok] = v - 0.3 * cnt - 0.2
+    assert torch.allclose(d.cpu(), want, atol=1e-6)

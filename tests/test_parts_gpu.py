@@ -1,0 +1,237 @@
+"""Each part alone against its plain formula, and the generality of the assembly: a toy mixer with
+state of its own, a windowed attention layer, a layer that runs twice and a layer that reads another
+layer's cache are registered and built here, in the test, and stepped through the unchanged engine."""
+import math
+import random
+
+import pytest
+import torch
+
+import helpers as H
+import plain_model as P
+
+pytestmark = pytest.mark.gpu
+
+
+def env(h, dt, maxpos=512):
+    from dinfer_b200.parts.base import BuildEnv
+    return BuildEnv(torch.device("cuda"), dt, h, maxpos)
+
+
+def make_ctx(reqs, bs, groups=None, num_blocks=64):
+    """reqs = [(history, new)]: a context and manager as the step function would build them."""
+    from dinfer_b200.cache.manager import CacheManager, GroupSpec
+    from dinfer_b200.engine.batch import PlanBuilder, StepEntry
+    m = CacheManager(groups or [GroupSpec()], bs, num_blocks, 8)
+    entries, starts = [], []
+    for i, (hist, new) in enumerate(reqs):
+        assert m.allocate(i, hist + new)
+        m.advance(i, hist)
+        entries.append(StepEntry(i, [0] * new, []))
+        starts.append(hist)
+    pb = PlanBuilder(m, "cuda", 4096, 8, 64)
+    ids, rows, ctx = pb.build(entries, starts)
+    return ctx, m
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_norm_and_feed_forward_parts(dt):
+    from dinfer_b200.parts.base import FEED_FORWARDS, NORMS
+    import dinfer_b200.models.decoder  # noqa: F401  registers the parts
+    h, I, T = 88, 136, 13
+    g = torch.Generator().manual_seed(1)
+    w = (1 + 0.1 * torch.randn(h, generator=g)).to(dt)
+    norm = NORMS.get("rmsnorm")({"size": h, "eps": 2e-6, "weight": "n.weight"}, env(h, dt), "p.")
+    assert [d.name for d in norm.declare()] == ["p.n.weight"]
+    norm.bind({"p.n.weight": w.cuda()})
+    x = torch.randn(T, h, generator=g)
+    got = norm.forward(x.cuda())
+    t = dict(atol=1e-5, rtol=1e-5) if dt == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    assert got.dtype == dt and torch.allclose(got.double().cpu(), P.rms_norm(x.double(), w.double(), 2e-6), **t)
+    ffn = FEED_FORWARDS.get("swiglu")({"intermediate_size": I}, env(h, dt), "m.")
+    W = {d.name: (torch.randn(d.shape, generator=g) * 0.1).to(dt) for d in ffn.declare()}
+    assert {d.name: d.shape for d in ffn.declare()} == {"m.gate_proj.weight": (I, h), "m.up_proj.weight": (I, h),
+                                                         "m.down_proj.weight": (h, I)}
+    ffn.bind({k: v.cuda() for k, v in W.items()})
+    xin = (torch.randn(T, h, generator=g)).to(dt)
+    y = ffn.forward(xin.cuda())
+    want = P.swiglu_mlp(xin.double(), W["m.gate_proj.weight"].double(), W["m.up_proj.weight"].double(),
+                        W["m.down_proj.weight"].double())
+    t = dict(atol=1e-5, rtol=1e-4) if dt == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+    assert torch.allclose(y.double().cpu(), want, **t)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 6])
+def test_attention_part_in_two_portions(dt, window):
+    """The mixer alone: a sequence given as 11 + 9 tokens equals the plain whole-sequence block."""
+    from dinfer_b200.parts.base import MIXERS, CacheBinding
+    from dinfer_b200.parts.spec import PartSpec
+    from dinfer_b200.cache.manager import GroupSpec
+    import dinfer_b200.models.decoder  # noqa: F401
+    h, Hq, Hkv, D, bs = 72, 6, 3, 16, 4
+    cfg = dict(num_attention_heads=Hq, num_key_value_heads=Hkv, head_dim=D, rms_norm_eps=1e-5, rope_theta=777.0)
+    g = torch.Generator().manual_seed(2)
+    mixer = MIXERS.get("gqa_attention")(
+        {"num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D, "qk_norm": True, "eps": 1e-5, "window": window,
+         "position": PartSpec("rope_neox", {"head_dim": D, "theta": 777.0, "max_positions": 64})}, env(h, dt, 64), "a.")
+    W = {}
+    for d in mixer.declare():
+        W[d.name] = ((1 + 0.1 * torch.randn(d.shape, generator=g)) if d.init == "ones"
+                     else torch.randn(d.shape, generator=g) * 0.15).to(dt)
+    mixer.bind({k: v.cuda() for k, v in W.items()})
+    x = torch.randn(20, h, generator=g).to(dt)
+    kv = torch.zeros(16, 2, Hkv, bs, D, dtype=dt, device="cuda")
+    from dinfer_b200.cache.manager import CacheManager
+    from dinfer_b200.engine.batch import PlanBuilder, StepEntry
+    m = CacheManager([GroupSpec(window)], bs, 16, 2)
+    pb = PlanBuilder(m, "cuda", 64, 2, 16)
+    outs = []
+    for lo, hi in ((0, 11), (11, 20)):
+        assert m.allocate("r", hi)
+        _, _, ctx = pb.build([StepEntry("r", [0] * (hi - lo), [])], [lo])
+        outs.append(mixer.forward(x[lo:hi].cuda(), ctx, CacheBinding(kv=kv, group=0, write=True)))
+        m.advance("r", hi)
+    got = torch.cat(outs).double().cpu()
+    want = P.attention_block(x.double(), {k: v.double() for k, v in W.items()}, "a.", cfg, torch.arange(20), window)
+    t = dict(atol=2e-5, rtol=1e-4) if dt == torch.float32 else dict(atol=4e-2, rtol=4e-2)
+    assert torch.allclose(got, want, **t)
+
+
+# ---------------------------------------------------------------- a toy architecture, defined here
+
+def register_toy():
+    from dinfer_b200.config.registry import register_architecture
+    from dinfer_b200.parts.base import MIXERS, Mixer, StateNeed
+    from dinfer_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorDecl
+
+    class RunningMean(Mixer):
+        """y_t = Wo mean_{j<=t}(Wi x_j): the state is the running sum and the count."""
+
+        def __init__(self, params, env, prefix=""):
+            super().__init__(params, env, prefix)
+            self.d = int(params["state_size"])
+            self.h = env.hidden_size
+
+        def declare(self):
+            return [TensorDecl(self.prefix + "mix.in.weight", (self.d, self.h)),
+                    TensorDecl(self.prefix + "mix.out.weight", (self.h, self.d))]
+
+        def bind(self, tensors):
+            self.wi = tensors[self.prefix + "mix.in.weight"].float()
+            self.wo = tensors[self.prefix + "mix.out.weight"].float()
+
+        def cache_need(self):
+            return StateNeed((self.d + 1,), torch.float32)
+
+        def forward(self, x, ctx, cache):
+            out = torch.empty_like(x)
+            for b in range(ctx.num_reqs):
+                lo, hi = ctx.cu_seqlens_host[b], ctx.cu_seqlens_host[b + 1]
+                st = cache.state[ctx.state_slots_host[b]]
+                if ctx.state_fresh_host[b]:
+                    st.zero_()
+                v = x[lo:hi].float() @ self.wi.T
+                sums = torch.cumsum(v, 0) + st[:self.d]
+                counts = st[self.d] + torch.arange(1, hi - lo + 1, device=x.device)
+                out[lo:hi] = ((sums / counts[:, None]) @ self.wo.T).to(x.dtype)
+                st[:self.d] = sums[-1]
+                st[self.d] = counts[-1]
+            return out
+
+    MIXERS.register("toy_running_mean", RunningMean, replace=True)
+
+    def parse(d):
+        return dict(d)
+
+    def spec(c):
+        h, Hq, Hkv, D = c["hidden_size"], c["heads"], c["kv_heads"], c["head_dim"]
+        pos = PartSpec("rope_neox", {"head_dim": D, "theta": c["theta"], "max_positions": c["max_positions"]})
+        norm = lambda name: PartSpec("rmsnorm", {"size": h, "eps": c["eps"], "weight": name})
+        ffn = PartSpec("swiglu", {"intermediate_size": c["inter"]})
+
+        def attn(window):
+            return PartSpec("gqa_attention", {"num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D, "qk_norm": True,
+                                              "eps": c["eps"], "position": pos, "window": window})
+        layers = (
+            LayerSpec("layers.0.", "prenorm_residual", PartSpec("toy_running_mean", {"state_size": c["state_size"]}),
+                      norm("n1.weight"), ffn, norm("n2.weight")),
+            LayerSpec("layers.1.", "prenorm_residual", attn(c["window"]), norm("n1.weight"), ffn, norm("n2.weight")),
+            LayerSpec("layers.2.", "prenorm_residual", attn(None), norm("n1.weight"), ffn, norm("n2.weight")),
+        )
+        schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(1), ScheduleEntry(0),
+                    ScheduleEntry(2, cache_from=2))
+        return ModelSpec("ToyMixedForTest", h, c["vocab_size"], c["max_positions"], "embed.weight", layers, schedule,
+                         norm("final.weight"), "head.weight", False)
+
+    register_architecture("ToyMixedForTest", parse, spec, replace=True)
+
+
+TOY = dict(architectures=["ToyMixedForTest"], vocab_size=203, hidden_size=56, heads=4, kv_heads=2, head_dim=16,
+           inter=72, state_size=24, window=9, theta=5000.0, eps=1e-5, max_positions=128)
+
+
+def toy_plain_logits(W, c, ids):
+    W = {k: v.double() for k, v in W.items()}
+    T = len(ids)
+    pos = torch.arange(T)
+    x = W["embed.weight"][torch.tensor(ids)]
+    acfg = dict(num_attention_heads=c["heads"], num_key_value_heads=c["kv_heads"], head_dim=c["head_dim"],
+                rms_norm_eps=c["eps"], rope_theta=c["theta"])
+    kept = {}
+
+    def ffn(x, p):
+        return P.swiglu_mlp(x, W[p + "gate_proj.weight"], W[p + "up_proj.weight"], W[p + "down_proj.weight"])
+
+    for entry, (layer, reuse) in enumerate([(0, None), (1, None), (2, None), (1, None), (0, None), (2, 2)]):
+        p = f"layers.{layer}."
+        hdn = P.rms_norm(x, W[p + "n1.weight"], c["eps"])
+        if layer == 0:
+            v = hdn @ W[p + "mix.in.weight"].T
+            a = (torch.cumsum(v, 0) / torch.arange(1, T + 1)[:, None]) @ W[p + "mix.out.weight"].T
+        else:
+            H_, Hkv, D = c["heads"], c["kv_heads"], c["head_dim"]
+            q = P.rms_norm((hdn @ W[p + "q_proj.weight"].T).reshape(T, H_, D), W[p + "q_norm.weight"], c["eps"])
+            cos, sin = P.rope_cos_sin(pos, D, c["theta"])
+            q = P.rope_neox(q, cos, sin)
+            if reuse is None:
+                k = P.rms_norm((hdn @ W[p + "k_proj.weight"].T).reshape(T, Hkv, D), W[p + "k_norm.weight"], c["eps"])
+                k = P.rope_neox(k, cos, sin)
+                v = (hdn @ W[p + "v_proj.weight"].T).reshape(T, Hkv, D)
+                kept[entry] = (k, v)
+            else:
+                k, v = kept[reuse]                      # this run reads the cache another run wrote
+            o = P.causal_gqa_attention(q, k, v, D ** -0.5, c["window"] if layer == 1 else None)
+            a = o.reshape(T, H_ * D) @ W[p + "o_proj.weight"].T
+        x = x + a
+        x = x + ffn(P.rms_norm(x, W[p + "n2.weight"], c["eps"]), p)
+    return (P.rms_norm(x, W["final.weight"], c["eps"]) @ W["head.weight"].T).numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_registered_in_the_test(tmp_path, dtype):
+    register_toy()
+    try:
+        d = H.make_model_dir(str(tmp_path / "toy"), TOY, 4, 0.08, 0.1,
+                             torch.float32 if dtype == "float32" else torch.bfloat16)
+        W = H.load_plain_weights(d)
+        rng = random.Random(8)
+        tokens = {r: H.random_tokens(rng, n, TOY["vocab_size"]) for r, n in {"a": 50, "b": 7, "c": 90, "d": 31}.items()}
+        want = {r: toy_plain_logits(W, TOY, t) for r, t in tokens.items()}
+        lengths = {r: len(t) for r, t in tokens.items()}
+        rp = H.LocalReplay(d, dtype, 256, block_size=8)
+        worst = {}
+        try:
+            for name, steps in (("whole", H.schedule_whole(lengths)), ("chunks", H.schedule_chunks(lengths, rng)),
+                                ("mixed", H.schedule_mixed(lengths, rng, max_live=3, decode_tail=10))):
+                got = H.run_schedule(rp, steps, tokens, tag=name + "/")
+                worst[name] = max(H.rel_err(got[r], want[r]) for r in tokens)
+        finally:
+            assert rp.close() == 0
+        print(dtype, worst)
+        assert all(v <= H.TOLERANCE[dtype] for v in worst.values()), worst
+    finally:
+        from dinfer_b200.config.registry import unregister_architecture
+        from dinfer_b200.parts.base import MIXERS
+        unregister_architecture("ToyMixedForTest")
+        MIXERS.unregister("toy_running_mean")
