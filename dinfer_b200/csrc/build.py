@@ -33,6 +33,7 @@ LIBRARIES: Dict[str, tuple] = {
     "attention_generic": ("attention_generic.cu", []),
     "gemm_f32": ("gemm_f32.cu", []),
     "sampling": ("sampling.cu", []),
+    "attention_tc": ("attention_tc.cu", []),
 }
 
 

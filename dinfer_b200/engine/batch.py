@@ -137,6 +137,7 @@ class PlanBuilder:
             groups=groups, state_slots=view("sslots"), state_fresh=view("fresh"),
             max_q_len=max(lens) if lens else 0, max_seq_len=int(seq.max()) if B else 0,
             all_decode=all(n == 1 for n in lens),
+            any_decode=any(n == 1 for n in lens), any_prefill=any(n > 1 for n in lens),
             cu_seqlens_host=cu.tolist(), seq_lens_host=seq.tolist(),
             state_slots_host=sslots.tolist(), state_fresh_host=fresh.tolist())
         self.h2d_bytes = off * 4

@@ -1,0 +1,59 @@
+"""Wrapper of the tensor-core attention library (bfloat16; head sizes 32, 64, 128)."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_int64, c_void_p
+from typing import Optional
+
+import torch
+
+from .lib import KernelError, check, library, ptr, require_cuda, stream_handle
+from .ops import _fn
+
+NUM_SMS = 148
+
+
+def tc_supported(dtype: torch.dtype, head_dim: int, group: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in (32, 64, 128) and 1 <= group <= 16
+
+
+def decode_splits(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
+    """Key splits of the decode shape: enough CTAs to fill the GPU about twice, never more than
+    there are 64-key tiles, at most 32."""
+    base = max(1, num_reqs * num_kv_heads)
+    want = (2 * NUM_SMS + base - 1) // base
+    tiles = max(1, (max_seq_len + 63) // 64)
+    return max(1, min(want, tiles, 32))
+
+
+def attention_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                 cu_seqlens: torch.Tensor, seq_lens: torch.Tensor, num_heads: int, num_kv_heads: int,
+                 head_dim: int, scale: float, window: int, max_q_len: int, any_decode: bool,
+                 any_prefill: bool, splits: int, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Paged causal attention on the tensor cores.  ``q`` / ``out``: rows with a contiguous last axis,
+    head h at columns [h*D, (h+1)*D).  ``splits`` > 1 needs ``scratch`` (f32) of
+    ``B * H * splits * (D + 2)`` elements; it is allocated here when not given."""
+    require_cuda(q, out, cache, block_table, cu_seqlens, seq_lens)
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("attention_tc: bfloat16 only")
+    if q.stride(-1) != 1 or out.stride(-1) != 1 or not cache.is_contiguous():
+        raise KernelError("attention_tc: contiguous last axes and a contiguous cache")
+    B = cu_seqlens.numel() - 1
+    for t, n in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (seq_lens, "seq_lens")):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError(f"attention_tc: {n} must be contiguous int32")
+    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
+        raise KernelError(f"attention_tc: cache shape {tuple(cache.shape)} is not [blocks, 2, Hkv, block, D]")
+    if not any_decode:
+        splits = 1
+    if splits > 1 and scratch is None:
+        scratch = torch.empty(B * num_heads * splits * (head_dim + 2), dtype=torch.float32, device=q.device)
+    if splits > 1 and (scratch.dtype != torch.float32 or scratch.numel() < B * num_heads * splits * (head_dim + 2)):
+        raise KernelError("attention_tc: scratch too small")
+    lib, f = _fn("attention_tc", "dinfer_attention_tc",
+                 [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                  c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), ptr(block_table), block_table.shape[1],
+                 ptr(cu_seqlens), ptr(seq_lens), B, num_heads, num_kv_heads, head_dim, cache.shape[3],
+                 float(scale), int(window), int(max_q_len), int(any_decode), int(any_prefill), int(splits),
+                 ptr(scratch if splits > 1 else None), stream_handle()), "attention_tc")
+    return out

@@ -15,7 +15,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..kernels import ops
+from ..kernels import attention_ops, ops
 from .base import (MIXERS, POSITION_ENCODINGS, BuildEnv, CacheBinding, KvCacheNeed, Mixer, StepContext,
                    build_part)
 from .linear import Linear
@@ -75,7 +75,9 @@ class GQAttention(Mixer):
         return KvCacheNeed(self.Hkv, self.D, self.window)
 
     def kernel_libraries(self):
-        return ["qk_post", "attention_generic"] + self.qkv.kernel_libraries() + self.o.kernel_libraries()
+        att = ("attention_tc" if attention_ops.tc_supported(self.env.act_dtype, self.D, self.H // self.Hkv)
+               else "attention_generic")
+        return ["qk_post", att] + self.qkv.kernel_libraries() + self.o.kernel_libraries()
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
         H, Hkv, D = self.H, self.Hkv, self.D
@@ -101,5 +103,14 @@ class GQAttention(Mixer):
         return self.o(out)
 
     def attend(self, q, out, kv, g, ctx: StepContext) -> None:
-        ops.attention_generic(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.positions, self.H, self.Hkv,
-                              self.D, self.scale, int(self.window or 0))
+        """Tensor-core kernels where they take the head size (bfloat16; 32, 64, 128), else the
+        plain-arithmetic kernel, which takes every size."""
+        window = int(self.window or 0)
+        if attention_ops.tc_supported(q.dtype, self.D, self.H // self.Hkv):
+            splits = ctx.decode_splits or attention_ops.decode_splits(ctx.num_reqs, self.Hkv, ctx.max_seq_len)
+            attention_ops.attention_tc(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H, self.Hkv,
+                                       self.D, self.scale, window, ctx.max_q_len, ctx.any_decode, ctx.any_prefill,
+                                       splits)
+        else:
+            ops.attention_generic(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.positions, self.H, self.Hkv,
+                                  self.D, self.scale, window)

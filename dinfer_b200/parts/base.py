@@ -66,6 +66,9 @@ class StepContext:
     max_q_len: int                     # longest portion in the batch
     max_seq_len: int                   # longest request after the step
     all_decode: bool                   # every request brings exactly one token
+    any_decode: bool = True            # some request brings exactly one token
+    any_prefill: bool = True           # some request brings more than one
+    decode_splits: int = 0             # > 0: the decode attention uses this many key splits (CUDA graphs)
     # host copies for parts written in plain torch (tests, toy parts)
     cu_seqlens_host: Sequence[int] = ()
     seq_lens_host: Sequence[int] = ()
