@@ -344,16 +344,24 @@ int launch(const Params& p, int B, int max_q_len, bool any_decode, bool any_pref
   if (any_prefill) {
     auto k = attention_tc_kernel<D, false>;
     const size_t sm = smem_bytes<D, false>();
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-    if (e != cudaSuccess) return refuse((int)e, "attention_tc: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    static bool opted = false;       // once per process: not a stream operation, kept out of graph captures
+    if (!opted) {
+      cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+      if (e != cudaSuccess) return refuse((int)e, "attention_tc: shared memory opt-in failed: %s", cudaGetErrorString(e));
+      opted = true;
+    }
     dim3 grid(((int64_t)max_q_len * p.group + BM - 1) / BM, p.Hkv, B);
     k<<<grid, NT, sm, stream>>>(p);
   }
   if (any_decode) {
     auto k = attention_tc_kernel<D, true>;
     const size_t sm = smem_bytes<D, true>();
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-    if (e != cudaSuccess) return refuse((int)e, "attention_tc: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    static bool opted = false;       // once per process: not a stream operation, kept out of graph captures
+    if (!opted) {
+      cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+      if (e != cudaSuccess) return refuse((int)e, "attention_tc: shared memory opt-in failed: %s", cudaGetErrorString(e));
+      opted = true;
+    }
     dim3 grid(p.splits, p.Hkv, B);
     k<<<grid, NT, sm, stream>>>(p);
     if (p.splits > 1) attention_merge_kernel<D><<<dim3(p.H, B), D, 0, stream>>>(p);

@@ -78,9 +78,11 @@ int launch(float* residual, const void* delta, const int* rows, const void* weig
   auto k4 = rmsnorm_kernel<TA, TW, 4>;
   auto k1 = rmsnorm_kernel<TA, TW, 1>;
   auto k = vec4 ? k4 : k1;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static bool opted[2] = {false, false};   // once per process and kernel, kept out of graph captures
+  if (smem > 48 * 1024 && !opted[vec4]) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     if (e != cudaSuccess) return refuse((int)e, "rmsnorm: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    opted[vec4] = true;
   }
   k<<<num_rows, threads, smem, stream>>>(residual, (const TA*)delta, rows, (const TW*)weight, (TA*)out, h, eps, stash);
   return cuda_status("rmsnorm");

@@ -5,11 +5,15 @@ wanted).  ``PlanBuilder`` flattens them request-major into one packed int32 buff
 memory, copied to the device in one transfer, and hands out views: ids, positions, cu_seqlens,
 seq_lens, and per cache group the block table and the slot of every new token.  The fields follow
 the reference's ``BatchPlan`` (crates/core/src/runner.rs:46-89, built at runner.rs:745-876).
+
+For CUDA graphs a batch can be padded to a fixed number of requests with dummy rows (token 0,
+position 0, no slot, length 1, no pages) and a fixed table width, so that every view keeps its
+address and shape (crates/layers/src/exec.rs:226-247,392-404 does the same padding).
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -35,7 +39,7 @@ def _align(n: int, a: int = 4) -> int:
 
 class PlanBuilder:
     """Owns the pinned staging buffers (a small ring, so that a buffer is not rewritten while its
-    copy may still be in flight) and the device buffer the views point into."""
+    copy may still be in flight) and the device buffers the views point into."""
 
     RING = 4
 
@@ -43,33 +47,44 @@ class PlanBuilder:
         self.manager = manager
         self.device = device
         self.max_blocks = max_blocks
-        ng = len(manager.groups)
-        cap = (3 * _align(max_tokens) + 6 * _align(max_reqs + 1) + ng * (_align(max_tokens) +
-               _align(max_reqs * max_blocks)) + 64)
-        self.capacity = cap
         self.max_tokens, self.max_reqs = max_tokens, max_reqs
+        self.capacity = self.words(max_tokens, max_reqs, max_tokens, max_blocks)
         on_gpu = torch.device(device).type == "cuda"
-        self._host = [torch.empty(cap, dtype=torch.int32, pin_memory=on_gpu) for _ in range(self.RING)]
+        self._host = [torch.empty(self.capacity, dtype=torch.int32, pin_memory=on_gpu) for _ in range(self.RING)]
         self._events = [None] * self.RING
-        self._dev = [torch.empty(cap, dtype=torch.int32, device=device) for _ in range(self.RING)]
+        self._dev = [torch.empty(self.capacity, dtype=torch.int32, device=device) for _ in range(self.RING)]
         self._turn = 0
+        self.h2d_bytes = 0
 
-    def build(self, entries: Sequence[StepEntry], starts: Sequence[int], table_width: Optional[int] = None):
-        """``starts[i]`` = tokens of entry i already in the cache.  Pages must be allocated already.
-        Returns (ids, logits_rows, ctx)."""
+    def words(self, T: int, B: int, R: int, width: int) -> int:
+        """int32 words of a packed plan of T tokens, B requests, R logits rows, tables ``width`` wide."""
+        ng = len(self.manager.groups)
+        return (2 * _align(T) + _align(R) + _align(B + 1) + 3 * _align(B)
+                + ng * (_align(T) + _align(B * width)) + 16)
+
+    def build(self, entries: Sequence[StepEntry], starts: Sequence[int], *, pad_reqs: Optional[int] = None,
+              table_width: Optional[int] = None, dev: Optional[torch.Tensor] = None):
+        """``starts[i]`` = tokens of entry i already in the cache; pages must be allocated already.
+        ``pad_reqs``: pad with one-token dummy requests up to this many and ask for every row's
+        logits (the layout of a captured decode graph).  ``dev``: the int32 device buffer to fill
+        (default: the next one of the ring).  Returns (ids, logits_rows, ctx)."""
         m = self.manager
         bs = m.block_size
-        B = len(entries)
-        lens = [len(e.tokens) for e in entries]
+        n_real = len(entries)
+        B = pad_reqs if pad_reqs is not None else n_real
+        if B < n_real:
+            raise ValueError("pad_reqs below the number of requests")
+        lens = [len(e.tokens) for e in entries] + [1] * (B - n_real)
         T = sum(lens)
         if T > self.max_tokens or B > self.max_reqs:
             raise ValueError(f"step of {T} tokens / {B} requests exceeds the plan buffers "
                              f"({self.max_tokens} / {self.max_reqs})")
         cu = np.zeros(B + 1, dtype=np.int32)
         np.cumsum(lens, out=cu[1:])
-        seq = np.asarray([s + n for s, n in zip(starts, lens)], dtype=np.int32)
-        ids = np.empty(T, dtype=np.int32)
-        pos = np.empty(T, dtype=np.int32)
+        seq = np.ones(B, dtype=np.int32)
+        seq[:n_real] = [s + n for s, n in zip(starts, lens)]
+        ids = np.zeros(T, dtype=np.int32)
+        pos = np.zeros(T, dtype=np.int32)
         rows: List[int] = []
         for i, e in enumerate(entries):
             a, b = cu[i], cu[i + 1]
@@ -79,13 +94,20 @@ class PlanBuilder:
                 if not (0 <= w < lens[i]):
                     raise ValueError(f"request {e.req_id!r}: wanted place {w} is outside its {lens[i]} tokens")
                 rows.append(int(a) + int(w))
-        width = table_width or max(1, max((int(s) + bs - 1) // bs for s in seq)) if B else 1
+        if pad_reqs is not None:
+            rows_np = np.arange(T, dtype=np.int32)
+        else:
+            rows_np = np.asarray(rows, dtype=np.int32)
+        if table_width is not None:
+            width = table_width
+        else:
+            width = max(1, max((int(s) + bs - 1) // bs for s in seq)) if B else 1
         if width > self.max_blocks:
             raise ValueError(f"a request needs {width} pages, the plan buffers hold {self.max_blocks}")
         tables, slots = [], []
         for g in range(len(m.groups)):
             tab = np.full((B, width), -1, dtype=np.int32)
-            sl = np.empty(T, dtype=np.int32)
+            sl = np.full(T, -1, dtype=np.int32)
             for i, e in enumerate(entries):
                 t = m.block_table(e.req_id, g)
                 n = min(len(t), width)
@@ -95,18 +117,19 @@ class PlanBuilder:
                 sl[cu[i]:cu[i + 1]] = np.where(blk >= 0, blk * bs + p % bs, -1)
             tables.append(tab)
             slots.append(sl)
-        sslots = np.asarray([m.state_slots.slot(e.req_id) for e in entries], dtype=np.int32)
-        fresh = np.asarray([1 if m.state_slots.take_fresh(e.req_id) else 0 for e in entries], dtype=np.int32)
-        rows_np = np.asarray(rows, dtype=np.int32)
+        sslots = np.zeros(B, dtype=np.int32)
+        fresh = np.zeros(B, dtype=np.int32)
+        sslots[:n_real] = [m.state_slots.slot(e.req_id) for e in entries]
+        fresh[:n_real] = [1 if m.state_slots.take_fresh(e.req_id) else 0 for e in entries]
 
-        # pack
+        # pack: the order and the alignment fix every view's offset for given (T, B, R, width)
         k = self._turn
         self._turn = (k + 1) % self.RING
         if self._events[k] is not None:
             self._events[k].synchronize()
         host = self._host[k].numpy()
         off = 0
-        views = {}
+        views: Dict[str, Tuple[int, int]] = {}
 
         def put(name, arr):
             nonlocal off
@@ -115,11 +138,14 @@ class PlanBuilder:
             views[name] = (off, n)
             off = _align(off + n)
 
-        put("ids", ids); put("pos", pos); put("cu", cu); put("seq", seq)
-        put("rows", rows_np); put("sslots", sslots); put("fresh", fresh)
+        put("ids", ids); put("pos", pos); put("rows", rows_np); put("cu", cu); put("seq", seq)
+        put("sslots", sslots); put("fresh", fresh)
         for g in range(len(m.groups)):
-            put(f"tab{g}", tables[g]); put(f"slot{g}", slots[g])
-        dev = self._dev[k]
+            put(f"slot{g}", slots[g]); put(f"tab{g}", tables[g])
+        if dev is None:
+            dev = self._dev[k]
+        if off > dev.numel():
+            raise ValueError("the plan does not fit its device buffer")
         dev[:off].copy_(self._host[k][:off], non_blocking=True)
         if dev.is_cuda:
             ev = torch.cuda.Event()

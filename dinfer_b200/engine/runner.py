@@ -62,6 +62,7 @@ class ModelRunner:
                                 max_reqs=engine.max_num_seqs,
                                 max_blocks=self.max_blocks_per_seq)
         self.steps_run = 0
+        self._init_graphs()
 
     @classmethod
     def from_dir(cls, model_dir: str, engine: EngineConfig) -> "ModelRunner":
@@ -145,12 +146,74 @@ class ModelRunner:
                 raise OutOfPages(f"no pages for request {e.req_id!r} ({total} tokens; "
                                  f"{[p.num_free for p in m.pools]} pages free)")
             starts.append(start)
-        ids, rows, ctx = self.plan.build(entries, starts)
-        logits = self.model.forward(ids, ctx, self.bindings, rows)
+        if self._graph_ok and len(entries) <= self._buckets[-1] and all(len(e.tokens) == 1 for e in entries):
+            logits = self._graph_step(entries, starts)
+        else:
+            ids, rows, ctx = self.plan.build(entries, starts)
+            logits = self.model.forward(ids, ctx, self.bindings, rows)
         for e, s in zip(entries, starts):
             m.advance(e.req_id, s + len(e.tokens))
         self.steps_run += 1
         return logits
+
+    # ---- decode-only steps replay a captured graph
+    def _init_graphs(self) -> None:
+        """Decode-only steps (every request brings one token) run as a CUDA graph per batch-size
+        bucket, the batch padded with dummy rows up to the bucket (models/qwen3/src/executor.rs:993-1023,
+        crates/layers/src/exec.rs:83-87).  Off for models with per-request state: a dummy row has no
+        state slot of its own."""
+        e = self.engine
+        has_state = any(isinstance(n, StateNeed) for n in self.model.cache_needs())
+        self._graph_ok = bool(e.enable_cuda_graph) and not has_state
+        b, buckets = 1, []
+        while b < e.max_num_seqs:
+            buckets.append(b)
+            b *= 2
+        buckets.append(e.max_num_seqs)
+        self._buckets = buckets
+        self._graphs: Dict[int, Any] = {}
+        self._graph_pool = None
+
+    def _capture(self, bucket: int):
+        from ..kernels import attention_ops
+        width = self.max_blocks_per_seq
+        dev = torch.empty(self.plan.words(bucket, bucket, bucket, width), dtype=torch.int32, device=self.device)
+        ids, rows, ctx = self.plan.build([], [], pad_reqs=bucket, table_width=width, dev=dev)
+        # the split count is part of the captured launch: fixed per bucket, for the longest context
+        hkv = max([n.num_kv_heads for n in self.model.cache_needs() if isinstance(n, KvCacheNeed)] or [1])
+        ctx.decode_splits = attention_ops.decode_splits(bucket, hkv, self.engine.max_model_len)
+        cur = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            for _ in range(2):                               # warm-up outside the capture
+                self.model.forward(ids, ctx, self.bindings, rows)
+        cur.wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        n0 = kernel_lib.launch_count()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.forward(ids, ctx, self.bindings, rows)
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        rec = dict(graph=graph, dev=dev, logits=logits, splits=ctx.decode_splits, width=width,
+                   launches=kernel_lib.launch_count() - n0)
+        self._graphs[bucket] = rec
+        return rec
+
+    def _graph_step(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
+        B = len(entries)
+        bucket = next(b for b in self._buckets if b >= B)
+        rec = self._graphs.get(bucket) or self._capture(bucket)
+        self.plan.build(entries, starts, pad_reqs=bucket, table_width=rec["width"], dev=rec["dev"])
+        rec["graph"].replay()
+        kernel_lib.add_launches(rec["launches"])
+        wanted = [i for i, e in enumerate(entries) if len(e.want)]
+        if len(wanted) == B:
+            return rec["logits"][:B]         # valid until the next step of this bucket
+        if not wanted:
+            return rec["logits"][:0]
+        return rec["logits"][torch.tensor(wanted, device=self.device)]
 
     def finish(self, req_id: Hashable) -> None:
         """The request is over: its pages and state slot go back to the pools."""

@@ -106,6 +106,55 @@ def test_preemption_gives_the_same_tokens(dirs):
     small.runner.manager.check_invariants()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuda_graph_decode_equals_eager(dirs, dtype):
+    """Decode-only steps replayed from a captured graph (batch padded to the bucket) give the logits
+    of the eager path; requests join and leave so that several buckets and dummy rows are used."""
+    from dinfer_b200.config.engine_config import EngineConfig
+    from dinfer_b200.engine.batch import StepEntry
+    from dinfer_b200.engine.runner import ModelRunner
+    cfg = H.TINY_B
+    rng = random.Random(11)
+    toks = {r: H.random_tokens(rng, n, cfg["vocab_size"]) for r, n in {"a": 40, "b": 23, "c": 31, "d": 18, "e": 9}.items()}
+    oracle = H.PlainOracle(dirs["B"])
+    runs = {}
+    for graphs in (False, True):
+        r = ModelRunner.from_dir(dirs["B"], EngineConfig(max_model_len=64, max_num_seqs=6, max_num_batched_tokens=64,
+                                                         num_blocks=40, block_size=4, dtype=dtype,
+                                                         enable_cuda_graph=graphs))
+        got = {k: [] for k in toks}
+        # prompts of 5 tokens each in one mixed step, then token by token, requests dropping out as they end
+        out = r.step([StepEntry(k, t[:5], [4]) for k, t in toks.items()])
+        for i, k in enumerate(toks):
+            got[k].append(out[i].cpu())
+        p = 5
+        while any(len(t) > p for t in toks.values()):
+            live = [k for k, t in toks.items() if len(t) > p]
+            out = r.step([StepEntry(k, [toks[k][p]], [0] if (p % 3 or k != "a") else []) for k in live])
+            j = 0
+            for k in live:
+                if p % 3 or k != "a":
+                    got[k].append(out[j].cpu())
+                    j += 1
+            for k in live:
+                if len(toks[k]) == p + 1:
+                    r.finish(k)
+            p += 1
+        assert r.manager.num_free_blocks() == 40
+        if graphs:
+            assert sorted(r._graphs) == [1, 2, 4, 6]
+        runs[graphs] = got
+    for k, t in toks.items():
+        want = oracle.logits(t)
+        rows = [4] + [q for q in range(5, len(t)) if (q % 3 or k != "a")]
+        g = torch.stack(runs[True][k]).numpy()
+        e = torch.stack(runs[False][k]).numpy()
+        assert H.rel_err(g, want[rows]) <= H.TOLERANCE[dtype]
+        assert H.rel_err(e, want[rows]) <= H.TOLERANCE[dtype]
+        if dtype == "float32":
+            assert (g == e).all()
+
+
 def test_stop_token_and_eos(dirs):
     from dinfer_b200 import LLM, SamplingParams
     cfg = H.TINY_A
