@@ -186,8 +186,46 @@ def prefill_run(llm, cfg, tokens, rng, reps=3):
     return best
 
 
+def profile_region(a) -> int:
+    """For a profiler: set up a small case, then bracket ONE decode step (or one prefill step) with
+    cudaProfilerStart/Stop, so that ``ncu --profile-from-start off`` sees only that step's kernels.
+    Prints no benchmark line: a run under a profiler is never a measurement."""
+    import torch
+    from dinfer_b200 import SamplingParams
+    from dinfer_b200.engine.batch import StepEntry
+    cfg = QWEN3_8B
+    rng = random.Random(42)
+    llm = make_llm(cfg, a.layers, max(a.batch, 1), a.context)
+    V = cfg["vocab_size"]
+    if a.profile == "prefill":
+        ids = [rng.randrange(V) for _ in range(PREFILL_TOKENS)]
+        llm.runner.step([StepEntry("w", ids, [PREFILL_TOKENS - 1])])
+        llm.runner.finish("w")
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        llm.runner.step([StepEntry("p", ids, [PREFILL_TOKENS - 1])])
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        return 0
+    sp = SamplingParams(temperature=0.0, max_tokens=1 << 20, ignore_eos=True)
+    for _ in range(a.batch):
+        llm.add_request([rng.randrange(V) for _ in range(a.context - 16)], sp)
+    while any(r.num_computed < len(r.prompt_ids) for r in llm._requests.values()) or llm.scheduler.waiting:
+        llm.step()
+    for _ in range(3):
+        llm.step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    llm.step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
+                    help="run one bracketed step for a profiler instead of the benchmark")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
@@ -207,6 +245,8 @@ def main() -> int:
         return 2
     a.warmup = max(a.warmup, 3)
     import torch
+    if a.profile:
+        return profile_region(a)
     cfg = QWEN3_8B
     pk = peaks()
     rng = random.Random(42)
