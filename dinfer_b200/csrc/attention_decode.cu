@@ -1,0 +1,354 @@
+// Paged attention for decoded tokens (one query token per request), bfloat16, head sizes 64 / 128,
+// group sizes up to 16, pages of a power-of-two size.
+//
+// The step is bound by reading K and V once, so the kernel is built to issue few instructions per
+// byte: keys, not heads, fill the 16 rows of the tensor-core tile.
+//     S^T[16 keys, 8 heads] = K[16 keys, D] * Q^T[D, 8 heads]          (A = K from shared memory)
+//     O^T[D, 8 heads]      += V^T[D, 16 keys] * P^T[16 keys, 8 heads]  (A = V through ldmatrix.trans,
+//                                                                       B = P^T by movmatrix.trans)
+// so a group of up to 8 query heads costs one n8 tile and nothing is padded to 16 rows.
+// Grid (split, kv head, request): a CTA walks a range of 64-key tiles with a 3-deep cp.async
+// pipeline (one page-table lookup and one address per thread and tile); each of its four warps takes
+// 16 keys of every tile with its own running max / sum; warps fold in shared memory; splits fold
+// through f32 partials in scratch, by whichever CTA of the (request, kv head) arrives last (a counter
+// in the same scratch, left at zero again for the next launch).
+//
+// Counterpart in the reference: gqa_decode_v3 + merge (crates/kernels/cuda/gqa_decode_v3_core.cuh:72-242,
+// crates/kernels/cuda/gqa.cu:1423-1461), CUDA-core dot products with the group limited to 4.
+#include "common.cuh"
+
+using namespace dinfer;
+
+namespace {
+
+constexpr int NT = 128;
+constexpr int BN = 64;
+constexpr int STAGES = 3;
+
+struct Params {
+  const __nv_bfloat16* q; int64_t ldq;
+  __nv_bfloat16* out; int64_t ldo;
+  const __nv_bfloat16* cache;
+  const int* block_table; int max_blocks;
+  const int* cu_seqlens; const int* seq_lens;
+  int H, Hkv, group, block_size, bs_log2, window;
+  float scale_log2;
+  int splits;
+  float* part_o;     // [B, H, splits, D]
+  float* part_ml;    // [B, H, splits, 2]
+  int* counters;     // [B, Hkv]
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
+  unsigned d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
+  constexpr int C = D / 8;
+  return row * D + ((chunk ^ (row % (C >= 8 ? 8 : C))) << 3);
+}
+
+// keys [j0, j0 + 64) of kv head hk into one stage; a thread copies half a row of K and of V
+template <int D>
+__device__ __forceinline__ void load_tile(const Params& p, const int* table, int hk, int j0, int lo, int hi,
+                                          __nv_bfloat16* sK, __nv_bfloat16* sV) {
+  constexpr int C = D / 8, PER = C / 2;
+  const int row = threadIdx.x >> 1, c0 = (threadIdx.x & 1) * PER;
+  const int j = j0 + row;
+  bool ok = j >= lo && j < hi;
+  int blk = 0;
+  if (ok) { blk = table[j >> p.bs_log2]; ok = blk >= 0; }
+  const int64_t plane = (int64_t)p.Hkv * p.block_size * D;
+  const __nv_bfloat16* src = p.cache;
+  if (ok) src += (int64_t)blk * 2 * plane + ((int64_t)hk * p.block_size + (j & (p.block_size - 1))) * D + c0 * 8;
+  const __nv_bfloat16* srcv = ok ? src + plane : src;
+#pragma unroll
+  for (int c = 0; c < PER; ++c) {
+    cp_async16(sK + swz<D>(row, c0 + c), src + (ok ? c * 8 : 0), ok);
+    cp_async16(sV + swz<D>(row, c0 + c), srcv + (ok ? c * 8 : 0), ok);
+  }
+}
+
+template <int D, int NH8>      // NH8 tiles of 8 heads cover the group
+__global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [STAGES][BN][D]
+  __nv_bfloat16* sV = sK + STAGES * BN * D;                                   // [STAGES][BN][D]
+  __shared__ int s_last;
+  constexpr int NHEADS = NH8 * 8;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  const int b = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
+  const int t0 = p.cu_seqlens[b];
+  if (p.cu_seqlens[b + 1] - t0 != 1) return;               // not a decoded token: another kernel's request
+  const int seq_len = p.seq_lens[b];
+  const int pos = seq_len - 1;
+  const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0, hi = seq_len;
+  const int* table = p.block_table + (int64_t)b * p.max_blocks;
+  int tile_begin = lo / BN, tile_end = (hi + BN - 1) / BN;
+  {
+    const int per = (tile_end - tile_begin + p.splits - 1) / p.splits;
+    tile_begin += split * per;
+    tile_end = min(tile_end, tile_begin + per);
+  }
+  const int n_tiles = max(0, tile_end - tile_begin);
+
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) {
+    if (i < n_tiles) load_tile<D>(p, table, hk, (tile_begin + i) * BN, lo, hi, sK + i * BN * D, sV + i * BN * D);
+    cp_async_commit();
+  }
+
+  // Q^T as the B operand: head nt*8 + g, dims ks*16 + {2tq, 2tq+1} and + 8
+  unsigned qb[D / 16][NH8][2];
+#pragma unroll
+  for (int nt = 0; nt < NH8; ++nt) {
+    const int head = nt * 8 + g;
+    const __nv_bfloat16* qrow = p.q + (int64_t)t0 * p.ldq + (int64_t)(hk * p.group + head) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qb[ks][nt][0] = head < p.group ? *reinterpret_cast<const unsigned*>(qrow + ks * 16 + 2 * tq) : 0u;
+      qb[ks][nt][1] = head < p.group ? *reinterpret_cast<const unsigned*>(qrow + ks * 16 + 8 + 2 * tq) : 0u;
+    }
+  }
+
+  float ot[D / 16][NH8][4];
+#pragma unroll
+  for (int i = 0; i < D / 16; ++i)
+#pragma unroll
+    for (int nt = 0; nt < NH8; ++nt) ot[i][nt][0] = ot[i][nt][1] = ot[i][nt][2] = ot[i][nt][3] = 0.f;
+  float m_run[NH8][2], l_run[NH8][2];                       // heads nt*8 + 2tq + {0, 1}
+#pragma unroll
+  for (int nt = 0; nt < NH8; ++nt) { m_run[nt][0] = m_run[nt][1] = -INFINITY; l_run[nt][0] = l_run[nt][1] = 0.f; }
+  const int key_off = warp * 16;
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int buf = t % STAGES;
+    if (t + STAGES - 1 < n_tiles)
+      load_tile<D>(p, table, hk, (tile_begin + t + STAGES - 1) * BN, lo, hi,
+                   sK + ((t + STAGES - 1) % STAGES) * BN * D, sV + ((t + STAGES - 1) % STAGES) * BN * D);
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();
+    __syncthreads();
+    const __nv_bfloat16* kt = sK + buf * BN * D;
+    const __nv_bfloat16* vt = sV + buf * BN * D;
+    const int jbase = (tile_begin + t) * BN + key_off;
+    if (jbase < hi) {                                       // warp-uniform: this warp's 16 keys hold something
+      float st[NH8][4];
+#pragma unroll
+      for (int nt = 0; nt < NH8; ++nt) st[nt][0] = st[nt][1] = st[nt][2] = st[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        unsigned a[4];
+        ldmatrix_x4(a, kt + swz<D>(key_off + (lane & 15), ks * 2 + (lane >> 4)));
+#pragma unroll
+        for (int nt = 0; nt < NH8; ++nt) mma_bf16(st[nt], a, qb[ks][nt][0], qb[ks][nt][1]);
+      }
+      const bool vis0 = jbase + g >= lo && jbase + g <= pos;
+      const bool vis1 = jbase + g + 8 >= lo && jbase + g + 8 <= pos;
+      bool rescale = false;
+      float alpha[NH8][2];
+      unsigned pb[NH8][2];
+#pragma unroll
+      for (int nt = 0; nt < NH8; ++nt) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const float s0 = vis0 ? st[nt][c] * p.scale_log2 : -INFINITY;
+          const float s1 = vis1 ? st[nt][c + 2] * p.scale_log2 : -INFINITY;
+          float mx = fmaxf(s0, s1);
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+          const float m_new = fmaxf(m_run[nt][c], mx);
+          const float m_use = m_new == -INFINITY ? 0.f : m_new;
+          alpha[nt][c] = exp2f(m_run[nt][c] - m_use);
+          rescale |= m_new != m_run[nt][c];
+          const float p0 = exp2f(s0 - m_use), p1 = exp2f(s1 - m_use);
+          l_run[nt][c] = l_run[nt][c] * alpha[nt][c] + p0 + p1;
+          m_run[nt][c] = m_new;
+          st[nt][c] = p0;
+          st[nt][c + 2] = p1;
+        }
+        pb[nt][0] = movmatrix_trans(pack_bf16(st[nt][0], st[nt][1]));
+        pb[nt][1] = movmatrix_trans(pack_bf16(st[nt][2], st[nt][3]));
+      }
+      if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i)
+#pragma unroll
+          for (int nt = 0; nt < NH8; ++nt) {
+            ot[i][nt][0] *= alpha[nt][0]; ot[i][nt][1] *= alpha[nt][1];
+            ot[i][nt][2] *= alpha[nt][0]; ot[i][nt][3] *= alpha[nt][1];
+          }
+      }
+#pragma unroll
+      for (int db = 0; db < D / 16; ++db) {
+        unsigned a[4];
+        ldmatrix_x4_trans(a, vt + swz<D>(key_off + (lane & 7) + ((lane >> 4) << 3), db * 2 + ((lane >> 3) & 1)));
+#pragma unroll
+        for (int nt = 0; nt < NH8; ++nt) mma_bf16(ot[db][nt], a, pb[nt][0], pb[nt][1]);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- fold the four warps
+  float* sm_o = reinterpret_cast<float*>(smem_raw);          // [4][NHEADS][D]
+  float* sm_m = sm_o + 4 * NHEADS * D;                       // [4][NHEADS]
+  float* sm_l = sm_m + 4 * NHEADS;
+#pragma unroll
+  for (int nt = 0; nt < NH8; ++nt) {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      float l = l_run[nt][c];
+      l += __shfl_xor_sync(0xffffffffu, l, 4);
+      l += __shfl_xor_sync(0xffffffffu, l, 8);
+      l += __shfl_xor_sync(0xffffffffu, l, 16);
+      const int head = nt * 8 + 2 * tq + c;
+      if (g == 0) { sm_m[warp * NHEADS + head] = m_run[nt][c]; sm_l[warp * NHEADS + head] = l; }
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i) {
+        sm_o[(warp * NHEADS + head) * D + i * 16 + g] = ot[i][nt][c];
+        sm_o[(warp * NHEADS + head) * D + i * 16 + g + 8] = ot[i][nt][c + 2];
+      }
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < p.group * D; idx += NT) {
+    const int head = idx / D, d = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * NHEADS + head]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sm_m[w * NHEADS + head];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += sm_l[w * NHEADS + head] * f;
+      acc += sm_o[(w * NHEADS + head) * D + d] * f;
+    }
+    const int gh = hk * p.group + head;
+    if (p.splits == 1) {
+      p.out[(int64_t)t0 * p.ldo + (int64_t)gh * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    } else {
+      const int64_t slot = ((int64_t)b * p.H + gh) * p.splits + split;
+      p.part_o[slot * D + d] = acc;
+      if (d == 0) { p.part_ml[slot * 2] = M; p.part_ml[slot * 2 + 1] = L; }
+    }
+  }
+  if (p.splits == 1) return;
+
+  // ---- fold the splits: the CTA that arrives last does it
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&p.counters[b * p.Hkv + hk], 1) == p.splits - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < p.group * D; idx += NT) {
+    const int head = idx / D, d = idx % D;
+    const int gh = hk * p.group + head;
+    const int64_t base = ((int64_t)b * p.H + gh) * p.splits;
+    float M = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (base + s) * 2));
+    float L = 0.f, acc = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+      const float ms = __ldcg(p.part_ml + (base + s) * 2);
+      const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+      L += __ldcg(p.part_ml + (base + s) * 2 + 1) * f;
+      acc += __ldcg(p.part_o + (base + s) * D + d) * f;
+    }
+    p.out[(int64_t)t0 * p.ldo + (int64_t)gh * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+  if (threadIdx.x == 0) p.counters[b * p.Hkv + hk] = 0;      // ready for the next launch
+}
+
+template <int D, int NH8>
+int launch(const Params& p, int B, cudaStream_t stream) {
+  auto k = attention_decode_kernel<D, NH8>;
+  size_t sm = (size_t)2 * STAGES * BN * D * sizeof(__nv_bfloat16);
+  const size_t fold = (size_t)(4 * NH8 * 8 * D + 2 * 4 * NH8 * 8) * sizeof(float);
+  if (fold > sm) sm = fold;
+  static bool opted = false;
+  if (!opted) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    if (e != cudaSuccess) return refuse((int)e, "attention_decode: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    opted = true;
+  }
+  k<<<dim3(p.splits, p.Hkv, B), NT, sm, stream>>>(p);
+  return cuda_status("attention_decode");
+}
+
+}  // namespace
+
+DINFER_DEFINE_LAST_ERROR()
+
+DINFER_API int dinfer_attention_decode_supports(int D, int group, int block_size) {
+  return (D == 64 || D == 128) && group >= 1 && group <= 16 && block_size > 0 && (block_size & (block_size - 1)) == 0;
+}
+
+// Scratch for `splits` > 1: floats [B*H*splits*(D+2)] then ints [B*Hkv] that must be zero before the
+// first launch (every launch leaves them zero).  Launches that share the scratch must not overlap.
+DINFER_API int64_t dinfer_attention_decode_scratch_bytes(int B, int H, int Hkv, int D, int splits) {
+  return splits > 1 ? ((int64_t)B * H * splits * (D + 2) + (int64_t)B * Hkv) * 4 : 0;
+}
+
+// Requests whose portion is not exactly one token are skipped (left to the prompt kernel).
+DINFER_API int dinfer_attention_decode(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                       const int* block_table, int max_blocks, const int* cu_seqlens,
+                                       const int* seq_lens, int B, int H, int Hkv, int D, int block_size,
+                                       float scale, int window, int splits, float* scratch_floats,
+                                       int* scratch_counters, cudaStream_t stream) {
+  if (B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || max_blocks <= 0)
+    return refuse(DINFER_BAD_ARGUMENT, "attention_decode: bad sizes B=%d H=%d Hkv=%d", B, H, Hkv);
+  if (!dinfer_attention_decode_supports(D, H / Hkv, block_size))
+    return refuse(DINFER_BAD_ARGUMENT, "attention_decode: head_dim %d, group %d, block_size %d not supported "
+                  "(head_dim 64 or 128, group <= 16, power-of-two pages)", D, H / Hkv, block_size);
+  if ((ldq % 2) || (ldo % 2) || (reinterpret_cast<uintptr_t>(q) & 3) || (reinterpret_cast<uintptr_t>(cache) & 15))
+    return refuse(DINFER_BAD_ARGUMENT, "attention_decode: q rows must be 4-byte and the cache 16-byte aligned");
+  if (splits < 1 || (splits > 1 && (!scratch_floats || !scratch_counters)))
+    return refuse(DINFER_BAD_ARGUMENT, "attention_decode: splits=%d needs scratch", splits);
+  if (Hkv > 65535 || B > 65535) return refuse(DINFER_BAD_ARGUMENT, "attention_decode: too many heads or requests for the grid");
+  Params p;
+  p.q = (const __nv_bfloat16*)q; p.ldq = ldq; p.out = (__nv_bfloat16*)out; p.ldo = ldo;
+  p.cache = (const __nv_bfloat16*)cache; p.block_table = block_table; p.max_blocks = max_blocks;
+  p.cu_seqlens = cu_seqlens; p.seq_lens = seq_lens; p.H = H; p.Hkv = Hkv; p.group = H / Hkv;
+  p.block_size = block_size; p.bs_log2 = 0;
+  while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
+  p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.splits = splits;
+  p.part_o = scratch_floats;
+  p.part_ml = scratch_floats ? scratch_floats + (int64_t)B * H * splits * D : nullptr;
+  p.counters = scratch_counters;
+  const int nh8 = (p.group + 7) / 8;
+  if (D == 64) return nh8 == 1 ? launch<64, 1>(p, B, stream) : launch<64, 2>(p, B, stream);
+  return nh8 == 1 ? launch<128, 1>(p, B, stream) : launch<128, 2>(p, B, stream);
+}

@@ -1,9 +1,9 @@
 // Paged causal attention on the tensor cores, bfloat16, head sizes 32 / 64 / 128.
 //
 // One kernel body, two shapes of work:
-//   * prompt portions (q_len > 1): a CTA owns 64 "rows" of one (request, kv head).  A row is a
+//   * prompt portions (q_len > 1): a CTA owns 128 "rows" of one (request, kv head).  A row is a
 //     (token, query head of the group) pair, so the query heads that share a kv head also share
-//     every K/V tile read from the cache.  Four warps of 16 rows walk the visible keys in tiles
+//     every K/V tile read from the cache.  Eight warps of 16 rows walk the visible keys in tiles
 //     of 64 with an online softmax (exp2 domain, 32-bit), K/V staged in shared memory by
 //     cp.async with double buffering, fragments by ldmatrix, products by mma.m16n8k16.
 //   * decoded tokens (q_len == 1): the rows are just the group's heads (<= 16), so the keys are
@@ -23,10 +23,12 @@ using namespace dinfer;
 
 namespace {
 
-constexpr int NT = 128;        // threads per CTA
-constexpr int BM = 64;         // rows per CTA (prompt shape)
+constexpr int NT_DECODE = 128; // threads per CTA, decode shape
+constexpr int NT_PROMPT = 256; // threads per CTA, prompt shape: eight warps of 16 rows
+constexpr int BM = 128;        // rows per CTA (prompt shape)
 constexpr int BN = 64;         // keys per tile
-constexpr int STAGES = 2;
+constexpr int STAGES_PROMPT = 2;   // K/V tiles in flight per CTA
+constexpr int STAGES_DECODE = 3;   // decode is bound by memory latency: one more tile in flight
 
 struct Params {
   const __nv_bfloat16* q; int64_t ldq;
@@ -77,7 +79,7 @@ template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
 }
 
 // Stage one K and one V tile: keys [j0, j0 + 64) of kv head hk; rows outside [lo, hi) are zero-filled.
-template <int D>
+template <int D, int NT>
 __device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, int hk, int j0, int lo, int hi,
                                              __nv_bfloat16* sK, __nv_bfloat16* sV) {
   constexpr int C = D / 8;
@@ -99,7 +101,9 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, 
 }
 
 template <int D, bool DECODE>
-__global__ void __launch_bounds__(NT) attention_tc_kernel(const Params p) {
+__global__ void __launch_bounds__(DECODE ? NT_DECODE : NT_PROMPT, 2) attention_tc_kernel(const Params p) {
+  constexpr int NT = DECODE ? NT_DECODE : NT_PROMPT;
+  constexpr int STAGES = DECODE ? STAGES_DECODE : STAGES_PROMPT;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [BM][D] (16 rows when DECODE)
   __nv_bfloat16* sK = sQ + (DECODE ? 16 : BM) * D;                                  // [STAGES][BN][D]
@@ -144,15 +148,18 @@ __global__ void __launch_bounds__(NT) attention_tc_kernel(const Params p) {
       cp_async16(sQ + swz<D>(r, chunk), src, ok);
     }
   }
-  if (n_tiles > 0) load_kv_tile<D>(p, table, hk, tile_begin * BN, lo, hi, sK, sV);
-  cp_async_commit();
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) {      // Q rides in the first group
+    if (i < n_tiles) load_kv_tile<D, NT>(p, table, hk, (tile_begin + i) * BN, lo, hi, sK + i * BN * D, sV + i * BN * D);
+    cp_async_commit();
+  }
 
   // per-thread softmax state for rows g and g + 8 of the warp's 16 rows
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o[D / 8][4];
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-  unsigned qf[D / 16][4];
+  unsigned qf[DECODE ? D / 16 : 1][4];   // decode keeps Q's fragments; the prompt shape reloads them (registers)
 
   const int wrow = DECODE ? 0 : warp * 16;                 // first row of this warp inside the CTA's rows
   int pos_r[2];                                            // position of the query of rows g, g + 8 (-1: no row)
@@ -166,15 +173,15 @@ __global__ void __launch_bounds__(NT) attention_tc_kernel(const Params p) {
 
   for (int t = 0; t < n_tiles; ++t) {
     const int buf = t % STAGES;
-    if (t + 1 < n_tiles)
-      load_kv_tile<D>(p, table, hk, (tile_begin + t + 1) * BN, lo, hi, sK + ((t + 1) % STAGES) * BN * D,
-                      sV + ((t + 1) % STAGES) * BN * D);
+    if (t + STAGES - 1 < n_tiles)
+      load_kv_tile<D, NT>(p, table, hk, (tile_begin + t + STAGES - 1) * BN, lo, hi,
+                          sK + ((t + STAGES - 1) % STAGES) * BN * D, sV + ((t + STAGES - 1) % STAGES) * BN * D);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<STAGES - 1>();
     __syncthreads();
-    if (t == 0) {
+    if (DECODE && t == 0) {
 #pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks)
+      for (int ks = 0; ks < (DECODE ? D / 16 : 1); ++ks)
         ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], sQ + swz<D>(wrow + (lane & 15), ks * 2 + (lane >> 4)));
     }
     const __nv_bfloat16* kt = sK + buf * BN * D;
@@ -186,12 +193,18 @@ __global__ void __launch_bounds__(NT) attention_tc_kernel(const Params p) {
     for (int i = 0; i < NK / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
+      unsigned qa[4];
+      if (DECODE) {
+        qa[0] = qf[DECODE ? ks : 0][0]; qa[1] = qf[DECODE ? ks : 0][1]; qa[2] = qf[DECODE ? ks : 0][2]; qa[3] = qf[DECODE ? ks : 0][3];
+      } else {
+        ldmatrix_x4(qa[0], qa[1], qa[2], qa[3], sQ + swz<D>(wrow + (lane & 15), ks * 2 + (lane >> 4)));
+      }
 #pragma unroll
       for (int nb = 0; nb < NK / 16; ++nb) {
         unsigned b0, b1, b2, b3;
         ldmatrix_x4(b0, b1, b2, b3, kt + swz<D>(key_off + nb * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
-        mma_bf16(s[nb * 2], qf[ks], b0, b1);
-        mma_bf16(s[nb * 2 + 1], qf[ks], b2, b3);
+        mma_bf16(s[nb * 2], qa, b0, b1);
+        mma_bf16(s[nb * 2 + 1], qa, b2, b3);
       }
     }
     // scale into the exp2 domain and mask by position
@@ -334,7 +347,7 @@ __global__ void __launch_bounds__(D) attention_merge_kernel(const Params p) {
 }
 
 template <int D, bool DECODE> size_t smem_bytes() {
-  const size_t tiles = (size_t)((DECODE ? 16 : BM) + 2 * STAGES * BN) * D * sizeof(__nv_bfloat16);
+  const size_t tiles = (size_t)((DECODE ? 16 : BM) + 2 * (DECODE ? STAGES_DECODE : STAGES_PROMPT) * BN) * D * sizeof(__nv_bfloat16);
   const size_t fold = DECODE ? (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float) : 0;
   return tiles > fold ? tiles : fold;
 }
@@ -351,7 +364,7 @@ int launch(const Params& p, int B, int max_q_len, bool any_decode, bool any_pref
       opted = true;
     }
     dim3 grid(((int64_t)max_q_len * p.group + BM - 1) / BM, p.Hkv, B);
-    k<<<grid, NT, sm, stream>>>(p);
+    k<<<grid, NT_PROMPT, sm, stream>>>(p);
   }
   if (any_decode) {
     auto k = attention_tc_kernel<D, true>;
@@ -363,7 +376,7 @@ int launch(const Params& p, int B, int max_q_len, bool any_decode, bool any_pref
       opted = true;
     }
     dim3 grid(p.splits, p.Hkv, B);
-    k<<<grid, NT, sm, stream>>>(p);
+    k<<<grid, NT_DECODE, sm, stream>>>(p);
     if (p.splits > 1) attention_merge_kernel<D><<<dim3(p.H, B), D, 0, stream>>>(p);
   }
   return cuda_status("attention_tc");

@@ -34,6 +34,7 @@ LIBRARIES: Dict[str, tuple] = {
     "gemm_f32": ("gemm_f32.cu", []),
     "sampling": ("sampling.cu", []),
     "attention_tc": ("attention_tc.cu", []),
+    "attention_decode": ("attention_decode.cu", []),
 }
 
 

@@ -14,6 +14,29 @@ using namespace dinfer;
 
 namespace {
 
+// four consecutive elements at once (16 bytes of f32, 8 bytes of bf16)
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 x = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, const float (&v)[4]);
+template <> __device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+  uint2 x;
+  *reinterpret_cast<__nv_bfloat162*>(&x.x) = __floats2bfloat162_rn(v[0], v[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&x.y) = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p) = x;
+}
+
 template <typename TA, typename TW, int VEC>
 __global__ void __launch_bounds__(1024)
 rmsnorm_kernel(float* __restrict__ residual, const TA* __restrict__ delta, const int* __restrict__ rows,
@@ -29,19 +52,21 @@ rmsnorm_kernel(float* __restrict__ residual, const TA* __restrict__ delta, const
 
   float ss = 0.f;
   for (int i = threadIdx.x * VEC; i < h; i += blockDim.x * VEC) {
-    float v[VEC];
+    float v[4];
     if (VEC == 4) {
-      const float4 x = *reinterpret_cast<const float4*>(res + i);
-      v[0] = x.x; v[1 % VEC] = x.y; v[2 % VEC] = x.z; v[3 % VEC] = x.w;
+      load4<float>(res + i, v);
+      if (del) {
+        float d[4];
+        load4<TA>(del + i, d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] += d[j];
+        if (writeback) store4<float>(res + i, v);
+      }
     } else {
       v[0] = res[i];
-    }
-    if (del) {
-#pragma unroll
-      for (int j = 0; j < VEC; ++j) v[j] += to_f32<TA>(del[i + j]);
-      if (writeback) {
-        if (VEC == 4) *reinterpret_cast<float4*>(res + i) = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
-        else res[i] = v[0];
+      if (del) {
+        v[0] += to_f32<TA>(del[i]);
+        if (writeback) res[i] = v[0];
       }
     }
 #pragma unroll
@@ -53,12 +78,19 @@ rmsnorm_kernel(float* __restrict__ residual, const TA* __restrict__ delta, const
   ss = block_sum(ss, red);
   const float rinv = rsqrtf(ss / (float)h + eps);
   for (int i = threadIdx.x * VEC; i < h; i += blockDim.x * VEC) {
+    float v[4], w[4];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
-      float v;
-      if (stash) v = sm_row[i + j];
-      else v = res[i + j] + ((del && !writeback) ? to_f32<TA>(del[i + j]) : 0.f);
-      o[i + j] = from_f32<TA>(v * rinv * to_f32<TW>(weight[i + j]));
+      if (stash) v[j] = sm_row[i + j];
+      else v[j] = res[i + j] + ((del && !writeback) ? to_f32<TA>(del[i + j]) : 0.f);
+    }
+    if (VEC == 4) {
+      load4<TW>(weight + i, w);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = v[j] * rinv * w[j];
+      store4<TA>(o + i, v);
+    } else {
+      o[i] = from_f32<TA>(v[0] * rinv * to_f32<TW>(weight[i]));
     }
   }
 }
@@ -67,7 +99,8 @@ template <typename TA, typename TW>
 int launch(float* residual, const void* delta, const int* rows, const void* weight, void* out,
            int num_rows, int h, float eps, cudaStream_t stream) {
   if (num_rows == 0) return 0;
-  const bool vec4 = (h % 4 == 0) && ((reinterpret_cast<uintptr_t>(residual) & 15) == 0);
+  const auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const bool vec4 = (h % 4 == 0) && al(residual) && al(delta) && al(weight) && al(out);
   const int per = vec4 ? 4 : 1;
   int threads = (h / per + 31) / 32 * 32;
   if (threads > 1024) threads = 1024;

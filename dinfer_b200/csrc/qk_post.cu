@@ -15,14 +15,40 @@ namespace {
 constexpr int WARPS = 8;
 constexpr int MAX_D = 512;
 
-template <typename TA, typename TW>
+// eight consecutive elements at once
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 x = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float (&v)[8]);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 x;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&x);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+  *reinterpret_cast<uint4*>(p) = x;
+}
+
+// One warp per (token, head); a lane owns runs of 8 elements (VEC8) or single elements.
+template <typename TA, typename TW, bool VEC8>
 __global__ void __launch_bounds__(WARPS * 32)
 qk_post_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ positions,
                const TW* __restrict__ q_weight, const TW* __restrict__ k_weight, float eps,
                const float* __restrict__ cos_sin, int rot,
                TA* __restrict__ cache, const int* __restrict__ slots, int block_size,
                int H, int Hkv, int D) {
-  __shared__ float sm[WARPS][MAX_D];
+  __shared__ __align__(16) float sm[WARPS][MAX_D];
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y * WARPS + warp;
@@ -30,18 +56,29 @@ qk_post_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ positio
   const int kind = head < H ? 0 : (head < H + Hkv ? 1 : 2);   // q, k, v
   TA* x = qkv + (int64_t)t * ld + (int64_t)head * D;
   float* xs = sm[warp];
+  constexpr int STEP = VEC8 ? 8 : 1;
 
   const TW* w = kind == 0 ? q_weight : (kind == 1 ? k_weight : nullptr);
   float ss = 0.f;
-  for (int e = lane; e < D; e += 32) {
-    const float v = to_f32<TA>(x[e]);
-    xs[e] = v;
-    ss += v * v;
+  for (int e = lane * STEP; e < D; e += 32 * STEP) {
+    if (VEC8) {
+      float v[8];
+      load8<TA>(x + e, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { xs[e + j] = v[j]; ss += v[j] * v[j]; }
+    } else {
+      const float v = to_f32<TA>(x[e]);
+      xs[e] = v;
+      ss += v * v;
+    }
   }
   if (w) {
     ss = warp_sum(ss);
     const float rinv = rsqrtf(ss / (float)D + eps);
-    for (int e = lane; e < D; e += 32) xs[e] = xs[e] * rinv * to_f32<TW>(w[e]);
+    for (int e = lane * STEP; e < D; e += 32 * STEP) {
+#pragma unroll
+      for (int j = 0; j < STEP; ++j) xs[e + j] = xs[e + j] * rinv * to_f32<TW>(w[e + j]);
+    }
   }
   __syncwarp();
 
@@ -55,18 +92,99 @@ qk_post_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ positio
     }
   }
   const bool rotate = cos_sin != nullptr && kind != 2;
+  const bool rewrite = kind != 2 && (w || rotate);
   const int half = rot >> 1;
   const float* cs = rotate ? cos_sin + (int64_t)positions[t] * rot : nullptr;
-  for (int e = lane; e < D; e += 32) {
-    float v = xs[e];
-    if (rotate && e < rot) {
-      if (e < half) v = v * cs[e] - xs[e + half] * cs[half + e];
-      else          v = v * cs[e - half] + xs[e - half] * cs[e];
+  for (int e0 = lane * STEP; e0 < D; e0 += 32 * STEP) {
+    float r[8];
+#pragma unroll
+    for (int j = 0; j < STEP; ++j) {
+      const int e = e0 + j;
+      float v = xs[e];
+      if (rotate && e < rot) {
+        if (e < half) v = v * cs[e] - xs[e + half] * cs[half + e];
+        else          v = v * cs[e - half] + xs[e - half] * cs[e];
+      }
+      r[j] = v;
     }
-    const TA r = from_f32<TA>(v);
-    if (kind != 2 && (w || rotate)) x[e] = r;
-    if (dst) dst[e] = r;
+    if (VEC8) {
+      if (rewrite) store8<TA>(x + e0, r);
+      if (dst) store8<TA>(dst + e0, r);
+    } else {
+      const TA o = from_f32<TA>(r[0]);
+      if (rewrite) x[e0] = o;
+      if (dst) dst[e0] = o;
+    }
   }
+}
+
+// Fast shape: bfloat16/f32 with D = 32 * EPL and the rotation over the whole head.  A lane owns EPL
+// consecutive elements in registers; its rotation partner (D/2 away) sits 16 lanes across.
+template <typename TA, typename TW, int EPL>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_post_lanes_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ positions,
+                     const TW* __restrict__ q_weight, const TW* __restrict__ k_weight, float eps,
+                     const float* __restrict__ cos_sin, TA* __restrict__ cache, const int* __restrict__ slots,
+                     int block_size, int H, int Hkv) {
+  constexpr int D = 32 * EPL;
+  struct alignas(sizeof(TA) * EPL) Vec { TA v[EPL]; };
+  struct alignas(sizeof(TW) * EPL) WVec { TW v[EPL]; };
+  struct alignas(sizeof(float) * EPL) FVec { float v[EPL]; };
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * WARPS + warp;
+  if (head >= H + 2 * Hkv) return;
+  const int kind = head < H ? 0 : (head < H + Hkv ? 1 : 2);
+  TA* x = qkv + (int64_t)t * ld + (int64_t)head * D + lane * EPL;
+  const Vec in = *reinterpret_cast<const Vec*>(x);
+  float v[EPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) { v[j] = to_f32<TA>(in.v[j]); ss += v[j] * v[j]; }
+  const TW* w = kind == 0 ? q_weight : (kind == 1 ? k_weight : nullptr);
+  if (w) {
+    ss = warp_sum(ss);
+    const float rinv = rsqrtf(ss / (float)D + eps);
+    const WVec wv = *reinterpret_cast<const WVec*>(w + lane * EPL);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) v[j] = v[j] * rinv * to_f32<TW>(wv.v[j]);
+  }
+  const bool rotate = cos_sin != nullptr && kind != 2;
+  if (rotate) {
+    const float* cs = cos_sin + (int64_t)positions[t] * D;
+    const int i = (lane & 15) * EPL;                        // index of the pair inside the half
+    const FVec c = *reinterpret_cast<const FVec*>(cs + i);
+    const FVec s = *reinterpret_cast<const FVec*>(cs + D / 2 + i);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+      v[j] = lane < 16 ? v[j] * c.v[j] - other * s.v[j] : v[j] * c.v[j] + other * s.v[j];
+    }
+  }
+  Vec out;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) out.v[j] = from_f32<TA>(v[j]);
+  if (kind != 2 && (w || rotate)) *reinterpret_cast<Vec*>(x) = out;
+  if (cache && kind != 0) {
+    const int slot = slots[t];
+    if (slot >= 0) {
+      const int64_t blk = slot / block_size, off = slot % block_size;
+      const int hk = kind == 1 ? head - H : head - H - Hkv;
+      TA* dst = cache + ((((blk * 2 + (kind - 1)) * Hkv + hk) * block_size + off) * (int64_t)D) + lane * EPL;
+      *reinterpret_cast<Vec*>(dst) = out;
+    }
+  }
+}
+
+template <typename TA, typename TW>
+void launch_lanes(dim3 grid, cudaStream_t stream, TA* qkv, int64_t ld, const int* positions, const TW* qw,
+                  const TW* kw, float eps, const float* cos_sin, TA* cache, const int* slots, int block_size,
+                  int H, int Hkv, int D) {
+  const int threads = WARPS * 32;
+  if (D == 32) qk_post_lanes_kernel<TA, TW, 1><<<grid, threads, 0, stream>>>(qkv, ld, positions, qw, kw, eps, cos_sin, cache, slots, block_size, H, Hkv);
+  else if (D == 64) qk_post_lanes_kernel<TA, TW, 2><<<grid, threads, 0, stream>>>(qkv, ld, positions, qw, kw, eps, cos_sin, cache, slots, block_size, H, Hkv);
+  else if (D == 128) qk_post_lanes_kernel<TA, TW, 4><<<grid, threads, 0, stream>>>(qkv, ld, positions, qw, kw, eps, cos_sin, cache, slots, block_size, H, Hkv);
+  else qk_post_lanes_kernel<TA, TW, 8><<<grid, threads, 0, stream>>>(qkv, ld, positions, qw, kw, eps, cos_sin, cache, slots, block_size, H, Hkv);
 }
 
 }  // namespace
@@ -94,9 +212,25 @@ DINFER_API int dinfer_qk_post(void* qkv, int64_t ld, const int* positions, const
   dim3 grid(T, (heads + WARPS - 1) / WARPS);
   DINFER_DISPATCH_DTYPE(act_dtype, TA,
     DINFER_DISPATCH_DTYPE(w_dtype, TW, {
-      qk_post_kernel<TA, TW><<<grid, WARPS * 32, 0, stream>>>(
-          (TA*)qkv, ld, positions, (const TW*)q_weight, (const TW*)k_weight, eps, cos_sin, rot,
-          (TA*)cache, slots, block_size, H, Hkv, D);
+      const bool aligned = ld % 8 == 0 && !(reinterpret_cast<uintptr_t>(qkv) & 31) &&
+                           !(reinterpret_cast<uintptr_t>(cache) & 31) && !(reinterpret_cast<uintptr_t>(q_weight) & 31) &&
+                           !(reinterpret_cast<uintptr_t>(k_weight) & 31) && !(reinterpret_cast<uintptr_t>(cos_sin) & 31);
+      if (aligned && (!cos_sin || rot == D) && (D == 32 || D == 64 || D == 128 || D == 256)) {
+        launch_lanes<TA, TW>(grid, stream, (TA*)qkv, ld, positions, (const TW*)q_weight, (const TW*)k_weight, eps,
+                             cos_sin, (TA*)cache, slots, block_size, H, Hkv, D);
+        return cuda_status("qk_post");
+      }
+      // 8-wide accesses need rows, heads and cache slots that start on 32-byte (f32) / 16-byte (bf16) bounds
+      const bool vec8 = D % 8 == 0 && ld % 8 == 0 && !(reinterpret_cast<uintptr_t>(qkv) & 31) &&
+                        !(reinterpret_cast<uintptr_t>(cache) & 31);
+      if (vec8)
+        qk_post_kernel<TA, TW, true><<<grid, WARPS * 32, 0, stream>>>(
+            (TA*)qkv, ld, positions, (const TW*)q_weight, (const TW*)k_weight, eps, cos_sin, rot,
+            (TA*)cache, slots, block_size, H, Hkv, D);
+      else
+        qk_post_kernel<TA, TW, false><<<grid, WARPS * 32, 0, stream>>>(
+            (TA*)qkv, ld, positions, (const TW*)q_weight, (const TW*)k_weight, eps, cos_sin, rot,
+            (TA*)cache, slots, block_size, H, Hkv, D);
       return cuda_status("qk_post");
     }));
   return 0;

@@ -17,12 +17,68 @@ def tc_supported(dtype: torch.dtype, head_dim: int, group: int) -> bool:
 
 
 def decode_splits(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
-    """Key splits of the decode shape: enough CTAs to fill the GPU about twice, never more than
-    there are 64-key tiles, at most 32."""
+    """Key splits of the decode shape.  Two CTAs fit an SM; with few (request, kv head) pairs the
+    splits fill those slots in one wave, with many they cut the work into about eight waves so that
+    the last wave's idle SMs cost little.  Never more than a quarter of the 64-key tiles, at most 32."""
+    slots = 2 * NUM_SMS
     base = max(1, num_reqs * num_kv_heads)
-    want = (2 * NUM_SMS + base - 1) // base
+    want = slots // base if base <= slots else (8 * slots + base - 1) // base
     tiles = max(1, (max_seq_len + 63) // 64)
-    return max(1, min(want, tiles, 32))
+    return max(1, min(want, max(1, tiles // 4), 32))
+
+
+def decode_supported(dtype: torch.dtype, head_dim: int, group: int, block_size: int) -> bool:
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and 1 <= group <= 16
+            and block_size > 0 and block_size & (block_size - 1) == 0)
+
+
+# Scratch of the split-key decode kernel, per device: f32 partial sums and a block of counters that
+# every launch leaves at zero.  Buffers are only ever replaced by larger ones and the old ones are
+# kept alive, because a captured CUDA graph holds their addresses.  All launches that use it run on
+# one stream (they must not overlap).
+_SCRATCH = {}
+_SCRATCH_KEEP = []
+
+
+def _decode_scratch(device, n_floats: int, n_counters: int):
+    cur = _SCRATCH.get(device)
+    if cur is None or cur[0].numel() < n_floats or cur[1].numel() < n_counters:
+        floats = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
+        counters = torch.zeros(max(n_counters, 1 << 14), dtype=torch.int32, device=device)
+        if cur is not None:
+            _SCRATCH_KEEP.append(cur)
+        cur = (floats, counters)
+        _SCRATCH[device] = cur
+    return cur
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                     cu_seqlens: torch.Tensor, seq_lens: torch.Tensor, num_heads: int, num_kv_heads: int,
+                     head_dim: int, scale: float, window: int, splits: int) -> torch.Tensor:
+    """Attention of the requests that bring exactly one token (the others are skipped), keys split
+    ``splits`` ways; the splits are folded inside the kernel."""
+    require_cuda(q, out, cache, block_table, cu_seqlens, seq_lens)
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("attention_decode: bfloat16 only")
+    if q.stride(-1) != 1 or out.stride(-1) != 1 or not cache.is_contiguous():
+        raise KernelError("attention_decode: contiguous last axes and a contiguous cache")
+    B = cu_seqlens.numel() - 1
+    for t, n in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (seq_lens, "seq_lens")):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError(f"attention_decode: {n} must be contiguous int32")
+    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
+        raise KernelError(f"attention_decode: cache shape {tuple(cache.shape)} is not [blocks, 2, Hkv, block, D]")
+    floats = counters = None
+    if splits > 1:
+        floats, counters = _decode_scratch(q.device, B * num_heads * splits * (head_dim + 2), B * num_kv_heads)
+    lib, f = _fn("attention_decode", "dinfer_attention_decode",
+                 [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                  c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), ptr(block_table), block_table.shape[1],
+                 ptr(cu_seqlens), ptr(seq_lens), B, num_heads, num_kv_heads, head_dim, cache.shape[3],
+                 float(scale), int(window), int(splits), ptr(floats), ptr(counters), stream_handle()),
+          "attention_decode")
+    return out
 
 
 def attention_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,

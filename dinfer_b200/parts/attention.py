@@ -75,9 +75,12 @@ class GQAttention(Mixer):
         return KvCacheNeed(self.Hkv, self.D, self.window)
 
     def kernel_libraries(self):
-        att = ("attention_tc" if attention_ops.tc_supported(self.env.act_dtype, self.D, self.H // self.Hkv)
-               else "attention_generic")
-        return ["qk_post", att] + self.qkv.kernel_libraries() + self.o.kernel_libraries()
+        att = ["attention_generic"]
+        if attention_ops.tc_supported(self.env.act_dtype, self.D, self.H // self.Hkv):
+            att = ["attention_tc"]
+            if self.D in (64, 128):
+                att.append("attention_decode")
+        return ["qk_post"] + att + self.qkv.kernel_libraries() + self.o.kernel_libraries()
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
         H, Hkv, D = self.H, self.Hkv, self.D
@@ -108,9 +111,16 @@ class GQAttention(Mixer):
         window = int(self.window or 0)
         if attention_ops.tc_supported(q.dtype, self.D, self.H // self.Hkv):
             splits = ctx.decode_splits or attention_ops.decode_splits(ctx.num_reqs, self.Hkv, ctx.max_seq_len)
-            attention_ops.attention_tc(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H, self.Hkv,
-                                       self.D, self.scale, window, ctx.max_q_len, ctx.any_decode, ctx.any_prefill,
-                                       splits)
+            tc_decode = ctx.any_decode
+            if ctx.any_decode and attention_ops.decode_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size):
+                # decoded tokens: the kernel made for them (keys on the tile's rows, in-kernel fold)
+                attention_ops.attention_decode(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
+                                               self.Hkv, self.D, self.scale, window, splits)
+                tc_decode = False
+            if tc_decode or ctx.any_prefill:
+                attention_ops.attention_tc(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
+                                           self.Hkv, self.D, self.scale, window, ctx.max_q_len, tc_decode,
+                                           ctx.any_prefill, splits)
         else:
             ops.attention_generic(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.positions, self.H, self.Hkv,
                                   self.D, self.scale, window)

@@ -50,6 +50,34 @@ def test_decode_splits(splits):
     run_tc(reqs, 8, 2, 128, 16, 100, splits, seed=splits + 100)
 
 
+@pytest.mark.parametrize("H,Hkv,D,bs", [(8, 2, 128, 16), (32, 8, 128, 16), (3, 3, 128, 4), (8, 1, 64, 32),
+                                        (16, 1, 128, 16), (12, 1, 64, 1), (10, 2, 64, 8)])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("splits", [1, 4, 7])
+def test_decode_kernel(H, Hkv, D, bs, window, splits):
+    """The decode kernel (keys on the tile's rows, splits folded in the kernel) against the plain
+    formula; a prompt portion in the batch must be left alone; two launches in a row share the scratch."""
+    from dinfer_b200.kernels import attention_ops as A
+    from test_kernels_gpu import paged_case, plain_paged
+    reqs = [(1000, 1), (63, 1), (0, 1), (129, 1), (40, 6), (2047, 1), (64, 1), (15, 1)]
+    rng = random.Random(H * D + bs + splits)
+    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, torch.bfloat16)
+    seq = torch.tensor([h + n for h, n in reqs], dtype=torch.int32)
+    scale = D ** -0.5
+    want = plain_paged(reqs, qs, ks, vs, scale, window).reshape(-1, H * D)
+    dec_rows = [int(cu[i]) for i, (_, n) in enumerate(reqs) if n == 1]
+    other = [r for r in range(q.shape[0]) if r not in dec_rows]
+    dq, dc, dt, dcu, dseq = q.reshape(-1, H * D).cuda(), cache.cuda(), table.cuda(), cu.cuda(), seq.cuda()
+    for _ in range(2):
+        out = torch.full((q.shape[0], H * D), 7.0, dtype=torch.bfloat16, device="cuda")
+        A.attention_decode(dq, out, dc, dt, dcu, dseq, H, Hkv, D, scale, window or 0, splits)
+        got = out.double().cpu()
+        assert torch.isfinite(got).all()
+        assert float((got[dec_rows] - want[dec_rows]).abs().max()) < 2e-2
+        assert float(torch.nn.functional.cosine_similarity(got[dec_rows], want[dec_rows], dim=-1).min()) > 0.999
+        assert bool((got[other] == 7.0).all())
+
+
 def test_long_prompt_portions():
     run_tc([(0, 700), (900, 300)], 8, 2, 128, 16, None, 1, seed=1)
     run_tc([(0, 700), (900, 300)], 3, 1, 64, 16, 257, 1, seed=2)
