@@ -8,7 +8,7 @@
 //                                                                       B = P^T by movmatrix.trans)
 // so a group of up to 8 query heads costs one n8 tile and nothing is padded to 16 rows.
 // Grid (split, kv head, request): a CTA walks a range of 64-key tiles with a 3-deep cp.async
-// pipeline (one page-table lookup and one address per thread and tile); each of its four warps takes
+// pipeline (the page-table slice of its keys staged in shared memory first); each of its four warps takes
 // 16 keys of every tile with its own running max / sum; warps fold in shared memory; splits fold
 // through f32 partials in scratch, by whichever CTA of the (request, kv head) arrives last (a counter
 // in the same scratch, left at zero again for the next launch).
@@ -24,6 +24,7 @@ namespace {
 constexpr int NT = 128;
 constexpr int BN = 64;
 constexpr int STAGES = 3;
+constexpr int TABLE_SLOTS = 1024;  // page-table entries of the CTA's key range kept in shared memory
 
 struct Params {
   const __nv_bfloat16* q; int64_t ldq;
@@ -75,24 +76,34 @@ template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
   return row * D + ((chunk ^ (row % (C >= 8 ? 8 : C))) << 3);
 }
 
-// keys [j0, j0 + 64) of kv head hk into one stage; a thread copies half a row of K and of V
+// keys [j0, j0 + 64) of kv head hk into one stage
+// The page-table entries of the CTA's keys are staged in shared memory once (s_table, entry 0 = page
+// `table_first`), so that a tile's loads do not wait for a dependent global read of the table.
 template <int D>
-__device__ __forceinline__ void load_tile(const Params& p, const int* table, int hk, int j0, int lo, int hi,
+__device__ __forceinline__ void load_tile(const Params& p, const int* table, const int* s_table, int table_first,
+                                          int hk, int j0, int lo, int hi,
                                           __nv_bfloat16* sK, __nv_bfloat16* sV) {
-  constexpr int C = D / 8, PER = C / 2;
-  const int row = threadIdx.x >> 1, c0 = (threadIdx.x & 1) * PER;
-  const int j = j0 + row;
-  bool ok = j >= lo && j < hi;
-  int blk = 0;
-  if (ok) { blk = table[j >> p.bs_log2]; ok = blk >= 0; }
+  // a warp's copy instruction covers whole rows (C lanes per row, 16 bytes each), so every 32-byte
+  // sector is asked for once
+  constexpr int C = D / 8, ROWS = NT / C;
+  const int chunk = threadIdx.x % C, r_in = threadIdx.x / C;
   const int64_t plane = (int64_t)p.Hkv * p.block_size * D;
-  const __nv_bfloat16* src = p.cache;
-  if (ok) src += (int64_t)blk * 2 * plane + ((int64_t)hk * p.block_size + (j & (p.block_size - 1))) * D + c0 * 8;
-  const __nv_bfloat16* srcv = ok ? src + plane : src;
+  const int64_t head_off = (int64_t)hk * p.block_size * D + chunk * 8;
 #pragma unroll
-  for (int c = 0; c < PER; ++c) {
-    cp_async16(sK + swz<D>(row, c0 + c), src + (ok ? c * 8 : 0), ok);
-    cp_async16(sV + swz<D>(row, c0 + c), srcv + (ok ? c * 8 : 0), ok);
+  for (int r0 = 0; r0 < BN; r0 += ROWS) {
+    const int row = r0 + r_in;
+    const int j = j0 + row;
+    bool ok = j >= lo && j < hi;
+    int blk = 0;
+    if (ok) {
+      const int e = (j >> p.bs_log2) - table_first;
+      blk = e < TABLE_SLOTS ? s_table[e] : table[j >> p.bs_log2];
+      ok = blk >= 0;
+    }
+    const __nv_bfloat16* src = p.cache;
+    if (ok) src += (int64_t)blk * 2 * plane + head_off + (int64_t)(j & (p.block_size - 1)) * D;
+    cp_async16(sK + swz<D>(row, chunk), src, ok);
+    cp_async16(sV + swz<D>(row, chunk), ok ? src + plane : src, ok);
   }
 }
 
@@ -119,10 +130,18 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
     tile_end = min(tile_end, tile_begin + per);
   }
   const int n_tiles = max(0, tile_end - tile_begin);
+  __shared__ int s_table[TABLE_SLOTS];
+  const int table_first = (tile_begin * BN) >> p.bs_log2;
+  {
+    const int last = (min(tile_end * BN, hi) - 1) >> p.bs_log2;
+    for (int i = threadIdx.x; i < TABLE_SLOTS && table_first + i <= last; i += NT) s_table[i] = table[table_first + i];
+    __syncthreads();
+  }
 
 #pragma unroll
   for (int i = 0; i < STAGES - 1; ++i) {
-    if (i < n_tiles) load_tile<D>(p, table, hk, (tile_begin + i) * BN, lo, hi, sK + i * BN * D, sV + i * BN * D);
+    if (i < n_tiles)
+      load_tile<D>(p, table, s_table, table_first, hk, (tile_begin + i) * BN, lo, hi, sK + i * BN * D, sV + i * BN * D);
     cp_async_commit();
   }
 
@@ -152,7 +171,7 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
   for (int t = 0; t < n_tiles; ++t) {
     const int buf = t % STAGES;
     if (t + STAGES - 1 < n_tiles)
-      load_tile<D>(p, table, hk, (tile_begin + t + STAGES - 1) * BN, lo, hi,
+      load_tile<D>(p, table, s_table, table_first, hk, (tile_begin + t + STAGES - 1) * BN, lo, hi,
                    sK + ((t + STAGES - 1) % STAGES) * BN * D, sV + ((t + STAGES - 1) % STAGES) * BN * D);
     cp_async_commit();
     cp_async_wait<STAGES - 1>();

@@ -27,6 +27,7 @@ constexpr int NT_DECODE = 128; // threads per CTA, decode shape
 constexpr int NT_PROMPT = 256; // threads per CTA, prompt shape: eight warps of 16 rows
 constexpr int BM = 128;        // rows per CTA (prompt shape)
 constexpr int BN = 64;         // keys per tile
+constexpr int TABLE_SLOTS = 2048;   // page-table entries of the CTA's key range kept in shared memory
 constexpr int STAGES_PROMPT = 2;   // K/V tiles in flight per CTA
 constexpr int STAGES_DECODE = 3;   // decode is bound by memory latency: one more tile in flight
 
@@ -80,7 +81,8 @@ template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
 
 // Stage one K and one V tile: keys [j0, j0 + 64) of kv head hk; rows outside [lo, hi) are zero-filled.
 template <int D, int NT>
-__device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, int hk, int j0, int lo, int hi,
+__device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, const int* s_table, int table_first,
+                                             int hk, int j0, int lo, int hi,
                                              __nv_bfloat16* sK, __nv_bfloat16* sV) {
   constexpr int C = D / 8;
   constexpr int ROWS = NT / C;
@@ -92,7 +94,11 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, 
     const int j = j0 + row;
     bool ok = j >= lo && j < hi;
     int blk = 0;
-    if (ok) { blk = table[j / p.block_size]; ok = blk >= 0; }
+    if (ok) {      // the CTA's slice of the page table sits in shared memory (no dependent global read per tile)
+      const int e = j / p.block_size - table_first;
+      blk = e < TABLE_SLOTS ? s_table[e] : table[j / p.block_size];
+      ok = blk >= 0;
+    }
     const __nv_bfloat16* src = p.cache;
     if (ok) src += (int64_t)blk * 2 * plane + ((int64_t)hk * p.block_size + j % p.block_size) * D + chunk * 8;
     cp_async16(sK + swz<D>(row, chunk), src, ok);
@@ -135,6 +141,13 @@ __global__ void __launch_bounds__(DECODE ? NT_DECODE : NT_PROMPT, 2) attention_t
     tile_end = min(tile_end, tile_begin + per);
   }
   const int n_tiles = max(0, tile_end - tile_begin);
+  __shared__ int s_table[TABLE_SLOTS];
+  const int table_first = (tile_begin * BN) / p.block_size;
+  {
+    const int last = (min(tile_end * BN, hi) - 1) / p.block_size;
+    for (int i = threadIdx.x; i < TABLE_SLOTS && table_first + i <= last; i += NT) s_table[i] = table[table_first + i];
+    __syncthreads();
+  }
 
   // ---- stage Q (rows = (token, head of the group)) and the first K/V tile
   {
@@ -150,7 +163,7 @@ __global__ void __launch_bounds__(DECODE ? NT_DECODE : NT_PROMPT, 2) attention_t
   }
 #pragma unroll
   for (int i = 0; i < STAGES - 1; ++i) {      // Q rides in the first group
-    if (i < n_tiles) load_kv_tile<D, NT>(p, table, hk, (tile_begin + i) * BN, lo, hi, sK + i * BN * D, sV + i * BN * D);
+    if (i < n_tiles) load_kv_tile<D, NT>(p, table, s_table, table_first, hk, (tile_begin + i) * BN, lo, hi, sK + i * BN * D, sV + i * BN * D);
     cp_async_commit();
   }
 
@@ -174,7 +187,7 @@ __global__ void __launch_bounds__(DECODE ? NT_DECODE : NT_PROMPT, 2) attention_t
   for (int t = 0; t < n_tiles; ++t) {
     const int buf = t % STAGES;
     if (t + STAGES - 1 < n_tiles)
-      load_kv_tile<D, NT>(p, table, hk, (tile_begin + t + STAGES - 1) * BN, lo, hi,
+      load_kv_tile<D, NT>(p, table, s_table, table_first, hk, (tile_begin + t + STAGES - 1) * BN, lo, hi,
                           sK + ((t + STAGES - 1) % STAGES) * BN * D, sV + ((t + STAGES - 1) % STAGES) * BN * D);
     cp_async_commit();
     cp_async_wait<STAGES - 1>();
