@@ -117,6 +117,7 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int b = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
+  pdl_enter();
   const int t0 = p.cu_seqlens[b];
   if (p.cu_seqlens[b + 1] - t0 != 1) return;               // not a decoded token: another kernel's request
   const int seq_len = p.seq_lens[b];
@@ -323,7 +324,7 @@ int launch(const Params& p, int B, cudaStream_t stream) {
     if (e != cudaSuccess) return refuse((int)e, "attention_decode: shared memory opt-in failed: %s", cudaGetErrorString(e));
     opted = true;
   }
-  k<<<dim3(p.splits, p.Hkv, B), NT, sm, stream>>>(p);
+  launch_pdl(k, dim3(p.splits, p.Hkv, B), dim3(NT), sm, stream, p);
   return cuda_status("attention_decode");
 }
 

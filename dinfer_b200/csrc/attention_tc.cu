@@ -118,6 +118,7 @@ __global__ void __launch_bounds__(DECODE ? NT_DECODE : NT_PROMPT, 2) attention_t
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int b = blockIdx.z, hk = blockIdx.y;
+  pdl_enter();
   const int t0 = p.cu_seqlens[b];
   const int q_len = p.cu_seqlens[b + 1] - t0;
   const int seq_len = p.seq_lens[b];
@@ -344,6 +345,7 @@ __global__ void __launch_bounds__(DECODE ? NT_DECODE : NT_PROMPT, 2) attention_t
 template <int D>
 __global__ void __launch_bounds__(D) attention_merge_kernel(const Params p) {
   const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  pdl_enter();
   const int t0 = p.cu_seqlens[b];
   if (p.cu_seqlens[b + 1] - t0 != 1) return;
   const int64_t base = ((int64_t)b * p.H + head) * p.splits;
@@ -377,7 +379,7 @@ int launch(const Params& p, int B, int max_q_len, bool any_decode, bool any_pref
       opted = true;
     }
     dim3 grid(((int64_t)max_q_len * p.group + BM - 1) / BM, p.Hkv, B);
-    k<<<grid, NT_PROMPT, sm, stream>>>(p);
+    launch_pdl(k, grid, dim3(NT_PROMPT), sm, stream, p);
   }
   if (any_decode) {
     auto k = attention_tc_kernel<D, true>;
@@ -389,8 +391,8 @@ int launch(const Params& p, int B, int max_q_len, bool any_decode, bool any_pref
       opted = true;
     }
     dim3 grid(p.splits, p.Hkv, B);
-    k<<<grid, NT_DECODE, sm, stream>>>(p);
-    if (p.splits > 1) attention_merge_kernel<D><<<dim3(p.H, B), D, 0, stream>>>(p);
+    launch_pdl(k, grid, dim3(NT_DECODE), sm, stream, p);
+    if (p.splits > 1) launch_pdl(attention_merge_kernel<D>, dim3(p.H, B), dim3(D), 0, stream, p);
   }
   return cuda_status("attention_tc");
 }

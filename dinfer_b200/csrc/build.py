@@ -35,6 +35,7 @@ LIBRARIES: Dict[str, tuple] = {
     "sampling": ("sampling.cu", []),
     "attention_tc": ("attention_tc.cu", []),
     "attention_decode": ("attention_decode.cu", []),
+    "gemm_tc": ("gemm_tc.cu", []),
 }
 
 

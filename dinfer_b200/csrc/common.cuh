@@ -97,6 +97,30 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 
 }  // namespace dinfer
 
+// ---- programmatic dependent launch: a kernel launched through launch_pdl may start while the kernel
+// before it on the stream is still running; everything it does before pdl_wait() must be independent
+// of all earlier work (no read of their outputs, no write at all).  pdl_wait() returns when the
+// preceding kernels have completed and their writes are visible; pdl_launch_dependents() lets the
+// NEXT kernel begin its own independent part.  Without the launch attribute both are no-ops.
+namespace dinfer {
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// the usual opening of a kernel with nothing to do ahead of its inputs
+__device__ __forceinline__ void pdl_enter() { pdl_wait(); pdl_launch_dependents(); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+}  // namespace dinfer
+
 // One of these per library gives Python the text of the last refusal.
 #define DINFER_DEFINE_LAST_ERROR() \
   DINFER_API const char* dinfer_last_error() { return dinfer::error_buffer(); }

@@ -10,6 +10,7 @@ namespace {
 template <typename TW>
 __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                                  float* __restrict__ out, int h, int vocab) {
+  pdl_enter();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;
@@ -35,6 +36,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, in
 // bfloat16, 8 elements (16 bytes) per thread: the shape prompts run at
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
                                        int inter8, int64_t ldx, int inter) {
+  pdl_enter();
   const int t = blockIdx.x;
   const uint4* g = reinterpret_cast<const uint4*>(x + (int64_t)t * ldx);
   const uint4* u = reinterpret_cast<const uint4*>(x + (int64_t)t * ldx + inter);
@@ -72,7 +74,7 @@ DINFER_API int dinfer_embedding(const int* ids, const void* table, float* out, i
   int threads = (h + 31) / 32 * 32;
   if (threads > 256) threads = 256;
   DINFER_DISPATCH_DTYPE(table_dtype, TW, {
-    embedding_kernel<TW><<<T, threads, 0, stream>>>(ids, (const TW*)table, out, h, vocab);
+    launch_pdl(embedding_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, (const TW*)table, out, h, vocab);
     return cuda_status("embedding");
   });
   return 0;
@@ -91,8 +93,8 @@ DINFER_API int dinfer_silu_mul(const void* x, void* out, int T, int inter, int64
       !(reinterpret_cast<uintptr_t>(out) & 15)) {
     int by = (inter / 8 + threads - 1) / threads;
     if (by > 64) by = 64;
-    silu_mul_bf16x8_kernel<<<dim3(T, by), threads, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out,
-                                                               inter / 8, ldx, inter);
+    launch_pdl(silu_mul_bf16x8_kernel, dim3(T, by), dim3(threads), 0, stream, (const __nv_bfloat16*)x,
+               (__nv_bfloat16*)out, inter / 8, ldx, inter);
     return cuda_status("silu_mul");
   }
   DINFER_DISPATCH_DTYPE(dtype, T_, {

@@ -1,0 +1,396 @@
+// C[M, N] = A[M, K] * W[N, K]^T in bfloat16 on the 5th-generation tensor cores:
+// TMA (cp.async.bulk.tensor, 128-byte swizzle) stages K-major operand tiles in shared memory,
+// one elected thread issues tcgen05.mma (cta_group::1, kind::f16, 128 x N_TILE x 16) with the f32
+// accumulator in tensor memory, tcgen05.commit hands shared-memory stages back to the producer, and
+// four epilogue warps read the accumulator with tcgen05.ld.  No cluster launch, no multicast.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocation + MMA issue,
+// warps 2..5 = epilogue (TMEM lane quarter = warp index mod 4).
+//
+// Two orientations share the kernel:
+//   * prompts:  the 128 tile rows are tokens, the N_TILE columns are weight rows;
+//   * decoding (few tokens): operands swapped, the 128 tile rows are WEIGHT rows and the (16..64)
+//     columns are tokens, so that a handful of tokens still fills the tensor-core tile and each CTA
+//     streams its weight rows from HBM exactly once; K may be split across CTAs, the partial sums go
+//     to an f32 scratch and the CTA of a tile that arrives last adds them up (a counter per tile in
+//     the same scratch, left at zero for the next launch).
+//
+// Every wait on an mbarrier is bounded: on time-out the kernel records a code in a status word,
+// lets copies in flight land, frees its tensor memory and returns (the host reads the status word).
+//
+// The reference uses cuBLASLt for these products (crates/kernels/src/gemm.rs:649-690) and mma.sync
+// kernels for small M (crates/kernels/cuda/gemm_small_m.cu:148-285); its tcgen05 code
+// (crates/kernels/cuda/umma.cuh) serves other architectures and stages by cp.async.
+#include <cuda.h>
+
+#include "common.cuh"
+
+using namespace dinfer;
+
+namespace {
+
+constexpr int TILE_M = 128;      // rows of the accumulator tile = TMEM lanes
+constexpr int BLOCK_K = 64;      // one 128-byte swizzle row of bf16
+constexpr int UMMA_K = 16;
+constexpr int NTHREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+struct GemmParams {
+  void* out; int64_t ldc;        // [tokens, N] row-major, bf16 or f32
+  int tokens, N, K;
+  int k_blocks_per_split, splits;
+  float* partial;                // [splits][tile pairs][N_TILE][TILE_M] f32 (swap + split only)
+  int* counters;                 // one per tile pair
+  int* status;                   // device status word: 0 = fine
+};
+
+// ---- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up after WAIT_LIMIT polls or about two seconds, whichever comes first.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  uint64_t start = 0;
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((i & 255) == 255) {
+      const uint64_t now = global_ns();
+      if (start == 0) start = now;
+      else if (now - start > 2000000000ull) return false;
+    }
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
+// start address >> 4, leading byte offset 1 (unused with swizzle), stride byte offset 1024 B (8 rows),
+// descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor: f32 accumulator, bf16 A and B, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <typename T> __device__ __forceinline__ T out_cast(float v);
+template <> __device__ __forceinline__ float out_cast<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 out_cast<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <int N_TILE> constexpr int tmem_cols() { return N_TILE <= 32 ? 32 : (N_TILE <= 64 ? 64 : (N_TILE <= 128 ? 128 : 256)); }
+template <int N_TILE, int STAGES> constexpr size_t gemm_smem_bytes() {
+  return (size_t)STAGES * (TILE_M * BLOCK_K + N_TILE * BLOCK_K) * 2 + 1024;   // + slack to align to 1024
+}
+
+// grid: (tiles of the 128-row operand, tiles of the N_TILE-row operand, K splits)
+template <int N_TILE, int STAGES, bool SWAP, typename OutT>
+__global__ void __launch_bounds__(NTHREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], tmem_full_bar;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort, s_last;
+  const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  constexpr uint32_t A_BYTES = TILE_M * BLOCK_K * 2, B_BYTES = N_TILE * BLOCK_K * 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int a0 = blockIdx.x * TILE_M, b0 = blockIdx.y * N_TILE;
+  const int total_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+  const int kb_begin = blockIdx.z * p.k_blocks_per_split;
+  const int kb_end = min(total_kb, kb_begin + p.k_blocks_per_split);
+  const int n_kb = max(0, kb_end - kb_begin);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+    mbar_init(smem_u32(&tmem_full_bar), 1);
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(tmem_cols<N_TILE>()) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem = s_tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {                                            // ---- TMA producer
+      // The weights do not depend on the kernels before this one: their first tiles are requested
+      // at once, while the preceding kernel may still be running; the activations only after it has
+      // completed (pdl_wait).  Both land on the same barrier of their stage.
+      const int ahead = min(STAGES, n_kb);
+      for (int i = 0; i < ahead; ++i) {
+        const uint32_t bar = smem_u32(&full_bar[i]);
+        mbar_expect_tx(bar, A_BYTES + B_BYTES);
+        const uint32_t sa = smem_base + i * (A_BYTES + B_BYTES);
+        if (SWAP) tma_load_2d(sa, &map_a, (kb_begin + i) * BLOCK_K, a0, bar);
+        else tma_load_2d(sa + A_BYTES, &map_b, (kb_begin + i) * BLOCK_K, b0, bar);
+      }
+      pdl_wait();
+      pdl_launch_dependents();
+      for (int i = 0; i < ahead; ++i) {
+        const uint32_t bar = smem_u32(&full_bar[i]);
+        const uint32_t sa = smem_base + i * (A_BYTES + B_BYTES);
+        if (SWAP) tma_load_2d(sa + A_BYTES, &map_b, (kb_begin + i) * BLOCK_K, b0, bar);
+        else tma_load_2d(sa, &map_a, (kb_begin + i) * BLOCK_K, a0, bar);
+      }
+      for (int i = ahead; i < n_kb; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), ((i / STAGES) & 1) ^ 1)) { s_abort = 1; atomicExch(p.status, 1); break; }
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        mbar_expect_tx(bar, A_BYTES + B_BYTES);
+        const uint32_t sa = smem_base + s * (A_BYTES + B_BYTES);
+        tma_load_2d(sa, &map_a, (kb_begin + i) * BLOCK_K, a0, bar);
+        tma_load_2d(sa + A_BYTES, &map_b, (kb_begin + i) * BLOCK_K, b0, bar);
+      }
+    } else {
+      pdl_enter();
+    }
+  } else if (warp == 1) {
+    pdl_enter();
+    if (lane == 0) {                                            // ---- MMA issue
+      constexpr uint32_t idesc = instr_desc_bf16(TILE_M, N_TILE);
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(smem_u32(&full_bar[s]), (i / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 2); ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t sa = smem_base + s * (A_BYTES + B_BYTES);
+        const uint64_t da = smem_desc_k_sw128(sa), db = smem_desc_k_sw128(sa + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BLOCK_K / UMMA_K; ++k)              // +32 bytes per 16-element K step, in 16-byte units
+          tcgen05_mma_f16(tmem, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        tcgen05_commit(smem_u32(&empty_bar[s]));                // the stage is free once these MMAs have read it
+      }
+      if (ok) tcgen05_commit(smem_u32(&tmem_full_bar));          // accumulator complete
+    }
+  } else {                                                      // ---- epilogue: TMEM -> registers -> global
+    pdl_enter();
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                          // accumulator row = TMEM lane
+    bool ok = true;
+    if (n_kb > 0) {
+      ok = mbar_wait(smem_u32(&tmem_full_bar), 0);
+      if (!ok && lane == 0) { s_abort = 1; atomicExch(p.status, 3); }
+      tcgen05_fence_after();
+    }
+    if (ok) {
+      OutT* out = reinterpret_cast<OutT*>(p.out);
+#pragma unroll 1
+      for (int c0 = 0; c0 < N_TILE; c0 += 16) {
+        uint32_t v[16];
+        if (n_kb > 0) {
+          tmem_ld_32x32b_x16(tmem + ((uint32_t)(quarter * 32) << 16) + c0, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0u;
+        }
+        if (!SWAP) {
+          const int t = a0 + r;
+          if (t < p.tokens) {
+            OutT* dst = out + (int64_t)t * p.ldc + b0 + c0;
+            if (b0 + c0 + 16 <= p.N && (p.ldc % 8 == 0) && sizeof(OutT) == 2) {
+              uint4 w0, w1;
+              __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&w0);
+              __nv_bfloat162* h1 = reinterpret_cast<__nv_bfloat162*>(&w1);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                h0[j] = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                h1[j] = __floats2bfloat162_rn(__uint_as_float(v[8 + 2 * j]), __uint_as_float(v[8 + 2 * j + 1]));
+              }
+              reinterpret_cast<uint4*>(dst)[0] = w0;
+              reinterpret_cast<uint4*>(dst)[1] = w1;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (b0 + c0 + j < p.N) dst[j] = out_cast<OutT>(__uint_as_float(v[j]));
+            }
+          }
+        } else {
+          const int n = a0 + r;                                 // weight row; the columns are tokens
+          if (p.splits == 1) {
+            if (n < p.N) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (b0 + c0 + j < p.tokens) out[(int64_t)(b0 + c0 + j) * p.ldc + n] = out_cast<OutT>(__uint_as_float(v[j]));
+            }
+          } else {
+            float* part = p.partial + (((int64_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * (N_TILE * TILE_M);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) part[(c0 + j) * TILE_M + r] = __uint_as_float(v[j]);
+          }
+        }
+      }
+    }
+    tcgen05_fence_before();
+  }
+
+  // ---- split-K: the CTA of this tile that arrives last adds the partial sums up
+  if (SWAP && p.splits > 1) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(&p.counters[blockIdx.y * gridDim.x + blockIdx.x], 1) == p.splits - 1;
+    __syncthreads();
+    if (s_last && !s_abort) {
+      __threadfence();
+      OutT* out = reinterpret_cast<OutT*>(p.out);
+      const int64_t tile = (int64_t)blockIdx.y * gridDim.x + blockIdx.x;
+      const int64_t split_stride = (int64_t)gridDim.y * gridDim.x * (N_TILE * TILE_M);
+      for (int idx = threadIdx.x; idx < N_TILE * TILE_M; idx += NTHREADS) {
+        const int c = idx / TILE_M, r = idx % TILE_M;
+        const int t = b0 + c, n = a0 + r;
+        if (t >= p.tokens || n >= p.N) continue;
+        float acc = 0.f;
+        for (int s = 0; s < p.splits; ++s) acc += __ldcg(p.partial + s * split_stride + tile * (N_TILE * TILE_M) + idx);
+        out[(int64_t)t * p.ldc + n] = out_cast<OutT>(acc);
+      }
+      if (threadIdx.x == 0) p.counters[blockIdx.y * gridDim.x + blockIdx.x] = 0;
+    }
+  }
+
+  __syncthreads();
+  if (warp == 1) {
+    if (s_abort) {                                              // let copies and MMAs in flight finish before the memory goes back
+      for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols<N_TILE>()) : "memory");
+  }
+}
+
+// ---- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+  }
+  return fn;
+}
+
+// bf16 matrix [rows, K] with row stride ld (elements); box = 64 columns x box_rows rows, 128-byte swizzle
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
+  return 0;
+}
+
+template <int N_TILE, int STAGES, bool SWAP, typename OutT>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+  auto k = gemm_tc_kernel<N_TILE, STAGES, SWAP, OutT>;
+  constexpr size_t sm = gemm_smem_bytes<N_TILE, STAGES>();
+  static bool opted = false;
+  if (!opted) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    if (e != cudaSuccess) return refuse((int)e, "gemm_tc: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    opted = true;
+  }
+  launch_pdl(k, grid, dim3(NTHREADS), sm, stream, ma, mb, p);
+  return cuda_status("gemm_tc");
+}
+
+}  // namespace
+
+DINFER_DEFINE_LAST_ERROR()
+
+// Bytes of scratch the decode orientation needs for `splits` > 1: f32 partial tiles, then one int
+// counter per tile (zero before the first launch; every launch leaves them zero).
+DINFER_API int64_t dinfer_gemm_tc_scratch_bytes(int tokens, int N, int splits) {
+  if (splits <= 1) return 0;
+  const int n_tile = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64);
+  const int64_t tiles = (int64_t)((N + TILE_M - 1) / TILE_M) * ((tokens + n_tile - 1) / n_tile);
+  return tiles * splits * n_tile * TILE_M * 4 + tiles * 4;
+}
+
+// x [tokens, K] (row stride ldx), w [N, K] (row stride ldw), both bf16; out [tokens, N] (row stride ldc)
+// bf16 (out_f32 = 0) or f32.  tokens <= 64: decode orientation with `splits` K splits (scratch from
+// dinfer_gemm_tc_scratch_bytes when splits > 1).  More tokens: prompt orientation, splits ignored.
+// status: a device int that a kernel sets non-zero when one of its bounded waits ran out.
+DINFER_API int dinfer_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldc,
+                              int out_f32, int tokens, int N, int K, int splits, float* partial, int* counters,
+                              int* status, cudaStream_t stream) {
+  if (tokens < 0 || N <= 0 || K <= 0) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: bad sizes tokens=%d N=%d K=%d", tokens, N, K);
+  if (tokens == 0) return 0;
+  if ((K % 8) || (ldx % 8) || (ldw % 8) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
+    return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: K and the row strides must be multiples of 8 and the bases 16-byte aligned "
+                  "(TMA); K=%d ldx=%lld ldw=%lld", K, (long long)ldx, (long long)ldw);
+  if (!status) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: a status word is required");
+  GemmParams p;
+  p.out = out; p.ldc = ldc; p.tokens = tokens; p.N = N; p.K = K; p.partial = partial; p.counters = counters; p.status = status;
+  const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  CUtensorMap ma, mb;
+  int rc;
+  if (tokens <= 64) {
+    const int n_tile = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64);
+    if (splits < 1) splits = 1;
+    if (splits > total_kb) splits = total_kb;
+    if (splits > 1 && (!partial || !counters)) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: splits=%d needs scratch", splits);
+    p.k_blocks_per_split = (total_kb + splits - 1) / splits;
+    p.splits = (total_kb + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+    if ((rc = make_map(&ma, w, N, K, ldw, TILE_M))) return rc;
+    if ((rc = make_map(&mb, x, tokens, K, ldx, n_tile))) return rc;
+    dim3 grid((N + TILE_M - 1) / TILE_M, (tokens + n_tile - 1) / n_tile, p.splits);
+#define GO(NT_) (out_f32 ? launch<NT_, 4, true, float>(ma, mb, p, grid, stream) \
+                         : launch<NT_, 4, true, __nv_bfloat16>(ma, mb, p, grid, stream))
+    if (n_tile == 16) return GO(16);
+    if (n_tile == 32) return GO(32);
+    return GO(64);
+#undef GO
+  }
+  p.k_blocks_per_split = total_kb;
+  p.splits = 1;
+  if ((rc = make_map(&ma, x, tokens, K, ldx, TILE_M))) return rc;
+  if ((rc = make_map(&mb, w, N, K, ldw, 256))) return rc;
+  dim3 grid((tokens + TILE_M - 1) / TILE_M, (N + 255) / 256, 1);
+  return out_f32 ? launch<256, 4, false, float>(ma, mb, p, grid, stream)
+                 : launch<256, 4, false, __nv_bfloat16>(ma, mb, p, grid, stream);
+}

@@ -43,6 +43,7 @@ rmsnorm_kernel(float* __restrict__ residual, const TA* __restrict__ delta, const
                const TW* __restrict__ weight, TA* __restrict__ out, int h, float eps, int stash) {
   extern __shared__ float sm_row[];
   __shared__ float red[33];
+  pdl_enter();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* res = residual + (int64_t)src * h;
@@ -117,7 +118,7 @@ int launch(float* residual, const void* delta, const int* rows, const void* weig
     if (e != cudaSuccess) return refuse((int)e, "rmsnorm: shared memory opt-in failed: %s", cudaGetErrorString(e));
     opted[vec4] = true;
   }
-  k<<<num_rows, threads, smem, stream>>>(residual, (const TA*)delta, rows, (const TW*)weight, (TA*)out, h, eps, stash);
+  launch_pdl(k, dim3(num_rows), dim3(threads), smem, stream, residual, (const TA*)delta, rows, (const TW*)weight, (TA*)out, h, eps, stash);
   return cuda_status("rmsnorm");
 }
 

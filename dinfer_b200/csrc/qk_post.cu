@@ -49,6 +49,7 @@ qk_post_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ positio
                TA* __restrict__ cache, const int* __restrict__ slots, int block_size,
                int H, int Hkv, int D) {
   __shared__ __align__(16) float sm[WARPS][MAX_D];
+  pdl_enter();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y * WARPS + warp;
@@ -130,6 +131,7 @@ qk_post_lanes_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ p
   struct alignas(sizeof(TA) * EPL) Vec { TA v[EPL]; };
   struct alignas(sizeof(TW) * EPL) WVec { TW v[EPL]; };
   struct alignas(sizeof(float) * EPL) FVec { float v[EPL]; };
+  pdl_enter();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y * WARPS + warp;
@@ -181,10 +183,10 @@ void launch_lanes(dim3 grid, cudaStream_t stream, TA* qkv, int64_t ld, const int
                   const TW* kw, float eps, const float* cos_sin, TA* cache, const int* slots, int block_size,
                   int H, int Hkv, int D) {
   const int threads = WARPS * 32;
-  if (D == 32) qk_post_lanes_kernel<TA, TW, 1><<<grid, threads, 0, stream>>>(qkv, ld, positions, qw, kw, eps, cos_sin, cache, slots, block_size, H, Hkv);
-  else if (D == 64) qk_post_lanes_kernel<TA, TW, 2><<<grid, threads, 0, stream>>>(qkv, ld, positions, qw, kw, eps, cos_sin, cache, slots, block_size, H, Hkv);
-  else if (D == 128) qk_post_lanes_kernel<TA, TW, 4><<<grid, threads, 0, stream>>>(qkv, ld, positions, qw, kw, eps, cos_sin, cache, slots, block_size, H, Hkv);
-  else qk_post_lanes_kernel<TA, TW, 8><<<grid, threads, 0, stream>>>(qkv, ld, positions, qw, kw, eps, cos_sin, cache, slots, block_size, H, Hkv);
+  if (D == 32) launch_pdl(qk_post_lanes_kernel<TA, TW, 1>, grid, dim3(threads), 0, stream, qkv, ld, positions, qw, kw, eps, cos_sin, cache, slots, block_size, H, Hkv);
+  else if (D == 64) launch_pdl(qk_post_lanes_kernel<TA, TW, 2>, grid, dim3(threads), 0, stream, qkv, ld, positions, qw, kw, eps, cos_sin, cache, slots, block_size, H, Hkv);
+  else if (D == 128) launch_pdl(qk_post_lanes_kernel<TA, TW, 4>, grid, dim3(threads), 0, stream, qkv, ld, positions, qw, kw, eps, cos_sin, cache, slots, block_size, H, Hkv);
+  else launch_pdl(qk_post_lanes_kernel<TA, TW, 8>, grid, dim3(threads), 0, stream, qkv, ld, positions, qw, kw, eps, cos_sin, cache, slots, block_size, H, Hkv);
 }
 
 }  // namespace

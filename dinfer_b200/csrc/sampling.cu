@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(BLOCK) argmax_kernel(const float* __restrict__
                                                        int* __restrict__ out, int vocab) {
   __shared__ float sv[32];
   __shared__ int si[32];
+  pdl_enter();
   const int r = block_argmax(logits + (int64_t)blockIdx.x * ld, vocab, sv, si);
   if (threadIdx.x == 0) out[blockIdx.x] = r;
 }
@@ -98,6 +99,7 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, const float* __restr
   __shared__ int si[32];
   __shared__ float seg_sum[BLOCK];
   __shared__ int choice;
+  pdl_enter();
   const int b = blockIdx.x;
   const float* row = logits + (int64_t)b * ld;
   const float temp = temperature[b];
@@ -229,7 +231,7 @@ DINFER_DEFINE_LAST_ERROR()
 DINFER_API int dinfer_argmax(const float* logits, int64_t ld, int* out, int rows, int vocab, cudaStream_t stream) {
   if (rows < 0 || vocab <= 0 || ld < vocab) return refuse(DINFER_BAD_ARGUMENT, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
   if (rows == 0) return 0;
-  argmax_kernel<<<rows, BLOCK, 0, stream>>>(logits, ld, out, vocab);
+  launch_pdl(argmax_kernel, dim3(rows), dim3(BLOCK), 0, stream, logits, ld, out, vocab);
   return cuda_status("argmax");
 }
 
@@ -239,7 +241,7 @@ DINFER_API int dinfer_sample(const float* logits, int64_t ld, const float* tempe
                              const uint64_t* offsets, int* out, int rows, int vocab, cudaStream_t stream) {
   if (rows < 0 || vocab <= 0 || ld < vocab) return refuse(DINFER_BAD_ARGUMENT, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
   if (rows == 0) return 0;
-  sample_kernel<<<rows, BLOCK, 0, stream>>>(logits, ld, temperature, top_k, top_p, min_p, seeds, offsets, out, vocab);
+  launch_pdl(sample_kernel, dim3(rows), dim3(BLOCK), 0, stream, logits, ld, temperature, top_k, top_p, min_p, seeds, offsets, out, vocab);
   return cuda_status("sample");
 }
 

@@ -124,6 +124,8 @@ class LLM:
                 self.stats.generated_tokens += len(host)
             finished += self.scheduler.update(plan, sampled)
             self.stats.steps += 1
+            if self.stats.steps % 256 == 0:
+                self.runner.check_device_status()
         self.stats.preemptions = self.scheduler.num_preemptions
         outs = []
         for r in finished:
@@ -154,4 +156,5 @@ class LLM:
             idle = idle + 1 if (not outs and self._last_scheduled == 0) else 0
             if idle > 100:
                 raise RuntimeError("the scheduler makes no progress")
+        self.runner.check_device_status()
         return [done[i] for i in ids]

@@ -215,6 +215,12 @@ class ModelRunner:
             return rec["logits"][:0]
         return rec["logits"][torch.tensor(wanted, device=self.device)]
 
+    def check_device_status(self) -> None:
+        """Raise if a kernel recorded a fault in its status word (a bounded wait that ran out).
+        Reading the word synchronizes with the device."""
+        from ..kernels import gemm_ops
+        gemm_ops.check_status(self.device)
+
     def finish(self, req_id: Hashable) -> None:
         """The request is over: its pages and state slot go back to the pools."""
         if req_id in self.manager:

@@ -1,12 +1,15 @@
 """``y = x W^T`` for a weight in the PyTorch ``[out, in]`` layout (crates/layers/src/nn.rs:16-76).
 
-Which product runs follows from the dtypes at hand:
+Which product runs follows from the dtypes and the number of rows at hand:
   * float32 activations (the true 32-bit engine): 32-bit multiply-adds on the CUDA cores;
-  * bfloat16 activations and weight: the tensor-core path (the library product, where the
-    reference's engine uses cuBLASLt: crates/kernels/src/gemm.rs:649-690, or this package's own
-    kernels once they are selected for the shape);
-  * bfloat16 activations and a weight the file stores in 32-bit: the 32-bit product, the
-    activations widened on the fly.
+  * bfloat16 activations and a weight the file stores in 32-bit: the same 32-bit product, the
+    activations widened on the fly;
+  * bfloat16 activations and weight, up to ``TC_MAX_DECODE_TOKENS`` rows (decode steps): this
+    package's tcgen05 / TMA kernel with the operands swapped, so that the weight is streamed from
+    memory exactly once (where the reference uses its own small-M kernels,
+    crates/kernels/cuda/gemm_small_m.cu:148-285);
+  * bfloat16 with more rows (prompts): the library product, where the reference's engine uses
+    cuBLASLt (crates/kernels/src/gemm.rs:649-690), or the tcgen05 kernel when ``PROMPT_BACKEND`` says so.
 """
 from __future__ import annotations
 
@@ -14,8 +17,13 @@ from typing import Optional
 
 import torch
 
-from ..kernels import ops
+from ..kernels import gemm_ops, ops
 from ..kernels.lib import add_launches
+
+# rows up to which a bfloat16 product takes the swapped-operand tcgen05 kernel
+TC_MAX_DECODE_TOKENS = 32
+# "library" or "tc": who multiplies prompts (more rows than the decode threshold)
+PROMPT_BACKEND = "library"
 
 
 class Linear:
@@ -26,7 +34,7 @@ class Linear:
         self.out_features, self.in_features = weight.shape
 
     def kernel_libraries(self):
-        return ["gemm_f32"] if self.weight.dtype == torch.float32 else []
+        return ["gemm_f32"] if self.weight.dtype == torch.float32 else ["gemm_tc"]
 
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -37,6 +45,10 @@ class Linear:
         if x.dtype == torch.float32 or w.dtype == torch.float32:
             return ops.gemm_f32(x, w, out)
         # bfloat16 x bfloat16, f32 accumulation
+        rows = x.shape[0]
+        use_tc = rows <= TC_MAX_DECODE_TOKENS or PROMPT_BACKEND == "tc"
+        if use_tc and gemm_ops.supported(x, w):
+            return gemm_ops.gemm_tc(x, w, out)
         add_launches(1)
         if out.dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)

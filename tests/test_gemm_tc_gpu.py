@@ -1,0 +1,87 @@
+"""The tcgen05 / TMA matrix product against a plain f32 product of the same bfloat16 operands: both
+orientations, ragged sizes (rows that are no multiple of the tile, K with a tail), K splits, strided
+operands, f32 output, and the status word."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def operands(tokens, N, K, seed, pad=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(tokens, K + pad, generator=g).to(torch.bfloat16).cuda()[:, :K]
+    w = (torch.randn(N, K + pad, generator=g) / math.sqrt(K)).to(torch.bfloat16).cuda()[:, :K]
+    return x, w
+
+
+def check(x, w, out):
+    want = x.float() @ w.float().T
+    got = out.float()
+    assert torch.isfinite(got).all()
+    tol = 2e-2 if out.dtype == torch.bfloat16 else 2e-4
+    err = float((got - want).abs().max())
+    assert err < tol * max(1.0, float(want.abs().max())), (err, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,K", [(128, 64), (256, 256), (517, 96), (1000, 4096), (6144, 1024)])
+def test_decode_orientation(tokens, N, K):
+    from dinfer_b200.kernels import gemm_ops as G
+    x, w = operands(tokens, N, K, tokens * N + K)
+    for splits in (1, 3, None):
+        out = torch.full((tokens, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        G.gemm_tc(x, w, out, splits=splits)
+        check(x, w, out)
+    G.check_status()
+
+
+@pytest.mark.parametrize("tokens,N,K", [(65, 256, 64), (128, 512, 128), (200, 300, 96), (300, 1000, 520),
+                                        (2048, 6144, 4096), (1000, 4096, 12288)])
+def test_prompt_orientation(tokens, N, K):
+    from dinfer_b200.kernels import gemm_ops as G
+    x, w = operands(tokens, N, K, tokens + N + K)
+    out = torch.full((tokens, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    G.gemm_tc(x, w, out)
+    check(x, w, out)
+    G.check_status()
+
+
+def test_strided_operands_and_f32_output():
+    from dinfer_b200.kernels import gemm_ops as G
+    x, w = operands(5, 777, 200, 1, pad=24)                # row strides 224 > K
+    assert x.stride(0) == 224
+    out = torch.empty(5, 777, dtype=torch.float32, device="cuda")
+    G.gemm_tc(x, w, out)
+    check(x, w, out)
+    x, w = operands(100, 333, 200, 2, pad=8)
+    wide = torch.zeros(100, 400, dtype=torch.bfloat16, device="cuda")
+    G.gemm_tc(x, w, wide[:, 8:341])                          # a column window of a wider output
+    check(x, w, wide[:, 8:341])
+    assert float(wide[:, :8].abs().max()) == 0 and float(wide[:, 341:].abs().max()) == 0
+    outf = torch.empty(100, 333, dtype=torch.float32, device="cuda")
+    G.gemm_tc(x, w, outf)
+    check(x, w, outf)
+    G.check_status()
+
+
+def test_refuses_what_tma_cannot_address():
+    from dinfer_b200.kernels import gemm_ops as G
+    from dinfer_b200.kernels.lib import KernelError
+    x = torch.zeros(4, 100, dtype=torch.bfloat16, device="cuda")      # K = 100 is no multiple of 8
+    w = torch.zeros(16, 100, dtype=torch.bfloat16, device="cuda")
+    assert not G.supported(x, w)
+    with pytest.raises(KernelError):
+        G.gemm_tc(x, w, torch.empty(4, 16, dtype=torch.bfloat16, device="cuda"))
+
+
+def test_repeated_launches_share_the_scratch():
+    from dinfer_b200.kernels import gemm_ops as G
+    x, w = operands(8, 4096, 4096, 9)
+    want = x.float() @ w.float().T
+    for _ in range(5):
+        out = torch.empty(8, 4096, dtype=torch.bfloat16, device="cuda")
+        G.gemm_tc(x, w, out, splits=8)
+        assert float((out.float() - want).abs().max()) < 2e-2 * float(want.abs().max())
+    G.check_status()
