@@ -133,6 +133,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int n_kb = max(0, kb_end - kb_begin);
 
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
     for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
     mbar_init(smem_u32(&tmem_full_bar), 1);
     s_abort = 0;
@@ -252,7 +254,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           } else {
             float* part = p.partial + (((int64_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * (N_TILE * TILE_M);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) part[(c0 + j) * TILE_M + r] = __uint_as_float(v[j]);
+            for (int j = 0; j < 16; ++j)
+              if (b0 + c0 + j < p.tokens) part[(c0 + j) * TILE_M + r] = __uint_as_float(v[j]);
           }
         }
       }
@@ -270,14 +273,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       __threadfence();
       OutT* out = reinterpret_cast<OutT*>(p.out);
       const int64_t tile = (int64_t)blockIdx.y * gridDim.x + blockIdx.x;
-      const int64_t split_stride = (int64_t)gridDim.y * gridDim.x * (N_TILE * TILE_M);
-      for (int idx = threadIdx.x; idx < N_TILE * TILE_M; idx += NTHREADS) {
-        const int c = idx / TILE_M, r = idx % TILE_M;
+      const int64_t split_stride4 = (int64_t)gridDim.y * gridDim.x * (N_TILE * TILE_M / 4);
+      const int cols = min(N_TILE, p.tokens - b0);             // token columns that exist
+      const float4* base = reinterpret_cast<const float4*>(p.partial) + tile * (N_TILE * TILE_M / 4);
+      // four consecutive weight rows of one token per thread; the loads of all splits are independent
+      for (int i4 = threadIdx.x; i4 < cols * (TILE_M / 4); i4 += NTHREADS) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int s = 0; s < p.splits; ++s) {
+          const float4 v = __ldcg(base + s * split_stride4 + i4);
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const int c = i4 / (TILE_M / 4), r = (i4 % (TILE_M / 4)) * 4;
         const int t = b0 + c, n = a0 + r;
-        if (t >= p.tokens || n >= p.N) continue;
-        float acc = 0.f;
-        for (int s = 0; s < p.splits; ++s) acc += __ldcg(p.partial + s * split_stride + tile * (N_TILE * TILE_M) + idx);
-        out[(int64_t)t * p.ldc + n] = out_cast<OutT>(acc);
+        OutT* dst = out + (int64_t)t * p.ldc + n;
+        const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (n + e < p.N) dst[e] = out_cast<OutT>(a4[e]);
       }
       if (threadIdx.x == 0) p.counters[blockIdx.y * gridDim.x + blockIdx.x] = 0;
     }

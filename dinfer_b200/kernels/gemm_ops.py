@@ -54,11 +54,11 @@ def supported(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def decode_splits(tokens: int, N: int, K: int) -> int:
-    """K splits of the decode orientation: about three CTAs per SM in flight, at least four 64-wide
-    K blocks per CTA."""
+    """K splits of the decode orientation: about two CTAs per SM in one wave, at least eight 64-wide
+    K blocks per CTA, at most 16 splits."""
     tiles = (N + 127) // 128
     k_blocks = (K + 63) // 64
-    return max(1, min((3 * NUM_SMS) // tiles, k_blocks // 4, 32))
+    return max(1, min((2 * NUM_SMS) // tiles, k_blocks // 8, 16))
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None) -> torch.Tensor:
