@@ -16,6 +16,7 @@
 // Counterpart in the reference: gqa_decode_v3 + merge (crates/kernels/cuda/gqa_decode_v3_core.cuh:72-242,
 // crates/kernels/cuda/gqa.cu:1423-1461), CUDA-core dot products with the group limited to 4.
 #include "common.cuh"
+#include "attention_decode_static.h"
 
 using namespace dinfer;
 
@@ -371,4 +372,46 @@ DINFER_API int dinfer_attention_decode(const void* q, int64_t ldq, void* out, in
   const int nh8 = (p.group + 7) / 8;
   if (D == 64) return nh8 == 1 ? launch<64, 1>(p, B, stream) : launch<64, 2>(p, B, stream);
   return nh8 == 1 ? launch<128, 1>(p, B, stream) : launch<128, 2>(p, B, stream);
+}
+
+// ---- the entry point that allocates nothing (see attention_decode_static.h)
+// The scratch of the split-key kernel as a fixed array in the library's device image.  In host code the
+// name below is only a handle; the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_decode_static_scratch[DINFER_DECODE_STATIC_SCRATCH_BYTES];
+
+DINFER_API int dinfer_attention_decode_static(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                              const int* block_table, int max_blocks, const int* cu_seqlens,
+                                              const int* seq_lens, int B, int H, int Hkv, int D, int block_size,
+                                              float scale, int window, int splits, cudaStream_t stream) {
+  constexpr int MAX_DEVICES = 64;
+  static unsigned char* base[MAX_DEVICES] = {nullptr};
+  if (B <= 0 || H <= 0 || Hkv <= 0 || D <= 0 || splits < 1)
+    return refuse(DINFER_BAD_ARGUMENT, "attention_decode_static: bad sizes B=%d H=%d Hkv=%d D=%d splits=%d", B, H, Hkv, D, splits);
+  const int64_t floats = splits > 1 ? (int64_t)B * H * splits * (D + 2) : 0;
+  const int64_t counters = splits > 1 ? (int64_t)B * Hkv : 0;
+  if (floats > (int64_t)DINFER_DECODE_STATIC_FLOATS || counters > DINFER_DECODE_STATIC_COUNTERS)
+    return refuse(DINFER_BAD_ARGUMENT,
+                  "attention_decode_static: needs %lld floats and %lld counters of scratch, the fixed array holds %lld and %d "
+                  "(fewer requests or splits, or the entry point that takes scratch from the caller)",
+                  (long long)floats, (long long)counters, (long long)DINFER_DECODE_STATIC_FLOATS, DINFER_DECODE_STATIC_COUNTERS);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
+    return refuse(e != cudaSuccess ? (int)e : DINFER_BAD_ARGUMENT, "attention_decode_static: no usable current device (%d)", dev);
+  if (!base[dev]) {                               // once per device, with that device current
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+    if (e != cudaSuccess || !p)
+      return refuse((int)e, "attention_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    base[dev] = static_cast<unsigned char*>(p);
+  }
+  float* fl = reinterpret_cast<float*>(base[dev]);
+  int* ct = reinterpret_cast<int*>(base[dev] + (size_t)DINFER_DECODE_STATIC_FLOATS * 4);
+  if (splits > 1) {                               // the counters must start at zero whatever the last call left
+    e = cudaMemsetAsync(ct, 0, (size_t)counters * sizeof(int), stream);
+    if (e != cudaSuccess) return refuse((int)e, "attention_decode_static: clearing the counters failed: %s", cudaGetErrorString(e));
+  }
+  return dinfer_attention_decode(q, ldq, out, ldo, cache, block_table, max_blocks, cu_seqlens, seq_lens, B, H, Hkv, D,
+                                 block_size, scale, window, splits, splits > 1 ? fl : nullptr, splits > 1 ? ct : nullptr,
+                                 stream);
 }
