@@ -1,0 +1,443 @@
+// Paged causal attention for prompt portions on the 5th-generation tensor cores (tcgen05 + TMEM + TMA),
+// bfloat16, head size 64 or 128, group sizes that divide 128, pages of 8..64 tokens (power of two).
+//
+// A CTA owns 128 rows of one (request, kv head); a row is a (token, query head of the group) pair, so
+// the heads of a group share every K/V tile.  Per 64-key tile:
+//     S[128, 64]  = Q K^T          tcgen05.mma, Q and K K-major in shared memory, S in tensor memory
+//     P = softmax step             one thread per row (= TMEM lane): tcgen05.ld, mask, exp2, P -> shared memory (bf16)
+//     PV[128, D]  = P V            tcgen05.mma, V used as it lies in the cache ([key][d] = MN-major B operand)
+//     O = O * alpha + PV           in the row's registers
+// Warp roles (192 threads): warp 0 = TMA producer (Q once through a 3-D map over [token][head][d]; K/V page
+// by page through a 2-D map over the layer's cache, looked up in the block table), warp 1 = TMEM
+// allocation + MMA issue, warps 2..5 = softmax / output.  K/V tiles ride a 3-stage mbarrier ring; the
+// MMA thread issues PV of tile j and QK^T of tile j+1 back to back, so the tensor core works while the
+// rows update O.  No cluster launch, no multicast.  Every mbarrier wait is bounded (status word).
+//
+// Counterpart in the reference: gqa_fa_v5_kernel (crates/kernels/cuda/gqa.cu:167-369, mma.sync) for this
+// head size; its tcgen05 attention (crates/kernels/cuda/gqa_fa_sm100.cu) exists for D = 256 only and stages
+// by cp.async.
+#include <cuda.h>
+
+#include "common.cuh"
+
+using namespace dinfer;
+
+namespace {
+
+constexpr int BM = 128, BN = 64, STAGES = 3, NTHREADS = 192;
+constexpr int TABLE_SLOTS = 2048;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+struct Params {
+  __nv_bfloat16* out; int64_t ldo;
+  const int* block_table; int max_blocks;
+  const int* cu_seqlens; const int* seq_lens;
+  int H, Hkv, group, block_size, bs_log2, window;
+  float scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  uint64_t start = 0;
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((i & 255) == 255) {
+      const uint64_t now = global_ns();
+      if (start == 0) start = now;
+      else if (now - start > 2000000000ull) return false;
+    }
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
+  uint32_t* u = reinterpret_cast<uint32_t*>(r);
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
+                 "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]),
+                 "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]),
+                 "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile with 128-byte rows, 128-byte swizzle: stride between 8-row groups 1024 B
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand (V as [key][d]): 64 d contiguous per 128-byte row, 8 keys per 1024-byte group (stride
+// byte offset), the next 64 d `lbo` bytes further (leading byte offset)
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t lbo) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+template <int D> constexpr size_t smem_bytes() {
+  return (size_t)(BM * D * 2 + 2 * STAGES * BN * D * 2 + BM * BN * 2) + 1024;
+}
+
+template <int D>
+__global__ void __launch_bounds__(NTHREADS, 1)
+attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Params p) {
+  constexpr int NH = D / 64;                          // 64-wide halves of the head
+  constexpr uint32_t Q_HALF = BM * 128, KV_HALF = BN * 128;
+  constexpr uint32_t Q_BYTES = NH * Q_HALF, KV_BYTES = NH * KV_HALF, P_BYTES = BM * BN * 2;
+  constexpr int TMEM_COLS = 256, S_COL = 0, PV_COL = 64;
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], s_full, p_full, pv_full;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_table[TABLE_SLOTS];
+  __shared__ int s_abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, hk = blockIdx.y;
+  pdl_enter();
+  const int t0 = p.cu_seqlens[b];
+  const int q_len = p.cu_seqlens[b + 1] - t0;
+  if (q_len <= 1) return;                              // decoded tokens belong to the decode kernel
+  const int rows_total = q_len * p.group;
+  const int row0 = blockIdx.x * BM;
+  if (row0 >= rows_total) return;
+  const int hist = p.seq_lens[b] - q_len;
+  const int* table = p.block_table + (int64_t)b * p.max_blocks;
+  const int last_row = min(row0 + BM, rows_total) - 1;
+  const int first_tok = row0 / p.group, last_tok = last_row / p.group;
+  const int hi = hist + last_tok + 1;
+  const int lo = p.window > 0 ? max(0, hist + first_tok - p.window + 1) : 0;
+  const int tile_begin = lo / BN, tile_end = (hi + BN - 1) / BN;
+  const int n_tiles = tile_end - tile_begin;
+
+  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  const uint32_t sQ = base, sK = sQ + Q_BYTES, sV = sK + STAGES * KV_BYTES, sP = sV + STAGES * KV_BYTES;
+
+  // page-table slice of this CTA's keys, and zeroed K/V stages (a page that is skipped leaves its slot as it
+  // was: it must hold finite numbers, because a masked key still meets 0 * V)
+  const int table_first = (tile_begin * BN) >> p.bs_log2;
+  {
+    const int last = (min(tile_end * BN, hi) - 1) >> p.bs_log2;
+    for (int i = threadIdx.x; i < TABLE_SLOTS && table_first + i <= last; i += NTHREADS) s_table[i] = table[table_first + i];
+    uint4* z = reinterpret_cast<uint4*>(smem_dyn + (sK - smem_u32(smem_dyn)));
+    for (int i = threadIdx.x; i < (int)(2 * STAGES * KV_BYTES / 16); i += NTHREADS) z[i] = make_uint4(0, 0, 0, 0);
+  }
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
+    mbar_init(smem_u32(&q_full), 1);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&kv_full[s]), 1); mbar_init(smem_u32(&kv_empty[s]), 1); }
+    mbar_init(smem_u32(&s_full), 1);
+    mbar_init(smem_u32(&p_full), 128);
+    mbar_init(smem_u32(&pv_full), 1);
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the zero fill above, before TMA writes the same bytes
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {                                                // ---- TMA producer
+      const uint32_t qb = smem_u32(&q_full);
+      mbar_expect_tx(qb, Q_BYTES);
+      for (int h = 0; h < NH; ++h) tma_load_3d(sQ + h * Q_HALF, &map_q, h * 64, hk * p.group, t0 + first_tok, qb);
+      const int br = min(p.block_size, BN);                          // rows of one K/V box
+      const int boxes = BN / br;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % STAGES;
+        if (!mbar_wait(smem_u32(&kv_empty[s]), ((j / STAGES) & 1) ^ 1)) { s_abort = 1; atomicExch(p.status, 11); break; }
+        const int j0 = (tile_begin + j) * BN;
+        const uint32_t bar = smem_u32(&kv_full[s]);
+        uint32_t bytes = 0;
+        for (int x = 0; x < boxes; ++x) {
+          const int key = j0 + x * br;
+          if (key >= hi || key + br <= lo) continue;
+          const int e = (key >> p.bs_log2) - table_first;
+          const int blk = e < TABLE_SLOTS ? s_table[e] : table[key >> p.bs_log2];
+          if (blk >= 0) bytes += 2 * NH * br * 128;
+        }
+        if (bytes == 0) { mbar_arrive(bar); continue; }
+        mbar_expect_tx(bar, bytes);
+        for (int x = 0; x < boxes; ++x) {
+          const int key = j0 + x * br;
+          if (key >= hi || key + br <= lo) continue;
+          const int e = (key >> p.bs_log2) - table_first;
+          const int blk = e < TABLE_SLOTS ? s_table[e] : table[key >> p.bs_log2];
+          if (blk < 0) continue;
+          const int row_k = ((blk * 2 + 0) * p.Hkv + hk) * p.block_size + (key & (p.block_size - 1));
+          const int row_v = row_k + p.Hkv * p.block_size;
+          for (int h = 0; h < NH; ++h) {
+            tma_load_2d(sK + s * KV_BYTES + h * KV_HALF + x * br * 128, &map_kv, h * 64, row_k, bar);
+            tma_load_2d(sV + s * KV_BYTES + h * KV_HALF + x * br * 128, &map_kv, h * 64, row_v, bar);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {                                                // ---- MMA issue
+      constexpr uint32_t idesc_qk = idesc_bf16(BM, BN, 0), idesc_pv = idesc_bf16(BM, D, 1);
+      auto issue_qk = [&](int s) {
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t da = desc_k_major(sQ + (k / 4) * Q_HALF + (k % 4) * 32);
+          const uint64_t db = desc_k_major(sK + s * KV_BYTES + (k / 4) * KV_HALF + (k % 4) * 32);
+          tc_mma(tmem + S_COL, da, db, idesc_qk, k > 0 ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&s_full));
+      };
+      bool ok = mbar_wait(smem_u32(&q_full), 0) && mbar_wait(smem_u32(&kv_full[0]), 0);
+      if (!ok) { s_abort = 1; atomicExch(p.status, 12); }
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % STAGES;
+        if (!mbar_wait(smem_u32(&p_full), j & 1)) { s_abort = 1; atomicExch(p.status, 13); ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k) {
+          const uint64_t da = desc_k_major(sP + k * 32);
+          const uint64_t db = desc_mn_major(sV + s * KV_BYTES + k * 16 * 128, KV_HALF);
+          tc_mma(tmem + PV_COL, da, db, idesc_pv, k > 0 ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&pv_full));
+        tc_commit(smem_u32(&kv_empty[s]));
+        if (j + 1 < n_tiles) {
+          const int s1 = (j + 1) % STAGES;
+          if (!mbar_wait(smem_u32(&kv_full[s1]), ((j + 1) / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); ok = false; break; }
+          tc_fence_after();
+          issue_qk(s1);
+        }
+      }
+    }
+  } else {                                                          // ---- softmax and output: one thread per row
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int row = row0 + r;
+    const bool row_ok = row < rows_total;
+    const int pos = row_ok ? hist + row / p.group : -1;
+    const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (!mbar_wait(smem_u32(&s_full), j & 1)) { s_abort = 1; atomicExch(p.status, 15); ok = false; break; }
+      tc_fence_after();
+      float s0[32], s1[32];
+      tmem_ld32(lane_addr + S_COL, s0);
+      tmem_ld32(lane_addr + S_COL + 32, s1);
+      tmem_ld_wait();
+      tc_fence_before();
+      const int jbase = (tile_begin + j) * BN;
+      const bool need_mask = (jbase + BN - 1 > hist + first_tok) || p.window > 0 || jbase < lo;
+      float mx = m_run;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float a = s0[i] * p.scale_log2, c = s1[i] * p.scale_log2;
+        if (need_mask) {
+          const int ja = jbase + i, jc = jbase + 32 + i;
+          if (!(ja <= pos && ja >= lo && (p.window <= 0 || ja > pos - p.window))) a = -INFINITY;
+          if (!(jc <= pos && jc >= lo && (p.window <= 0 || jc > pos - p.window))) c = -INFINITY;
+        }
+        s0[i] = a; s1[i] = c;
+        mx = fmaxf(mx, fmaxf(a, c));
+      }
+      const float m_use = mx == -INFINITY ? 0.f : mx;
+      const float alpha = exp2f(m_run - m_use);
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        s0[i] = exp2f(s0[i] - m_use);
+        s1[i] = exp2f(s1[i] - m_use);
+        sum += s0[i] + s1[i];
+      }
+      l_run = l_run * alpha + sum;
+      m_run = mx;
+      // P row r: 64 keys = 8 chunks of 16 bytes, swizzled like a K-major tile with 128-byte rows
+      unsigned char* prow = smem_dyn + (sP - smem_u32(smem_dyn)) + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float* src = c < 4 ? s0 + c * 8 : s1 + (c - 4) * 8;
+        uint4 w;
+        w.x = pack_bf16(src[0], src[1]); w.y = pack_bf16(src[2], src[3]);
+        w.z = pack_bf16(src[4], src[5]); w.w = pack_bf16(src[6], src[7]);
+        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = w;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(smem_u32(&p_full));
+      if (!mbar_wait(smem_u32(&pv_full), j & 1)) { s_abort = 1; atomicExch(p.status, 16); ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float pv[32];
+        tmem_ld32(lane_addr + PV_COL + c * 32, pv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + pv[i];
+      }
+      tc_fence_before();
+    }
+    if (ok && row_ok) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* dst = p.out + (int64_t)(t0 + row / p.group) * p.ldo + (int64_t)(hk * p.group + row % p.group) * D;
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) {
+        uint4 w;
+        w.x = pack_bf16(o[c * 8] * inv, o[c * 8 + 1] * inv); w.y = pack_bf16(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
+        w.z = pack_bf16(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); w.w = pack_bf16(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
+        reinterpret_cast<uint4*>(dst)[c] = w;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (s_abort) {
+      for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+  }
+  return fn;
+}
+
+template <int D>
+int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const Params& p, dim3 grid, cudaStream_t stream) {
+  auto k = attention_umma_kernel<D>;
+  constexpr size_t sm = smem_bytes<D>();
+  static bool opted = false;
+  if (!opted) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    if (e != cudaSuccess) return refuse((int)e, "attention_umma: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    opted = true;
+  }
+  launch_pdl(k, grid, dim3(NTHREADS), sm, stream, mq, mkv, p);
+  return cuda_status("attention_umma");
+}
+
+}  // namespace
+
+DINFER_DEFINE_LAST_ERROR()
+
+DINFER_API int dinfer_attention_umma_supports(int D, int group, int block_size) {
+  return (D == 64 || D == 128) && group >= 1 && group <= 128 && (128 % group) == 0 && block_size >= 8 &&
+         (block_size & (block_size - 1)) == 0;
+}
+
+// Prompt portions (q_len > 1) only; requests that bring one token are skipped.
+// q: [T, ...] rows of stride ldq with head h at h*D (all H heads); cache [num_blocks, 2, Hkv, block, D] bf16.
+DINFER_API int dinfer_attention_umma(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                     int64_t num_blocks, const int* block_table, int max_blocks,
+                                     const int* cu_seqlens, const int* seq_lens, int T, int B, int H, int Hkv, int D,
+                                     int block_size, float scale, int window, int max_q_len, int* status,
+                                     cudaStream_t stream) {
+  if (T <= 0 || B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || max_blocks <= 0 || num_blocks <= 0)
+    return refuse(DINFER_BAD_ARGUMENT, "attention_umma: bad sizes T=%d B=%d H=%d Hkv=%d", T, B, H, Hkv);
+  const int group = H / Hkv;
+  if (!dinfer_attention_umma_supports(D, group, block_size))
+    return refuse(DINFER_BAD_ARGUMENT, "attention_umma: head_dim %d, group %d, block_size %d not supported "
+                  "(head_dim 64 or 128, group dividing 128, power-of-two pages of at least 8)", D, group, block_size);
+  if ((ldq % 8) || (ldo % 8) || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
+      (reinterpret_cast<uintptr_t>(cache) & 15))
+    return refuse(DINFER_BAD_ARGUMENT, "attention_umma: rows and bases must be 16-byte aligned");
+  if (!status) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: a status word is required");
+  if (Hkv > 65535 || B > 65535) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: too many heads or requests for the grid");
+  const int64_t cache_rows = num_blocks * 2 * Hkv * block_size;
+  if (cache_rows > 0x7fffffffLL) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: the cache has too many rows for a tensor map coordinate");
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap mq, mkv;
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)T};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)ldq * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)group, (cuuint32_t)(BM / group)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: tensor map of q failed with %d", (int)r);
+  }
+  {
+    const int br = block_size < BN ? block_size : BN;
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)cache_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)br};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(&mkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: tensor map of the cache failed with %d", (int)r);
+  }
+  Params p;
+  p.out = (__nv_bfloat16*)out; p.ldo = ldo; p.block_table = block_table; p.max_blocks = max_blocks;
+  p.cu_seqlens = cu_seqlens; p.seq_lens = seq_lens; p.H = H; p.Hkv = Hkv; p.group = group; p.block_size = block_size;
+  p.bs_log2 = 0;
+  while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
+  p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  dim3 grid(((int64_t)max_q_len * group + BM - 1) / BM, Hkv, B);
+  return D == 64 ? launch<64>(mq, mkv, p, grid, stream) : launch<128>(mq, mkv, p, grid, stream);
+}

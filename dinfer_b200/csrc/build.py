@@ -36,6 +36,7 @@ LIBRARIES: Dict[str, tuple] = {
     "attention_tc": ("attention_tc.cu", []),
     "attention_decode": ("attention_decode.cu", []),
     "gemm_tc": ("gemm_tc.cu", []),
+    "attention_umma": ("attention_umma.cu", []),
 }
 
 

@@ -81,6 +81,42 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
     return out
 
 
+def umma_supported(dtype: torch.dtype, head_dim: int, group: int, block_size: int) -> bool:
+    """The tcgen05 prompt attention: bfloat16, head size 64 or 128, a group that divides 128,
+    power-of-two pages of at least 8 tokens."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and group >= 1 and 128 % group == 0
+            and block_size >= 8 and block_size & (block_size - 1) == 0)
+
+
+def attention_umma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                   cu_seqlens: torch.Tensor, seq_lens: torch.Tensor, num_heads: int, num_kv_heads: int,
+                   head_dim: int, scale: float, window: int, max_q_len: int) -> torch.Tensor:
+    """Attention of the prompt portions of the batch (requests with more than one token; the others
+    are skipped) on tcgen05 / TMEM / TMA.  ``q``: the [T, H*D] columns of the step's rows (a view with a
+    row stride is fine)."""
+    from . import gemm_ops
+    require_cuda(q, out, cache, block_table, cu_seqlens, seq_lens)
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("attention_umma: bfloat16 only")
+    if q.stride(-1) != 1 or out.stride(-1) != 1 or not cache.is_contiguous():
+        raise KernelError("attention_umma: contiguous last axes and a contiguous cache")
+    B = cu_seqlens.numel() - 1
+    for t, n in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (seq_lens, "seq_lens")):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError(f"attention_umma: {n} must be contiguous int32")
+    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
+        raise KernelError(f"attention_umma: cache shape {tuple(cache.shape)} is not [blocks, 2, Hkv, block, D]")
+    status = gemm_ops._state(q.device)["status"]
+    lib, f = _fn("attention_umma", "dinfer_attention_umma",
+                 [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
+    check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), cache.shape[0], ptr(block_table),
+                 block_table.shape[1], ptr(cu_seqlens), ptr(seq_lens), q.shape[0], B, num_heads, num_kv_heads,
+                 head_dim, cache.shape[3], float(scale), int(window), int(max_q_len), ptr(status), stream_handle()),
+          "attention_umma")
+    return out
+
+
 def attention_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                  cu_seqlens: torch.Tensor, seq_lens: torch.Tensor, num_heads: int, num_kv_heads: int,
                  head_dim: int, scale: float, window: int, max_q_len: int, any_decode: bool,

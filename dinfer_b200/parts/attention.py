@@ -79,7 +79,7 @@ class GQAttention(Mixer):
         if attention_ops.tc_supported(self.env.act_dtype, self.D, self.H // self.Hkv):
             att = ["attention_tc"]
             if self.D in (64, 128):
-                att.append("attention_decode")
+                att += ["attention_decode", "attention_umma"]
         return ["qk_post"] + att + self.qkv.kernel_libraries() + self.o.kernel_libraries()
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
@@ -117,10 +117,16 @@ class GQAttention(Mixer):
                 attention_ops.attention_decode(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
                                                self.Hkv, self.D, self.scale, window, splits)
                 tc_decode = False
-            if tc_decode or ctx.any_prefill:
+            tc_prefill = ctx.any_prefill
+            if ctx.any_prefill and attention_ops.umma_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size):
+                # prompt portions: tcgen05 / TMEM / TMA
+                attention_ops.attention_umma(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
+                                             self.Hkv, self.D, self.scale, window, ctx.max_q_len)
+                tc_prefill = False
+            if tc_decode or tc_prefill:
                 attention_ops.attention_tc(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
                                            self.Hkv, self.D, self.scale, window, ctx.max_q_len, tc_decode,
-                                           ctx.any_prefill, splits)
+                                           tc_prefill, splits)
         else:
             ops.attention_generic(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.positions, self.H, self.Hkv,
                                   self.D, self.scale, window)

@@ -1,0 +1,70 @@
+"""The tcgen05 / TMEM / TMA prompt attention against the plain formula: portions with and without
+history, several requests, both head sizes, group sizes that divide 128, page sizes 8..64, windows,
+decoded tokens in the batch left alone, garbage in unused cache slots, a decisive far key."""
+import random
+
+import pytest
+import torch
+
+from test_kernels_gpu import paged_case, plain_paged
+
+pytestmark = pytest.mark.gpu
+
+
+def run(reqs, H, Hkv, D, bs, window, seed):
+    from dinfer_b200.kernels import attention_ops as A
+    from dinfer_b200.kernels import gemm_ops as G
+    rng = random.Random(seed)
+    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, torch.bfloat16)
+    seq = torch.tensor([h + n for h, n in reqs], dtype=torch.int32)
+    scale = D ** -0.5
+    T = q.shape[0]
+    wide = torch.zeros(T, (H + 2 * Hkv) * D, dtype=torch.bfloat16, device="cuda")    # q as columns of the qkv rows
+    wide[:, :H * D] = q.reshape(T, H * D).cuda()
+    out = torch.full((T, H * D), 7.0, dtype=torch.bfloat16, device="cuda")
+    A.attention_umma(wide[:, :H * D], out, cache.cuda(), table.cuda(), cu.cuda(), seq.cuda(), H, Hkv, D, scale,
+                     window or 0, max(n for _, n in reqs))
+    G.check_status()
+    want = plain_paged(reqs, qs, ks, vs, scale, window).reshape(T, H * D)
+    got = out.double().cpu()
+    rows = [r for i, (_, n) in enumerate(reqs) if n > 1 for r in range(int(cu[i]), int(cu[i + 1]))]
+    skipped = [r for r in range(T) if r not in rows]
+    assert torch.isfinite(got).all()
+    err = float((got[rows] - want[rows]).abs().max())
+    assert err < 2e-2, err
+    assert float(torch.nn.functional.cosine_similarity(got[rows], want[rows], dim=-1).min()) > 0.999
+    assert bool((got[skipped] == 7.0).all())
+
+
+@pytest.mark.parametrize("H,Hkv,D,bs", [(8, 2, 128, 16), (4, 4, 128, 8), (16, 1, 128, 64), (8, 4, 64, 16),
+                                        (2, 1, 64, 32), (32, 8, 128, 16)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_mixed_portions(H, Hkv, D, bs, window):
+    reqs = [(40, 5), (70, 1), (0, 33), (130, 64), (0, 1), (250, 17), (0, 2), (65, 130), (0, 300)]
+    run(reqs, H, Hkv, D, bs, window, seed=H * D + bs)
+
+
+def test_long_prompt_and_history():
+    run([(0, 1100)], 8, 2, 128, 16, None, seed=1)
+    run([(1500, 700), (3, 129)], 8, 2, 128, 16, None, seed=2)
+    run([(900, 260)], 4, 1, 64, 16, 333, seed=3)
+
+
+def test_far_key_wins():
+    from dinfer_b200.kernels import attention_ops as A
+    H, Hkv, D, bs = 4, 2, 128, 16
+    rng = random.Random(4)
+    hist, new, far = 700, 50, 37
+    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, [(hist, new)], H, Hkv, D, bs, torch.bfloat16)
+    q[:] = 0
+    q[:, :, 0] = 100.0
+    cache[:, 0, :, :, 0] = 0
+    blk = int(table[0, far // bs])
+    cache[blk, 0, :, far % bs, 0] = 10.0
+    seq = torch.tensor([hist + new], dtype=torch.int32)
+    out = torch.empty(new, H * D, dtype=torch.bfloat16, device="cuda")
+    A.attention_umma(q.reshape(new, H * D).cuda(), out, cache.cuda(), table.cuda(), cu.cuda(), seq.cuda(), H, Hkv, D,
+                     1.0, 0, new)
+    want = cache[blk, 1, :, far % bs].float().repeat_interleave(H // Hkv, 0)
+    for t in (0, new // 2, new - 1):
+        assert torch.allclose(out[t].float().reshape(H, D).cpu(), want, atol=2e-2)
