@@ -1,17 +1,18 @@
 // Paged causal attention for prompt portions on the 5th-generation tensor cores (tcgen05 + TMEM + TMA),
 // bfloat16, head size 64 or 128, group sizes that divide 128, pages of 8..64 tokens (power of two).
 //
-// A CTA owns 128 rows of one (request, kv head); a row is a (token, query head of the group) pair, so
-// the heads of a group share every K/V tile.  Per 64-key tile:
+// A CTA owns 2 x 128 rows of one (request, kv head); a row is a (token, query head of the group) pair, so
+// the heads of a group share every K/V tile.  Per 64-key tile and 128-row group:
 //     S[128, 64]  = Q K^T          tcgen05.mma, Q and K K-major in shared memory, S in tensor memory
 //     P = softmax step             one thread per row (= TMEM lane): tcgen05.ld, mask, exp2, P -> shared memory (bf16)
-//     PV[128, D]  = P V            tcgen05.mma, V used as it lies in the cache ([key][d] = MN-major B operand)
-//     O = O * alpha + PV           in the row's registers
-// Warp roles (192 threads): warp 0 = TMA producer (Q once through a 3-D map over [token][head][d]; K/V page
+//     O[128, D]  += P V            tcgen05.mma accumulating in tensor memory, V used as it lies in the cache
+//                                  ([key][d] = MN-major B operand); O is rescaled in place only when a row's
+//                                  maximum grows by more than 2^8
+// Warp roles (320 threads): warp 0 = TMA producer (Q once through a 3-D map over [token][head][d]; K/V page
 // by page through a 2-D map over the layer's cache, looked up in the block table), warp 1 = TMEM
-// allocation + MMA issue, warps 2..5 = softmax / output.  K/V tiles ride a 3-stage mbarrier ring; the
-// MMA thread issues PV of tile j and QK^T of tile j+1 back to back, so the tensor core works while the
-// rows update O.  No cluster launch, no multicast.  Every mbarrier wait is bounded (status word).
+// allocation + MMA issue, warps 2..5 and 6..9 = the softmax / output groups of the two row tiles.  K/V tiles
+// ride a 3-stage mbarrier ring; the MMA thread serves the two groups alternately, so one group's softmax
+// overlaps the other's products.  No cluster launch, no multicast.  Every mbarrier wait is bounded.
 //
 // Counterpart in the reference: gqa_fa_v5_kernel (crates/kernels/cuda/gqa.cu:167-369, mma.sync) for this
 // head size; its tcgen05 attention (crates/kernels/cuda/gqa_fa_sm100.cu) exists for D = 256 only and stages
@@ -24,7 +25,7 @@ using namespace dinfer;
 
 namespace {
 
-constexpr int BM = 128, BN = 64, STAGES = 3, NTHREADS = 192;
+constexpr int BM = 128, BN = 64, STAGES = 3, NTHREADS = 320;   // BM rows per softmax group, two groups per CTA
 constexpr int TABLE_SLOTS = 2048;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
@@ -116,19 +117,41 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
-template <int D> constexpr size_t smem_bytes() {
-  return (size_t)(BM * D * 2 + 2 * STAGES * BN * D * 2 + BM * BN * 2) + 1024;
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&r)[32]) {
+  const uint32_t* u = reinterpret_cast<const uint32_t*>(r);
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+               "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]),
+                 "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]),
+                 "r"(u[16]), "r"(u[17]), "r"(u[18]), "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]),
+                 "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
+template <int D> constexpr size_t smem_bytes() {
+  return (size_t)(2 * BM * D * 2 + 2 * STAGES * BN * D * 2 + 2 * BM * BN * 2) + 1024;
+}
+
+// Two row tiles (A, B) of 128 rows per CTA, each with its own softmax warpgroup; the MMA thread feeds
+// them alternately, so one group's softmax runs while the tensor core works for the other.
+// O accumulates in tensor memory across tiles; a row's reference maximum is only raised when it grows
+// by more than 2^8 (the accumulator and the running sum are then rescaled in place), so P stays below
+// 256 and the rescale is rare.
 template <int D>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Params p) {
   constexpr int NH = D / 64;                          // 64-wide halves of the head
   constexpr uint32_t Q_HALF = BM * 128, KV_HALF = BN * 128;
   constexpr uint32_t Q_BYTES = NH * Q_HALF, KV_BYTES = NH * KV_HALF, P_BYTES = BM * BN * 2;
-  constexpr int TMEM_COLS = 256, S_COL = 0, PV_COL = 64;
+  constexpr int TMEM_COLS = 512, S_COL = 0, O_COL = 128;       // S_A 0, S_B 64, O_A 128, O_B 256
   extern __shared__ unsigned char smem_dyn[];
-  __shared__ __align__(8) uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], s_full, p_full, pv_full;
+  __shared__ __align__(8) uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2], p_full[2], o_full[2];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_table[TABLE_SLOTS];
   __shared__ int s_abort;
@@ -139,19 +162,23 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const int q_len = p.cu_seqlens[b + 1] - t0;
   if (q_len <= 1) return;                              // decoded tokens belong to the decode kernel
   const int rows_total = q_len * p.group;
-  const int row0 = blockIdx.x * BM;
+  const int row0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * 2 * BM;    // long (late) row tiles first
   if (row0 >= rows_total) return;
   const int hist = p.seq_lens[b] - q_len;
   const int* table = p.block_table + (int64_t)b * p.max_blocks;
-  const int last_row = min(row0 + BM, rows_total) - 1;
-  const int first_tok = row0 / p.group, last_tok = last_row / p.group;
+  const bool b_on = row0 + BM < rows_total;            // the second row tile exists
+  const int first_tok = row0 / p.group;
+  const int last_tok_a = (min(row0 + BM, rows_total) - 1) / p.group;
+  const int last_tok = (min(row0 + 2 * BM, rows_total) - 1) / p.group;
   const int hi = hist + last_tok + 1;
+  const int hi_a = hist + last_tok_a + 1;
   const int lo = p.window > 0 ? max(0, hist + first_tok - p.window + 1) : 0;
   const int tile_begin = lo / BN, tile_end = (hi + BN - 1) / BN;
-  const int n_tiles = tile_end - tile_begin;
+  const int n_tiles = tile_end - tile_begin;           // tiles of B (or of A when B does not exist)
+  const int n_tiles_a = (hi_a + BN - 1) / BN - tile_begin;
 
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-  const uint32_t sQ = base, sK = sQ + Q_BYTES, sV = sK + STAGES * KV_BYTES, sP = sV + STAGES * KV_BYTES;
+  const uint32_t sQ = base, sK = sQ + 2 * Q_BYTES, sV = sK + STAGES * KV_BYTES, sP = sV + STAGES * KV_BYTES;
 
   // page-table slice of this CTA's keys, and zeroed K/V stages (a page that is skipped leaves its slot as it
   // was: it must hold finite numbers, because a masked key still meets 0 * V)
@@ -167,9 +194,11 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
     mbar_init(smem_u32(&q_full), 1);
     for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&kv_full[s]), 1); mbar_init(smem_u32(&kv_empty[s]), 1); }
-    mbar_init(smem_u32(&s_full), 1);
-    mbar_init(smem_u32(&p_full), 128);
-    mbar_init(smem_u32(&pv_full), 1);
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(smem_u32(&s_full[w]), 1);
+      mbar_init(smem_u32(&p_full[w]), 128);
+      mbar_init(smem_u32(&o_full[w]), 1);
+    }
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -186,8 +215,10 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   if (warp == 0) {
     if (lane == 0) {                                                // ---- TMA producer
       const uint32_t qb = smem_u32(&q_full);
-      mbar_expect_tx(qb, Q_BYTES);
-      for (int h = 0; h < NH; ++h) tma_load_3d(sQ + h * Q_HALF, &map_q, h * 64, hk * p.group, t0 + first_tok, qb);
+      mbar_expect_tx(qb, (b_on ? 2 : 1) * Q_BYTES);
+      for (int w = 0; w < (b_on ? 2 : 1); ++w)
+        for (int h = 0; h < NH; ++h)
+          tma_load_3d(sQ + w * Q_BYTES + h * Q_HALF, &map_q, h * 64, hk * p.group, t0 + first_tok + w * (BM / p.group), qb);
       const int br = min(p.block_size, BN);                          // rows of one K/V box
       const int boxes = BN / br;
       for (int j = 0; j < n_tiles; ++j) {
@@ -223,64 +254,77 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   } else if (warp == 1) {
     if (lane == 0) {                                                // ---- MMA issue
       constexpr uint32_t idesc_qk = idesc_bf16(BM, BN, 0), idesc_pv = idesc_bf16(BM, D, 1);
-      auto issue_qk = [&](int s) {
+      auto issue_qk = [&](int w, int s) {
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint64_t da = desc_k_major(sQ + (k / 4) * Q_HALF + (k % 4) * 32);
+          const uint64_t da = desc_k_major(sQ + w * Q_BYTES + (k / 4) * Q_HALF + (k % 4) * 32);
           const uint64_t db = desc_k_major(sK + s * KV_BYTES + (k / 4) * KV_HALF + (k % 4) * 32);
-          tc_mma(tmem + S_COL, da, db, idesc_qk, k > 0 ? 1u : 0u);
+          tc_mma(tmem + S_COL + w * BN, da, db, idesc_qk, k > 0 ? 1u : 0u);
         }
-        tc_commit(smem_u32(&s_full));
+        tc_commit(smem_u32(&s_full[w]));
+      };
+      auto issue_pv = [&](int w, int s, int j) {
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k) {
+          const uint64_t da = desc_k_major(sP + w * P_BYTES + k * 32);
+          const uint64_t db = desc_mn_major(sV + s * KV_BYTES + k * 16 * 128, KV_HALF);
+          tc_mma(tmem + O_COL + w * 128, da, db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        }
       };
       bool ok = mbar_wait(smem_u32(&q_full), 0) && mbar_wait(smem_u32(&kv_full[0]), 0);
       if (!ok) { s_abort = 1; atomicExch(p.status, 12); }
       if (ok) {
         tc_fence_after();
-        issue_qk(0);
+        if (n_tiles_a > 0) issue_qk(0, 0);
+        if (b_on) issue_qk(1, 0);
       }
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % STAGES;
-        if (!mbar_wait(smem_u32(&p_full), j & 1)) { s_abort = 1; atomicExch(p.status, 13); ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < BN / 16; ++k) {
-          const uint64_t da = desc_k_major(sP + k * 32);
-          const uint64_t db = desc_mn_major(sV + s * KV_BYTES + k * 16 * 128, KV_HALF);
-          tc_mma(tmem + PV_COL, da, db, idesc_pv, k > 0 ? 1u : 0u);
-        }
-        tc_commit(smem_u32(&pv_full));
-        tc_commit(smem_u32(&kv_empty[s]));
-        if (j + 1 < n_tiles) {
-          const int s1 = (j + 1) % STAGES;
-          if (!mbar_wait(smem_u32(&kv_full[s1]), ((j + 1) / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); ok = false; break; }
+        const int s = j % STAGES, s1 = (j + 1) % STAGES;
+        bool next_ready = false;
+        for (int w = 0; w < 2 && ok; ++w) {
+          const int n_w = w == 0 ? n_tiles_a : (b_on ? n_tiles : 0);
+          if (j >= n_w) continue;
+          if (!mbar_wait(smem_u32(&p_full[w]), j & 1)) { s_abort = 1; atomicExch(p.status, 13); ok = false; break; }
           tc_fence_after();
-          issue_qk(s1);
+          issue_pv(w, s, j);
+          if (j + 1 < n_w) {
+            if (!next_ready) {
+              if (!mbar_wait(smem_u32(&kv_full[s1]), ((j + 1) / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); ok = false; break; }
+              tc_fence_after();
+              next_ready = true;
+            }
+            issue_qk(w, s1);
+          } else {
+            tc_commit(smem_u32(&o_full[w]));                       // this row tile's last PV
+          }
         }
+        if (ok) tc_commit(smem_u32(&kv_empty[s]));
       }
     }
   } else {                                                          // ---- softmax and output: one thread per row
+    const int w = (warp - 2) >> 2;                                  // row tile A (warps 2..5) or B (warps 6..9)
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    const int row = row0 + r;
+    const int row = row0 + w * BM + r;
     const bool row_ok = row < rows_total;
     const int pos = row_ok ? hist + row / p.group : -1;
+    const int n_w = w == 0 ? n_tiles_a : (b_on ? n_tiles : 0);
+    const int first_tok_w = (row0 + w * BM) / p.group;
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    const uint32_t s_addr = lane_addr + S_COL + w * BN, o_addr = lane_addr + O_COL + w * 128;
+    unsigned char* prow = smem_dyn + (sP - smem_u32(smem_dyn)) + w * P_BYTES + r * 128;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!mbar_wait(smem_u32(&s_full), j & 1)) { s_abort = 1; atomicExch(p.status, 15); ok = false; break; }
+    for (int j = 0; j < n_w && ok; ++j) {
+      if (!mbar_wait(smem_u32(&s_full[w]), j & 1)) { s_abort = 1; atomicExch(p.status, 15); ok = false; break; }
       tc_fence_after();
       float s0[32], s1[32];
-      tmem_ld32(lane_addr + S_COL, s0);
-      tmem_ld32(lane_addr + S_COL + 32, s1);
+      tmem_ld32(s_addr, s0);
+      tmem_ld32(s_addr + 32, s1);
       tmem_ld_wait();
-      tc_fence_before();
       const int jbase = (tile_begin + j) * BN;
-      const bool need_mask = (jbase + BN - 1 > hist + first_tok) || p.window > 0 || jbase < lo;
-      float mx = m_run;
+      const bool need_mask = (jbase + BN - 1 > hist + first_tok_w) || p.window > 0 || jbase < lo;
+      float mx = -INFINITY;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         float a = s0[i] * p.scale_log2, c = s1[i] * p.scale_log2;
@@ -292,50 +336,68 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         s0[i] = a; s1[i] = c;
         mx = fmaxf(mx, fmaxf(a, c));
       }
-      const float m_use = mx == -INFINITY ? 0.f : mx;
-      const float alpha = exp2f(m_run - m_use);
+      // raise the reference maximum only when it grows by more than 8 (in log2 units)
+      const bool raise = mx > m_run + 8.f;
+      if (j > 0 && __any_sync(0xffffffffu, raise)) {
+        // O_w is quiet here: PV of tile j-1 completed before s_full fired, PV of tile j waits for our P
+        const float alpha = raise ? fast_exp2(m_run - mx) : 1.f;     // m_run = -inf gives 0
+        l_run *= alpha;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          float o[32];
+          tmem_ld32(o_addr + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= alpha;
+          tmem_st32(o_addr + c * 32, o);
+        }
+        tmem_st_wait();
+      }
+      if (raise) m_run = mx;
+      const float m_use = m_run == -INFINITY ? 0.f : m_run;
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        s0[i] = exp2f(s0[i] - m_use);
-        s1[i] = exp2f(s1[i] - m_use);
+        s0[i] = fast_exp2(s0[i] - m_use);
+        s1[i] = fast_exp2(s1[i] - m_use);
         sum += s0[i] + s1[i];
       }
-      l_run = l_run * alpha + sum;
-      m_run = mx;
+      l_run += sum;
       // P row r: 64 keys = 8 chunks of 16 bytes, swizzled like a K-major tile with 128-byte rows
-      unsigned char* prow = smem_dyn + (sP - smem_u32(smem_dyn)) + r * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         const float* src = c < 4 ? s0 + c * 8 : s1 + (c - 4) * 8;
-        uint4 w;
-        w.x = pack_bf16(src[0], src[1]); w.y = pack_bf16(src[2], src[3]);
-        w.z = pack_bf16(src[4], src[5]); w.w = pack_bf16(src[6], src[7]);
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = w;
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(smem_u32(&p_full));
-      if (!mbar_wait(smem_u32(&pv_full), j & 1)) { s_abort = 1; atomicExch(p.status, 16); ok = false; break; }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        float pv[32];
-        tmem_ld32(lane_addr + PV_COL + c * 32, pv);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + pv[i];
+        uint4 v;
+        v.x = pack_bf16(src[0], src[1]); v.y = pack_bf16(src[2], src[3]);
+        v.z = pack_bf16(src[4], src[5]); v.w = pack_bf16(src[6], src[7]);
+        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = v;
       }
       tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(smem_u32(&p_full[w]));
     }
-    if (ok && row_ok) {
+    if (ok && n_w > 0) {
+      if (!mbar_wait(smem_u32(&o_full[w]), 0)) { s_abort = 1; atomicExch(p.status, 16); ok = false; }
+      tc_fence_after();
+    }
+    if (ok && n_w > 0) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = p.out + (int64_t)(t0 + row / p.group) * p.ldo + (int64_t)(hk * p.group + row % p.group) * D;
+      __nv_bfloat16* dst = row_ok ? p.out + (int64_t)(t0 + row / p.group) * p.ldo + (int64_t)(hk * p.group + row % p.group) * D
+                                  : nullptr;
 #pragma unroll
-      for (int c = 0; c < D / 8; ++c) {
-        uint4 w;
-        w.x = pack_bf16(o[c * 8] * inv, o[c * 8 + 1] * inv); w.y = pack_bf16(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
-        w.z = pack_bf16(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); w.w = pack_bf16(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
-        reinterpret_cast<uint4*>(dst)[c] = w;
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        tmem_ld32(o_addr + c * 32, o);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 v;
+            v.x = pack_bf16(o[q4 * 8] * inv, o[q4 * 8 + 1] * inv); v.y = pack_bf16(o[q4 * 8 + 2] * inv, o[q4 * 8 + 3] * inv);
+            v.z = pack_bf16(o[q4 * 8 + 4] * inv, o[q4 * 8 + 5] * inv); v.w = pack_bf16(o[q4 * 8 + 6] * inv, o[q4 * 8 + 7] * inv);
+            reinterpret_cast<uint4*>(dst + c * 32)[q4] = v;
+          }
+        }
       }
     }
   }
@@ -438,6 +500,6 @@ DINFER_API int dinfer_attention_umma(const void* q, int64_t ldq, void* out, int6
   p.bs_log2 = 0;
   while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
   p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-  dim3 grid(((int64_t)max_q_len * group + BM - 1) / BM, Hkv, B);
+  dim3 grid(((int64_t)max_q_len * group + 2 * BM - 1) / (2 * BM), Hkv, B);
   return D == 64 ? launch<64>(mq, mkv, p, grid, stream) : launch<128>(mq, mkv, p, grid, stream);
 }
