@@ -118,7 +118,10 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int b = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
-  pdl_enter();
+  // Before pdl_wait(): only what no kernel of this step writes (the batch's index arrays, copied to the
+  // device before the step's first kernel, and cache pages of older tokens).  The newest token's K/V and
+  // the q rows come from the kernel just before this one, so the tile that holds position `pos` and q
+  // are read after the wait.
   const int t0 = p.cu_seqlens[b];
   if (p.cu_seqlens[b + 1] - t0 != 1) return;               // not a decoded token: another kernel's request
   const int seq_len = p.seq_lens[b];
@@ -140,12 +143,17 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
     __syncthreads();
   }
 
+  bool waited = false;
 #pragma unroll
   for (int i = 0; i < STAGES - 1; ++i) {
-    if (i < n_tiles)
+    if (i < n_tiles) {
+      if (!waited && (tile_begin + i + 1) * BN > pos) { pdl_wait(); waited = true; }
       load_tile<D>(p, table, s_table, table_first, hk, (tile_begin + i) * BN, lo, hi, sK + i * BN * D, sV + i * BN * D);
+    }
     cp_async_commit();
   }
+  if (!waited) pdl_wait();
+  pdl_launch_dependents();
 
   // Q^T as the B operand: head nt*8 + g, dims ks*16 + {2tq, 2tq+1} and + 8
   unsigned qb[D / 16][NH8][2];
@@ -172,12 +180,12 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
 
   for (int t = 0; t < n_tiles; ++t) {
     const int buf = t % STAGES;
-    if (t + STAGES - 1 < n_tiles)
+    cp_async_wait<STAGES - 2>();          // tile t has landed (this thread's part) ...
+    __syncthreads();                      // ... everyone's part, and everyone is done with tile t-1:
+    if (t + STAGES - 1 < n_tiles)         // its buffer takes tile t + STAGES - 1
       load_tile<D>(p, table, s_table, table_first, hk, (tile_begin + t + STAGES - 1) * BN, lo, hi,
                    sK + ((t + STAGES - 1) % STAGES) * BN * D, sV + ((t + STAGES - 1) % STAGES) * BN * D);
     cp_async_commit();
-    cp_async_wait<STAGES - 1>();
-    __syncthreads();
     const __nv_bfloat16* kt = sK + buf * BN * D;
     const __nv_bfloat16* vt = sV + buf * BN * D;
     const int jbase = (tile_begin + t) * BN + key_off;
@@ -237,7 +245,6 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
         for (int nt = 0; nt < NH8; ++nt) mma_bf16(ot[db][nt], a, pb[nt][0], pb[nt][1]);
       }
     }
-    __syncthreads();
   }
   cp_async_wait<0>();
   __syncthreads();

@@ -9,6 +9,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
+#include <stdlib.h>
 
 #define DINFER_API extern "C" __attribute__((visibility("default")))
 
@@ -116,7 +117,9 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  // DINFER_NO_PDL=1 (read once) launches without the attribute: a switch for measuring what the overlap buys
+  static const bool off = [] { const char* e = getenv("DINFER_NO_PDL"); return e && e[0] == '1'; }();
+  cfg.attrs = attr; cfg.numAttrs = off ? 0 : 1;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 }  // namespace dinfer
