@@ -302,20 +302,37 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
   __syncthreads();
   if (!s_last) return;
   __threadfence();
+  // weights of the splits first (one (head, split) pair per thread, all loads independent), then the sums
+  float* sm_f = reinterpret_cast<float*>(smem_raw);           // [group][splits] factor, then [group] 1 / L
+  float* sm_inv = sm_f + NHEADS * 32;
+  for (int i = threadIdx.x; i < p.group * p.splits; i += NT) {
+    const int head = i / p.splits, sp = i % p.splits;
+    sm_f[head * 32 + sp] = __ldcg(p.part_ml + (((int64_t)b * p.H + hk * p.group + head) * p.splits + sp) * 2);
+  }
+  __syncthreads();
+  if (threadIdx.x < p.group) {
+    const int head = threadIdx.x;
+    const int64_t base = ((int64_t)b * p.H + hk * p.group + head) * p.splits;
+    float M = -INFINITY;
+    for (int sp = 0; sp < p.splits; ++sp) M = fmaxf(M, sm_f[head * 32 + sp]);
+    float L = 0.f;
+    for (int sp = 0; sp < p.splits; ++sp) {
+      const float ms = sm_f[head * 32 + sp];
+      const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+      L += __ldcg(p.part_ml + (base + sp) * 2 + 1) * f;
+      sm_f[head * 32 + sp] = f;
+    }
+    sm_inv[head] = L > 0.f ? 1.f / L : 0.f;
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < p.group * D; idx += NT) {
     const int head = idx / D, d = idx % D;
     const int gh = hk * p.group + head;
-    const int64_t base = ((int64_t)b * p.H + gh) * p.splits;
-    float M = -INFINITY;
-    for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (base + s) * 2));
-    float L = 0.f, acc = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-      const float ms = __ldcg(p.part_ml + (base + s) * 2);
-      const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-      L += __ldcg(p.part_ml + (base + s) * 2 + 1) * f;
-      acc += __ldcg(p.part_o + (base + s) * D + d) * f;
-    }
-    p.out[(int64_t)t0 * p.ldo + (int64_t)gh * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    const float* po = p.part_o + ((int64_t)b * p.H + gh) * p.splits * D + d;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int sp = 0; sp < p.splits; ++sp) acc += __ldcg(po + sp * D) * sm_f[head * 32 + sp];
+    p.out[(int64_t)t0 * p.ldo + (int64_t)gh * D + d] = __float2bfloat16_rn(acc * sm_inv[head]);
   }
   if (threadIdx.x == 0) p.counters[b * p.Hkv + hk] = 0;      // ready for the next launch
 }
@@ -363,6 +380,7 @@ DINFER_API int dinfer_attention_decode(const void* q, int64_t ldq, void* out, in
                   "(head_dim 64 or 128, group <= 16, power-of-two pages)", D, H / Hkv, block_size);
   if ((ldq % 2) || (ldo % 2) || (reinterpret_cast<uintptr_t>(q) & 3) || (reinterpret_cast<uintptr_t>(cache) & 15))
     return refuse(DINFER_BAD_ARGUMENT, "attention_decode: q rows must be 4-byte and the cache 16-byte aligned");
+  if (splits > 32) return refuse(DINFER_BAD_ARGUMENT, "attention_decode: at most 32 key splits, got %d", splits);
   if (splits < 1 || (splits > 1 && (!scratch_floats || !scratch_counters)))
     return refuse(DINFER_BAD_ARGUMENT, "attention_decode: splits=%d needs scratch", splits);
   if (Hkv > 65535 || B > 65535) return refuse(DINFER_BAD_ARGUMENT, "attention_decode: too many heads or requests for the grid");

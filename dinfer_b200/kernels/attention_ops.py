@@ -17,12 +17,13 @@ def tc_supported(dtype: torch.dtype, head_dim: int, group: int) -> bool:
 
 
 def decode_splits(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
-    """Key splits of the decode shape.  Two CTAs fit an SM; with few (request, kv head) pairs the
-    splits fill those slots in one wave, with many they cut the work into about eight waves so that
-    the last wave's idle SMs cost little.  Never more than a quarter of the 64-key tiles, at most 32."""
+    """Key splits of the decode shape.  Two CTAs fit an SM: with few (request, kv head) pairs the
+    splits fill those slots in one wave; with as many pairs as slots or more, splitting only adds
+    partial sums to write and fold, so there is none.  Never more than a quarter of the 64-key
+    tiles, at most 32."""
     slots = 2 * NUM_SMS
     base = max(1, num_reqs * num_kv_heads)
-    want = slots // base if base <= slots else (8 * slots + base - 1) // base
+    want = slots // base if base <= slots else 1
     tiles = max(1, (max_seq_len + 63) // 64)
     return max(1, min(want, max(1, tiles // 4), 32))
 
