@@ -15,6 +15,8 @@
 //
 // Counterpart in the reference: gqa_decode_v3 + merge (crates/kernels/cuda/gqa_decode_v3_core.cuh:72-242,
 // crates/kernels/cuda/gqa.cu:1423-1461), CUDA-core dot products with the group limited to 4.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "attention_decode_static.h"
 
@@ -39,6 +41,7 @@ struct Params {
   float* part_o;     // [B, H, splits, D]
   float* part_ml;    // [B, H, splits, 2]
   int* counters;     // [B, Hkv]
+  int* status;       // device status word of the TMA variant (bounded waits)
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -71,6 +74,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ float fast_exp2(float x) {     // ex2.approx: -inf -> 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
   constexpr int C = D / 8;
@@ -190,15 +198,26 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
     const __nv_bfloat16* vt = sV + buf * BN * D;
     const int jbase = (tile_begin + t) * BN + key_off;
     if (jbase < hi) {                                       // warp-uniform: this warp's 16 keys hold something
-      float st[NH8][4];
+      float st[NH8][4], st2[NH8][4];                        // two accumulators: half the dependent chain
 #pragma unroll
-      for (int nt = 0; nt < NH8; ++nt) st[nt][0] = st[nt][1] = st[nt][2] = st[nt][3] = 0.f;
+      for (int nt = 0; nt < NH8; ++nt) {
+        st[nt][0] = st[nt][1] = st[nt][2] = st[nt][3] = 0.f;
+        st2[nt][0] = st2[nt][1] = st2[nt][2] = st2[nt][3] = 0.f;
+      }
 #pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        unsigned a[4];
+      for (int ks = 0; ks < D / 16; ks += 2) {
+        unsigned a[4], a2[4];
         ldmatrix_x4(a, kt + swz<D>(key_off + (lane & 15), ks * 2 + (lane >> 4)));
+        ldmatrix_x4(a2, kt + swz<D>(key_off + (lane & 15), (ks + 1) * 2 + (lane >> 4)));
 #pragma unroll
-        for (int nt = 0; nt < NH8; ++nt) mma_bf16(st[nt], a, qb[ks][nt][0], qb[ks][nt][1]);
+        for (int nt = 0; nt < NH8; ++nt) {
+          mma_bf16(st[nt], a, qb[ks][nt][0], qb[ks][nt][1]);
+          mma_bf16(st2[nt], a2, qb[ks + 1][nt][0], qb[ks + 1][nt][1]);
+        }
+      }
+#pragma unroll
+      for (int nt = 0; nt < NH8; ++nt) {
+        st[nt][0] += st2[nt][0]; st[nt][1] += st2[nt][1]; st[nt][2] += st2[nt][2]; st[nt][3] += st2[nt][3];
       }
       const bool vis0 = jbase + g >= lo && jbase + g <= pos;
       const bool vis1 = jbase + g + 8 >= lo && jbase + g + 8 <= pos;
@@ -217,9 +236,9 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
           mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
           const float m_new = fmaxf(m_run[nt][c], mx);
           const float m_use = m_new == -INFINITY ? 0.f : m_new;
-          alpha[nt][c] = exp2f(m_run[nt][c] - m_use);
+          alpha[nt][c] = fast_exp2(m_run[nt][c] - m_use);
           rescale |= m_new != m_run[nt][c];
-          const float p0 = exp2f(s0 - m_use), p1 = exp2f(s1 - m_use);
+          const float p0 = fast_exp2(s0 - m_use), p1 = fast_exp2(s1 - m_use);
           l_run[nt][c] = l_run[nt][c] * alpha[nt][c] + p0 + p1;
           m_run[nt][c] = m_new;
           st[nt][c] = p0;
@@ -305,21 +324,23 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
   // weights of the splits first (one (head, split) pair per thread, all loads independent), then the sums
   float* sm_f = reinterpret_cast<float*>(smem_raw);           // [group][splits] factor, then [group] 1 / L
   float* sm_inv = sm_f + NHEADS * 32;
+  float* sm_l2 = sm_inv + NHEADS;
   for (int i = threadIdx.x; i < p.group * p.splits; i += NT) {
     const int head = i / p.splits, sp = i % p.splits;
-    sm_f[head * 32 + sp] = __ldcg(p.part_ml + (((int64_t)b * p.H + hk * p.group + head) * p.splits + sp) * 2);
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml) + ((int64_t)b * p.H + hk * p.group + head) * p.splits + sp);
+    sm_f[head * 32 + sp] = ml.x;                              // the split's maximum
+    sm_l2[head * 32 + sp] = ml.y;                             // and its sum
   }
   __syncthreads();
   if (threadIdx.x < p.group) {
     const int head = threadIdx.x;
-    const int64_t base = ((int64_t)b * p.H + hk * p.group + head) * p.splits;
     float M = -INFINITY;
     for (int sp = 0; sp < p.splits; ++sp) M = fmaxf(M, sm_f[head * 32 + sp]);
     float L = 0.f;
     for (int sp = 0; sp < p.splits; ++sp) {
       const float ms = sm_f[head * 32 + sp];
       const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-      L += __ldcg(p.part_ml + (base + sp) * 2 + 1) * f;
+      L += sm_l2[head * 32 + sp] * f;
       sm_f[head * 32 + sp] = f;
     }
     sm_inv[head] = L > 0.f ? 1.f / L : 0.f;
@@ -335,6 +356,374 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
     p.out[(int64_t)t0 * p.ldo + (int64_t)gh * D + d] = __float2bfloat16_rn(acc * sm_inv[head]);
   }
   if (threadIdx.x == 0) p.counters[b * p.Hkv + hk] = 0;      // ready for the next launch
+}
+
+// ------------------------------------------------------------------------------------------------
+// The same computation with the tiles brought in by TMA: a fifth warp's elected lane requests every
+// page of a tile (one box per page, 64-wide half and K / V) through a tensor map over the layer's
+// cache, tiles ride an mbarrier ring (full: bytes landed; empty: the four compute warps are done), and
+// the compute warps issue no address arithmetic or copies at all and meet at no CTA-wide barrier per
+// tile.  Shared-memory tiles have TMA's 128-byte swizzle: [half][key][128 bytes].  Pages of at least
+// 8 tokens (a swizzle atom is 8 rows).  Every mbarrier wait is bounded (status word).
+constexpr int NT_TMA = 160;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  uint64_t start = 0;
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((i & 255) == 255) {
+      uint64_t now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (start == 0) start = now;
+      else if (now - start > 2000000000ull) return false;
+    }
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// byte offset of (key row, 16-byte chunk c of the head) inside a [half][64 keys][128 B] tile with 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128(int row, int c) {
+  return (uint32_t)((c >> 3) * (BN * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4));
+}
+
+template <int D, int NH8>
+__global__ void __launch_bounds__(NT_TMA, 2)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) {
+  constexpr int NHF = D / 64;                                 // 64-wide halves of the head
+  constexpr uint32_t KV_BYTES = NHF * BN * 128;               // one of K / V of a tile
+  constexpr int NHEADS = NH8 * 8;
+  extern __shared__ __align__(128) unsigned char smem_raw[];   // aligned to 1024 by hand below
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES];
+  __shared__ int s_table[TABLE_SLOTS];
+  __shared__ int s_last, s_abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  const int b = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
+  // before pdl_wait(): only the batch's index arrays and cache pages of older tokens (see the other kernel)
+  const int t0 = p.cu_seqlens[b];
+  if (p.cu_seqlens[b + 1] - t0 != 1) return;
+  const int seq_len = p.seq_lens[b];
+  const int pos = seq_len - 1;
+  const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0, hi = seq_len;
+  const int* table = p.block_table + (int64_t)b * p.max_blocks;
+  int tile_begin = lo / BN, tile_end = (hi + BN - 1) / BN;
+  {
+    const int per = (tile_end - tile_begin + p.splits - 1) / p.splits;
+    tile_begin += split * per;
+    tile_end = min(tile_end, tile_begin + per);
+  }
+  const int n_tiles = max(0, tile_end - tile_begin);
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* gbase = smem_raw + (base - smem_u32(smem_raw));
+  const int table_first = (tile_begin * BN) >> p.bs_log2;
+  {
+    const int last = (min(tile_end * BN, hi) - 1) >> p.bs_log2;
+    for (int i = threadIdx.x; i < TABLE_SLOTS && table_first + i <= last; i += NT_TMA) s_table[i] = table[table_first + i];
+    // a page that is skipped leaves its rows as they were: they must hold finite numbers (0 * V)
+    uint4* z = reinterpret_cast<uint4*>(gbase);
+    for (int i = threadIdx.x; i < (int)(2 * STAGES * KV_BYTES / 16); i += NT_TMA) z[i] = make_uint4(0, 0, 0, 0);
+  }
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
+    for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 4); }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+
+  float ot[D / 16][NH8][4];
+  float m_run[NH8][2], l_run[NH8][2];
+#pragma unroll
+  for (int i = 0; i < D / 16; ++i)
+#pragma unroll
+    for (int nt = 0; nt < NH8; ++nt) ot[i][nt][0] = ot[i][nt][1] = ot[i][nt][2] = ot[i][nt][3] = 0.f;
+#pragma unroll
+  for (int nt = 0; nt < NH8; ++nt) { m_run[nt][0] = m_run[nt][1] = -INFINITY; l_run[nt][0] = l_run[nt][1] = 0.f; }
+
+  if (warp == 4) {
+    // ---- TMA producer: the whole warp.  A tile is (64 / page rows) pages x (K, V) x 64-wide halves of
+    // copies; each lane owns up to two of them, so they are requested side by side instead of one after
+    // another from a single thread (that serial issue, not the memory, bounded the kernel).
+    const int br = min(p.block_size, BN), boxes = BN / br;
+    constexpr int PER_BOX = 2 * NHF;                          // K/V x halves
+    const int n_ops = boxes * PER_BOX;                        // <= 64
+    bool waited = false, alive = true;
+    for (int t = 0; t < n_tiles && alive; ++t) {
+      const int s = t % STAGES;
+      const int j0 = (tile_begin + t) * BN;
+      if (!waited && j0 + BN > pos) { pdl_wait(); waited = true; }        // the newest token's page
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(smem_u32(&empty_bar[s]), ((t / STAGES) & 1) ^ 1);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { if (lane == 0) { s_abort = 1; atomicExch(p.status, 21); } alive = false; break; }
+      const uint32_t bar = smem_u32(&full_bar[s]);
+      const uint32_t sk = base + s * 2 * KV_BYTES;
+      int row[2]; uint32_t dst[2]; int col[2]; bool valid[2];
+      uint32_t bytes = 0;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int o = lane + 32 * u;
+        valid[u] = false;
+        if (o < n_ops) {
+          const int x = o / PER_BOX, r = o % PER_BOX, kv = r / NHF, h = r % NHF;
+          const int key = j0 + x * br;
+          if (key < hi && key + br > lo) {
+            const int e = (key >> p.bs_log2) - table_first;
+            const int blk = e < TABLE_SLOTS ? s_table[e] : table[key >> p.bs_log2];
+            if (blk >= 0) {
+              valid[u] = true;
+              row[u] = ((blk * 2 + kv) * p.Hkv + hk) * p.block_size + (key & (p.block_size - 1));
+              col[u] = h * 64;
+              dst[u] = sk + kv * KV_BYTES + h * (BN * 128) + x * br * 128;
+              bytes += br * 128;
+            }
+          }
+        }
+      }
+      bytes = __reduce_add_sync(0xffffffffu, bytes);
+      if (lane == 0) {
+        if (bytes == 0) mbar_arrive(bar); else mbar_expect_tx(bar, bytes);
+      }
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+        if (valid[u]) tma_load_2d(dst[u], &map_kv, col[u], row[u], bar);
+    }
+    if (!waited) pdl_wait();
+    pdl_launch_dependents();
+  } else {                                                    // ---- four compute warps, 16 keys of every tile each
+    pdl_wait();                                               // q comes from the kernel before this one
+    unsigned qb[D / 16][NH8][2];
+#pragma unroll
+    for (int nt = 0; nt < NH8; ++nt) {
+      const int head = nt * 8 + g;
+      const __nv_bfloat16* qrow = p.q + (int64_t)t0 * p.ldq + (int64_t)(hk * p.group + head) * D;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        qb[ks][nt][0] = head < p.group ? *reinterpret_cast<const unsigned*>(qrow + ks * 16 + 2 * tq) : 0u;
+        qb[ks][nt][1] = head < p.group ? *reinterpret_cast<const unsigned*>(qrow + ks * 16 + 8 + 2 * tq) : 0u;
+      }
+    }
+    const int key_off = warp * 16;
+    bool ok = true;
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      const int s = t % STAGES;
+      if (!mbar_wait(smem_u32(&full_bar[s]), (t / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 22); ok = false; break; }
+      const unsigned char* kt = gbase + s * 2 * KV_BYTES;
+      const unsigned char* vt = kt + KV_BYTES;
+      const int jbase = (tile_begin + t) * BN + key_off;
+      if (jbase < hi) {
+        float st[NH8][4], st2[NH8][4];
+#pragma unroll
+        for (int nt = 0; nt < NH8; ++nt) {
+          st[nt][0] = st[nt][1] = st[nt][2] = st[nt][3] = 0.f;
+          st2[nt][0] = st2[nt][1] = st2[nt][2] = st2[nt][3] = 0.f;
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ks += 2) {
+          unsigned a[4], a2[4];
+          ldmatrix_x4(a, kt + sw128(key_off + (lane & 15), ks * 2 + (lane >> 4)));
+          ldmatrix_x4(a2, kt + sw128(key_off + (lane & 15), (ks + 1) * 2 + (lane >> 4)));
+#pragma unroll
+          for (int nt = 0; nt < NH8; ++nt) {
+            mma_bf16(st[nt], a, qb[ks][nt][0], qb[ks][nt][1]);
+            mma_bf16(st2[nt], a2, qb[ks + 1][nt][0], qb[ks + 1][nt][1]);
+          }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NH8; ++nt) {
+          st[nt][0] += st2[nt][0]; st[nt][1] += st2[nt][1]; st[nt][2] += st2[nt][2]; st[nt][3] += st2[nt][3];
+        }
+        const bool vis0 = jbase + g >= lo && jbase + g <= pos;
+        const bool vis1 = jbase + g + 8 >= lo && jbase + g + 8 <= pos;
+        bool rescale = false;
+        float alpha[NH8][2];
+        unsigned pb[NH8][2];
+#pragma unroll
+        for (int nt = 0; nt < NH8; ++nt) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const float s0 = vis0 ? st[nt][c] * p.scale_log2 : -INFINITY;
+            const float s1 = vis1 ? st[nt][c + 2] * p.scale_log2 : -INFINITY;
+            float mx = fmaxf(s0, s1);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m_run[nt][c], mx);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            alpha[nt][c] = fast_exp2(m_run[nt][c] - m_use);
+            rescale |= m_new != m_run[nt][c];
+            const float p0 = fast_exp2(s0 - m_use), p1 = fast_exp2(s1 - m_use);
+            l_run[nt][c] = l_run[nt][c] * alpha[nt][c] + p0 + p1;
+            m_run[nt][c] = m_new;
+            st[nt][c] = p0;
+            st[nt][c + 2] = p1;
+          }
+          pb[nt][0] = movmatrix_trans(pack_bf16(st[nt][0], st[nt][1]));
+          pb[nt][1] = movmatrix_trans(pack_bf16(st[nt][2], st[nt][3]));
+        }
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+          for (int i = 0; i < D / 16; ++i)
+#pragma unroll
+            for (int nt = 0; nt < NH8; ++nt) {
+              ot[i][nt][0] *= alpha[nt][0]; ot[i][nt][1] *= alpha[nt][1];
+              ot[i][nt][2] *= alpha[nt][0]; ot[i][nt][3] *= alpha[nt][1];
+            }
+        }
+#pragma unroll
+        for (int db = 0; db < D / 16; ++db) {
+          unsigned a[4];
+          ldmatrix_x4_trans(a, vt + sw128(key_off + (lane & 7) + ((lane >> 4) << 3), db * 2 + ((lane >> 3) & 1)));
+#pragma unroll
+          for (int nt = 0; nt < NH8; ++nt) mma_bf16(ot[db][nt], a, pb[nt][0], pb[nt][1]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));     // this warp is done with the stage
+    }
+    pdl_launch_dependents();
+  }
+  __syncthreads();
+
+  // ---- fold the four warps (the tiles' shared memory is free now)
+  float* sm_o = reinterpret_cast<float*>(gbase);             // [4][NHEADS][D]
+  float* sm_m = sm_o + 4 * NHEADS * D;                       // [4][NHEADS]
+  float* sm_l = sm_m + 4 * NHEADS;
+  if (warp < 4) {
+#pragma unroll
+    for (int nt = 0; nt < NH8; ++nt) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float l = l_run[nt][c];
+        l += __shfl_xor_sync(0xffffffffu, l, 4);
+        l += __shfl_xor_sync(0xffffffffu, l, 8);
+        l += __shfl_xor_sync(0xffffffffu, l, 16);
+        const int head = nt * 8 + 2 * tq + c;
+        if (g == 0) { sm_m[warp * NHEADS + head] = m_run[nt][c]; sm_l[warp * NHEADS + head] = l; }
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) {
+          sm_o[(warp * NHEADS + head) * D + i * 16 + g] = ot[i][nt][c];
+          sm_o[(warp * NHEADS + head) * D + i * 16 + g + 8] = ot[i][nt][c + 2];
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (s_abort) return;
+  for (int idx = threadIdx.x; idx < p.group * D; idx += NT_TMA) {
+    const int head = idx / D, d = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * NHEADS + head]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sm_m[w * NHEADS + head];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += sm_l[w * NHEADS + head] * f;
+      acc += sm_o[(w * NHEADS + head) * D + d] * f;
+    }
+    const int gh = hk * p.group + head;
+    if (p.splits == 1) {
+      p.out[(int64_t)t0 * p.ldo + (int64_t)gh * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    } else {
+      const int64_t slot = ((int64_t)b * p.H + gh) * p.splits + split;
+      p.part_o[slot * D + d] = acc;
+      if (d == 0) { p.part_ml[slot * 2] = M; p.part_ml[slot * 2 + 1] = L; }
+    }
+  }
+  if (p.splits == 1) return;
+
+  // ---- fold the splits: the CTA that arrives last does it
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&p.counters[b * p.Hkv + hk], 1) == p.splits - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  float* sm_f = reinterpret_cast<float*>(gbase);
+  float* sm_inv = sm_f + NHEADS * 32;
+  float* sm_l2 = sm_inv + NHEADS;
+  for (int i = threadIdx.x; i < p.group * p.splits; i += NT_TMA) {
+    const int head = i / p.splits, sp = i % p.splits;
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml) + ((int64_t)b * p.H + hk * p.group + head) * p.splits + sp);
+    sm_f[head * 32 + sp] = ml.x;                              // the split's maximum
+    sm_l2[head * 32 + sp] = ml.y;                             // and its sum
+  }
+  __syncthreads();
+  if (threadIdx.x < p.group) {
+    const int head = threadIdx.x;
+    float M = -INFINITY;
+    for (int sp = 0; sp < p.splits; ++sp) M = fmaxf(M, sm_f[head * 32 + sp]);
+    float L = 0.f;
+    for (int sp = 0; sp < p.splits; ++sp) {
+      const float ms = sm_f[head * 32 + sp];
+      const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+      L += sm_l2[head * 32 + sp] * f;
+      sm_f[head * 32 + sp] = f;
+    }
+    sm_inv[head] = L > 0.f ? 1.f / L : 0.f;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < p.group * D; idx += NT_TMA) {
+    const int head = idx / D, d = idx % D;
+    const int gh = hk * p.group + head;
+    const float* po = p.part_o + ((int64_t)b * p.H + gh) * p.splits * D + d;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int sp = 0; sp < p.splits; ++sp) acc += __ldcg(po + sp * D) * sm_f[head * 32 + sp];
+    p.out[(int64_t)t0 * p.ldo + (int64_t)gh * D + d] = __float2bfloat16_rn(acc * sm_inv[head]);
+  }
+  if (threadIdx.x == 0) p.counters[b * p.Hkv + hk] = 0;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+  }
+  return fn;
+}
+
+template <int D, int NH8>
+int launch_tma(const CUtensorMap& map, const Params& p, int B, cudaStream_t stream) {
+  auto k = attention_decode_tma_kernel<D, NH8>;
+  size_t sm = (size_t)2 * STAGES * (D / 64) * BN * 128 + 1024;
+  const size_t fold = (size_t)(4 * NH8 * 8 * D + 2 * 4 * NH8 * 8) * sizeof(float) + 1024;
+  if (fold > sm) sm = fold;
+  static bool opted = false;
+  if (!opted) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    if (e != cudaSuccess) return refuse((int)e, "attention_decode: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    opted = true;
+  }
+  launch_pdl(k, dim3(p.splits, p.Hkv, B), dim3(NT_TMA), sm, stream, map, p);
+  return cuda_status("attention_decode");
 }
 
 template <int D, int NH8>
@@ -393,10 +782,59 @@ DINFER_API int dinfer_attention_decode(const void* q, int64_t ldq, void* out, in
   p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.splits = splits;
   p.part_o = scratch_floats;
   p.part_ml = scratch_floats ? scratch_floats + (int64_t)B * H * splits * D : nullptr;
-  p.counters = scratch_counters;
+  p.counters = scratch_counters; p.status = nullptr;
   const int nh8 = (p.group + 7) / 8;
   if (D == 64) return nh8 == 1 ? launch<64, 1>(p, B, stream) : launch<64, 2>(p, B, stream);
   return nh8 == 1 ? launch<128, 1>(p, B, stream) : launch<128, 2>(p, B, stream);
+}
+
+// The TMA variant (pages of at least 8 tokens): same arguments plus the number of pages of the cache
+// tensor (for the tensor map) and the device status word that a bounded wait sets when it runs out.
+DINFER_API int dinfer_attention_decode_tma(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                           int64_t num_blocks, const int* block_table, int max_blocks,
+                                           const int* cu_seqlens, const int* seq_lens, int B, int H, int Hkv, int D,
+                                           int block_size, float scale, int window, int splits, float* scratch_floats,
+                                           int* scratch_counters, int* status, cudaStream_t stream) {
+  if (B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || max_blocks <= 0 || num_blocks <= 0)
+    return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: bad sizes B=%d H=%d Hkv=%d", B, H, Hkv);
+  if (!dinfer_attention_decode_supports(D, H / Hkv, block_size) || block_size < 8)
+    return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: head_dim %d, group %d, block_size %d not supported "
+                  "(head_dim 64 or 128, group <= 16, power-of-two pages of at least 8)", D, H / Hkv, block_size);
+  if ((ldq % 2) || (ldo % 2) || (reinterpret_cast<uintptr_t>(q) & 3) || (reinterpret_cast<uintptr_t>(cache) & 15))
+    return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: q rows must be 4-byte and the cache 16-byte aligned");
+  if (splits > 32) return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: at most 32 key splits, got %d", splits);
+  if (splits < 1 || (splits > 1 && (!scratch_floats || !scratch_counters)) || !status)
+    return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: splits=%d needs scratch, and a status word is required", splits);
+  if (Hkv > 65535 || B > 65535) return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: too many heads or requests for the grid");
+  const int64_t cache_rows = num_blocks * 2 * Hkv * block_size;
+  if (cache_rows > 0x7fffffffLL) return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: the cache has too many rows for a tensor map coordinate");
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap map;
+  {
+    const int br = block_size < BN ? block_size : BN;
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)cache_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)br};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: tensor map of the cache failed with %d", (int)r);
+  }
+  Params p;
+  p.q = (const __nv_bfloat16*)q; p.ldq = ldq; p.out = (__nv_bfloat16*)out; p.ldo = ldo;
+  p.cache = (const __nv_bfloat16*)cache; p.block_table = block_table; p.max_blocks = max_blocks;
+  p.cu_seqlens = cu_seqlens; p.seq_lens = seq_lens; p.H = H; p.Hkv = Hkv; p.group = H / Hkv;
+  p.block_size = block_size; p.bs_log2 = 0;
+  while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
+  p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.splits = splits;
+  p.part_o = scratch_floats;
+  p.part_ml = scratch_floats ? scratch_floats + (int64_t)B * H * splits * D : nullptr;
+  p.counters = scratch_counters; p.status = status;
+  const int nh8 = (p.group + 7) / 8;
+  if (D == 64) return nh8 == 1 ? launch_tma<64, 1>(map, p, B, stream) : launch_tma<64, 2>(map, p, B, stream);
+  return nh8 == 1 ? launch_tma<128, 1>(map, p, B, stream) : launch_tma<128, 2>(map, p, B, stream);
 }
 
 // ---- the entry point that allocates nothing (see attention_decode_static.h)

@@ -213,43 +213,57 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const uint32_t tmem = s_tmem_base;
 
   if (warp == 0) {
-    if (lane == 0) {                                                // ---- TMA producer
+    // ---- TMA producer: the whole warp.  Q once (lane 0); then per tile one copy per page, K / V and
+    // 64-wide half, spread over the lanes so that they are requested side by side.
+    if (lane == 0) {
       const uint32_t qb = smem_u32(&q_full);
       mbar_expect_tx(qb, (b_on ? 2 : 1) * Q_BYTES);
       for (int w = 0; w < (b_on ? 2 : 1); ++w)
         for (int h = 0; h < NH; ++h)
           tma_load_3d(sQ + w * Q_BYTES + h * Q_HALF, &map_q, h * 64, hk * p.group, t0 + first_tok + w * (BM / p.group), qb);
-      const int br = min(p.block_size, BN);                          // rows of one K/V box
-      const int boxes = BN / br;
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j % STAGES;
-        if (!mbar_wait(smem_u32(&kv_empty[s]), ((j / STAGES) & 1) ^ 1)) { s_abort = 1; atomicExch(p.status, 11); break; }
-        const int j0 = (tile_begin + j) * BN;
-        const uint32_t bar = smem_u32(&kv_full[s]);
-        uint32_t bytes = 0;
-        for (int x = 0; x < boxes; ++x) {
+    }
+    const int br = min(p.block_size, BN);                          // rows of one K/V box
+    const int boxes = BN / br;
+    constexpr int PER_BOX = 2 * NH;
+    const int n_ops = boxes * PER_BOX;                             // <= 64
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j % STAGES;
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(smem_u32(&kv_empty[s]), ((j / STAGES) & 1) ^ 1);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { if (lane == 0) { s_abort = 1; atomicExch(p.status, 11); } break; }
+      const int j0 = (tile_begin + j) * BN;
+      const uint32_t bar = smem_u32(&kv_full[s]);
+      int row[2], col[2]; uint32_t dst[2]; bool valid[2];
+      uint32_t bytes = 0;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int o = lane + 32 * u;
+        valid[u] = false;
+        if (o < n_ops) {
+          const int x = o / PER_BOX, r = o % PER_BOX, kv = r / NH, h = r % NH;
           const int key = j0 + x * br;
-          if (key >= hi || key + br <= lo) continue;
-          const int e = (key >> p.bs_log2) - table_first;
-          const int blk = e < TABLE_SLOTS ? s_table[e] : table[key >> p.bs_log2];
-          if (blk >= 0) bytes += 2 * NH * br * 128;
-        }
-        if (bytes == 0) { mbar_arrive(bar); continue; }
-        mbar_expect_tx(bar, bytes);
-        for (int x = 0; x < boxes; ++x) {
-          const int key = j0 + x * br;
-          if (key >= hi || key + br <= lo) continue;
-          const int e = (key >> p.bs_log2) - table_first;
-          const int blk = e < TABLE_SLOTS ? s_table[e] : table[key >> p.bs_log2];
-          if (blk < 0) continue;
-          const int row_k = ((blk * 2 + 0) * p.Hkv + hk) * p.block_size + (key & (p.block_size - 1));
-          const int row_v = row_k + p.Hkv * p.block_size;
-          for (int h = 0; h < NH; ++h) {
-            tma_load_2d(sK + s * KV_BYTES + h * KV_HALF + x * br * 128, &map_kv, h * 64, row_k, bar);
-            tma_load_2d(sV + s * KV_BYTES + h * KV_HALF + x * br * 128, &map_kv, h * 64, row_v, bar);
+          if (key < hi && key + br > lo) {
+            const int e = (key >> p.bs_log2) - table_first;
+            const int blk = e < TABLE_SLOTS ? s_table[e] : table[key >> p.bs_log2];
+            if (blk >= 0) {
+              valid[u] = true;
+              row[u] = ((blk * 2 + kv) * p.Hkv + hk) * p.block_size + (key & (p.block_size - 1));
+              col[u] = h * 64;
+              dst[u] = (kv == 0 ? sK : sV) + s * KV_BYTES + h * KV_HALF + x * br * 128;
+              bytes += br * 128;
+            }
           }
         }
       }
+      bytes = __reduce_add_sync(0xffffffffu, bytes);
+      if (lane == 0) {
+        if (bytes == 0) mbar_arrive(bar); else mbar_expect_tx(bar, bytes);
+      }
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+        if (valid[u]) tma_load_2d(dst[u], &map_kv, col[u], row[u], bar);
     }
   } else if (warp == 1) {
     if (lane == 0) {                                                // ---- MMA issue

@@ -72,6 +72,18 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
     floats = counters = None
     if splits > 1:
         floats, counters = _decode_scratch(q.device, B * num_heads * splits * (head_dim + 2), B * num_kv_heads)
+    if cache.shape[3] >= 8:
+        # pages of at least 8 tokens: tiles by TMA through a tensor map over the cache, mbarrier ring
+        from . import gemm_ops
+        status = gemm_ops._state(q.device)["status"]
+        lib, f = _fn("attention_decode", "dinfer_attention_decode_tma",
+                     [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
+                      c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+        check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), cache.shape[0], ptr(block_table),
+                     block_table.shape[1], ptr(cu_seqlens), ptr(seq_lens), B, num_heads, num_kv_heads, head_dim,
+                     cache.shape[3], float(scale), int(window), int(splits), ptr(floats), ptr(counters), ptr(status),
+                     stream_handle()), "attention_decode_tma")
+        return out
     lib, f = _fn("attention_decode", "dinfer_attention_decode",
                  [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                   c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p])
