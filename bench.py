@@ -127,7 +127,7 @@ def decode_run(llm, cfg, batch, context, steps, warmup, rng, measure_e2e, want_l
     import torch
     from dinfer_b200 import SamplingParams
     V = cfg["vocab_size"]
-    total_steps = warmup + steps * (2 if measure_e2e else 1) + (1 if want_launches else 0)
+    total_steps = warmup + (steps if measure_e2e else 1)
     # requests that finish their prompt early decode while the others still prefill (two portions each),
     # so leave room for that drift; the bytes of the roofline use the contexts actually reached
     prompt_len = context - total_steps - 2 * batch - 1
@@ -142,14 +142,9 @@ def decode_run(llm, cfg, batch, context, steps, warmup, rng, measure_e2e, want_l
     torch.cuda.synchronize()
     sampler = ClockSampler()
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        llm.step()
-    e1.record()
-    torch.cuda.synchronize()
-    res["ms_per_step"] = e0.elapsed_time(e1) / steps
     if measure_e2e:
+        # end to end: K steps through the Python entry point; every step copies its plan (token ids,
+        # positions, page tables) host->device from pinned memory and reads the sampled tokens back
         t0 = time.perf_counter()
         for _ in range(steps):
             llm.step()
@@ -157,10 +152,24 @@ def decode_run(llm, cfg, batch, context, steps, warmup, rng, measure_e2e, want_l
         res["e2e_ms_per_step"] = (time.perf_counter() - t0) * 1e3 / steps
         res["h2d_bytes_per_step"] = llm.runner.plan.h2d_bytes
         res["d2h_bytes_per_step"] = 4 * batch
+    else:
+        llm.step()
+    # device time of one decode step: the step's captured graph (forward of the whole batch) replayed K
+    # times back to back at the context just reached, timed with CUDA events, no host in between
+    res["mean_context"] = sum(r.num_tokens for r in llm._requests.values()) / batch - 1
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    from dinfer_b200.kernels import lib as _lib
+    l0 = _lib.launch_count()
+    e0.record()
+    from dinfer_b200.sampling.sampler import argmax
+    tokens = torch.empty(llm.runner.engine.max_num_seqs, dtype=torch.int32, device=llm.runner.device)
+    llm.runner.replay_last_decode(steps, after=lambda logits: argmax(logits[:batch], out=tokens[:batch]))
+    e1.record()
+    torch.cuda.synchronize()
+    res["ms_per_step"] = e0.elapsed_time(e1) / steps
+    res["launches_per_step"] = (_lib.launch_count() - l0) // steps
     res["clocks"] = sampler.stop()
-    if want_launches:
-        res["launches_per_step"] = count_launches(llm.step)
-    res["mean_context"] = sum(r.num_tokens for r in llm._requests.values()) / batch
     for rid in list(llm._requests):
         llm.abort(rid)
     return res
@@ -256,8 +265,8 @@ def main() -> int:
     main_run = decode_run(llm, cfg, a.batch, a.context, a.steps, a.warmup, rng, measure_e2e=True, want_launches=True)
     ms = main_run["ms_per_step"]
     value = a.batch * 1e3 / ms
-    # mean context during the device-timed steps (the e2e steps and the launch count came after them)
-    ctx_mid = main_run["mean_context"] - 1 - a.steps - a.steps / 2
+    # context of the device-timed step (the graph is replayed at the context the requests had reached)
+    ctx_mid = main_run["mean_context"]
     step_bytes = nums["weight_bytes"] + a.batch * ctx_mid * nums["kv_bytes_per_token"]
     achieved = step_bytes / (ms * 1e-3) / 1e9
 

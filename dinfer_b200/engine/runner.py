@@ -207,6 +207,7 @@ class ModelRunner:
         rec = self._graphs.get(bucket) or self._capture(bucket)
         self.plan.build(entries, starts, pad_reqs=bucket, table_width=rec["width"], dev=rec["dev"])
         rec["graph"].replay()
+        self._last_graph = rec
         kernel_lib.add_launches(rec["launches"])
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
         if len(wanted) == B:
@@ -214,6 +215,21 @@ class ModelRunner:
         if not wanted:
             return rec["logits"][:0]
         return rec["logits"][torch.tensor(wanted, device=self.device)]
+
+    def replay_last_decode(self, times: int = 1, after=None) -> int:
+        """Replay the decode graph of the last decode-only step ``times`` more times with the same
+        batch (same tokens, positions and pages: the step's device work again, nothing advances).
+        For measuring the device time of one decode step without the host between steps.  Returns the
+        kernel launches replayed."""
+        rec = getattr(self, "_last_graph", None)
+        if rec is None:
+            raise RuntimeError("no decode-only step has run through a CUDA graph yet")
+        for _ in range(times):
+            rec["graph"].replay()
+            if after is not None:
+                after(rec["logits"])                  # e.g. the sampling kernel, launched behind the graph
+        kernel_lib.add_launches(rec["launches"] * times)
+        return rec["launches"] * times
 
     def check_device_status(self) -> None:
         """Raise if a kernel recorded a fault in its status word (a bounded wait that ran out).
