@@ -62,6 +62,36 @@ class PlanBuilder:
         return (2 * _align(T) + _align(R) + _align(B + 1) + 3 * _align(B)
                 + ng * (_align(T) + _align(B * width)) + 16)
 
+    def layout(self, T: int, B: int, R: int, width: int) -> Tuple[Dict[str, Tuple[int, int]], int]:
+        """(offset, words) of every field of a packed plan, and the plan's length in words."""
+        views: Dict[str, Tuple[int, int]] = {}
+        off = 0
+        fields = [("ids", T), ("pos", T), ("rows", R), ("cu", B + 1), ("seq", B), ("sslots", B), ("fresh", B)]
+        for g in range(len(self.manager.groups)):
+            fields += [(f"slot{g}", T), (f"tab{g}", B * width)]
+        for name, n in fields:
+            views[name] = (off, n)
+            off = _align(off + n)
+        return views, off
+
+    def _next_turn(self) -> int:
+        """The next pinned buffer of the ring, once its last copy has left it."""
+        k = self._turn
+        self._turn = (k + 1) % self.RING
+        if self._events[k] is not None:
+            self._events[k].synchronize()
+        return k
+
+    def _send(self, k: int, words: int, dev: torch.Tensor) -> None:
+        if words > dev.numel():
+            raise ValueError("the plan does not fit its device buffer")
+        dev[:words].copy_(self._host[k][:words], non_blocking=True)
+        if dev.is_cuda:
+            ev = self._events[k] or torch.cuda.Event()
+            ev.record()
+            self._events[k] = ev
+        self.h2d_bytes = words * 4
+
     def build(self, entries: Sequence[StepEntry], starts: Sequence[int], *, pad_reqs: Optional[int] = None,
               table_width: Optional[int] = None, dev: Optional[torch.Tensor] = None):
         """``starts[i]`` = tokens of entry i already in the cache; pages must be allocated already.
@@ -123,20 +153,13 @@ class PlanBuilder:
         fresh[:n_real] = [1 if m.state_slots.take_fresh(e.req_id) else 0 for e in entries]
 
         # pack: the order and the alignment fix every view's offset for given (T, B, R, width)
-        k = self._turn
-        self._turn = (k + 1) % self.RING
-        if self._events[k] is not None:
-            self._events[k].synchronize()
+        k = self._next_turn()
         host = self._host[k].numpy()
-        off = 0
-        views: Dict[str, Tuple[int, int]] = {}
+        views, off = self.layout(T, B, rows_np.size, width)
 
         def put(name, arr):
-            nonlocal off
-            n = arr.size
-            host[off:off + n] = arr.reshape(-1)
-            views[name] = (off, n)
-            off = _align(off + n)
+            o, n = views[name]
+            host[o:o + n] = arr.reshape(-1)
 
         put("ids", ids); put("pos", pos); put("rows", rows_np); put("cu", cu); put("seq", seq)
         put("sslots", sslots); put("fresh", fresh)
@@ -144,13 +167,7 @@ class PlanBuilder:
             put(f"slot{g}", slots[g]); put(f"tab{g}", tables[g])
         if dev is None:
             dev = self._dev[k]
-        if off > dev.numel():
-            raise ValueError("the plan does not fit its device buffer")
-        dev[:off].copy_(self._host[k][:off], non_blocking=True)
-        if dev.is_cuda:
-            ev = torch.cuda.Event()
-            ev.record()
-            self._events[k] = ev
+        self._send(k, off, dev)
 
         def view(name):
             o, n = views[name]
@@ -166,5 +183,87 @@ class PlanBuilder:
             any_decode=any(n == 1 for n in lens), any_prefill=any(n > 1 for n in lens),
             cu_seqlens_host=cu.tolist(), seq_lens_host=seq.tolist(),
             state_slots_host=sslots.tolist(), state_fresh_host=fresh.tolist())
-        self.h2d_bytes = off * 4
         return view("ids"), view("rows"), ctx
+
+
+class DecodePlan:
+    """The packed plan of a captured decode graph, kept on the host between steps.
+
+    A decode-only step changes little of its plan: one token, position and slot per request and,
+    now and then, one more page at the end of a table.  So the host keeps the last plan of the
+    graph's bucket and rewrites only that; rows whose request changed (or whose table is another
+    list, as after a preemption) are written whole.  The layout is the one ``PlanBuilder.build``
+    makes for ``pad_reqs=bucket`` and this table width, which the graph was captured with."""
+
+    def __init__(self, builder: PlanBuilder, bucket: int, width: int, dev: torch.Tensor):
+        self.builder, self.bucket, self.width, self.dev = builder, bucket, width, dev
+        self.views, self.words = builder.layout(bucket, bucket, bucket, width)
+        self.ng = len(builder.manager.groups)
+        self.shadow = np.zeros(self.words, dtype=np.int32)
+        f = self._field
+        f("rows")[:] = np.arange(bucket, dtype=np.int32)
+        f("cu")[:] = np.arange(bucket + 1, dtype=np.int32)
+        f("seq")[:] = 1
+        for g in range(self.ng):
+            f(f"slot{g}")[:] = -1
+            f(f"tab{g}")[:] = -1
+        self._ids, self._pos, self._seq = f("ids"), f("pos"), f("seq")
+        self._sslots, self._fresh = f("sslots"), f("fresh")
+        self._slot = [f(f"slot{g}") for g in range(self.ng)]
+        self._tab = [f(f"tab{g}").reshape(bucket, width) for g in range(self.ng)]
+        self._windowed = [builder.manager.groups[g].window is not None for g in range(self.ng)]
+        # per row and group: the table list last copied from, and how many of its entries
+        self._src = [[None] * self.ng for _ in range(bucket)]
+        self._copied = [[0] * self.ng for _ in range(bucket)]
+        self._live = 0
+
+    def _field(self, name: str) -> np.ndarray:
+        o, n = self.views[name]
+        return self.shadow[o:o + n]
+
+    def fill(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> None:
+        """Write the step of ``entries`` (one token each) into the plan and send it to the device."""
+        b = self.builder
+        m = b.manager
+        bs = m.block_size
+        n_real = len(entries)
+        if n_real > self.bucket:
+            raise ValueError("more requests than the graph's bucket")
+        width = self.width
+        for i, e in enumerate(entries):
+            p = starts[i]
+            self._ids[i] = e.tokens[0]
+            self._pos[i] = p
+            self._seq[i] = p + 1
+            self._sslots[i] = m.state_slots.slot(e.req_id)
+            self._fresh[i] = 1 if m.state_slots.take_fresh(e.req_id) else 0
+            for g in range(self.ng):
+                t = m.block_table(e.req_id, g)
+                n = min(len(t), width)
+                row = self._tab[g][i]
+                if self._src[i][g] is not t or self._windowed[g]:
+                    row[:n] = t[:n]
+                    row[n:] = -1
+                    self._src[i][g] = t
+                else:
+                    c = self._copied[i][g]
+                    if n > c:
+                        row[c:n] = t[c:n]
+                self._copied[i][g] = n
+                blk = t[p // bs] if p // bs < n else -1
+                self._slot[g][i] = blk * bs + p % bs if blk >= 0 else -1
+        for i in range(n_real, self._live):           # rows that fell out of use become dummy rows
+            self._ids[i] = 0
+            self._pos[i] = 0
+            self._seq[i] = 1
+            self._sslots[i] = 0
+            self._fresh[i] = 0
+            for g in range(self.ng):
+                self._tab[g][i] = -1
+                self._slot[g][i] = -1
+                self._src[i][g] = None
+                self._copied[i][g] = 0
+        self._live = n_real
+        k = b._next_turn()
+        b._host[k].numpy()[:self.words] = self.shadow
+        b._send(k, self.words, self.dev)

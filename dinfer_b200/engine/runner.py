@@ -26,7 +26,7 @@ from ..kernels import lib as kernel_lib
 from ..models.decoder import DecoderModel
 from ..parts.base import BuildEnv, CacheBinding, KvCacheNeed, StateNeed
 from ..weights.loader import SafetensorsSource, WeightSource, load_tensors
-from .batch import OutOfPages, PlanBuilder, StepEntry
+from .batch import DecodePlan, OutOfPages, PlanBuilder, StepEntry
 
 _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -197,7 +197,7 @@ class ModelRunner:
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
         rec = dict(graph=graph, dev=dev, logits=logits, splits=ctx.decode_splits, width=width,
-                   launches=kernel_lib.launch_count() - n0)
+                   launches=kernel_lib.launch_count() - n0, plan=DecodePlan(self.plan, bucket, width, dev))
         self._graphs[bucket] = rec
         return rec
 
@@ -205,7 +205,7 @@ class ModelRunner:
         B = len(entries)
         bucket = next(b for b in self._buckets if b >= B)
         rec = self._graphs.get(bucket) or self._capture(bucket)
-        self.plan.build(entries, starts, pad_reqs=bucket, table_width=rec["width"], dev=rec["dev"])
+        rec["plan"].fill(entries, starts)
         rec["graph"].replay()
         self._last_graph = rec
         kernel_lib.add_launches(rec["launches"])
