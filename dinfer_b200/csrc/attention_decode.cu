@@ -126,6 +126,7 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int b = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
+  pdl_launch_dependents();
   // Before pdl_wait(): only what no kernel of this step writes (the batch's index arrays, copied to the
   // device before the step's first kernel, and cache pages of older tokens).  The newest token's K/V and
   // the q rows come from the kernel just before this one, so the tile that holds position `pos` and q
@@ -161,7 +162,6 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
     cp_async_commit();
   }
   if (!waited) pdl_wait();
-  pdl_launch_dependents();
 
   // Q^T as the B operand: head nt*8 + g, dims ks*16 + {2tq, 2tq+1} and + 8
   unsigned qb[D / 16][NH8][2];
@@ -416,6 +416,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Pa
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int b = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
+  pdl_launch_dependents();
   // before pdl_wait(): only the batch's index arrays and cache pages of older tokens (see the other kernel)
   const int t0 = p.cu_seqlens[b];
   if (p.cu_seqlens[b + 1] - t0 != 1) return;
@@ -508,7 +509,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Pa
         if (valid[u]) tma_load_2d(dst[u], &map_kv, col[u], row[u], bar);
     }
     if (!waited) pdl_wait();
-    pdl_launch_dependents();
   } else {                                                    // ---- four compute warps, 16 keys of every tile each
     pdl_wait();                                               // q comes from the kernel before this one
     unsigned qb[D / 16][NH8][2];
@@ -600,7 +600,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Pa
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));     // this warp is done with the stage
     }
-    pdl_launch_dependents();
   }
   __syncthreads();
 

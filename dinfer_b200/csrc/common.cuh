@@ -107,20 +107,36 @@ namespace dinfer {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 // the usual opening of a kernel with nothing to do ahead of its inputs
-__device__ __forceinline__ void pdl_enter() { pdl_wait(); pdl_launch_dependents(); }
+__device__ __forceinline__ void pdl_enter() { pdl_launch_dependents(); pdl_wait(); }
+
+// `cluster`: thread-block cluster dimensions (all 1 = no cluster attribute).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, dim3 cluster, size_t smem,
+                                      cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (cluster.x * cluster.y * cluster.z > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster.x; attr[n].val.clusterDim.y = cluster.y; attr[n].val.clusterDim.z = cluster.z;
+    ++n;
+  }
+  // DINFER_NO_PDL=1 (read once) launches without the attribute: a switch for measuring what the overlap buys
+  static const bool off = [] { const char* e = getenv("DINFER_NO_PDL"); return e && e[0] == '1'; }();
+  if (!off) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr; cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  // DINFER_NO_PDL=1 (read once) launches without the attribute: a switch for measuring what the overlap buys
-  static const bool off = [] { const char* e = getenv("DINFER_NO_PDL"); return e && e[0] == '1'; }();
-  cfg.attrs = attr; cfg.numAttrs = off ? 0 : 1;
-  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  return launch_pdl_cluster(kernel, grid, block, dim3(1, 1, 1), smem, stream, args...);
 }
 }  // namespace dinfer
 

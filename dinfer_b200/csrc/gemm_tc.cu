@@ -2,7 +2,7 @@
 // TMA (cp.async.bulk.tensor, 128-byte swizzle) stages K-major operand tiles in shared memory,
 // one elected thread issues tcgen05.mma (cta_group::1, kind::f16, 128 x N_TILE x 16) with the f32
 // accumulator in tensor memory, tcgen05.commit hands shared-memory stages back to the producer, and
-// four epilogue warps read the accumulator with tcgen05.ld.  No cluster launch, no multicast.
+// four epilogue warps read the accumulator with tcgen05.ld.  No multicast; a cluster only for split K.
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocation + MMA issue,
 // warps 2..5 = epilogue (TMEM lane quarter = warp index mod 4).
@@ -11,9 +11,10 @@
 //   * prompts:  the 128 tile rows are tokens, the N_TILE columns are weight rows;
 //   * decoding (few tokens): operands swapped, the 128 tile rows are WEIGHT rows and the (16..64)
 //     columns are tokens, so that a handful of tokens still fills the tensor-core tile and each CTA
-//     streams its weight rows from HBM exactly once; K may be split across CTAs, the partial sums go
-//     to an f32 scratch and the CTA of a tile that arrives last adds them up (a counter per tile in
-//     the same scratch, left at zero for the next launch).
+//     streams its weight rows from HBM exactly once; K may be split across up to 8 CTAs, which then
+//     form a thread-block cluster: every CTA owns a share of the tile's 128 rows, the others store
+//     their partial sums of those rows into its shared memory (st.shared::cluster), and after one
+//     cluster barrier each CTA adds its share up, always in split order, and writes it.
 //
 // Every wait on an mbarrier is bounded: on time-out the kernel records a code in a status word,
 // lets copies in flight land, frees its tensor memory and returns (the host reads the status word).
@@ -39,8 +40,6 @@ struct GemmParams {
   void* out; int64_t ldc;        // [tokens, N] row-major, bf16 or f32
   int tokens, N, K;
   int k_blocks_per_split, splits;
-  float* partial;                // [splits][tile pairs][N_TILE][TILE_M] f32 (swap + split only)
-  int* counters;                 // one per tile pair
   int* status;                   // device status word: 0 = fine
 };
 
@@ -93,6 +92,23 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
                : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// ---- thread-block cluster: barrier phases and stores into another CTA's shared memory
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
 // start address >> 4, leading byte offset 1 (unused with swizzle), stride byte offset 1024 B (8 rows),
@@ -111,8 +127,14 @@ template <> __device__ __forceinline__ float out_cast<float>(float v) { return v
 template <> __device__ __forceinline__ __nv_bfloat16 out_cast<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 template <int N_TILE> constexpr int tmem_cols() { return N_TILE <= 32 ? 32 : (N_TILE <= 64 ? 64 : (N_TILE <= 128 ? 128 : 256)); }
-template <int N_TILE, int STAGES> constexpr size_t gemm_smem_bytes() {
-  return (size_t)STAGES * (TILE_M * BLOCK_K + N_TILE * BLOCK_K) * 2 + 1024;   // + slack to align to 1024
+// Rows of the tile that one CTA of a split-K cluster owns, and the floats of its receive buffer
+// [splits][N_TILE][rows]: splits * ceil(128 / splits) <= RECV_ROWS for every split count up to 8.
+constexpr int MAX_SPLITS = 8;
+constexpr int RECV_ROWS = 136;
+__host__ __device__ constexpr int rows_per_cta(int splits) { return (TILE_M + splits - 1) / splits; }
+template <int N_TILE, int STAGES> constexpr size_t gemm_smem_bytes(bool with_recv) {
+  return (size_t)STAGES * (TILE_M * BLOCK_K + N_TILE * BLOCK_K) * 2 + 1024      // + slack to align to 1024
+         + (with_recv ? (size_t)N_TILE * RECV_ROWS * 4 : 0);
 }
 
 // grid: (tiles of the 128-row operand, tiles of the N_TILE-row operand, K splits)
@@ -122,15 +144,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], tmem_full_bar;
   __shared__ uint32_t s_tmem_base;
-  __shared__ int s_abort, s_last;
+  __shared__ int s_abort;
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   constexpr uint32_t A_BYTES = TILE_M * BLOCK_K * 2, B_BYTES = N_TILE * BLOCK_K * 2;
+  const uint32_t recv_base = smem_base + STAGES * (A_BYTES + B_BYTES);       // split-K receive buffer (SWAP only)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int a0 = blockIdx.x * TILE_M, b0 = blockIdx.y * N_TILE;
   const int total_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
   const int kb_begin = blockIdx.z * p.k_blocks_per_split;
   const int kb_end = min(total_kb, kb_begin + p.k_blocks_per_split);
   const int n_kb = max(0, kb_end - kb_begin);
+  pdl_launch_dependents();
+  // split K: the CTAs of a tile are one cluster.  First phase of its barrier: every CTA has started,
+  // so its shared memory may be written from the others (waited for just before those stores).
+  const bool clustered = SWAP && p.splits > 1;
+  if (clustered) cluster_arrive_relaxed();
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -163,7 +191,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         else tma_load_2d(sa + A_BYTES, &map_b, (kb_begin + i) * BLOCK_K, b0, bar);
       }
       pdl_wait();
-      pdl_launch_dependents();
       for (int i = 0; i < ahead; ++i) {
         const uint32_t bar = smem_u32(&full_bar[i]);
         const uint32_t sa = smem_base + i * (A_BYTES + B_BYTES);
@@ -210,8 +237,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!ok && lane == 0) { s_abort = 1; atomicExch(p.status, 3); }
       tcgen05_fence_after();
     }
+    if (clustered) cluster_wait_acquire();                      // all CTAs of the cluster run: stores may go out
     if (ok) {
       OutT* out = reinterpret_cast<OutT*>(p.out);
+      const int rows_per = rows_per_cta(p.splits);
+      const int owner = r / rows_per;                           // the CTA that adds up this row
+      const uint32_t recv_remote = clustered ? map_to_cta(recv_base, owner) : 0u;
+      const uint32_t my_rank = clustered ? cluster_ctarank() : 0u;
 #pragma unroll 1
       for (int c0 = 0; c0 < N_TILE; c0 += 16) {
         uint32_t v[16];
@@ -252,10 +284,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (b0 + c0 + j < p.tokens) out[(int64_t)(b0 + c0 + j) * p.ldc + n] = out_cast<OutT>(__uint_as_float(v[j]));
             }
           } else {
-            float* part = p.partial + (((int64_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * (N_TILE * TILE_M);
+            // recv[split][token column][row of the owner's share]: consecutive lanes, consecutive words
+            const uint32_t dst = recv_remote + (uint32_t)(((my_rank * N_TILE + c0) * rows_per + (r - owner * rows_per)) * 4);
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-              if (b0 + c0 + j < p.tokens) part[(c0 + j) * TILE_M + r] = __uint_as_float(v[j]);
+              if (b0 + c0 + j < p.tokens) st_cluster_f32(dst + (uint32_t)(j * rows_per * 4), __uint_as_float(v[j]));
           }
         }
       }
@@ -263,36 +296,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tcgen05_fence_before();
   }
 
-  // ---- split-K: the CTA of this tile that arrives last adds the partial sums up
-  if (SWAP && p.splits > 1) {
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) s_last = atomicAdd(&p.counters[blockIdx.y * gridDim.x + blockIdx.x], 1) == p.splits - 1;
-    __syncthreads();
-    if (s_last && !s_abort) {
-      __threadfence();
+  // ---- split K: after the second barrier phase the partial sums of this CTA's rows are all here
+  if (clustered) {
+    __syncwarp();
+    if (warp < 2) cluster_wait_acquire();                       // first phase (the epilogue warps have passed it)
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (!s_abort) {
       OutT* out = reinterpret_cast<OutT*>(p.out);
-      const int64_t tile = (int64_t)blockIdx.y * gridDim.x + blockIdx.x;
-      const int64_t split_stride4 = (int64_t)gridDim.y * gridDim.x * (N_TILE * TILE_M / 4);
-      const int cols = min(N_TILE, p.tokens - b0);             // token columns that exist
-      const float4* base = reinterpret_cast<const float4*>(p.partial) + tile * (N_TILE * TILE_M / 4);
-      // four consecutive weight rows of one token per thread; the loads of all splits are independent
-      for (int i4 = threadIdx.x; i4 < cols * (TILE_M / 4); i4 += NTHREADS) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-        for (int s = 0; s < p.splits; ++s) {
-          const float4 v = __ldcg(base + s * split_stride4 + i4);
-          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        }
-        const int c = i4 / (TILE_M / 4), r = (i4 % (TILE_M / 4)) * 4;
-        const int t = b0 + c, n = a0 + r;
-        OutT* dst = out + (int64_t)t * p.ldc + n;
-        const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (n + e < p.N) dst[e] = out_cast<OutT>(a4[e]);
+      const int rank = (int)cluster_ctarank();
+      const int rows_per = rows_per_cta(p.splits);
+      const int rows_mine = min(rows_per, TILE_M - rank * rows_per);
+      const int cols = min(N_TILE, p.tokens - b0);              // token columns that exist
+      const float* recv = reinterpret_cast<const float*>(smem_dyn + (recv_base - smem_u32(smem_dyn)));
+      for (int i = threadIdx.x; i < cols * rows_mine; i += NTHREADS) {
+        const int c = i / rows_mine, rl = i - c * rows_mine;
+        float acc = 0.f;
+        for (int s = 0; s < p.splits; ++s) acc += recv[(s * N_TILE + c) * rows_per + rl];
+        const int n = a0 + rank * rows_per + rl;
+        if (n < p.N) out[(int64_t)(b0 + c) * p.ldc + n] = out_cast<OutT>(acc);
       }
-      if (threadIdx.x == 0) p.counters[blockIdx.y * gridDim.x + blockIdx.x] = 0;
     }
   }
 
@@ -340,14 +363,15 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_
 template <int N_TILE, int STAGES, bool SWAP, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
   auto k = gemm_tc_kernel<N_TILE, STAGES, SWAP, OutT>;
-  constexpr size_t sm = gemm_smem_bytes<N_TILE, STAGES>();
+  const size_t sm = gemm_smem_bytes<N_TILE, STAGES>(SWAP && p.splits > 1);
   static bool opted = false;
   if (!opted) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<N_TILE, STAGES>(SWAP));
     if (e != cudaSuccess) return refuse((int)e, "gemm_tc: shared memory opt-in failed: %s", cudaGetErrorString(e));
     opted = true;
   }
-  launch_pdl(k, grid, dim3(NTHREADS), sm, stream, ma, mb, p);
+  cudaError_t e = launch_pdl_cluster(k, grid, dim3(NTHREADS), dim3(1, 1, SWAP ? p.splits : 1), sm, stream, ma, mb, p);
+  if (e != cudaSuccess) return refuse((int)e, "gemm_tc: launch failed: %s", cudaGetErrorString(e));
   return cuda_status("gemm_tc");
 }
 
@@ -355,22 +379,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
 
 DINFER_DEFINE_LAST_ERROR()
 
-// Bytes of scratch the decode orientation needs for `splits` > 1: f32 partial tiles, then one int
-// counter per tile (zero before the first launch; every launch leaves them zero).
-DINFER_API int64_t dinfer_gemm_tc_scratch_bytes(int tokens, int N, int splits) {
-  if (splits <= 1) return 0;
-  const int n_tile = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64);
-  const int64_t tiles = (int64_t)((N + TILE_M - 1) / TILE_M) * ((tokens + n_tile - 1) / n_tile);
-  return tiles * splits * n_tile * TILE_M * 4 + tiles * 4;
-}
-
 // x [tokens, K] (row stride ldx), w [N, K] (row stride ldw), both bf16; out [tokens, N] (row stride ldc)
-// bf16 (out_f32 = 0) or f32.  tokens <= 64: decode orientation with `splits` K splits (scratch from
-// dinfer_gemm_tc_scratch_bytes when splits > 1).  More tokens: prompt orientation, splits ignored.
+// bf16 (out_f32 = 0) or f32.  tokens <= 64: decode orientation with `splits` K splits (at most 8: the
+// CTAs of a tile form a cluster).  More tokens: prompt orientation, splits ignored.
 // status: a device int that a kernel sets non-zero when one of its bounded waits ran out.
 DINFER_API int dinfer_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldc,
-                              int out_f32, int tokens, int N, int K, int splits, float* partial, int* counters,
-                              int* status, cudaStream_t stream) {
+                              int out_f32, int tokens, int N, int K, int splits, int* status, cudaStream_t stream) {
   if (tokens < 0 || N <= 0 || K <= 0) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: bad sizes tokens=%d N=%d K=%d", tokens, N, K);
   if (tokens == 0) return 0;
   if ((K % 8) || (ldx % 8) || (ldw % 8) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
@@ -378,25 +392,27 @@ DINFER_API int dinfer_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t
                   "(TMA); K=%d ldx=%lld ldw=%lld", K, (long long)ldx, (long long)ldw);
   if (!status) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: a status word is required");
   GemmParams p;
-  p.out = out; p.ldc = ldc; p.tokens = tokens; p.N = N; p.K = K; p.partial = partial; p.counters = counters; p.status = status;
+  p.out = out; p.ldc = ldc; p.tokens = tokens; p.N = N; p.K = K; p.status = status;
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
   CUtensorMap ma, mb;
   int rc;
   if (tokens <= 64) {
     const int n_tile = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64);
     if (splits < 1) splits = 1;
+    if (splits > MAX_SPLITS) splits = MAX_SPLITS;
     if (splits > total_kb) splits = total_kb;
-    if (splits > 1 && (!partial || !counters)) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: splits=%d needs scratch", splits);
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
     p.splits = (total_kb + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
     if ((rc = make_map(&ma, w, N, K, ldw, TILE_M))) return rc;
     if ((rc = make_map(&mb, x, tokens, K, ldx, n_tile))) return rc;
     dim3 grid((N + TILE_M - 1) / TILE_M, (tokens + n_tile - 1) / n_tile, p.splits);
-#define GO(NT_) (out_f32 ? launch<NT_, 4, true, float>(ma, mb, p, grid, stream) \
-                         : launch<NT_, 4, true, __nv_bfloat16>(ma, mb, p, grid, stream))
-    if (n_tile == 16) return GO(16);
-    if (n_tile == 32) return GO(32);
-    return GO(64);
+#define GO(NT_, ST_) (out_f32 ? launch<NT_, ST_, true, float>(ma, mb, p, grid, stream) \
+                              : launch<NT_, ST_, true, __nv_bfloat16>(ma, mb, p, grid, stream))
+    // Four stages leave room for two CTAs of a split launch on an SM; a launch with more CTAs than that
+    // takes three stages, of which three CTAs fit (as many bytes in flight, one wave instead of two).
+    if (n_tile == 16) return (p.splits > 1 && (int64_t)grid.x * grid.y * grid.z > 264) ? GO(16, 3) : GO(16, 4);
+    if (n_tile == 32) return GO(32, 4);
+    return GO(64, 4);
 #undef GO
   }
   p.k_blocks_per_split = total_kb;

@@ -11,20 +11,16 @@ from .ops import _fn
 
 NUM_SMS = 148
 DECODE_MAX_TOKENS = 64          # up to here the operands are swapped (weight rows fill the tile)
+MAX_SPLITS = 8                  # the portable cluster size
 
-# Per device: scratch of the split-K decode orientation (f32 partial tiles + counters the kernel leaves
-# at zero) and the status word the kernels set when a bounded wait runs out.  Buffers only grow and old
-# ones stay alive (captured CUDA graphs hold their addresses).  Launches sharing them run on one stream.
+# Per device: the status word the tcgen05 kernels set when a bounded wait runs out.
 _STATE = {}
-_KEEP = []
 
 
 def _state(device):
     st = _STATE.get(device)
     if st is None:
-        st = {"partial": torch.empty(1 << 22, dtype=torch.float32, device=device),
-              "counters": torch.zeros(1 << 14, dtype=torch.int32, device=device),
-              "status": torch.zeros(1, dtype=torch.int32, device=device)}
+        st = {"status": torch.zeros(1, dtype=torch.int32, device=device)}
         _STATE[device] = st
     return st
 
@@ -54,11 +50,13 @@ def supported(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def decode_splits(tokens: int, N: int, K: int) -> int:
-    """K splits of the decode orientation: about two CTAs per SM in one wave, at least eight 64-wide
-    K blocks per CTA, at most 16 splits."""
+    """K splits of the decode orientation: one wave of CTAs (three fit an SM up to 16 tokens, two
+    beyond), at least eight 64-wide K blocks per CTA, at most ``MAX_SPLITS`` (the CTAs of a tile are
+    one thread-block cluster)."""
     tiles = (N + 127) // 128
     k_blocks = (K + 63) // 64
-    return max(1, min((2 * NUM_SMS) // tiles, k_blocks // 8, 16))
+    slots = 3 * NUM_SMS if tokens <= 16 else 2 * NUM_SMS - 16
+    return max(1, min(slots // tiles, k_blocks // 8, MAX_SPLITS))
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None) -> torch.Tensor:
@@ -71,24 +69,13 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optiona
     if w.shape[1] != K or out.shape != (tokens, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
     st = _state(x.device)
-    partial = counters = None
     if tokens <= DECODE_MAX_TOKENS:
-        if splits is None:
-            splits = decode_splits(tokens, N, K)
-        if splits > 1:
-            n_tile = 16 if tokens <= 16 else (32 if tokens <= 32 else 64)
-            tiles = ((N + 127) // 128) * ((tokens + n_tile - 1) // n_tile)
-            need = tiles * splits * n_tile * 128
-            if st["partial"].numel() < need or st["counters"].numel() < tiles:
-                _KEEP.append((st["partial"], st["counters"]))
-                st["partial"] = torch.empty(max(need, 2 * st["partial"].numel()), dtype=torch.float32, device=x.device)
-                st["counters"] = torch.zeros(max(tiles, 2 * st["counters"].numel()), dtype=torch.int32, device=x.device)
-            partial, counters = st["partial"], st["counters"]
+        splits = decode_splits(tokens, N, K) if splits is None else max(1, min(int(splits), MAX_SPLITS))
     else:
         splits = 1
     lib, f = _fn("gemm_tc", "dinfer_gemm_tc",
                  [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
-                  c_void_p, c_void_p, c_void_p, c_void_p])
+                  c_void_p, c_void_p])
     check(lib, f(ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(out), out.stride(0), int(out.dtype == torch.float32),
-                 tokens, N, K, int(splits), ptr(partial), ptr(counters), ptr(st["status"]), stream_handle()), "gemm_tc")
+                 tokens, N, K, int(splits), ptr(st["status"]), stream_handle()), "gemm_tc")
     return out
