@@ -365,6 +365,9 @@ __global__ void __launch_bounds__(NT, 2) attention_decode_kernel(const Params p)
 // the compute warps issue no address arithmetic or copies at all and meet at no CTA-wide barrier per
 // tile.  Shared-memory tiles have TMA's 128-byte swizzle: [half][key][128 bytes].  Pages of at least
 // 8 tokens (a swizzle atom is 8 rows).  Every mbarrier wait is bounded (status word).
+// With key splits the CTAs of a (request, kv head) are one thread-block cluster: each owns a share of
+// the (head, dim) outputs, the others store their unnormalised sums of that share (and their maxima
+// and sums) into its shared memory, and after one cluster barrier every CTA folds and writes its share.
 constexpr int NT_TMA = 160;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
@@ -398,6 +401,30 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+// ---- thread-block cluster: the CTAs of one (request, kv head) that split its keys
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+constexpr int MAX_CLUSTER_SPLITS = 16;
+// floats of the receive buffer of a CTA: its share of the (head, dim) sums from every split, then
+// every split's (maximum, sum) of every head
+__host__ __device__ constexpr int fold_share(int group, int D, int splits) { return (group * D + splits - 1) / splits; }
+__host__ __device__ constexpr int fold_recv_floats(int group, int D, int splits) {
+  return splits * fold_share(group, D, splits) + splits * group * 2;
+}
 // byte offset of (key row, 16-byte chunk c of the head) inside a [half][64 keys][128 B] tile with 128-byte swizzle
 __device__ __forceinline__ uint32_t sw128(int row, int c) {
   return (uint32_t)((c >> 3) * (BN * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4));
@@ -412,14 +439,16 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Pa
   extern __shared__ __align__(128) unsigned char smem_raw[];   // aligned to 1024 by hand below
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES];
   __shared__ int s_table[TABLE_SLOTS];
-  __shared__ int s_last, s_abort;
+  __shared__ int s_abort;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int b = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
   pdl_launch_dependents();
   // before pdl_wait(): only the batch's index arrays and cache pages of older tokens (see the other kernel)
   const int t0 = p.cu_seqlens[b];
-  if (p.cu_seqlens[b + 1] - t0 != 1) return;
+  if (p.cu_seqlens[b + 1] - t0 != 1) return;                  // the whole cluster leaves: same request
+  // first phase of the cluster barrier: this CTA runs, its shared memory may be written by the others
+  if (p.splits > 1) cluster_arrive_relaxed();
   const int seq_len = p.seq_lens[b];
   const int pos = seq_len - 1;
   const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0, hi = seq_len;
@@ -627,72 +656,66 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Pa
     }
   }
   __syncthreads();
-  if (s_abort) return;
-  for (int idx = threadIdx.x; idx < p.group * D; idx += NT_TMA) {
-    const int head = idx / D, d = idx % D;
-    float M = -INFINITY;
+  const bool clustered = p.splits > 1;
+  const int share = fold_share(p.group, D, p.splits);        // (head, dim) outputs per CTA of the cluster
+  const uint32_t recv_base = base + 2 * STAGES * KV_BYTES;   // beyond the tiles: others write it while tiles still land
+  if (clustered) cluster_wait_acquire();                     // every CTA of the cluster runs
+  if (!s_abort) {
+    for (int idx = threadIdx.x; idx < p.group * D; idx += NT_TMA) {
+      const int head = idx / D, d = idx % D;
+      float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * NHEADS + head]);
-    float L = 0.f, acc = 0.f;
+      for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * NHEADS + head]);
+      float L = 0.f, acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float mw = sm_m[w * NHEADS + head];
-      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
-      L += sm_l[w * NHEADS + head] * f;
-      acc += sm_o[(w * NHEADS + head) * D + d] * f;
-    }
-    const int gh = hk * p.group + head;
-    if (p.splits == 1) {
-      p.out[(int64_t)t0 * p.ldo + (int64_t)gh * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-    } else {
-      const int64_t slot = ((int64_t)b * p.H + gh) * p.splits + split;
-      p.part_o[slot * D + d] = acc;
-      if (d == 0) { p.part_ml[slot * 2] = M; p.part_ml[slot * 2 + 1] = L; }
+      for (int w = 0; w < 4; ++w) {
+        const float mw = sm_m[w * NHEADS + head];
+        const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+        L += sm_l[w * NHEADS + head] * f;
+        acc += sm_o[(w * NHEADS + head) * D + d] * f;
+      }
+      if (!clustered) {
+        p.out[(int64_t)t0 * p.ldo + (int64_t)(hk * p.group + head) * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+      } else {
+        const int owner = idx / share;
+        st_cluster_f32(map_to_cta(recv_base, owner) + (uint32_t)((split * share + idx - owner * share) * 4), acc);
+        if (d == 0) {                                         // this head's maximum and sum, to every CTA
+          const uint32_t off = recv_base + (uint32_t)((p.splits * share + (split * p.group + head) * 2) * 4);
+          for (int o = 0; o < p.splits; ++o) {
+            const uint32_t dst = map_to_cta(off, o);
+            st_cluster_f32(dst, M);
+            st_cluster_f32(dst + 4, L);
+          }
+        }
+      }
     }
   }
-  if (p.splits == 1) return;
+  if (!clustered) return;
 
-  // ---- fold the splits: the CTA that arrives last does it
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) s_last = atomicAdd(&p.counters[b * p.Hkv + hk], 1) == p.splits - 1;
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  float* sm_f = reinterpret_cast<float*>(gbase);
-  float* sm_inv = sm_f + NHEADS * 32;
-  float* sm_l2 = sm_inv + NHEADS;
-  for (int i = threadIdx.x; i < p.group * p.splits; i += NT_TMA) {
-    const int head = i / p.splits, sp = i % p.splits;
-    const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml) + ((int64_t)b * p.H + hk * p.group + head) * p.splits + sp);
-    sm_f[head * 32 + sp] = ml.x;                              // the split's maximum
-    sm_l2[head * 32 + sp] = ml.y;                             // and its sum
-  }
-  __syncthreads();
-  if (threadIdx.x < p.group) {
-    const int head = threadIdx.x;
-    float M = -INFINITY;
-    for (int sp = 0; sp < p.splits; ++sp) M = fmaxf(M, sm_f[head * 32 + sp]);
-    float L = 0.f;
-    for (int sp = 0; sp < p.splits; ++sp) {
-      const float ms = sm_f[head * 32 + sp];
-      const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-      L += sm_l2[head * 32 + sp] * f;
-      sm_f[head * 32 + sp] = f;
+  // ---- second phase: all partial sums of this CTA's share have arrived
+  cluster_arrive_release();
+  cluster_wait_acquire();
+  if (s_abort) return;
+  {
+    const float* recv = reinterpret_cast<const float*>(gbase + 2 * STAGES * KV_BYTES);
+    const float* recv_ml = recv + p.splits * share;
+    const int rank = (int)cluster_ctarank();                  // = split: the cluster spans the grid's x
+    const int mine = min(share, p.group * D - rank * share);
+    for (int i = threadIdx.x; i < mine; i += NT_TMA) {
+      const int idx = rank * share + i;
+      const int head = idx / D, d = idx % D;
+      float M = -INFINITY;
+      for (int sp = 0; sp < p.splits; ++sp) M = fmaxf(M, recv_ml[(sp * p.group + head) * 2]);
+      float L = 0.f, acc = 0.f;
+      for (int sp = 0; sp < p.splits; ++sp) {
+        const float ms = recv_ml[(sp * p.group + head) * 2];
+        const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+        L += recv_ml[(sp * p.group + head) * 2 + 1] * f;
+        acc += recv[sp * share + i] * f;
+      }
+      p.out[(int64_t)t0 * p.ldo + (int64_t)(hk * p.group + head) * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     }
-    sm_inv[head] = L > 0.f ? 1.f / L : 0.f;
   }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < p.group * D; idx += NT_TMA) {
-    const int head = idx / D, d = idx % D;
-    const int gh = hk * p.group + head;
-    const float* po = p.part_o + ((int64_t)b * p.H + gh) * p.splits * D + d;
-    float acc = 0.f;
-#pragma unroll 8
-    for (int sp = 0; sp < p.splits; ++sp) acc += __ldcg(po + sp * D) * sm_f[head * 32 + sp];
-    p.out[(int64_t)t0 * p.ldo + (int64_t)gh * D + d] = __float2bfloat16_rn(acc * sm_inv[head]);
-  }
-  if (threadIdx.x == 0) p.counters[b * p.Hkv + hk] = 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -712,16 +735,22 @@ EncodeTiledFn encode_fn() {
 template <int D, int NH8>
 int launch_tma(const CUtensorMap& map, const Params& p, int B, cudaStream_t stream) {
   auto k = attention_decode_tma_kernel<D, NH8>;
-  size_t sm = (size_t)2 * STAGES * (D / 64) * BN * 128 + 1024;
-  const size_t fold = (size_t)(4 * NH8 * 8 * D + 2 * 4 * NH8 * 8) * sizeof(float) + 1024;
-  if (fold > sm) sm = fold;
+  // tiles (the four warps' fold reuses them: it is smaller), then the cluster's receive buffer
+  static_assert((size_t)(4 * NH8 * 8 * D + 2 * 4 * NH8 * 8) * sizeof(float) <= (size_t)2 * STAGES * (D / 64) * BN * 128,
+                "the fold of the four warps fits the tiles");
+  const size_t tiles = (size_t)2 * STAGES * (D / 64) * BN * 128 + 1024;
+  const size_t sm = tiles + (p.splits > 1 ? (size_t)fold_recv_floats(p.group, D, p.splits) * sizeof(float) : 0);
   static bool opted = false;
   if (!opted) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    const size_t most = tiles + (size_t)fold_recv_floats(NH8 * 8, D, MAX_CLUSTER_SPLITS) * sizeof(float);
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
     if (e != cudaSuccess) return refuse((int)e, "attention_decode: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);     // clusters of up to 16
+    if (e != cudaSuccess) return refuse((int)e, "attention_decode: cluster size opt-in failed: %s", cudaGetErrorString(e));
     opted = true;
   }
-  launch_pdl(k, dim3(p.splits, p.Hkv, B), dim3(NT_TMA), sm, stream, map, p);
+  cudaError_t e = launch_pdl_cluster(k, dim3(p.splits, p.Hkv, B), dim3(NT_TMA), dim3(p.splits, 1, 1), sm, stream, map, p);
+  if (e != cudaSuccess) return refuse((int)e, "attention_decode: launch failed: %s", cudaGetErrorString(e));
   return cuda_status("attention_decode");
 }
 
@@ -787,13 +816,14 @@ DINFER_API int dinfer_attention_decode(const void* q, int64_t ldq, void* out, in
   return nh8 == 1 ? launch<128, 1>(p, B, stream) : launch<128, 2>(p, B, stream);
 }
 
-// The TMA variant (pages of at least 8 tokens): same arguments plus the number of pages of the cache
-// tensor (for the tensor map) and the device status word that a bounded wait sets when it runs out.
+// The TMA variant (pages of at least 8 tokens): no scratch (the splits fold inside a cluster, at most
+// 16 of them), plus the number of pages of the cache tensor (for the tensor map) and the device status
+// word that a bounded wait sets when it runs out.
 DINFER_API int dinfer_attention_decode_tma(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
                                            int64_t num_blocks, const int* block_table, int max_blocks,
                                            const int* cu_seqlens, const int* seq_lens, int B, int H, int Hkv, int D,
-                                           int block_size, float scale, int window, int splits, float* scratch_floats,
-                                           int* scratch_counters, int* status, cudaStream_t stream) {
+                                           int block_size, float scale, int window, int splits, int* status,
+                                           cudaStream_t stream) {
   if (B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || max_blocks <= 0 || num_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: bad sizes B=%d H=%d Hkv=%d", B, H, Hkv);
   if (!dinfer_attention_decode_supports(D, H / Hkv, block_size) || block_size < 8)
@@ -801,9 +831,9 @@ DINFER_API int dinfer_attention_decode_tma(const void* q, int64_t ldq, void* out
                   "(head_dim 64 or 128, group <= 16, power-of-two pages of at least 8)", D, H / Hkv, block_size);
   if ((ldq % 2) || (ldo % 2) || (reinterpret_cast<uintptr_t>(q) & 3) || (reinterpret_cast<uintptr_t>(cache) & 15))
     return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: q rows must be 4-byte and the cache 16-byte aligned");
-  if (splits > 32) return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: at most 32 key splits, got %d", splits);
-  if (splits < 1 || (splits > 1 && (!scratch_floats || !scratch_counters)) || !status)
-    return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: splits=%d needs scratch, and a status word is required", splits);
+  if (splits < 1 || splits > MAX_CLUSTER_SPLITS)
+    return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: 1 to %d key splits (one cluster), got %d", MAX_CLUSTER_SPLITS, splits);
+  if (!status) return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: a status word is required");
   if (Hkv > 65535 || B > 65535) return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: too many heads or requests for the grid");
   const int64_t cache_rows = num_blocks * 2 * Hkv * block_size;
   if (cache_rows > 0x7fffffffLL) return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: the cache has too many rows for a tensor map coordinate");
@@ -828,9 +858,7 @@ DINFER_API int dinfer_attention_decode_tma(const void* q, int64_t ldq, void* out
   p.block_size = block_size; p.bs_log2 = 0;
   while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
   p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.splits = splits;
-  p.part_o = scratch_floats;
-  p.part_ml = scratch_floats ? scratch_floats + (int64_t)B * H * splits * D : nullptr;
-  p.counters = scratch_counters; p.status = status;
+  p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr; p.status = status;
   const int nh8 = (p.group + 7) / 8;
   if (D == 64) return nh8 == 1 ? launch_tma<64, 1>(map, p, B, stream) : launch_tma<64, 2>(map, p, B, stream);
   return nh8 == 1 ? launch_tma<128, 1>(map, p, B, stream) : launch_tma<128, 2>(map, p, B, stream);

@@ -10,6 +10,7 @@ from .lib import KernelError, check, library, ptr, require_cuda, stream_handle
 from .ops import _fn
 
 NUM_SMS = 148
+MAX_CLUSTER_SPLITS = 16         # key splits of the TMA decode kernel: one thread-block cluster
 
 
 def tc_supported(dtype: torch.dtype, head_dim: int, group: int) -> bool:
@@ -19,13 +20,13 @@ def tc_supported(dtype: torch.dtype, head_dim: int, group: int) -> bool:
 def decode_splits(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
     """Key splits of the decode shape.  Two CTAs fit an SM: with few (request, kv head) pairs the
     splits fill those slots in one wave; with as many pairs as slots or more, splitting only adds
-    partial sums to write and fold, so there is none.  Never more than a quarter of the 64-key
-    tiles, at most 32."""
+    partial sums to fold, so there is none.  Never more than a quarter of the 64-key tiles, at
+    most 16 (the largest cluster)."""
     slots = 2 * NUM_SMS
     base = max(1, num_reqs * num_kv_heads)
     want = slots // base if base <= slots else 1
     tiles = max(1, (max_seq_len + 63) // 64)
-    return max(1, min(want, max(1, tiles // 4), 32))
+    return max(1, min(want, max(1, tiles // 4), MAX_CLUSTER_SPLITS))
 
 
 def decode_supported(dtype: torch.dtype, head_dim: int, group: int, block_size: int) -> bool:
@@ -69,21 +70,22 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
             raise KernelError(f"attention_decode: {n} must be contiguous int32")
     if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
         raise KernelError(f"attention_decode: cache shape {tuple(cache.shape)} is not [blocks, 2, Hkv, block, D]")
-    floats = counters = None
-    if splits > 1:
-        floats, counters = _decode_scratch(q.device, B * num_heads * splits * (head_dim + 2), B * num_kv_heads)
     if cache.shape[3] >= 8:
-        # pages of at least 8 tokens: tiles by TMA through a tensor map over the cache, mbarrier ring
+        # pages of at least 8 tokens: tiles by TMA through a tensor map over the cache, mbarrier ring;
+        # the splits of a (request, kv head) are one thread-block cluster and fold through shared memory
         from . import gemm_ops
         status = gemm_ops._state(q.device)["status"]
         lib, f = _fn("attention_decode", "dinfer_attention_decode_tma",
                      [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
-                      c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+                      c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
         check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), cache.shape[0], ptr(block_table),
                      block_table.shape[1], ptr(cu_seqlens), ptr(seq_lens), B, num_heads, num_kv_heads, head_dim,
-                     cache.shape[3], float(scale), int(window), int(splits), ptr(floats), ptr(counters), ptr(status),
+                     cache.shape[3], float(scale), int(window), min(int(splits), MAX_CLUSTER_SPLITS), ptr(status),
                      stream_handle()), "attention_decode_tma")
         return out
+    floats = counters = None
+    if splits > 1:
+        floats, counters = _decode_scratch(q.device, B * num_heads * splits * (head_dim + 2), B * num_kv_heads)
     lib, f = _fn("attention_decode", "dinfer_attention_decode",
                  [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                   c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p])

@@ -53,10 +53,11 @@ def test_decode_splits(splits):
 @pytest.mark.parametrize("H,Hkv,D,bs", [(8, 2, 128, 16), (32, 8, 128, 16), (3, 3, 128, 4), (8, 1, 64, 32),
                                         (16, 1, 128, 16), (12, 1, 64, 1), (10, 2, 64, 8)])
 @pytest.mark.parametrize("window", [None, 100])
-@pytest.mark.parametrize("splits", [1, 4, 7])
+@pytest.mark.parametrize("splits", [1, 4, 7, 16])
 def test_decode_kernel(H, Hkv, D, bs, window, splits):
     """The decode kernel (keys on the tile's rows, splits folded in the kernel) against the plain
-    formula; a prompt portion in the batch must be left alone; two launches in a row share the scratch."""
+    formula; a prompt portion in the batch must be left alone; two launches in a row (the splits fold
+    through a cluster's shared memory, or through a scratch that every launch leaves clean)."""
     from dinfer_b200.kernels import attention_ops as A
     from test_kernels_gpu import paged_case, plain_paged
     reqs = [(1000, 1), (63, 1), (0, 1), (129, 1), (40, 6), (2047, 1), (64, 1), (15, 1)]
