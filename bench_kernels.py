@@ -1,0 +1,198 @@
+#!/usr/bin/env python3
+"""Kernel-level timings of the hot ops at the layer sizes of a model shape (default: Qwen3-8B).
+
+Every op is captured back to back in one CUDA graph over operands that rotate through more memory
+than the L2 holds, so that each launch reads its weights or its cache from HBM and programmatic
+dependent launch overlaps neighbours as it does inside a decode step; the time per launch is the
+graph's CUDA-event time divided by its launches.  Beside each time stands the time the op's bytes
+(decode) or flops (prompts) take at the measured peaks.
+
+    python bench_kernels.py                     # all sections
+    python bench_kernels.py --only gemm_decode --tokens 1 8 32
+
+Sections: gemm_decode (tcgen05 swapped-operand product per split count), gemm_prompt (tcgen05 product
+and the library's), attention_decode (per split count), attention_prompt.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPE = dict(hidden=4096, heads=32, kv_heads=8, head_dim=128, intermediate=12288, block_size=16)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def graph_time_us(fn, launches: int, replays: int = 5) -> float:
+    """fn(i) launches op number i; ``launches`` of them are captured in one graph."""
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for i in range(3):
+            fn(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(launches):
+            fn(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (replays * launches) * 1e3
+
+
+def layer_products(s):
+    h, H, Hkv, D, I = s["hidden"], s["heads"], s["kv_heads"], s["head_dim"], s["intermediate"]
+    return [("qkv", (H + 2 * Hkv) * D, h), ("o", h, H * D), ("gate_up", 2 * I, h), ("down", h, I)]
+
+
+def rotating_weights(N, K):
+    copies = max(2, int(400e6 // (N * K * 2)) + 1)             # > 3 x L2 in rotation
+    return [(torch.randn(N, K, device="cuda") / math.sqrt(K)).to(torch.bfloat16) for _ in range(copies)]
+
+
+def gemm_decode(s, tokens_list, hbm):
+    from dinfer_b200.kernels import gemm_ops as G
+    print("# gemm_decode: us per launch by K splits; 'auto' is the split count the engine picks")
+    for tokens in tokens_list:
+        for name, N, K in layer_products(s):
+            ws = rotating_weights(N, K)
+            x = torch.randn(tokens, K, device="cuda").to(torch.bfloat16)
+            out = torch.empty(tokens, N, dtype=torch.bfloat16, device="cuda")
+            cells = []
+            for splits in (1, 2, 4, 8):
+                t = graph_time_us(lambda i: G.gemm_tc(x, ws[i % len(ws)], out, splits=splits), 2 * len(ws))
+                cells.append(f"s{splits} {t:6.1f}")
+            auto = G.decode_splits(tokens, N, K)
+            t_auto = graph_time_us(lambda i: G.gemm_tc(x, ws[i % len(ws)], out), 2 * len(ws))
+            ideal = N * K * 2 / hbm * 1e-3
+            print(f"tokens {tokens:3d} {name:8s} N {N:6d} K {K:6d} | {' '.join(cells)} | auto s{auto} {t_auto:6.1f} us"
+                  f" | weights at peak {ideal:5.1f} us -> {ideal / t_auto:.2f}", flush=True)
+            del ws
+    G.check_status()
+
+
+def gemm_prompt(s, tokens, tflops):
+    from dinfer_b200.kernels import gemm_ops as G
+    print("# gemm_prompt: us per launch, this package's tcgen05 product and the library's")
+    for name, N, K in layer_products(s):
+        ws = rotating_weights(N, K)
+        x = torch.randn(tokens, K, device="cuda").to(torch.bfloat16)
+        out = torch.empty(tokens, N, dtype=torch.bfloat16, device="cuda")
+        t_own = graph_time_us(lambda i: G.gemm_tc(x, ws[i % len(ws)], out), 2 * len(ws))
+        t_lib = graph_time_us(lambda i: torch.mm(x, ws[i % len(ws)].t(), out=out), 2 * len(ws))
+        flops = 2.0 * tokens * N * K
+        print(f"tokens {tokens} {name:8s} N {N:6d} K {K:6d} | tcgen05 {t_own:7.1f} us {flops / t_own * 1e-6:7.1f} TFLOP/s"
+              f" | library {t_lib:7.1f} us {flops / t_lib * 1e-6:7.1f} TFLOP/s | at peak {flops / tflops * 1e-6:6.1f} us", flush=True)
+        del ws
+    G.check_status()
+
+
+def paged_cache(B, ctx, Hkv, D, bs, copies):
+    per = (ctx + bs - 1) // bs
+    caches = [torch.randn(B * per + 1, 2, Hkv, bs, D, device="cuda").to(torch.bfloat16) for _ in range(copies)]
+    table = torch.randperm(B * per, device="cuda").to(torch.int32).reshape(B, per)       # scattered pages
+    return caches, table
+
+
+def attention_decode(s, batches, contexts, hbm):
+    from dinfer_b200.kernels import attention_ops as A
+    from dinfer_b200.kernels import gemm_ops as G
+    H, Hkv, D, bs = s["heads"], s["kv_heads"], s["head_dim"], s["block_size"]
+    print("# attention_decode: us per launch by key splits; 'auto' is the split count the engine picks")
+    for B in batches:
+        for ctx in contexts:
+            bytes_ = B * ctx * Hkv * D * 4
+            copies = min(24, max(2, int(400e6 // bytes_) + 1))
+            caches, table = paged_cache(B, ctx, Hkv, D, bs, copies)
+            cu = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+            seq = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+            q = torch.randn(B, H * D, device="cuda").to(torch.bfloat16)
+            out = torch.empty(B, H * D, dtype=torch.bfloat16, device="cuda")
+            cells = []
+            for splits in (1, 2, 4, 8, 16):
+                if splits > max(1, ctx // 64):
+                    continue
+                t = graph_time_us(lambda i: A.attention_decode(q, out, caches[i % copies], table, cu, seq, H, Hkv, D,
+                                                               D ** -0.5, 0, splits), 2 * copies)
+                cells.append(f"s{splits} {t:6.1f}")
+            auto = A.decode_splits(B, Hkv, ctx)
+            t_auto = graph_time_us(lambda i: A.attention_decode(q, out, caches[i % copies], table, cu, seq, H, Hkv, D,
+                                                                D ** -0.5, 0, auto), 2 * copies)
+            ideal = bytes_ / hbm * 1e-3
+            print(f"batch {B:3d} context {ctx:5d} | {' '.join(cells)} | auto s{auto} {t_auto:6.1f} us"
+                  f" | cache at peak {ideal:6.1f} us -> {ideal / t_auto:.2f}", flush=True)
+            del caches
+    G.check_status()
+
+
+def attention_prompt(s, tokens_list, tflops):
+    from dinfer_b200.kernels import attention_ops as A
+    from dinfer_b200.kernels import gemm_ops as G
+    H, Hkv, D, bs = s["heads"], s["kv_heads"], s["head_dim"], s["block_size"]
+    print("# attention_prompt: one request, whole prompt in one step (causal), us per launch")
+    for T in tokens_list:
+        caches, table = paged_cache(1, T, Hkv, D, bs, 4)
+        cu = torch.tensor([0, T], dtype=torch.int32, device="cuda")
+        seq = torch.tensor([T], dtype=torch.int32, device="cuda")
+        qkv = torch.randn(T, (H + 2 * Hkv) * D, device="cuda").to(torch.bfloat16)
+        q = qkv[:, :H * D]
+        out = torch.empty(T, H * D, dtype=torch.bfloat16, device="cuda")
+        flops = 4.0 * (T * (T + 1) / 2) * D * H
+        t_umma = graph_time_us(lambda i: A.attention_umma(q, out, caches[i % 4], table, cu, seq, H, Hkv, D, D ** -0.5,
+                                                          0, T), 8)
+        t_tc = graph_time_us(lambda i: A.attention_tc(q, out, caches[i % 4], table, cu, seq, H, Hkv, D, D ** -0.5,
+                                                      0, T, False, True, 1), 8)
+        print(f"tokens {T:5d} | tcgen05 {t_umma:7.1f} us {flops / t_umma * 1e-6:6.1f} TFLOP/s"
+              f" | mma.sync {t_tc:7.1f} us {flops / t_tc * 1e-6:6.1f} TFLOP/s | at peak {flops / tflops * 1e-6:6.1f} us", flush=True)
+        del caches
+    G.check_status()
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--only", choices=["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt"])
+    ap.add_argument("--tokens", type=int, nargs="*", default=[1, 8, 32], help="rows of the decode products")
+    ap.add_argument("--batches", type=int, nargs="*", default=[1, 8, 64], help="requests of the decode attention")
+    ap.add_argument("--contexts", type=int, nargs="*", default=[1024, 4096, 16384])
+    ap.add_argument("--prompt-tokens", type=int, nargs="*", default=[2048, 8192])
+    a = ap.parse_args()
+    if not torch.cuda.is_available():
+        print("bench_kernels.py needs a GPU", file=sys.stderr)
+        return 2
+    hbm, tflops, source = peaks()
+    print(f"# peaks ({source}): {hbm:.1f} GB/s, {tflops:.1f} TFLOP/s bf16; {torch.cuda.get_device_name(0)}")
+    torch.manual_seed(0)
+    todo = [a.only] if a.only else ["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt"]
+    if "gemm_decode" in todo:
+        gemm_decode(SHAPE, a.tokens, hbm)
+    if "gemm_prompt" in todo:
+        gemm_prompt(SHAPE, a.prompt_tokens[0], tflops)
+    if "attention_decode" in todo:
+        attention_decode(SHAPE, a.batches, a.contexts, hbm)
+    if "attention_prompt" in todo:
+        attention_prompt(SHAPE, a.prompt_tokens, tflops)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

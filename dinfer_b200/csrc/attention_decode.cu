@@ -749,6 +749,24 @@ int launch_tma(const CUtensorMap& map, const Params& p, int B, cudaStream_t stre
     if (e != cudaSuccess) return refuse((int)e, "attention_decode: cluster size opt-in failed: %s", cudaGetErrorString(e));
     opted = true;
   }
+  if (p.splits > 8) {
+    // beyond the portable cluster size: ask once per size whether such a cluster fits this GPU
+    static int fits[MAX_CLUSTER_SPLITS + 1] = {0};            // 0 = not asked, 1 = yes, -1 = no
+    if (!fits[p.splits]) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(p.splits, p.Hkv, B); cfg.blockDim = dim3(NT_TMA); cfg.dynamicSmemBytes = sm;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = p.splits; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      cfg.attrs = at; cfg.numAttrs = 1;
+      int n = 0;
+      const cudaError_t q = cudaOccupancyMaxActiveClusters(&n, k, &cfg);
+      if (q != cudaSuccess) (void)cudaGetLastError();
+      fits[p.splits] = (q == cudaSuccess && n > 0) ? 1 : -1;
+    }
+    if (fits[p.splits] < 0)
+      return refuse(DINFER_BAD_ARGUMENT, "attention_decode: a cluster of %d CTAs does not fit this GPU; use at most 8 key splits", p.splits);
+  }
   cudaError_t e = launch_pdl_cluster(k, dim3(p.splits, p.Hkv, B), dim3(NT_TMA), dim3(p.splits, 1, 1), sm, stream, map, p);
   if (e != cudaSuccess) return refuse((int)e, "attention_decode: launch failed: %s", cudaGetErrorString(e));
   return cuda_status("attention_decode");

@@ -412,7 +412,7 @@ DINFER_API int dinfer_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t
     // takes three stages, of which three CTAs fit (as many bytes in flight, one wave instead of two).
     if (n_tile == 16) return (p.splits > 1 && (int64_t)grid.x * grid.y * grid.z > 264) ? GO(16, 3) : GO(16, 4);
     if (n_tile == 32) return GO(32, 4);
-    return GO(64, 4);
+    return p.splits > 1 ? GO(64, 3) : GO(64, 4);              // with the receive buffer, two CTAs fit with three stages
 #undef GO
   }
   p.k_blocks_per_split = total_kb;
