@@ -8,11 +8,15 @@
 //     O[128, D]  += P V            tcgen05.mma accumulating in tensor memory, V used as it lies in the cache
 //                                  ([key][d] = MN-major B operand); O is rescaled in place only when a row's
 //                                  maximum grows by more than 2^8
-// Warp roles (320 threads): warp 0 = TMA producer (Q once through a 3-D map over [token][head][d]; K/V page
+// Warp roles (352 threads): warp 0 = TMA producer (Q once through a 3-D map over [token][head][d]; K/V page
 // by page through a 2-D map over the layer's cache, looked up in the block table), warp 1 = TMEM
-// allocation + MMA issue, warps 2..5 and 6..9 = the softmax / output groups of the two row tiles.  K/V tiles
-// ride a 3-stage mbarrier ring; the MMA thread serves the two groups alternately, so one group's softmax
-// overlaps the other's products.  No cluster launch, no multicast.  Every mbarrier wait is bounded.
+// allocation + MMA issue for row tile A, warp 10 = MMA issue for row tile B (a tile's chain of products
+// hangs on one issuing thread; two threads keep the tiles from waiting for each other), warps 2..5 and
+// 6..9 = the softmax / output groups of the two row tiles.  K tiles
+// and V tiles ride a 3-stage mbarrier ring each (K runs two tiles ahead of V).  S is double-buffered in
+// tensor memory: the MMA thread issues Q K^T of tile j+2 right behind P V of tile j, so a group's softmax
+// of tile j+1 finds its S ready when it has handed P of tile j over, and the tensor core works for one
+// group while the other computes.  No cluster launch, no multicast.  Every mbarrier wait is bounded.
 //
 // Counterpart in the reference: gqa_fa_v5_kernel (crates/kernels/cuda/gqa.cu:167-369, mma.sync) for this
 // head size; its tcgen05 attention (crates/kernels/cuda/gqa_fa_sm100.cu) exists for D = 256 only and stages
@@ -25,7 +29,8 @@ using namespace dinfer;
 
 namespace {
 
-constexpr int BM = 128, BN = 64, STAGES = 3, NTHREADS = 320;   // BM rows per softmax group, two groups per CTA
+constexpr int BM = 128, BN = 64, STAGES = 3, NTHREADS = 352;   // BM rows per softmax group, two groups per CTA
+constexpr int MMA_WARP_B = 10;                                  // the second MMA issuer (the first is warp 1)
 constexpr int TABLE_SLOTS = 2048;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
@@ -149,20 +154,23 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   constexpr int NH = D / 64;                          // 64-wide halves of the head
   constexpr uint32_t Q_HALF = BM * 128, KV_HALF = BN * 128;
   constexpr uint32_t Q_BYTES = NH * Q_HALF, KV_BYTES = NH * KV_HALF, P_BYTES = BM * BN * 2;
-  constexpr int TMEM_COLS = 512, S_COL = 0, O_COL = 128;       // S_A 0, S_B 64, O_A 128, O_B 256
+  constexpr int TMEM_COLS = 512, O_COL = 256;                  // S of (tile w, buffer b) at (2w + b) * 64; O_A 256, O_B 384
   extern __shared__ unsigned char smem_dyn[];
-  __shared__ __align__(8) uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2], p_full[2], o_full[2];
+  __shared__ __align__(8) uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES],
+      s_full[2][2], p_full[2], pv_done[2], o_full[2];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_table[TABLE_SLOTS];
   __shared__ int s_abort;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, hk = blockIdx.y;
+  const int b = blockIdx.z, hk = blockIdx.x;
   pdl_enter();
   const int t0 = p.cu_seqlens[b];
   const int q_len = p.cu_seqlens[b + 1] - t0;
   if (q_len <= 1) return;                              // decoded tokens belong to the decode kernel
   const int rows_total = q_len * p.group;
-  const int row0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * 2 * BM;    // long (late) row tiles first
+  // CTAs start in the order of blockIdx (x fastest): every kv head of the longest (latest) row tile first,
+  // so that the long CTAs do not start last and leave the other SMs idle at the end
+  const int row0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * 2 * BM;
   if (row0 >= rows_total) return;
   const int hist = p.seq_lens[b] - q_len;
   const int* table = p.block_table + (int64_t)b * p.max_blocks;
@@ -193,10 +201,15 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
     mbar_init(smem_u32(&q_full), 1);
-    for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&kv_full[s]), 1); mbar_init(smem_u32(&kv_empty[s]), 1); }
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&k_full[s]), 1); mbar_init(smem_u32(&k_empty[s]), 2);       // empty: both MMA issuers
+      mbar_init(smem_u32(&v_full[s]), 1); mbar_init(smem_u32(&v_empty[s]), 2);
+    }
     for (int w = 0; w < 2; ++w) {
-      mbar_init(smem_u32(&s_full[w]), 1);
+      mbar_init(smem_u32(&s_full[w][0]), 1);
+      mbar_init(smem_u32(&s_full[w][1]), 1);
       mbar_init(smem_u32(&p_full[w]), 128);
+      mbar_init(smem_u32(&pv_done[w]), 1);
       mbar_init(smem_u32(&o_full[w]), 1);
     }
     s_abort = 0;
@@ -224,95 +237,114 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
     const int br = min(p.block_size, BN);                          // rows of one K/V box
     const int boxes = BN / br;
-    constexpr int PER_BOX = 2 * NH;
-    const int n_ops = boxes * PER_BOX;                             // <= 64
-    for (int j = 0; j < n_tiles; ++j) {
+    const int n_ops = boxes * NH;                                  // copies of one of K / V of a tile, <= 16
+    bool alive = true;
+    for (int j = 0; j < n_tiles && alive; ++j) {
       const int s = j % STAGES;
-      bool ok = true;
-      if (lane == 0) ok = mbar_wait(smem_u32(&kv_empty[s]), ((j / STAGES) & 1) ^ 1);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) { if (lane == 0) { s_abort = 1; atomicExch(p.status, 11); } break; }
       const int j0 = (tile_begin + j) * BN;
-      const uint32_t bar = smem_u32(&kv_full[s]);
-      int row[2], col[2]; uint32_t dst[2]; bool valid[2];
-      uint32_t bytes = 0;
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int o = lane + 32 * u;
-        valid[u] = false;
-        if (o < n_ops) {
-          const int x = o / PER_BOX, r = o % PER_BOX, kv = r / NH, h = r % NH;
-          const int key = j0 + x * br;
-          if (key < hi && key + br > lo) {
-            const int e = (key >> p.bs_log2) - table_first;
-            const int blk = e < TABLE_SLOTS ? s_table[e] : table[key >> p.bs_log2];
-            if (blk >= 0) {
-              valid[u] = true;
-              row[u] = ((blk * 2 + kv) * p.Hkv + hk) * p.block_size + (key & (p.block_size - 1));
-              col[u] = h * 64;
-              dst[u] = (kv == 0 ? sK : sV) + s * KV_BYTES + h * KV_HALF + x * br * 128;
-              bytes += br * 128;
-            }
+      // this lane's copy: page x of the tile, 64-wide half h (the same for K and for V)
+      bool valid = false;
+      int row_k = 0, col = 0; uint32_t off = 0;
+      if (lane < n_ops) {
+        const int x = lane / NH, h = lane % NH;
+        const int key = j0 + x * br;
+        if (key < hi && key + br > lo) {
+          const int e = (key >> p.bs_log2) - table_first;
+          const int blk = e < TABLE_SLOTS ? s_table[e] : table[key >> p.bs_log2];
+          if (blk >= 0) {
+            valid = true;
+            row_k = (blk * 2 * p.Hkv + hk) * p.block_size + (key & (p.block_size - 1));
+            col = h * 64;
+            off = s * KV_BYTES + h * KV_HALF + x * br * 128;
           }
         }
       }
-      bytes = __reduce_add_sync(0xffffffffu, bytes);
-      if (lane == 0) {
-        if (bytes == 0) mbar_arrive(bar); else mbar_expect_tx(bar, bytes);
-      }
-      __syncwarp();
+      const uint32_t bytes = __reduce_add_sync(0xffffffffu, valid ? (uint32_t)(br * 128) : 0u);
 #pragma unroll
-      for (int u = 0; u < 2; ++u)
-        if (valid[u]) tma_load_2d(dst[u], &map_kv, col[u], row[u], bar);
+      for (int kv = 0; kv < 2; ++kv) {
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait(smem_u32(kv == 0 ? &k_empty[s] : &v_empty[s]), ((j / STAGES) & 1) ^ 1);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { if (lane == 0) { s_abort = 1; atomicExch(p.status, 11); } alive = false; break; }
+        const uint32_t bar = smem_u32(kv == 0 ? &k_full[s] : &v_full[s]);
+        if (lane == 0) {
+          if (bytes == 0) mbar_arrive(bar); else mbar_expect_tx(bar, bytes);
+        }
+        __syncwarp();
+        if (valid) tma_load_2d((kv == 0 ? sK : sV) + off, &map_kv, col, row_k + kv * p.Hkv * p.block_size, bar);
+      }
     }
-  } else if (warp == 1) {
-    if (lane == 0) {                                                // ---- MMA issue
+  } else if (warp == 1 || warp == MMA_WARP_B) {
+    if (lane == 0) {
+      // ---- MMA issue: one thread per row tile (warp 1: tile A, the last warp: tile B).  Each runs its tile's
+      // chain on its own, so neither waits for the other's softmax; the K and V stages go back to the producer
+      // when both have committed (or, past the end of its tile, plainly arrived on) their empty barriers.
+      const int w = warp == 1 ? 0 : 1;
+      const int n_w = w == 0 ? n_tiles_a : (b_on ? n_tiles : 0);
       constexpr uint32_t idesc_qk = idesc_bf16(BM, BN, 0), idesc_pv = idesc_bf16(BM, D, 1);
-      auto issue_qk = [&](int w, int s) {
+      // descriptors differ from these bases by constants (16-byte units in the low field)
+      const uint64_t dq = desc_k_major(sQ + w * Q_BYTES), dk = desc_k_major(sK);
+      const uint64_t dp = desc_k_major(sP + w * P_BYTES), dv = desc_mn_major(sV, KV_HALF);
+      const uint32_t o_tmem = tmem + O_COL + w * 128;
+      auto issue_qk = [&](int t) {                                  // S_w[t % 2] = Q_w K(t)^T
+        const uint64_t dks = dk + (uint64_t)((t % STAGES) * (KV_BYTES >> 4));
+        const uint32_t s_tmem = tmem + (2 * w + (t & 1)) * BN;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint64_t da = desc_k_major(sQ + w * Q_BYTES + (k / 4) * Q_HALF + (k % 4) * 32);
-          const uint64_t db = desc_k_major(sK + s * KV_BYTES + (k / 4) * KV_HALF + (k % 4) * 32);
-          tc_mma(tmem + S_COL + w * BN, da, db, idesc_qk, k > 0 ? 1u : 0u);
+          tc_mma(s_tmem, dq + (uint64_t)(((k / 4) * Q_HALF + (k % 4) * 32) >> 4),
+                 dks + (uint64_t)(((k / 4) * KV_HALF + (k % 4) * 32) >> 4), idesc_qk, k > 0 ? 1u : 0u);
         }
-        tc_commit(smem_u32(&s_full[w]));
+        tc_commit(smem_u32(&s_full[w][t & 1]));
       };
-      auto issue_pv = [&](int w, int s, int j) {
+      auto issue_pv = [&](int s, int j) {
+        const uint64_t dvs = dv + (uint64_t)(s * (KV_BYTES >> 4));
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k) {
-          const uint64_t da = desc_k_major(sP + w * P_BYTES + k * 32);
-          const uint64_t db = desc_mn_major(sV + s * KV_BYTES + k * 16 * 128, KV_HALF);
-          tc_mma(tmem + O_COL + w * 128, da, db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-        }
+        for (int k = 0; k < BN / 16; ++k)
+          tc_mma(o_tmem, dp + (uint64_t)(k * 2), dvs + (uint64_t)((k * 16 * 128) >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
       };
-      bool ok = mbar_wait(smem_u32(&q_full), 0) && mbar_wait(smem_u32(&kv_full[0]), 0);
-      if (!ok) { s_abort = 1; atomicExch(p.status, 12); }
-      if (ok) {
-        tc_fence_after();
-        if (n_tiles_a > 0) issue_qk(0, 0);
-        if (b_on) issue_qk(1, 0);
-      }
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % STAGES, s1 = (j + 1) % STAGES;
-        bool next_ready = false;
-        for (int w = 0; w < 2 && ok; ++w) {
-          const int n_w = w == 0 ? n_tiles_a : (b_on ? n_tiles : 0);
-          if (j >= n_w) continue;
-          if (!mbar_wait(smem_u32(&p_full[w]), j & 1)) { s_abort = 1; atomicExch(p.status, 13); ok = false; break; }
+      bool ok = true;
+      if (n_w > 0 && !mbar_wait(smem_u32(&q_full), 0)) { s_abort = 1; atomicExch(p.status, 12); ok = false; }
+      // prologue: S of this row tile's first two key tiles
+      for (int t = 0; t < 2 && t < n_tiles && ok; ++t) {
+        if (t < n_w) {
+          if (!mbar_wait(smem_u32(&k_full[t % STAGES]), 0)) { s_abort = 1; atomicExch(p.status, 12); ok = false; break; }
           tc_fence_after();
-          issue_pv(w, s, j);
-          if (j + 1 < n_w) {
-            if (!next_ready) {
-              if (!mbar_wait(smem_u32(&kv_full[s1]), ((j + 1) / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); ok = false; break; }
-              tc_fence_after();
-              next_ready = true;
-            }
-            issue_qk(w, s1);
+          issue_qk(t);
+          tc_commit(smem_u32(&k_empty[t % STAGES]));
+        } else {                                                   // not this tile's key tile: hand the stage back once it is full
+          if (!mbar_wait(smem_u32(&k_full[t % STAGES]), 0)) { s_abort = 1; atomicExch(p.status, 12); ok = false; break; }
+          mbar_arrive(smem_u32(&k_empty[t % STAGES]));
+        }
+      }
+      // Past the end of its own row tile an issuer still takes every stage in step (it waits for the stage
+      // to be full before it arrives on its empty barrier), so that a barrier never gets two arrivals of one
+      // issuer in one phase.
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % STAGES;
+        if (j < n_w) {
+          if (!mbar_wait(smem_u32(&p_full[w]), j & 1)) { s_abort = 1; atomicExch(p.status, 13); ok = false; break; }
+          if (!mbar_wait(smem_u32(&v_full[s]), (j / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); ok = false; break; }
+          tc_fence_after();
+          issue_pv(s, j);
+          tc_commit(smem_u32(&pv_done[w]));                         // P_w is free again, O_w is quiet until the next P V
+          if (j + 1 == n_w) tc_commit(smem_u32(&o_full[w]));         // this row tile's last P V
+          tc_commit(smem_u32(&v_empty[s]));
+        } else {
+          if (!mbar_wait(smem_u32(&v_full[s]), (j / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); ok = false; break; }
+          mbar_arrive(smem_u32(&v_empty[s]));
+        }
+        if (j + 2 < n_tiles) {
+          const int s2 = (j + 2) % STAGES;
+          if (j + 2 < n_w) {                                         // S of tile j + 2 into the buffer tile j just left
+            if (!mbar_wait(smem_u32(&k_full[s2]), ((j + 2) / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); ok = false; break; }
+            tc_fence_after();
+            issue_qk(j + 2);
+            tc_commit(smem_u32(&k_empty[s2]));
           } else {
-            tc_commit(smem_u32(&o_full[w]));                       // this row tile's last PV
+            if (!mbar_wait(smem_u32(&k_full[s2]), ((j + 2) / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); ok = false; break; }
+            mbar_arrive(smem_u32(&k_empty[s2]));
           }
         }
-        if (ok) tc_commit(smem_u32(&kv_empty[s]));
       }
     }
   } else {                                                          // ---- softmax and output: one thread per row
@@ -325,35 +357,43 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int n_w = w == 0 ? n_tiles_a : (b_on ? n_tiles : 0);
     const int first_tok_w = (row0 + w * BM) / p.group;
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t s_addr = lane_addr + S_COL + w * BN, o_addr = lane_addr + O_COL + w * 128;
+    const uint32_t s_addr = lane_addr + 2 * w * BN, o_addr = lane_addr + O_COL + w * 128;
     unsigned char* prow = smem_dyn + (sP - smem_u32(smem_dyn)) + w * P_BYTES + r * 128;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;                           // reference maximum (scaled, log2 units), running sum
     bool ok = true;
     for (int j = 0; j < n_w && ok; ++j) {
-      if (!mbar_wait(smem_u32(&s_full[w]), j & 1)) { s_abort = 1; atomicExch(p.status, 15); ok = false; break; }
+      if (!mbar_wait(smem_u32(&s_full[w][j & 1]), (j >> 1) & 1)) { s_abort = 1; atomicExch(p.status, 15); ok = false; break; }
       tc_fence_after();
       float s0[32], s1[32];
-      tmem_ld32(s_addr, s0);
-      tmem_ld32(s_addr + 32, s1);
+      tmem_ld32(s_addr + (j & 1) * BN, s0);
+      tmem_ld32(s_addr + (j & 1) * BN + 32, s1);
       tmem_ld_wait();
       const int jbase = (tile_begin + j) * BN;
       const bool need_mask = (jbase + BN - 1 > hist + first_tok_w) || p.window > 0 || jbase < lo;
-      float mx = -INFINITY;
+      if (need_mask) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float a = s0[i] * p.scale_log2, c = s1[i] * p.scale_log2;
-        if (need_mask) {
+        for (int i = 0; i < 32; ++i) {
           const int ja = jbase + i, jc = jbase + 32 + i;
-          if (!(ja <= pos && ja >= lo && (p.window <= 0 || ja > pos - p.window))) a = -INFINITY;
-          if (!(jc <= pos && jc >= lo && (p.window <= 0 || jc > pos - p.window))) c = -INFINITY;
+          if (!(ja <= pos && ja >= lo && (p.window <= 0 || ja > pos - p.window))) s0[i] = -INFINITY;
+          if (!(jc <= pos && jc >= lo && (p.window <= 0 || jc > pos - p.window))) s1[i] = -INFINITY;
         }
-        s0[i] = a; s1[i] = c;
-        mx = fmaxf(mx, fmaxf(a, c));
       }
+      // maximum of the raw scores (the scale is positive), as eight short chains instead of one long one
+      float mq[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mq[i] = fmaxf(s0[i], s1[i]);
+#pragma unroll
+      for (int i = 8; i < 32; ++i) mq[i & 7] = fmaxf(mq[i & 7], fmaxf(s0[i], s1[i]));
+      float mx = fmaxf(fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])), fmaxf(fmaxf(mq[4], mq[5]), fmaxf(mq[6], mq[7])));
+      mx *= p.scale_log2;
       // raise the reference maximum only when it grows by more than 8 (in log2 units)
       const bool raise = mx > m_run + 8.f;
+      bool pv_seen = j == 0;                                        // P V of tile j-1 known to be complete
       if (j > 0 && __any_sync(0xffffffffu, raise)) {
-        // O_w is quiet here: PV of tile j-1 completed before s_full fired, PV of tile j waits for our P
+        // O_w must be quiet: P V of tile j-1 complete (P V of tile j waits for our P)
+        if (!mbar_wait(smem_u32(&pv_done[w]), (j - 1) & 1)) { s_abort = 1; atomicExch(p.status, 15); ok = false; break; }
+        tc_fence_after();
+        pv_seen = true;
         const float alpha = raise ? fast_exp2(m_run - mx) : 1.f;     // m_run = -inf gives 0
         l_run *= alpha;
 #pragma unroll
@@ -368,15 +408,21 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         tmem_st_wait();
       }
       if (raise) m_run = mx;
-      const float m_use = m_run == -INFINITY ? 0.f : m_run;
-      float sum = 0.f;
+      const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+      float sq[8];                                                  // eight partial sums: short dependency chains
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sq[i] = 0.f;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        s0[i] = fast_exp2(s0[i] - m_use);
-        s1[i] = fast_exp2(s1[i] - m_use);
-        sum += s0[i] + s1[i];
+        s0[i] = fast_exp2(fmaf(s0[i], p.scale_log2, neg_m));         // masked: -inf stays -inf, 2^-inf = 0
+        s1[i] = fast_exp2(fmaf(s1[i], p.scale_log2, neg_m));
+        sq[i & 7] += s0[i] + s1[i];
       }
-      l_run += sum;
+      l_run += ((sq[0] + sq[1]) + (sq[2] + sq[3])) + ((sq[4] + sq[5]) + (sq[6] + sq[7]));
+      // the P V of tile j-1 must have read P before it is overwritten
+      if (!pv_seen) {
+        if (!mbar_wait(smem_u32(&pv_done[w]), (j - 1) & 1)) { s_abort = 1; atomicExch(p.status, 15); ok = false; break; }
+      }
       // P row r: 64 keys = 8 chunks of 16 bytes, swizzled like a K-major tile with 128-byte rows
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -474,6 +520,7 @@ DINFER_API int dinfer_attention_umma(const void* q, int64_t ldq, void* out, int6
   if (T <= 0 || B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || max_blocks <= 0 || num_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_umma: bad sizes T=%d B=%d H=%d Hkv=%d", T, B, H, Hkv);
   const int group = H / Hkv;
+  if (!(scale > 0.f)) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: the score scale must be positive, got %g", (double)scale);
   if (!dinfer_attention_umma_supports(D, group, block_size))
     return refuse(DINFER_BAD_ARGUMENT, "attention_umma: head_dim %d, group %d, block_size %d not supported "
                   "(head_dim 64 or 128, group dividing 128, power-of-two pages of at least 8)", D, group, block_size);
@@ -514,6 +561,6 @@ DINFER_API int dinfer_attention_umma(const void* q, int64_t ldq, void* out, int6
   p.bs_log2 = 0;
   while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
   p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-  dim3 grid(((int64_t)max_q_len * group + 2 * BM - 1) / (2 * BM), Hkv, B);
+  dim3 grid(Hkv, ((int64_t)max_q_len * group + 2 * BM - 1) / (2 * BM), B);
   return D == 64 ? launch<64>(mq, mkv, p, grid, stream) : launch<128>(mq, mkv, p, grid, stream);
 }
