@@ -32,9 +32,19 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size
               intermediate_size=200, num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5,
               head_dim=48, rms_norm_eps=3e-6, rope_theta=50000.0, max_position_embeddings=512,
               tie_word_embeddings=False)
+# Head geometries of the tensor-core kernels at a small width: head size 128 in groups of 4, head size 64 in
+# groups of 2 (tcgen05 prompt attention, TMA decode attention, tcgen05 decode products, lane kernel of q/k).
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=1000, hidden_size=256,
+              intermediate_size=384, num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2,
+              head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=1024,
+              tie_word_embeddings=False)
+TINY_E = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=777, hidden_size=192,
+              intermediate_size=320, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=64, rms_norm_eps=2e-6, rope_theta=10000.0, max_position_embeddings=1024,
+              tie_word_embeddings=True)
 # init rules of the tiny models: (seed, std, norm jitter)
-INIT = {"A": (0, 0.05, 0.1), "B": (1, 0.03, 0.2), "C": (2, 0.04, 0.15)}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+INIT = {"A": (0, 0.05, 0.1), "B": (1, 0.03, 0.2), "C": (2, 0.04, 0.15), "D": (3, 0.03, 0.1), "E": (4, 0.04, 0.1)}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def make_model_dir(path: str, cfg: dict, seed: int, std: float, jitter: float,

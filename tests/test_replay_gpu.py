@@ -16,6 +16,8 @@ LENGTHS = {
     "A": {"a": 1, "b": 7, "c": 19, "d": 64, "e": 97, "f": 128},
     "B": {"a": 3, "b": 16, "c": 17, "d": 40, "e": 63, "f": 150, "g": 255},
     "C": {"a": 2, "b": 33, "c": 129, "d": 200},
+    "D": {"a": 5, "b": 100, "c": 300, "d": 515},          # several 64-key tiles per request
+    "E": {"a": 3, "b": 64, "c": 257, "d": 450},
 }
 
 
@@ -31,7 +33,7 @@ def model_dirs(tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_replay_all_ways(model_dirs, tmp_path, name, dtype):
     model_dir = model_dirs[(name, dtype)]
     cfg = H.CONFIGS[name]
