@@ -1,4 +1,7 @@
-// Sampling on f32 logits, one 1024-thread block per row.
+// Sampling on f32 logits.  A row is shared by a thread-block cluster of ROW_CTAS CTAs of 1024 threads:
+// every CTA keeps its contiguous slice of the row (scaled by 1/temperature) in shared memory, so the
+// row is read from memory once, and the CTAs exchange their partial results through each other's
+// shared memory (st.shared::cluster + one cluster barrier per exchange).
 //
 //   dinfer_argmax      greedy, ties to the lowest index
 //   dinfer_sample      temperature -> min_p -> top-k -> top-p -> inverse CDF in vocabulary order,
@@ -10,7 +13,11 @@
 //
 // Same contract as the reference (crates/kernels/cuda/sampling.cu:13-56,60-133,143-157,196-283,
 // 322-349; order of operations models/qwen3/src/executor.rs:552-605).  Unlike it the logits are not
-// rewritten: the three filters reduce to one keep-threshold on the scaled logits.
+// rewritten: the three filters reduce to one keep-threshold on the scaled logits.  The top-k and the
+// top-p threshold are each found by a radix-16 descent over the order-preserving 32-bit image of a
+// float (eight rounds, every round one pass over shared memory): the largest value t such that the
+// kept entries >= t number at least k (have at least the share p of the mass).  All sums are taken in
+// a fixed order (thread, warp, CTA rank), so the same logits, seed and count give the same token.
 #include "common.cuh"
 
 using namespace dinfer;
@@ -18,41 +25,131 @@ using namespace dinfer;
 namespace {
 
 constexpr int BLOCK = 1024;
+constexpr int ROW_CTAS = 8;                 // cluster size: CTAs that share a row
+constexpr int MAX_SLICE = 48 * 1024;        // floats of a row slice that shared memory holds (192 KB)
+constexpr int XCH = 16;                     // floats a CTA hands to the others per exchange
+
+// ---- cluster plumbing
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t local_addr, uint32_t rank, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
+// What the CTAs of a row share: two exchange buffers used alternately (a CTA may write the next
+// exchange while a slower one still reads the last) and the block-level scratch.
+struct Shared {
+  float xchg[2][ROW_CTAS][XCH];
+  float warp_part[32][XCH];
+  float blk[XCH];
+  float warp_tot[32];
+  int pick[4];
+  int turn;
+};
+
+// Every CTA contributes n <= XCH floats (valid in threads 0..n-1 as `mine`); afterwards
+// sh.xchg[turn][r][j] holds the contribution j of CTA r, the same in every CTA.  Returns the buffer.
+__device__ float (*exchange(Shared& sh, float mine, int n, uint32_t rank))[XCH] {
+  const int t = sh.turn;
+  if ((int)threadIdx.x < n) {
+#pragma unroll
+    for (uint32_t r = 0; r < ROW_CTAS; ++r) st_cluster_f32(smem_u32(&sh.xchg[t][rank][threadIdx.x]), r, mine);
+  }
+  cluster_sync_all();
+  __syncthreads();
+  if (threadIdx.x == 0) sh.turn = t ^ 1;
+  __syncthreads();
+  return sh.xchg[t];
+}
+
+// Deterministic block sum of a per-thread vector v[0..N): warp shuffle tree, then the warps in order.
+// The result is in sh.blk[0..N) for all threads.
+template <int N>
+__device__ void block_sum_vec(Shared& sh, float (&v)[N]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int j = 0; j < N; ++j) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v[j] += __shfl_xor_sync(0xffffffffu, v[j], o);
+  }
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) sh.warp_part[warp][j] = v[j];
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < N) {
+    float s = 0.f;
+    for (int w = 0; w < BLOCK / 32; ++w) s += sh.warp_part[w][threadIdx.x];
+    sh.blk[threadIdx.x] = s;
+  }
+  __syncthreads();
+}
+
+// Sum over the whole row of a per-thread vector: block sum, exchange, CTAs in rank order.
+template <int N>
+__device__ void row_sum_vec(Shared& sh, float (&v)[N], uint32_t rank, float (&out)[N]) {
+  block_sum_vec<N>(sh, v);
+  const float mine = (int)threadIdx.x < N ? sh.blk[threadIdx.x] : 0.f;
+  float (*x)[XCH] = exchange(sh, mine, N, rank);
+#pragma unroll
+  for (int j = 0; j < N; ++j) {
+    float s = 0.f;
+#pragma unroll
+    for (int r = 0; r < ROW_CTAS; ++r) s += x[r][j];
+    out[j] = s;
+  }
+}
+
+// order-preserving image of a float: a < b  <=>  key(a) < key(b)   (-0 is folded into +0 by the caller)
+__device__ __forceinline__ uint32_t float_key(float x) {
+  const uint32_t u = __float_as_uint(x);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
 
 struct ArgMax { float v; int i; };
-
 __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
   return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
 }
 
-__device__ int block_argmax(const float* row, int vocab, float* sv, int* si) {
+// argmax over the row (ties to the lowest index), the same in every CTA of the cluster
+__device__ int row_argmax(Shared& sh, const float* xs, int n_mine, int first, uint32_t rank) {
   ArgMax best{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < vocab; i += BLOCK) best = better(best, ArgMax{row[i], i});
+  for (int i = threadIdx.x; i < n_mine; i += BLOCK) best = better(best, ArgMax{xs[i], first + i});
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1)
     best = better(best, ArgMax{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)});
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   __syncthreads();
-  if (lane == 0) { sv[warp] = best.v; si[warp] = best.i; }
+  if (lane == 0) { sh.warp_part[warp][0] = best.v; sh.warp_part[warp][1] = __int_as_float(best.i); }
   __syncthreads();
   if (warp == 0) {
-    best = ArgMax{sv[lane], si[lane]};
+    best = ArgMax{sh.warp_part[lane][0], __float_as_int(sh.warp_part[lane][1])};
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
       best = better(best, ArgMax{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)});
-    if (lane == 0) si[0] = best.i == 0x7fffffff ? 0 : best.i;
+    if (lane == 0) { sh.blk[0] = best.v; sh.blk[1] = __int_as_float(best.i); }
   }
   __syncthreads();
-  return si[0];
-}
-
-__global__ void __launch_bounds__(BLOCK) argmax_kernel(const float* __restrict__ logits, int64_t ld,
-                                                       int* __restrict__ out, int vocab) {
-  __shared__ float sv[32];
-  __shared__ int si[32];
-  pdl_enter();
-  const int r = block_argmax(logits + (int64_t)blockIdx.x * ld, vocab, sv, si);
-  if (threadIdx.x == 0) out[blockIdx.x] = r;
+  const float mine = threadIdx.x < 2 ? sh.blk[threadIdx.x] : 0.f;
+  float (*x)[XCH] = exchange(sh, mine, 2, rank);
+  ArgMax all{-INFINITY, 0x7fffffff};
+#pragma unroll
+  for (int r = 0; r < ROW_CTAS; ++r) all = better(all, ArgMax{x[r][0], __float_as_int(x[r][1])});
+  return all.i == 0x7fffffff ? 0 : all.i;
 }
 
 __device__ __forceinline__ uint32_t mulhilo(uint32_t a, uint32_t b, uint32_t* hi) {
@@ -77,126 +174,240 @@ __device__ float philox_uniform(uint64_t seed, uint64_t offset) {
   return (float)(c0 >> 8) * (1.f / 16777216.f);
 }
 
-// Count and softmax mass of the scaled logits x = v * inv_t with x >= t (and x >= floor).
-__device__ void count_mass(const float* row, int vocab, float inv_t, float m, float t, float floor_,
-                           float* red, float* count, float* mass) {
-  float c = 0.f, s = 0.f;
-  for (int i = threadIdx.x; i < vocab; i += BLOCK) {
-    const float x = row[i] * inv_t;
-    if (x >= t && x >= floor_) { c += 1.f; s += expf(x - m); }
+// The slice of the row this CTA owns: ids [first, first + n_mine).  Thread t owns the contiguous
+// ids [t*seg, (t+1)*seg) of the slice, so thread order, then CTA rank, is vocabulary order.
+struct Slice {
+  const float* xs;      // scaled values in shared memory, or null: read the row and scale on the fly
+  const float* row;
+  float inv_t;
+  int first, n_mine, seg;
+  __device__ __forceinline__ float at(int i) const { return xs ? xs[i] : row[first + i] * inv_t + 0.f; }
+};
+
+// The largest value t such that the entries x >= max(t, floor_) weigh at least `target`, where an
+// entry weighs 1 (MASS = false) or exp(x - m) (MASS = true).  Radix-16 descent over float_key:
+// `above` is the weight of the entries beyond the digits fixed so far.
+template <bool MASS>
+__device__ float radix_threshold(Shared& sh, const Slice& sl, uint32_t rank, float m, float floor_, float target) {
+  uint32_t prefix = 0;
+  float above = 0.f;
+  const int i0 = min(sl.n_mine, (int)threadIdx.x * sl.seg), i1 = min(sl.n_mine, i0 + sl.seg);
+#pragma unroll 1
+  for (int shift = 28; shift >= 0; shift -= 4) {
+    float h[16];
+#pragma unroll
+    for (int d = 0; d < 16; ++d) h[d] = 0.f;
+    for (int i = i0; i < i1; ++i) {
+      const float x = sl.at(i);
+      if (!(x >= floor_)) continue;
+      const uint32_t k = float_key(x);
+      if (shift < 28 && (k >> (shift + 4)) != (prefix >> (shift + 4))) continue;
+      const float w = MASS ? expf(x - m) : 1.f;
+      const int dgt = (k >> shift) & 15;
+#pragma unroll
+      for (int d = 0; d < 16; ++d) h[d] += dgt == d ? w : 0.f;
+    }
+    float tot[16];
+    row_sum_vec<16>(sh, h, rank, tot);
+    int chosen = 0;
+    float run = above;
+    bool found = false;
+#pragma unroll
+    for (int d = 15; d >= 0; --d) {
+      if (!found) {
+        if (run + tot[d] >= target) { chosen = d; found = true; }
+        else run += tot[d];
+      }
+    }
+    if (!found) { chosen = 0; run -= tot[0]; }          // less than the target in all: keep everything
+    above = run;
+    prefix |= (uint32_t)chosen << shift;
   }
-  *count = block_sum(c, red);
-  *mass = block_sum(s, red);
+  return key_float(prefix);
+}
+
+__global__ void __launch_bounds__(BLOCK)
+argmax_kernel(const float* __restrict__ logits, int64_t ld, int* __restrict__ out, int vocab) {
+  extern __shared__ __align__(16) float xs_dyn[];
+  __shared__ Shared sh;
+  pdl_enter();
+  const uint32_t rank = cluster_ctarank();
+  const int b = blockIdx.x / ROW_CTAS;
+  const float* row = logits + (int64_t)b * ld;
+  const int per = (vocab + ROW_CTAS - 1) / ROW_CTAS;
+  const int first = min(vocab, (int)rank * per), n_mine = min(vocab, first + per) - first;
+  if (threadIdx.x == 0) sh.turn = 0;
+  __syncthreads();
+  cluster_sync_all();                                    // every CTA runs before any writes into its memory
+  const int r = row_argmax(sh, row + first, n_mine, first, rank);
+  if (rank == 0 && threadIdx.x == 0) out[b] = r;
+  cluster_sync_all();                                    // nobody leaves while others may still write to it
 }
 
 __global__ void __launch_bounds__(BLOCK)
 sample_kernel(const float* __restrict__ logits, int64_t ld, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
               const uint64_t* __restrict__ seeds, const uint64_t* __restrict__ offsets,
-              int* __restrict__ out, int vocab) {
-  __shared__ float red[33];
-  __shared__ float sv[32];
-  __shared__ int si[32];
-  __shared__ float seg_sum[BLOCK];
-  __shared__ int choice;
+              int* __restrict__ out, int vocab, int cache_slice) {
+  extern __shared__ __align__(16) float xs_dyn[];
+  __shared__ Shared sh;
   pdl_enter();
-  const int b = blockIdx.x;
+  const uint32_t rank = cluster_ctarank();
+  const int b = blockIdx.x / ROW_CTAS;
   const float* row = logits + (int64_t)b * ld;
+  const int per = (vocab + ROW_CTAS - 1) / ROW_CTAS;
+  const int first = min(vocab, (int)rank * per), n_mine = min(vocab, first + per) - first;
+  if (threadIdx.x == 0) sh.turn = 0;
+  __syncthreads();
+  cluster_sync_all();                                    // every CTA runs before any writes into its memory
   const float temp = temperature[b];
   if (temp <= 1e-5f) {
-    const int r = block_argmax(row, vocab, sv, si);
-    if (threadIdx.x == 0) out[b] = r;
+    const int r = row_argmax(sh, row + first, n_mine, first, rank);
+    if (rank == 0 && threadIdx.x == 0) out[b] = r;
+    cluster_sync_all();
     return;
   }
   const float inv_t = 1.f / temp;
+  Slice sl;
+  sl.row = row; sl.inv_t = inv_t; sl.first = first; sl.n_mine = n_mine;
+  sl.seg = (per + BLOCK - 1) / BLOCK;
+  sl.xs = cache_slice ? xs_dyn : nullptr;
+
+  // one pass over the row: scaled values into shared memory, maximum and smallest finite value
   float m = -INFINITY, lo = INFINITY;
-  for (int i = threadIdx.x; i < vocab; i += BLOCK) {
-    const float x = row[i] * inv_t;
+  for (int i = threadIdx.x; i < n_mine; i += BLOCK) {
+    const float x = row[first + i] * inv_t + 0.f;        // + 0: -0 becomes +0 (one image per value)
+    if (cache_slice) xs_dyn[i] = x;
     m = fmaxf(m, x);
     if (x > -INFINITY) lo = fminf(lo, x);
   }
-  m = block_max(m, red);
-  lo = -block_max(-lo, red);
+  {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sh.warp_part[warp][0] = m; sh.warp_part[warp][1] = lo; }
+    __syncthreads();
+    if (threadIdx.x < 2) {
+      float v = sh.warp_part[0][threadIdx.x];
+      for (int w = 1; w < BLOCK / 32; ++w) v = threadIdx.x == 0 ? fmaxf(v, sh.warp_part[w][0]) : fminf(v, sh.warp_part[w][1]);
+      sh.blk[threadIdx.x] = v;
+    }
+    __syncthreads();
+    const float mine = threadIdx.x < 2 ? sh.blk[threadIdx.x] : 0.f;
+    float (*x)[XCH] = exchange(sh, mine, 2, rank);
+    m = -INFINITY; lo = INFINITY;
+#pragma unroll
+    for (int r = 0; r < ROW_CTAS; ++r) { m = fmaxf(m, x[r][0]); lo = fminf(lo, x[r][1]); }
+  }
 
   // keep-threshold on x: min_p, then top-k, then top-p on what top-k and min_p left
   float thr = -INFINITY;
   const float mp = min_p ? min_p[b] : 0.f;
   if (mp > 0.f) thr = m + logf(mp);                      // p_i >= min_p * p_max
   const int k = top_k ? top_k[b] : -1;
-  if (k > 0 && k < vocab) {
-    float a = fmaxf(lo, thr), hi = m;                     // largest t with count(x >= t) >= k
-    for (int it = 0; it < 48 && hi > a; ++it) {
-      const float mid = 0.5f * (a + hi);
-      float c, s;
-      count_mass(row, vocab, inv_t, m, mid, thr, red, &c, &s);
-      if (c >= (float)k) a = mid; else hi = mid;
-    }
-    thr = fmaxf(thr, a);
-  }
+  if (k > 0 && k < vocab) thr = fmaxf(thr, radix_threshold<false>(sh, sl, rank, m, thr, (float)k));
   const float p = top_p ? top_p[b] : 1.f;
+  const int i0 = min(n_mine, (int)threadIdx.x * sl.seg), i1 = min(n_mine, i0 + sl.seg);
   if (p < 1.f && p > 0.f) {
-    float c, denom;
-    count_mass(row, vocab, inv_t, m, -INFINITY, thr, red, &c, &denom);
-    float a = fmaxf(lo, thr), hi = m;                     // largest t with mass(x >= t) >= p * denom
-    for (int it = 0; it < 48 && hi > a; ++it) {
-      const float mid = 0.5f * (a + hi);
-      float s;
-      count_mass(row, vocab, inv_t, m, mid, thr, red, &c, &s);
-      if (s >= p * denom) a = mid; else hi = mid;
+    float d1[1] = {0.f}, denom[1];
+    for (int i = i0; i < i1; ++i) {
+      const float x = sl.at(i);
+      if (x >= thr) d1[0] += expf(x - m);
     }
-    thr = fmaxf(thr, a);
+    row_sum_vec<1>(sh, d1, rank, denom);
+    thr = fmaxf(thr, radix_threshold<true>(sh, sl, rank, m, thr, p * denom[0]));
   }
 
-  // inverse CDF in vocabulary order: thread t owns the contiguous ids [t*seg, (t+1)*seg)
-  const int seg = (vocab + BLOCK - 1) / BLOCK;
-  const int i0 = threadIdx.x * seg, i1 = min(vocab, i0 + seg);
+  // inverse CDF in vocabulary order: threads in order within a CTA, CTAs in rank order
   float mine = 0.f;
   for (int i = i0; i < i1; ++i) {
-    const float x = row[i] * inv_t;
+    const float x = sl.at(i);
     if (x >= thr) mine += expf(x - m);
   }
-  seg_sum[threadIdx.x] = mine;
-  if (threadIdx.x == 0) choice = -1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float incl = mine;                                     // inclusive scan over the lanes of the warp
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) sh.warp_tot[warp] = incl;
   __syncthreads();
   if (threadIdx.x == 0) {
-    float total = 0.f;
-    for (int t = 0; t < BLOCK; ++t) total += seg_sum[t];
-    const float target = philox_uniform(seeds[b], offsets[b]) * total;
-    float before = 0.f;
-    int owner = -1;
-    for (int t = 0; t < BLOCK; ++t) {
-      if (seg_sum[t] > 0.f && before + seg_sum[t] >= target) { owner = t; break; }
-      before += seg_sum[t];
-    }
-    red[0] = target;
-    red[1] = before;
-    si[0] = owner;
+    float s = 0.f;
+    for (int w = 0; w < BLOCK / 32; ++w) s += sh.warp_tot[w];
+    sh.blk[0] = s;
   }
   __syncthreads();
-  const int owner = si[0];
-  if (owner == (int)threadIdx.x) {
-    float cum = red[1];
-    const float target = red[0];
-    int last = -1;
-    for (int i = i0; i < i1; ++i) {
-      const float x = row[i] * inv_t;
-      if (x >= thr) {
-        cum += expf(x - m);
-        last = i;
-        if (cum >= target) break;
+  float (*x)[XCH] = exchange(sh, threadIdx.x == 0 ? sh.blk[0] : 0.f, 1, rank);
+  float total = 0.f;
+#pragma unroll
+  for (int r = 0; r < ROW_CTAS; ++r) total += x[r][0];
+  const float target = philox_uniform(seeds[b], offsets[b]) * total;
+  // the CTA whose share of the cumulative mass reaches the target; beyond the total by rounding: the
+  // last CTA that keeps anything, at the end of its share
+  int owner = -1, last_nonzero = -1;
+  float before = 0.f, before_last = 0.f, run = 0.f;
+#pragma unroll
+  for (int r = 0; r < ROW_CTAS; ++r) {
+    const float t = x[r][0];
+    if (t > 0.f) { last_nonzero = r; before_last = run; }
+    if (owner < 0 && t > 0.f && run + t >= target) { owner = r; before = run; }
+    run += t;
+  }
+  bool clamp = false;
+  if (owner < 0) { owner = last_nonzero; before = before_last; clamp = true; }
+  if (owner == (int)rank) {
+    // within this CTA: the warp, then the lane, then the entry
+    if (threadIdx.x == 0) {
+      float cum = before;
+      int w_own = -1;
+      float w_before = before;
+      int w_last = -1;
+      float w_before_last = before;
+      for (int w = 0; w < BLOCK / 32; ++w) {
+        const float t = sh.warp_tot[w];
+        if (t > 0.f) { w_last = w; w_before_last = cum; }
+        if (w_own < 0 && !clamp && t > 0.f && cum + t >= target) { w_own = w; w_before = cum; }
+        cum += t;
+      }
+      if (w_own < 0) { w_own = w_last; w_before = w_before_last; sh.pick[2] = 1; } else sh.pick[2] = 0;
+      sh.pick[0] = w_own;
+      sh.blk[1] = w_before;
+    }
+    __syncthreads();
+    if (warp == sh.pick[0]) {
+      const bool clamp_w = sh.pick[2] != 0;
+      const float base = sh.blk[1];
+      const float excl = incl - mine;                    // mass of the lanes before this one
+      // the first lane whose inclusive sum reaches the target (or the last lane that keeps anything)
+      const bool hit = !clamp_w && mine > 0.f && base + incl >= target;
+      const unsigned hits = __ballot_sync(0xffffffffu, hit);
+      const unsigned keeps = __ballot_sync(0xffffffffu, mine > 0.f);
+      int l_own;
+      bool clamp_l = false;
+      if (hits) l_own = __ffs(hits) - 1;
+      else { l_own = 31 - __clz(keeps); clamp_l = true; }
+      if (lane == l_own) {
+        float cum = base + excl;
+        int last = -1;
+        for (int i = i0; i < i1; ++i) {
+          const float xv = sl.at(i);
+          if (xv >= thr) {
+            cum += expf(xv - m);
+            last = i;
+            if (!clamp_l && cum >= target) break;
+          }
+        }
+        out[b] = first + (last < 0 ? 0 : last);
       }
     }
-    choice = last;
   }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int c = choice;
-    if (c < 0) {   // the target lies a rounding above the total: the last kept token
-      for (int i = vocab - 1; i >= 0; --i) if (row[i] * inv_t >= thr) { c = i; break; }
-      if (c < 0) c = 0;
-    }
-    out[b] = c;
-  }
+  if (owner < 0 && rank == 0 && threadIdx.x == 0) out[b] = 0;   // nothing kept at all (no finite logit)
+  cluster_sync_all();                                    // nobody leaves while others may still write to it
 }
 
 // history of row b: ids[offsets[b] .. offsets[b+1]), the first prompt_len[b] of them the prompt.
@@ -224,6 +435,13 @@ __global__ void penalties_kernel(float* __restrict__ logits, int64_t ld, const i
   }
 }
 
+template <typename... KArgs, typename... Args>
+int launch_rows(void (*kernel)(KArgs...), int rows, size_t smem, cudaStream_t stream, const char* what, Args... args) {
+  cudaError_t e = launch_pdl_cluster(kernel, dim3(rows * ROW_CTAS), dim3(BLOCK), dim3(ROW_CTAS, 1, 1), smem, stream, args...);
+  if (e != cudaSuccess) return refuse((int)e, "%s: launch failed: %s", what, cudaGetErrorString(e));
+  return cuda_status(what);
+}
+
 }  // namespace
 
 DINFER_DEFINE_LAST_ERROR()
@@ -231,8 +449,7 @@ DINFER_DEFINE_LAST_ERROR()
 DINFER_API int dinfer_argmax(const float* logits, int64_t ld, int* out, int rows, int vocab, cudaStream_t stream) {
   if (rows < 0 || vocab <= 0 || ld < vocab) return refuse(DINFER_BAD_ARGUMENT, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
   if (rows == 0) return 0;
-  launch_pdl(argmax_kernel, dim3(rows), dim3(BLOCK), 0, stream, logits, ld, out, vocab);
-  return cuda_status("argmax");
+  return launch_rows(argmax_kernel, rows, 0, stream, "argmax", logits, ld, out, vocab);
 }
 
 // temperature [rows]; top_k (<=0: off), top_p, min_p may be null; seeds, offsets [rows] uint64.
@@ -241,8 +458,18 @@ DINFER_API int dinfer_sample(const float* logits, int64_t ld, const float* tempe
                              const uint64_t* offsets, int* out, int rows, int vocab, cudaStream_t stream) {
   if (rows < 0 || vocab <= 0 || ld < vocab) return refuse(DINFER_BAD_ARGUMENT, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
   if (rows == 0) return 0;
-  launch_pdl(sample_kernel, dim3(rows), dim3(BLOCK), 0, stream, logits, ld, temperature, top_k, top_p, min_p, seeds, offsets, out, vocab);
-  return cuda_status("sample");
+  // a row slice that fits shared memory is kept there (read once); a longer one is read again every pass
+  const int per = (vocab + ROW_CTAS - 1) / ROW_CTAS;
+  const int cache_slice = per <= MAX_SLICE ? 1 : 0;
+  const size_t smem = cache_slice ? (size_t)per * sizeof(float) : 0;
+  static bool opted = false;
+  if (!opted) {
+    cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SLICE * (int)sizeof(float));
+    if (e != cudaSuccess) return refuse((int)e, "sample: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    opted = true;
+  }
+  return launch_rows(sample_kernel, rows, smem, stream, "sample", logits, ld, temperature, top_k, top_p, min_p, seeds,
+                     offsets, out, vocab, cache_slice);
 }
 
 DINFER_API int dinfer_penalties(float* logits, int64_t ld, const int* ids, const int* offsets,

@@ -72,7 +72,15 @@ def check(lib: ctypes.CDLL, code: int, what: str) -> None:
         raise KernelError(f"{what} failed (code {code}): {msg.decode('utf-8', 'replace') if msg else ''}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def stream_handle() -> ctypes.c_void_p:
+    """The current stream of the current device (the capture stream while a graph is being captured).
+    Asked for at every launch, so through torch's raw accessor where this torch has it."""
+    if _raw_stream is not None and _raw_device is not None:
+        return ctypes.c_void_p(_raw_stream(_raw_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
