@@ -235,3 +235,153 @@ def test_toy_architecture_registered_in_the_test(tmp_path, dtype):
         from dinfer_b200.parts.base import MIXERS
         unregister_architecture("ToyMixedForTest")
         MIXERS.unregister("toy_running_mean")
+
+
+# ------------------------------------------- a second toy: routed feed-forward, another position encoding
+
+def register_toy_routed():
+    from dinfer_b200.config.registry import register_architecture
+    from dinfer_b200.parts.base import FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, PositionEncoding
+    from dinfer_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorDecl
+
+    class Decay(PositionEncoding):
+        """q_d <- q_d e^(-lambda_d p), k_d <- k_d e^(+lambda_d p): the score of (i, j) is weighted per
+        dimension by e^(-lambda_d (i - j)).  Not a table rotation, so the mixer calls apply()."""
+        fused = False
+
+        def __init__(self, params, env, prefix=""):
+            super().__init__(params, env, prefix)
+            D = int(params["head_dim"])
+            self.lam = (float(params["rate"]) * torch.arange(D, dtype=torch.float32) / D).to(env.device)
+
+        def apply(self, q, k, ctx):
+            f = torch.exp(ctx.positions.float()[:, None, None] * self.lam[None, None, :])
+            q.copy_((q.float() / f).to(q.dtype))
+            k.copy_((k.float() * f).to(k.dtype))
+
+    class Routed(FeedForward):
+        """Router logits in 32-bit -> the top_k experts -> softmax over the chosen -> weighted sum of
+        their gated feed-forwards."""
+
+        def __init__(self, params, env, prefix=""):
+            super().__init__(params, env, prefix)
+            self.E, self.k, self.I, self.h = int(params["experts"]), int(params["top_k"]), int(params["inter"]), env.hidden_size
+
+        def declare(self):
+            d = [TensorDecl(self.prefix + "router.weight", (self.E, self.h))]
+            for e in range(self.E):
+                d += [TensorDecl(self.prefix + f"experts.{e}.gate.weight", (self.I, self.h)),
+                      TensorDecl(self.prefix + f"experts.{e}.up.weight", (self.I, self.h)),
+                      TensorDecl(self.prefix + f"experts.{e}.down.weight", (self.h, self.I))]
+            return d
+
+        def bind(self, tensors):
+            self.t = {k[len(self.prefix):]: v for k, v in tensors.items() if k.startswith(self.prefix)}
+
+        def forward(self, x, ctx):
+            xf = x.float()
+            logits = xf @ self.t["router.weight"].float().T
+            top, idx = torch.topk(logits, self.k, dim=-1)
+            w = torch.softmax(top, dim=-1)
+            out = torch.zeros_like(xf)
+            for e in range(self.E):
+                g = xf @ self.t[f"experts.{e}.gate.weight"].float().T
+                u = xf @ self.t[f"experts.{e}.up.weight"].float().T
+                y = (torch.nn.functional.silu(g) * u) @ self.t[f"experts.{e}.down.weight"].float().T
+                out += y * (w * (idx == e)).sum(-1, keepdim=True)
+            return out.to(x.dtype)
+
+    POSITION_ENCODINGS.register("toy_decay", Decay, replace=True)
+    FEED_FORWARDS.register("toy_routed", Routed, replace=True)
+
+    def spec(c):
+        h, Hq, Hkv, D = c["hidden_size"], c["heads"], c["kv_heads"], c["head_dim"]
+        norm = lambda name: PartSpec("rmsnorm", {"size": h, "eps": c["eps"], "weight": name})
+
+        def attn(pos):
+            return PartSpec("gqa_attention", {"num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D, "qk_norm": True,
+                                              "eps": c["eps"], "position": pos})
+        decay = PartSpec("toy_decay", {"head_dim": D, "rate": c["rate"]})
+        rope = PartSpec("rope_neox", {"head_dim": D, "theta": c["theta"], "max_positions": c["max_positions"]})
+        layers = (
+            LayerSpec("layers.0.", "prenorm_residual", attn(decay), norm("n1.weight"),
+                      PartSpec("toy_routed", {"experts": c["experts"], "top_k": c["top_k"], "inter": c["inter"]}),
+                      norm("n2.weight")),
+            LayerSpec("layers.1.", "prenorm_residual", attn(rope), norm("n1.weight"),
+                      PartSpec("swiglu", {"intermediate_size": c["inter"]}), norm("n2.weight")),
+        )
+        return ModelSpec("ToyRoutedForTest", h, c["vocab_size"], c["max_positions"], "embed.weight", layers,
+                         (ScheduleEntry(0), ScheduleEntry(1)), norm("final.weight"), "head.weight", False)
+
+    register_architecture("ToyRoutedForTest", lambda d: dict(d), spec, replace=True)
+
+
+TOY_ROUTED = dict(architectures=["ToyRoutedForTest"], vocab_size=157, hidden_size=40, heads=6, kv_heads=3, head_dim=16,
+                  inter=48, experts=4, top_k=2, rate=0.03, theta=20000.0, eps=1e-6, max_positions=128)
+
+
+def toy_routed_plain_logits(W, c, ids):
+    W = {k: v.double() for k, v in W.items()}
+    T, H_, Hkv, D = len(ids), c["heads"], c["kv_heads"], c["head_dim"]
+    pos = torch.arange(T)
+    x = W["embed.weight"][torch.tensor(ids)]
+    for layer in (0, 1):
+        p = f"layers.{layer}."
+        hdn = P.rms_norm(x, W[p + "n1.weight"], c["eps"])
+        q = P.rms_norm((hdn @ W[p + "q_proj.weight"].T).reshape(T, H_, D), W[p + "q_norm.weight"], c["eps"])
+        k = P.rms_norm((hdn @ W[p + "k_proj.weight"].T).reshape(T, Hkv, D), W[p + "k_norm.weight"], c["eps"])
+        v = (hdn @ W[p + "v_proj.weight"].T).reshape(T, Hkv, D)
+        if layer == 0:
+            lam = (torch.tensor(c["rate"], dtype=torch.float32) * torch.arange(D, dtype=torch.float32) / D).double()
+            f = torch.exp(pos.double()[:, None, None] * lam[None, None, :])
+            q, k = q / f, k * f
+        else:
+            cos, sin = P.rope_cos_sin(pos, D, c["theta"])
+            q, k = P.rope_neox(q, cos, sin), P.rope_neox(k, cos, sin)
+        o = P.causal_gqa_attention(q, k, v, D ** -0.5, None)
+        x = x + o.reshape(T, H_ * D) @ W[p + "o_proj.weight"].T
+        hdn = P.rms_norm(x, W[p + "n2.weight"], c["eps"])
+        if layer == 0:
+            logits = hdn @ W[p + "router.weight"].T
+            top, idx = torch.topk(logits, c["top_k"], dim=-1)
+            w = torch.softmax(top, dim=-1)
+            y = torch.zeros_like(hdn)
+            for e in range(c["experts"]):
+                ye = P.swiglu_mlp(hdn, W[p + f"experts.{e}.gate.weight"], W[p + f"experts.{e}.up.weight"],
+                                  W[p + f"experts.{e}.down.weight"])
+                y += ye * (w * (idx == e)).sum(-1, keepdim=True)
+        else:
+            y = P.swiglu_mlp(hdn, W[p + "gate_proj.weight"], W[p + "up_proj.weight"], W[p + "down_proj.weight"])
+        x = x + y
+    return (P.rms_norm(x, W["final.weight"], c["eps"]) @ W["head.weight"].T).numpy()
+
+
+def test_toy_routed_feed_forward_and_other_position_encoding(tmp_path):
+    """A feed-forward with routing and a position encoding that is no table rotation, both defined here,
+    registered, built from a model folder and stepped whole / in portions / mixed (32-bit: the routing
+    must pick the same experts as the plain implementation)."""
+    register_toy_routed()
+    try:
+        d = H.make_model_dir(str(tmp_path / "toyr"), TOY_ROUTED, 5, 0.1, 0.1, torch.float32)
+        W = H.load_plain_weights(d)
+        rng = random.Random(9)
+        tokens = {r: H.random_tokens(rng, n, TOY_ROUTED["vocab_size"]) for r, n in {"a": 40, "b": 3, "c": 77}.items()}
+        want = {r: toy_routed_plain_logits(W, TOY_ROUTED, t) for r, t in tokens.items()}
+        lengths = {r: len(t) for r, t in tokens.items()}
+        rp = H.LocalReplay(d, "float32", 192, block_size=8)
+        worst = {}
+        try:
+            for name, steps in (("whole", H.schedule_whole(lengths)), ("chunks", H.schedule_chunks(lengths, rng)),
+                                ("mixed", H.schedule_mixed(lengths, rng, max_live=3, decode_tail=10))):
+                got = H.run_schedule(rp, steps, tokens, tag=name + "/")
+                worst[name] = max(H.rel_err(got[r], want[r]) for r in tokens)
+        finally:
+            assert rp.close() == 0
+        print(worst)
+        assert all(v <= H.TOLERANCE["float32"] for v in worst.values()), worst
+    finally:
+        from dinfer_b200.config.registry import unregister_architecture
+        from dinfer_b200.parts.base import FEED_FORWARDS, POSITION_ENCODINGS
+        unregister_architecture("ToyRoutedForTest")
+        FEED_FORWARDS.unregister("toy_routed")
+        POSITION_ENCODINGS.unregister("toy_decay")
