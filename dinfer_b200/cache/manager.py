@@ -10,9 +10,16 @@ Allocation is all-or-nothing over the groups and leaves the state untouched when
 the reference's ``allocate_slots`` (crates/core/src/kv/manager.rs:203-281); ``free`` gives
 pages back last-first (manager.rs:337-345).  Beside the pages every request holds one slot for
 state of fixed size (used by mixers that keep such state; a Qwen3 model has none).
+
+Prefix cache (optional; only for groups that keep every key): a full page whose keys are in the
+cache is registered under a hash chained over the token ids of the request up to and including that
+page.  ``begin`` gives a new request the pages of the longest chain of its tokens that every group
+still has, never including the request's last token, so that at least one token is run and yields
+logits (manager.rs:147-155).  Shared pages are only read: a request writes at positions behind its hit.
 """
 from __future__ import annotations
 
+import hashlib
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -30,14 +37,28 @@ class _Held:
     tables: List[List[int]]           # per group: page id per block index, -1 = released / not held
     num_tokens: int = 0               # tokens the pages cover (allocated for)
     num_computed: int = 0             # tokens whose keys are in the cache
+    tokens: List[int] = field(default_factory=list)      # prefix cache: the ids of the computed tokens
+    hashes: List[bytes] = field(default_factory=list)    # prefix cache: chained hash per full page so far
+
+
+def chain_hash(parent: bytes, tokens: Sequence[int]) -> bytes:
+    """Hash of a page's contents given the hash of the page before it (16 bytes of BLAKE2b)."""
+    h = hashlib.blake2b(parent, digest_size=16)
+    h.update(b"".join(int(t).to_bytes(4, "little", signed=True) for t in tokens))
+    return h.digest()
 
 
 class CacheManager:
     def __init__(self, groups: Sequence[GroupSpec], block_size: int, num_blocks: Sequence[int] | int,
-                 max_num_seqs: int):
+                 max_num_seqs: int, enable_prefix_caching: bool = False):
         if block_size <= 0:
             raise ValueError("block_size must be positive")
         self.groups = list(groups)
+        if enable_prefix_caching and any(g.window is not None for g in self.groups):
+            raise ValueError("the prefix cache needs groups that keep every key (no window)")
+        self.prefix_caching = bool(enable_prefix_caching)
+        self.prefix_queries = 0           # tokens asked for / found by begin()
+        self.prefix_hits = 0
         self.block_size = block_size
         if isinstance(num_blocks, int):
             num_blocks = [num_blocks] * len(self.groups)
@@ -90,6 +111,39 @@ class CacheManager:
         return all(n <= p.num_free for n, p in zip(self._need(held, total_tokens), self.pools))
 
     # ---- changes
+    def begin(self, req: Hashable, token_ids: Sequence[int]) -> int:
+        """A request enters with these tokens: take the pages of their longest cached prefix (whole
+        pages, every group, never the last token) and return how many tokens they cover.  0 without
+        the prefix cache, for a request that already holds pages, or when no state slot is free."""
+        if not self.prefix_caching or req in self._reqs:
+            return 0
+        bs = self.block_size
+        limit = (len(token_ids) - 1) // bs             # full pages that leave the last token out
+        self.prefix_queries += len(token_ids)
+        chain: List[bytes] = []
+        found: List[List[int]] = [[] for _ in self.groups]
+        parent = b""
+        for i in range(limit):
+            parent = chain_hash(parent, token_ids[i * bs:(i + 1) * bs])
+            pages = [p.lookup(parent) for p in self.pools]
+            if any(b is None for b in pages):
+                break
+            chain.append(parent)
+            for g, b in enumerate(pages):
+                found[g].append(b)
+        n = len(chain)
+        if n == 0:
+            return 0
+        if self.state_slots.acquire(req) is None:
+            return 0
+        for g, pool in enumerate(self.pools):
+            for b in found[g]:
+                pool.touch(b)
+        self._reqs[req] = _Held(tables=found, num_tokens=n * bs, num_computed=n * bs,
+                                tokens=list(token_ids[:n * bs]), hashes=chain)
+        self.prefix_hits += n * bs
+        return n * bs
+
     def allocate(self, req: Hashable, total_tokens: int) -> bool:
         """Grow the request's tables to cover ``total_tokens`` tokens.  False (and nothing changed)
         when some group lacks pages or no state slot is free."""
@@ -106,12 +160,25 @@ class CacheManager:
         held.num_tokens = max(held.num_tokens, total_tokens)
         return True
 
-    def advance(self, req: Hashable, num_computed: int) -> None:
+    def advance(self, req: Hashable, num_computed: int, new_tokens: Optional[Sequence[int]] = None) -> None:
         """The cache now holds the keys of the first ``num_computed`` tokens: give back the pages
-        that every window has passed."""
+        that every window has passed.  With the prefix cache, ``new_tokens`` are the ids of the tokens
+        computed since the last call; pages they fill become findable."""
         held = self._reqs[req]
         if num_computed > held.num_tokens:
             raise PoolError(f"request {req!r}: {num_computed} tokens computed but pages cover {held.num_tokens}")
+        if self.prefix_caching and new_tokens is not None:
+            if len(held.tokens) + len(new_tokens) != num_computed:
+                raise PoolError(f"request {req!r}: {len(held.tokens)} known + {len(new_tokens)} new tokens "
+                                f"do not make {num_computed}")
+            held.tokens.extend(int(t) for t in new_tokens)
+            bs = self.block_size
+            while (len(held.hashes) + 1) * bs <= num_computed:
+                i = len(held.hashes)
+                h = chain_hash(held.hashes[-1] if held.hashes else b"", held.tokens[i * bs:(i + 1) * bs])
+                held.hashes.append(h)
+                for g, pool in enumerate(self.pools):
+                    pool.set_hash(held.tables[g][i], h)     # stays unhashed if another page holds these contents
         held.num_computed = num_computed
         for g in range(len(self.groups)):
             if self.groups[g].window is None:
@@ -136,18 +203,24 @@ class CacheManager:
     def check_invariants(self) -> None:
         """No page lost or held twice: per group, held pages + free pages = the pool, disjoint."""
         for g, pool in enumerate(self.pools):
-            seen = {}
+            seen: Dict[int, list] = {}
             for req, held in self._reqs.items():
-                for b in held.tables[g]:
+                for i, b in enumerate(held.tables[g]):
                     if b < 0:
                         continue
-                    if b in seen:
-                        raise AssertionError(f"group {g}: page {b} held by {seen[b]!r} and {req!r}")
+                    if b in seen and not self.prefix_caching:
+                        raise AssertionError(f"group {g}: page {b} held by {seen[b][0]!r} and {req!r}")
+                    if b in seen and (i >= len(held.hashes) or pool.hash_of(b) != held.hashes[i]):
+                        raise AssertionError(f"group {g}: page {b} shared by {seen[b]!r} and {req!r} without a common hash")
                     if not pool.is_held(b):
                         raise AssertionError(f"group {g}: page {b} of {req!r} is marked free")
-                    seen[b] = req
+                    seen.setdefault(b, []).append(req)
+            for b, holders in seen.items():
+                if pool.refcount(b) != len(holders):
+                    raise AssertionError(f"group {g}: page {b} has {pool.refcount(b)} references, {len(holders)} holders")
             if len(seen) + pool.num_free != pool.num_blocks:
                 raise AssertionError(f"group {g}: {len(seen)} held + {pool.num_free} free != {pool.num_blocks}")
+            pool.check()
         holders = self.state_slots.holders()
         if set(holders) != set(self._reqs):
             raise AssertionError("state slots and page holders differ")

@@ -28,6 +28,9 @@ class EngineConfig:
     long_prefill_token_threshold: int = 0
     # decode-only steps replay a captured CUDA graph
     enable_cuda_graph: bool = True
+    # full pages of computed tokens stay findable by the hash of their tokens and are shared by later
+    # requests with the same beginning (off by default: with it on, freed pages are not the next ones used)
+    enable_prefix_caching: bool = False
     # "bfloat16" = what serving uses; "float32" = everything in true 32-bit
     dtype: str = "bfloat16"
     device: int = 0

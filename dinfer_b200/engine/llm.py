@@ -44,6 +44,7 @@ class EngineStats:
     prompt_tokens: int = 0
     generated_tokens: int = 0
     preemptions: int = 0
+    prefix_hit_tokens: int = 0        # prompt tokens found in the prefix cache (not run again)
 
 
 class LLM:
@@ -52,7 +53,7 @@ class LLM:
                  max_num_seqs: int = 16, max_num_batched_tokens: int = 2048, num_blocks: Optional[int] = None,
                  block_size: int = 16, gpu_memory_utilization: float = 0.9,
                  decode_exempt_from_budget: bool = True, long_prefill_token_threshold: int = 0,
-                 enable_cuda_graph: bool = True, device: int = 0):
+                 enable_cuda_graph: bool = True, enable_prefix_caching: bool = False, device: int = 0):
         """``model``: a folder with config.json and *.safetensors; or ``config`` (the config.json
         dictionary) with ``weights`` (any WeightSource, e.g. ``RandomSource``)."""
         self.engine_config = EngineConfig(
@@ -61,7 +62,8 @@ class LLM:
             gpu_memory_utilization=gpu_memory_utilization,
             decode_exempt_from_budget=decode_exempt_from_budget,
             long_prefill_token_threshold=long_prefill_token_threshold,
-            enable_cuda_graph=enable_cuda_graph, dtype=dtype, device=device)
+            enable_cuda_graph=enable_cuda_graph, enable_prefix_caching=enable_prefix_caching, dtype=dtype,
+            device=device)
         if model is not None:
             self.runner = ModelRunner.from_dir(model, self.engine_config)
         elif config is not None and weights is not None:
@@ -127,6 +129,7 @@ class LLM:
             if self.stats.steps % 256 == 0:
                 self.runner.check_device_status()
         self.stats.preemptions = self.scheduler.num_preemptions
+        self.stats.prefix_hit_tokens = self.runner.manager.prefix_hits
         outs = []
         for r in finished:
             self._requests.pop(r.req_id, None)

@@ -105,7 +105,12 @@ class ModelRunner:
             # never more than every sequence at full length could use
             num_blocks = min(num_blocks, self.max_blocks_per_seq * e.max_num_seqs)
         self.num_blocks = int(num_blocks)
-        self.manager = CacheManager(groups, bs, [self.num_blocks] * len(groups), e.max_num_seqs)
+        prefix = bool(e.enable_prefix_caching)
+        if prefix and (any(g.window is not None for g in groups) or any(isinstance(n, StateNeed) for n in needs)):
+            raise ValueError("enable_prefix_caching: this model has windowed layers or per-request state, "
+                             "whose cache cannot be shared between requests")
+        self.manager = CacheManager(groups, bs, [self.num_blocks] * len(groups), e.max_num_seqs,
+                                    enable_prefix_caching=prefix)
         self.bindings: List[CacheBinding] = []
         for i, (entry, n) in enumerate(zip(self.spec.schedule, needs)):
             if entry.cache_from is not None:
@@ -152,7 +157,7 @@ class ModelRunner:
             ids, rows, ctx = self.plan.build(entries, starts)
             logits = self.model.forward(ids, ctx, self.bindings, rows)
         for e, s in zip(entries, starts):
-            m.advance(e.req_id, s + len(e.tokens))
+            m.advance(e.req_id, s + len(e.tokens), e.tokens if m.prefix_caching else None)
         self.steps_run += 1
         return logits
 

@@ -8,7 +8,8 @@ token 0 later; a request never preempts itself while others run (it sits the ste
 request that alone does not fit is finished with ``length``.  Nothing is admitted in a step that
 preempted.  This is the policy of the reference's scheduler (crates/core/src/sched/mod.rs:318-644
 for schedule, :646-680 for the bookkeeping after it and preemption, :687-828 for the update and
-the stop check), without its asynchronous placeholders, speculative tokens and prefix cache.
+the stop check), without its asynchronous placeholders and speculative tokens.  With the prefix
+cache on, a request that enters takes over the cached pages of its beginning first.
 
 Pure host code: it owns the queues and asks the cache manager for pages; it never touches the GPU.
 """
@@ -127,11 +128,19 @@ class Scheduler:
         if not out.preempted:
             while self.waiting and budget > 0 and len(self.running) < cfg.max_num_seqs:
                 req = self.waiting[0]
+                began = False
+                if req.num_computed == 0 and self.manager.prefix_caching and req.req_id not in self.manager:
+                    # pages of an earlier request with the same beginning: those tokens are not run again
+                    req.num_computed = self.manager.begin(req.req_id, req.tokens(0, req.num_tokens))
+                    began = req.num_computed > 0
                 num_new = req.num_tokens - req.num_computed
                 if threshold > 0:
                     num_new = min(num_new, threshold)
                 num_new = min(num_new, budget, cfg.max_model_len - req.num_computed)
                 if num_new <= 0 or not self.manager.allocate(req.req_id, req.num_computed + num_new):
+                    if began:
+                        self.manager.free(req.req_id)
+                        req.num_computed = 0
                     break
                 self.waiting.popleft()
                 req.status = RequestStatus.RUNNING

@@ -118,3 +118,105 @@ def test_random_orders(seed):
     m.check_invariants()
     assert all(m.num_free_blocks(g) == m.pools[g].num_blocks for g in range(len(groups)))
     assert m.state_slots.num_free == 5
+
+
+# ---------------------------------------------------------------- prefix cache
+
+def _run_tokens(m, rid, toks, chunk=7):
+    """Bring request ``rid`` with tokens ``toks`` through begin / allocate / advance; the tokens computed."""
+    start = m.begin(rid, toks)
+    done, computed = start, 0
+    while done < len(toks):
+        n = min(chunk, len(toks) - done)
+        assert m.allocate(rid, done + n)
+        m.advance(rid, done + n, toks[done:done + n])
+        done += n
+        computed += n
+    return start, computed
+
+
+def test_prefix_cache_hits_whole_pages_and_never_the_last_token():
+    m = CacheManager([GroupSpec()], 4, 32, 8, enable_prefix_caching=True)
+    a = list(range(100, 118))                       # 18 tokens: 4 full pages + 2
+    assert _run_tokens(m, "a", a) == (0, 18)
+    m.check_invariants()
+    # the same tokens again: 4 pages are cached, but the last token must be run -> (18-1)//4 = 4 pages
+    assert _run_tokens(m, "b", a) == (16, 2)
+    assert m.block_table("b", 0)[:4] == m.block_table("a", 0)[:4]
+    assert m.block_table("b", 0)[4] != m.block_table("a", 0)[4]
+    # exactly 16 tokens: only 3 pages may be taken, the last token has to run
+    assert _run_tokens(m, "c", a[:16]) == (12, 4)
+    # a different token in page 1 breaks the chain after page 0
+    d = a[:5] + [999] + a[6:]
+    assert _run_tokens(m, "d", d)[0] == 4
+    m.check_invariants()
+    for r in ("a", "b", "c", "d"):
+        m.free(r)
+    m.check_invariants()
+    assert m.num_free_blocks() == 32
+    # freed, but still findable until the pages are needed
+    assert _run_tokens(m, "e", a)[0] == 16
+    m.check_invariants()
+
+
+def test_prefix_cache_eviction_is_least_recently_used_and_unhashed_pages_go_first():
+    m = CacheManager([GroupSpec()], 4, 8, 8, enable_prefix_caching=True)
+    a, b = list(range(8)), list(range(50, 58))
+    _run_tokens(m, "a", a + [1])                    # 2 hashed pages + 1 page in use
+    _run_tokens(m, "b", b + [1])
+    m.free("a"); m.free("b")                        # a's pages are older on the free list than b's
+    m.check_invariants()
+    pool = m.pools[0]
+    assert pool.num_free == 8 and pool.evictions == 0
+    # 8 pages free: 2 never used, 2 unhashed (the partly filled ones), 4 hashed.  Taking 5 evicts one hashed
+    # page: the deepest page of the request freed first.
+    assert m.allocate("x", 20)
+    assert pool.evictions == 1
+    m.free("x")                                     # unhashed pages: they are used before the hashed ones
+    assert _run_tokens(m, "b2", b + [2])[0] == 8    # b's chain is whole
+    m.free("b2")
+    assert _run_tokens(m, "a2", a + [2])[0] == 4    # a's second page is gone, its first still there
+    m.check_invariants()
+
+
+def test_prefix_cache_random_orders_keep_the_books():
+    rng = random.Random(11)
+    m = CacheManager([GroupSpec(), GroupSpec()], 4, 40, 6, enable_prefix_caching=True)
+    stems = [[rng.randrange(50) for _ in range(rng.randrange(4, 30))] for _ in range(4)]
+    live = {}
+    hits = 0
+    for step in range(600):
+        if live and (len(live) >= 6 or rng.random() < 0.4):
+            rid = rng.choice(list(live))
+            toks, done = live[rid]
+            if done >= len(toks) or rng.random() < 0.2:
+                m.free(rid)
+                del live[rid]
+            else:
+                n = min(rng.randrange(1, 9), len(toks) - done)
+                if m.allocate(rid, done + n):
+                    m.advance(rid, done + n, toks[done:done + n])
+                    live[rid] = (toks, done + n)
+                else:                                   # out of pages: give up (a preemption)
+                    m.free(rid)
+                    del live[rid]
+        else:
+            rid = f"r{step}"
+            toks = rng.choice(stems) + [rng.randrange(50) for _ in range(rng.randrange(1, 10))]
+            start = m.begin(rid, toks)
+            assert start % 4 == 0 and start <= len(toks) - 1
+            hits += start
+            if start or m.allocate(rid, 1):
+                if rid in m:
+                    live[rid] = (toks, start)
+        m.check_invariants()
+    assert hits > 0 and m.prefix_hits == hits
+    for rid in list(live):
+        m.free(rid)
+    m.check_invariants()
+    assert all(p.num_free == p.num_blocks for p in m.pools)
+
+
+def test_prefix_cache_refuses_windowed_groups():
+    with pytest.raises(ValueError):
+        CacheManager([GroupSpec(window=8)], 4, 8, 2, enable_prefix_caching=True)

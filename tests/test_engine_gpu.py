@@ -204,3 +204,31 @@ def test_out_of_pages_is_an_error_at_the_step_function(dirs):
         r.step([StepEntry("b", list(range(8)), [])])
     r.finish("a")
     assert r.step([StepEntry("b", list(range(8)), [7])]).shape == (1, 256)
+
+
+def test_prefix_caching_gives_the_same_tokens_and_skips_the_shared_beginning(dirs):
+    """Requests that begin alike, one after the other and all at once, with the prefix cache on: the
+    tokens of the plain implementation, fewer prompt tokens run, pages shared and given back."""
+    from dinfer_b200 import LLM, SamplingParams
+    cfg = H.TINY_B
+    rng = random.Random(21)
+    stem = H.random_tokens(rng, 45, cfg["vocab_size"])
+    prompts = [stem + H.random_tokens(rng, n, cfg["vocab_size"]) for n in (3, 11, 0, 20)] + [stem[:30]]
+    prompts[2] = list(prompts[0])                            # an exact repeat
+    W = H.load_plain_weights(dirs["B"])
+    want = [P.greedy_generate(W, cfg, p, 6) for p in prompts]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    llm = LLM(dirs["B"], dtype="float32", max_model_len=128, max_num_seqs=4, max_num_batched_tokens=32,
+              num_blocks=64, block_size=8, enable_prefix_caching=True)
+    got = [llm.generate([p], sp)[0].output_ids for p in prompts]          # one after the other: later ones hit
+    assert got == want
+    # the stem's five whole pages (40 tokens) for three followers, 24 of the 30-token prompt for the last
+    assert llm.stats.prefix_hit_tokens >= 3 * 40 + 24
+    ran = llm.stats.prompt_tokens
+    assert ran == sum(len(p) for p in prompts) - llm.stats.prefix_hit_tokens
+    llm.runner.manager.check_invariants()
+    assert llm.runner.manager.num_free_blocks() == 64
+    got2 = [o.output_ids for o in llm.generate(prompts, sp)]             # all at once, chunked and mixed
+    assert got2 == want
+    llm.runner.manager.check_invariants()
+    assert llm.runner.manager.num_free_blocks() == 64

@@ -12,7 +12,8 @@ from dinfer_b200.sampling.params import SamplingParams
 def make(num_blocks=64, block_size=4, **kw):
     cfg = EngineConfig(block_size=block_size, num_blocks=num_blocks,
                        **{"max_model_len": 64, "max_num_seqs": 4, "max_num_batched_tokens": 16, **kw})
-    m = CacheManager([GroupSpec()], block_size, num_blocks, cfg.max_num_seqs)
+    m = CacheManager([GroupSpec()], block_size, num_blocks, cfg.max_num_seqs,
+                     enable_prefix_caching=cfg.enable_prefix_caching)
     return Scheduler(cfg, m, eos_token_ids=[99]), m
 
 
@@ -24,7 +25,9 @@ def run_step(s, m, token=lambda r: 1000 + r.num_tokens):
     out = s.schedule()
     for x in out.scheduled:                       # what the step function does to the cache
         assert x.request.req_id in m and m.num_tokens(x.request.req_id) >= x.start + x.num_tokens
-        m.advance(x.request.req_id, x.start + x.num_tokens)
+        assert m.num_computed(x.request.req_id) == x.start
+        m.advance(x.request.req_id, x.start + x.num_tokens,
+                  x.request.tokens(x.start, x.start + x.num_tokens) if m.prefix_caching else None)
     done = s.update(out, {x.request.req_id: token(x.request) for x in out.scheduled if x.samples})
     m.check_invariants()
     return out, done
@@ -173,3 +176,27 @@ def test_abort_frees_pages():
     assert m.num_free_blocks() < 64
     s.abort("a")
     assert a.finish_reason == FinishReason.ABORT and m.num_free_blocks() == 64 and not s.has_unfinished()
+
+
+def test_prefix_cache_skips_the_tokens_an_earlier_request_left():
+    s, m = make(enable_prefix_caching=True)
+    s.add_request(req("a", 14, max_tokens=2))
+    while s.has_unfinished():
+        run_step(s, m)
+    # the same 14 prompt tokens: 3 whole pages of 4 are found, the rest is run
+    s.add_request(req("b", 14, max_tokens=2))
+    out, _ = run_step(s, m)
+    assert [(x.request.req_id, x.start, x.num_tokens, x.samples) for x in out.scheduled] == [("b", 12, 2, True)]
+    assert m.prefix_hits == 12
+    # a request that is preempted finds its own pages again when it comes back
+    s2, m2 = make(num_blocks=9, enable_prefix_caching=True, max_num_batched_tokens=32)
+    s2.add_request(req("x", 16, max_tokens=30))
+    s2.add_request(req("y", 16, max_tokens=30))
+    preempted = False
+    for _ in range(60):
+        out, _ = run_step(s2, m2)
+        preempted |= bool(out.preempted)
+        if not s2.has_unfinished():
+            break
+    assert preempted and not s2.has_unfinished()
+    assert m2.prefix_hits > 0
