@@ -109,3 +109,23 @@ def test_far_key_and_window_edge():
             assert torch.allclose(got, far_value, atol=2e-2), (hist, new, far, window)
         else:
             assert not torch.allclose(got, far_value, atol=0.2), (hist, new, far, window)
+
+
+def test_decode_kernel_with_more_pages_than_its_shared_memory_table():
+    """A context of more than 2048 pages: the page ids beyond the slice in shared memory come from the
+    table in memory (one split, and as many as the largest cluster)."""
+    from dinfer_b200.kernels import attention_ops as A
+    from dinfer_b200.kernels import gemm_ops as G
+    from test_kernels_gpu import paged_case, plain_paged
+    H, Hkv, D, bs = 8, 2, 128, 8
+    reqs = [(17500, 1), (30, 1)]
+    rng = random.Random(77)
+    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, torch.bfloat16)
+    seq = torch.tensor([h + n for h, n in reqs], dtype=torch.int32)
+    want = plain_paged(reqs, qs, ks, vs, D ** -0.5, None).reshape(-1, H * D)
+    for splits in (1, 16):
+        out = torch.zeros(q.shape[0], H * D, dtype=torch.bfloat16, device="cuda")
+        A.attention_decode(q.reshape(-1, H * D).cuda(), out, cache.cuda(), table.cuda(), cu.cuda(), seq.cuda(),
+                           H, Hkv, D, D ** -0.5, 0, splits)
+        G.check_status()
+        assert float((out.double().cpu() - want).abs().max()) < 2e-2

@@ -50,6 +50,13 @@ def test_long_prompt_and_history():
     run([(900, 260)], 4, 1, 64, 16, 333, seed=3)
 
 
+def test_more_pages_than_the_shared_memory_table_holds():
+    """Block tables longer than the slice a CTA keeps in shared memory (2048 entries): the entries
+    beyond it are read from the table in memory."""
+    run([(17000, 40)], 4, 2, 128, 8, None, seed=5)
+    run([(16500, 300)], 4, 1, 64, 8, 9000, seed=6)
+
+
 def test_far_key_wins():
     from dinfer_b200.kernels import attention_ops as A
     H, Hkv, D, bs = 4, 2, 128, 16
