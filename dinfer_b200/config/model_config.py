@@ -170,4 +170,28 @@ def read_config_json(model_dir: str) -> Dict[str, Any]:
             raise ConfigError(f"{path}: not valid JSON ({e})") from e
     if not isinstance(d, dict):
         raise ConfigError(f"{path}: top level must be an object")
+    _merge_generation_eos(model_dir, d)
     return d
+
+
+def _merge_generation_eos(model_dir: str, d: Dict[str, Any]) -> None:
+    """End-of-sequence ids that only ``generation_config.json`` names join those of config.json
+    (the reference takes its stop ids from the generation config too: crates/server/src/service.rs:407)."""
+    path = os.path.join(model_dir, "generation_config.json")
+    if not os.path.isfile(path):
+        return
+    with open(path, "r", encoding="utf-8") as f:
+        try:
+            g = json.load(f)
+        except json.JSONDecodeError as e:
+            raise ConfigError(f"{path}: not valid JSON ({e})") from e
+    extra = g.get("eos_token_id") if isinstance(g, dict) else None
+    if extra is None:
+        return
+    def as_list(v):
+        return [] if v is None else (list(v) if isinstance(v, (list, tuple)) else [v])
+    have = as_list(d.get("eos_token_id"))
+    merged = have + [t for t in as_list(extra) if t not in have]
+    if not all(isinstance(t, int) and not isinstance(t, bool) for t in merged):
+        raise ConfigError(f"{path}: eos_token_id must be an integer or a list of integers")
+    d["eos_token_id"] = merged if len(merged) != 1 else merged[0]

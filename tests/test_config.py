@@ -92,3 +92,18 @@ def test_engine_config_checks():
                 dict(max_model_len=1), dict(num_blocks=0)):
         with pytest.raises(ValueError):
             EngineConfig(**bad).check()
+
+
+def test_generation_config_adds_eos_ids(tmp_path):
+    import json
+    from dinfer_b200.config.model_config import Qwen3Config, read_config_json
+    import helpers as H
+    d = tmp_path / "m"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(dict(H.TINY_A)))                     # eos_token_id 7
+    (d / "generation_config.json").write_text(json.dumps({"eos_token_id": [7, 11], "temperature": 0.6}))
+    cfg = Qwen3Config.from_dict(read_config_json(str(d)))
+    assert list(cfg.eos_token_ids) == [7, 11]
+    (d / "generation_config.json").write_text(json.dumps({"eos_token_id": "x"}))
+    with pytest.raises(Exception):
+        read_config_json(str(d))
