@@ -232,3 +232,47 @@ def test_prefix_caching_gives_the_same_tokens_and_skips_the_shared_beginning(dir
     assert got2 == want
     llm.runner.manager.check_invariants()
     assert llm.runner.manager.num_free_blocks() == 64
+
+
+@pytest.mark.parametrize("prefix", [False, True])
+def test_many_requests_small_pool_all_options(tmp_path, prefix):
+    """A busy engine on the tensor-core head geometry (head size 128, groups of 4), bfloat16, CUDA graphs,
+    a pool small enough to preempt, every sampling option, with and without the prefix cache: everything
+    finishes within its limits, the books balance, no kernel gave up a wait, and a second run with the same
+    seeds gives the same tokens."""
+    from dinfer_b200 import LLM, SamplingParams
+    cfg = H.TINY_D
+    d = H.make_model_dir(str(tmp_path / "d"), cfg, *H.INIT["D"], torch.bfloat16)
+
+    def run():
+        rng = random.Random(5)
+        llm = LLM(d, dtype="bfloat16", max_model_len=512, max_num_seqs=8, max_num_batched_tokens=96,
+                  num_blocks=36, block_size=16, enable_prefix_caching=prefix)
+        stem = H.random_tokens(rng, 70, cfg["vocab_size"])
+        prompts, params = [], []
+        for i in range(24):
+            n = rng.choice([1, 2, 15, 16, 17, 60, 130, 200])
+            p = (stem[:rng.choice([32, 48, 70])] if i % 3 == 0 else []) + H.random_tokens(rng, n, cfg["vocab_size"])
+            prompts.append(p)
+            kind = i % 4
+            params.append(SamplingParams(
+                temperature=[0.0, 0.8, 1.0, 0.6][kind], top_k=[-1, -1, 20, 50][kind], top_p=[1.0, 1.0, 0.9, 0.95][kind],
+                min_p=0.02 if kind == 3 else 0.0, repetition_penalty=1.1 if kind == 2 else 1.0,
+                max_tokens=rng.choice([1, 5, 40, 90]), seed=1000 + i, ignore_eos=(i % 5 != 0)))
+        outs = llm.generate(prompts, params)
+        llm.runner.check_device_status()
+        llm.runner.manager.check_invariants()
+        assert llm.runner.manager.num_free_blocks() == 36
+        for o, sp, p in zip(outs, params, prompts):
+            assert 1 <= len(o.output_ids) <= sp.max_tokens
+            assert all(0 <= t < cfg["vocab_size"] for t in o.output_ids)
+            if o.finish_reason == "length":
+                assert len(o.output_ids) == sp.max_tokens or len(p) + len(o.output_ids) >= 512
+        return [o.output_ids for o in outs], llm.stats
+
+    first, stats = run()
+    second, _ = run()
+    assert first == second
+    assert stats.preemptions > 0
+    if prefix:
+        assert stats.prefix_hit_tokens > 0
