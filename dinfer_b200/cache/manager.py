@@ -37,6 +37,7 @@ class _Held:
     tables: List[List[int]]           # per group: page id per block index, -1 = released / not held
     num_tokens: int = 0               # tokens the pages cover (allocated for)
     num_computed: int = 0             # tokens whose keys are in the cache
+    capacity: int = 0                 # tokens the pages of every group cover (the shortest table)
     tokens: List[int] = field(default_factory=list)      # prefix cache: the ids of the computed tokens
     hashes: List[bytes] = field(default_factory=list)    # prefix cache: chained hash per full page so far
 
@@ -139,7 +140,7 @@ class CacheManager:
         for g, pool in enumerate(self.pools):
             for b in found[g]:
                 pool.touch(b)
-        self._reqs[req] = _Held(tables=found, num_tokens=n * bs, num_computed=n * bs,
+        self._reqs[req] = _Held(tables=found, num_tokens=n * bs, num_computed=n * bs, capacity=n * bs,
                                 tokens=list(token_ids[:n * bs]), hashes=chain)
         self.prefix_hits += n * bs
         return n * bs
@@ -147,9 +148,13 @@ class CacheManager:
     def allocate(self, req: Hashable, total_tokens: int) -> bool:
         """Grow the request's tables to cover ``total_tokens`` tokens.  False (and nothing changed)
         when some group lacks pages or no state slot is free."""
+        held = self._reqs.get(req)
+        if held is not None and total_tokens <= held.capacity:      # the usual decode step: room on the last page
+            if total_tokens > held.num_tokens:
+                held.num_tokens = total_tokens
+            return True
         if not self.can_allocate(req, total_tokens):
             return False
-        held = self._reqs.get(req)
         if held is None:
             if self.state_slots.acquire(req) is None:
                 return False
@@ -157,6 +162,7 @@ class CacheManager:
             self._reqs[req] = held
         for g, n in enumerate(self._need(held, total_tokens)):
             held.tables[g].extend(self.pools[g].allocate(n))
+        held.capacity = min(len(t) for t in held.tables) * self.block_size
         held.num_tokens = max(held.num_tokens, total_tokens)
         return True
 
