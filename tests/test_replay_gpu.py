@@ -63,3 +63,34 @@ def test_replay_all_ways(model_dirs, tmp_path, name, dtype):
     tol = H.TOLERANCE[dtype]
     bad = {k: v for k, v in worst.items() if not v <= tol}
     assert not bad, f"{name} {dtype}: relative error above {tol}: {bad} (all: {worst})"
+
+
+# The layer sizes of the benchmark shape (hidden 4096, 32 / 8 heads of 128, intermediate 12288), two layers and a
+# shorter vocabulary so that the plain implementation stays affordable on the CPU.
+LAYER_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=20011, hidden_size=4096,
+                intermediate_size=12288, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8,
+                head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=40960,
+                tie_word_embeddings=False)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_at_the_benchmark_layer_sizes(tmp_path, dtype):
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    model_dir = H.make_model_dir(str(tmp_path / "m8b"), LAYER_8B, 42, 0.02, 0.0, tdt)
+    rng = random.Random(88)
+    lengths = {"a": 70, "b": 33, "c": 2}
+    tokens = {r: H.random_tokens(rng, n, LAYER_8B["vocab_size"]) for r, n in lengths.items()}
+    oracle = H.PlainOracle(model_dir)
+    want = {r: oracle.logits(t) for r, t in tokens.items()}
+    schedules = {"whole": H.schedule_whole(lengths), "tail32": H.schedule_tail(lengths, 32),
+                 "mixed": H.schedule_mixed(lengths, rng, max_live=3, decode_tail=9)}
+    rp = H.LocalReplay(model_dir, dtype, max(H.max_live_tokens(s) for s in schedules.values()))
+    worst = {}
+    try:
+        for sname, steps in schedules.items():
+            got = H.run_schedule(rp, steps, tokens, tag=sname + "/")
+            worst[sname] = max(H.rel_err(got[r], want[r]) for r in tokens)
+    finally:
+        assert rp.close() == 0
+    print("8B layer sizes", dtype, worst)
+    assert all(v <= H.TOLERANCE[dtype] for v in worst.values()), worst
