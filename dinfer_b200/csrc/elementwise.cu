@@ -19,17 +19,41 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restri
   for (int i = threadIdx.x; i < h; i += blockDim.x) o[i] = to_f32<TW>(row[i]);
 }
 
-// out[t, i] = silu(x[t, i]) * x[t, I + i]; silu(g) = g / (1 + exp(-g)) in 32-bit, one rounding.
+// out[t, i] = silu(gate_i) * up_i; silu(g) = g / (1 + exp(-g)) in 32-bit, one rounding.  The row of x holds
+// gate and up as two halves (gate_i at i, up_i at I + i) or in pairs (gate_i at 2i, up_i at 2i + 1).
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int inter, int64_t ldx) {
+__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int inter, int64_t ldx, int pairs) {
   const int t = blockIdx.x;
-  const T* g = x + (int64_t)t * ldx;
-  const T* u = g + inter;
+  const T* row = x + (int64_t)t * ldx;
   T* o = out + (int64_t)t * inter;
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x) {
-    const float a = to_f32<T>(g[i]);
-    const float b = to_f32<T>(u[i]);
+    const float a = to_f32<T>(pairs ? row[2 * i] : row[i]);
+    const float b = to_f32<T>(pairs ? row[2 * i + 1] : row[inter + i]);
     o[i] = from_f32<T>(a / (1.f + expf(-a)) * b);
+  }
+}
+
+// bfloat16 in pairs, 8 inputs (16 bytes) -> 4 outputs per thread
+__global__ void silu_mul_pairs_bf16_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                                           int inter4, int64_t ldx, int inter) {
+  pdl_enter();
+  const int t = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)t * ldx);
+  uint2* o = reinterpret_cast<uint2*>(out + (int64_t)t * inter);
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter4; i += gridDim.y * blockDim.x) {
+    const uint4 a = src[i];
+    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+    float r[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 gu = __bfloat1622float2(pa[j]);
+      r[j] = gu.x / (1.f + expf(-gu.x)) * gu.y;
+    }
+    uint2 w;
+    __nv_bfloat162 w0 = __floats2bfloat162_rn(r[0], r[1]), w1 = __floats2bfloat162_rn(r[2], r[3]);
+    w.x = *reinterpret_cast<unsigned*>(&w0);
+    w.y = *reinterpret_cast<unsigned*>(&w1);
+    o[i] = w;
   }
 }
 
@@ -80,8 +104,8 @@ DINFER_API int dinfer_embedding(const int* ids, const void* table, float* out, i
   return 0;
 }
 
-// x [T, 2*inter] with row stride ldx (gate first, then up); out [T, inter].
-DINFER_API int dinfer_silu_mul(const void* x, void* out, int T, int inter, int64_t ldx, int dtype,
+// x [T, 2*inter] with row stride ldx; out [T, inter].  pairs = 0: gate first, then up; 1: (gate_i, up_i) pairs.
+DINFER_API int dinfer_silu_mul(const void* x, void* out, int T, int inter, int64_t ldx, int dtype, int pairs,
                                cudaStream_t stream) {
   if (T < 0 || inter <= 0 || ldx < 2 * (int64_t)inter)
     return refuse(DINFER_BAD_ARGUMENT, "silu_mul: bad sizes T=%d inter=%d ldx=%lld", T, inter, (long long)ldx);
@@ -89,7 +113,15 @@ DINFER_API int dinfer_silu_mul(const void* x, void* out, int T, int inter, int64
   const int threads = 256;
   int bx = (inter + threads - 1) / threads;
   if (bx > 64) bx = 64;
-  if (dtype == DINFER_BF16 && inter % 8 == 0 && ldx % 8 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) &&
+  if (pairs && dtype == DINFER_BF16 && inter % 4 == 0 && ldx % 8 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) &&
+      !(reinterpret_cast<uintptr_t>(out) & 7)) {
+    int by = (inter / 4 + threads - 1) / threads;
+    if (by > 128) by = 128;
+    launch_pdl(silu_mul_pairs_bf16_kernel, dim3(T, by), dim3(threads), 0, stream, (const __nv_bfloat16*)x,
+               (__nv_bfloat16*)out, inter / 4, ldx, inter);
+    return cuda_status("silu_mul");
+  }
+  if (!pairs && dtype == DINFER_BF16 && inter % 8 == 0 && ldx % 8 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) &&
       !(reinterpret_cast<uintptr_t>(out) & 15)) {
     int by = (inter / 8 + threads - 1) / threads;
     if (by > 64) by = 64;
@@ -98,7 +130,7 @@ DINFER_API int dinfer_silu_mul(const void* x, void* out, int T, int inter, int64
     return cuda_status("silu_mul");
   }
   DINFER_DISPATCH_DTYPE(dtype, T_, {
-    silu_mul_kernel<T_><<<dim3(T, bx), threads, 0, stream>>>((const T_*)x, (T_*)out, inter, ldx);
+    silu_mul_kernel<T_><<<dim3(T, bx), threads, 0, stream>>>((const T_*)x, (T_*)out, inter, ldx, pairs);
     return cuda_status("silu_mul");
   });
   return 0;

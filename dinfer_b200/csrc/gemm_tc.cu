@@ -14,7 +14,9 @@
 //     streams its weight rows from HBM exactly once; K may be split across up to 8 CTAs, which then
 //     form a thread-block cluster: every CTA owns a share of the tile's 128 rows, the others store
 //     their partial sums of those rows into its shared memory (st.shared::cluster), and after one
-//     cluster barrier each CTA adds its share up, always in split order, and writes it.
+//     cluster barrier each CTA adds its share up, always in split order, and writes it.  With `act` the
+//     weight rows are (gate, up) pairs and the same epilogue writes silu(gate) * up, half as wide, so
+//     the gated feed-forward needs no kernel between its two products.
 //
 // Every wait on an mbarrier is bounded: on time-out the kernel records a code in a status word,
 // lets copies in flight land, frees its tensor memory and returns (the host reads the status word).
@@ -40,6 +42,7 @@ struct GemmParams {
   void* out; int64_t ldc;        // [tokens, N] row-major, bf16 or f32
   int tokens, N, K;
   int k_blocks_per_split, splits;
+  int act;                       // 1: weight rows come in (gate, up) pairs and out[t, j] = silu(gate_j) * up_j, N / 2 wide
   int* status;                   // device status word: 0 = fine
 };
 
@@ -125,6 +128,8 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
 template <typename T> __device__ __forceinline__ T out_cast(float v);
 template <> __device__ __forceinline__ float out_cast<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 out_cast<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
 
 template <int N_TILE> constexpr int tmem_cols() { return N_TILE <= 32 ? 32 : (N_TILE <= 64 ? 64 : (N_TILE <= 128 ? 128 : 256)); }
 // Rows of the tile that one CTA of a split-K cluster owns, and the floats of its receive buffer
@@ -277,7 +282,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         } else {
           const int n = a0 + r;                                 // weight row; the columns are tokens
-          if (p.splits == 1) {
+          if (p.splits == 1 && p.act) {
+            // the up row of a pair sits in the next lane
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float g = __uint_as_float(v[j]);
+              const float u = __shfl_down_sync(0xffffffffu, g, 1);
+              if (!(lane & 1) && n + 1 < p.N && b0 + c0 + j < p.tokens)
+                out[(int64_t)(b0 + c0 + j) * p.ldc + (n >> 1)] = out_cast<OutT>(silu_mul(g, u));
+            }
+          } else if (p.splits == 1) {
             if (n < p.N) {
 #pragma unroll
               for (int j = 0; j < 16; ++j)
@@ -309,12 +323,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int rows_mine = min(rows_per, TILE_M - rank * rows_per);
       const int cols = min(N_TILE, p.tokens - b0);              // token columns that exist
       const float* recv = reinterpret_cast<const float*>(smem_dyn + (recv_base - smem_u32(smem_dyn)));
-      for (int i = threadIdx.x; i < cols * rows_mine; i += NTHREADS) {
-        const int c = i / rows_mine, rl = i - c * rows_mine;
-        float acc = 0.f;
-        for (int s = 0; s < p.splits; ++s) acc += recv[(s * N_TILE + c) * rows_per + rl];
-        const int n = a0 + rank * rows_per + rl;
-        if (n < p.N) out[(int64_t)(b0 + c) * p.ldc + n] = out_cast<OutT>(acc);
+      if (p.act) {                                              // (gate, up) pairs: rows_per is even (host)
+        const int pairs_mine = rows_mine >> 1;
+        for (int i = threadIdx.x; i < cols * pairs_mine; i += NTHREADS) {
+          const int c = i / pairs_mine, pr = i - c * pairs_mine;
+          float g = 0.f, u = 0.f;
+          for (int s = 0; s < p.splits; ++s) {
+            const float2 v = *reinterpret_cast<const float2*>(recv + (s * N_TILE + c) * rows_per + 2 * pr);
+            g += v.x;
+            u += v.y;
+          }
+          const int n = a0 + rank * rows_per + 2 * pr;
+          if (n + 1 < p.N) out[(int64_t)(b0 + c) * p.ldc + (n >> 1)] = out_cast<OutT>(silu_mul(g, u));
+        }
+      } else {
+        for (int i = threadIdx.x; i < cols * rows_mine; i += NTHREADS) {
+          const int c = i / rows_mine, rl = i - c * rows_mine;
+          float acc = 0.f;
+          for (int s = 0; s < p.splits; ++s) acc += recv[(s * N_TILE + c) * rows_per + rl];
+          const int n = a0 + rank * rows_per + rl;
+          if (n < p.N) out[(int64_t)(b0 + c) * p.ldc + n] = out_cast<OutT>(acc);
+        }
       }
     }
   }
@@ -382,16 +411,22 @@ DINFER_DEFINE_LAST_ERROR()
 // x [tokens, K] (row stride ldx), w [N, K] (row stride ldw), both bf16; out [tokens, N] (row stride ldc)
 // bf16 (out_f32 = 0) or f32.  tokens <= 64: decode orientation with `splits` K splits (at most 8: the
 // CTAs of a tile form a cluster).  More tokens: prompt orientation, splits ignored.
+// act = 1 (decode orientation only, N even): the rows of w are (gate, up) pairs and out is [tokens, N / 2],
+// out[t, j] = silu(x w_{2j}) * (x w_{2j+1}).
 // status: a device int that a kernel sets non-zero when one of its bounded waits ran out.
 DINFER_API int dinfer_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldc,
-                              int out_f32, int tokens, int N, int K, int splits, int* status, cudaStream_t stream) {
+                              int out_f32, int tokens, int N, int K, int splits, int act, int* status,
+                              cudaStream_t stream) {
   if (tokens < 0 || N <= 0 || K <= 0) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: bad sizes tokens=%d N=%d K=%d", tokens, N, K);
   if (tokens == 0) return 0;
   if ((K % 8) || (ldx % 8) || (ldw % 8) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: K and the row strides must be multiples of 8 and the bases 16-byte aligned "
                   "(TMA); K=%d ldx=%lld ldw=%lld", K, (long long)ldx, (long long)ldw);
   if (!status) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: a status word is required");
+  if (act && (tokens > 64 || (N & 1)))
+    return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: the gated epilogue takes at most 64 tokens and an even N (tokens=%d N=%d)", tokens, N);
   GemmParams p;
+  p.act = act ? 1 : 0;
   p.out = out; p.ldc = ldc; p.tokens = tokens; p.N = N; p.K = K; p.status = status;
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
   CUtensorMap ma, mb;
@@ -401,8 +436,13 @@ DINFER_API int dinfer_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t
     if (splits < 1) splits = 1;
     if (splits > MAX_SPLITS) splits = MAX_SPLITS;
     if (splits > total_kb) splits = total_kb;
-    p.k_blocks_per_split = (total_kb + splits - 1) / splits;
-    p.splits = (total_kb + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+    for (;;) {
+      p.k_blocks_per_split = (total_kb + splits - 1) / splits;
+      p.splits = (total_kb + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+      // with the gated epilogue a (gate, up) pair must stay in one CTA: 128 / splits rows each, a power of two
+      if (!act || !(p.splits & (p.splits - 1))) break;
+      --splits;
+    }
     if ((rc = make_map(&ma, w, N, K, ldw, TILE_M))) return rc;
     if ((rc = make_map(&mb, x, tokens, K, ldx, n_tile))) return rc;
     dim3 grid((N + TILE_M - 1) / TILE_M, (tokens + n_tile - 1) / n_tile, p.splits);

@@ -59,14 +59,20 @@ def decode_splits(tokens: int, N: int, K: int) -> int:
     return max(1, min(slots // tiles, k_blocks // 8, MAX_SPLITS))
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None) -> torch.Tensor:
-    """out[tokens, N] = x[tokens, K] @ w[N, K]^T.  out: bfloat16 or float32, last axis contiguous."""
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None,
+            gated: bool = False) -> torch.Tensor:
+    """out[tokens, N] = x[tokens, K] @ w[N, K]^T.  out: bfloat16 or float32, last axis contiguous.
+    ``gated`` (at most ``DECODE_MAX_TOKENS`` rows): the rows of w are (gate, up) pairs and out is
+    [tokens, N / 2] with out[t, j] = silu(x w_2j) * (x w_2j+1)."""
     require_cuda(x, w, out)
     if not supported(x, w):
         raise KernelError("gemm_tc: bfloat16 operands with K and row strides multiples of 8 and 16-byte aligned bases")
     tokens, K = x.shape
     N = w.shape[0]
-    if w.shape[1] != K or out.shape != (tokens, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
+    if gated and (tokens > DECODE_MAX_TOKENS or N % 2):
+        raise KernelError("gemm_tc: the gated epilogue takes at most 64 rows and an even number of weight rows")
+    if w.shape[1] != K or out.shape != (tokens, N // 2 if gated else N) or out.stride(1) != 1 \
+            or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
     st = _state(x.device)
     if tokens <= DECODE_MAX_TOKENS:
@@ -74,8 +80,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optiona
     else:
         splits = 1
     lib, f = _fn("gemm_tc", "dinfer_gemm_tc",
-                 [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+                 [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
                   c_void_p, c_void_p])
     check(lib, f(ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(out), out.stride(0), int(out.dtype == torch.float32),
-                 tokens, N, K, int(splits), ptr(st["status"]), stream_handle()), "gemm_tc")
+                 tokens, N, K, int(splits), int(bool(gated)), ptr(st["status"]), stream_handle()), "gemm_tc")
     return out

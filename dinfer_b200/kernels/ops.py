@@ -85,16 +85,18 @@ def rmsnorm_plain(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.
     return out
 
 
-def silu_mul(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, i] = silu(x[t, i]) * x[t, I + i], x [T, 2I]."""
+def silu_mul(x: torch.Tensor, out: torch.Tensor, pairs: bool = False) -> torch.Tensor:
+    """out[t, i] = silu(gate_i) * up_i for x [T, 2I] that holds gate and up as halves (gate_i = x[t, i],
+    up_i = x[t, I + i]) or, with ``pairs``, side by side (gate_i = x[t, 2i], up_i = x[t, 2i + 1])."""
     require_cuda(x, out)
     _rows_contiguous(x, "silu_mul")
     T, two_i = x.shape
     inter = two_i // 2
     if two_i % 2 or out.shape != (T, inter) or not out.is_contiguous() or out.dtype != x.dtype:
         raise KernelError("silu_mul: x [T, 2I], out [T, I] contiguous, same dtype")
-    lib, f = _fn("elementwise", "dinfer_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_void_p])
-    check(lib, f(ptr(x), ptr(out), T, inter, x.stride(0), dtype_code(x.dtype), stream_handle()), "silu_mul")
+    lib, f = _fn("elementwise", "dinfer_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_void_p])
+    check(lib, f(ptr(x), ptr(out), T, inter, x.stride(0), dtype_code(x.dtype), int(bool(pairs)), stream_handle()),
+          "silu_mul")
     return out
 
 

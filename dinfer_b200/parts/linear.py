@@ -36,6 +36,19 @@ class Linear:
     def kernel_libraries(self):
         return ["gemm_f32"] if self.weight.dtype == torch.float32 else ["gemm_tc"]
 
+    def fuses_gate(self, x: torch.Tensor) -> bool:
+        """Whether ``gated_pairs`` runs as one kernel for these rows (the decode product)."""
+        return (x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and x.shape[0] <= TC_MAX_DECODE_TOKENS
+                and self.out_features % 2 == 0 and gemm_ops.supported(x, self.weight))
+
+    def gated_pairs(self, x: torch.Tensor) -> torch.Tensor:
+        """For a weight whose rows are (gate, up) pairs: ``silu(x gate_j^T) * (x up_j^T)``, [rows, out/2].
+        One kernel where ``fuses_gate``, else the product followed by the gate kernel."""
+        act = torch.empty((x.shape[0], self.out_features // 2), dtype=x.dtype, device=x.device)
+        if self.fuses_gate(x):
+            return gemm_ops.gemm_tc(x, self.weight, act, gated=True)
+        return ops.silu_mul(self(x), act, pairs=True)
+
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
         out_dtype = out_dtype or x.dtype

@@ -1,7 +1,9 @@
 """Dense gated feed-forward: ``down( silu(gate(x)) * up(x) )``.
 
-gate and up are stacked once at load into one ``[2I, h]`` matrix, gate rows first, so one
-product feeds the gate kernel (crates/layers/src/nn.rs:288-311,373-381)."""
+gate and up are stacked once at load into one ``[2I, h]`` matrix whose rows are (gate_j, up_j) pairs, so
+that one product feeds the gate (the reference stacks them as two halves and runs the gate as its own
+kernel: crates/layers/src/nn.rs:288-311,373-381).  With the pairs in neighbouring rows the decode
+product applies the gate in its epilogue; prompts run the product and then the gate kernel."""
 from __future__ import annotations
 
 from typing import Dict, List, Optional
@@ -36,14 +38,12 @@ class SwiGLU(FeedForward):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         g, u = tensors[self.names["g"]], tensors[self.names["u"]]
         dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
-        self.gate_up = Linear(torch.cat([g.to(dt), u.to(dt)], dim=0))
+        # row 2j = gate_j, row 2j + 1 = up_j
+        self.gate_up = Linear(torch.stack([g.to(dt), u.to(dt)], dim=1).reshape(2 * self.inter, self.hidden))
         self.down = Linear(tensors[self.names["d"]])
 
     def kernel_libraries(self):
         return ["elementwise"] + self.gate_up.kernel_libraries() + self.down.kernel_libraries()
 
     def forward(self, x: torch.Tensor, ctx=None) -> torch.Tensor:
-        gu = self.gate_up(x)
-        act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        ops.silu_mul(gu, act)
-        return self.down(act)
+        return self.down(self.gate_up.gated_pairs(x))

@@ -88,3 +88,20 @@ def test_repeated_split_launches_agree_bitwise():
         first = out if first is None else first
         assert torch.equal(out, first)                   # the partial sums are added in split order
     G.check_status()
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 17, 32, 64])
+@pytest.mark.parametrize("N,K", [(256, 256), (518, 96), (6144, 1024), (24576, 4096)])
+def test_gated_epilogue(tokens, N, K):
+    """Weight rows in (gate, up) pairs: out[t, j] = silu(x w_2j) * (x w_2j+1), whatever the K split."""
+    from dinfer_b200.kernels import gemm_ops as G
+    x, w = operands(tokens, N, K, tokens + N + K)
+    y = x.float() @ w.float().T
+    want = torch.nn.functional.silu(y[:, 0::2]) * y[:, 1::2]
+    for splits in (1, 2, 3, 5, 8, None):
+        out = torch.full((tokens, N // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
+        G.gemm_tc(x, w, out, splits=splits, gated=True)
+        got = out.float()
+        assert torch.isfinite(got).all()
+        assert float((got - want).abs().max()) < 2e-2 * max(1.0, float(want.abs().max())), splits
+    G.check_status()

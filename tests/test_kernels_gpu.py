@@ -67,6 +67,12 @@ def test_embedding_and_silu(dt):
     xd = x.double()
     want = P.silu(xd[:, :250]) * xd[:, 250:]
     assert torch.allclose(o.double().cpu(), want, **tol(dt))
+    for inter in (250, 256, 44):                              # gate and up side by side, vector and plain paths
+        x = (torch.randn(7, 2 * inter, generator=g) * 4).to(dt)
+        o = torch.empty(7, inter, dtype=dt, device="cuda")
+        ops.silu_mul(dev(x), o, pairs=True)
+        xd = x.double()
+        assert torch.allclose(o.double().cpu(), P.silu(xd[:, 0::2]) * xd[:, 1::2], **tol(dt))
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 37, 50), (8, 130, 999), (9, 260, 70), (130, 129, 1031), (300, 17, 8)])
