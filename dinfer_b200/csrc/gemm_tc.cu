@@ -16,7 +16,11 @@
 //     their partial sums of those rows into its shared memory (st.shared::cluster), and after one
 //     cluster barrier each CTA adds its share up, always in split order, and writes it.  With `act` the
 //     weight rows are (gate, up) pairs and the same epilogue writes silu(gate) * up, half as wide, so
-//     the gated feed-forward needs no kernel between its two products.
+//     the gated feed-forward needs no kernel between its two products.  Two more epilogues take the
+//     RMSNorm between two products apart so that it needs no kernel either: `resid` adds the product into
+//     the 32-bit residual, writes the new residual times the norm's weight (rounded) for the next product
+//     and leaves each row's partial sums of squares; `ss_in` multiplies the next product's result by
+//     rsqrt(mean of squares + eps) of its row, which commutes with the product.
 //
 // Every wait on an mbarrier is bounded: on time-out the kernel records a code in a status word,
 // lets copies in flight land, frees its tensor memory and returns (the host reads the status word).
@@ -43,6 +47,16 @@ struct GemmParams {
   int tokens, N, K;
   int k_blocks_per_split, splits;
   int act;                       // 1: weight rows come in (gate, up) pairs and out[t, j] = silu(gate_j) * up_j, N / 2 wide
+  // residual mode (decode orientation): the product is added into resid [tokens, ldr] (f32) and out gets the new
+  // residual times norm_w, rounded; the sums of squares of the rows this CTA owns go to ss_out[part][token]
+  float* resid; int64_t ldr;
+  const void* norm_w; int norm_w_f32;
+  float* ss_out;
+  // scaled mode: x holds rows that still lack their division by the root mean square; out is multiplied by
+  // rsqrt(sum over parts of ss_in[part][token] * inv_size + eps)
+  const float* ss_in; int ss_parts;
+  int ss_stride;                 // floats between the parts of ss_out / ss_in
+  float inv_size, eps;
   int* status;                   // device status word: 0 = fine
 };
 
@@ -150,6 +164,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], tmem_full_bar;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ float s_rstd[64];                                // scaled mode: per token column of this tile
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   constexpr uint32_t A_BYTES = TILE_M * BLOCK_K * 2, B_BYTES = N_TILE * BLOCK_K * 2;
   const uint32_t recv_base = smem_base + STAGES * (A_BYTES + B_BYTES);       // split-K receive buffer (SWAP only)
@@ -162,7 +177,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   pdl_launch_dependents();
   // split K: the CTAs of a tile are one cluster.  First phase of its barrier: every CTA has started,
   // so its shared memory may be written from the others (waited for just before those stores).
-  const bool clustered = SWAP && p.splits > 1;
+  const bool clustered = SWAP && (p.splits > 1 || p.resid != nullptr);   // the residual epilogue lives in the fold
   if (clustered) cluster_arrive_relaxed();
 
   if (threadIdx.x == 0) {
@@ -236,6 +251,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     pdl_enter();
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;                          // accumulator row = TMEM lane
+    if (SWAP && p.ss_in) {
+      // scaled mode: while the products run, one thread per token column adds that row's partial sums of
+      // squares (always in the same order) and keeps 1 / rms
+      const int e = (warp - 2) * 32 + lane;
+      if (e < N_TILE) {
+        float sum = 0.f;
+        if (b0 + e < p.tokens) {
+#pragma unroll 8
+          for (int q = 0; q < p.ss_parts; ++q) sum += __ldcg(p.ss_in + (int64_t)q * p.ss_stride + b0 + e);
+        }
+        s_rstd[e] = rsqrtf(sum * p.inv_size + p.eps);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps
+    }
     bool ok = true;
     if (n_kb > 0) {
       ok = mbar_wait(smem_u32(&tmem_full_bar), 0);
@@ -282,7 +311,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         } else {
           const int n = a0 + r;                                 // weight row; the columns are tokens
-          if (p.splits == 1 && p.act) {
+          if (!clustered && p.ss_in) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * s_rstd[c0 + j]);
+          }
+          if (!clustered && p.act) {
             // the up row of a pair sits in the next lane
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -291,7 +324,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               if (!(lane & 1) && n + 1 < p.N && b0 + c0 + j < p.tokens)
                 out[(int64_t)(b0 + c0 + j) * p.ldc + (n >> 1)] = out_cast<OutT>(silu_mul(g, u));
             }
-          } else if (p.splits == 1) {
+          } else if (!clustered) {
             if (n < p.N) {
 #pragma unroll
               for (int j = 0; j < 16; ++j)
@@ -323,7 +356,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int rows_mine = min(rows_per, TILE_M - rank * rows_per);
       const int cols = min(N_TILE, p.tokens - b0);              // token columns that exist
       const float* recv = reinterpret_cast<const float*>(smem_dyn + (recv_base - smem_u32(smem_dyn)));
-      if (p.act) {                                              // (gate, up) pairs: rows_per is even (host)
+      if (p.resid) {
+        // residual mode: a warp per token column, lanes over this CTA's rows; the squares of the new
+        // residual are added per lane and then across the lanes in a fixed order
+        const int part = (int)blockIdx.x * p.splits + rank;    // every (part, token) is written by exactly one warp
+        for (int c = warp; c < cols; c += NTHREADS / 32) {
+          const int64_t t = b0 + c;
+          float sq = 0.f;
+          for (int rl = lane; rl < rows_mine; rl += 32) {
+            const int n = a0 + rank * rows_per + rl;
+            if (n < p.N) {
+              float acc = 0.f;
+              for (int s = 0; s < p.splits; ++s) acc += recv[(s * N_TILE + c) * rows_per + rl];
+              const float v = p.resid[t * p.ldr + n] + acc;
+              p.resid[t * p.ldr + n] = v;
+              const float w = p.norm_w_f32 ? reinterpret_cast<const float*>(p.norm_w)[n]
+                                           : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.norm_w)[n]);
+              out[t * p.ldc + n] = out_cast<OutT>(v * w);
+              sq += v * v;
+            }
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+          if (lane == 0) p.ss_out[(int64_t)part * p.ss_stride + t] = sq;
+        }
+      } else if (p.act) {                                       // (gate, up) pairs: rows_per is even (host)
         const int pairs_mine = rows_mine >> 1;
         for (int i = threadIdx.x; i < cols * pairs_mine; i += NTHREADS) {
           const int c = i / pairs_mine, pr = i - c * pairs_mine;
@@ -333,6 +390,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             g += v.x;
             u += v.y;
           }
+          if (p.ss_in) { g *= s_rstd[c]; u *= s_rstd[c]; }
           const int n = a0 + rank * rows_per + 2 * pr;
           if (n + 1 < p.N) out[(int64_t)(b0 + c) * p.ldc + (n >> 1)] = out_cast<OutT>(silu_mul(g, u));
         }
@@ -341,6 +399,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const int c = i / rows_mine, rl = i - c * rows_mine;
           float acc = 0.f;
           for (int s = 0; s < p.splits; ++s) acc += recv[(s * N_TILE + c) * rows_per + rl];
+          if (p.ss_in) acc *= s_rstd[c];
           const int n = a0 + rank * rows_per + rl;
           if (n < p.N) out[(int64_t)(b0 + c) * p.ldc + n] = out_cast<OutT>(acc);
         }
@@ -392,7 +451,7 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_
 template <int N_TILE, int STAGES, bool SWAP, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
   auto k = gemm_tc_kernel<N_TILE, STAGES, SWAP, OutT>;
-  const size_t sm = gemm_smem_bytes<N_TILE, STAGES>(SWAP && p.splits > 1);
+  const size_t sm = gemm_smem_bytes<N_TILE, STAGES>(SWAP && (p.splits > 1 || p.resid != nullptr));
   static bool opted = false;
   if (!opted) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<N_TILE, STAGES>(SWAP));
@@ -414,9 +473,16 @@ DINFER_DEFINE_LAST_ERROR()
 // act = 1 (decode orientation only, N even): the rows of w are (gate, up) pairs and out is [tokens, N / 2],
 // out[t, j] = silu(x w_{2j}) * (x w_{2j+1}).
 // status: a device int that a kernel sets non-zero when one of its bounded waits ran out.
-DINFER_API int dinfer_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldc,
-                              int out_f32, int tokens, int N, int K, int splits, int act, int* status,
-                              cudaStream_t stream) {
+//
+// The two halves of an RMSNorm between two decode products (tokens <= 64, see the kernel's header):
+//   resid != null: resid [tokens, ldr] f32 += product; out = (new residual) * norm_w (bf16 or f32 vector of N);
+//                  ss_out[part * ss_stride + token] = sum of squares of the new residual over the part's rows,
+//                  for part < dinfer_gemm_tc_parts(tokens, N, K, splits);
+//   ss_in != null: out *= rsqrt(sum_{part < ss_parts} ss_in[part * ss_stride + token] * inv_size + eps).
+DINFER_API int dinfer_gemm_tc_fused(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldc,
+                                    int out_f32, int tokens, int N, int K, int splits, int act, float* resid, int64_t ldr,
+                                    const void* norm_w, int norm_w_f32, float* ss_out, const float* ss_in, int ss_parts,
+                                    int ss_stride, float inv_size, float eps, int* status, cudaStream_t stream) {
   if (tokens < 0 || N <= 0 || K <= 0) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: bad sizes tokens=%d N=%d K=%d", tokens, N, K);
   if (tokens == 0) return 0;
   if ((K % 8) || (ldx % 8) || (ldw % 8) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
@@ -425,8 +491,16 @@ DINFER_API int dinfer_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t
   if (!status) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: a status word is required");
   if (act && (tokens > 64 || (N & 1)))
     return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: the gated epilogue takes at most 64 tokens and an even N (tokens=%d N=%d)", tokens, N);
+  if ((resid || ss_in) && tokens > 64)
+    return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: the norm epilogues take at most 64 tokens, got %d", tokens);
+  if (resid && (act || !norm_w || !ss_out || ss_stride < tokens))
+    return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: the residual epilogue needs the norm's weight and room for the sums, and no gate");
+  if (ss_in && (ss_parts <= 0 || ss_stride < tokens))
+    return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: the scaled epilogue needs the parts of the sums (parts=%d stride=%d)", ss_parts, ss_stride);
   GemmParams p;
   p.act = act ? 1 : 0;
+  p.resid = resid; p.ldr = ldr; p.norm_w = norm_w; p.norm_w_f32 = norm_w_f32; p.ss_out = ss_out;
+  p.ss_in = ss_in; p.ss_parts = ss_parts; p.ss_stride = ss_stride; p.inv_size = inv_size; p.eps = eps;
   p.out = out; p.ldc = ldc; p.tokens = tokens; p.N = N; p.K = K; p.status = status;
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
   CUtensorMap ma, mb;
@@ -462,4 +536,22 @@ DINFER_API int dinfer_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t
   dim3 grid((tokens + TILE_M - 1) / TILE_M, (N + 255) / 256, 1);
   return out_f32 ? launch<256, 4, false, float>(ma, mb, p, grid, stream)
                  : launch<256, 4, false, __nv_bfloat16>(ma, mb, p, grid, stream);
+}
+
+DINFER_API int dinfer_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldc,
+                              int out_f32, int tokens, int N, int K, int splits, int act, int* status,
+                              cudaStream_t stream) {
+  return dinfer_gemm_tc_fused(x, ldx, w, ldw, out, ldc, out_f32, tokens, N, K, splits, act, nullptr, 0, nullptr, 0,
+                              nullptr, nullptr, 0, 0, 0.f, 0.f, status, stream);
+}
+
+// Parts of the sums of squares the residual epilogue writes for these sizes: 128-row tiles times effective K splits.
+DINFER_API int dinfer_gemm_tc_parts(int tokens, int N, int K, int splits) {
+  if (tokens <= 0 || tokens > 64 || N <= 0 || K <= 0) return 0;
+  const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  if (splits < 1) splits = 1;
+  if (splits > MAX_SPLITS) splits = MAX_SPLITS;
+  if (splits > total_kb) splits = total_kb;
+  const int per = (total_kb + splits - 1) / splits;
+  return ((N + TILE_M - 1) / TILE_M) * ((total_kb + per - 1) / per);
 }

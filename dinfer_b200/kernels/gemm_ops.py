@@ -1,7 +1,7 @@
 """Wrapper of the tcgen05 / TMA matrix product (bfloat16 operands, f32 accumulation in tensor memory)."""
 from __future__ import annotations
 
-from ctypes import c_int, c_int64, c_void_p
+from ctypes import c_float, c_int, c_int64, c_void_p
 from typing import Optional
 
 import torch
@@ -60,17 +60,27 @@ def decode_splits(tokens: int, N: int, K: int) -> int:
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None,
-            gated: bool = False) -> torch.Tensor:
+            gated: bool = False, residual: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
+            sums: Optional[torch.Tensor] = None, row_scale=None) -> torch.Tensor:
     """out[tokens, N] = x[tokens, K] @ w[N, K]^T.  out: bfloat16 or float32, last axis contiguous.
-    ``gated`` (at most ``DECODE_MAX_TOKENS`` rows): the rows of w are (gate, up) pairs and out is
-    [tokens, N / 2] with out[t, j] = silu(x w_2j) * (x w_2j+1)."""
+
+    Epilogues of the decode orientation (at most ``DECODE_MAX_TOKENS`` rows):
+      ``gated``: the rows of w are (gate, up) pairs, out is [tokens, N / 2], out[t, j] = silu(x w_2j) * (x w_2j+1);
+      ``residual`` [tokens, N] f32 with ``norm_weight`` [N] and ``sums`` [parts, stride >= tokens] f32
+        (``parts = residual_parts(...)``): the product is added into the residual, out gets the new
+        residual times the norm weight, ``sums[p, t]`` the squares of row t summed over part p;
+      ``row_scale = (sums, parts, size, eps)``: out[t] *= rsqrt(sum_p sums[p, t] / size + eps).
+    """
     require_cuda(x, w, out)
     if not supported(x, w):
         raise KernelError("gemm_tc: bfloat16 operands with K and row strides multiples of 8 and 16-byte aligned bases")
     tokens, K = x.shape
     N = w.shape[0]
-    if gated and (tokens > DECODE_MAX_TOKENS or N % 2):
-        raise KernelError("gemm_tc: the gated epilogue takes at most 64 rows and an even number of weight rows")
+    fused = gated or residual is not None or row_scale is not None
+    if fused and tokens > DECODE_MAX_TOKENS:
+        raise KernelError("gemm_tc: the fused epilogues take at most 64 rows")
+    if gated and (N % 2 or residual is not None):
+        raise KernelError("gemm_tc: the gated epilogue needs an even number of weight rows and no residual")
     if w.shape[1] != K or out.shape != (tokens, N // 2 if gated else N) or out.stride(1) != 1 \
             or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
@@ -79,9 +89,41 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optiona
         splits = decode_splits(tokens, N, K) if splits is None else max(1, min(int(splits), MAX_SPLITS))
     else:
         splits = 1
-    lib, f = _fn("gemm_tc", "dinfer_gemm_tc",
+    r_ptr = nw_ptr = so_ptr = si_ptr = None
+    ldr = nw_f32 = parts = stride = 0
+    inv_size = eps = 0.0
+    if residual is not None:
+        require_cuda(residual, norm_weight, sums)
+        if (residual.dtype != torch.float32 or residual.shape != (tokens, N) or residual.stride(1) != 1
+                or norm_weight.shape != (N,) or not norm_weight.is_contiguous()
+                or norm_weight.dtype not in (torch.bfloat16, torch.float32)
+                or sums.dtype != torch.float32 or sums.dim() != 2 or sums.stride(1) != 1 or sums.shape[1] < tokens
+                or sums.shape[0] < residual_parts(tokens, N, K, splits)):
+            raise KernelError("gemm_tc: residual [tokens, N] f32, norm_weight [N], sums [parts, >= tokens] f32")
+        r_ptr, ldr, nw_ptr, nw_f32 = ptr(residual), residual.stride(0), ptr(norm_weight), int(norm_weight.dtype == torch.float32)
+        so_ptr, stride = ptr(sums), sums.stride(0)
+    if row_scale is not None:
+        s_in, parts, size, eps = row_scale
+        require_cuda(s_in)
+        if s_in.dtype != torch.float32 or s_in.dim() != 2 or s_in.stride(1) != 1 or s_in.shape[1] < tokens \
+                or not (0 < parts <= s_in.shape[0]):
+            raise KernelError("gemm_tc: row_scale sums [parts, >= tokens] f32")
+        if residual is not None and s_in.stride(0) != stride:
+            raise KernelError("gemm_tc: the sums read and written must have one row stride")
+        si_ptr, stride, inv_size = ptr(s_in), s_in.stride(0), 1.0 / float(size)
+    lib, f = _fn("gemm_tc", "dinfer_gemm_tc_fused",
                  [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
+                  c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float,
                   c_void_p, c_void_p])
     check(lib, f(ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(out), out.stride(0), int(out.dtype == torch.float32),
-                 tokens, N, K, int(splits), int(bool(gated)), ptr(st["status"]), stream_handle()), "gemm_tc")
+                 tokens, N, K, int(splits), int(bool(gated)), r_ptr, ldr, nw_ptr, nw_f32, so_ptr, si_ptr, int(parts),
+                 int(stride), float(inv_size), float(eps), ptr(st["status"]), stream_handle()), "gemm_tc")
     return out
+
+
+def residual_parts(tokens: int, N: int, K: int, splits: Optional[int] = None) -> int:
+    """Rows of the ``sums`` the residual epilogue writes for these sizes."""
+    if splits is None:
+        splits = decode_splits(tokens, N, K)
+    lib, f = _fn("gemm_tc", "dinfer_gemm_tc_parts", [c_int, c_int, c_int, c_int])
+    return int(f(tokens, N, K, int(splits)))

@@ -105,3 +105,41 @@ def test_gated_epilogue(tokens, N, K):
         assert torch.isfinite(got).all()
         assert float((got - want).abs().max()) < 2e-2 * max(1.0, float(want.abs().max())), splits
     G.check_status()
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 17, 33])
+@pytest.mark.parametrize("N,K,N2", [(256, 128, 384), (1000, 96, 130), (4096, 4096, 6144), (1024, 3072, 2048)])
+def test_norm_taken_apart_between_two_products(tokens, N, K, N2):
+    """``residual += x w^T``; the next product's input is the new residual times the norm weight, and its
+    result is scaled by 1 / rms of the residual row: together the RMSNorm between the two products."""
+    from dinfer_b200.kernels import gemm_ops as G
+    g = torch.Generator().manual_seed(tokens + N + K)
+    x, w = operands(tokens, N, K, tokens * 3 + N)
+    resid = torch.randn(tokens, N, generator=g)
+    nw = (1 + 0.1 * torch.randn(N, generator=g)).to(torch.bfloat16).cuda()
+    eps = 1e-5
+    for splits in (1, 2, 3, None):
+        parts = G.residual_parts(tokens, N, K, splits)
+        sums = torch.full((parts + 1, 64), float("nan"), device="cuda")
+        r = resid.clone().cuda()
+        xw = torch.full((tokens, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        G.gemm_tc(x, w, xw, splits=splits, residual=r, norm_weight=nw, sums=sums)
+        want_r = resid.cuda() + x.float() @ w.float().T
+        assert float((r - want_r).abs().max()) < 1e-3 * max(1.0, float(want_r.abs().max()))
+        want_xw = (want_r * nw.float())
+        assert float((xw.float() - want_xw).abs().max()) < 1e-2 * max(1.0, float(want_xw.abs().max()))
+        ss = sums[:parts, :tokens].sum(0)
+        assert torch.allclose(ss, (want_r ** 2).sum(1), rtol=1e-4)
+        assert torch.isnan(sums[parts]).all()                   # nothing written beyond the parts
+        # the consumer: a plain product and a gated one, scaled by 1 / rms
+        w2 = (torch.randn(N2, N, generator=g) / math.sqrt(N)).to(torch.bfloat16).cuda()
+        rstd = torch.rsqrt((r ** 2).sum(1) / N + eps)
+        y = (xw.float() @ w2.float().T) * rstd[:, None]
+        out = torch.full((tokens, N2), float("nan"), dtype=torch.bfloat16, device="cuda")
+        G.gemm_tc(xw, w2, out, row_scale=(sums, parts, N, eps))
+        assert float((out.float() - y).abs().max()) < 2e-2 * max(1.0, float(y.abs().max()))
+        act = torch.full((tokens, N2 // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
+        G.gemm_tc(xw, w2, act, gated=True, row_scale=(sums, parts, N, eps))
+        want_act = torch.nn.functional.silu(y[:, 0::2]) * y[:, 1::2]
+        assert float((act.float() - want_act).abs().max()) < 2e-2 * max(1.0, float(want_act.abs().max()))
+    G.check_status()
