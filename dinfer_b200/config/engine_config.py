@@ -31,6 +31,11 @@ class EngineConfig:
     # full pages of computed tokens stay findable by the hash of their tokens and are shared by later
     # requests with the same beginning (off by default: with it on, freed pages are not the next ones used)
     enable_prefix_caching: bool = False
+    # RMSNorms between two decode products (steps of at most 32 rows, bfloat16): True = taken apart into the
+    # products' epilogues wherever the parts can (two launches per layer less), False = kernels of their own.
+    # Off by default: it pays where a step is bound by launch latency (small models, +4..9 % at the 0.6B shape
+    # up to batch 8) and costs where the products' longer tails show (-6 % at the 8B shape at batch 1).
+    split_norms: bool = False
     # "bfloat16" = what serving uses; "float32" = everything in true 32-bit
     dtype: str = "bfloat16"
     device: int = 0

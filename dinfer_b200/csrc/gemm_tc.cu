@@ -143,6 +143,10 @@ template <typename T> __device__ __forceinline__ T out_cast(float v);
 template <> __device__ __forceinline__ float out_cast<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 out_cast<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+__device__ __forceinline__ float norm_weight(const GemmParams& p, int n) {
+  return p.norm_w_f32 ? reinterpret_cast<const float*>(p.norm_w)[n]
+                      : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.norm_w)[n]);
+}
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
 
 template <int N_TILE> constexpr int tmem_cols() { return N_TILE <= 32 ? 32 : (N_TILE <= 64 ? 64 : (N_TILE <= 128 ? 128 : 256)); }
@@ -165,6 +169,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   __shared__ float s_rstd[64];                                // scaled mode: per token column of this tile
+  __shared__ float s_share[128];                              // [threads of a column][N_TILE]
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   constexpr uint32_t A_BYTES = TILE_M * BLOCK_K * 2, B_BYTES = N_TILE * BLOCK_K * 2;
   const uint32_t recv_base = smem_base + STAGES * (A_BYTES + B_BYTES);       // split-K receive buffer (SWAP only)
@@ -251,19 +256,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     pdl_enter();
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;                          // accumulator row = TMEM lane
-    if (SWAP && p.ss_in) {
+    if constexpr (SWAP) if (p.ss_in) {
       // scaled mode: while the products run, one thread per token column adds that row's partial sums of
       // squares (always in the same order) and keeps 1 / rms
+      // 128 / N_TILE threads share a column: thread k of them takes the parts k, k + that many, ... (loads in
+      // flight side by side), then the first adds the shares up in order
+      constexpr int TPC = 128 / N_TILE;
       const int e = (warp - 2) * 32 + lane;
-      if (e < N_TILE) {
-        float sum = 0.f;
-        if (b0 + e < p.tokens) {
-#pragma unroll 8
-          for (int q = 0; q < p.ss_parts; ++q) sum += __ldcg(p.ss_in + (int64_t)q * p.ss_stride + b0 + e);
+      const int c = e % N_TILE, k = e / N_TILE;
+      float sum = 0.f;
+      if (b0 + c < p.tokens) {
+        const float* src = p.ss_in + b0 + c;
+        for (int q0 = k; q0 < p.ss_parts; q0 += 16 * TPC) {
+          float v[16];
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const int q = q0 + u * TPC;
+            v[u] = q < p.ss_parts ? __ldcg(src + (int64_t)q * p.ss_stride) : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < 16; ++u) sum += v[u];
         }
-        s_rstd[e] = rsqrtf(sum * p.inv_size + p.eps);
       }
+      s_share[k * N_TILE + c] = sum;
       asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps
+      if (k == 0) {
+        float total = 0.f;
+#pragma unroll
+        for (int j = 0; j < TPC; ++j) total += s_share[j * N_TILE + c];
+        s_rstd[c] = rsqrtf(total * p.inv_size + p.eps);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
     }
     bool ok = true;
     if (n_kb > 0) {
@@ -347,38 +370,58 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (clustered) {
     __syncwarp();
     if (warp < 2) cluster_wait_acquire();                       // first phase (the epilogue warps have passed it)
+    const int rank = (int)cluster_ctarank();
+    const int rows_per = rows_per_cta(p.splits);
+    const int rows_mine = min(rows_per, TILE_M - rank * rows_per);
+    const int cols = min(N_TILE, p.tokens - b0);                // token columns that exist
+    // residual mode: what this thread will add to is requested before the barrier, not behind it
+    constexpr int PRE = 4;
+    float pre_r[PRE], pre_w[PRE];
+    if (p.resid) {
+#pragma unroll
+      for (int k = 0; k < PRE; ++k) {
+        const int i = threadIdx.x + k * NTHREADS;
+        pre_r[k] = 0.f; pre_w[k] = 0.f;
+        if (i < cols * rows_mine) {
+          const int c = i / rows_mine, rl = i - c * rows_mine;
+          const int n = a0 + rank * rows_per + rl;
+          if (n < p.N) { pre_r[k] = p.resid[(int64_t)(b0 + c) * p.ldr + n]; pre_w[k] = norm_weight(p, n); }
+        }
+      }
+    }
     cluster_arrive_release();
     cluster_wait_acquire();
     if (!s_abort) {
       OutT* out = reinterpret_cast<OutT*>(p.out);
-      const int rank = (int)cluster_ctarank();
-      const int rows_per = rows_per_cta(p.splits);
-      const int rows_mine = min(rows_per, TILE_M - rank * rows_per);
-      const int cols = min(N_TILE, p.tokens - b0);              // token columns that exist
       const float* recv = reinterpret_cast<const float*>(smem_dyn + (recv_base - smem_u32(smem_dyn)));
       if (p.resid) {
-        // residual mode: a warp per token column, lanes over this CTA's rows; the squares of the new
-        // residual are added per lane and then across the lanes in a fixed order
-        const int part = (int)blockIdx.x * p.splits + rank;    // every (part, token) is written by exactly one warp
-        for (int c = warp; c < cols; c += NTHREADS / 32) {
-          const int64_t t = b0 + c;
-          float sq = 0.f;
-          for (int rl = lane; rl < rows_mine; rl += 32) {
-            const int n = a0 + rank * rows_per + rl;
-            if (n < p.N) {
-              float acc = 0.f;
-              for (int s = 0; s < p.splits; ++s) acc += recv[(s * N_TILE + c) * rows_per + rl];
-              const float v = p.resid[t * p.ldr + n] + acc;
-              p.resid[t * p.ldr + n] = v;
-              const float w = p.norm_w_f32 ? reinterpret_cast<const float*>(p.norm_w)[n]
-                                           : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.norm_w)[n]);
-              out[t * p.ldc + n] = out_cast<OutT>(v * w);
-              sq += v * v;
-            }
+        // residual mode: the new residual, the next product's input, and the squares, which go through the
+        // (now free) first receive slot so that one thread per token column adds them up in a fixed order
+        float* sq = const_cast<float*>(recv);
+        const int total = cols * rows_mine;
+        int k = 0;
+        for (int i = threadIdx.x; i < total; i += NTHREADS, ++k) {
+          const int c = i / rows_mine, rl = i - c * rows_mine;
+          const int n = a0 + rank * rows_per + rl;
+          float acc = 0.f;
+          for (int s = 0; s < p.splits; ++s) acc += recv[(s * N_TILE + c) * rows_per + rl];
+          float v2 = 0.f;
+          if (n < p.N) {
+            const int64_t t = b0 + c;
+            const float r0 = k < PRE ? pre_r[k] : p.resid[t * p.ldr + n];
+            const float w = k < PRE ? pre_w[k] : norm_weight(p, n);
+            const float v = r0 + acc;
+            p.resid[t * p.ldr + n] = v;
+            out[t * p.ldc + n] = out_cast<OutT>(v * w);
+            v2 = v * v;
           }
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-          if (lane == 0) p.ss_out[(int64_t)part * p.ss_stride + t] = sq;
+          sq[c * rows_per + rl] = v2;
+        }
+        __syncthreads();
+        if ((int)threadIdx.x < cols) {
+          float sum = 0.f;
+          for (int rl = 0; rl < rows_mine; ++rl) sum += sq[threadIdx.x * rows_per + rl];
+          p.ss_out[(int64_t)((int)blockIdx.x * p.splits + rank) * p.ss_stride + b0 + threadIdx.x] = sum;
         }
       } else if (p.act) {                                       // (gate, up) pairs: rows_per is even (host)
         const int pairs_mine = rows_mine >> 1;

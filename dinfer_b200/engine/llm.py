@@ -53,7 +53,8 @@ class LLM:
                  max_num_seqs: int = 16, max_num_batched_tokens: int = 2048, num_blocks: Optional[int] = None,
                  block_size: int = 16, gpu_memory_utilization: float = 0.9,
                  decode_exempt_from_budget: bool = True, long_prefill_token_threshold: int = 0,
-                 enable_cuda_graph: bool = True, enable_prefix_caching: bool = False, device: int = 0):
+                 enable_cuda_graph: bool = True, enable_prefix_caching: bool = False,
+                 split_norms: bool = False, device: int = 0):
         """``model``: a folder with config.json and *.safetensors; or ``config`` (the config.json
         dictionary) with ``weights`` (any WeightSource, e.g. ``RandomSource``)."""
         self.engine_config = EngineConfig(
@@ -62,7 +63,8 @@ class LLM:
             gpu_memory_utilization=gpu_memory_utilization,
             decode_exempt_from_budget=decode_exempt_from_budget,
             long_prefill_token_threshold=long_prefill_token_threshold,
-            enable_cuda_graph=enable_cuda_graph, enable_prefix_caching=enable_prefix_caching, dtype=dtype,
+            enable_cuda_graph=enable_cuda_graph, enable_prefix_caching=enable_prefix_caching,
+            split_norms=split_norms, dtype=dtype,
             device=device)
         if model is not None:
             self.runner = ModelRunner.from_dir(model, self.engine_config)

@@ -155,6 +155,7 @@ class ModelRunner:
             logits = self._graph_step(entries, starts)
         else:
             ids, rows, ctx = self.plan.build(entries, starts)
+            ctx.split_norms = bool(self.engine.split_norms)
             logits = self.model.forward(ids, ctx, self.bindings, rows)
         for e, s in zip(entries, starts):
             m.advance(e.req_id, s + len(e.tokens), e.tokens if m.prefix_caching else None)
@@ -187,6 +188,13 @@ class ModelRunner:
         # the split count is part of the captured launch: fixed per bucket, for the longest context
         hkv = max([n.num_kv_heads for n in self.model.cache_needs() if isinstance(n, KvCacheNeed)] or [1])
         ctx.decode_splits = attention_ops.decode_splits(bucket, hkv, self.engine.max_model_len)
+        ctx.split_norms = bool(self.engine.split_norms)
+        rec = self._capture_one(ids, rows, ctx)
+        rec.update(dev=dev, splits=ctx.decode_splits, width=width, plan=DecodePlan(self.plan, bucket, width, dev))
+        self._graphs[bucket] = rec
+        return rec
+
+    def _capture_one(self, ids, rows, ctx):
         cur = torch.cuda.current_stream()
         side = torch.cuda.Stream()
         side.wait_stream(cur)
@@ -201,10 +209,7 @@ class ModelRunner:
             logits = self.model.forward(ids, ctx, self.bindings, rows)
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
-        rec = dict(graph=graph, dev=dev, logits=logits, splits=ctx.decode_splits, width=width,
-                   launches=kernel_lib.launch_count() - n0, plan=DecodePlan(self.plan, bucket, width, dev))
-        self._graphs[bucket] = rec
-        return rec
+        return dict(graph=graph, logits=logits, launches=kernel_lib.launch_count() - n0)
 
     def _graph_step(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
         B = len(entries)

@@ -73,6 +73,17 @@ class DecoderModel:
             out.append(None if e.cache_from is not None else self.blocks[e.layer].mixer.cache_need())
         return out
 
+    def can_split_norms(self, rows: int) -> bool:
+        """Whether some norm of the model can be taken apart for steps of this many rows."""
+        from ..parts.block import norm_comes_apart
+        order = [self.blocks[e.layer] for e in self.spec.schedule]
+        for i, b in enumerate(order):
+            if norm_comes_apart(b.mixer, b.feed_forward_norm, b.feed_forward, rows):
+                return True
+            if i + 1 < len(order) and norm_comes_apart(b.feed_forward, order[i + 1].mixer_norm, order[i + 1].mixer, rows):
+                return True
+        return False
+
     # ---- one step
     def forward(self, ids: torch.Tensor, ctx: StepContext, bindings: List[CacheBinding],
                 logits_rows: torch.Tensor) -> torch.Tensor:
@@ -82,8 +93,9 @@ class DecoderModel:
         x = torch.empty((T, s.hidden_size), dtype=torch.float32, device=ids.device)
         ops.embedding(ids, self.embedding, x)
         stream = ResidualStream(x)
-        for entry, binding in zip(s.schedule, bindings):
-            self.blocks[entry.layer].forward(stream, ctx, binding)
+        order = [self.blocks[e.layer] for e in s.schedule]
+        for i, (block, binding) in enumerate(zip(order, bindings)):
+            block.forward(stream, ctx, binding, next_block=order[i + 1] if i + 1 < len(order) else None)
         if logits_rows.numel() == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=ids.device)
         f = self.final_norm.forward(stream.x, delta=stream.pending, rows=logits_rows)

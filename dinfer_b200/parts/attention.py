@@ -82,7 +82,13 @@ class GQAttention(Mixer):
                 att += ["attention_decode", "attention_umma"]
         return ["qk_post"] + att + self.qkv.kernel_libraries() + self.o.kernel_libraries()
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+    def takes_half_normed(self, rows: int) -> bool:
+        return self.qkv.fuses_norm(rows, self.env.act_dtype)
+
+    def adds_into_residual(self, rows: int) -> bool:
+        return self.o.fuses_norm(rows, self.env.act_dtype)
+
+    def forward(self, x, ctx: StepContext, cache: CacheBinding, sink=None):
         H, Hkv, D = self.H, self.Hkv, self.D
         g = ctx.groups[cache.group]
         qkv = self.qkv(x)
@@ -103,6 +109,8 @@ class GQAttention(Mixer):
                             g.slot_mapping, g.block_size)
         out = torch.empty((qkv.shape[0], H * D), dtype=qkv.dtype, device=qkv.device)
         self.attend(qkv[:, :H * D], out, cache.kv, g, ctx)
+        if sink is not None:                               # (residual, the norm behind this mixer)
+            return self.o.into_residual(out, sink[0], sink[1])
         return self.o(out)
 
     def attend(self, q, out, kv, g, ctx: StepContext) -> None:

@@ -69,6 +69,7 @@ class StepContext:
     any_decode: bool = True            # some request brings exactly one token
     any_prefill: bool = True           # some request brings more than one
     decode_splits: int = 0             # > 0: the decode attention uses this many key splits (CUDA graphs)
+    split_norms: bool = False          # norms between two products may be taken apart (see HalfNormed)
     # host copies for parts written in plain torch (tests, toy parts)
     cu_seqlens_host: Sequence[int] = ()
     seq_lens_host: Sequence[int] = ()
@@ -113,7 +114,31 @@ class Part:
         return []
 
 
+@dataclass
+class HalfNormed:
+    """Rows on their way through an RMSNorm that is taken apart between two matrix products: ``xw`` is the
+    32-bit residual times the norm's weight, rounded to the activation type, and ``sums[p, t]`` are partial
+    sums of the squares of residual row t.  What is missing is the division by the row's root mean square,
+    ``rsqrt(sum_p sums[p, t] / size + eps)``; it commutes with a matrix product, so the product that
+    consumes the rows applies it to its result."""
+    xw: torch.Tensor
+    sums: torch.Tensor
+    parts: int
+    size: int
+    eps: float
+
+    @property
+    def shape(self):
+        return self.xw.shape
+
+
 class Mixer(Part):
+    """Optional beside ``forward``, for parts whose first and last operation can take an RMSNorm apart (see
+    ``HalfNormed``): ``takes_half_normed(rows) -> bool`` says that ``forward`` accepts a ``HalfNormed`` as
+    ``x`` for this many rows; ``adds_into_residual(rows) -> bool`` says that ``forward(..., sink=(residual,
+    norm))`` adds the part's output into the residual itself and returns the ``HalfNormed`` input of the
+    next part instead of the output.  A part without them always gets and gives plain tensors."""
+
     def cache_need(self):
         return None
 
@@ -122,6 +147,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    """The optional ``takes_half_normed`` / ``adds_into_residual`` of a ``Mixer`` hold here too."""
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
@@ -146,9 +173,13 @@ class PositionEncoding(Part):
 
 @dataclass
 class ResidualStream:
-    """The 32-bit residual ``x`` and a part's output that has not been added to it yet."""
+    """The 32-bit residual ``x`` and either a part's output that has not been added to it yet (``pending``) or
+    the input of the next block's mixer, already added and half normed by the part before (``half``, made for
+    the norm ``half_norm``)."""
     x: torch.Tensor
     pending: Optional[torch.Tensor] = None
+    half: Optional["HalfNormed"] = None
+    half_norm: Optional["Norm"] = None
 
 
 class Block:
@@ -159,7 +190,10 @@ class Block:
     def parts(self) -> List[Part]:
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
 
-    def forward(self, stream: ResidualStream, ctx: StepContext, cache: CacheBinding) -> None:
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache: CacheBinding,
+                next_block: Optional["Block"] = None) -> None:
+        """``next_block``: the block that runs after this one (None after the last), for arrangements that
+        hand their output to its first norm in another form than a pending tensor."""
         raise NotImplementedError
 
 

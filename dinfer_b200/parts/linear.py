@@ -19,6 +19,7 @@ import torch
 
 from ..kernels import gemm_ops, ops
 from ..kernels.lib import add_launches
+from .base import HalfNormed
 
 # rows up to which a bfloat16 product takes the swapped-operand tcgen05 kernel
 TC_MAX_DECODE_TOKENS = 32
@@ -41,16 +42,40 @@ class Linear:
         return (x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and x.shape[0] <= TC_MAX_DECODE_TOKENS
                 and self.out_features % 2 == 0 and gemm_ops.supported(x, self.weight))
 
-    def gated_pairs(self, x: torch.Tensor) -> torch.Tensor:
+    def fuses_norm(self, rows: int, act_dtype: torch.dtype) -> bool:
+        """Whether this product can take one half of an RMSNorm for ``rows`` rows (the decode product with its
+        residual or row-scale epilogue): bfloat16 throughout and rows that TMA can address."""
+        w = self.weight
+        return (act_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < rows <= TC_MAX_DECODE_TOKENS
+                and self.in_features % 8 == 0 and self.out_features % 8 == 0 and w.data_ptr() % 16 == 0)
+
+    def gated_pairs(self, x) -> torch.Tensor:
         """For a weight whose rows are (gate, up) pairs: ``silu(x gate_j^T) * (x up_j^T)``, [rows, out/2].
         One kernel where ``fuses_gate``, else the product followed by the gate kernel."""
+        if isinstance(x, HalfNormed):
+            act = torch.empty((x.shape[0], self.out_features // 2), dtype=x.xw.dtype, device=x.xw.device)
+            return gemm_ops.gemm_tc(x.xw, self.weight, act, gated=True, row_scale=(x.sums, x.parts, x.size, x.eps))
         act = torch.empty((x.shape[0], self.out_features // 2), dtype=x.dtype, device=x.device)
         if self.fuses_gate(x):
             return gemm_ops.gemm_tc(x, self.weight, act, gated=True)
         return ops.silu_mul(self(x), act, pairs=True)
 
+    def into_residual(self, x: torch.Tensor, residual: torch.Tensor, norm) -> HalfNormed:
+        """``residual += x W^T`` and the half-normed rows for the product behind ``norm`` (an RMSNorm over
+        ``out_features``), in one kernel.  Only where ``fuses_norm``."""
+        rows = x.shape[0]
+        parts = gemm_ops.residual_parts(rows, self.out_features, self.in_features)
+        sums = torch.empty((parts, rows), dtype=torch.float32, device=x.device)
+        xw = torch.empty((rows, self.out_features), dtype=x.dtype, device=x.device)
+        gemm_ops.gemm_tc(x, self.weight, xw, residual=residual, norm_weight=norm.weight, sums=sums)
+        return HalfNormed(xw, sums, parts, norm.size, norm.eps)
+
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if isinstance(x, HalfNormed):                      # the product finishes the norm (see HalfNormed)
+            if out is None:
+                out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or x.xw.dtype, device=x.xw.device)
+            return gemm_ops.gemm_tc(x.xw, self.weight, out, row_scale=(x.sums, x.parts, x.size, x.eps))
         out_dtype = out_dtype or x.dtype
         if out is None:
             out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype, device=x.device)

@@ -45,5 +45,14 @@ class SwiGLU(FeedForward):
     def kernel_libraries(self):
         return ["elementwise"] + self.gate_up.kernel_libraries() + self.down.kernel_libraries()
 
-    def forward(self, x: torch.Tensor, ctx=None) -> torch.Tensor:
-        return self.down(self.gate_up.gated_pairs(x))
+    def takes_half_normed(self, rows: int) -> bool:
+        return self.gate_up.fuses_norm(rows, self.env.act_dtype) and self.gate_up.out_features % 2 == 0
+
+    def adds_into_residual(self, rows: int) -> bool:
+        return self.down.fuses_norm(rows, self.env.act_dtype)
+
+    def forward(self, x, ctx=None, sink=None):
+        act = self.gate_up.gated_pairs(x)
+        if sink is not None:                               # (residual, the norm behind this feed-forward)
+            return self.down.into_residual(act, sink[0], sink[1])
+        return self.down(act)

@@ -206,7 +206,7 @@ class LocalReplay:
     """The same ``step`` interface as ``Replay`` on a ModelRunner of this process (for architectures
     that exist only in the test that registers them)."""
 
-    def __init__(self, model_dir: str, dtype: str, max_tokens: int, block_size: int = 16):
+    def __init__(self, model_dir: str, dtype: str, max_tokens: int, block_size: int = 16, **engine):
         from dinfer_b200.config.engine_config import EngineConfig
         from dinfer_b200.engine.runner import ModelRunner
         cfg = json.load(open(os.path.join(model_dir, "config.json")))
@@ -215,7 +215,7 @@ class LocalReplay:
         self.runner = ModelRunner.from_dir(model_dir, EngineConfig(
             max_model_len=min(n, cfg.get("max_position_embeddings", cfg.get("max_positions", n))), max_num_seqs=16,
             max_num_batched_tokens=n, num_blocks=n // block_size, block_size=block_size, dtype=dtype,
-            enable_cuda_graph=False))
+            enable_cuda_graph=False, **engine))
 
     def step(self, entries: List[dict], end: Sequence[str] = ()) -> Optional[np.ndarray]:
         from dinfer_b200.engine.batch import StepEntry

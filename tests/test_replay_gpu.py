@@ -94,3 +94,29 @@ def test_replay_at_the_benchmark_layer_sizes(tmp_path, dtype):
         assert rp.close() == 0
     print("8B layer sizes", dtype, worst)
     assert all(v <= H.TOLERANCE[dtype] for v in worst.values()), worst
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_replay_with_the_norms_taken_apart(model_dirs, name):
+    """The steps of at most 32 tokens (decoded tokens, small portions, mixed) with every norm between two
+    products taken apart into their epilogues (bfloat16; the engine otherwise chooses by measurement)."""
+    model_dir = model_dirs[(name, "bfloat16")]
+    cfg = H.CONFIGS[name]
+    rng = random.Random(4321 + ord(name))
+    lengths = {"a": 5, "b": 100, "c": 290}
+    tokens = {r: H.random_tokens(rng, n, cfg["vocab_size"]) for r, n in lengths.items()}
+    oracle = H.PlainOracle(model_dir)
+    want = {r: oracle.logits(t) for r, t in tokens.items()}
+    schedules = {"tail32": H.schedule_tail(lengths, 32), "chunks": H.schedule_chunks(lengths, rng),
+                 "mixed": H.schedule_mixed(lengths, rng, max_live=3, decode_tail=20)}
+    rp = H.LocalReplay(model_dir, "bfloat16", max(H.max_live_tokens(s) for s in schedules.values()), split_norms=True)
+    assert rp.runner.model.can_split_norms(8)
+    worst = {}
+    try:
+        for sname, steps in schedules.items():
+            got = H.run_schedule(rp, steps, tokens, tag=sname + "/")
+            worst[sname] = max(H.rel_err(got[r], want[r]) for r in tokens)
+    finally:
+        assert rp.close() == 0
+    print(name, "split norms", worst)
+    assert all(v <= H.TOLERANCE["bfloat16"] for v in worst.values()), worst
