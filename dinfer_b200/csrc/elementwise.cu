@@ -33,26 +33,28 @@ __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, in
   }
 }
 
-// bfloat16 in pairs, 8 inputs (16 bytes) -> 4 outputs per thread
+// bfloat16 in pairs: 16 inputs (two 16-byte loads) -> 8 outputs (one 16-byte store) per thread
 __global__ void silu_mul_pairs_bf16_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
-                                           int inter4, int64_t ldx, int inter) {
+                                           int inter8, int64_t ldx, int inter) {
   pdl_enter();
   const int t = blockIdx.x;
   const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)t * ldx);
-  uint2* o = reinterpret_cast<uint2*>(out + (int64_t)t * inter);
-  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter4; i += gridDim.y * blockDim.x) {
-    const uint4 a = src[i];
+  uint4* o = reinterpret_cast<uint4*>(out + (int64_t)t * inter);
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter8; i += gridDim.y * blockDim.x) {
+    const uint4 a = src[2 * i], b = src[2 * i + 1];
     const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-    float r[4];
+    const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+    float r[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float2 gu = __bfloat1622float2(pa[j]);
-      r[j] = gu.x / (1.f + expf(-gu.x)) * gu.y;
+      const float2 g0 = __bfloat1622float2(pa[j]), g1 = __bfloat1622float2(pb[j]);
+      r[j] = g0.x / (1.f + expf(-g0.x)) * g0.y;
+      r[4 + j] = g1.x / (1.f + expf(-g1.x)) * g1.y;
     }
-    uint2 w;
-    __nv_bfloat162 w0 = __floats2bfloat162_rn(r[0], r[1]), w1 = __floats2bfloat162_rn(r[2], r[3]);
-    w.x = *reinterpret_cast<unsigned*>(&w0);
-    w.y = *reinterpret_cast<unsigned*>(&w1);
+    uint4 w;
+    __nv_bfloat162* pw = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pw[j] = __floats2bfloat162_rn(r[2 * j], r[2 * j + 1]);
     o[i] = w;
   }
 }
@@ -113,12 +115,12 @@ DINFER_API int dinfer_silu_mul(const void* x, void* out, int T, int inter, int64
   const int threads = 256;
   int bx = (inter + threads - 1) / threads;
   if (bx > 64) bx = 64;
-  if (pairs && dtype == DINFER_BF16 && inter % 4 == 0 && ldx % 8 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) &&
-      !(reinterpret_cast<uintptr_t>(out) & 7)) {
-    int by = (inter / 4 + threads - 1) / threads;
-    if (by > 128) by = 128;
+  if (pairs && dtype == DINFER_BF16 && inter % 8 == 0 && ldx % 8 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) &&
+      !(reinterpret_cast<uintptr_t>(out) & 15)) {
+    int by = (inter / 8 + threads - 1) / threads;
+    if (by > 64) by = 64;
     launch_pdl(silu_mul_pairs_bf16_kernel, dim3(T, by), dim3(threads), 0, stream, (const __nv_bfloat16*)x,
-               (__nv_bfloat16*)out, inter / 4, ldx, inter);
+               (__nv_bfloat16*)out, inter / 8, ldx, inter);
     return cuda_status("silu_mul");
   }
   if (!pairs && dtype == DINFER_BF16 && inter % 8 == 0 && ldx % 8 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) &&
