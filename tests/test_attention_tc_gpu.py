@@ -53,7 +53,7 @@ def test_decode_splits(splits):
 @pytest.mark.parametrize("H,Hkv,D,bs", [(8, 2, 128, 16), (32, 8, 128, 16), (3, 3, 128, 4), (8, 1, 64, 32),
                                         (16, 1, 128, 16), (12, 1, 64, 1), (10, 2, 64, 8)])
 @pytest.mark.parametrize("window", [None, 100])
-@pytest.mark.parametrize("splits", [1, 4, 7, 16])
+@pytest.mark.parametrize("splits", [1, 2, 3, 4, 5, 6, 7, 9, 12, 16])     # every cluster size the engine can pick
 def test_decode_kernel(H, Hkv, D, bs, window, splits):
     """The decode kernel (keys on the tile's rows, splits folded in the kernel) against the plain
     formula; a prompt portion in the batch must be left alone; two launches in a row (the splits fold
