@@ -120,7 +120,11 @@ qk_post_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ positio
 }
 
 // Fast shape: bfloat16/f32 with D = 32 * EPL and the rotation over the whole head.  A lane owns EPL
-// consecutive elements in registers; its rotation partner (D/2 away) sits 16 lanes across.
+// consecutive elements in registers; its rotation partner (D/2 away) sits 16 lanes across.  A warp takes
+// HPW consecutive heads of one token and requests all of them before it works on the first, so that
+// enough bytes are in flight for prompts (one 8-byte load per lane and head is not).
+constexpr int HPW = 4;
+
 template <typename TA, typename TW, int EPL>
 __global__ void __launch_bounds__(WARPS * 32)
 qk_post_lanes_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ positions,
@@ -134,42 +138,53 @@ qk_post_lanes_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ p
   pdl_enter();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y * WARPS + warp;
-  if (head >= H + 2 * Hkv) return;
-  const int kind = head < H ? 0 : (head < H + Hkv ? 1 : 2);
-  TA* x = qkv + (int64_t)t * ld + (int64_t)head * D + lane * EPL;
-  const Vec in = *reinterpret_cast<const Vec*>(x);
-  float v[EPL];
-  float ss = 0.f;
+  const int head0 = (blockIdx.y * WARPS + warp) * HPW;
+  const int heads = H + 2 * Hkv;
+  if (head0 >= heads) return;
+  TA* row = qkv + (int64_t)t * ld + lane * EPL;
+  Vec in[HPW];
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) { v[j] = to_f32<TA>(in.v[j]); ss += v[j] * v[j]; }
-  const TW* w = kind == 0 ? q_weight : (kind == 1 ? k_weight : nullptr);
-  if (w) {
-    ss = warp_sum(ss);
-    const float rinv = rsqrtf(ss / (float)D + eps);
-    const WVec wv = *reinterpret_cast<const WVec*>(w + lane * EPL);
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) v[j] = v[j] * rinv * to_f32<TW>(wv.v[j]);
-  }
-  const bool rotate = cos_sin != nullptr && kind != 2;
-  if (rotate) {
+  for (int u = 0; u < HPW; ++u)
+    if (head0 + u < heads) in[u] = *reinterpret_cast<const Vec*>(row + (int64_t)(head0 + u) * D);
+  FVec c, sn;
+  const bool has_table = cos_sin != nullptr;
+  if (has_table) {
     const float* cs = cos_sin + (int64_t)positions[t] * D;
-    const int i = (lane & 15) * EPL;                        // index of the pair inside the half
-    const FVec c = *reinterpret_cast<const FVec*>(cs + i);
-    const FVec s = *reinterpret_cast<const FVec*>(cs + D / 2 + i);
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
-      v[j] = lane < 16 ? v[j] * c.v[j] - other * s.v[j] : v[j] * c.v[j] + other * s.v[j];
-    }
+    const int i = (lane & 15) * EPL;                          // index of the pair inside the half
+    c = *reinterpret_cast<const FVec*>(cs + i);
+    sn = *reinterpret_cast<const FVec*>(cs + D / 2 + i);
   }
-  Vec out;
+  const int slot = cache ? slots[t] : -1;
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) out.v[j] = from_f32<TA>(v[j]);
-  if (kind != 2 && (w || rotate)) *reinterpret_cast<Vec*>(x) = out;
-  if (cache && kind != 0) {
-    const int slot = slots[t];
-    if (slot >= 0) {
+  for (int u = 0; u < HPW; ++u) {
+    const int head = head0 + u;
+    if (head >= heads) break;
+    const int kind = head < H ? 0 : (head < H + Hkv ? 1 : 2);
+    float v[EPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) { v[j] = to_f32<TA>(in[u].v[j]); ss += v[j] * v[j]; }
+    const TW* w = kind == 0 ? q_weight : (kind == 1 ? k_weight : nullptr);
+    if (w) {
+      ss = warp_sum(ss);
+      const float rinv = rsqrtf(ss / (float)D + eps);
+      const WVec wv = *reinterpret_cast<const WVec*>(w + lane * EPL);
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) v[j] = v[j] * rinv * to_f32<TW>(wv.v[j]);
+    }
+    const bool rotate = has_table && kind != 2;
+    if (rotate) {
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+        v[j] = lane < 16 ? v[j] * c.v[j] - other * sn.v[j] : v[j] * c.v[j] + other * sn.v[j];
+      }
+    }
+    Vec out;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) out.v[j] = from_f32<TA>(v[j]);
+    if (kind != 2 && (w || rotate)) *reinterpret_cast<Vec*>(row + (int64_t)head * D) = out;
+    if (kind != 0 && slot >= 0) {
       const int64_t blk = slot / block_size, off = slot % block_size;
       const int hk = kind == 1 ? head - H : head - H - Hkv;
       TA* dst = cache + ((((blk * 2 + (kind - 1)) * Hkv + hk) * block_size + off) * (int64_t)D) + lane * EPL;
@@ -218,7 +233,8 @@ DINFER_API int dinfer_qk_post(void* qkv, int64_t ld, const int* positions, const
                            !(reinterpret_cast<uintptr_t>(cache) & 31) && !(reinterpret_cast<uintptr_t>(q_weight) & 31) &&
                            !(reinterpret_cast<uintptr_t>(k_weight) & 31) && !(reinterpret_cast<uintptr_t>(cos_sin) & 31);
       if (aligned && (!cos_sin || rot == D) && (D == 32 || D == 64 || D == 128 || D == 256)) {
-        launch_lanes<TA, TW>(grid, stream, (TA*)qkv, ld, positions, (const TW*)q_weight, (const TW*)k_weight, eps,
+        const dim3 lanes_grid(T, (heads + WARPS * HPW - 1) / (WARPS * HPW));
+        launch_lanes<TA, TW>(lanes_grid, stream, (TA*)qkv, ld, positions, (const TW*)q_weight, (const TW*)k_weight, eps,
                              cos_sin, (TA*)cache, slots, block_size, H, Hkv, D);
         return cuda_status("qk_post");
       }
