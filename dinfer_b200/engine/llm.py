@@ -13,20 +13,18 @@ sample -> update, until every request has finished.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Dict, Hashable, List, Optional, Sequence, Union
 
-import torch
 
 from ..config.engine_config import EngineConfig
-from ..config.model_config import read_config_json
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
-from ..weights.loader import SafetensorsSource, WeightSource
+from ..weights.loader import WeightSource
 from .batch import StepEntry
-from .request import FinishReason, Request
+from .request import Request
 from .runner import ModelRunner
-from .scheduler import Scheduler, SchedulerOutput
+from .scheduler import Scheduler
 
 
 @dataclass

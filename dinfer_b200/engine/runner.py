@@ -12,9 +12,8 @@ models/qwen3/src/model.rs:684-832), with sampling kept out of it.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
-from typing import Any, Dict, Hashable, List, Optional, Sequence
+from typing import Any, Dict, Hashable, List, Sequence
 
 import torch
 

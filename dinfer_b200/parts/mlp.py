@@ -10,7 +10,6 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..kernels import ops
 from .base import FEED_FORWARDS, FeedForward
 from .linear import Linear
 from .spec import TensorDecl

@@ -15,7 +15,7 @@ models/qwen3/src/model.rs:147-153,494).
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Dict, List, Sequence, Tuple
 
 import torch
 

@@ -1,7 +1,6 @@
 """Each part alone against its plain formula, and the generality of the assembly: a toy mixer with
 state of its own, a windowed attention layer, a layer that runs twice and a layer that reads another
 layer's cache are registered and built here, in the test, and stepped through the unchanged engine."""
-import math
 import random
 
 import pytest

@@ -1,6 +1,5 @@
 """The plain implementation against the reference's own torch-CPU formulas (outputs committed under
 tests/golden/, made by tests/golden/make_golden.py) and against itself (no GPU)."""
-import math
 import os
 
 import numpy as np

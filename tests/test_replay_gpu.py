@@ -4,7 +4,6 @@ four live requests with so few pages that they are used again.  In 32-bit and in
 tiny configurations that differ in every size."""
 import random
 
-import numpy as np
 import pytest
 import torch
 
