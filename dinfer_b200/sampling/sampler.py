@@ -65,10 +65,33 @@ def _u64(x: int) -> int:
 
 
 class Sampler:
-    """Builds the per-row columns on the host, uploads them in one copy and launches the kernels."""
+    """Builds the per-row columns on the host in pinned memory, uploads them in one copy and launches the
+    kernels."""
+
+    RING = 4
 
     def __init__(self, device):
         self.device = device
+        self._host: List[torch.Tensor] = []
+        self._dev: List[torch.Tensor] = []
+        self._events: List[Optional[torch.cuda.Event]] = []
+        self._turn = 0
+        self._rows = 0
+
+    def _staging(self, rows: int):
+        """Pinned and device buffers of 32 bytes a row (a small ring: a buffer is rewritten only after its
+        last copy has left it)."""
+        if rows > self._rows:
+            self._rows = max(64, 2 * rows)
+            pin = torch.device(self.device).type == "cuda"
+            self._host = [torch.empty(32 * self._rows, dtype=torch.uint8, pin_memory=pin) for _ in range(self.RING)]
+            self._dev = [torch.empty(32 * self._rows, dtype=torch.uint8, device=self.device) for _ in range(self.RING)]
+            self._events = [None] * self.RING
+        k = self._turn
+        self._turn = (k + 1) % self.RING
+        if self._events[k] is not None:
+            self._events[k].synchronize()
+        return k
 
     def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                  num_generated: Sequence[int], histories: Optional[Sequence[tuple]] = None) -> torch.Tensor:
@@ -94,15 +117,24 @@ class Sampler:
                 torch.tensor([p.repetition_penalty for p in params], dtype=torch.float32, device=dev),
                 torch.tensor([p.frequency_penalty for p in params], dtype=torch.float32, device=dev),
                 torch.tensor([p.presence_penalty for p in params], dtype=torch.float32, device=dev))
-        f32 = np.empty((3, R), dtype=np.float32)
-        i64 = np.empty((2, R), dtype=np.int64)
-        i32 = np.empty(R, dtype=np.int32)
+        # columns of one packed buffer: seeds, offsets (int64), temperature, top_p, min_p (float32), top_k (int32)
+        k = self._staging(R)
+        cap = self._rows
+        host = self._host[k].numpy()
+        i64 = host[:16 * cap].view(np.int64).reshape(2, cap)
+        f32 = host[16 * cap:28 * cap].view(np.float32).reshape(3, cap)
+        i32 = host[28 * cap:32 * cap].view(np.int32)
         for i, p in enumerate(params):
             f32[0, i], f32[1, i], f32[2, i] = p.temperature, p.top_p, p.min_p
             i32[i] = p.top_k
             i64[0, i], i64[1, i] = _u64(seeds[i]), _u64(num_generated[i])
-        dev = self.device
-        f32d = torch.from_numpy(f32).to(dev, non_blocking=True)
-        i64d = torch.from_numpy(i64).to(dev, non_blocking=True)
-        i32d = torch.from_numpy(i32).to(dev, non_blocking=True)
-        return sample(logits, f32d[0], i64d[0], i64d[1], top_k=i32d, top_p=f32d[1], min_p=f32d[2])
+        dev = self._dev[k]
+        dev.copy_(self._host[k], non_blocking=True)
+        if dev.is_cuda:
+            ev = self._events[k] or torch.cuda.Event()
+            ev.record()
+            self._events[k] = ev
+        d64 = dev[:16 * cap].view(torch.int64).view(2, cap)
+        d32f = dev[16 * cap:28 * cap].view(torch.float32).view(3, cap)
+        d32i = dev[28 * cap:32 * cap].view(torch.int32)
+        return sample(logits, d32f[0, :R], d64[0, :R], d64[1, :R], top_k=d32i[:R], top_p=d32f[1, :R], min_p=d32f[2, :R])
