@@ -103,6 +103,17 @@ def gemm_prompt(s, tokens, tflops):
         flops = 2.0 * tokens * N * K
         print(f"tokens {tokens} {name:8s} N {N:6d} K {K:6d} | tcgen05 {t_own:7.1f} us {flops / t_own * 1e-6:7.1f} TFLOP/s"
               f" | library {t_lib:7.1f} us {flops / t_lib * 1e-6:7.1f} TFLOP/s | at peak {flops / tflops * 1e-6:6.1f} us", flush=True)
+        if name == "gate_up":                                  # with the gate: one kernel against product + gate kernel
+            from dinfer_b200.kernels import ops as O
+            act = torch.empty(tokens, N // 2, dtype=torch.bfloat16, device="cuda")
+            t_own = graph_time_us(lambda i: G.gemm_tc(x, ws[i % len(ws)], act, gated=True), 2 * len(ws))
+
+            def lib_then_gate(i):
+                torch.mm(x, ws[i % len(ws)].t(), out=out)
+                O.silu_mul(out, act, pairs=True)
+            t_lib = graph_time_us(lib_then_gate, 2 * len(ws))
+            print(f"tokens {tokens} {name:8s} with the gate          | tcgen05 {t_own:7.1f} us (one kernel)"
+                  f"      | library {t_lib:7.1f} us (product, then the gate kernel)", flush=True)
         del ws
     G.check_status()
 

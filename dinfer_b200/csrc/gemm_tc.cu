@@ -1,19 +1,18 @@
 // C[M, N] = A[M, K] * W[N, K]^T in bfloat16 on the 5th-generation tensor cores:
 // TMA (cp.async.bulk.tensor, 128-byte swizzle) stages K-major operand tiles in shared memory,
-// one elected thread issues tcgen05.mma (cta_group::1, kind::f16, 128 x N_TILE x 16) with the f32
-// accumulator in tensor memory, tcgen05.commit hands shared-memory stages back to the producer, and
-// four epilogue warps read the accumulator with tcgen05.ld.  No multicast; a cluster only for split K.
+// one elected thread issues tcgen05.mma (kind::f16) with the f32 accumulator in tensor memory,
+// tcgen05.commit hands shared-memory stages back to the producer, and four epilogue warps read the
+// accumulator with tcgen05.ld.  No load is multicast.
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocation + MMA issue,
 // warps 2..5 = epilogue (TMEM lane quarter = warp index mod 4).
 //
-// Two orientations share the kernel:
-//   * prompts:  the 128 tile rows are tokens, the N_TILE columns are weight rows;
-//   * decoding (few tokens): operands swapped, the 128 tile rows are WEIGHT rows and the (16..64)
-//     columns are tokens, so that a handful of tokens still fills the tensor-core tile and each CTA
-//     streams its weight rows from HBM exactly once; K may be split across up to 8 CTAs, which then
-//     form a thread-block cluster: every CTA owns a share of the tile's 128 rows, the others store
-//     their partial sums of those rows into its shared memory (st.shared::cluster), and after one
+// Two kernels:
+//   * decoding (at most 64 tokens), gemm_tc_kernel: the 128 tile rows are WEIGHT rows and the (16..64)
+//     columns are tokens (cta_group::1, 128 x N_TILE x 16), so that a handful of tokens still fills the
+//     tensor-core tile and each CTA streams its weight rows from HBM exactly once; K may be split across up to
+//     8 CTAs, which then form a thread-block cluster: every CTA owns a share of the tile's 128 rows, the others
+//     store their partial sums of those rows into its shared memory (st.shared::cluster), and after one
 //     cluster barrier each CTA adds its share up, always in split order, and writes it.  With `act` the
 //     weight rows are (gate, up) pairs and the same epilogue writes silu(gate) * up, half as wide, so
 //     the gated feed-forward needs no kernel between its two products.  Two more epilogues take the
@@ -21,6 +20,8 @@
 //     the 32-bit residual, writes the new residual times the norm's weight (rounded) for the next product
 //     and leaves each row's partial sums of squares; `ss_in` multiplies the next product's result by
 //     rsqrt(mean of squares + eps) of its row, which commutes with the product.
+//   * prompts (more tokens), gemm_tc_pair_kernel: the tile rows are tokens; two SMs share a 256 x 256 tile
+//     (cta_group::2), persistent over tiles, with the same gated epilogue (see the kernel).
 //
 // Every wait on an mbarrier is bounded: on time-out the kernel records a code in a status word,
 // lets copies in flight land, frees its tensor memory and returns (the host reads the status word).
@@ -148,6 +149,9 @@ __device__ __forceinline__ float norm_weight(const GemmParams& p, int n) {
                       : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.norm_w)[n]);
 }
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
+// the prompt epilogue's: fast exponential and division, as the reference's gate kernel has them
+// (crates/kernels/cuda/common.cuh:55); the quotient is 0 where 1 + e^-g passes 2^126, as is its limit
+__device__ __forceinline__ float silu_mul_fast(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 template <int N_TILE> constexpr int tmem_cols() { return N_TILE <= 32 ? 32 : (N_TILE <= 64 ? 64 : (N_TILE <= 128 ? 128 : 256)); }
 // Rows of the tile that one CTA of a split-K cluster owns, and the floats of its receive buffer
@@ -161,7 +165,7 @@ template <int N_TILE, int STAGES> constexpr size_t gemm_smem_bytes(bool with_rec
 }
 
 // grid: (tiles of the 128-row operand, tiles of the N_TILE-row operand, K splits)
-template <int N_TILE, int STAGES, bool SWAP, typename OutT>
+template <int N_TILE, int STAGES, typename OutT>
 __global__ void __launch_bounds__(NTHREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
   extern __shared__ unsigned char smem_dyn[];
@@ -172,7 +176,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __shared__ float s_share[128];                              // [threads of a column][N_TILE]
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   constexpr uint32_t A_BYTES = TILE_M * BLOCK_K * 2, B_BYTES = N_TILE * BLOCK_K * 2;
-  const uint32_t recv_base = smem_base + STAGES * (A_BYTES + B_BYTES);       // split-K receive buffer (SWAP only)
+  const uint32_t recv_base = smem_base + STAGES * (A_BYTES + B_BYTES);       // split-K receive buffer
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int a0 = blockIdx.x * TILE_M, b0 = blockIdx.y * N_TILE;
   const int total_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
@@ -182,7 +186,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   pdl_launch_dependents();
   // split K: the CTAs of a tile are one cluster.  First phase of its barrier: every CTA has started,
   // so its shared memory may be written from the others (waited for just before those stores).
-  const bool clustered = SWAP && (p.splits > 1 || p.resid != nullptr);   // the residual epilogue lives in the fold
+  const bool clustered = p.splits > 1 || p.resid != nullptr;   // the residual epilogue lives in the fold
   if (clustered) cluster_arrive_relaxed();
 
   if (threadIdx.x == 0) {
@@ -212,15 +216,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t bar = smem_u32(&full_bar[i]);
         mbar_expect_tx(bar, A_BYTES + B_BYTES);
         const uint32_t sa = smem_base + i * (A_BYTES + B_BYTES);
-        if (SWAP) tma_load_2d(sa, &map_a, (kb_begin + i) * BLOCK_K, a0, bar);
-        else tma_load_2d(sa + A_BYTES, &map_b, (kb_begin + i) * BLOCK_K, b0, bar);
+        tma_load_2d(sa, &map_a, (kb_begin + i) * BLOCK_K, a0, bar);
       }
       pdl_wait();
       for (int i = 0; i < ahead; ++i) {
         const uint32_t bar = smem_u32(&full_bar[i]);
         const uint32_t sa = smem_base + i * (A_BYTES + B_BYTES);
-        if (SWAP) tma_load_2d(sa + A_BYTES, &map_b, (kb_begin + i) * BLOCK_K, b0, bar);
-        else tma_load_2d(sa, &map_a, (kb_begin + i) * BLOCK_K, a0, bar);
+        tma_load_2d(sa + A_BYTES, &map_b, (kb_begin + i) * BLOCK_K, b0, bar);
       }
       for (int i = ahead; i < n_kb; ++i) {
         const int s = i % STAGES;
@@ -256,7 +258,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     pdl_enter();
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;                          // accumulator row = TMEM lane
-    if constexpr (SWAP) if (p.ss_in) {
+    if (p.ss_in) {
       // scaled mode: while the products run, one thread per token column adds that row's partial sums of
       // squares (always in the same order) and keeps 1 / rms
       // 128 / N_TILE threads share a column: thread k of them takes the parts k, k + that many, ... (loads in
@@ -311,28 +313,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = 0u;
         }
-        if (!SWAP) {
-          const int t = a0 + r;
-          if (t < p.tokens) {
-            OutT* dst = out + (int64_t)t * p.ldc + b0 + c0;
-            if (b0 + c0 + 16 <= p.N && (p.ldc % 8 == 0) && sizeof(OutT) == 2) {
-              uint4 w0, w1;
-              __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&w0);
-              __nv_bfloat162* h1 = reinterpret_cast<__nv_bfloat162*>(&w1);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                h0[j] = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-                h1[j] = __floats2bfloat162_rn(__uint_as_float(v[8 + 2 * j]), __uint_as_float(v[8 + 2 * j + 1]));
-              }
-              reinterpret_cast<uint4*>(dst)[0] = w0;
-              reinterpret_cast<uint4*>(dst)[1] = w1;
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (b0 + c0 + j < p.N) dst[j] = out_cast<OutT>(__uint_as_float(v[j]));
-            }
-          }
-        } else {
+        {
           const int n = a0 + r;                                 // weight row; the columns are tokens
           if (!clustered && p.ss_in) {
 #pragma unroll
@@ -460,6 +441,224 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// ---- prompts, two SMs on one tile: the CTAs of a cluster of two share a 256 x 256 output tile
+// (tcgen05.mma.cta_group::2).  Each CTA stages its own 128 token rows and its own 128 of the 256 weight rows,
+// so a stage is 32 KB instead of 48 and every byte of the weight tile is fetched by one SM of the pair only;
+// the leader (cluster rank 0) issues the MMAs for both, which leave 128 accumulator rows in each CTA's tensor
+// memory.  TMA completions of both CTAs count on the leader's barrier; tcgen05.commit hands stages and
+// accumulators back to both CTAs at once.  No load is multicast.
+// CTAs are persistent: a pair walks over tiles (token tile fastest, so that pairs running at the same time read the
+// same few weight tiles from L2), the shared-memory ring runs on across tiles, and the accumulator is double-buffered
+// in tensor memory (2 x 256 columns): the epilogue warps drain tile i while the MMAs of tile i + 1 run.  With GATED
+// the weight rows are (gate, up) pairs and the epilogue writes silu(gate) * up, half as wide.
+// (Narrower tiles were measured and are slower at every shape: the kernel is bound by the traffic from L2 into
+// shared memory, which grows as the tile narrows.)
+constexpr int NT = 256;                                                       // columns of the pair's tile
+constexpr int C_STAGES = 6, C_ACC_BUFS = 2, C_TMEM_COLS = NT * C_ACC_BUFS;
+constexpr uint32_t C_A_BYTES = TILE_M * BLOCK_K * 2, C_B_BYTES = (NT / 2) * BLOCK_K * 2;   // this CTA's rows of both operands
+constexpr size_t C_SMEM_BYTES = (size_t)C_STAGES * (C_A_BYTES + C_B_BYTES) + 1024;
+
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint64_t start = 0;
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((i & 255) == 255) {
+      const uint64_t now = global_ns();
+      if (start == 0) start = now;
+      else if (now - start > 2000000000ull) return false;
+    }
+  }
+  return false;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// the completion is counted on a barrier that may live in the other CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {     // arrives on this barrier in both CTAs
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <typename OutT, bool GATED>
+__global__ void __launch_bounds__(NTHREADS)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t full_bar[C_STAGES], empty_bar[C_STAGES], acc_full_bar[C_ACC_BUFS], acc_empty_bar[C_ACC_BUFS];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();                      // 0 = leader
+  const int m_tiles = (p.tokens + 255) / 256, n_tiles = (p.N + NT - 1) / NT;
+  const int tiles = m_tiles * n_tiles;
+  const int total_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  pdl_enter();
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    for (int s = 0; s < C_STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+    for (int b = 0; b < C_ACC_BUFS; ++b) { mbar_init(smem_u32(&acc_full_bar[b]), 1); mbar_init(smem_u32(&acc_empty_bar[b]), 8); }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(C_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_arrive_release();                                     // both CTAs' barriers and tensor memory are ready
+  cluster_wait_acquire();
+  tcgen05_fence_after();
+  const uint32_t tmem = s_tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {                                            // ---- TMA producer (both CTAs)
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < tiles && ok; tile += pairs) {
+        const int m0 = (tile % m_tiles) * 256 + (int)rank * 128, n0 = (tile / m_tiles) * NT + (int)rank * (NT / 2);
+        for (int kb = 0; kb < total_kb; ++kb, ++it) {
+          const uint32_t s = it % C_STAGES;
+          if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / C_STAGES) & 1) ^ 1)) { s_abort = 1; atomicExch(p.status, 1); ok = false; break; }
+          if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * (C_A_BYTES + C_B_BYTES));
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
+          const uint32_t sa = smem_base + s * (C_A_BYTES + C_B_BYTES);
+          tma_load_2d_pair(sa, &map_a, kb * BLOCK_K, m0, bar);
+          tma_load_2d_pair(sa + C_A_BYTES, &map_b, kb * BLOCK_K, n0, bar);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {                               // ---- MMA issue (the leader, for both CTAs)
+      constexpr uint32_t idesc = instr_desc_bf16(256, NT);
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = pair; tile < tiles && ok; tile += pairs, ++lt) {
+        const uint32_t b = lt % C_ACC_BUFS;
+        if (!mbar_wait_cluster(smem_u32(&acc_empty_bar[b]), ((lt / C_ACC_BUFS) & 1) ^ 1)) { s_abort = 1; atomicExch(p.status, 2); break; }
+        tcgen05_fence_after();
+        const uint32_t acc = tmem + b * NT;
+        for (int kb = 0; kb < total_kb; ++kb, ++it) {
+          const uint32_t s = it % C_STAGES;
+          if (!mbar_wait_cluster(smem_u32(&full_bar[s]), (it / C_STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 2); ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_base + s * (C_A_BYTES + C_B_BYTES);
+          const uint64_t da = smem_desc_k_sw128(sa), db = smem_desc_k_sw128(sa + C_A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+            tcgen05_mma_f16_pair(acc, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          tcgen05_commit_pair(smem_u32(&empty_bar[s]));
+        }
+        if (ok) tcgen05_commit_pair(smem_u32(&acc_full_bar[b]));
+      }
+    }
+  } else {                                                      // ---- epilogue (both CTAs, 128 rows each)
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    OutT* out = reinterpret_cast<OutT*>(p.out);
+    const bool vec = sizeof(OutT) == 2 && (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    const int n_out = GATED ? p.N / 2 : p.N;
+    uint32_t lt = 0;
+    for (int tile = pair; tile < tiles; tile += pairs, ++lt) {
+      const uint32_t b = lt % C_ACC_BUFS;
+      const int m0 = (tile % m_tiles) * 256 + (int)rank * 128, n0 = (tile / m_tiles) * NT;
+      if (total_kb > 0) {
+        if (!mbar_wait(smem_u32(&acc_full_bar[b]), (lt / C_ACC_BUFS) & 1)) {
+          if (lane == 0) { s_abort = 1; atomicExch(p.status, 3); }
+          break;
+        }
+        tcgen05_fence_after();
+      }
+      const int t = m0 + r;
+      const uint32_t acc = tmem + ((uint32_t)(quarter * 32) << 16) + b * NT;
+#pragma unroll 1
+      for (int c0 = 0; c0 < NT; c0 += 32) {
+        uint32_t v[2][16];
+        if (total_kb > 0) {
+          tmem_ld_32x32b_x16(acc + c0, v[0]);
+          tmem_ld_32x32b_x16(acc + c0 + 16, v[1]);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { v[0][j] = 0u; v[1][j] = 0u; }
+        }
+        if (t >= p.tokens) continue;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if constexpr (GATED) {
+            const int o0 = (n0 + c0 + h * 16) >> 1;
+            OutT* dst = out + (int64_t)t * p.ldc + o0;
+            float y[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] = silu_mul_fast(__uint_as_float(v[h][2 * j]), __uint_as_float(v[h][2 * j + 1]));
+            if (vec && o0 + 8 <= n_out) {
+              uint4 w0;
+              __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&w0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) h0[j] = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+              *reinterpret_cast<uint4*>(dst) = w0;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (o0 + j < n_out) dst[j] = out_cast<OutT>(y[j]);
+            }
+          } else {
+            const int o0 = n0 + c0 + h * 16;
+            OutT* dst = out + (int64_t)t * p.ldc + o0;
+            if (vec && o0 + 16 <= n_out) {
+              uint4 w0, w1;
+              __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&w0);
+              __nv_bfloat162* h1 = reinterpret_cast<__nv_bfloat162*>(&w1);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                h0[j] = __floats2bfloat162_rn(__uint_as_float(v[h][2 * j]), __uint_as_float(v[h][2 * j + 1]));
+                h1[j] = __floats2bfloat162_rn(__uint_as_float(v[h][8 + 2 * j]), __uint_as_float(v[h][8 + 2 * j + 1]));
+              }
+              reinterpret_cast<uint4*>(dst)[0] = w0;
+              reinterpret_cast<uint4*>(dst)[1] = w1;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (o0 + j < n_out) dst[j] = out_cast<OutT>(__uint_as_float(v[h][j]));
+            }
+          }
+        }
+      }
+      // read: the leader may let the MMAs of a later tile overwrite this accumulator in both CTAs
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&acc_empty_bar[b]), 0));
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_arrive_release();                                     // neither CTA leaves while the other may still signal it
+  cluster_wait_acquire();
+  if (warp == 1) {
+    if (s_abort) {
+      for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C_TMEM_COLS) : "memory");
+  }
+}
+
 // ---- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -491,17 +690,57 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_
   return 0;
 }
 
-template <int N_TILE, int STAGES, bool SWAP, typename OutT>
+template <int N_TILE, int STAGES, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
-  auto k = gemm_tc_kernel<N_TILE, STAGES, SWAP, OutT>;
-  const size_t sm = gemm_smem_bytes<N_TILE, STAGES>(SWAP && (p.splits > 1 || p.resid != nullptr));
+  auto k = gemm_tc_kernel<N_TILE, STAGES, OutT>;
+  const size_t sm = gemm_smem_bytes<N_TILE, STAGES>(p.splits > 1 || p.resid != nullptr);
   static bool opted = false;
   if (!opted) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<N_TILE, STAGES>(SWAP));
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<N_TILE, STAGES>(true));
     if (e != cudaSuccess) return refuse((int)e, "gemm_tc: shared memory opt-in failed: %s", cudaGetErrorString(e));
     opted = true;
   }
-  cudaError_t e = launch_pdl_cluster(k, grid, dim3(NTHREADS), dim3(1, 1, SWAP ? p.splits : 1), sm, stream, ma, mb, p);
+  cudaError_t e = launch_pdl_cluster(k, grid, dim3(NTHREADS), dim3(1, 1, p.splits), sm, stream, ma, mb, p);
+  if (e != cudaSuccess) return refuse((int)e, "gemm_tc: launch failed: %s", cudaGetErrorString(e));
+  return cuda_status("gemm_tc");
+}
+
+int num_sms() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
+// clusters of two CTAs of `kernel` that the device runs at a time
+int cluster_pairs_resident(const void* kernel, size_t smem) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * num_sms()); cfg.blockDim = dim3(NTHREADS); cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return n;
+}
+
+template <typename OutT, bool GATED>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
+  auto k = gemm_tc_pair_kernel<OutT, GATED>;
+  static int max_pairs = 0;
+  if (!max_pairs) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C_SMEM_BYTES);
+    if (e != cudaSuccess) return refuse((int)e, "gemm_tc: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    const int n = cluster_pairs_resident(reinterpret_cast<const void*>(k), C_SMEM_BYTES);
+    if (n <= 0) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: no cluster of two CTAs fits this device");
+    max_pairs = n;
+  }
+  const int tiles = ((p.tokens + 255) / 256) * ((p.N + NT - 1) / NT);
+  dim3 grid(2 * (tiles < max_pairs ? tiles : max_pairs));
+  cudaError_t e = launch_pdl_cluster(k, grid, dim3(NTHREADS), dim3(2, 1, 1), C_SMEM_BYTES, stream, ma, mb, p);
   if (e != cudaSuccess) return refuse((int)e, "gemm_tc: launch failed: %s", cudaGetErrorString(e));
   return cuda_status("gemm_tc");
 }
@@ -512,8 +751,8 @@ DINFER_DEFINE_LAST_ERROR()
 
 // x [tokens, K] (row stride ldx), w [N, K] (row stride ldw), both bf16; out [tokens, N] (row stride ldc)
 // bf16 (out_f32 = 0) or f32.  tokens <= 64: decode orientation with `splits` K splits (at most 8: the
-// CTAs of a tile form a cluster).  More tokens: prompt orientation, splits ignored.
-// act = 1 (decode orientation only, N even): the rows of w are (gate, up) pairs and out is [tokens, N / 2],
+// CTAs of a tile form a cluster).  More tokens: prompt orientation (two SMs on a tile), splits ignored.
+// act = 1 (N even): the rows of w are (gate, up) pairs and out is [tokens, N / 2],
 // out[t, j] = silu(x w_{2j}) * (x w_{2j+1}).
 // status: a device int that a kernel sets non-zero when one of its bounded waits ran out.
 //
@@ -532,8 +771,8 @@ DINFER_API int dinfer_gemm_tc_fused(const void* x, int64_t ldx, const void* w, i
     return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: K and the row strides must be multiples of 8 and the bases 16-byte aligned "
                   "(TMA); K=%d ldx=%lld ldw=%lld", K, (long long)ldx, (long long)ldw);
   if (!status) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: a status word is required");
-  if (act && (tokens > 64 || (N & 1)))
-    return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: the gated epilogue takes at most 64 tokens and an even N (tokens=%d N=%d)", tokens, N);
+  if (act && (N & 1))
+    return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: the gated epilogue takes an even N (N=%d)", N);
   if ((resid || ss_in) && tokens > 64)
     return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: the norm epilogues take at most 64 tokens, got %d", tokens);
   if (resid && (act || !norm_w || !ss_out || ss_stride < tokens))
@@ -563,8 +802,8 @@ DINFER_API int dinfer_gemm_tc_fused(const void* x, int64_t ldx, const void* w, i
     if ((rc = make_map(&ma, w, N, K, ldw, TILE_M))) return rc;
     if ((rc = make_map(&mb, x, tokens, K, ldx, n_tile))) return rc;
     dim3 grid((N + TILE_M - 1) / TILE_M, (tokens + n_tile - 1) / n_tile, p.splits);
-#define GO(NT_, ST_) (out_f32 ? launch<NT_, ST_, true, float>(ma, mb, p, grid, stream) \
-                              : launch<NT_, ST_, true, __nv_bfloat16>(ma, mb, p, grid, stream))
+#define GO(NT_, ST_) (out_f32 ? launch<NT_, ST_, float>(ma, mb, p, grid, stream) \
+                              : launch<NT_, ST_, __nv_bfloat16>(ma, mb, p, grid, stream))
     // Four stages leave room for two CTAs of a split launch on an SM; a launch with more CTAs than that
     // takes three stages, of which three CTAs fit (as many bytes in flight, one wave instead of two).
     if (n_tile == 16) return (p.splits > 1 && (int64_t)grid.x * grid.y * grid.z > 264) ? GO(16, 3) : GO(16, 4);
@@ -575,10 +814,9 @@ DINFER_API int dinfer_gemm_tc_fused(const void* x, int64_t ldx, const void* w, i
   p.k_blocks_per_split = total_kb;
   p.splits = 1;
   if ((rc = make_map(&ma, x, tokens, K, ldx, TILE_M))) return rc;
-  if ((rc = make_map(&mb, w, N, K, ldw, 256))) return rc;
-  dim3 grid((tokens + TILE_M - 1) / TILE_M, (N + 255) / 256, 1);
-  return out_f32 ? launch<256, 4, false, float>(ma, mb, p, grid, stream)
-                 : launch<256, 4, false, __nv_bfloat16>(ma, mb, p, grid, stream);
+  if ((rc = make_map(&mb, w, N, K, ldw, NT / 2))) return rc;
+  if (act) return out_f32 ? launch_pair<float, true>(ma, mb, p, stream) : launch_pair<__nv_bfloat16, true>(ma, mb, p, stream);
+  return out_f32 ? launch_pair<float, false>(ma, mb, p, stream) : launch_pair<__nv_bfloat16, false>(ma, mb, p, stream);
 }
 
 DINFER_API int dinfer_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldc,

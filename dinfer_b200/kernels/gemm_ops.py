@@ -64,8 +64,9 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optiona
             sums: Optional[torch.Tensor] = None, row_scale=None) -> torch.Tensor:
     """out[tokens, N] = x[tokens, K] @ w[N, K]^T.  out: bfloat16 or float32, last axis contiguous.
 
+    ``gated`` (any number of rows): the rows of w are (gate, up) pairs, out is [tokens, N / 2],
+    out[t, j] = silu(x w_2j) * (x w_2j+1).
     Epilogues of the decode orientation (at most ``DECODE_MAX_TOKENS`` rows):
-      ``gated``: the rows of w are (gate, up) pairs, out is [tokens, N / 2], out[t, j] = silu(x w_2j) * (x w_2j+1);
       ``residual`` [tokens, N] f32 with ``norm_weight`` [N] and ``sums`` [parts, stride >= tokens] f32
         (``parts = residual_parts(...)``): the product is added into the residual, out gets the new
         residual times the norm weight, ``sums[p, t]`` the squares of row t summed over part p;
@@ -76,9 +77,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optiona
         raise KernelError("gemm_tc: bfloat16 operands with K and row strides multiples of 8 and 16-byte aligned bases")
     tokens, K = x.shape
     N = w.shape[0]
-    fused = gated or residual is not None or row_scale is not None
-    if fused and tokens > DECODE_MAX_TOKENS:
-        raise KernelError("gemm_tc: the fused epilogues take at most 64 rows")
+    if (residual is not None or row_scale is not None) and tokens > DECODE_MAX_TOKENS:
+        raise KernelError("gemm_tc: the norm epilogues take at most 64 rows")
     if gated and (N % 2 or residual is not None):
         raise KernelError("gemm_tc: the gated epilogue needs an even number of weight rows and no residual")
     if w.shape[1] != K or out.shape != (tokens, N // 2 if gated else N) or out.stride(1) != 1 \
@@ -127,3 +127,4 @@ def residual_parts(tokens: int, N: int, K: int, splits: Optional[int] = None) ->
         splits = decode_splits(tokens, N, K)
     lib, f = _fn("gemm_tc", "dinfer_gemm_tc_parts", [c_int, c_int, c_int, c_int])
     return int(f(tokens, N, K, int(splits)))
+

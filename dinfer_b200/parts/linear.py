@@ -9,7 +9,9 @@ Which product runs follows from the dtypes and the number of rows at hand:
     memory exactly once (where the reference uses its own small-M kernels,
     crates/kernels/cuda/gemm_small_m.cu:148-285);
   * bfloat16 with more rows (prompts): the library product, where the reference's engine uses
-    cuBLASLt (crates/kernels/src/gemm.rs:649-690), or the tcgen05 kernel when ``PROMPT_BACKEND`` says so.
+    cuBLASLt (crates/kernels/src/gemm.rs:649-690), or the tcgen05 kernel when ``PROMPT_BACKEND`` says so;
+    the gated pair product of the feed-forward is this package's tcgen05 kernel at every number of rows, with
+    silu(gate) * up in its epilogue.
 """
 from __future__ import annotations
 
@@ -38,8 +40,9 @@ class Linear:
         return ["gemm_f32"] if self.weight.dtype == torch.float32 else ["gemm_tc"]
 
     def fuses_gate(self, x: torch.Tensor) -> bool:
-        """Whether ``gated_pairs`` runs as one kernel for these rows (the decode product)."""
-        return (x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and x.shape[0] <= TC_MAX_DECODE_TOKENS
+        """Whether ``gated_pairs`` runs as one kernel for these rows: the tcgen05 product with the gate in its
+        epilogue, at any number of rows (with the gate kernel saved it is ahead of the library for prompts too)."""
+        return (x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16
                 and self.out_features % 2 == 0 and gemm_ops.supported(x, self.weight))
 
     def fuses_norm(self, rows: int, act_dtype: torch.dtype) -> bool:

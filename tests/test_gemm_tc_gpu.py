@@ -38,7 +38,7 @@ def test_decode_orientation(tokens, N, K):
 
 
 @pytest.mark.parametrize("tokens,N,K", [(65, 256, 64), (128, 512, 128), (200, 300, 96), (300, 1000, 520),
-                                        (2048, 6144, 4096), (1000, 4096, 12288)])
+                                        (2048, 6144, 4096), (1000, 4096, 12288), (4096, 6000, 264), (129, 40000, 72)])
 def test_prompt_orientation(tokens, N, K):
     from dinfer_b200.kernels import gemm_ops as G
     x, w = operands(tokens, N, K, tokens + N + K)
@@ -104,6 +104,24 @@ def test_gated_epilogue(tokens, N, K):
         got = out.float()
         assert torch.isfinite(got).all()
         assert float((got - want).abs().max()) < 2e-2 * max(1.0, float(want.abs().max())), splits
+    G.check_status()
+
+
+@pytest.mark.parametrize("tokens,N,K", [(65, 256, 64), (300, 518, 96), (200, 1004, 520), (2048, 24576, 4096),
+                                        (1111, 6144, 1024)])
+@pytest.mark.parametrize("f32_out", [False, True])
+def test_gated_epilogue_of_the_prompt_orientation(tokens, N, K, f32_out):
+    """More than 64 rows: persistent pairs of CTAs, each over several tiles; the gate runs in their epilogue."""
+    from dinfer_b200.kernels import gemm_ops as G
+    x, w = operands(tokens, N, K, tokens + N + K)
+    y = x.float() @ w.float().T
+    want = torch.nn.functional.silu(y[:, 0::2]) * y[:, 1::2]
+    out = torch.full((tokens, N // 2), float("nan"), dtype=torch.float32 if f32_out else torch.bfloat16, device="cuda")
+    G.gemm_tc(x, w, out, gated=True)
+    got = out.float()
+    assert torch.isfinite(got).all()
+    tol = (1e-3 if f32_out else 2e-2) * max(1.0, float(want.abs().max()))
+    assert float((got - want).abs().max()) < tol
     G.check_status()
 
 
