@@ -451,8 +451,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // same few weight tiles from L2), the shared-memory ring runs on across tiles, and the accumulator is double-buffered
 // in tensor memory (2 x 256 columns): the epilogue warps drain tile i while the MMAs of tile i + 1 run.  With GATED
 // the weight rows are (gate, up) pairs and the epilogue writes silu(gate) * up, half as wide.
-// (Narrower tiles were measured and are slower at every shape: the kernel is bound by the traffic from L2 into
-// shared memory, which grows as the tile narrows.)
+// (Narrower tiles, chosen so that the last round of tiles leaves fewer SMs idle, were measured and are slower at
+// every shape.)
 constexpr int NT = 256;                                                       // columns of the pair's tile
 constexpr int C_STAGES = 6, C_ACC_BUFS = 2, C_TMEM_COLS = NT * C_ACC_BUFS;
 constexpr uint32_t C_A_BYTES = TILE_M * BLOCK_K * 2, C_B_BYTES = (NT / 2) * BLOCK_K * 2;   // this CTA's rows of both operands
