@@ -36,6 +36,11 @@ class EngineConfig:
     # Off by default: it pays where a step is bound by launch latency (small models, +4..9 % at the 0.6B shape
     # up to batch 8) and costs where the products' longer tails show (-6 % at the 8B shape at batch 1).
     split_norms: bool = False
+    # the next step is scheduled and launched while the last one still runs; the host reads a step's tokens one
+    # step late (the reference's ASYNC_SCHED, on by default there too: crates/core/src/engine.rs:153,822).
+    # Steps with penalties (which need the token history on the host) and the prefix cache (which hashes
+    # token values) run one at a time whatever this says.
+    async_scheduling: bool = True
     # "bfloat16" = what serving uses; "float32" = everything in true 32-bit
     dtype: str = "bfloat16"
     device: int = 0

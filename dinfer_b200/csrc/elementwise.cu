@@ -1,6 +1,9 @@
 // Embedding gather into the 32-bit residual stream, and the SwiGLU gate.
 // Counterparts in the reference: crates/kernels/cuda/activation.cu:121-129 (embedding, an id out of
 // range reads row 0) and :80-99 (silu_and_mul).
+// A negative id -(r + 1) names row r of `prev`, the tokens the previous step sampled, which are still on
+// the device when this step is launched before the host has read them (the reference's asynchronous
+// scheduling feeds its placeholders the same way: crates/core/src/sched/mod.rs:645-668).
 #include "common.cuh"
 
 using namespace dinfer;
@@ -8,11 +11,12 @@ using namespace dinfer;
 namespace {
 
 template <typename TW>
-__global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
-                                 float* __restrict__ out, int h, int vocab) {
+__global__ void embedding_kernel(const int* __restrict__ ids, const int* __restrict__ prev, int prev_rows,
+                                 const TW* __restrict__ table, float* __restrict__ out, int h, int vocab) {
   pdl_enter();
   const int t = blockIdx.x;
   int id = ids[t];
+  if (id < 0 && prev != nullptr && -id - 1 < prev_rows) id = prev[-id - 1];
   if (id < 0 || id >= vocab) id = 0;
   const TW* row = table + (int64_t)id * h;
   float* o = out + (int64_t)t * h;
@@ -92,15 +96,15 @@ __global__ void cast_kernel(const TS* __restrict__ src, TD* __restrict__ dst, in
 
 DINFER_DEFINE_LAST_ERROR()
 
-// ids [T] int32; table [vocab, h]; out [T, h] f32.
-DINFER_API int dinfer_embedding(const int* ids, const void* table, float* out, int T, int h, int vocab,
-                                int table_dtype, cudaStream_t stream) {
+// ids [T] int32; table [vocab, h]; out [T, h] f32; prev [prev_rows] int32 or null (see the head of the file).
+DINFER_API int dinfer_embedding(const int* ids, const int* prev, int prev_rows, const void* table, float* out, int T,
+                                int h, int vocab, int table_dtype, cudaStream_t stream) {
   if (T < 0 || h <= 0 || vocab <= 0) return refuse(DINFER_BAD_ARGUMENT, "embedding: bad sizes T=%d h=%d vocab=%d", T, h, vocab);
   if (T == 0) return 0;
   int threads = (h + 31) / 32 * 32;
   if (threads > 256) threads = 256;
   DINFER_DISPATCH_DTYPE(table_dtype, TW, {
-    launch_pdl(embedding_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, (const TW*)table, out, h, vocab);
+    launch_pdl(embedding_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, prev, prev_rows, (const TW*)table, out, h, vocab);
     return cuda_status("embedding");
   });
   return 0;

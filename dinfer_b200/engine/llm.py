@@ -9,13 +9,17 @@ The options carry the names of the reference's ``dinfer serve`` flags / ``ServeO
 (bins/dinfer/src/main.rs:30-131, models/qwen3/src/service.rs:43-140).  The reference itself has no
 in-process API (its only entry is the HTTP server); the loop below is its engine loop
 (crates/core/src/engine.rs:538-728) without the thread and the channels: schedule -> step ->
-sample -> update, until every request has finished.
+sample -> update, until every request has finished.  With ``async_scheduling`` (the default) one step
+is kept in flight: step n + 1 is scheduled and launched while step n runs, its requests' newest tokens
+taken on the device from step n's sampling, and only then are step n's tokens read and its requests
+updated; ``step()`` then returns what finished one launch earlier.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
 from typing import Any, Dict, Hashable, List, Optional, Sequence, Union
 
+import torch
 
 from ..config.engine_config import EngineConfig
 from ..sampling.params import SamplingParams
@@ -45,6 +49,17 @@ class EngineStats:
     prefix_hit_tokens: int = 0        # prompt tokens found in the prefix cache (not run again)
 
 
+class _InFlight:
+    """A step whose device work is queued and whose tokens the host has not read."""
+
+    def __init__(self, plan, samplers: List[Request], row: Dict[Hashable, int]):
+        self.plan = plan
+        self.samplers = samplers
+        self.row = row                      # request -> its row in the step's sampled tokens
+        self.host: Optional[torch.Tensor] = None
+        self.event: Optional[torch.cuda.Event] = None
+
+
 class LLM:
     def __init__(self, model: Optional[str] = None, *, config: Optional[Dict[str, Any]] = None,
                  weights: Optional[WeightSource] = None, dtype: str = "bfloat16", max_model_len: int = 4096,
@@ -52,7 +67,7 @@ class LLM:
                  block_size: int = 16, gpu_memory_utilization: float = 0.9,
                  decode_exempt_from_budget: bool = True, long_prefill_token_threshold: int = 0,
                  enable_cuda_graph: bool = True, enable_prefix_caching: bool = False,
-                 split_norms: bool = False, device: int = 0):
+                 split_norms: bool = False, async_scheduling: bool = True, device: int = 0):
         """``model``: a folder with config.json and *.safetensors; or ``config`` (the config.json
         dictionary) with ``weights`` (any WeightSource, e.g. ``RandomSource``)."""
         self.engine_config = EngineConfig(
@@ -62,7 +77,7 @@ class LLM:
             decode_exempt_from_budget=decode_exempt_from_budget,
             long_prefill_token_threshold=long_prefill_token_threshold,
             enable_cuda_graph=enable_cuda_graph, enable_prefix_caching=enable_prefix_caching,
-            split_norms=split_norms, dtype=dtype,
+            split_norms=split_norms, async_scheduling=async_scheduling, dtype=dtype,
             device=device)
         if model is not None:
             self.runner = ModelRunner.from_dir(model, self.engine_config)
@@ -75,6 +90,14 @@ class LLM:
         self.stats = EngineStats()
         self._next_id = 0
         self._requests: Dict[Hashable, Request] = {}
+        # scheduling ahead: the step in flight, and pinned buffers its tokens are copied to (two: one being
+        # read by the host while the next step's copy is queued)
+        self._ahead = bool(self.engine_config.async_scheduling) and not self.engine_config.enable_prefix_caching
+        self._inflight: Optional[_InFlight] = None
+        self._num_penalized = 0
+        rows = self.runner.sampled.numel()
+        self._tok_host = [torch.empty(rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._tok_turn = 0
 
     # ---- requests
     def add_request(self, prompt_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -90,53 +113,92 @@ class LLM:
         req = Request(req_id, list(prompt_ids), params or SamplingParams())
         self.scheduler.add_request(req)
         self._requests[req_id] = req
+        self._num_penalized += int(req.params.has_penalties)
         return req_id
 
     def abort(self, req_id: Hashable) -> None:
         self.scheduler.abort(req_id)
-        self._requests.pop(req_id, None)
+        self._forget(req_id)
+
+    def _forget(self, req_id: Hashable) -> None:
+        req = self._requests.pop(req_id, None)
+        if req is not None:
+            self._num_penalized -= int(req.params.has_penalties)
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.has_unfinished() or self._inflight is not None
 
     # ---- one engine step
     def step(self) -> List[RequestOutput]:
-        """Schedule, run, sample, update.  Returns the requests that finished in this step."""
-        plan = self.scheduler.schedule()
+        """Schedule, run, sample, update.  Returns the requests known to have finished: those of this step,
+        or, when scheduling ahead, those of the step launched by the call before."""
+        # penalties need every earlier token on the host: such steps run one at a time
+        ahead = self._ahead and self._num_penalized == 0
+        finished: List[Request] = []
+        if not ahead and self._inflight is not None:
+            finished += self._collect()
+        plan = self.scheduler.schedule(lookahead=ahead)
         self._last_scheduled = len(plan.scheduled)
-        finished = list(plan.finished)
-        if plan.scheduled:
-            entries, samplers = [], []
-            for s in plan.scheduled:
-                r = s.request
-                entries.append(StepEntry(r.req_id, r.tokens(s.start, s.start + s.num_tokens),
-                                         [s.num_tokens - 1] if s.samples else []))
-                if s.samples:
-                    samplers.append(r)
-                self.stats.prompt_tokens += max(0, min(s.start + s.num_tokens, len(r.prompt_ids)) - s.start)
-            logits = self.runner.step(entries)
-            sampled: Dict[Hashable, int] = {}
-            if samplers:
-                toks = self.sampler(
-                    logits, [r.params for r in samplers], [r.seed for r in samplers],
-                    [len(r.output_ids) for r in samplers],
-                    [(r.prompt_ids, r.output_ids) for r in samplers])
-                host = toks.cpu().tolist()                   # the step's one device->host read
-                sampled = {r.req_id: t for r, t in zip(samplers, host)}
-                self.stats.generated_tokens += len(host)
-            finished += self.scheduler.update(plan, sampled)
-            self.stats.steps += 1
-            if self.stats.steps % 256 == 0:
-                self.runner.check_device_status()
+        finished += plan.finished
+        launched = self._launch(plan) if plan.scheduled else None
+        if self._inflight is not None:              # the step before this one: its tokens have arrived by now
+            finished += self._collect()
+        self._inflight = launched
+        if launched is not None and not ahead:
+            finished += self._collect()
         self.stats.preemptions = self.scheduler.num_preemptions
         self.stats.prefix_hit_tokens = self.runner.manager.prefix_hits
         outs = []
         for r in finished:
-            self._requests.pop(r.req_id, None)
+            self._forget(r.req_id)
             outs.append(RequestOutput(r.req_id, r.prompt_ids, r.output_ids,
                                       r.finish_reason.value if r.finish_reason else "abort",
                                       r.num_preemptions))
         return outs
+
+    def _launch(self, plan) -> "_InFlight":
+        """Queue the step's device work and the copy of its sampled tokens to the host; wait for nothing."""
+        prev_row = self._inflight.row if self._inflight is not None else {}
+        entries, samplers, generated = [], [], []
+        for s in plan.scheduled:
+            r = s.request
+            end = s.start + s.num_tokens
+            if end > r.num_tokens:                  # its newest token is still on the device: named by its row
+                toks = r.tokens(s.start, r.num_tokens) + [-(prev_row[r.req_id] + 1)]
+            else:
+                toks = r.tokens(s.start, end)
+            entries.append(StepEntry(r.req_id, toks, [s.num_tokens - 1] if s.samples else []))
+            if s.samples:
+                samplers.append(r)
+                generated.append(s.num_generated)
+            self.stats.prompt_tokens += max(0, min(end, len(r.prompt_ids)) - s.start)
+        logits = self.runner.step(entries, placeholders=True)
+        flight = _InFlight(plan, samplers, {r.req_id: i for i, r in enumerate(samplers)})
+        if samplers:
+            out = self.runner.sampled[:len(samplers)]
+            self.sampler(logits, [r.params for r in samplers], [r.seed for r in samplers], generated,
+                         [(r.prompt_ids, r.output_ids) for r in samplers], out=out)
+            k = self._tok_turn
+            self._tok_turn = 1 - k
+            flight.host = self._tok_host[k]
+            flight.host[:len(samplers)].copy_(out, non_blocking=True)     # the step's one device->host read
+            flight.event = torch.cuda.Event()
+            flight.event.record()
+        self.stats.steps += 1
+        if self.stats.steps % 256 == 0:
+            self.runner.check_device_status()
+        return flight
+
+    def _collect(self) -> List[Request]:
+        """Wait for the tokens of the step in flight and update its requests."""
+        flight, self._inflight = self._inflight, None
+        sampled: Dict[Hashable, int] = {}
+        if flight.samplers:
+            flight.event.synchronize()
+            host = flight.host[:len(flight.samplers)].tolist()
+            sampled = {r.req_id: t for r, t in zip(flight.samplers, host)}
+            self.stats.generated_tokens += len(host)
+        return self.scheduler.update(flight.plan, sampled)
 
     # ---- whole generation
     def generate(self, prompt_token_ids: Sequence[Sequence[int]],

@@ -30,6 +30,7 @@ class Request:
     seed: int = 0
     output_ids: List[int] = field(default_factory=list)
     num_computed: int = 0              # tokens whose keys are in the cache (or scheduled to be)
+    num_placeholders: int = 0          # output tokens sampled on the device that the host has not read yet
     status: RequestStatus = RequestStatus.WAITING
     finish_reason: Optional[FinishReason] = None
     num_preemptions: int = 0

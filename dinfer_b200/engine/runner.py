@@ -60,6 +60,9 @@ class ModelRunner:
                                 max_tokens=engine.max_num_batched_tokens + engine.max_num_seqs,
                                 max_reqs=engine.max_num_seqs,
                                 max_blocks=self.max_blocks_per_seq)
+        # the tokens the last step sampled stay here (a fixed address, so that captured graphs can read it):
+        # a step launched before the host has read them names them by row (see StepEntry.tokens)
+        self.sampled = torch.zeros(max(1, engine.max_num_seqs), dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self._init_graphs()
 
@@ -126,7 +129,9 @@ class ModelRunner:
                 self.bindings.append(CacheBinding())
 
     # ---- one step
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], placeholders: bool = False) -> torch.Tensor:
+        """``placeholders``: a token id -(r + 1) is allowed and stands for ``self.sampled[r]``, the token that
+        row r of the previous step's sampling produced (still on the device)."""
         if not entries:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         m = self.manager
@@ -138,7 +143,7 @@ class ModelRunner:
             seen.add(e.req_id)
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.req_id!r} brings no token")
-            if min(e.tokens) < 0 or max(e.tokens) >= self.spec.vocab_size:
+            if min(e.tokens) < (-self.sampled.numel() if placeholders else 0) or max(e.tokens) >= self.spec.vocab_size:
                 raise ValueError(f"request {e.req_id!r}: a token id is outside the vocabulary "
                                  f"[0, {self.spec.vocab_size})")
             start = m.num_computed(e.req_id) if e.req_id in m else 0
@@ -155,6 +160,7 @@ class ModelRunner:
         else:
             ids, rows, ctx = self.plan.build(entries, starts)
             ctx.split_norms = bool(self.engine.split_norms)
+            ctx.prev_tokens = self.sampled
             logits = self.model.forward(ids, ctx, self.bindings, rows)
         for e, s in zip(entries, starts):
             m.advance(e.req_id, s + len(e.tokens), e.tokens if m.prefix_caching else None)
@@ -188,6 +194,7 @@ class ModelRunner:
         hkv = max([n.num_kv_heads for n in self.model.cache_needs() if isinstance(n, KvCacheNeed)] or [1])
         ctx.decode_splits = attention_ops.decode_splits(bucket, hkv, self.engine.max_model_len)
         ctx.split_norms = bool(self.engine.split_norms)
+        ctx.prev_tokens = self.sampled
         rec = self._capture_one(ids, rows, ctx)
         rec.update(dev=dev, splits=ctx.decode_splits, width=width, plan=DecodePlan(self.plan, bucket, width, dev))
         self._graphs[bucket] = rec

@@ -8,8 +8,16 @@ token 0 later; a request never preempts itself while others run (it sits the ste
 request that alone does not fit is finished with ``length``.  Nothing is admitted in a step that
 preempted.  This is the policy of the reference's scheduler (crates/core/src/sched/mod.rs:318-644
 for schedule, :646-680 for the bookkeeping after it and preemption, :687-828 for the update and
-the stop check), without its asynchronous placeholders and speculative tokens.  With the prefix
-cache on, a request that enters takes over the cached pages of its beginning first.
+the stop check), without its speculative tokens.  With the prefix cache on, a request that enters
+takes over the cached pages of its beginning first.
+
+Scheduling ahead (the reference's asynchronous scheduling, :645-668 and :700-760): ``schedule(lookahead=True)``
+is called while the previous step still runs.  A request that samples in a step is then counted as one
+token longer at once (``num_placeholders``: sampled on the device, not yet read), so the next step can
+decode that token before the host knows it; ``update`` fills the value in when it arrives.  A request
+whose token in flight is certainly its last (``max_tokens``, ``max_model_len``) is not scheduled again;
+one that stops on an end-of-sequence token has run one step in vain, whose result is dropped; one that
+was preempted with a token in flight still gets that token appended.
 
 Pure host code: it owns the queues and asks the cache manager for pages; it never touches the GPU.
 """
@@ -30,6 +38,7 @@ class ScheduledRequest:
     start: int            # tokens already in the cache
     num_tokens: int       # tokens run in this step
     samples: bool         # the step's last row yields the request's next token
+    num_generated: int = 0    # output tokens the request had before this step, those in flight included
 
 
 @dataclass
@@ -81,7 +90,7 @@ class Scheduler:
         return None
 
     # ---- one step's decisions
-    def schedule(self) -> SchedulerOutput:
+    def schedule(self, lookahead: bool = False) -> SchedulerOutput:
         cfg = self.config
         out = SchedulerOutput()
         budget = cfg.max_num_batched_tokens
@@ -89,7 +98,12 @@ class Scheduler:
         i = 0
         while i < len(self.running):
             req = self.running[i]
-            num_new = req.num_tokens - req.num_computed
+            ahead = req.num_placeholders
+            if ahead and (len(req.output_ids) + ahead >= req.params.max_tokens
+                          or req.num_tokens + ahead >= cfg.max_model_len):
+                i += 1                          # the token in flight is its last: nothing more to run
+                continue
+            num_new = req.num_tokens + ahead - req.num_computed
             is_decode = num_new == 1 and req.num_computed > 0
             if threshold > 0:
                 num_new = min(num_new, threshold)
@@ -120,7 +134,8 @@ class Scheduler:
                 i += 1
                 continue
             out.scheduled.append(ScheduledRequest(req, req.num_computed, num_new,
-                                                  req.num_computed + num_new == req.num_tokens))
+                                                  req.num_computed + num_new == req.num_tokens + ahead,
+                                                  len(req.output_ids) + ahead))
             if not (is_decode and cfg.decode_exempt_from_budget):
                 budget -= num_new
             i += 1
@@ -146,17 +161,21 @@ class Scheduler:
                 req.status = RequestStatus.RUNNING
                 self.running.append(req)
                 out.scheduled.append(ScheduledRequest(req, req.num_computed, num_new,
-                                                      req.num_computed + num_new == req.num_tokens))
+                                                      req.num_computed + num_new == req.num_tokens,
+                                                      len(req.output_ids)))
                 budget -= num_new
 
         for s in out.scheduled:                 # the cache will hold these once the step has run
             s.request.num_computed += s.num_tokens
+            if lookahead and s.samples:
+                s.request.num_placeholders += 1
         return out
 
     def _preempt(self, req: Request) -> None:
         if req.req_id in self.manager:
             self.manager.free(req.req_id)
         req.num_computed = 0
+        req.num_placeholders = 0                # a token in flight is still appended when it arrives (update)
         req.status = RequestStatus.WAITING
         req.num_preemptions += 1
         self.num_preemptions += 1
@@ -174,13 +193,19 @@ class Scheduler:
         done = []
         for s in step.scheduled:
             req = s.request
-            if not s.samples or req.finished or req.status != RequestStatus.RUNNING:
-                continue
+            if not s.samples or req.finished:
+                continue                        # finished meanwhile: what a step ahead computed for it is dropped
             tok = int(sampled[req.req_id])
             req.output_ids.append(tok)
             reason = self._check_stop(req, tok)
+            if req.status == RequestStatus.RUNNING:
+                if req.num_placeholders > 0:
+                    req.num_placeholders -= 1
+                if reason is not None:
+                    self.running.remove(req)
+            elif reason is not None:            # preempted while this token was in flight, and it ends the request
+                self.waiting.remove(req)
             if reason is not None:
-                self.running.remove(req)
                 self._finish(req, reason)
                 done.append(req)
         return done

@@ -31,17 +31,23 @@ def _rows_contiguous(t: torch.Tensor, what: str) -> None:
         raise KernelError(f"{what}: last axis must be contiguous")
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, :] = table[ids[t], :] into the f32 residual stream."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+              prev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, :] = table[ids[t], :] into the f32 residual stream.  With ``prev`` (int32 [rows], the tokens
+    the previous step sampled) an id -(r + 1) stands for prev[r]."""
     require_cuda(ids, table, out)
     T, h = out.shape
     if ids.dtype != torch.int32 or out.dtype != torch.float32 or not out.is_contiguous() \
             or not table.is_contiguous() or table.shape[1] != h or ids.numel() != T:
         raise KernelError("embedding: ids int32 [T], table [V, h] contiguous, out f32 [T, h] contiguous")
+    if prev is not None:
+        require_cuda(prev)
+        if prev.dtype != torch.int32 or prev.dim() != 1 or not prev.is_contiguous():
+            raise KernelError("embedding: prev int32 [rows] contiguous")
     lib, f = _fn("elementwise", "dinfer_embedding",
-                 [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    check(lib, f(ptr(ids), ptr(table), ptr(out), T, h, table.shape[0], dtype_code(table.dtype),
-                 stream_handle()), "embedding")
+                 [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(ids), ptr(prev) if prev is not None else None, prev.numel() if prev is not None else 0,
+                 ptr(table), ptr(out), T, h, table.shape[0], dtype_code(table.dtype), stream_handle()), "embedding")
     return out
 
 

@@ -91,7 +91,7 @@ class DecoderModel:
         s = self.spec
         T = ids.numel()
         x = torch.empty((T, s.hidden_size), dtype=torch.float32, device=ids.device)
-        ops.embedding(ids, self.embedding, x)
+        ops.embedding(ids, self.embedding, x, prev=ctx.prev_tokens)
         stream = ResidualStream(x)
         order = [self.blocks[e.layer] for e in s.schedule]
         for i, (block, binding) in enumerate(zip(order, bindings)):

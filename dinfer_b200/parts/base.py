@@ -70,6 +70,7 @@ class StepContext:
     any_prefill: bool = True           # some request brings more than one
     decode_splits: int = 0             # > 0: the decode attention uses this many key splits (CUDA graphs)
     split_norms: bool = False          # norms between two products may be taken apart (see HalfNormed)
+    prev_tokens: Optional[torch.Tensor] = None   # int32 [rows]: a token id -(r + 1) stands for prev_tokens[r]
     # host copies for parts written in plain torch (tests, toy parts)
     cu_seqlens_host: Sequence[int] = ()
     seq_lens_host: Sequence[int] = ()

@@ -94,12 +94,13 @@ class Sampler:
         return k
 
     def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-                 num_generated: Sequence[int], histories: Optional[Sequence[tuple]] = None) -> torch.Tensor:
+                 num_generated: Sequence[int], histories: Optional[Sequence[tuple]] = None,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``histories[i] = (prompt_ids, output_ids)`` is needed only for rows with penalties.
-        Returns int32 [R] on the device."""
+        Returns int32 [R] on the device (``out`` if given)."""
         R = logits.shape[0]
         if all(p.is_greedy and not p.has_penalties for p in params):
-            return argmax(logits)
+            return argmax(logits, out)
         if any(p.has_penalties for p in params):
             logits = logits.clone()
             flat: List[int] = []
@@ -137,4 +138,5 @@ class Sampler:
         d64 = dev[:16 * cap].view(torch.int64).view(2, cap)
         d32f = dev[16 * cap:28 * cap].view(torch.float32).view(3, cap)
         d32i = dev[28 * cap:32 * cap].view(torch.int32)
-        return sample(logits, d32f[0, :R], d64[0, :R], d64[1, :R], top_k=d32i[:R], top_p=d32f[1, :R], min_p=d32f[2, :R])
+        return sample(logits, d32f[0, :R], d64[0, :R], d64[1, :R], top_k=d32i[:R], top_p=d32f[1, :R], min_p=d32f[2, :R],
+                      out=out)

@@ -276,3 +276,46 @@ def test_many_requests_small_pool_all_options(tmp_path, prefix):
     assert stats.preemptions > 0
     if prefix:
         assert stats.prefix_hit_tokens > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_scheduling_ahead_gives_the_same_tokens(dirs, tmp_path, dtype):
+    """One step kept in flight (the host reads a step's tokens after it has launched the next, which takes
+    them on the device) against one step at a time: prompts in portions beside decoding requests, stop tokens
+    (so that steps run in vain and are dropped), max_tokens, a pool small enough to preempt requests whose
+    token is in flight, greedy and seeded sampling.  In 32-bit the tokens must be the same; in bfloat16
+    (where a batch of another size may round differently) everything must finish within its limits."""
+    from dinfer_b200 import LLM, SamplingParams
+    cfg = H.TINY_B if dtype == "float32" else H.TINY_D
+    d = dirs["B"] if dtype == "float32" else H.make_model_dir(str(tmp_path / "d"), cfg, *H.INIT["D"], torch.bfloat16)
+    stops = list(range(0, cfg["vocab_size"], 40))
+
+    def run(ahead):
+        rng = random.Random(11)
+        llm = LLM(d, dtype=dtype, max_model_len=256, max_num_seqs=6, max_num_batched_tokens=48,
+                  num_blocks=13, block_size=16, async_scheduling=ahead)
+        assert llm._ahead == ahead
+        prompts, params = [], []
+        for i in range(18):
+            prompts.append(H.random_tokens(rng, rng.choice([1, 3, 16, 17, 40, 90]), cfg["vocab_size"]))
+            params.append(SamplingParams(temperature=[0.0, 0.9, 0.7][i % 3], top_k=[-1, -1, 40][i % 3],
+                                         max_tokens=rng.choice([1, 2, 7, 60, 100]), seed=500 + i,
+                                         stop_token_ids=stops if i % 2 else [], ignore_eos=True))
+        outs = llm.generate(prompts, params)
+        llm.runner.check_device_status()
+        llm.runner.manager.check_invariants()
+        assert llm.runner.manager.num_free_blocks() == 13 and not llm.has_unfinished()
+        for o, sp in zip(outs, params):
+            assert 1 <= len(o.output_ids) <= sp.max_tokens
+            assert all(0 <= t < cfg["vocab_size"] for t in o.output_ids)
+            if o.finish_reason == "stop":
+                assert o.output_ids[-1] in stops and not any(t in stops for t in o.output_ids[:-1])
+            else:
+                assert len(o.output_ids) == sp.max_tokens
+        return [(o.output_ids, o.finish_reason) for o in outs], llm.stats
+
+    one, stats_one = run(False)
+    two, stats_two = run(True)
+    assert stats_two.preemptions > 0 and any(r == "stop" for _, r in two)
+    if dtype == "float32":
+        assert one == two

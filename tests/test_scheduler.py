@@ -200,3 +200,84 @@ def test_prefix_cache_skips_the_tokens_an_earlier_request_left():
             break
     assert preempted and not s2.has_unfinished()
     assert m2.prefix_hits > 0
+
+
+# ---- scheduling one step ahead (the tokens of a step are read after the next one is scheduled)
+def drive(s, m, ahead, token, max_steps=400):
+    """Run until nothing is left, the way the engine loop does: with ``ahead`` the next step is scheduled and
+    its cache bookkeeping done BEFORE the last step's tokens are applied.  ``token(req, length)`` is the token a
+    step yields for a request whose sequence is ``length`` long after the step (a pure function, so both ways
+    of driving must generate the same sequences)."""
+    plans, flight, steps = [], None, 0
+
+    def collect(f):
+        plan, toks = f
+        return s.update(plan, toks)
+
+    while (s.has_unfinished() or flight is not None) and steps < max_steps:
+        steps += 1
+        plan = s.schedule(lookahead=ahead)
+        toks = {}
+        for x in plan.scheduled:
+            r = x.request
+            assert r.req_id in m and m.num_tokens(r.req_id) >= x.start + x.num_tokens
+            assert m.num_computed(r.req_id) == x.start
+            assert x.start + x.num_tokens <= r.num_tokens + 1          # at most one token not yet read
+            m.advance(r.req_id, x.start + x.num_tokens)
+            if x.samples:
+                toks[r.req_id] = token(r, x.start + x.num_tokens)
+        plans.append(plan)
+        if flight is not None:
+            collect(flight)
+            flight = None
+        if plan.scheduled:
+            flight = (plan, toks)
+            if not ahead:
+                collect(flight)
+                flight = None
+        m.check_invariants()
+    assert steps < max_steps
+    return plans
+
+
+@pytest.mark.parametrize("num_blocks", [64, 7])
+def test_scheduling_ahead_generates_the_same_sequences(num_blocks):
+    """Prompts in portions, decoding, an end-of-sequence token, max_tokens, and (with 7 pages) preemption with a
+    token in flight: the sequences do not depend on whether the host reads tokens at once or a step late."""
+    def token(r, length):
+        return 99 if (r.req_id == "b" and length == 14) else 1000 + length
+
+    results = {}
+    for ahead in (False, True):
+        s, m = make(num_blocks=num_blocks, block_size=4, max_num_batched_tokens=8)
+        reqs = [req("a", 9, max_tokens=12), req("b", 10, max_tokens=12), req("c", 3, max_tokens=5)]
+        for r in reqs:
+            s.add_request(r)
+        plans = drive(s, m, ahead, token)
+        assert all(r.finished for r in reqs) and m.num_free_blocks() == num_blocks
+        results[ahead] = [(r.req_id, list(r.output_ids), r.finish_reason) for r in reqs]
+        if ahead:
+            assert all(r.num_placeholders == 0 for r in reqs if r.finish_reason == FinishReason.LENGTH)
+        if num_blocks == 7:
+            assert s.num_preemptions > 0
+    assert results[False] == results[True]
+    b = results[True][1]
+    assert b[1][-1] == 99 and b[2] == FinishReason.STOP and len(b[1]) == 5
+
+
+def test_scheduling_ahead_does_not_run_past_a_certain_end():
+    """max_tokens is known before the token arrives: the request is not scheduled for a step that cannot count;
+    an end-of-sequence token is not: one step runs in vain and its token is dropped."""
+    s, m = make()
+    a = req("a", 4, max_tokens=3)
+    s.add_request(a)
+    plans = drive(s, m, True, lambda r, n: 1000 + n)
+    assert [len(p.scheduled) for p in plans] == [1, 1, 1, 0]          # 3 tokens, then only the last read
+    assert a.output_ids == [1004, 1005, 1006] and a.finish_reason == FinishReason.LENGTH
+    s, m = make()
+    b = req("b", 4, max_tokens=8)
+    s.add_request(b)
+    plans = drive(s, m, True, lambda r, n: 99 if n == 5 else 1000 + n)
+    assert b.output_ids == [1004, 99] and b.finish_reason == FinishReason.STOP
+    assert [len(p.scheduled) for p in plans] == [1, 1, 1, 0]          # the third ran before the 99 was read
+    assert m.num_free_blocks() == 64
