@@ -10,8 +10,10 @@ fraction of the memory / tensor-core roofline each reaches.
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch.  ``value`` times K steps on
 the device (CUDA events); ``e2e`` is the same K steps through the Python entry point ``LLM.step()``,
-each step copying its token ids host->device from pinned memory and reading the sampled tokens
-device->host.  The cache is filled by really prefilling the prompts through the engine.
+each step copying its plan (token ids, positions, page tables) host->device from pinned memory and
+reading sampled tokens device->host; the engine keeps one step in flight (it launches a step, then
+reads the tokens of the step before), so K calls cover K steps' launches, copies and read-backs.
+The cache is filled by really prefilling the prompts through the engine.
 """
 from __future__ import annotations
 
@@ -163,7 +165,7 @@ def decode_run(llm, cfg, batch, context, steps, warmup, rng, measure_e2e, want_l
         llm.step()
     # device time of one decode step: the step's captured graph (forward of the whole batch) replayed K
     # times back to back at the context just reached, timed with CUDA events, no host in between
-    res["mean_context"] = sum(r.num_tokens for r in llm._requests.values()) / batch - 1
+    res["mean_context"] = sum(r.num_tokens + r.num_placeholders for r in llm._requests.values()) / batch - 1
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     from dinfer_b200.kernels import lib as _lib
