@@ -72,33 +72,43 @@ class Sampler:
 
     def __init__(self, device):
         self.device = device
-        self._host: List[torch.Tensor] = []
-        self._dev: List[torch.Tensor] = []
-        self._events: List[Optional[torch.cuda.Event]] = []
+        self._slots: List[dict] = []
         self._turn = 0
         self._rows = 0
 
-    def _staging(self, rows: int):
+    def _staging(self, rows: int) -> dict:
         """Pinned and device buffers of 32 bytes a row (a small ring: a buffer is rewritten only after its
-        last copy has left it)."""
+        last copy has left it), with the views of their columns made once."""
         if rows > self._rows:
-            self._rows = max(64, 2 * rows)
+            cap = self._rows = max(64, 2 * rows)
             pin = torch.device(self.device).type == "cuda"
-            self._host = [torch.empty(32 * self._rows, dtype=torch.uint8, pin_memory=pin) for _ in range(self.RING)]
-            self._dev = [torch.empty(32 * self._rows, dtype=torch.uint8, device=self.device) for _ in range(self.RING)]
-            self._events = [None] * self.RING
+            self._slots = []
+            for _ in range(self.RING):
+                host = torch.empty(32 * cap, dtype=torch.uint8, pin_memory=pin)
+                dev = torch.empty(32 * cap, dtype=torch.uint8, device=self.device)
+                h = host.numpy()
+                base = dev.data_ptr()
+                self._slots.append(dict(
+                    host=host, dev=dev, event=None,
+                    # columns: seeds, offsets (int64), temperature, top_p, min_p (float32), top_k (int32)
+                    i64=h[:16 * cap].view(np.int64).reshape(2, cap),
+                    f32=h[16 * cap:28 * cap].view(np.float32).reshape(3, cap),
+                    i32=h[28 * cap:32 * cap].view(np.int32),
+                    seeds=base, offsets=base + 8 * cap, temperature=base + 16 * cap, top_p=base + 20 * cap,
+                    min_p=base + 24 * cap, top_k=base + 28 * cap))
         k = self._turn
         self._turn = (k + 1) % self.RING
-        if self._events[k] is not None:
-            self._events[k].synchronize()
-        return k
+        slot = self._slots[k]
+        if slot["event"] is not None:
+            slot["event"].synchronize()
+        return slot
 
     def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                  num_generated: Sequence[int], histories: Optional[Sequence[tuple]] = None,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``histories[i] = (prompt_ids, output_ids)`` is needed only for rows with penalties.
         Returns int32 [R] on the device (``out`` if given)."""
-        R = logits.shape[0]
+        R, V = logits.shape
         if all(p.is_greedy and not p.has_penalties for p in params):
             return argmax(logits, out)
         if any(p.has_penalties for p in params):
@@ -118,25 +128,24 @@ class Sampler:
                 torch.tensor([p.repetition_penalty for p in params], dtype=torch.float32, device=dev),
                 torch.tensor([p.frequency_penalty for p in params], dtype=torch.float32, device=dev),
                 torch.tensor([p.presence_penalty for p in params], dtype=torch.float32, device=dev))
-        # columns of one packed buffer: seeds, offsets (int64), temperature, top_p, min_p (float32), top_k (int32)
-        k = self._staging(R)
-        cap = self._rows
-        host = self._host[k].numpy()
-        i64 = host[:16 * cap].view(np.int64).reshape(2, cap)
-        f32 = host[16 * cap:28 * cap].view(np.float32).reshape(3, cap)
-        i32 = host[28 * cap:32 * cap].view(np.int32)
+        if logits.dtype != torch.float32 or logits.stride(1) != 1:
+            raise ValueError("sample: logits must be float32 with a contiguous last axis")
+        slot = self._staging(R)
+        i64, f32, i32 = slot["i64"], slot["f32"], slot["i32"]
         for i, p in enumerate(params):
             f32[0, i], f32[1, i], f32[2, i] = p.temperature, p.top_p, p.min_p
             i32[i] = p.top_k
             i64[0, i], i64[1, i] = _u64(seeds[i]), _u64(num_generated[i])
-        dev = self._dev[k]
-        dev.copy_(self._host[k], non_blocking=True)
-        if dev.is_cuda:
-            ev = self._events[k] or torch.cuda.Event()
+        slot["dev"].copy_(slot["host"], non_blocking=True)
+        if slot["dev"].is_cuda:
+            ev = slot["event"] or torch.cuda.Event()
             ev.record()
-            self._events[k] = ev
-        d64 = dev[:16 * cap].view(torch.int64).view(2, cap)
-        d32f = dev[16 * cap:28 * cap].view(torch.float32).view(3, cap)
-        d32i = dev[28 * cap:32 * cap].view(torch.int32)
-        return sample(logits, d32f[0, :R], d64[0, :R], d64[1, :R], top_k=d32i[:R], top_p=d32f[1, :R], min_p=d32f[2, :R],
-                      out=out)
+            slot["event"] = ev
+        if out is None:
+            out = torch.empty(R, dtype=torch.int32, device=logits.device)
+        lib, f = _fn("sampling", "dinfer_sample",
+                     [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_int, c_int, c_void_p])
+        check(lib, f(ptr(logits), logits.stride(0), slot["temperature"], slot["top_k"], slot["top_p"], slot["min_p"],
+                     slot["seeds"], slot["offsets"], ptr(out), R, V, stream_handle()), "sample")
+        return out
