@@ -10,6 +10,8 @@
 //                      tokens do not depend on its place in the batch; rows whose temperature is
 //                      <= 1e-5 are greedy
 //   dinfer_penalties   repetition / frequency / presence penalties from the token history
+//   dinfer_logit_bias  per-request additive biases on given tokens
+//   dinfer_logprobs    log-probability and rank of the chosen token and the k most likely tokens
 //
 // Same contract as the reference (crates/kernels/cuda/sampling.cu:13-56,60-133,143-157,196-283,
 // 322-349; order of operations models/qwen3/src/executor.rs:552-605).  Unlike it the logits are not
@@ -435,6 +437,101 @@ __global__ void penalties_kernel(float* __restrict__ logits, int64_t ld, const i
   }
 }
 
+// logits[rows[i], ids[i]] += bias[i]; a (row, id) pair appears once.
+__global__ void logit_bias_kernel(float* __restrict__ logits, int64_t ld, const int* __restrict__ rows,
+                                  const int* __restrict__ ids, const float* __restrict__ bias, int n, int vocab) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int t = ids[i];
+  if (t >= 0 && t < vocab) logits[(int64_t)rows[i] * ld + t] += bias[i];
+}
+
+// Log-probabilities of a row under log_softmax of the logits as given (no temperature, no filter): the chosen
+// token's, how many tokens are strictly more likely (its rank), and the k most likely in descending order, ties
+// to the lower id.  One CTA per row.  The k best are found one after the other, each as the best entry that comes
+// after the last one in that order, so nothing has to be remembered but the last winner.
+constexpr int LP_MAX_K = 32;
+__global__ void logprobs_kernel(const float* __restrict__ logits, int64_t ld, const int* __restrict__ chosen, int k,
+                                int* __restrict__ out_ids, float* __restrict__ out_lp, int* __restrict__ out_rank,
+                                int vocab) {
+  __shared__ float s_f[BLOCK / 32];
+  __shared__ int s_i[BLOCK / 32];
+  __shared__ float s_m, s_lse, s_last_v;
+  __shared__ int s_last_i;
+  const int b = blockIdx.x;
+  const float* row = logits + (int64_t)b * ld;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // maximum
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < vocab; i += BLOCK) m = fmaxf(m, row[i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) s_f[warp] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float v = s_f[0];
+    for (int w = 1; w < BLOCK / 32; ++w) v = fmaxf(v, s_f[w]);
+    s_m = v;
+  }
+  __syncthreads();
+  m = s_m;
+  // log of the sum of exponentials, and the rank of the chosen token (sums in a fixed order)
+  const int c = chosen[b];
+  const bool c_ok = c >= 0 && c < vocab;
+  const float xc = c_ok ? row[c] : -INFINITY;
+  float d = 0.f;
+  int gt = 0;
+  for (int i = threadIdx.x; i < vocab; i += BLOCK) {
+    const float v = row[i];
+    if (v > -INFINITY) d += expf(v - m);
+    gt += v > xc;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    d += __shfl_xor_sync(0xffffffffu, d, o);
+    gt += __shfl_xor_sync(0xffffffffu, gt, o);
+  }
+  if (lane == 0) { s_f[warp] = d; s_i[warp] = gt; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float sum = 0.f;
+    int cnt = 0;
+    for (int w = 0; w < BLOCK / 32; ++w) { sum += s_f[w]; cnt += s_i[w]; }
+    s_lse = m + logf(sum);
+    out_ids[(int64_t)b * (k + 1)] = c;
+    out_lp[(int64_t)b * (k + 1)] = xc - s_lse;
+    out_rank[b] = cnt;
+    s_last_v = INFINITY;                  // before the first entry of the order
+    s_last_i = -1;
+  }
+  __syncthreads();
+  for (int j = 0; j < k; ++j) {
+    const float last_v = s_last_v;
+    const int last_i = s_last_i;
+    ArgMax best{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < vocab; i += BLOCK) {
+      const float v = row[i];
+      if (v < last_v || (v == last_v && i > last_i)) best = better(best, ArgMax{v, i});
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      best = better(best, ArgMax{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)});
+    __syncthreads();                      // the last round's readers of s_f / s_i are done
+    if (lane == 0) { s_f[warp] = best.v; s_i[warp] = best.i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      ArgMax a{s_f[0], s_i[0]};
+      for (int w = 1; w < BLOCK / 32; ++w) a = better(a, ArgMax{s_f[w], s_i[w]});
+      const bool any = a.i != 0x7fffffff;  // fewer than k entries in the row: the rest is marked -1
+      out_ids[(int64_t)b * (k + 1) + 1 + j] = any ? a.i : -1;
+      out_lp[(int64_t)b * (k + 1) + 1 + j] = any ? a.v - s_lse : -INFINITY;
+      s_last_v = any ? a.v : -INFINITY;
+      s_last_i = any ? a.i : 0x7fffffff;
+    }
+    __syncthreads();
+  }
+}
+
 template <typename... KArgs, typename... Args>
 int launch_rows(void (*kernel)(KArgs...), int rows, size_t smem, cudaStream_t stream, const char* what, Args... args) {
   cudaError_t e = launch_pdl_cluster(kernel, dim3(rows * ROW_CTAS), dim3(BLOCK), dim3(ROW_CTAS, 1, 1), smem, stream, args...);
@@ -479,4 +576,25 @@ DINFER_API int dinfer_penalties(float* logits, int64_t ld, const int* ids, const
   if (rows == 0) return 0;
   penalties_kernel<<<rows, 256, 0, stream>>>(logits, ld, ids, offsets, prompt_len, rep, freq, pres, vocab);
   return cuda_status("penalties");
+}
+
+// rows, ids, bias [n]: logits[rows[i], ids[i]] += bias[i] (the reference adds its logit_bias before the penalties:
+// crates/core/src/sample.rs:104-106).
+DINFER_API int dinfer_logit_bias(float* logits, int64_t ld, const int* rows, const int* ids, const float* bias, int n,
+                                 int vocab, cudaStream_t stream) {
+  if (n < 0 || vocab <= 0 || ld < vocab) return refuse(DINFER_BAD_ARGUMENT, "logit_bias: bad sizes n=%d vocab=%d", n, vocab);
+  if (n == 0) return 0;
+  logit_bias_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, ld, rows, ids, bias, n, vocab);
+  return cuda_status("logit_bias");
+}
+
+// chosen [rows]; out_ids, out_lp [rows, k + 1]: column 0 the chosen token, then the k most likely, descending;
+// out_rank [rows]: tokens strictly more likely than the chosen one (crates/kernels/cuda/sampling.cu:381-430).
+DINFER_API int dinfer_logprobs(const float* logits, int64_t ld, const int* chosen, int k, int* out_ids, float* out_lp,
+                               int* out_rank, int rows, int vocab, cudaStream_t stream) {
+  if (rows < 0 || vocab <= 0 || ld < vocab) return refuse(DINFER_BAD_ARGUMENT, "logprobs: bad sizes rows=%d vocab=%d", rows, vocab);
+  if (k < 0 || k > LP_MAX_K) return refuse(DINFER_BAD_ARGUMENT, "logprobs: k must be in [0, %d], got %d", LP_MAX_K, k);
+  if (rows == 0) return 0;
+  logprobs_kernel<<<rows, BLOCK, 0, stream>>>(logits, ld, chosen, k, out_ids, out_lp, out_rank, vocab);
+  return cuda_status("logprobs");
 }

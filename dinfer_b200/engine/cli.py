@@ -69,9 +69,15 @@ def cmd_generate(a) -> int:
                         repetition_penalty=a.repetition_penalty, frequency_penalty=a.frequency_penalty,
                         presence_penalty=a.presence_penalty, seed=a.seed,
                         stop_token_ids=_ids(a.stop_token_ids) if a.stop_token_ids else [],
-                        ignore_eos=a.ignore_eos)
+                        ignore_eos=a.ignore_eos, logprobs=a.logprobs,
+                        logit_bias={int(t): float(b) for t, b in
+                                    (x.split(":") for x in a.logit_bias.replace(",", " ").split())})
     for o in llm.generate(prompts, sp):
-        print(json.dumps({"id": o.req_id, "output_ids": o.output_ids, "finish_reason": o.finish_reason}))
+        rec = {"id": o.req_id, "output_ids": o.output_ids, "finish_reason": o.finish_reason}
+        if o.logprobs is not None:
+            rec["logprobs"] = [{"token_id": t.token_id, "logprob": t.logprob, "rank": t.rank,
+                                "top": list(zip(t.top_ids, t.top_logprobs))} for t in o.logprobs]
+        print(json.dumps(rec))
     s = llm.stats
     print(f"steps {s.steps}  prompt tokens {s.prompt_tokens}  generated {s.generated_tokens}  "
           f"preemptions {s.preemptions}", file=sys.stderr)
@@ -123,6 +129,9 @@ def main(argv=None) -> int:
     g.add_argument("--seed", type=int, default=None)
     g.add_argument("--stop-token-ids", default="")
     g.add_argument("--ignore-eos", action="store_true")
+    g.add_argument("--logprobs", type=int, default=None,
+                   help="with every generated token: its log-probability, its rank and this many most likely tokens")
+    g.add_argument("--logit-bias", default="", help="TOKEN:BIAS pairs, comma separated, added to the logits")
     g.set_defaults(fn=cmd_generate)
     r = sub.add_parser("random-model", help="write a model folder with random weights")
     r.add_argument("--config", required=True, help="a config.json")

@@ -22,7 +22,7 @@ from typing import Any, Dict, Hashable, List, Optional, Sequence, Union
 import torch
 
 from ..config.engine_config import EngineConfig
-from ..sampling.params import SamplingParams
+from ..sampling.params import SamplingParams, TokenLogprobs
 from ..sampling.sampler import Sampler
 from ..weights.loader import WeightSource
 from .batch import StepEntry
@@ -38,6 +38,7 @@ class RequestOutput:
     output_ids: List[int]
     finish_reason: str
     num_preemptions: int = 0
+    logprobs: Optional[List[TokenLogprobs]] = None      # one per output token, if the request asked for them
 
 
 @dataclass
@@ -58,6 +59,7 @@ class _InFlight:
         self.row = row                      # request -> its row in the step's sampled tokens
         self.host: Optional[torch.Tensor] = None
         self.event: Optional[torch.cuda.Event] = None
+        self.logprobs = None                # (ids, logprobs, rank) on the device, if a row asked for them
 
 
 class LLM:
@@ -111,9 +113,11 @@ class LLM:
         if any((t < 0 or t >= vocab) for t in prompt_ids):
             raise ValueError(f"request {req_id!r}: a token id is outside the vocabulary [0, {vocab})")
         req = Request(req_id, list(prompt_ids), params or SamplingParams())
+        if any(t >= vocab for t in req.params.logit_bias):
+            raise ValueError(f"request {req_id!r}: a logit_bias token id is outside the vocabulary [0, {vocab})")
         self.scheduler.add_request(req)
         self._requests[req_id] = req
-        self._num_penalized += int(req.params.has_penalties)
+        self._num_penalized += int(req.params.needs_host_history)
         return req_id
 
     def abort(self, req_id: Hashable) -> None:
@@ -123,7 +127,7 @@ class LLM:
     def _forget(self, req_id: Hashable) -> None:
         req = self._requests.pop(req_id, None)
         if req is not None:
-            self._num_penalized -= int(req.params.has_penalties)
+            self._num_penalized -= int(req.params.needs_host_history)
 
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished() or self._inflight is not None
@@ -132,7 +136,8 @@ class LLM:
     def step(self) -> List[RequestOutput]:
         """Schedule, run, sample, update.  Returns the requests known to have finished: those of this step,
         or, when scheduling ahead, those of the step launched by the call before."""
-        # penalties need every earlier token on the host: such steps run one at a time
+        # penalties need every earlier token on the host, log-probabilities are read with the tokens: such steps
+        # run one at a time
         ahead = self._ahead and self._num_penalized == 0
         finished: List[Request] = []
         if not ahead and self._inflight is not None:
@@ -153,7 +158,8 @@ class LLM:
             self._forget(r.req_id)
             outs.append(RequestOutput(r.req_id, r.prompt_ids, r.output_ids,
                                       r.finish_reason.value if r.finish_reason else "abort",
-                                      r.num_preemptions))
+                                      r.num_preemptions,
+                                      r.logprobs if r.params.logprobs is not None else None))
         return outs
 
     def _launch(self, plan) -> "_InFlight":
@@ -184,6 +190,7 @@ class LLM:
             flight.host[:len(samplers)].copy_(out, non_blocking=True)     # the step's one device->host read
             flight.event = torch.cuda.Event()
             flight.event.record()
+            flight.logprobs = self.sampler.last_logprobs
         self.stats.steps += 1
         if self.stats.steps % 256 == 0:
             self.runner.check_device_status()
@@ -198,7 +205,14 @@ class LLM:
             host = flight.host[:len(flight.samplers)].tolist()
             sampled = {r.req_id: t for r, t in zip(flight.samplers, host)}
             self.stats.generated_tokens += len(host)
-        return self.scheduler.update(flight.plan, sampled)
+        done = self.scheduler.update(flight.plan, sampled)
+        if flight.logprobs is not None:
+            ids, lps, rank = (t.cpu().tolist() for t in flight.logprobs)
+            for i, r in enumerate(flight.samplers):
+                k = r.params.logprobs
+                if k is not None and r.output_ids and r.output_ids[-1] == ids[i][0]:
+                    r.logprobs.append(TokenLogprobs(ids[i][0], lps[i][0], rank[i], ids[i][1:1 + k], lps[i][1:1 + k]))
+        return done
 
     # ---- whole generation
     def generate(self, prompt_token_ids: Sequence[Sequence[int]],

@@ -7,7 +7,7 @@ import secrets
 from dataclasses import dataclass, field
 from typing import Hashable, List, Optional
 
-from ..sampling.params import SamplingParams
+from ..sampling.params import SamplingParams, TokenLogprobs
 
 
 class RequestStatus(enum.Enum):
@@ -34,6 +34,7 @@ class Request:
     status: RequestStatus = RequestStatus.WAITING
     finish_reason: Optional[FinishReason] = None
     num_preemptions: int = 0
+    logprobs: List[TokenLogprobs] = field(default_factory=list)   # one per output token, if asked for
 
     def __post_init__(self):
         if self.params.seed is not None:

@@ -1,10 +1,24 @@
 """Per-request sampling options: names, defaults and ranges of the reference's ``SamplingParams``
-(crates/core/src/sample.rs:81-205), without the text-level options (stop strings, logprobs,
-grammars) that belong to the server."""
+(crates/core/src/sample.rs:81-205), without the options that need the tokenizer or the server (stop strings,
+grammars) and without prompt_logprobs."""
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional
+from typing import Dict, List, Optional
+
+
+MAX_LOGPROBS = 32          # the most candidates a token's log-probabilities list (crates/kernels/cuda/sampling.cu:382)
+MAX_LOGIT_BIAS = 300       # crates/core/src/sample.rs:104
+
+
+@dataclass
+class TokenLogprobs:
+    """Log-probabilities at one generated token."""
+    token_id: int
+    logprob: float
+    rank: int                           # tokens strictly more likely than this one
+    top_ids: List[int] = field(default_factory=list)
+    top_logprobs: List[float] = field(default_factory=list)
 
 
 @dataclass
@@ -21,6 +35,11 @@ class SamplingParams:
     seed: Optional[int] = None          # None: drawn once per request
     stop_token_ids: List[int] = field(default_factory=list)
     ignore_eos: bool = False
+    # None: no log-probabilities; k >= 0: every generated token comes with its log-probability and rank under
+    # log_softmax of the model's logits (before bias, penalties and temperature) and with the k most likely tokens
+    logprobs: Optional[int] = None
+    # token id -> bias added to the logits before the penalties (at most 300 entries)
+    logit_bias: Dict[int, float] = field(default_factory=dict)
 
     @property
     def is_greedy(self) -> bool:
@@ -31,7 +50,21 @@ class SamplingParams:
         return (self.repetition_penalty != 1.0 or self.frequency_penalty != 0.0
                 or self.presence_penalty != 0.0)
 
+    @property
+    def needs_host_history(self) -> bool:
+        """Options whose step cannot be launched before the last step's tokens are on the host."""
+        return self.has_penalties or self.logprobs is not None
+
     def validate(self) -> None:
+        if self.logprobs is not None and not (0 <= self.logprobs <= MAX_LOGPROBS):
+            raise ValueError(f"logprobs must be in [0, {MAX_LOGPROBS}], got {self.logprobs}")
+        if len(self.logit_bias) > MAX_LOGIT_BIAS:
+            raise ValueError(f"logit_bias takes at most {MAX_LOGIT_BIAS} entries, got {len(self.logit_bias)}")
+        for t, b in self.logit_bias.items():
+            if isinstance(t, bool) or not isinstance(t, int) or t < 0:
+                raise ValueError(f"logit_bias: {t!r} is not a token id")
+            if not (-100.0 <= float(b) <= 100.0):
+                raise ValueError(f"logit_bias: bias {b} of token {t} is outside [-100, 100]")
         if self.temperature < 0.0:
             raise ValueError(f"temperature must be non-negative, got {self.temperature}")
         if not (0.0 < self.top_p <= 1.0):

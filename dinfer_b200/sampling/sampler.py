@@ -59,6 +59,32 @@ def apply_penalties(logits: torch.Tensor, ids: torch.Tensor, offsets: torch.Tens
     return logits
 
 
+def logit_bias(logits: torch.Tensor, rows: torch.Tensor, ids: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """In place: logits[rows[i], ids[i]] += bias[i] (int32, int32, float32 [n]; a pair appears once)."""
+    R, V = logits.shape
+    lib, f = _fn("sampling", "dinfer_logit_bias", [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    check(lib, f(ptr(logits), logits.stride(0), ptr(rows), ptr(ids), ptr(bias), rows.numel(), V, stream_handle()),
+          "logit_bias")
+    return logits
+
+
+def logprobs(logits: torch.Tensor, chosen: torch.Tensor, k: int):
+    """(ids int32 [R, k+1], logprobs float32 [R, k+1], rank int32 [R]) under log_softmax of ``logits``: column 0
+    the chosen token, then the k most likely in descending order (ties to the lower id); rank = tokens strictly
+    more likely than the chosen one."""
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or chosen.dtype != torch.int32 or chosen.numel() != R:
+        raise ValueError("logprobs: logits float32 [R, V] with a contiguous last axis, chosen int32 [R]")
+    ids = torch.empty((R, k + 1), dtype=torch.int32, device=logits.device)
+    lp = torch.empty((R, k + 1), dtype=torch.float32, device=logits.device)
+    rank = torch.empty(R, dtype=torch.int32, device=logits.device)
+    lib, f = _fn("sampling", "dinfer_logprobs",
+                 [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    check(lib, f(ptr(logits), logits.stride(0), ptr(chosen), int(k), ptr(ids), ptr(lp), ptr(rank), R, V,
+                 stream_handle()), "logprobs")
+    return ids, lp, rank
+
+
 def _u64(x: int) -> int:
     x &= 0xFFFFFFFFFFFFFFFF
     return x - (1 << 64) if x >= (1 << 63) else x
@@ -72,6 +98,7 @@ class Sampler:
 
     def __init__(self, device):
         self.device = device
+        self.last_logprobs = None       # (ids, logprobs, rank) of the last call, if any of its rows asked
         self._slots: List[dict] = []
         self._turn = 0
         self._rows = 0
@@ -106,13 +133,37 @@ class Sampler:
     def __call__(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                  num_generated: Sequence[int], histories: Optional[Sequence[tuple]] = None,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """``histories[i] = (prompt_ids, output_ids)`` is needed only for rows with penalties.
-        Returns int32 [R] on the device (``out`` if given)."""
+        """Order: logit_bias -> penalties -> temperature -> min_p -> top-k -> top-p -> sample.
+        ``histories[i] = (prompt_ids, output_ids)`` is needed only for rows with penalties.
+        Returns int32 [R] on the device (``out`` if given); ``self.last_logprobs`` holds the log-probabilities
+        if a row asked for them."""
+        R, V = logits.shape
+        raw = logits
+        self.last_logprobs = None
+        want_lp = [p.logprobs for p in params if p.logprobs is not None]
+        if any(p.logit_bias for p in params):
+            logits = logits.clone()
+            rows_, ids_, vals_ = [], [], []
+            for i, p in enumerate(params):
+                for t, v in p.logit_bias.items():
+                    rows_.append(i); ids_.append(int(t)); vals_.append(float(v))
+            dev = self.device
+            logit_bias(logits, torch.tensor(rows_, dtype=torch.int32, device=dev),
+                       torch.tensor(ids_, dtype=torch.int32, device=dev),
+                       torch.tensor(vals_, dtype=torch.float32, device=dev))
+        toks = self._sample(logits, raw, params, seeds, num_generated, histories, out)
+        if want_lp:
+            # from the logits as the model gave them (models/qwen3/src/executor.rs:7,606-635)
+            self.last_logprobs = logprobs(raw, toks, max(want_lp))
+        return toks
+
+    def _sample(self, logits, raw, params, seeds, num_generated, histories, out) -> torch.Tensor:
         R, V = logits.shape
         if all(p.is_greedy and not p.has_penalties for p in params):
             return argmax(logits, out)
         if any(p.has_penalties for p in params):
-            logits = logits.clone()
+            if logits is raw:
+                logits = logits.clone()
             flat: List[int] = []
             offs, plen = [0], []
             for i, p in enumerate(params):

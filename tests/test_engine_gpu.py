@@ -319,3 +319,38 @@ def test_scheduling_ahead_gives_the_same_tokens(dirs, tmp_path, dtype):
     assert stats_two.preemptions > 0 and any(r == "stop" for _, r in two)
     if dtype == "float32":
         assert one == two
+
+
+def test_logit_bias_and_logprobs_through_the_entry_point(dirs):
+    """A bias of +100 on one token makes greedy generation emit it; log-probabilities come from the model's own
+    logits (before the bias) and agree with the plain implementation: chosen token, rank, the most likely tokens."""
+    from dinfer_b200 import LLM, SamplingParams
+    cfg = H.TINY_A
+    W = H.load_plain_weights(dirs["A"])
+    rng = random.Random(4)
+    prompts = [H.random_tokens(rng, n, cfg["vocab_size"]) for n in (5, 9)]
+    llm = LLM(dirs["A"], dtype="float32", max_model_len=64, max_num_seqs=4, max_num_batched_tokens=16,
+              num_blocks=40, block_size=4)
+    sp = [SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=3),
+          SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logit_bias={17: 100.0}, logprobs=0)]
+    outs = llm.generate(prompts, sp)
+    assert outs[1].output_ids == [17] * 6
+    for o, p, k in zip(outs, prompts, (3, 0)):
+        assert len(o.logprobs) == 6
+        seq = list(p)
+        for t, rec in zip(o.output_ids, o.logprobs):
+            lg = P.qwen3_logits(W, cfg, seq)[-1].double()
+            want = torch.log_softmax(lg, dim=-1)
+            assert rec.token_id == t and abs(rec.logprob - float(want[t])) < 1e-4
+            assert rec.rank == int((lg > lg[t]).sum())
+            assert len(rec.top_ids) == k
+            if k:
+                assert rec.top_ids == torch.topk(lg, k).indices.tolist()
+                assert all(abs(a - float(want[i])) < 1e-4 for a, i in zip(rec.top_logprobs, rec.top_ids))
+            seq.append(t)
+    greedy = llm.generate(prompts[:1], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    assert greedy[0].logprobs is None and greedy[0].output_ids == outs[0].output_ids
+    with pytest.raises(ValueError):
+        llm.add_request([1, 2], SamplingParams(logit_bias={cfg["vocab_size"]: 1.0}))
+    with pytest.raises(ValueError):
+        llm.add_request([1, 2], SamplingParams(logprobs=33))

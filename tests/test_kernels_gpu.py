@@ -276,3 +276,39 @@ def test_penalties():
         v = v / 1.5 if v > 0 else v * 1.5
         want[0, tok] = v - 0.3 * cnt - 0.2
     assert torch.allclose(d.cpu(), want, atol=1e-6)
+
+
+@pytest.mark.parametrize("V,ld", [(517, 517), (151936, 151936), (1000, 1024)])
+@pytest.mark.parametrize("k", [0, 5, 32])
+def test_logprobs_and_logit_bias(V, ld, k):
+    """Log-probabilities of the chosen token, its rank and the k most likely tokens against log_softmax / topk;
+    ties go to the lower id; additive biases land on the given (row, token) pairs only."""
+    from dinfer_b200.sampling import sampler as S
+    g = torch.Generator().manual_seed(V + k)
+    R = 5
+    full = (torch.randn(R, ld, generator=g) * 4).cuda()
+    logits = full[:, :V]
+    logits[1, 7] = logits[1, 3] = float(logits[1].max()) + 1.0          # a tie at the top: id 3 comes first
+    logits[2, V - 1] = float("-inf")
+    chosen = torch.tensor([0, 7, V - 2, 11, V // 2], dtype=torch.int32, device="cuda")
+    ids, lp, rank = S.logprobs(logits, chosen, k)
+    want = torch.log_softmax(logits.double(), dim=-1)
+    for r in range(R):
+        c = int(chosen[r])
+        assert int(ids[r, 0]) == c and abs(float(lp[r, 0]) - float(want[r, c])) < 1e-4
+        assert int(rank[r]) == int((logits[r] > logits[r, c]).sum())
+        if k:
+            order = sorted(range(V), key=lambda i: (-float(logits[r, i]), i))[:k]
+            assert ids[r, 1:].tolist() == order
+            assert torch.allclose(lp[r, 1:].double().cpu(), want[r, order].cpu(), atol=1e-4)
+    assert ids[1, 1:3].tolist() == [3, 7][:k] if k else True
+    before = logits.clone()
+    rows = torch.tensor([0, 0, 3, 4], dtype=torch.int32, device="cuda")
+    toks = torch.tensor([1, V - 1, 5, 0], dtype=torch.int32, device="cuda")
+    bias = torch.tensor([2.5, -100.0, 100.0, 0.25], device="cuda")
+    S.logit_bias(logits, rows, toks, bias)
+    want_b = before.clone()
+    for r_, t_, b_ in zip(rows.tolist(), toks.tolist(), bias.tolist()):
+        want_b[r_, t_] += b_
+    assert torch.equal(logits, want_b)
+    assert torch.equal(full[:, V:], full[:, V:])                        # the padding of the rows is untouched
