@@ -93,64 +93,86 @@ class PlanBuilder:
         self.h2d_bytes = words * 4
 
     def build(self, entries: Sequence[StepEntry], starts: Sequence[int], *, pad_reqs: Optional[int] = None,
-              table_width: Optional[int] = None, dev: Optional[torch.Tensor] = None):
+              table_width: Optional[int] = None, dev: Optional[torch.Tensor] = None,
+              slots: Optional[Sequence[Tuple[int, int]]] = None):
         """``starts[i]`` = tokens of entry i already in the cache; pages must be allocated already.
         ``pad_reqs``: pad with one-token dummy requests up to this many and ask for every row's
-        logits (the layout of a captured decode graph).  ``dev``: the int32 device buffer to fill
-        (default: the next one of the ring).  Returns (ids, logits_rows, ctx)."""
+        logits (the layout of a captured decode graph).  ``slots``: the layout of a captured graph in
+        general: one ``(entry index or -1, tokens)`` per request place, in the order of the batch; a place
+        without an entry is a dummy request of that many tokens (none, or tokens 0 at positions 0.. with no
+        slot and no pages), and the logits of every place's last token are asked for (of token 0 for a place
+        without tokens).  ``dev``: the int32 device buffer to fill (default: the next one of the ring).
+        Returns (ids, logits_rows, ctx)."""
         m = self.manager
         bs = m.block_size
-        n_real = len(entries)
-        B = pad_reqs if pad_reqs is not None else n_real
-        if B < n_real:
-            raise ValueError("pad_reqs below the number of requests")
-        lens = [len(e.tokens) for e in entries] + [1] * (B - n_real)
+        if slots is None:
+            n_pad = (pad_reqs - len(entries)) if pad_reqs is not None else 0
+            if n_pad < 0:
+                raise ValueError("pad_reqs below the number of requests")
+            slots = [(i, len(e.tokens)) for i, e in enumerate(entries)] + [(-1, 1)] * n_pad
+            every_place = pad_reqs is not None
+        else:
+            every_place = True
+            used = sorted(i for i, _ in slots if i >= 0)
+            if used != list(range(len(entries))) or any(n != len(entries[i].tokens) for i, n in slots if i >= 0):
+                raise ValueError("slots must place every entry once, with its number of tokens")
+        B = len(slots)
+        lens = [n for _, n in slots]
         T = sum(lens)
         if T > self.max_tokens or B > self.max_reqs:
             raise ValueError(f"step of {T} tokens / {B} requests exceeds the plan buffers "
                              f"({self.max_tokens} / {self.max_reqs})")
         cu = np.zeros(B + 1, dtype=np.int32)
         np.cumsum(lens, out=cu[1:])
-        seq = np.ones(B, dtype=np.int32)
-        seq[:n_real] = [s + n for s, n in zip(starts, lens)]
+        seq = np.asarray([max(1, n) for n in lens], dtype=np.int32)      # a dummy request is as long as its tokens
         ids = np.zeros(T, dtype=np.int32)
         pos = np.zeros(T, dtype=np.int32)
         rows: List[int] = []
-        for i, e in enumerate(entries):
-            a, b = cu[i], cu[i + 1]
+        for j, (i, n) in enumerate(slots):
+            a, b = cu[j], cu[j + 1]
+            if i < 0:
+                pos[a:b] = np.arange(n, dtype=np.int32)
+                continue
+            e = entries[i]
+            seq[j] = starts[i] + n
             ids[a:b] = np.asarray(e.tokens, dtype=np.int64)
-            pos[a:b] = np.arange(starts[i], starts[i] + lens[i], dtype=np.int32)
+            pos[a:b] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
             for w in e.want:
-                if not (0 <= w < lens[i]):
-                    raise ValueError(f"request {e.req_id!r}: wanted place {w} is outside its {lens[i]} tokens")
+                if not (0 <= w < n):
+                    raise ValueError(f"request {e.req_id!r}: wanted place {w} is outside its {n} tokens")
                 rows.append(int(a) + int(w))
-        if pad_reqs is not None:
-            rows_np = np.arange(T, dtype=np.int32)
+        if every_place:
+            rows_np = np.asarray([max(0, int(cu[j + 1]) - 1) if lens[j] else 0 for j in range(B)], dtype=np.int32)
         else:
             rows_np = np.asarray(rows, dtype=np.int32)
         if table_width is not None:
             width = table_width
         else:
-            width = max(1, max((int(s) + bs - 1) // bs for s in seq)) if B else 1
+            width = max(1, max((int(s_) + bs - 1) // bs for s_ in seq)) if B else 1
         if width > self.max_blocks:
             raise ValueError(f"a request needs {width} pages, the plan buffers hold {self.max_blocks}")
-        tables, slots = [], []
+        tables, slot_maps = [], []
         for g in range(len(m.groups)):
             tab = np.full((B, width), -1, dtype=np.int32)
             sl = np.full(T, -1, dtype=np.int32)
-            for i, e in enumerate(entries):
-                t = m.block_table(e.req_id, g)
-                n = min(len(t), width)
-                tab[i, :n] = t[:n]
-                p = pos[cu[i]:cu[i + 1]]
-                blk = tab[i, p // bs]
-                sl[cu[i]:cu[i + 1]] = np.where(blk >= 0, blk * bs + p % bs, -1)
+            for j, (i, n) in enumerate(slots):
+                if i < 0:
+                    continue
+                t = m.block_table(entries[i].req_id, g)
+                k = min(len(t), width)
+                tab[j, :k] = t[:k]
+                p = pos[cu[j]:cu[j + 1]]
+                blk = tab[j, p // bs]
+                sl[cu[j]:cu[j + 1]] = np.where(blk >= 0, blk * bs + p % bs, -1)
             tables.append(tab)
-            slots.append(sl)
+            slot_maps.append(sl)
         sslots = np.zeros(B, dtype=np.int32)
         fresh = np.zeros(B, dtype=np.int32)
-        sslots[:n_real] = [m.state_slots.slot(e.req_id) for e in entries]
-        fresh[:n_real] = [1 if m.state_slots.take_fresh(e.req_id) else 0 for e in entries]
+        for j, (i, n) in enumerate(slots):
+            if i >= 0:
+                sslots[j] = m.state_slots.slot(entries[i].req_id)
+                fresh[j] = 1 if m.state_slots.take_fresh(entries[i].req_id) else 0
+        slots_ = slot_maps
 
         # pack: the order and the alignment fix every view's offset for given (T, B, R, width)
         k = self._next_turn()
@@ -164,7 +186,7 @@ class PlanBuilder:
         put("ids", ids); put("pos", pos); put("rows", rows_np); put("cu", cu); put("seq", seq)
         put("sslots", sslots); put("fresh", fresh)
         for g in range(len(m.groups)):
-            put(f"slot{g}", slots[g]); put(f"tab{g}", tables[g])
+            put(f"slot{g}", slots_[g]); put(f"tab{g}", tables[g])
         if dev is None:
             dev = self._dev[k]
         self._send(k, off, dev)

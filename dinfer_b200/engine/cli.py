@@ -1,7 +1,7 @@
 """Command line, in the manner of the reference's ``dinfer`` binary (bins/dinfer/src/main.rs:28-151):
 sub-commands, and for the engine options the reference's own flag names and defaults
 (``--model --max-model-len --max-num-seqs --max-num-batched-tokens --num-blocks --block-size
---gpu-memory-utilization --no-cuda-graph --enable-prefix-caching --split-norms --no-async-scheduling --no-decode-exempt
+--gpu-memory-utilization --no-cuda-graph --no-mixed-cuda-graph --enable-prefix-caching --split-norms --no-async-scheduling --no-decode-exempt
 --long-prefill-token-threshold
 --device``).  The reference serves HTTP; this engine starts at token ids, so ``generate`` takes the
 place of ``serve``:
@@ -36,6 +36,8 @@ def _engine_flags(p: argparse.ArgumentParser) -> None:
     p.add_argument("--split-norms", action="store_true",
                    help="decode steps: take the RMSNorms between two products apart into the products' epilogues "
                         "(pays for small models, see EngineConfig.split_norms)")
+    p.add_argument("--no-mixed-cuda-graph", action="store_true",
+                   help="steps with prompt portions always launch their kernels one by one")
     p.add_argument("--no-async-scheduling", action="store_true",
                    help="read every step's tokens before the next step is scheduled (default: one step in flight)")
     p.add_argument("--device", type=int, default=0)
@@ -63,7 +65,8 @@ def cmd_generate(a) -> int:
               decode_exempt_from_budget=not a.no_decode_exempt,
               long_prefill_token_threshold=a.long_prefill_token_threshold,
               enable_cuda_graph=not a.no_cuda_graph, enable_prefix_caching=a.enable_prefix_caching, split_norms=a.split_norms,
-              async_scheduling=not a.no_async_scheduling, device=a.device)
+              async_scheduling=not a.no_async_scheduling, mixed_cuda_graph=not a.no_mixed_cuda_graph,
+              device=a.device)
     sp = SamplingParams(max_tokens=a.max_tokens, min_tokens=a.min_tokens, temperature=a.temperature,
                         top_p=a.top_p, top_k=a.top_k, min_p=a.min_p,
                         repetition_penalty=a.repetition_penalty, frequency_penalty=a.frequency_penalty,

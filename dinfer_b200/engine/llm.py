@@ -69,7 +69,8 @@ class LLM:
                  block_size: int = 16, gpu_memory_utilization: float = 0.9,
                  decode_exempt_from_budget: bool = True, long_prefill_token_threshold: int = 0,
                  enable_cuda_graph: bool = True, enable_prefix_caching: bool = False,
-                 split_norms: bool = False, async_scheduling: bool = True, device: int = 0):
+                 split_norms: bool = False, async_scheduling: bool = True, mixed_cuda_graph: bool = True,
+                 device: int = 0):
         """``model``: a folder with config.json and *.safetensors; or ``config`` (the config.json
         dictionary) with ``weights`` (any WeightSource, e.g. ``RandomSource``)."""
         self.engine_config = EngineConfig(
@@ -79,7 +80,8 @@ class LLM:
             decode_exempt_from_budget=decode_exempt_from_budget,
             long_prefill_token_threshold=long_prefill_token_threshold,
             enable_cuda_graph=enable_cuda_graph, enable_prefix_caching=enable_prefix_caching,
-            split_norms=split_norms, async_scheduling=async_scheduling, dtype=dtype,
+            split_norms=split_norms, async_scheduling=async_scheduling, mixed_cuda_graph=mixed_cuda_graph,
+            dtype=dtype,
             device=device)
         if model is not None:
             self.runner = ModelRunner.from_dir(model, self.engine_config)

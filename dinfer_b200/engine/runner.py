@@ -31,6 +31,9 @@ _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
 class ModelRunner:
+    # prompt portions a captured mixed step has places for (see _mixed_layout)
+    PROMPT_PLACES = 4
+
     def __init__(self, config_dict: Dict[str, Any], source: WeightSource, engine: EngineConfig):
         engine.check()
         if not torch.cuda.is_available():
@@ -58,7 +61,7 @@ class ModelRunner:
         self._make_caches()
         self.plan = PlanBuilder(self.manager, self.device,
                                 max_tokens=engine.max_num_batched_tokens + engine.max_num_seqs,
-                                max_reqs=engine.max_num_seqs,
+                                max_reqs=engine.max_num_seqs + self.PROMPT_PLACES,
                                 max_blocks=self.max_blocks_per_seq)
         # the tokens the last step sampled stay here (a fixed address, so that captured graphs can read it):
         # a step launched before the host has read them names them by row (see StepEntry.tokens)
@@ -155,8 +158,11 @@ class ModelRunner:
                 raise OutOfPages(f"no pages for request {e.req_id!r} ({total} tokens; "
                                  f"{[p.num_free for p in m.pools]} pages free)")
             starts.append(start)
+        mixed = None
         if self._graph_ok and len(entries) <= self._buckets[-1] and all(len(e.tokens) == 1 for e in entries):
             logits = self._graph_step(entries, starts)
+        elif self._graph_ok and (mixed := self._mixed_layout(entries)) is not None:
+            logits = self._mixed_graph_step(entries, starts, *mixed)
         else:
             ids, rows, ctx = self.plan.build(entries, starts)
             ctx.split_norms = bool(self.engine.split_norms)
@@ -182,8 +188,9 @@ class ModelRunner:
             b *= 2
         buckets.append(e.max_num_seqs)
         self._buckets = buckets
-        self._graphs: Dict[int, Any] = {}
+        self._graphs: Dict[Any, Any] = {}
         self._graph_pool = None
+        self._mixed_seen: Dict[int, int] = {}
 
     def _capture(self, bucket: int):
         from ..kernels import attention_ops
@@ -228,6 +235,65 @@ class ModelRunner:
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
         if len(wanted) == B:
             return rec["logits"][:B]         # valid until the next step of this bucket
+        if not wanted:
+            return rec["logits"][:0]
+        return rec["logits"][torch.tensor(wanted, device=self.device)]
+
+    # ---- steps that fill the token budget with prompt portions replay a captured graph too
+    def _mixed_layout(self, entries: Sequence[StepEntry]):
+        """A step whose prompt portions (at most ``PROMPT_PLACES``) add up to exactly the token budget, beside any
+        number of decoded tokens, has a fixed shape but for the number of decoded tokens: the steady state while
+        prompts are taken in.  Such steps replay a graph per decode bucket, laid out as ``PROMPT_PLACES`` prompt
+        places (the unused ones without tokens) followed by the bucket's one-token places (the unused ones dummy
+        rows).  Returns (bucket, places) or None when the step is not of that shape (it then runs eagerly).  A
+        bucket is captured when it comes up the second time."""
+        if not self.engine.mixed_cuda_graph:
+            return None
+        budget = self.engine.max_num_batched_tokens
+        prompts = [i for i, e in enumerate(entries) if len(e.tokens) > 1]
+        decodes = [i for i, e in enumerate(entries) if len(e.tokens) == 1]
+        if not (1 <= len(prompts) <= self.PROMPT_PLACES) or sum(len(entries[i].tokens) for i in prompts) != budget:
+            return None
+        if any(tuple(e.want) not in ((), (len(e.tokens) - 1,)) for e in entries):
+            return None                                      # only the last token's logits come out of a place
+        bucket = 0 if not decodes else next((b for b in self._buckets if b >= len(decodes)), None)
+        if bucket is None:
+            return None
+        key = ("mixed", bucket)
+        if key not in self._graphs:
+            self._mixed_seen[bucket] = self._mixed_seen.get(bucket, 0) + 1
+            if self._mixed_seen[bucket] < 2:
+                return None
+        places = [(i, len(entries[i].tokens)) for i in prompts] + [(-1, 0)] * (self.PROMPT_PLACES - len(prompts))
+        places += [(i, 1) for i in decodes] + [(-1, 1)] * (bucket - len(decodes))
+        return bucket, places
+
+    def _capture_mixed(self, bucket: int):
+        from ..kernels import attention_ops
+        width = self.max_blocks_per_seq
+        budget = self.engine.max_num_batched_tokens
+        B = self.PROMPT_PLACES + bucket
+        dev = torch.empty(self.plan.words(budget + bucket, B, B, width), dtype=torch.int32, device=self.device)
+        # captured on a dummy batch of the same shape: one prompt place with the whole budget (no pages, no slots)
+        places = [(-1, budget)] + [(-1, 0)] * (self.PROMPT_PLACES - 1) + [(-1, 1)] * bucket
+        ids, rows, ctx = self.plan.build([], [], table_width=width, dev=dev, slots=places)
+        hkv = max([n.num_kv_heads for n in self.model.cache_needs() if isinstance(n, KvCacheNeed)] or [1])
+        ctx.decode_splits = attention_ops.decode_splits(max(1, bucket), hkv, self.engine.max_model_len)
+        ctx.max_seq_len = self.engine.max_model_len
+        ctx.split_norms = False
+        ctx.prev_tokens = self.sampled
+        rec = self._capture_one(ids, rows, ctx)
+        rec.update(dev=dev, width=width)
+        self._graphs[("mixed", bucket)] = rec
+        return rec
+
+    def _mixed_graph_step(self, entries: Sequence[StepEntry], starts: Sequence[int], bucket: int, places) -> torch.Tensor:
+        rec = self._graphs.get(("mixed", bucket)) or self._capture_mixed(bucket)
+        self.plan.build(entries, starts, table_width=rec["width"], dev=rec["dev"], slots=places)
+        rec["graph"].replay()
+        kernel_lib.add_launches(rec["launches"])
+        place_of = {i: j for j, (i, _) in enumerate(places) if i >= 0}
+        wanted = [place_of[i] for i, e in enumerate(entries) if len(e.want)]
         if not wanted:
             return rec["logits"][:0]
         return rec["logits"][torch.tensor(wanted, device=self.device)]
