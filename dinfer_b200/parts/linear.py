@@ -10,8 +10,8 @@ Which product runs follows from the dtypes and the number of rows at hand:
     crates/kernels/cuda/gemm_small_m.cu:148-285);
   * bfloat16 with more rows (prompts): the library product, where the reference's engine uses
     cuBLASLt (crates/kernels/src/gemm.rs:649-690), or the tcgen05 kernel when ``PROMPT_BACKEND`` says so;
-    the gated pair product of the feed-forward is this package's tcgen05 kernel at every number of rows, with
-    silu(gate) * up in its epilogue.
+    the gated pair product of the feed-forward is this package's two-SM tcgen05 kernel from
+    ``TC_MIN_GATED_PROMPT_TOKENS`` rows on, with silu(gate) * up in its epilogue.
 """
 from __future__ import annotations
 
@@ -27,6 +27,10 @@ from .base import HalfNormed
 TC_MAX_DECODE_TOKENS = 32
 # "library" or "tc": who multiplies prompts (more rows than the decode threshold)
 PROMPT_BACKEND = "library"
+# rows from which the gated pair product runs on the two-SM tcgen05 kernel with the gate in its epilogue; between
+# the two thresholds the library product followed by the gate kernel is faster (measured at the 0.6B, 8B and 32B
+# shapes: 38.7 against 42.7 us at 33 rows, 43.4 against 55.4 at 128, even at 512, 280 against 300 at 2048)
+TC_MIN_GATED_PROMPT_TOKENS = 512
 
 
 class Linear:
@@ -41,8 +45,10 @@ class Linear:
 
     def fuses_gate(self, x: torch.Tensor) -> bool:
         """Whether ``gated_pairs`` runs as one kernel for these rows: the tcgen05 product with the gate in its
-        epilogue, at any number of rows (with the gate kernel saved it is ahead of the library for prompts too)."""
+        epilogue, for decode steps and for prompt portions that are long enough."""
+        rows = x.shape[0]
         return (x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16
+                and (rows <= TC_MAX_DECODE_TOKENS or rows >= TC_MIN_GATED_PROMPT_TOKENS)
                 and self.out_features % 2 == 0 and gemm_ops.supported(x, self.weight))
 
     def fuses_norm(self, rows: int, act_dtype: torch.dtype) -> bool:
