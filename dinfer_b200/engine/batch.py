@@ -12,7 +12,7 @@ address and shape (crates/layers/src/exec.rs:226-247,392-404 does the same paddi
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np

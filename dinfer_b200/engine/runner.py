@@ -12,7 +12,6 @@ models/qwen3/src/model.rs:684-832), with sampling kept out of it.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import Any, Dict, Hashable, List, Sequence
 
 import torch

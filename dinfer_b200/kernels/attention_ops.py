@@ -6,7 +6,7 @@ from typing import Optional
 
 import torch
 
-from .lib import KernelError, check, library, ptr, require_cuda, stream_handle
+from .lib import KernelError, check, ptr, require_cuda, stream_handle
 from .ops import _fn
 
 NUM_SMS = 148

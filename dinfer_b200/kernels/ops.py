@@ -5,7 +5,6 @@ explicit strides and the live token count, and launches on torch's current strea
 """
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_int64, c_void_p
 from typing import Optional
 
