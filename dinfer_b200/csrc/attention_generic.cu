@@ -55,8 +55,9 @@ attention_generic_kernel(const T* __restrict__ q, int64_t ldq, T* __restrict__ o
       const int j = j0 + u;
       kp[u] = nullptr;
       s[u] = 0.f;
-      if (j <= pos) {
-        const int64_t blk = table[j / block_size];
+      // a page the table does not hold (-1: a dummy row of a captured graph, a page a window has passed) is no key
+      const int64_t blk = j <= pos ? table[j / block_size] : -1;
+      if (blk >= 0) {
         kp[u] = cache + blk * 2 * plane + ((int64_t)hk * block_size + j % block_size) * D;
 #pragma unroll
         for (int c = 0; c < C; ++c) {
@@ -70,6 +71,7 @@ attention_generic_kernel(const T* __restrict__ q, int64_t ldq, T* __restrict__ o
     float m_new = m;
 #pragma unroll
     for (int u = 0; u < KEYS; ++u) m_new = fmaxf(m_new, s[u]);
+    if (m_new == -INFINITY) continue;                            // no key so far
     const float alpha = expf(m - m_new);
     l *= alpha;
 #pragma unroll
@@ -89,7 +91,7 @@ attention_generic_kernel(const T* __restrict__ q, int64_t ldq, T* __restrict__ o
     }
     m = m_new;
   }
-  const float inv = 1.f / l;
+  const float inv = l > 0.f ? 1.f / l : 0.f;                      // a row without keys gives zeros
 #pragma unroll
   for (int c = 0; c < C; ++c) {
     const int e = lane + 32 * c;

@@ -18,8 +18,10 @@
 // rewritten: the three filters reduce to one keep-threshold on the scaled logits.  The top-k and the
 // top-p threshold are each found by a radix-16 descent over the order-preserving 32-bit image of a
 // float (eight rounds, every round one pass over shared memory): the largest value t such that the
-// kept entries >= t number at least k (have at least the share p of the mass).  All sums are taken in
-// a fixed order (thread, warp, CTA rank), so the same logits, seed and count give the same token.
+// kept entries >= t number at least k (have at least the share p of the mass).  A small k (up to 512)
+// takes a short way instead: a histogram names the bin of the k-th largest entry, the entries from
+// there up are collected in every CTA, and both thresholds are counted out among them.  All sums are
+// taken in a fixed order (thread, warp, CTA rank), so the same logits, seed and count give the same token.
 #include "common.cuh"
 
 using namespace dinfer;
@@ -228,6 +230,170 @@ __device__ float radix_threshold(Shared& sh, const Slice& sl, uint32_t rank, flo
   return key_float(prefix);
 }
 
+// ---- the short way to a top-k threshold (and the top-p threshold behind it) when k is small
+// One pass counts the kept entries by the upper 12 bits of their key (a histogram in shared memory; the CTAs
+// read each other's counts), which names the bin that holds the k-th largest entry; the entries from that bin
+// up, at most CAND_MAX of them, are copied into every CTA in vocabulary order, and the thresholds are found
+// among them by direct counting.  With more entries than that from the bin up, the radix descent does it.
+constexpr int CAND_MAX = 1024;
+constexpr int HIST_BITS = 12, HIST_BINS = 1 << HIST_BITS, BINS_PER_CTA = HIST_BINS / ROW_CTAS;
+static_assert(BINS_PER_CTA <= BLOCK, "a thread per bin of a CTA's share");
+
+struct Candidates {
+  uint32_t hist[HIST_BINS];
+  float x[CAND_MAX];                  // the candidates, the same list in every CTA of the row
+  float w[CAND_MAX];                  // their weights exp(x - m), 0 below the floor
+  int warp_tot[BLOCK / 32];
+  int n;
+  float thr;
+};
+
+__device__ __forceinline__ uint32_t ld_cluster_u32(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote, v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+// inclusive prefix sum of v over the threads of the block, in thread order; `total` is the block's sum
+__device__ int block_scan_inclusive(int v, int* warp_tot, int& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int u = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += u;
+  }
+  __syncthreads();
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  int before = 0, all = 0;
+#pragma unroll
+  for (int w = 0; w < BLOCK / 32; ++w) {
+    const int t = warp_tot[w];
+    if (w < warp) before += t;
+    all += t;
+  }
+  total = all;
+  return incl + before;
+}
+
+// Fills c.x with the kept entries (x >= floor_) from the bin of the k-th largest up; returns their number, or -1
+// if they are more than CAND_MAX.  With fewer than k kept entries all of them are candidates.
+__device__ int gather_candidates(Shared& sh, Candidates& c, const Slice& sl, uint32_t rank, float floor_, int k) {
+  const int i0 = min(sl.n_mine, (int)threadIdx.x * sl.seg), i1 = min(sl.n_mine, i0 + sl.seg);
+  for (int i = threadIdx.x; i < HIST_BINS; i += BLOCK) c.hist[i] = 0u;
+  __syncthreads();
+  for (int i = i0; i < i1; ++i) {
+    const float x = sl.at(i);
+    if (x >= floor_) atomicAdd(&c.hist[float_key(x) >> (32 - HIST_BITS)], 1u);
+  }
+  __syncthreads();
+  cluster_sync_all();
+  // this CTA adds up the bins [rank * BINS_PER_CTA, +BINS_PER_CTA) over all CTAs; thread u takes them from the top
+  int v = 0;
+  const int bin = (int)rank * BINS_PER_CTA + (BINS_PER_CTA - 1 - (int)threadIdx.x);
+  if ((int)threadIdx.x < BINS_PER_CTA) {
+#pragma unroll
+    for (uint32_t r = 0; r < ROW_CTAS; ++r) v += (int)ld_cluster_u32(smem_u32(&c.hist[bin]), r);
+  }
+  int mine_total;
+  const int incl = block_scan_inclusive(v, c.warp_tot, mine_total);     // entries of my bins from `bin` up
+  float (*x)[XCH] = exchange(sh, threadIdx.x == 0 ? (float)mine_total : 0.f, 1, rank);
+  int above = 0, kept = 0;
+#pragma unroll
+  for (int r = 0; r < ROW_CTAS; ++r) {
+    const int t = (int)x[r][0];
+    kept += t;
+    if (r > (int)rank) above += t;
+  }
+  // the bin where the count from the top reaches k: at most one thread of the row finds it
+  if (threadIdx.x < 2) sh.blk[threadIdx.x] = -1.f;
+  __syncthreads();
+  if ((int)threadIdx.x < BINS_PER_CTA && v > 0 && above + incl - v < k && above + incl >= k) {
+    sh.blk[0] = (float)bin;
+    sh.blk[1] = (float)(above + incl);
+  }
+  __syncthreads();
+  x = exchange(sh, threadIdx.x < 2 ? sh.blk[threadIdx.x] : 0.f, 2, rank);
+  int pivot_bin = 0, n = kept;                           // fewer than k kept: all of them
+#pragma unroll
+  for (int r = 0; r < ROW_CTAS; ++r)
+    if (x[r][0] >= 0.f) { pivot_bin = (int)x[r][0]; n = (int)x[r][1]; }
+  if (n > CAND_MAX) return -1;
+  // copy them into every CTA, in vocabulary order
+  int cnt = 0;
+  for (int i = i0; i < i1; ++i) {
+    const float xv = sl.at(i);
+    cnt += xv >= floor_ && (int)(float_key(xv) >> (32 - HIST_BITS)) >= pivot_bin;
+  }
+  int cta_total;
+  const int my_end = block_scan_inclusive(cnt, c.warp_tot, cta_total);
+  x = exchange(sh, threadIdx.x == 0 ? (float)cta_total : 0.f, 1, rank);
+  int base = 0;
+#pragma unroll
+  for (int r = 0; r < ROW_CTAS; ++r)
+    if (r < (int)rank) base += (int)x[r][0];
+  int at = base + my_end - cnt;
+  for (int i = i0; i < i1 && cnt > 0; ++i) {
+    const float xv = sl.at(i);
+    if (xv >= floor_ && (int)(float_key(xv) >> (32 - HIST_BITS)) >= pivot_bin) {
+      const uint32_t dst = smem_u32(&c.x[at]);
+#pragma unroll
+      for (uint32_t r = 0; r < ROW_CTAS; ++r) st_cluster_f32(dst, r, xv);
+      ++at;
+    }
+  }
+  cluster_sync_all();
+  __syncthreads();
+  return n;
+}
+
+// the k-th largest of the n candidates (all kept if they are fewer than k)
+__device__ float topk_of_candidates(Candidates& c, int n, int k) {
+  if (threadIdx.x == 0) c.thr = -INFINITY;
+  __syncthreads();
+  if (k <= n && (int)threadIdx.x < n) {
+    const float v = c.x[threadIdx.x];
+    int before = 0;                                      // candidates that come before this one, larger first
+    for (int j = 0; j < n; ++j) {
+      const float xj = c.x[j];
+      before += xj > v || (xj == v && j < (int)threadIdx.x);
+    }
+    if (before == k - 1) c.thr = v;
+  }
+  __syncthreads();
+  return c.thr;
+}
+
+// the largest candidate value v >= floor_ such that the candidates >= v hold at least the share p of the mass of
+// those >= floor_; every thread adds the masses in the same order
+__device__ float topp_of_candidates(Candidates& c, int n, float m, float floor_, float p) {
+  for (int j = threadIdx.x; j < n; j += BLOCK) c.w[j] = c.x[j] >= floor_ ? expf(c.x[j] - m) : 0.f;
+  __syncthreads();
+  float best = -INFINITY;
+  if ((int)threadIdx.x < n) {
+    const float v = c.x[threadIdx.x];
+    float denom = 0.f, mass = 0.f;
+    for (int j = 0; j < n; ++j) {
+      const float wj = c.w[j];
+      denom += wj;
+      if (c.x[j] >= v) mass += wj;
+    }
+    if (v >= floor_ && mass >= p * denom) best = v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) c.w[threadIdx.x >> 5] = best;            // the weights are done with
+  __syncthreads();
+  float all = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < BLOCK / 32; ++w) all = fmaxf(all, c.w[w]);
+  __syncthreads();
+  return all;
+}
+
 __global__ void __launch_bounds__(BLOCK)
 argmax_kernel(const float* __restrict__ logits, int64_t ld, int* __restrict__ out, int vocab) {
   extern __shared__ __align__(16) float xs_dyn[];
@@ -253,6 +419,7 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, const float* __restr
               int* __restrict__ out, int vocab, int cache_slice) {
   extern __shared__ __align__(16) float xs_dyn[];
   __shared__ Shared sh;
+  __shared__ Candidates cand;
   pdl_enter();
   const uint32_t rank = cluster_ctarank();
   const int b = blockIdx.x / ROW_CTAS;
@@ -310,10 +477,17 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, const float* __restr
   const float mp = min_p ? min_p[b] : 0.f;
   if (mp > 0.f) thr = m + logf(mp);                      // p_i >= min_p * p_max
   const int k = top_k ? top_k[b] : -1;
-  if (k > 0 && k < vocab) thr = fmaxf(thr, radix_threshold<false>(sh, sl, rank, m, thr, (float)k));
+  int n_cand = -1;                                       // >= 0: cand holds every entry from the top-k threshold up
+  if (k > 0 && k < vocab) {
+    if (k <= CAND_MAX / 2) n_cand = gather_candidates(sh, cand, sl, rank, thr, k);
+    if (n_cand >= 0) thr = fmaxf(thr, topk_of_candidates(cand, n_cand, k));
+    else thr = fmaxf(thr, radix_threshold<false>(sh, sl, rank, m, thr, (float)k));
+  }
   const float p = top_p ? top_p[b] : 1.f;
   const int i0 = min(n_mine, (int)threadIdx.x * sl.seg), i1 = min(n_mine, i0 + sl.seg);
-  if (p < 1.f && p > 0.f) {
+  if (p < 1.f && p > 0.f && n_cand >= 0) {
+    thr = fmaxf(thr, topp_of_candidates(cand, n_cand, m, thr, p));
+  } else if (p < 1.f && p > 0.f) {
     float d1[1] = {0.f}, denom[1];
     for (int i = i0; i < i1; ++i) {
       const float x = sl.at(i);

@@ -312,3 +312,73 @@ def test_logprobs_and_logit_bias(V, ld, k):
         want_b[r_, t_] += b_
     assert torch.equal(logits, want_b)
     assert torch.equal(full[:, V:], full[:, V:])                        # the padding of the rows is untouched
+
+
+def test_top_k_the_short_way_and_its_fallbacks():
+    """A small k takes the candidate list, a large one or a crowded bin the radix descent; fewer kept entries than
+    k keep them all.  Every way must keep the same set as the plain sampler: same tokens for the same draws."""
+    from dinfer_b200.sampling import sampler as S
+    g = torch.Generator().manual_seed(77)
+    V = 20011
+    rows = []
+    base = torch.randn(V, generator=g) * 3
+    rows.append((base.clone(), 512, 1.0, 0.0))                 # the largest k of the short way
+    rows.append((base.clone(), 513, 0.9, 0.0))                 # just beyond it: radix
+    crowded = base.clone()
+    crowded[100:6100] = float(base.max()) + 1.0                # 6000 equal values at the top: the bin overflows
+    rows.append((crowded, 10, 1.0, 0.0))                       # (all 6000 ties are kept)
+    rows.append((base.clone(), 50, 0.7, 0.3))                  # min_p leaves fewer than k
+    tied = base.clone()
+    tied[[5, 900, 15000]] = float(base.max()) + 2.0            # ties across the k-th place are all kept
+    rows.append((tied, 2, 1.0, 0.0))
+    rows.append((base.clone(), 1, 0.5, 0.0))
+    logits = torch.stack([r[0] for r in rows])
+    R = len(rows)
+    d = dev(logits)
+    temps = torch.full((R,), 0.9)
+    topk = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    topp = torch.tensor([r[2] for r in rows])
+    minp = torch.tensor([r[3] for r in rows])
+    agree = total = 0
+    for off in range(30):
+        seeds = torch.arange(R, dtype=torch.int64) + 3
+        offs = torch.full((R,), off, dtype=torch.int64)
+        got = S.sample(d, dev(temps), dev(seeds), dev(offs), top_k=dev(topk), top_p=dev(topp), min_p=dev(minp)).cpu()
+        for i in range(R):
+            want = P.sample_token(logits[i], float(temps[i]), int(seeds[i]), off, int(topk[i]), float(topp[i]),
+                                  float(minp[i]))
+            total += 1
+            agree += int(got[i]) == want
+    assert agree >= total - 2, f"{agree}/{total}"
+    got = S.sample(d, dev(temps), dev(seeds), dev(offs), top_k=dev(topk), top_p=dev(topp), min_p=dev(minp)).cpu()
+    assert int(got[5]) == int(torch.argmax(base)) and int(got[4]) in (5, 900, 15000)
+    # top-p over thousands of exact ties: the threshold keeps all entries of a value or none (as the reference's
+    # kernel does, crates/kernels/cuda/sampling.cu:99-124), where a sort would cut through them
+    topp2 = topp.clone()
+    topp2[2] = 0.8
+    seen = set()
+    for off in range(40):
+        offs = torch.full((R,), off, dtype=torch.int64)
+        seen.add(int(S.sample(d, dev(temps), dev(seeds), dev(offs), top_k=dev(topk), top_p=dev(topp2), min_p=dev(minp)).cpu()[2]))
+    assert all(100 <= t < 6100 for t in seen) and max(seen) > 100 + 0.9 * 6000
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_attention_generic_without_pages(dt):
+    """A request whose table holds no page (a dummy row of a captured graph) has no keys: its output is zero and
+    nothing outside the cache is read; the request beside it is untouched by it."""
+    from dinfer_b200.kernels import ops
+    H_, Hkv, D, bs = 4, 2, 24, 4
+    g = torch.Generator().manual_seed(5)
+    cache = dev(torch.randn(6, 2, Hkv, bs, D, generator=g)).to(dt)
+    q = dev(torch.randn(2, H_ * D, generator=g)).to(dt)
+    out = torch.full((2, H_ * D), float("nan"), dtype=dt, device="cuda")
+    table = dev(torch.tensor([[-1, -1], [3, 1]], dtype=torch.int32))
+    cu = dev(torch.tensor([0, 1, 2], dtype=torch.int32))
+    pos = dev(torch.tensor([0, 5], dtype=torch.int32))
+    ops.attention_generic(q, out, cache, table, cu, pos, H_, Hkv, D, D ** -0.5, 0)
+    assert torch.equal(out[0].float(), torch.zeros(H_ * D, device="cuda"))
+    alone = torch.empty((1, H_ * D), dtype=dt, device="cuda")
+    ops.attention_generic(q[1:], alone, cache, table[1:], dev(torch.tensor([0, 1], dtype=torch.int32)), pos[1:],
+                          H_, Hkv, D, D ** -0.5, 0)
+    assert torch.equal(out[1], alone[0]) and torch.isfinite(out[1].float()).all()
