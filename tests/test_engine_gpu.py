@@ -430,3 +430,43 @@ def test_budget_filling_steps_replay_a_graph(dirs, tmp_path, dtype):
     else:
         agree = sum(a == b for x, y in zip(res[False], res[True]) for a, b in zip(x, y))
         assert agree >= 0.8 * sum(len(x) for x in res[False])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_whole_and_in_portions(tmp_path, dtype):
+    """4,400 tokens through the step function whole, in portions of 512 (which replay the graph of budget-filling
+    steps from the second one on) and in portions of 1000 launched kernel by kernel, then 40 tokens decoded one by
+    one after each: page tables longer than the kernels' shared-memory slices, long histories behind a portion.
+    The logits at the compared places agree within the dtype's rounding."""
+    from dinfer_b200.config.engine_config import EngineConfig
+    from dinfer_b200.engine.batch import StepEntry
+    from dinfer_b200.engine.runner import ModelRunner
+    cfg = dict(H.TINY_D, max_position_embeddings=8192, num_hidden_layers=2)
+    d = H.make_model_dir(str(tmp_path / "long"), cfg, *H.INIT["D"], torch.float32 if dtype == "float32" else torch.bfloat16)
+    rng = random.Random(8)
+    toks = H.random_tokens(rng, 4440, cfg["vocab_size"])
+    n0 = 4400
+    results = []
+    for budget in (4608, 512, 1000):
+        r = ModelRunner.from_dir(d, EngineConfig(max_model_len=4608, max_num_seqs=4, max_num_batched_tokens=budget,
+                                                 num_blocks=4608 // 16 + 8, block_size=16, dtype=dtype))
+        got = []
+        at = 0
+        while at < n0:
+            n = min(budget, n0 - at)
+            want = [n - 1] if at + n == n0 else ([n - 1] if (at // budget) % 3 == 0 else [])
+            out = r.step([StepEntry("a", toks[at:at + n], want)])
+            if at + n == n0:
+                got.append(out[-1].float().cpu())
+            at += n
+        for t in toks[n0:]:
+            got.append(r.step([StepEntry("a", [t], [0])])[0].float().cpu())
+        if budget == 512:
+            assert ("mixed", 0) in r._graphs
+        r.finish("a")
+        r.check_device_status()
+        results.append(torch.stack(got))
+    scale = float(results[0].abs().max())
+    tol = 1e-4 if dtype == "float32" else 2e-2
+    for other in results[1:]:
+        assert float((other - results[0]).abs().max()) <= tol * scale
