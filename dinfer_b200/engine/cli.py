@@ -1,14 +1,14 @@
 """Command line, in the manner of the reference's ``dinfer`` binary (bins/dinfer/src/main.rs:28-151):
 sub-commands, and for the engine options the reference's own flag names and defaults
 (``--model --max-model-len --max-num-seqs --max-num-batched-tokens --num-blocks --block-size
---gpu-memory-utilization --no-cuda-graph --no-mixed-cuda-graph --enable-prefix-caching --split-norms --no-async-scheduling --no-decode-exempt
---long-prefill-token-threshold
---device``).  The reference serves HTTP; this engine starts at token ids, so ``generate`` takes the
+--gpu-memory-utilization --no-cuda-graph --no-mixed-cuda-graph --enable-prefix-caching --split-norms
+--no-async-scheduling --no-decode-exempt --long-prefill-token-threshold --device``).  The reference serves HTTP; this engine starts at token ids, so ``generate`` takes the
 place of ``serve``:
 
     dinfer generate --model DIR --prompt-ids 1,2,3 --prompt-ids 4,5 --max-tokens 16 --temperature 0
     dinfer random-model --config config.json --out DIR --seed 0
     dinfer device-info
+    dinfer replay --model DIR --dtype bfloat16 --out DIR --max-tokens N < steps.jsonl     (= bin/trace_run)
 """
 from __future__ import annotations
 
@@ -112,7 +112,22 @@ def cmd_device_info(a) -> int:
     return 0
 
 
+def cmd_replay(rest) -> int:
+    import os
+    import runpy
+    script = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "bin", "trace_run")
+    sys.argv = [script] + list(rest)
+    try:
+        runpy.run_path(script, run_name="__main__")
+    except SystemExit as e:
+        return int(e.code or 0)
+    return 0
+
+
 def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] == "replay":                     # everything behind it belongs to trace_run
+        return cmd_replay(argv[1:])
     ap = argparse.ArgumentParser(prog="dinfer", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -146,6 +161,8 @@ def main(argv=None) -> int:
     r.set_defaults(fn=cmd_random_model)
     d = sub.add_parser("device-info", help="list the CUDA devices")
     d.set_defaults(fn=cmd_device_info)
+    sub.add_parser("replay", help="trace replay: the arguments and the standard input of bin/trace_run",
+                   add_help=False)
     a = ap.parse_args(argv)
     return a.fn(a)
 
