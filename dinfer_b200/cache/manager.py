@@ -169,22 +169,24 @@ class CacheManager:
     def advance(self, req: Hashable, num_computed: int, new_tokens: Optional[Sequence[int]] = None) -> None:
         """The cache now holds the keys of the first ``num_computed`` tokens: give back the pages
         that every window has passed.  With the prefix cache, ``new_tokens`` are the ids of the tokens
-        computed since the last call; pages they fill become findable."""
+        computed since the last call; pages they fill become findable.  An id that is not known yet (negative: a
+        token the device still holds, see ``resolve``) may stand at the end of them."""
         held = self._reqs[req]
         if num_computed > held.num_tokens:
             raise PoolError(f"request {req!r}: {num_computed} tokens computed but pages cover {held.num_tokens}")
         if self.prefix_caching and new_tokens is not None:
-            if len(held.tokens) + len(new_tokens) != num_computed:
+            known = [int(t) for t in new_tokens]
+            while known and known[-1] < 0:
+                known.pop()
+            if any(t < 0 for t in known):
+                raise PoolError(f"request {req!r}: an unknown token before a known one")
+            behind = len(held.tokens) + len(new_tokens) - num_computed     # tokens earlier calls left unknown
+            if behind > 0 or (behind < 0 and known):
                 raise PoolError(f"request {req!r}: {len(held.tokens)} known + {len(new_tokens)} new tokens "
                                 f"do not make {num_computed}")
-            held.tokens.extend(int(t) for t in new_tokens)
-            bs = self.block_size
-            while (len(held.hashes) + 1) * bs <= num_computed:
-                i = len(held.hashes)
-                h = chain_hash(held.hashes[-1] if held.hashes else b"", held.tokens[i * bs:(i + 1) * bs])
-                held.hashes.append(h)
-                for g, pool in enumerate(self.pools):
-                    pool.set_hash(held.tables[g][i], h)     # stays unhashed if another page holds these contents
+            held.tokens.extend(known)
+            held.num_computed = num_computed
+            self._hash_full_pages(held)
         held.num_computed = num_computed
         for g in range(len(self.groups)):
             if self.groups[g].window is None:
@@ -195,6 +197,27 @@ class CacheManager:
             self.pools[g].free([table[i] for i in gone])
             for i in gone:
                 table[i] = -1
+
+    def resolve(self, req: Hashable, tokens: Sequence[int]) -> None:
+        """The ids of tokens that ``advance`` was told of as unknown, in order, now that the host has read them."""
+        held = self._reqs.get(req)
+        if held is None or not self.prefix_caching:
+            return
+        if len(held.tokens) + len(tokens) > held.num_computed:
+            raise PoolError(f"request {req!r}: more tokens resolved than were computed")
+        held.tokens.extend(int(t) for t in tokens)
+        self._hash_full_pages(held)
+
+    def _hash_full_pages(self, held: _Held) -> None:
+        """Pages whose tokens are all computed and known get their hash (and become findable)."""
+        bs = self.block_size
+        ready = min(len(held.tokens), held.num_computed)
+        while (len(held.hashes) + 1) * bs <= ready:
+            i = len(held.hashes)
+            h = chain_hash(held.hashes[-1] if held.hashes else b"", held.tokens[i * bs:(i + 1) * bs])
+            held.hashes.append(h)
+            for g, pool in enumerate(self.pools):
+                pool.set_hash(held.tables[g][i], h)     # stays unhashed if another page holds these contents
 
     def free(self, req: Hashable) -> None:
         """The request ends (or is preempted): all its pages and its state slot go back."""

@@ -42,8 +42,8 @@ class EngineConfig:
     split_norms: bool = False
     # the next step is scheduled and launched while the last one still runs; the host reads a step's tokens one
     # step late (the reference's ASYNC_SCHED, on by default there too: crates/core/src/engine.rs:153,822).
-    # Steps with penalties (which need the token history on the host) and the prefix cache (which hashes
-    # token values) run one at a time whatever this says.
+    # Steps with penalties or log-probabilities (which need the last tokens on the host) run one at a time
+    # whatever this says.
     async_scheduling: bool = True
     # "bfloat16" = what serving uses; "float32" = everything in true 32-bit
     dtype: str = "bfloat16"

@@ -60,6 +60,7 @@ class _InFlight:
         self.host: Optional[torch.Tensor] = None
         self.event: Optional[torch.cuda.Event] = None
         self.logprobs = None                # (ids, logprobs, rank) on the device, if a row asked for them
+        self.taken_ahead = set()            # requests whose token of this step the next step took on the device
 
 
 class LLM:
@@ -96,7 +97,7 @@ class LLM:
         self._requests: Dict[Hashable, Request] = {}
         # scheduling ahead: the step in flight, and pinned buffers its tokens are copied to (two: one being
         # read by the host while the next step's copy is queued)
-        self._ahead = bool(self.engine_config.async_scheduling) and not self.engine_config.enable_prefix_caching
+        self._ahead = bool(self.engine_config.async_scheduling)
         self._inflight: Optional[_InFlight] = None
         self._num_penalized = 0
         rows = self.runner.sampled.numel()
@@ -173,6 +174,7 @@ class LLM:
             end = s.start + s.num_tokens
             if end > r.num_tokens:                  # its newest token is still on the device: named by its row
                 toks = r.tokens(s.start, r.num_tokens) + [-(prev_row[r.req_id] + 1)]
+                self._inflight.taken_ahead.add(r.req_id)
             else:
                 toks = r.tokens(s.start, end)
             entries.append(StepEntry(r.req_id, toks, [s.num_tokens - 1] if s.samples else []))
@@ -208,6 +210,11 @@ class LLM:
             sampled = {r.req_id: t for r, t in zip(flight.samplers, host)}
             self.stats.generated_tokens += len(host)
         done = self.scheduler.update(flight.plan, sampled)
+        manager = self.runner.manager
+        if manager.prefix_caching:                  # tokens the next step took on the device: the cache learns them
+            for rid in flight.taken_ahead:
+                if rid in manager:
+                    manager.resolve(rid, [sampled[rid]])
         if flight.logprobs is not None:
             ids, lps, rank = (t.cpu().tolist() for t in flight.logprobs)
             for i, r in enumerate(flight.samplers):

@@ -220,3 +220,28 @@ def test_prefix_cache_random_orders_keep_the_books():
 def test_prefix_cache_refuses_windowed_groups():
     with pytest.raises(ValueError):
         CacheManager([GroupSpec(window=8)], 4, 8, 2, enable_prefix_caching=True)
+
+
+def test_tokens_that_are_not_known_yet():
+    """``advance`` may be told of a computed token whose id the host has not read (negative); the page it
+    completes gets its hash when ``resolve`` brings the id, and not before."""
+    m = CacheManager([GroupSpec()], 4, 16, 4, enable_prefix_caching=True)
+    assert m.allocate("a", 8)
+    m.advance("a", 7, [1, 2, 3, 4, 5, 6, 7])
+    m.advance("a", 8, [-1])                           # computed on the device from the last sampling
+    assert m.begin("probe", [1, 2, 3, 4, 5, 6, 7, 9, 0]) == 4      # only the first page is findable
+    m.free("probe")
+    assert m.allocate("a", 9)
+    m.resolve("a", [9])
+    m.advance("a", 9, [-2])
+    assert m.begin("probe", [1, 2, 3, 4, 5, 6, 7, 9, 0]) == 8
+    m.free("probe")
+    assert m.allocate("a", 10)
+    with pytest.raises(PoolError, match="do not make"):
+        m.advance("a", 10, [33])                      # a known token cannot follow one that is still unknown
+    with pytest.raises(PoolError, match="more tokens resolved"):
+        m.resolve("a", [1, 2])                        # more than was computed
+    m.resolve("a", [11])
+    m.free("a")
+    m.check_invariants()
+    assert m.num_free_blocks() == 16

@@ -470,3 +470,31 @@ def test_a_long_prompt_whole_and_in_portions(tmp_path, dtype):
     tol = 1e-4 if dtype == "float32" else 2e-2
     for other in results[1:]:
         assert float((other - results[0]).abs().max()) <= tol * scale
+
+
+def test_scheduling_ahead_with_the_prefix_cache_on(dirs):
+    """Both of the reference's defaults together: one step in flight and the prefix cache.  Tokens a step took on
+    the device reach the cache manager when the host reads them, so pages of generated tokens become findable
+    too.  32-bit: the same tokens as one step at a time, prefix hits in both, every page back."""
+    from dinfer_b200 import LLM, SamplingParams
+    cfg = H.TINY_B
+    rng = random.Random(31)
+    stem = H.random_tokens(rng, 50, cfg["vocab_size"])
+    prompts = [stem[:rng.choice([20, 35, 50])] + H.random_tokens(rng, rng.choice([1, 5, 30]), cfg["vocab_size"])
+               for _ in range(14)]
+    sp = [SamplingParams(temperature=[0.0, 0.9][i % 2], max_tokens=rng.choice([3, 20, 45]), seed=90 + i,
+                         ignore_eos=True) for i in range(len(prompts))]
+    res = {}
+    for ahead in (False, True):
+        llm = LLM(dirs["B"], dtype="float32", max_model_len=160, max_num_seqs=4, max_num_batched_tokens=32,
+                  num_blocks=24, block_size=16, enable_prefix_caching=True, async_scheduling=ahead)
+        assert llm._ahead == ahead
+        outs = llm.generate(prompts, sp)
+        # a second round repeats the first request with what it generated: found in the cache
+        rep = llm.generate([prompts[0] + outs[0].output_ids + [7]], SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+        res[ahead] = ([o.output_ids for o in outs], rep[0].output_ids)
+        assert llm.stats.prefix_hit_tokens > 0
+        llm.runner.manager.check_invariants()
+        assert llm.runner.manager.num_free_blocks() == 24
+        llm.runner.check_device_status()
+    assert res[False] == res[True]

@@ -211,8 +211,12 @@ def drive(s, m, ahead, token, max_steps=400):
     plans, flight, steps = [], None, 0
 
     def collect(f):
-        plan, toks = f
-        return s.update(plan, toks)
+        plan, toks, ahead_of = f
+        done = s.update(plan, toks)
+        for rid in ahead_of:                        # tokens the next step took without knowing them
+            if rid in m:
+                m.resolve(rid, [toks[rid]])
+        return done
 
     while (s.has_unfinished() or flight is not None) and steps < max_steps:
         steps += 1
@@ -220,18 +224,23 @@ def drive(s, m, ahead, token, max_steps=400):
         toks = {}
         for x in plan.scheduled:
             r = x.request
-            assert r.req_id in m and m.num_tokens(r.req_id) >= x.start + x.num_tokens
+            end = x.start + x.num_tokens
+            assert r.req_id in m and m.num_tokens(r.req_id) >= end
             assert m.num_computed(r.req_id) == x.start
-            assert x.start + x.num_tokens <= r.num_tokens + 1          # at most one token not yet read
-            m.advance(r.req_id, x.start + x.num_tokens)
+            assert end <= r.num_tokens + 1                              # at most one token not yet read
+            ids = r.tokens(x.start, min(end, r.num_tokens))
+            if end > r.num_tokens:
+                ids = ids + [-1]
+                flight[2].add(r.req_id)
+            m.advance(r.req_id, end, ids if m.prefix_caching else None)
             if x.samples:
-                toks[r.req_id] = token(r, x.start + x.num_tokens)
+                toks[r.req_id] = token(r, end)
         plans.append(plan)
         if flight is not None:
             collect(flight)
             flight = None
         if plan.scheduled:
-            flight = (plan, toks)
+            flight = (plan, toks, set())
             if not ahead:
                 collect(flight)
                 flight = None
@@ -281,3 +290,25 @@ def test_scheduling_ahead_does_not_run_past_a_certain_end():
     assert b.output_ids == [1004, 99] and b.finish_reason == FinishReason.STOP
     assert [len(p.scheduled) for p in plans] == [1, 1, 1, 0]          # the third ran before the 99 was read
     assert m.num_free_blocks() == 64
+
+
+def test_scheduling_ahead_with_the_prefix_cache():
+    """Tokens that a step took without knowing them reach the cache manager when they are read (``resolve``): the
+    pages they fill become findable, later requests with the same beginning skip them, and the sequences are
+    those of one step at a time."""
+    results = {}
+    for ahead in (False, True):
+        s, m = make(num_blocks=40, block_size=4, max_num_batched_tokens=8, enable_prefix_caching=True)
+        first = req("a", 9, max_tokens=12)
+        s.add_request(first)
+        drive(s, m, ahead, lambda r, n: 1000 + n)
+        assert first.finished and m.num_free_blocks() == 40
+        # the second request repeats the first one's prompt and its first outputs
+        again = Request("b", first.prompt_ids + first.output_ids[:7] + [5, 6], SamplingParams(max_tokens=4, temperature=0.0), seed=1)
+        s.add_request(again)
+        plans = drive(s, m, ahead, lambda r, n: 1000 + n)
+        first_run = [x for p in plans for x in p.scheduled if x.request is again][0]
+        assert first_run.start == 16                 # four full pages of prompt and generated tokens were found
+        results[ahead] = (list(first.output_ids), list(again.output_ids), m.prefix_hits)
+        m.check_invariants()
+    assert results[False] == results[True]
