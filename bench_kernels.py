@@ -11,7 +11,7 @@ graph's CUDA-event time divided by its launches.  Beside each time stands the ti
     python bench_kernels.py --only gemm_decode --tokens 1 8 32
 
 Sections: gemm_decode (tcgen05 swapped-operand product per split count), gemm_prompt (tcgen05 product
-and the library's), attention_decode (per split count), attention_prompt.
+and the library's), attention_decode (per split count), attention_prompt, sampling.
 """
 from __future__ import annotations
 
@@ -179,9 +179,33 @@ def attention_prompt(s, tokens_list, tflops):
     G.check_status()
 
 
+def sampling(vocab, rows_list):
+    """The sampling kernels behind a step: device time per launch (the rows' columns already on the device)."""
+    from dinfer_b200.sampling import sampler as S
+    print("# sampling: us per launch over f32 logits [rows, vocabulary], by what the rows ask for")
+    for R in rows_list:
+        logits = torch.randn(R, vocab, device="cuda") * 3
+        out = torch.empty(R, dtype=torch.int32, device="cuda")
+        temp = torch.full((R,), 0.7, device="cuda")
+        seeds = torch.arange(R, dtype=torch.int64, device="cuda")
+        offs = torch.full((R,), 3, dtype=torch.int64, device="cuda")
+        one = torch.ones(R, device="cuda")
+        zero = torch.zeros(R, device="cuda")
+
+        def ints(v):
+            return torch.full((R,), v, dtype=torch.int32, device="cuda")
+        cases = [("greedy", lambda i: S.argmax(logits, out)),
+                 ("temperature", lambda i: S.sample(logits, temp, seeds, offs, ints(-1), one, zero, out)),
+                 ("top-k 20 + top-p 0.95", lambda i: S.sample(logits, temp, seeds, offs, ints(20), one * 0.95, zero, out)),
+                 ("top-p 0.95 alone", lambda i: S.sample(logits, temp, seeds, offs, ints(-1), one * 0.95, zero, out)),
+                 ("top-k 1000 (radix descent)", lambda i: S.sample(logits, temp, seeds, offs, ints(1000), one, zero, out))]
+        cells = [f"{name} {graph_time_us(fn, 8):6.1f}" for name, fn in cases]
+        print(f"rows {R:3d} | " + " | ".join(cells), flush=True)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--only", choices=["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt"])
+    ap.add_argument("--only", choices=["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "sampling"])
     ap.add_argument("--tokens", type=int, nargs="*", default=[1, 8, 32], help="rows of the decode products")
     ap.add_argument("--batches", type=int, nargs="*", default=[1, 8, 64], help="requests of the decode attention")
     ap.add_argument("--contexts", type=int, nargs="*", default=[1024, 4096, 16384])
@@ -193,7 +217,7 @@ def main() -> int:
     hbm, tflops, source = peaks()
     print(f"# peaks ({source}): {hbm:.1f} GB/s, {tflops:.1f} TFLOP/s bf16; {torch.cuda.get_device_name(0)}")
     torch.manual_seed(0)
-    todo = [a.only] if a.only else ["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt"]
+    todo = [a.only] if a.only else ["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "sampling"]
     if "gemm_decode" in todo:
         gemm_decode(SHAPE, a.tokens, hbm)
     if "gemm_prompt" in todo:
@@ -202,6 +226,8 @@ def main() -> int:
         attention_decode(SHAPE, a.batches, a.contexts, hbm)
     if "attention_prompt" in todo:
         attention_prompt(SHAPE, a.prompt_tokens, tflops)
+    if "sampling" in todo:
+        sampling(151936, a.batches)
     return 0
 
 
