@@ -28,9 +28,10 @@ class EngineConfig:
     long_prefill_token_threshold: int = 0
     # decode-only steps replay a captured CUDA graph
     enable_cuda_graph: bool = True
-    # steps whose prompt portions fill the token budget exactly (the steady state while prompts are taken in)
-    # replay a captured graph as well, one per bucket of decoded tokens beside them; pays where launching a
-    # step's kernels one by one takes the host longer than the device needs to run them (small models)
+    # steps whose prompt portions fill the token budget exactly (the steady state while prompts are taken in) and
+    # steps with at most 128 prompt tokens (padded up to a power of two) replay a captured graph as well, one per
+    # shape and bucket of decoded tokens beside them; pays where launching a step's kernels one by one takes the
+    # host longer than the device needs to run them (small models, short prompts)
     mixed_cuda_graph: bool = True
     # full pages of computed tokens stay findable by the hash of their tokens and are shared by later
     # requests with the same beginning (off by default: with it on, freed pages are not the next ones used)

@@ -30,8 +30,10 @@ _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
 class ModelRunner:
-    # prompt portions a captured mixed step has places for (see _mixed_layout)
+    # prompt portions a captured mixed step has places for, and the most prompt tokens of a step that is padded up
+    # to a power of two to replay a graph (see _mixed_layout)
     PROMPT_PLACES = 4
+    PADDED_PROMPT_TOKENS = 128
 
     def __init__(self, config_dict: Dict[str, Any], source: WeightSource, engine: EngineConfig):
         engine.check()
@@ -189,7 +191,7 @@ class ModelRunner:
         self._buckets = buckets
         self._graphs: Dict[Any, Any] = {}
         self._graph_pool = None
-        self._mixed_seen: Dict[int, int] = {}
+        self._mixed_seen: Dict[Any, int] = {}
 
     def _capture(self, bucket: int):
         from ..kernels import attention_ops
@@ -238,43 +240,59 @@ class ModelRunner:
             return rec["logits"][:0]
         return rec["logits"][torch.tensor(wanted, device=self.device)]
 
-    # ---- steps that fill the token budget with prompt portions replay a captured graph too
+    # ---- steps with prompt portions replay a captured graph too where their shape comes again
     def _mixed_layout(self, entries: Sequence[StepEntry]):
-        """A step whose prompt portions (at most ``PROMPT_PLACES``) add up to exactly the token budget, beside any
-        number of decoded tokens, has a fixed shape but for the number of decoded tokens: the steady state while
-        prompts are taken in.  Such steps replay a graph per decode bucket, laid out as ``PROMPT_PLACES`` prompt
-        places (the unused ones without tokens) followed by the bucket's one-token places (the unused ones dummy
-        rows).  Returns (bucket, places) or None when the step is not of that shape (it then runs eagerly).  A
-        bucket is captured when it comes up the second time."""
+        """Two kinds of steps with prompt portions have a shape that comes again: those whose portions add up to
+        exactly the token budget (the steady state while prompts are taken in), and those with at most
+        ``PADDED_PROMPT_TOKENS`` prompt tokens, which are padded up to a power of two by a dummy portion (so few
+        rows cost a product nothing: it is bound by reading its weights).  Such a step replays a graph per
+        (prompt tokens, decode bucket), laid out as ``PROMPT_PLACES`` prompt places (the dummy portion in one of
+        them, the unused ones without tokens) followed by the bucket's one-token places (the unused ones dummy
+        rows).  Returns (key, places), or None when the step is not of such a shape (it then runs kernel by
+        kernel).  A shape is captured when it comes up the second time."""
         if not self.engine.mixed_cuda_graph:
             return None
         budget = self.engine.max_num_batched_tokens
         prompts = [i for i, e in enumerate(entries) if len(e.tokens) > 1]
         decodes = [i for i, e in enumerate(entries) if len(e.tokens) == 1]
-        if not (1 <= len(prompts) <= self.PROMPT_PLACES) or sum(len(entries[i].tokens) for i in prompts) != budget:
+        have = sum(len(entries[i].tokens) for i in prompts)
+        if not prompts or len(prompts) > self.PROMPT_PLACES:
+            return None
+        if have == budget:
+            total = budget
+        elif have <= min(self.PADDED_PROMPT_TOKENS, budget):
+            total = 16
+            while total < have:
+                total *= 2
+            if total > budget or (total > have and len(prompts) == self.PROMPT_PLACES):
+                return None                                  # no room, or no place left, for the dummy portion
+        else:
             return None
         if any(tuple(e.want) not in ((), (len(e.tokens) - 1,)) for e in entries):
             return None                                      # only the last token's logits come out of a place
         bucket = 0 if not decodes else next((b for b in self._buckets if b >= len(decodes)), None)
         if bucket is None:
             return None
-        key = ("mixed", bucket)
+        key = ("mixed", total, bucket)
         if key not in self._graphs:
-            self._mixed_seen[bucket] = self._mixed_seen.get(bucket, 0) + 1
-            if self._mixed_seen[bucket] < 2:
+            self._mixed_seen[key] = self._mixed_seen.get(key, 0) + 1
+            if self._mixed_seen[key] < 2:
                 return None
-        places = [(i, len(entries[i].tokens)) for i in prompts] + [(-1, 0)] * (self.PROMPT_PLACES - len(prompts))
+        places = [(i, len(entries[i].tokens)) for i in prompts]
+        if total > have:
+            places.append((-1, total - have))
+        places += [(-1, 0)] * (self.PROMPT_PLACES - len(places))
         places += [(i, 1) for i in decodes] + [(-1, 1)] * (bucket - len(decodes))
-        return bucket, places
+        return key, places
 
-    def _capture_mixed(self, bucket: int):
+    def _capture_mixed(self, key):
         from ..kernels import attention_ops
+        _, total, bucket = key
         width = self.max_blocks_per_seq
-        budget = self.engine.max_num_batched_tokens
         B = self.PROMPT_PLACES + bucket
-        dev = torch.empty(self.plan.words(budget + bucket, B, B, width), dtype=torch.int32, device=self.device)
-        # captured on a dummy batch of the same shape: one prompt place with the whole budget (no pages, no slots)
-        places = [(-1, budget)] + [(-1, 0)] * (self.PROMPT_PLACES - 1) + [(-1, 1)] * bucket
+        dev = torch.empty(self.plan.words(total + bucket, B, B, width), dtype=torch.int32, device=self.device)
+        # captured on a dummy batch of the same shape: one prompt place with all the tokens (no pages, no slots)
+        places = [(-1, total)] + [(-1, 0)] * (self.PROMPT_PLACES - 1) + [(-1, 1)] * bucket
         ids, rows, ctx = self.plan.build([], [], table_width=width, dev=dev, slots=places)
         hkv = max([n.num_kv_heads for n in self.model.cache_needs() if isinstance(n, KvCacheNeed)] or [1])
         ctx.decode_splits = attention_ops.decode_splits(max(1, bucket), hkv, self.engine.max_model_len)
@@ -283,11 +301,11 @@ class ModelRunner:
         ctx.prev_tokens = self.sampled
         rec = self._capture_one(ids, rows, ctx)
         rec.update(dev=dev, width=width)
-        self._graphs[("mixed", bucket)] = rec
+        self._graphs[key] = rec
         return rec
 
-    def _mixed_graph_step(self, entries: Sequence[StepEntry], starts: Sequence[int], bucket: int, places) -> torch.Tensor:
-        rec = self._graphs.get(("mixed", bucket)) or self._capture_mixed(bucket)
+    def _mixed_graph_step(self, entries: Sequence[StepEntry], starts: Sequence[int], key, places) -> torch.Tensor:
+        rec = self._graphs.get(key) or self._capture_mixed(key)
         self.plan.build(entries, starts, table_width=rec["width"], dev=rec["dev"], slots=places)
         rec["graph"].replay()
         kernel_lib.add_launches(rec["launches"])

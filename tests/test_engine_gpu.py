@@ -404,7 +404,8 @@ def test_scheduling_ahead_with_arrivals_and_aborts(dirs, seed):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_budget_filling_steps_replay_a_graph(dirs, tmp_path, dtype):
-    """Steps whose prompt portions fill the token budget exactly replay a captured graph (one per bucket of decoded
+    """Steps whose prompt portions fill the token budget exactly, and steps with few prompt tokens (padded up to a
+    power of two by a dummy portion), replay a captured graph (one per number of prompt tokens and bucket of decoded
     tokens beside them, with places for up to four portions).  Against the same engine launching every such step
     kernel by kernel: the same tokens in 32-bit; in bfloat16 the same up to a near-tie."""
     from dinfer_b200 import LLM, SamplingParams
@@ -420,8 +421,12 @@ def test_budget_filling_steps_replay_a_graph(dirs, tmp_path, dtype):
         llm = LLM(d, dtype=dtype, max_model_len=256, max_num_seqs=6, max_num_batched_tokens=32,
                   num_blocks=120, block_size=16, mixed_cuda_graph=mixed)
         res[mixed] = [o.output_ids for o in llm.generate(prompts, sp)]
+        for n in (5, 7, 11, 20):                      # short prompts one after the other: 16, 16, 16, 32 prompt rows
+            res[mixed] += [o.output_ids for o in llm.generate([prompts[0][:n]], sp[1])]
         captured = [k for k in llm.runner._graphs if isinstance(k, tuple)]
         assert bool(captured) == mixed
+        if mixed:        # steps that fill the budget, and steps with few prompt tokens padded up to a power of two
+            assert any(k[1] == 32 for k in captured) and any(k[1] < 32 for k in captured)
         llm.runner.check_device_status()
         llm.runner.manager.check_invariants()
         assert llm.runner.manager.num_free_blocks() == 120
@@ -462,7 +467,7 @@ def test_a_long_prompt_whole_and_in_portions(tmp_path, dtype):
         for t in toks[n0:]:
             got.append(r.step([StepEntry("a", [t], [0])])[0].float().cpu())
         if budget == 512:
-            assert ("mixed", 0) in r._graphs
+            assert ("mixed", 512, 0) in r._graphs
         r.finish("a")
         r.check_device_status()
         results.append(torch.stack(got))
