@@ -12,6 +12,7 @@ models/qwen3/src/model.rs:684-832), with sampling kept out of it.
 """
 from __future__ import annotations
 
+import math
 from typing import Any, Dict, Hashable, List, Sequence
 
 import torch
@@ -34,6 +35,8 @@ class ModelRunner:
     # to a power of two to replay a graph (see _mixed_layout)
     PROMPT_PLACES = 4
     PADDED_PROMPT_TOKENS = 128
+    HOST_US_PER_LAYER = 120.0          # launching one layer's kernels one by one (measured, Python wrappers)
+    DEVICE_FLOPS = 1.2e15              # what a prompt-sized step reaches on the device, roughly
 
     def __init__(self, config_dict: Dict[str, Any], source: WeightSource, engine: EngineConfig):
         engine.check()
@@ -192,6 +195,7 @@ class ModelRunner:
         self._graphs: Dict[Any, Any] = {}
         self._graph_pool = None
         self._mixed_seen: Dict[Any, int] = {}
+        self._padded_tokens = self._padded_limit()
 
     def _capture(self, bucket: int):
         from ..kernels import attention_ops
@@ -241,15 +245,30 @@ class ModelRunner:
         return rec["logits"][torch.tensor(wanted, device=self.device)]
 
     # ---- steps with prompt portions replay a captured graph too where their shape comes again
+    def _padded_limit(self) -> int:
+        """The most prompt tokens of a step that is padded (up to a multiple of 128) to replay a graph: as long as
+        launching the step kernel by kernel would keep the host busy for longer than the device needs for the
+        padded step.  Both sides are estimates from the model's sizes, so the answer is the same in every run:
+        ``HOST_US_PER_LAYER`` for the host (measured: 120 us a layer through the Python wrappers, whatever the
+        rows), two flops per weight and token at ``DEVICE_FLOPS`` for the device."""
+        table = (self.spec.vocab_size, self.spec.hidden_size)       # the table and the head do not see every row
+        weights = sum(math.prod(d.shape) for d in self.model.declarations()
+                      if len(d.shape) == 2 and tuple(d.shape) != table)
+        host_s = len(self.spec.schedule) * self.HOST_US_PER_LAYER * 1e-6
+        tokens = int(host_s * self.DEVICE_FLOPS / (2.0 * max(1, weights)))
+        return max(self.PADDED_PROMPT_TOKENS, tokens // 128 * 128)
+
     def _mixed_layout(self, entries: Sequence[StepEntry]):
-        """Two kinds of steps with prompt portions have a shape that comes again: those whose portions add up to
-        exactly the token budget (the steady state while prompts are taken in), and those with at most
-        ``PADDED_PROMPT_TOKENS`` prompt tokens, which are padded up to a power of two by a dummy portion (so few
-        rows cost a product nothing: it is bound by reading its weights).  Such a step replays a graph per
-        (prompt tokens, decode bucket), laid out as ``PROMPT_PLACES`` prompt places (the dummy portion in one of
-        them, the unused ones without tokens) followed by the bucket's one-token places (the unused ones dummy
-        rows).  Returns (key, places), or None when the step is not of such a shape (it then runs kernel by
-        kernel).  A shape is captured when it comes up the second time."""
+        """Steps with prompt portions whose shape comes again replay a graph per (prompt tokens, decode bucket), laid
+        out as ``PROMPT_PLACES`` prompt places (a dummy portion that pads the prompt tokens in one of them, the
+        unused ones without tokens) followed by the bucket's one-token places (the unused ones dummy rows):
+          * portions that add up to exactly the token budget (the steady state while prompts are taken in);
+          * at most ``PADDED_PROMPT_TOKENS`` prompt tokens, padded up to a power of two (so few rows cost a product
+            nothing: it is bound by reading its weights);
+          * more than that, padded up to a multiple of 128 (256 beyond 1024 tokens), for models small enough that
+            the host would be the slower side of such a step (``_padded_limit``).
+        Returns (key, places), or None for a step that runs kernel by kernel.  A shape is captured when it comes
+        up the second time."""
         if not self.engine.mixed_cuda_graph:
             return None
         budget = self.engine.max_num_batched_tokens
@@ -264,10 +283,13 @@ class ModelRunner:
             total = 16
             while total < have:
                 total *= 2
-            if total > budget or (total > have and len(prompts) == self.PROMPT_PLACES):
-                return None                                  # no room, or no place left, for the dummy portion
         else:
-            return None
+            unit = 128 if have <= 1024 else 256
+            total = min(budget, (have + unit - 1) // unit * unit)
+            if total > self._padded_tokens:
+                return None
+        if total > budget or (total > have and len(prompts) == self.PROMPT_PLACES):
+            return None                                      # no room, or no place left, for the dummy portion
         if any(tuple(e.want) not in ((), (len(e.tokens) - 1,)) for e in entries):
             return None                                      # only the last token's logits come out of a place
         bucket = 0 if not decodes else next((b for b in self._buckets if b >= len(decodes)), None)

@@ -427,6 +427,7 @@ def test_budget_filling_steps_replay_a_graph(dirs, tmp_path, dtype):
         assert bool(captured) == mixed
         if mixed:        # steps that fill the budget, and steps with few prompt tokens padded up to a power of two
             assert any(k[1] == 32 for k in captured) and any(k[1] < 32 for k in captured)
+            assert llm.runner._padded_tokens >= 2048         # a tiny model: the host is always the slower side
         llm.runner.check_device_status()
         llm.runner.manager.check_invariants()
         assert llm.runner.manager.num_free_blocks() == 120
