@@ -154,11 +154,15 @@ def decode_run(llm, cfg, batch, context, steps, warmup, rng, measure_e2e, want_l
     if measure_e2e:
         # end to end: K steps through the Python entry point; every step copies its plan (token ids,
         # positions, page tables) host->device from pinned memory and reads the sampled tokens back
+        host0 = (llm.stats.host_schedule_s, llm.stats.host_launch_s, llm.stats.host_collect_s)
         t0 = time.perf_counter()
         for _ in range(steps):
             llm.step()
         torch.cuda.synchronize()
         res["e2e_ms_per_step"] = (time.perf_counter() - t0) * 1e3 / steps
+        st = llm.stats
+        res["host_us"] = [round((x - y) * 1e6 / steps, 1) for x, y in zip(
+            (st.host_schedule_s, st.host_launch_s, st.host_collect_s), host0)]
         res["h2d_bytes_per_step"] = llm.runner.plan.h2d_bytes
         res["d2h_bytes_per_step"] = 4 * batch
     else:
@@ -342,7 +346,10 @@ def main() -> int:
                    "l2": "inputs larger than L2 (weights + cache read per step)", "peaks": pk["source"]},
         "e2e": {"value": round(a.batch * 1e3 / main_run["e2e_ms_per_step"], 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": main_run["h2d_bytes_per_step"],
-                "d2h_bytes_per_step": main_run["d2h_bytes_per_step"]},
+                "d2h_bytes_per_step": main_run["d2h_bytes_per_step"],
+                # the host's share of a step in us: deciding it, plan + launch, waiting for and applying the tokens
+                # of the step before (one step is in flight, so the wait is where the device's time shows)
+                "host_us_schedule_launch_collect": main_run.get("host_us")},
         "gpu_launches": main_run["launches_per_step"] * a.steps,
         "prefill": {"value": round(PREFILL_TOKENS * 1e3 / pre_ms, 1), "tokens": PREFILL_TOKENS,
                     "ms": round(pre_ms, 3), "frac": round(pf / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},

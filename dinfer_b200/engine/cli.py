@@ -83,7 +83,11 @@ def cmd_generate(a) -> int:
         print(json.dumps(rec))
     s = llm.stats
     print(f"steps {s.steps}  prompt tokens {s.prompt_tokens}  generated {s.generated_tokens}  "
-          f"preemptions {s.preemptions}", file=sys.stderr)
+          f"preemptions {s.preemptions}  prefix hits {s.prefix_hit_tokens}", file=sys.stderr)
+    if s.steps:
+        print(f"host time per step: schedule {s.host_schedule_s / s.steps * 1e6:.0f} us  plan and launch "
+              f"{s.host_launch_s / s.steps * 1e6:.0f} us  wait for and apply tokens {s.host_collect_s / s.steps * 1e6:.0f} us",
+              file=sys.stderr)
     return 0
 
 

@@ -16,6 +16,7 @@ updated; ``step()`` then returns what finished one launch earlier.
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass
 from typing import Any, Dict, Hashable, List, Optional, Sequence, Union
 
@@ -48,6 +49,12 @@ class EngineStats:
     generated_tokens: int = 0
     preemptions: int = 0
     prefix_hit_tokens: int = 0        # prompt tokens found in the prefix cache (not run again)
+    # where the host's time of the steps went, in seconds (the reference prints such segments with HOST_TIME=1,
+    # crates/core/src/engine.rs:664-711): deciding the step, building its plan and queueing its kernels, and waiting
+    # for and applying the tokens of the step before (with one step in flight the wait is where the device shows)
+    host_schedule_s: float = 0.0
+    host_launch_s: float = 0.0
+    host_collect_s: float = 0.0
 
 
 class _InFlight:
@@ -145,15 +152,22 @@ class LLM:
         finished: List[Request] = []
         if not ahead and self._inflight is not None:
             finished += self._collect()
+        t0 = time.perf_counter()
         plan = self.scheduler.schedule(lookahead=ahead)
         self._last_scheduled = len(plan.scheduled)
         finished += plan.finished
+        t1 = time.perf_counter()
         launched = self._launch(plan) if plan.scheduled else None
+        t2 = time.perf_counter()
         if self._inflight is not None:              # the step before this one: its tokens have arrived by now
             finished += self._collect()
         self._inflight = launched
         if launched is not None and not ahead:
             finished += self._collect()
+        t3 = time.perf_counter()
+        self.stats.host_schedule_s += t1 - t0
+        self.stats.host_launch_s += t2 - t1
+        self.stats.host_collect_s += t3 - t2
         self.stats.preemptions = self.scheduler.num_preemptions
         self.stats.prefix_hit_tokens = self.runner.manager.prefix_hits
         outs = []
