@@ -12,6 +12,7 @@ address and shape (crates/layers/src/exec.rs:226-247,392-404 does the same paddi
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
@@ -27,6 +28,10 @@ class StepEntry:
     req_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()          # indices into ``tokens`` whose logits are returned
+
+
+# DINFER_VALIDATE_PLANS=1: every plan is checked on the host before it goes to the device (see PlanBuilder._validate)
+VALIDATE_PLANS = os.environ.get("DINFER_VALIDATE_PLANS", "0") == "1"
 
 
 class OutOfPages(RuntimeError):
@@ -73,6 +78,27 @@ class PlanBuilder:
             views[name] = (off, n)
             off = _align(off + n)
         return views, off
+
+    def _validate(self, T, B, cu, seq, pos, rows, tables, slot_maps) -> None:
+        """What every kernel takes for granted about a plan (checked on the host when DINFER_VALIDATE_PLANS=1, as
+        the tests do: the device tools that would catch an access out of range are not at hand everywhere)."""
+        m = self.manager
+        bs = m.block_size
+        if int(cu[0]) != 0 or int(cu[-1]) != T or np.any(np.diff(cu) < 0):
+            raise AssertionError("plan: request offsets must rise from 0 to the number of tokens")
+        if rows.size and (rows.min() < 0 or rows.max() >= max(T, 1)):
+            raise AssertionError("plan: a logits row outside the step's tokens")
+        if T and (pos.min() < 0 or np.any(pos >= np.repeat(seq, np.diff(cu)))):
+            raise AssertionError("plan: a token's position is not inside its request")
+        for g, (tab, sl) in enumerate(zip(tables, slot_maps)):
+            n = m.pools[g].num_blocks
+            if tab.min() < -1 or tab.max() >= n:
+                raise AssertionError(f"plan: group {g}: a page id outside the pool of {n}")
+            if T and (sl.min() < -1 or sl.max() >= n * bs):
+                raise AssertionError(f"plan: group {g}: a slot outside the pool")
+            live = sl[sl >= 0]
+            if live.size != np.unique(live).size:
+                raise AssertionError(f"plan: group {g}: two tokens of a step write the same slot")
 
     def _next_turn(self) -> int:
         """The next pinned buffer of the ring, once its last copy has left it."""
@@ -173,6 +199,9 @@ class PlanBuilder:
                 sslots[j] = m.state_slots.slot(entries[i].req_id)
                 fresh[j] = 1 if m.state_slots.take_fresh(entries[i].req_id) else 0
         slots_ = slot_maps
+
+        if VALIDATE_PLANS:
+            self._validate(T, B, cu, seq, pos, rows_np, tables, slot_maps)
 
         # pack: the order and the alignment fix every view's offset for given (T, B, R, width)
         k = self._next_turn()
@@ -286,6 +315,13 @@ class DecodePlan:
                 self._src[i][g] = None
                 self._copied[i][g] = 0
         self._live = n_real
+        if VALIDATE_PLANS:
+            for g in range(self.ng):
+                n = m.pools[g].num_blocks
+                live = self._slot[g][self._slot[g] >= 0]
+                if self._tab[g].min() < -1 or self._tab[g].max() >= n or (live.size and live.max() >= n * bs) \
+                        or live.size != np.unique(live).size:
+                    raise AssertionError(f"decode plan: group {g}: a page or slot outside the pool, or a slot written twice")
         k = b._next_turn()
         b._host[k].numpy()[:self.words] = self.shadow
         b._send(k, self.words, self.dev)

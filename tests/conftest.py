@@ -3,6 +3,8 @@ import sys
 
 import pytest
 
+os.environ.setdefault("DINFER_VALIDATE_PLANS", "1")      # every plan a test builds is checked on the host
+
 sys.path.insert(0, os.path.abspath(os.path.join(os.path.dirname(__file__), "..")))
 sys.path.insert(0, os.path.dirname(__file__))
 
