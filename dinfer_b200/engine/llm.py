@@ -222,7 +222,8 @@ class LLM:
             flight.event.synchronize()
             host = flight.host[:len(flight.samplers)].tolist()
             sampled = {r.req_id: t for r, t in zip(flight.samplers, host)}
-            self.stats.generated_tokens += len(host)
+            # what a step ahead computed for a request that has finished meanwhile is dropped, not counted
+            self.stats.generated_tokens += sum(1 for r in flight.samplers if not r.finished)
         done = self.scheduler.update(flight.plan, sampled)
         manager = self.runner.manager
         if manager.prefix_caching:                  # tokens the next step took on the device: the cache learns them
