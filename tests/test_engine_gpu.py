@@ -1,6 +1,6 @@
 """The engine through its Python entry point: greedy and sampled generation against the plain
-implementation, long decoding, the first tokens, preemption under a small pool, and the BASELINE
-workloads of the two tiny configurations."""
+implementation, long decoding, the first tokens, preemption under a small pool, and the
+workloads set for the two tiny configurations."""
 import random
 
 import pytest
