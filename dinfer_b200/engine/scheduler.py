@@ -96,25 +96,30 @@ class Scheduler:
         budget = cfg.max_num_batched_tokens
         threshold = cfg.long_prefill_token_threshold
         i = 0
+        max_len, exempt = cfg.max_model_len, cfg.decode_exempt_from_budget
+        allocate = self.manager.allocate
         while i < len(self.running):
             req = self.running[i]
             ahead = req.num_placeholders
-            if ahead and (len(req.output_ids) + ahead >= req.params.max_tokens
-                          or req.num_tokens + ahead >= cfg.max_model_len):
+            n_out = len(req.output_ids)
+            known = len(req.prompt_ids) + n_out + ahead         # tokens of the request, those in flight included
+            computed = req.num_computed
+            if ahead and (n_out + ahead >= req.params.max_tokens or known >= max_len):
                 i += 1                          # the token in flight is its last: nothing more to run
                 continue
-            num_new = req.num_tokens + ahead - req.num_computed
-            is_decode = num_new == 1 and req.num_computed > 0
+            num_new = known - computed
+            is_decode = num_new == 1 and computed > 0
             if threshold > 0:
                 num_new = min(num_new, threshold)
-            if not (is_decode and cfg.decode_exempt_from_budget):
+            if not (is_decode and exempt):
                 num_new = min(num_new, budget)
-            num_new = min(num_new, cfg.max_model_len - req.num_computed)
+            if computed + num_new > max_len:
+                num_new = max_len - computed
             if num_new <= 0:
                 i += 1
                 continue
             placed = True
-            while not self.manager.allocate(req.req_id, req.num_computed + num_new):
+            while not allocate(req.req_id, computed + num_new):
                 victim = self.running[-1]
                 if victim is req:
                     if len(self.running) > 1:
@@ -133,10 +138,8 @@ class Scheduler:
                     continue
                 i += 1
                 continue
-            out.scheduled.append(ScheduledRequest(req, req.num_computed, num_new,
-                                                  req.num_computed + num_new == req.num_tokens + ahead,
-                                                  len(req.output_ids) + ahead))
-            if not (is_decode and cfg.decode_exempt_from_budget):
+            out.scheduled.append(ScheduledRequest(req, computed, num_new, computed + num_new == known, n_out + ahead))
+            if not (is_decode and exempt):
                 budget -= num_new
             i += 1
 
