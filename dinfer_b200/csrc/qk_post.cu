@@ -193,6 +193,85 @@ qk_post_lanes_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ p
   }
 }
 
+// Head size 128 in bfloat16, the rotation over the whole head: half a warp per head, a lane owns 8 consecutive
+// elements (one 16-byte access), its rotation partner sits 8 lanes across.  A warp takes HALF_HP pairs of heads of
+// one token and requests all of them before it works on the first.
+constexpr int HALF_HP = 3;
+
+template <typename TW>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_post_half_warp_kernel(__nv_bfloat16* __restrict__ qkv, int64_t ld, const int* __restrict__ positions,
+                         const TW* __restrict__ q_weight, const TW* __restrict__ k_weight, float eps,
+                         const float* __restrict__ cos_sin, __nv_bfloat16* __restrict__ cache,
+                         const int* __restrict__ slots, int block_size, int H, int Hkv) {
+  constexpr int D = 128;
+  pdl_enter();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int side = lane >> 4, l = lane & 15;
+  const int head0 = (blockIdx.y * WARPS + warp) * 2 * HALF_HP + side;
+  const int heads = H + 2 * Hkv;
+  __nv_bfloat16* row = qkv + (int64_t)t * ld + l * 8;
+  uint4 in[HALF_HP];
+#pragma unroll
+  for (int u = 0; u < HALF_HP; ++u)
+    if (head0 + 2 * u < heads) in[u] = *reinterpret_cast<const uint4*>(row + (int64_t)(head0 + 2 * u) * D);
+  float c[8], sn[8];
+  const bool has_table = cos_sin != nullptr;
+  if (has_table) {
+    const float* cs = cos_sin + (int64_t)positions[t] * D + (l & 7) * 8;   // the pair's index inside the half
+    load8<float>(cs, c);
+    load8<float>(cs + D / 2, sn);
+  }
+  const int slot = cache ? slots[t] : -1;
+#pragma unroll
+  for (int u = 0; u < HALF_HP; ++u) {
+    const int head = head0 + 2 * u;
+    const bool live = head < heads;                            // (the other half of the warp may still have a head)
+    const int kind = head < H ? 0 : (head < H + Hkv ? 1 : 2);
+    float v[8];
+    float ss = 0.f;
+    if (live) {
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&in[u]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h2[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    }
+    const TW* w = !live ? nullptr : (kind == 0 ? q_weight : (kind == 1 ? k_weight : nullptr));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // over the head's 16 lanes
+    if (w) {
+      const float rinv = rsqrtf(ss / (float)D + eps);
+      float wv[8];
+      load8<TW>(w + l * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = v[j] * rinv * wv[j];
+    }
+    const bool rotate = has_table && live && kind != 2;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
+      if (rotate) v[j] = l < 8 ? v[j] * c[j] - other * sn[j] : v[j] * c[j] + other * sn[j];
+    }
+    if (!live) continue;
+    uint4 out;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    if (kind != 2 && (w || rotate)) *reinterpret_cast<uint4*>(row + (int64_t)head * D) = out;
+    if (kind != 0 && slot >= 0) {
+      const int64_t blk = slot / block_size, off = slot % block_size;
+      const int hk = kind == 1 ? head - H : head - H - Hkv;
+      __nv_bfloat16* dst = cache + ((((blk * 2 + (kind - 1)) * Hkv + hk) * block_size + off) * (int64_t)D) + l * 8;
+      *reinterpret_cast<uint4*>(dst) = out;
+    }
+  }
+}
+
 template <typename TA, typename TW>
 void launch_lanes(dim3 grid, cudaStream_t stream, TA* qkv, int64_t ld, const int* positions, const TW* qw,
                   const TW* kw, float eps, const float* cos_sin, TA* cache, const int* slots, int block_size,
@@ -232,6 +311,14 @@ DINFER_API int dinfer_qk_post(void* qkv, int64_t ld, const int* positions, const
       const bool aligned = ld % 8 == 0 && !(reinterpret_cast<uintptr_t>(qkv) & 31) &&
                            !(reinterpret_cast<uintptr_t>(cache) & 31) && !(reinterpret_cast<uintptr_t>(q_weight) & 31) &&
                            !(reinterpret_cast<uintptr_t>(k_weight) & 31) && !(reinterpret_cast<uintptr_t>(cos_sin) & 31);
+      if constexpr (sizeof(TA) == 2) {
+        if (aligned && (!cos_sin || rot == D) && D == 128) {
+          const dim3 half_grid(T, (heads + WARPS * 2 * HALF_HP - 1) / (WARPS * 2 * HALF_HP));
+          launch_pdl(qk_post_half_warp_kernel<TW>, half_grid, dim3(WARPS * 32), 0, stream, (__nv_bfloat16*)qkv, ld, positions,
+                     (const TW*)q_weight, (const TW*)k_weight, eps, cos_sin, (__nv_bfloat16*)cache, slots, block_size, H, Hkv);
+          return cuda_status("qk_post");
+        }
+      }
       if (aligned && (!cos_sin || rot == D) && (D == 32 || D == 64 || D == 128 || D == 256)) {
         const dim3 lanes_grid(T, (heads + WARPS * HPW - 1) / (WARPS * HPW));
         launch_lanes<TA, TW>(lanes_grid, stream, (TA*)qkv, ld, positions, (const TW*)q_weight, (const TW*)k_weight, eps,

@@ -104,7 +104,9 @@ def test_gemm_f32_strided_operands():
 
 @pytest.mark.parametrize("dt", DT)
 @pytest.mark.parametrize("H,Hkv,D,rot,bs", [(4, 1, 16, 16, 4), (6, 2, 32, 32, 16), (5, 5, 48, 48, 8),
-                                             (8, 2, 128, 64, 16), (3, 3, 256, 256, 32), (2, 1, 80, 80, 16)])
+                                             (8, 2, 128, 64, 16), (3, 3, 256, 256, 32), (2, 1, 80, 80, 16),
+                                             (32, 8, 128, 128, 16), (5, 1, 128, 128, 16), (16, 8, 128, 128, 8),
+                                             (6, 2, 64, 64, 16)])
 def test_qk_post(dt, H, Hkv, D, rot, bs):
     from dinfer_b200.kernels import ops
     from dinfer_b200.parts.rope import rope_table
