@@ -30,6 +30,35 @@ from .batch import DecodePlan, OutOfPages, PlanBuilder, StepEntry
 _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
+def graph_shape(prompt_lens: Sequence[int], num_decodes: int, budget: int, buckets: Sequence[int], places: int,
+                small_max: int, padded_limit: int):
+    """The shape of the captured graph a step with prompt portions replays, as (prompt tokens after padding,
+    decode bucket), or None for a step that runs kernel by kernel.  ``prompt_lens``: the tokens of the step's
+    prompt portions; ``places``: prompt portions a graph has room for (one of them taken by the padding);
+    ``small_max``: up to so many prompt tokens are padded to a power of two (from 16); ``padded_limit``: up to so
+    many are padded to a multiple of 128 (256 beyond 1024); portions that fill ``budget`` exactly need no padding."""
+    have = sum(prompt_lens)
+    if not prompt_lens or len(prompt_lens) > places or any(n < 2 for n in prompt_lens):
+        return None
+    if have == budget:
+        total = budget
+    elif have <= min(small_max, budget):
+        total = 16
+        while total < have:
+            total *= 2
+    else:
+        unit = 128 if have <= 1024 else 256
+        total = min(budget, (have + unit - 1) // unit * unit)
+        if total > padded_limit:
+            return None
+    if total > budget or (total > have and len(prompt_lens) == places):
+        return None                                          # no room, or no place left, for the dummy portion
+    bucket = 0 if not num_decodes else next((b for b in buckets if b >= num_decodes), None)
+    if bucket is None:
+        return None
+    return total, bucket
+
+
 class ModelRunner:
     # prompt portions a captured mixed step has places for, and the most prompt tokens of a step that is padded up
     # to a power of two to replay a graph (see _mixed_layout)
@@ -271,30 +300,17 @@ class ModelRunner:
         up the second time."""
         if not self.engine.mixed_cuda_graph:
             return None
-        budget = self.engine.max_num_batched_tokens
         prompts = [i for i, e in enumerate(entries) if len(e.tokens) > 1]
         decodes = [i for i, e in enumerate(entries) if len(e.tokens) == 1]
-        have = sum(len(entries[i].tokens) for i in prompts)
-        if not prompts or len(prompts) > self.PROMPT_PLACES:
-            return None
-        if have == budget:
-            total = budget
-        elif have <= min(self.PADDED_PROMPT_TOKENS, budget):
-            total = 16
-            while total < have:
-                total *= 2
-        else:
-            unit = 128 if have <= 1024 else 256
-            total = min(budget, (have + unit - 1) // unit * unit)
-            if total > self._padded_tokens:
-                return None
-        if total > budget or (total > have and len(prompts) == self.PROMPT_PLACES):
-            return None                                      # no room, or no place left, for the dummy portion
         if any(tuple(e.want) not in ((), (len(e.tokens) - 1,)) for e in entries):
             return None                                      # only the last token's logits come out of a place
-        bucket = 0 if not decodes else next((b for b in self._buckets if b >= len(decodes)), None)
-        if bucket is None:
+        shape = graph_shape([len(entries[i].tokens) for i in prompts], len(decodes),
+                            self.engine.max_num_batched_tokens, self._buckets, self.PROMPT_PLACES,
+                            self.PADDED_PROMPT_TOKENS, self._padded_tokens)
+        if shape is None:
             return None
+        total, bucket = shape
+        have = sum(len(entries[i].tokens) for i in prompts)
         key = ("mixed", total, bucket)
         if key not in self._graphs:
             self._mixed_seen[key] = self._mixed_seen.get(key, 0) + 1

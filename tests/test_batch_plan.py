@@ -63,3 +63,28 @@ def test_decode_plan_matches_full_build(groups):
             m.advance(e.req_id, s + 1)
             live[e.req_id] = s + 1
         m.check_invariants()
+
+
+def test_which_steps_replay_a_graph():
+    """The decision which steps with prompt portions have a shape that comes again (and is worth a captured graph):
+    portions that fill the budget, few prompt tokens padded up to a power of two, and, for models small enough,
+    more of them padded up to a multiple of 128 or 256."""
+    from dinfer_b200.engine.runner import graph_shape
+    buckets = [1, 2, 4, 8, 16]
+
+    def shape(prompts, decodes=0, budget=2048, limit=128):
+        return graph_shape(prompts, decodes, budget, buckets, 4, 128, limit)
+
+    assert shape([2048]) == (2048, 0) and shape([1000, 1048], 5) == (2048, 8)        # the budget, exactly
+    assert shape([5]) == (16, 0) and shape([16], 1) == (16, 1) and shape([17, 3]) == (32, 0)
+    assert shape([100], 16) == (128, 16) and shape([128]) == (128, 0)
+    assert shape([129]) is None and shape([2047]) is None                            # a large model: kernel by kernel
+    assert shape([129], limit=4480) == (256, 0) and shape([1025], limit=4480) == (1280, 0)
+    assert shape([2000], limit=4480) == (2048, 0)                                    # never beyond the budget
+    assert shape([600], limit=512) is None and shape([500], limit=512) == (512, 0)
+    assert shape([], 4) is None and shape([100], 17) is None                         # no portion; too many decodes
+    assert shape([4, 4, 4, 4]) == (16, 0)                                            # four portions, nothing to pad
+    assert shape([4, 4, 4, 3]) is None                                               # no place left for the padding
+    assert shape([4, 4, 4, 4, 4]) is None
+    assert shape([40], budget=48) is None                                            # the padding would pass the budget
+    assert shape([48], budget=48) == (48, 0)
