@@ -9,6 +9,10 @@ Generation (scheduler + sampling) and trace replay both drive this one function.
 It stands where the reference has ``Runner::execute`` -> ``Qwen3Executor::forward_sample`` ->
 ``Qwen3Model::forward`` (crates/core/src/runner.rs:362-429, models/qwen3/src/executor.rs:977-1026,
 models/qwen3/src/model.rs:684-832), with sampling kept out of it.
+
+How a step reaches the device is an optimisation, never a difference in meaning: decode-only steps replay a
+CUDA graph per batch bucket, steps with prompt portions replay one where their shape comes again
+(``graph_shape``), every other step launches its kernels one by one.
 """
 from __future__ import annotations
 
