@@ -5,6 +5,13 @@
     outs = llm.generate([[1, 2, 3], [4, 5]], SamplingParams(temperature=0.0, max_tokens=16))
     outs[0].output_ids
 
+or step by step, for a caller that streams tokens on:
+
+    rid = llm.add_request([1, 2, 3], SamplingParams(max_tokens=16))
+    while llm.has_unfinished():
+        finished = llm.step()                   # RequestOutput of every request that ended
+        fresh = llm.take_new_tokens()           # {request: tokens it got since the last look}
+
 The options carry the names of the reference's ``dinfer serve`` flags / ``ServeOptions``
 (bins/dinfer/src/main.rs:30-131, models/qwen3/src/service.rs:43-140).  The reference itself has no
 in-process API (its only entry is the HTTP server); the loop below is its engine loop
@@ -110,6 +117,7 @@ class LLM:
         rows = self.runner.sampled.numel()
         self._tok_host = [torch.empty(rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._tok_turn = 0
+        self._new_tokens: Dict[Hashable, List[int]] = {}   # tokens appended since take_new_tokens() was last called
 
     # ---- requests
     def add_request(self, prompt_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -224,7 +232,11 @@ class LLM:
             sampled = {r.req_id: t for r, t in zip(flight.samplers, host)}
             # what a step ahead computed for a request that has finished meanwhile is dropped, not counted
             self.stats.generated_tokens += sum(1 for r in flight.samplers if not r.finished)
+        before = {r.req_id: len(r.output_ids) for r in flight.samplers}
         done = self.scheduler.update(flight.plan, sampled)
+        for r in flight.samplers:                   # what was appended (a dropped token is not)
+            if len(r.output_ids) > before[r.req_id]:
+                self._new_tokens.setdefault(r.req_id, []).extend(r.output_ids[before[r.req_id]:])
         manager = self.runner.manager
         if manager.prefix_caching:                  # tokens the next step took on the device: the cache learns them
             for rid in flight.taken_ahead:
@@ -237,6 +249,12 @@ class LLM:
                 if k is not None and r.output_ids and r.output_ids[-1] == ids[i][0]:
                     r.logprobs.append(TokenLogprobs(ids[i][0], lps[i][0], rank[i], ids[i][1:1 + k], lps[i][1:1 + k]))
         return done
+
+    def take_new_tokens(self) -> Dict[Hashable, List[int]]:
+        """The tokens every request has got since the last call, in order (for a caller that streams them on):
+        ``while llm.has_unfinished(): done = llm.step(); fresh = llm.take_new_tokens()``."""
+        fresh, self._new_tokens = self._new_tokens, {}
+        return fresh
 
     # ---- whole generation
     def generate(self, prompt_token_ids: Sequence[Sequence[int]],

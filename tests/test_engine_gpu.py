@@ -505,3 +505,27 @@ def test_scheduling_ahead_with_the_prefix_cache_on(dirs):
         assert llm.runner.manager.num_free_blocks() == 24
         llm.runner.check_device_status()
     assert res[False] == res[True]
+
+
+def test_tokens_can_be_taken_step_by_step(dirs):
+    """A caller that streams: after every ``step()`` the tokens each request got since the last look; put together
+    they are the requests' outputs, with and without a step in flight."""
+    from dinfer_b200 import LLM, SamplingParams
+    cfg = H.TINY_A
+    rng = random.Random(2)
+    prompts = [H.random_tokens(rng, n, cfg["vocab_size"]) for n in (3, 9, 14)]
+    for ahead in (False, True):
+        llm = LLM(dirs["A"], dtype="float32", max_model_len=64, max_num_seqs=4, max_num_batched_tokens=8,
+                  num_blocks=40, block_size=4, async_scheduling=ahead)
+        ids = [llm.add_request(p, SamplingParams(temperature=0.0, max_tokens=5 + i, stop_token_ids=[3, 7, 11]))
+               for i, p in enumerate(prompts)]
+        streamed = {i: [] for i in ids}
+        done = {}
+        while llm.has_unfinished():
+            for o in llm.step():
+                done[o.req_id] = o
+            for rid, toks in llm.take_new_tokens().items():
+                assert rid not in done or streamed[rid] + toks == done[rid].output_ids
+                streamed[rid] += toks
+        assert all(streamed[i] == done[i].output_ids for i in ids)
+        assert llm.take_new_tokens() == {}
