@@ -76,7 +76,8 @@ def cmd_generate(a) -> int:
                         logit_bias={int(t): float(b) for t, b in
                                     (x.split(":") for x in a.logit_bias.replace(",", " ").split())})
     for o in llm.generate(prompts, sp):
-        rec = {"id": o.req_id, "output_ids": o.output_ids, "finish_reason": o.finish_reason}
+        rec = {"id": o.req_id, "output_ids": o.output_ids, "finish_reason": o.finish_reason,
+               "ttft_ms": round(o.ttft_s * 1e3, 3), "tpot_ms": round(o.tpot_s * 1e3, 3), "e2e_ms": round(o.e2e_s * 1e3, 3)}
         if o.logprobs is not None:
             rec["logprobs"] = [{"token_id": t.token_id, "logprob": t.logprob, "rank": t.rank,
                                 "top": list(zip(t.top_ids, t.top_logprobs))} for t in o.logprobs]

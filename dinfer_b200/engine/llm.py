@@ -47,6 +47,11 @@ class RequestOutput:
     finish_reason: str
     num_preemptions: int = 0
     logprobs: Optional[List[TokenLogprobs]] = None      # one per output token, if the request asked for them
+    # seconds on the host's clock, as the reference's metrics define them (crates/server/src/metrics.rs:63-142):
+    # from arrival to the first token, mean time per token after the first, from arrival to the end
+    ttft_s: float = 0.0
+    tpot_s: float = 0.0
+    e2e_s: float = 0.0
 
 
 @dataclass
@@ -131,6 +136,7 @@ class LLM:
         if any((t < 0 or t >= vocab) for t in prompt_ids):
             raise ValueError(f"request {req_id!r}: a token id is outside the vocabulary [0, {vocab})")
         req = Request(req_id, list(prompt_ids), params or SamplingParams())
+        req.t_arrival = time.perf_counter()
         if any(t >= vocab for t in req.params.logit_bias):
             raise ValueError(f"request {req_id!r}: a logit_bias token id is outside the vocabulary [0, {vocab})")
         self.scheduler.add_request(req)
@@ -181,10 +187,14 @@ class LLM:
         outs = []
         for r in finished:
             self._forget(r.req_id)
+            n = len(r.output_ids)
             outs.append(RequestOutput(r.req_id, r.prompt_ids, r.output_ids,
                                       r.finish_reason.value if r.finish_reason else "abort",
                                       r.num_preemptions,
-                                      r.logprobs if r.params.logprobs is not None else None))
+                                      r.logprobs if r.params.logprobs is not None else None,
+                                      ttft_s=max(0.0, r.t_first_token - r.t_arrival) if n else 0.0,
+                                      tpot_s=(r.t_last_token - r.t_first_token) / (n - 1) if n > 1 else 0.0,
+                                      e2e_s=max(0.0, r.t_last_token - r.t_arrival) if n else 0.0))
         return outs
 
     def _launch(self, plan) -> "_InFlight":
@@ -234,9 +244,13 @@ class LLM:
             self.stats.generated_tokens += sum(1 for r in flight.samplers if not r.finished)
         before = {r.req_id: len(r.output_ids) for r in flight.samplers}
         done = self.scheduler.update(flight.plan, sampled)
+        now = time.perf_counter()
         for r in flight.samplers:                   # what was appended (a dropped token is not)
             if len(r.output_ids) > before[r.req_id]:
                 self._new_tokens.setdefault(r.req_id, []).extend(r.output_ids[before[r.req_id]:])
+                if before[r.req_id] == 0 and r.t_first_token == 0.0:
+                    r.t_first_token = now
+                r.t_last_token = now
         manager = self.runner.manager
         if manager.prefix_caching:                  # tokens the next step took on the device: the cache learns them
             for rid in flight.taken_ahead:

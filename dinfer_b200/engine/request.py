@@ -35,6 +35,10 @@ class Request:
     finish_reason: Optional[FinishReason] = None
     num_preemptions: int = 0
     logprobs: List[TokenLogprobs] = field(default_factory=list)   # one per output token, if asked for
+    # host clock (time.perf_counter): when the request came in, when the host read its first and its latest token
+    t_arrival: float = 0.0
+    t_first_token: float = 0.0
+    t_last_token: float = 0.0
 
     def __post_init__(self):
         if self.params.seed is not None:
