@@ -6,6 +6,7 @@ fraction of the memory / tensor-core roofline each reaches.
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--context C] [--layers L]
     python bench.py --shape 32b             # the same at the Qwen3-32B (or 0.6b) layer sizes
     python bench.py --serving               # 32 requests through LLM.generate at the Qwen3-0.6B shape
+    python bench.py --shape 0.6b --closed-loop 8,128,128    # the reference's "c8 p128 o128" at engine level
     python bench.py --impl reference        # the reference engine, where it can be installed
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch.  ``value`` times K steps on
@@ -281,6 +282,54 @@ def serving_run() -> int:
     return 0
 
 
+def closed_loop_run(shape: str, clients: int, prompt_len: int, output_len: int, requests_per_client: int = 6) -> int:
+    """The reference's serving measurement without the HTTP in between (its ``bench`` tool,
+    scripts/verify/bench_compare.sh: "cN pP oO" = N clients, each sending its next request when the last has ended,
+    prompts of P tokens, O generated tokens, temperature 0, ignore_eos, the first 2 requests of each client left
+    out): output tokens a second over the measured requests, time to the first token and time per token after it."""
+    import torch
+    from dinfer_b200 import LLM, SamplingParams
+    from dinfer_b200.weights.random_init import RandomSource
+    name, cfg = SHAPES[shape]
+    llm = LLM(config=cfg, weights=RandomSource(cfg, 3, std=0.02, norm_jitter=0.0), dtype="bfloat16",
+              max_model_len=max(2048, prompt_len + output_len + 64), max_num_seqs=max(16, clients),
+              max_num_batched_tokens=2048, block_size=16)
+    rng = random.Random(11)
+    sp = SamplingParams(temperature=0.0, max_tokens=output_len, ignore_eos=True)
+
+    def prompt():
+        return [rng.randrange(cfg["vocab_size"]) for _ in range(prompt_len)]
+    sent = {c: 0 for c in range(clients)}
+    owner, outs = {}, []
+    for c in range(clients):
+        owner[llm.add_request(prompt(), sp)] = c
+        sent[c] += 1
+    t_start = None
+    while llm.has_unfinished():
+        for o in llm.step():
+            c = owner.pop(o.req_id)
+            if sent[c] > 2:                                   # measured (the first two of a client warm up)
+                outs.append(o)
+            if sent[c] == 2 and t_start is None and all(n >= 2 for n in sent.values()):
+                torch.cuda.synchronize()
+                t_start = time.perf_counter()
+            if sent[c] < requests_per_client:
+                owner[llm.add_request(prompt(), sp)] = c
+                sent[c] += 1
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - (t_start or 0.0)
+    gen = sum(len(o.output_ids) for o in outs)
+    mid = len(outs) // 2
+    print(json.dumps({"metric": f"closed loop c{clients} p{prompt_len} o{output_len}: output tok/s ({name}, bf16, random "
+                                "weights, engine level, no HTTP)",
+                      "value": round(gen / dt, 1), "unit": "tokens/s", "requests": len(outs),
+                      "ttft_ms_p50": round(sorted(o.ttft_s for o in outs)[mid] * 1e3, 2),
+                      "tpot_ms_p50": round(sorted(o.tpot_s for o in outs)[mid] * 1e3, 3),
+                      "e2e_ms_p50": round(sorted(o.e2e_s for o in outs)[mid] * 1e3, 1),
+                      "seconds": round(dt, 3), "impl": "ours", "data": "synthetic"}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
@@ -297,6 +346,9 @@ def main() -> int:
     ap.add_argument("--serving", action="store_true",
                     help="the mixed serving workload instead: 32 requests, prompts of 16..1024 tokens, portions of "
                          "512, 256 tokens each at temperature 0.7, at the Qwen3-0.6B shape")
+    ap.add_argument("--closed-loop", default=None, metavar="C,P,O",
+                    help="the reference's serving measurement at engine level instead: C clients, each sending its "
+                         "next request when the last has ended, prompts of P tokens, O generated tokens (--shape applies)")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -312,6 +364,9 @@ def main() -> int:
         return profile_region(a)
     if a.serving:
         return serving_run()
+    if a.closed_loop:
+        c, p_len, o_len = (int(x) for x in a.closed_loop.split(","))
+        return closed_loop_run(a.shape, c, p_len, o_len)
     shape_name, cfg = SHAPES[a.shape]
     full_layers = cfg["num_hidden_layers"]
     if a.shape != "8b" and a.layers == FULL_LAYERS:

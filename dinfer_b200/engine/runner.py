@@ -34,15 +34,17 @@ from .batch import DecodePlan, OutOfPages, PlanBuilder, StepEntry
 _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
-def graph_shape(prompt_lens: Sequence[int], num_decodes: int, budget: int, buckets: Sequence[int], places: int,
-                small_max: int, padded_limit: int):
+def graph_shape(prompt_lens: Sequence[int], num_decodes: int, budget: int, buckets: Sequence[int],
+                place_counts: Sequence[int], small_max: int, padded_limit: int):
     """The shape of the captured graph a step with prompt portions replays, as (prompt tokens after padding,
-    decode bucket), or None for a step that runs kernel by kernel.  ``prompt_lens``: the tokens of the step's
-    prompt portions; ``places``: prompt portions a graph has room for (one of them taken by the padding);
-    ``small_max``: up to so many prompt tokens are padded to a power of two (from 16); ``padded_limit``: up to so
-    many are padded to a multiple of 128 (256 beyond 1024); portions that fill ``budget`` exactly need no padding."""
+    prompt places, decode bucket), or None for a step that runs kernel by kernel.  ``prompt_lens``: the tokens of
+    the step's prompt portions; ``place_counts``: the numbers of prompt places graphs are made with, rising (the
+    padding takes a place too; a place without tokens still costs the attention kernel an empty CTA per head and
+    row tile, hence more than one size); ``small_max``: up to so many prompt tokens are padded to a power of two
+    (from 16); ``padded_limit``: up to so many are padded to a multiple of 128 (256 beyond 1024); portions that
+    fill ``budget`` exactly need no padding."""
     have = sum(prompt_lens)
-    if not prompt_lens or len(prompt_lens) > places or any(n < 2 for n in prompt_lens):
+    if not prompt_lens or any(n < 2 for n in prompt_lens):
         return None
     if have == budget:
         total = budget
@@ -55,18 +57,20 @@ def graph_shape(prompt_lens: Sequence[int], num_decodes: int, budget: int, bucke
         total = min(budget, (have + unit - 1) // unit * unit)
         if total > padded_limit:
             return None
-    if total > budget or (total > have and len(prompt_lens) == places):
-        return None                                          # no room, or no place left, for the dummy portion
+    if total > budget:
+        return None                                          # no room for the dummy portion
+    need = len(prompt_lens) + (1 if total > have else 0)
+    places = next((p for p in place_counts if p >= need), None)
     bucket = 0 if not num_decodes else next((b for b in buckets if b >= num_decodes), None)
-    if bucket is None:
+    if places is None or bucket is None:
         return None
-    return total, bucket
+    return total, places, bucket
 
 
 class ModelRunner:
-    # prompt portions a captured mixed step has places for, and the most prompt tokens of a step that is padded up
-    # to a power of two to replay a graph (see _mixed_layout)
-    PROMPT_PLACES = 4
+    # the numbers of prompt places captured mixed steps are made with, and the most prompt tokens of a step that is
+    # padded up to a power of two to replay a graph (see graph_shape)
+    PROMPT_PLACES = (4, 16)
     PADDED_PROMPT_TOKENS = 128
     HOST_US_PER_LAYER = 120.0          # launching one layer's kernels one by one (measured, Python wrappers)
     DEVICE_FLOPS = 1.2e15              # what a prompt-sized step reaches on the device, roughly
@@ -98,7 +102,7 @@ class ModelRunner:
         self._make_caches()
         self.plan = PlanBuilder(self.manager, self.device,
                                 max_tokens=engine.max_num_batched_tokens + engine.max_num_seqs,
-                                max_reqs=engine.max_num_seqs + self.PROMPT_PLACES,
+                                max_reqs=engine.max_num_seqs + self.PROMPT_PLACES[-1],
                                 max_blocks=self.max_blocks_per_seq)
         # the tokens the last step sampled stay here (a fixed address, so that captured graphs can read it):
         # a step launched before the host has read them names them by row (see StepEntry.tokens)
@@ -313,9 +317,9 @@ class ModelRunner:
                             self.PADDED_PROMPT_TOKENS, self._padded_tokens)
         if shape is None:
             return None
-        total, bucket = shape
+        total, n_places, bucket = shape
         have = sum(len(entries[i].tokens) for i in prompts)
-        key = ("mixed", total, bucket)
+        key = ("mixed", total, n_places, bucket)
         if key not in self._graphs:
             self._mixed_seen[key] = self._mixed_seen.get(key, 0) + 1
             if self._mixed_seen[key] < 2:
@@ -323,18 +327,18 @@ class ModelRunner:
         places = [(i, len(entries[i].tokens)) for i in prompts]
         if total > have:
             places.append((-1, total - have))
-        places += [(-1, 0)] * (self.PROMPT_PLACES - len(places))
+        places += [(-1, 0)] * (n_places - len(places))
         places += [(i, 1) for i in decodes] + [(-1, 1)] * (bucket - len(decodes))
         return key, places
 
     def _capture_mixed(self, key):
         from ..kernels import attention_ops
-        _, total, bucket = key
+        _, total, n_places, bucket = key
         width = self.max_blocks_per_seq
-        B = self.PROMPT_PLACES + bucket
+        B = n_places + bucket
         dev = torch.empty(self.plan.words(total + bucket, B, B, width), dtype=torch.int32, device=self.device)
         # captured on a dummy batch of the same shape: one prompt place with all the tokens (no pages, no slots)
-        places = [(-1, total)] + [(-1, 0)] * (self.PROMPT_PLACES - 1) + [(-1, 1)] * bucket
+        places = [(-1, total)] + [(-1, 0)] * (n_places - 1) + [(-1, 1)] * bucket
         ids, rows, ctx = self.plan.build([], [], table_width=width, dev=dev, slots=places)
         hkv = max([n.num_kv_heads for n in self.model.cache_needs() if isinstance(n, KvCacheNeed)] or [1])
         ctx.decode_splits = attention_ops.decode_splits(max(1, bucket), hkv, self.engine.max_model_len)

@@ -73,18 +73,20 @@ def test_which_steps_replay_a_graph():
     buckets = [1, 2, 4, 8, 16]
 
     def shape(prompts, decodes=0, budget=2048, limit=128):
-        return graph_shape(prompts, decodes, budget, buckets, 4, 128, limit)
+        return graph_shape(prompts, decodes, budget, buckets, (4, 16), 128, limit)
 
-    assert shape([2048]) == (2048, 0) and shape([1000, 1048], 5) == (2048, 8)        # the budget, exactly
-    assert shape([5]) == (16, 0) and shape([16], 1) == (16, 1) and shape([17, 3]) == (32, 0)
-    assert shape([100], 16) == (128, 16) and shape([128]) == (128, 0)
+    assert shape([2048]) == (2048, 4, 0) and shape([1000, 1048], 5) == (2048, 4, 8)  # the budget, exactly
+    assert shape([128] * 16) == (2048, 16, 0)                                        # many short prompts: more places
+    assert shape([5]) == (16, 4, 0) and shape([16], 1) == (16, 4, 1) and shape([17, 3]) == (32, 4, 0)
+    assert shape([100], 16) == (128, 4, 16) and shape([128]) == (128, 4, 0)
     assert shape([129]) is None and shape([2047]) is None                            # a large model: kernel by kernel
-    assert shape([129], limit=4480) == (256, 0) and shape([1025], limit=4480) == (1280, 0)
-    assert shape([2000], limit=4480) == (2048, 0)                                    # never beyond the budget
-    assert shape([600], limit=512) is None and shape([500], limit=512) == (512, 0)
+    assert shape([129], limit=4480) == (256, 4, 0) and shape([1025], limit=4480) == (1280, 4, 0)
+    assert shape([2000], limit=4480) == (2048, 4, 0)                                 # never beyond the budget
+    assert shape([600], limit=512) is None and shape([500], limit=512) == (512, 4, 0)
     assert shape([], 4) is None and shape([100], 17) is None                         # no portion; too many decodes
-    assert shape([4, 4, 4, 4]) == (16, 0)                                            # four portions, nothing to pad
-    assert shape([4, 4, 4, 3]) is None                                               # no place left for the padding
-    assert shape([4, 4, 4, 4, 4]) is None
+    assert shape([4, 4, 4, 4]) == (16, 4, 0)                                         # four portions, nothing to pad
+    assert shape([4, 4, 4, 3]) == (16, 16, 0)                                        # the padding needs a fifth place
+    assert shape([4] * 16) == (64, 16, 0)
+    assert shape([4] * 15 + [3]) is None and shape([2] * 17) is None                 # 16 portions and padding; 17
     assert shape([40], budget=48) is None                                            # the padding would pass the budget
-    assert shape([48], budget=48) == (48, 0)
+    assert shape([48], budget=48) == (48, 4, 0)

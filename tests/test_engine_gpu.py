@@ -469,7 +469,7 @@ def test_a_long_prompt_whole_and_in_portions(tmp_path, dtype):
         for t in toks[n0:]:
             got.append(r.step([StepEntry("a", [t], [0])])[0].float().cpu())
         if budget == 512:
-            assert ("mixed", 512, 0) in r._graphs
+            assert ("mixed", 512, 4, 0) in r._graphs
         r.finish("a")
         r.check_device_status()
         results.append(torch.stack(got))
