@@ -72,12 +72,16 @@ def cmd_generate(a) -> int:
                         repetition_penalty=a.repetition_penalty, frequency_penalty=a.frequency_penalty,
                         presence_penalty=a.presence_penalty, seed=a.seed,
                         stop_token_ids=_ids(a.stop_token_ids) if a.stop_token_ids else [],
-                        ignore_eos=a.ignore_eos, logprobs=a.logprobs,
+                        ignore_eos=a.ignore_eos, logprobs=a.logprobs, prompt_logprobs=a.prompt_logprobs,
                         logit_bias={int(t): float(b) for t, b in
                                     (x.split(":") for x in a.logit_bias.replace(",", " ").split())})
     for o in llm.generate(prompts, sp):
         rec = {"id": o.req_id, "output_ids": o.output_ids, "finish_reason": o.finish_reason,
                "ttft_ms": round(o.ttft_s * 1e3, 3), "tpot_ms": round(o.tpot_s * 1e3, 3), "e2e_ms": round(o.e2e_s * 1e3, 3)}
+        if o.prompt_logprobs is not None:
+            rec["prompt_logprobs"] = [None if t is None else {"token_id": t.token_id, "logprob": t.logprob, "rank": t.rank,
+                                                             "top": list(zip(t.top_ids, t.top_logprobs))}
+                                      for t in o.prompt_logprobs]
         if o.logprobs is not None:
             rec["logprobs"] = [{"token_id": t.token_id, "logprob": t.logprob, "rank": t.rank,
                                 "top": list(zip(t.top_ids, t.top_logprobs))} for t in o.logprobs]
@@ -154,6 +158,9 @@ def main(argv=None) -> int:
     g.add_argument("--ignore-eos", action="store_true")
     g.add_argument("--logprobs", type=int, default=None,
                    help="with every generated token: its log-probability, its rank and this many most likely tokens")
+    g.add_argument("--prompt-logprobs", type=int, default=None,
+                   help="with every prompt token but the first: its log-probability given the tokens before it, its "
+                        "rank and this many most likely tokens")
     g.add_argument("--logit-bias", default="", help="TOKEN:BIAS pairs, comma separated, added to the logits")
     g.set_defaults(fn=cmd_generate)
     r = sub.add_parser("random-model", help="write a model folder with random weights")

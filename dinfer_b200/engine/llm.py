@@ -47,6 +47,7 @@ class RequestOutput:
     finish_reason: str
     num_preemptions: int = 0
     logprobs: Optional[List[TokenLogprobs]] = None      # one per output token, if the request asked for them
+    prompt_logprobs: Optional[List[Optional[TokenLogprobs]]] = None   # one per prompt token, None for the first
     # seconds on the host's clock, as the reference's metrics define them (crates/server/src/metrics.rs:63-142):
     # from arrival to the first token, mean time per token after the first, from arrival to the end
     ttft_s: float = 0.0
@@ -192,6 +193,7 @@ class LLM:
                                       r.finish_reason.value if r.finish_reason else "abort",
                                       r.num_preemptions,
                                       r.logprobs if r.params.logprobs is not None else None,
+                                      r.prompt_logprobs if r.params.prompt_logprobs is not None else None,
                                       ttft_s=max(0.0, r.t_first_token - r.t_arrival) if n else 0.0,
                                       tpot_s=(r.t_last_token - r.t_first_token) / (n - 1) if n > 1 else 0.0,
                                       e2e_s=max(0.0, r.t_last_token - r.t_arrival) if n else 0.0))
@@ -200,7 +202,7 @@ class LLM:
     def _launch(self, plan) -> "_InFlight":
         """Queue the step's device work and the copy of its sampled tokens to the host; wait for nothing."""
         prev_row = self._inflight.row if self._inflight is not None else {}
-        entries, samplers, generated = [], [], []
+        entries, samplers, generated, scored = [], [], [], []
         for s in plan.scheduled:
             r = s.request
             end = s.start + s.num_tokens
@@ -209,12 +211,24 @@ class LLM:
                 self._inflight.taken_ahead.add(r.req_id)
             else:
                 toks = r.tokens(s.start, end)
-            entries.append(StepEntry(r.req_id, toks, [s.num_tokens - 1] if s.samples else []))
+            want = [s.num_tokens - 1] if s.samples else []
+            if r.params.prompt_logprobs is not None and s.start == 0:
+                r.prompt_logprobs = [None]          # (a request that was preempted is scored again from the start)
+            if r.params.prompt_logprobs is not None and s.start < len(r.prompt_ids) - 1:
+                # every position of this portion that is followed by another prompt token: its logits say how
+                # likely that token was
+                if len(r.prompt_logprobs) == s.start + 1:
+                    upto = min(end, len(r.prompt_ids) - 1)
+                    scored.append((r, len(entries), s.start, upto))
+                    want = list(range(upto - s.start)) + want
+            entries.append(StepEntry(r.req_id, toks, want))
             if s.samples:
                 samplers.append(r)
                 generated.append(s.num_generated)
             self.stats.prompt_tokens += max(0, min(end, len(r.prompt_ids)) - s.start)
         logits = self.runner.step(entries, placeholders=True)
+        if scored:                                  # rows come in the order of the entries and of their wanted places
+            logits = self._score_prompts(logits, entries, scored)
         flight = _InFlight(plan, samplers, {r.req_id: i for i, r in enumerate(samplers)})
         if samplers:
             out = self.runner.sampled[:len(samplers)]
@@ -231,6 +245,26 @@ class LLM:
         if self.stats.steps % 256 == 0:
             self.runner.check_device_status()
         return flight
+
+    def _score_prompts(self, logits: torch.Tensor, entries, scored) -> torch.Tensor:
+        """Log-probabilities of the prompt tokens from the rows asked for them; returns the rows that are sampled
+        from.  (Such requests run one step at a time, so reading the result here stalls nothing that matters.)"""
+        from ..sampling.sampler import logprobs as row_logprobs
+        first_row, n = [], 0
+        for e in entries:
+            first_row.append(n)
+            n += len(e.want)
+        keep = torch.ones(n, dtype=torch.bool, device=logits.device)
+        for r, ei, lo, hi in scored:
+            a = first_row[ei]
+            rows = logits[a:a + hi - lo]
+            targets = torch.tensor(r.prompt_ids[lo + 1:hi + 1], dtype=torch.int32, device=logits.device)
+            k = r.params.prompt_logprobs
+            ids, lps, rank = (t.cpu().tolist() for t in row_logprobs(rows, targets, k))
+            for i in range(hi - lo):
+                r.prompt_logprobs.append(TokenLogprobs(ids[i][0], lps[i][0], rank[i], ids[i][1:1 + k], lps[i][1:1 + k]))
+            keep[a:a + hi - lo] = False
+        return logits[keep]
 
     def _collect(self) -> List[Request]:
         """Wait for the tokens of the step in flight and update its requests."""

@@ -35,6 +35,7 @@ class Request:
     finish_reason: Optional[FinishReason] = None
     num_preemptions: int = 0
     logprobs: List[TokenLogprobs] = field(default_factory=list)   # one per output token, if asked for
+    prompt_logprobs: List[Optional[TokenLogprobs]] = field(default_factory=list)   # one per prompt token (None first)
     # host clock (time.perf_counter): when the request came in, when the host read its first and its latest token
     t_arrival: float = 0.0
     t_first_token: float = 0.0

@@ -147,7 +147,8 @@ class Scheduler:
             while self.waiting and budget > 0 and len(self.running) < cfg.max_num_seqs:
                 req = self.waiting[0]
                 began = False
-                if req.num_computed == 0 and self.manager.prefix_caching and req.req_id not in self.manager:
+                if req.num_computed == 0 and self.manager.prefix_caching and req.req_id not in self.manager \
+                        and req.params.prompt_logprobs is None:      # (those want every prompt position run)
                     # pages of an earlier request with the same beginning: those tokens are not run again
                     req.num_computed = self.manager.begin(req.req_id, req.tokens(0, req.num_tokens))
                     began = req.num_computed > 0

@@ -1,6 +1,6 @@
 """Per-request sampling options: names, defaults and ranges of the reference's ``SamplingParams``
 (crates/core/src/sample.rs:81-205), without the options that need the tokenizer or the server (stop strings,
-grammars) and without prompt_logprobs."""
+grammars)."""
 from __future__ import annotations
 
 from dataclasses import dataclass, field
@@ -38,6 +38,10 @@ class SamplingParams:
     # None: no log-probabilities; k >= 0: every generated token comes with its log-probability and rank under
     # log_softmax of the model's logits (before bias, penalties and temperature) and with the k most likely tokens
     logprobs: Optional[int] = None
+    # k >= 0: every prompt position but the first comes with the log-probability and rank of its token given the
+    # tokens before it, and with the k most likely tokens there (the prompt is then run whole, not taken from the
+    # prefix cache)
+    prompt_logprobs: Optional[int] = None
     # token id -> bias added to the logits before the penalties (at most 300 entries)
     logit_bias: Dict[int, float] = field(default_factory=dict)
 
@@ -53,11 +57,13 @@ class SamplingParams:
     @property
     def needs_host_history(self) -> bool:
         """Options whose step cannot be launched before the last step's tokens are on the host."""
-        return self.has_penalties or self.logprobs is not None
+        return self.has_penalties or self.logprobs is not None or self.prompt_logprobs is not None
 
     def validate(self) -> None:
         if self.logprobs is not None and not (0 <= self.logprobs <= MAX_LOGPROBS):
             raise ValueError(f"logprobs must be in [0, {MAX_LOGPROBS}], got {self.logprobs}")
+        if self.prompt_logprobs is not None and not (0 <= self.prompt_logprobs <= MAX_LOGPROBS):
+            raise ValueError(f"prompt_logprobs must be in [0, {MAX_LOGPROBS}], got {self.prompt_logprobs}")
         if len(self.logit_bias) > MAX_LOGIT_BIAS:
             raise ValueError(f"logit_bias takes at most {MAX_LOGIT_BIAS} entries, got {len(self.logit_bias)}")
         for t, b in self.logit_bias.items():

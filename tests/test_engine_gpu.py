@@ -529,3 +529,32 @@ def test_tokens_can_be_taken_step_by_step(dirs):
                 streamed[rid] += toks
         assert all(streamed[i] == done[i].output_ids for i in ids)
         assert llm.take_new_tokens() == {}
+
+
+def test_prompt_logprobs(dirs):
+    """Every prompt token but the first comes with its log-probability given the tokens before it, also when the
+    prompt runs in portions beside other requests; against log_softmax of the plain implementation's logits."""
+    from dinfer_b200 import LLM, SamplingParams
+    cfg = H.TINY_A
+    W = H.load_plain_weights(dirs["A"])
+    rng = random.Random(6)
+    prompts = [H.random_tokens(rng, n, cfg["vocab_size"]) for n in (11, 2, 1, 7)]
+    llm = LLM(dirs["A"], dtype="float32", max_model_len=64, max_num_seqs=4, max_num_batched_tokens=4,
+              num_blocks=40, block_size=4, enable_prefix_caching=True)
+    sp = [SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True, prompt_logprobs=2),
+          SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True, prompt_logprobs=0),
+          SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True, prompt_logprobs=1),
+          SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)]
+    outs = llm.generate(prompts, sp)
+    assert outs[3].prompt_logprobs is None
+    for o, p, k in zip(outs[:3], prompts[:3], (2, 0, 1)):
+        assert o.output_ids == P.greedy_generate(W, cfg, p, 3)
+        assert len(o.prompt_logprobs) == len(p) and o.prompt_logprobs[0] is None
+        if len(p) > 1:
+            want = torch.log_softmax(P.qwen3_logits(W, cfg, p).double(), dim=-1)
+            for i in range(1, len(p)):
+                rec = o.prompt_logprobs[i]
+                assert rec.token_id == p[i] and abs(rec.logprob - float(want[i - 1, p[i]])) < 1e-4
+                assert rec.rank == int((want[i - 1] > want[i - 1, p[i]]).sum())
+                assert rec.top_ids == torch.topk(want[i - 1], k).indices.tolist() if k else rec.top_ids == []
+    llm.runner.manager.check_invariants()
