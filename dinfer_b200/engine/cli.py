@@ -67,8 +67,11 @@ def cmd_generate(a) -> int:
               enable_cuda_graph=not a.no_cuda_graph, enable_prefix_caching=a.enable_prefix_caching, split_norms=a.split_norms,
               async_scheduling=not a.no_async_scheduling, mixed_cuda_graph=not a.no_mixed_cuda_graph,
               device=a.device)
-    sp = SamplingParams(max_tokens=a.max_tokens, min_tokens=a.min_tokens, temperature=a.temperature,
-                        top_p=a.top_p, top_k=a.top_k, min_p=a.min_p,
+    d = llm.default_sampling_params
+    sp = SamplingParams(max_tokens=a.max_tokens, min_tokens=a.min_tokens,
+                        temperature=d.temperature if a.temperature is None else a.temperature,
+                        top_p=d.top_p if a.top_p is None else a.top_p,
+                        top_k=d.top_k if a.top_k is None else a.top_k, min_p=a.min_p,
                         repetition_penalty=a.repetition_penalty, frequency_penalty=a.frequency_penalty,
                         presence_penalty=a.presence_penalty, seed=a.seed,
                         stop_token_ids=_ids(a.stop_token_ids) if a.stop_token_ids else [],
@@ -146,9 +149,11 @@ def main(argv=None) -> int:
     g.add_argument("--prompt-file", help="one prompt a line: JSON list or separated ids")
     g.add_argument("--max-tokens", type=int, default=256)
     g.add_argument("--min-tokens", type=int, default=0)
-    g.add_argument("--temperature", type=float, default=1.0)
-    g.add_argument("--top-p", type=float, default=1.0)
-    g.add_argument("--top-k", type=int, default=-1)
+    g.add_argument("--temperature", type=float, default=None,
+                   help="default: the model folder's generation_config.json, else 1.0 (the same for --top-p, 1.0, "
+                        "and --top-k, -1 = off)")
+    g.add_argument("--top-p", type=float, default=None)
+    g.add_argument("--top-k", type=int, default=None)
     g.add_argument("--min-p", type=float, default=0.0)
     g.add_argument("--repetition-penalty", type=float, default=1.0)
     g.add_argument("--frequency-penalty", type=float, default=0.0)

@@ -23,6 +23,7 @@ updated; ``step()`` then returns what finished one launch earlier.
 """
 from __future__ import annotations
 
+import copy
 import time
 from dataclasses import dataclass
 from typing import Any, Dict, Hashable, List, Optional, Sequence, Union
@@ -30,7 +31,7 @@ from typing import Any, Dict, Hashable, List, Optional, Sequence, Union
 import torch
 
 from ..config.engine_config import EngineConfig
-from ..sampling.params import SamplingParams, TokenLogprobs
+from ..sampling.params import SamplingParams, TokenLogprobs, generation_defaults
 from ..sampling.sampler import Sampler
 from ..weights.loader import WeightSource
 from .batch import StepEntry
@@ -104,6 +105,9 @@ class LLM:
             split_norms=split_norms, async_scheduling=async_scheduling, mixed_cuda_graph=mixed_cuda_graph,
             dtype=dtype,
             device=device)
+        # what a request gets that brings no SamplingParams of its own: the model folder's generation_config.json
+        # (temperature, top_p, top_k) over the built-in defaults
+        self.default_sampling_params = generation_defaults(model)
         if model is not None:
             self.runner = ModelRunner.from_dir(model, self.engine_config)
         elif config is not None and weights is not None:
@@ -136,7 +140,7 @@ class LLM:
         vocab = self.runner.spec.vocab_size
         if any((t < 0 or t >= vocab) for t in prompt_ids):
             raise ValueError(f"request {req_id!r}: a token id is outside the vocabulary [0, {vocab})")
-        req = Request(req_id, list(prompt_ids), params or SamplingParams())
+        req = Request(req_id, list(prompt_ids), params or copy.copy(self.default_sampling_params))
         req.t_arrival = time.perf_counter()
         if any(t >= vocab for t in req.params.logit_bias):
             raise ValueError(f"request {req_id!r}: a logit_bias token id is outside the vocabulary [0, {vocab})")
@@ -309,12 +313,11 @@ class LLM:
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None
                  ) -> List[RequestOutput]:
         if sampling_params is None or isinstance(sampling_params, SamplingParams):
-            params = [sampling_params or SamplingParams()] * len(prompt_token_ids)
+            params = [sampling_params or self.default_sampling_params] * len(prompt_token_ids)
         else:
             params = list(sampling_params)
             if len(params) != len(prompt_token_ids):
                 raise ValueError("one SamplingParams per prompt")
-        import copy
         ids = [self.add_request(p, copy.copy(sp)) for p, sp in zip(prompt_token_ids, params)]
         done: Dict[Hashable, RequestOutput] = {}
         idle = 0

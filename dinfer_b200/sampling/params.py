@@ -3,6 +3,8 @@
 grammars)."""
 from __future__ import annotations
 
+import json
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
@@ -89,3 +91,26 @@ class SamplingParams:
             raise ValueError("max_tokens must be at least 1")
         if self.min_tokens > self.max_tokens:
             raise ValueError(f"min_tokens {self.min_tokens} > max_tokens {self.max_tokens}")
+
+
+def generation_defaults(model_dir: Optional[str]) -> SamplingParams:
+    """The sampling defaults a model folder brings: temperature, top_p and top_k of its ``generation_config.json``
+    over the built-in defaults, as the reference's server takes them (models/qwen3/src/service.rs:477-493).  A
+    folder without the file, or no folder, gives the built-in defaults."""
+    sp = SamplingParams()
+    path = os.path.join(model_dir, "generation_config.json") if model_dir else None
+    if path and os.path.isfile(path):
+        try:
+            with open(path, "r", encoding="utf-8") as f:
+                g = json.load(f)
+        except (OSError, json.JSONDecodeError):
+            return sp
+        if isinstance(g, dict):
+            t, p, k = g.get("temperature"), g.get("top_p"), g.get("top_k")
+            if isinstance(t, (int, float)) and not isinstance(t, bool):
+                sp.temperature = float(t)
+            if isinstance(p, (int, float)) and not isinstance(p, bool):
+                sp.top_p = float(p)
+            if isinstance(k, int) and not isinstance(k, bool):
+                sp.top_k = int(k) if k > 0 else -1
+    return sp

@@ -107,3 +107,22 @@ def test_generation_config_adds_eos_ids(tmp_path):
     (d / "generation_config.json").write_text(json.dumps({"eos_token_id": "x"}))
     with pytest.raises(Exception):
         read_config_json(str(d))
+
+
+def test_sampling_defaults_of_a_model_folder(tmp_path):
+    """temperature, top_p and top_k of generation_config.json stand in for the built-in defaults
+    (models/qwen3/src/service.rs:477-493); other keys, a broken file or no file change nothing."""
+    import json
+    from dinfer_b200.sampling.params import SamplingParams, generation_defaults
+    assert generation_defaults(None) == SamplingParams()
+    assert generation_defaults(str(tmp_path)) == SamplingParams()
+    (tmp_path / "generation_config.json").write_text(json.dumps(
+        {"temperature": 0.6, "top_p": 0.95, "top_k": 20, "do_sample": True, "eos_token_id": [1, 2], "max_new_tokens": 9}))
+    sp = generation_defaults(str(tmp_path))
+    assert (sp.temperature, sp.top_p, sp.top_k) == (0.6, 0.95, 20) and sp.max_tokens == SamplingParams().max_tokens
+    sp.validate()
+    (tmp_path / "generation_config.json").write_text(json.dumps({"top_k": 0, "temperature": True}))
+    sp = generation_defaults(str(tmp_path))
+    assert sp.top_k == -1 and sp.temperature == SamplingParams().temperature
+    (tmp_path / "generation_config.json").write_text("{ not json")
+    assert generation_defaults(str(tmp_path)) == SamplingParams()
