@@ -67,6 +67,9 @@ def cmd_generate(a) -> int:
               enable_cuda_graph=not a.no_cuda_graph, enable_prefix_caching=a.enable_prefix_caching, split_norms=a.split_norms,
               async_scheduling=not a.no_async_scheduling, mixed_cuda_graph=not a.no_mixed_cuda_graph,
               device=a.device)
+    su = llm.runner.startup_seconds
+    print(f"start-up: weights {su['weights']:.2f} s  kernels {su['kernels']:.2f} s  caches {su['caches']:.2f} s  "
+          f"({llm.runner.num_blocks} pages of {llm.engine_config.block_size} tokens)", file=sys.stderr)
     d = llm.default_sampling_params
     sp = SamplingParams(max_tokens=a.max_tokens, min_tokens=a.min_tokens,
                         temperature=d.temperature if a.temperature is None else a.temperature,

@@ -17,6 +17,7 @@ CUDA graph per batch bucket, steps with prompt portions replay one where their s
 from __future__ import annotations
 
 import math
+import time
 from typing import Any, Dict, Hashable, List, Sequence
 
 import torch
@@ -95,11 +96,18 @@ class ModelRunner:
                              f"max_position_embeddings {self.spec.max_positions}")
         env = BuildEnv(self.device, self.act_dtype, self.spec.hidden_size, self.spec.max_positions)
         self.model = DecoderModel(self.spec, env)
+        # where the start-up time goes, in seconds (the reference logs such phases: crates/layers/src/load.rs:35-136)
+        t0 = time.perf_counter()
         tensors = load_tensors(source, self.model.declarations(), self.act_dtype, self.device)
         self.model.bind(tensors)
         del tensors
+        torch.cuda.synchronize(self.device)
+        t1 = time.perf_counter()
         kernel_lib.preload(self.model.kernel_libraries())
+        t2 = time.perf_counter()
         self._make_caches()
+        torch.cuda.synchronize(self.device)
+        self.startup_seconds = {"weights": t1 - t0, "kernels": t2 - t1, "caches": time.perf_counter() - t2}
         self.plan = PlanBuilder(self.manager, self.device,
                                 max_tokens=engine.max_num_batched_tokens + engine.max_num_seqs,
                                 max_reqs=engine.max_num_seqs + self.PROMPT_PLACES[-1],
