@@ -193,10 +193,24 @@ qk_post_lanes_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ p
   }
 }
 
-// Head size 128 in bfloat16, the rotation over the whole head: half a warp per head, a lane owns 8 consecutive
-// elements (one 16-byte access), its rotation partner sits 8 lanes across.  A warp takes HALF_HP pairs of heads of
-// one token and requests all of them before it works on the first.
+// Head size 128 in bfloat16, the rotation over the whole head: half a warp per head.  A lane owns four consecutive
+// elements of the head's first half and the four elements 64 further on, which are their rotation partners, so the
+// rotation needs no exchange between lanes (two 8-byte accesses a head).  A warp takes HALF_HP pairs of heads of one
+// token and requests all of them before it works on the first.  Value heads are only copied into the cache.
 constexpr int HALF_HP = 3;
+
+__device__ __forceinline__ void unpack4(const uint2& x, float (&v)[4]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ uint2 pack4(const float (&v)[4]) {
+  uint2 x;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&x);
+  h[0] = __floats2bfloat162_rn(v[0], v[1]);
+  h[1] = __floats2bfloat162_rn(v[2], v[3]);
+  return x;
+}
 
 template <typename TW>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -211,63 +225,76 @@ qk_post_half_warp_kernel(__nv_bfloat16* __restrict__ qkv, int64_t ld, const int*
   const int side = lane >> 4, l = lane & 15;
   const int head0 = (blockIdx.y * WARPS + warp) * 2 * HALF_HP + side;
   const int heads = H + 2 * Hkv;
-  __nv_bfloat16* row = qkv + (int64_t)t * ld + l * 8;
-  uint4 in[HALF_HP];
+  __nv_bfloat16* row = qkv + (int64_t)t * ld + l * 4;          // this lane's elements of the first half
+  uint2 lo[HALF_HP], hi[HALF_HP];
 #pragma unroll
   for (int u = 0; u < HALF_HP; ++u)
-    if (head0 + 2 * u < heads) in[u] = *reinterpret_cast<const uint4*>(row + (int64_t)(head0 + 2 * u) * D);
-  float c[8], sn[8];
+    if (head0 + 2 * u < heads) {
+      lo[u] = *reinterpret_cast<const uint2*>(row + (int64_t)(head0 + 2 * u) * D);
+      hi[u] = *reinterpret_cast<const uint2*>(row + (int64_t)(head0 + 2 * u) * D + D / 2);
+    }
+  float4 c = make_float4(1.f, 1.f, 1.f, 1.f), sn = make_float4(0.f, 0.f, 0.f, 0.f);
   const bool has_table = cos_sin != nullptr;
   if (has_table) {
-    const float* cs = cos_sin + (int64_t)positions[t] * D + (l & 7) * 8;   // the pair's index inside the half
-    load8<float>(cs, c);
-    load8<float>(cs + D / 2, sn);
+    const float* cs = cos_sin + (int64_t)positions[t] * D + l * 4;
+    c = *reinterpret_cast<const float4*>(cs);
+    sn = *reinterpret_cast<const float4*>(cs + D / 2);
   }
+  const float cv[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
   const int slot = cache ? slots[t] : -1;
+  const int64_t blk = slot >= 0 ? slot / block_size : 0, off = slot >= 0 ? slot % block_size : 0;
 #pragma unroll
   for (int u = 0; u < HALF_HP; ++u) {
     const int head = head0 + 2 * u;
     const bool live = head < heads;                            // (the other half of the warp may still have a head)
     const int kind = head < H ? 0 : (head < H + Hkv ? 1 : 2);
-    float v[8];
-    float ss = 0.f;
-    if (live) {
-      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&in[u]);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h2[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = 0.f;
-    }
     const TW* w = !live ? nullptr : (kind == 0 ? q_weight : (kind == 1 ? k_weight : nullptr));
+    const bool rotate = has_table && live && kind != 2;
+    uint2 out_lo = lo[u], out_hi = hi[u];
+    float a[4], b[4];
+    float ss = 0.f;
+    if (live && kind != 2) {
+      unpack4(lo[u], a);
+      unpack4(hi[u], b);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ss += a[j] * a[j] + b[j] * b[j];
+    }
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // over the head's 16 lanes
-    if (w) {
-      const float rinv = rsqrtf(ss / (float)D + eps);
-      float wv[8];
-      load8<TW>(w + l * 8, wv);
+    if (live && kind != 2) {
+      if (w) {
+        const float rinv = rsqrtf(ss / (float)D + eps);
+        float wa[4], wb[4];
+        if constexpr (sizeof(TW) == 2) {
+          unpack4(*reinterpret_cast<const uint2*>(w + l * 4), wa);
+          unpack4(*reinterpret_cast<const uint2*>(w + D / 2 + l * 4), wb);
+        } else {
+          const float4 x = *reinterpret_cast<const float4*>(w + l * 4), y = *reinterpret_cast<const float4*>(w + D / 2 + l * 4);
+          wa[0] = x.x; wa[1] = x.y; wa[2] = x.z; wa[3] = x.w; wb[0] = y.x; wb[1] = y.y; wb[2] = y.z; wb[3] = y.w;
+        }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = v[j] * rinv * wv[j];
+        for (int j = 0; j < 4; ++j) { a[j] = a[j] * rinv * wa[j]; b[j] = b[j] * rinv * wb[j]; }
+      }
+      if (rotate) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float x = a[j], y = b[j];
+          a[j] = x * cv[j] - y * sv[j];
+          b[j] = y * cv[j] + x * sv[j];
+        }
+      }
+      out_lo = pack4(a);
+      out_hi = pack4(b);
+      if (w || rotate) {
+        *reinterpret_cast<uint2*>(row + (int64_t)head * D) = out_lo;
+        *reinterpret_cast<uint2*>(row + (int64_t)head * D + D / 2) = out_hi;
+      }
     }
-    const bool rotate = has_table && live && kind != 2;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
-      if (rotate) v[j] = l < 8 ? v[j] * c[j] - other * sn[j] : v[j] * c[j] + other * sn[j];
-    }
-    if (!live) continue;
-    uint4 out;
-    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-    if (kind != 2 && (w || rotate)) *reinterpret_cast<uint4*>(row + (int64_t)head * D) = out;
-    if (kind != 0 && slot >= 0) {
-      const int64_t blk = slot / block_size, off = slot % block_size;
+    if (live && kind != 0 && slot >= 0) {
       const int hk = kind == 1 ? head - H : head - H - Hkv;
-      __nv_bfloat16* dst = cache + ((((blk * 2 + (kind - 1)) * Hkv + hk) * block_size + off) * (int64_t)D) + l * 8;
-      *reinterpret_cast<uint4*>(dst) = out;
+      __nv_bfloat16* dst = cache + ((((blk * 2 + (kind - 1)) * Hkv + hk) * block_size + off) * (int64_t)D) + l * 4;
+      *reinterpret_cast<uint2*>(dst) = out_lo;
+      *reinterpret_cast<uint2*>(dst + D / 2) = out_hi;
     }
   }
 }
