@@ -111,6 +111,20 @@ class CacheManager:
             return False
         return all(n <= p.num_free for n, p in zip(self._need(held, total_tokens), self.pools))
 
+    def can_allocate_all(self, wanted: Sequence) -> bool:
+        """Whether every ``(request, total_tokens)`` of ``wanted`` can be allocated together (a step's batch:
+        asked before any of them is, so that a step that does not fit changes nothing)."""
+        need = [0] * len(self.groups)
+        new = 0
+        for req, total in wanted:
+            held = self._reqs.get(req)
+            new += held is None
+            if held is not None and total <= held.capacity:
+                continue
+            for g, n in enumerate(self._need(held, total)):
+                need[g] += n
+        return new <= self.state_slots.num_free and all(n <= p.num_free for n, p in zip(need, self.pools))
+
     # ---- changes
     def begin(self, req: Hashable, token_ids: Sequence[int]) -> int:
         """A request enters with these tokens: take the pages of their longest cached prefix (whole

@@ -33,6 +33,12 @@ class EngineConfig:
     # shape and bucket of decoded tokens beside them; pays where launching a step's kernels one by one takes the
     # host longer than the device needs to run them (small models, short prompts)
     mixed_cuda_graph: bool = True
+    # the two estimates that decide up to how many prompt tokens a step is padded to replay a graph: what launching
+    # one layer's kernels one by one costs the host (microseconds; measured through the Python wrappers) and what a
+    # prompt-sized step reaches on the device (flops a second).  Fixed numbers, not measurements at start-up, so
+    # that every run of a workload decides the same way
+    graph_host_us_per_layer: float = 120.0
+    graph_device_flops: float = 1.2e15
     # full pages of computed tokens stay findable by the hash of their tokens and are shared by later
     # requests with the same beginning (off by default: with it on, freed pages are not the next ones used)
     enable_prefix_caching: bool = False
@@ -63,5 +69,7 @@ class EngineConfig:
             raise ValueError("max_model_len must be at least 2")
         if not (0.0 < self.gpu_memory_utilization <= 1.0):
             raise ValueError("gpu_memory_utilization must be in (0, 1]")
+        if self.graph_host_us_per_layer < 0 or self.graph_device_flops <= 0:
+            raise ValueError("graph_host_us_per_layer must not be negative and graph_device_flops must be positive")
         if self.num_blocks is not None and self.num_blocks <= 0:
             raise ValueError("num_blocks must be positive")

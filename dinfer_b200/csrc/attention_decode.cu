@@ -17,6 +17,8 @@
 // crates/kernels/cuda/gqa.cu:1423-1461), CUDA-core dot products with the group limited to 4.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "attention_decode_static.h"
 
@@ -802,12 +804,9 @@ DINFER_API int64_t dinfer_attention_decode_scratch_bytes(int B, int H, int Hkv, 
   return splits > 1 ? ((int64_t)B * H * splits * (D + 2) + (int64_t)B * Hkv) * 4 : 0;
 }
 
-// Requests whose portion is not exactly one token are skipped (left to the prompt kernel).
-DINFER_API int dinfer_attention_decode(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
-                                       const int* block_table, int max_blocks, const int* cu_seqlens,
-                                       const int* seq_lens, int B, int H, int Hkv, int D, int block_size,
-                                       float scale, int window, int splits, float* scratch_floats,
-                                       int* scratch_counters, cudaStream_t stream) {
+// What the cp.async variant takes (shared by the two entry points that launch it); 0 or a refusal.
+static int check_decode_arguments(const void* q, int64_t ldq, int64_t ldo, const void* cache, int max_blocks, int B, int H,
+                                  int Hkv, int D, int block_size, int splits) {
   if (B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || max_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_decode: bad sizes B=%d H=%d Hkv=%d", B, H, Hkv);
   if (!dinfer_attention_decode_supports(D, H / Hkv, block_size))
@@ -816,9 +815,20 @@ DINFER_API int dinfer_attention_decode(const void* q, int64_t ldq, void* out, in
   if ((ldq % 2) || (ldo % 2) || (reinterpret_cast<uintptr_t>(q) & 3) || (reinterpret_cast<uintptr_t>(cache) & 15))
     return refuse(DINFER_BAD_ARGUMENT, "attention_decode: q rows must be 4-byte and the cache 16-byte aligned");
   if (splits > 32) return refuse(DINFER_BAD_ARGUMENT, "attention_decode: at most 32 key splits, got %d", splits);
-  if (splits < 1 || (splits > 1 && (!scratch_floats || !scratch_counters)))
-    return refuse(DINFER_BAD_ARGUMENT, "attention_decode: splits=%d needs scratch", splits);
+  if (splits < 1) return refuse(DINFER_BAD_ARGUMENT, "attention_decode: splits=%d", splits);
   if (Hkv > 65535 || B > 65535) return refuse(DINFER_BAD_ARGUMENT, "attention_decode: too many heads or requests for the grid");
+  return 0;
+}
+
+// Requests whose portion is not exactly one token are skipped (left to the prompt kernel).
+DINFER_API int dinfer_attention_decode(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                       const int* block_table, int max_blocks, const int* cu_seqlens,
+                                       const int* seq_lens, int B, int H, int Hkv, int D, int block_size,
+                                       float scale, int window, int splits, float* scratch_floats,
+                                       int* scratch_counters, cudaStream_t stream) {
+  if (int rc = check_decode_arguments(q, ldq, ldo, cache, max_blocks, B, H, Hkv, D, block_size, splits)) return rc;
+  if (splits > 1 && (!scratch_floats || !scratch_counters))
+    return refuse(DINFER_BAD_ARGUMENT, "attention_decode: splits=%d needs scratch", splits);
   Params p;
   p.q = (const __nv_bfloat16*)q; p.ldq = ldq; p.out = (__nv_bfloat16*)out; p.ldo = ldo;
   p.cache = (const __nv_bfloat16*)cache; p.block_table = block_table; p.max_blocks = max_blocks;
@@ -893,8 +903,9 @@ DINFER_API int dinfer_attention_decode_static(const void* q, int64_t ldq, void* 
                                               float scale, int window, int splits, cudaStream_t stream) {
   constexpr int MAX_DEVICES = 64;
   static unsigned char* base[MAX_DEVICES] = {nullptr};
-  if (B <= 0 || H <= 0 || Hkv <= 0 || D <= 0 || splits < 1)
-    return refuse(DINFER_BAD_ARGUMENT, "attention_decode_static: bad sizes B=%d H=%d Hkv=%d D=%d splits=%d", B, H, Hkv, D, splits);
+  static std::mutex base_lock;                    // two host threads may make their first calls together
+  // everything is checked before anything is queued on the caller's stream
+  if (int rc = check_decode_arguments(q, ldq, ldo, cache, max_blocks, B, H, Hkv, D, block_size, splits)) return rc;
   const int64_t floats = splits > 1 ? (int64_t)B * H * splits * (D + 2) : 0;
   const int64_t counters = splits > 1 ? (int64_t)B * Hkv : 0;
   if (floats > (int64_t)DINFER_DECODE_STATIC_FLOATS || counters > DINFER_DECODE_STATIC_COUNTERS)
@@ -906,15 +917,20 @@ DINFER_API int dinfer_attention_decode_static(const void* q, int64_t ldq, void* 
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
     return refuse(e != cudaSuccess ? (int)e : DINFER_BAD_ARGUMENT, "attention_decode_static: no usable current device (%d)", dev);
-  if (!base[dev]) {                               // once per device, with that device current
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
-    if (e != cudaSuccess || !p)
-      return refuse((int)e, "attention_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-    base[dev] = static_cast<unsigned char*>(p);
+  unsigned char* mine;
+  {
+    std::lock_guard<std::mutex> hold(base_lock);
+    if (!base[dev]) {                             // once per device, with that device current
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+      if (e != cudaSuccess || !p)
+        return refuse((int)e, "attention_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      base[dev] = static_cast<unsigned char*>(p);
+    }
+    mine = base[dev];
   }
-  float* fl = reinterpret_cast<float*>(base[dev]);
-  int* ct = reinterpret_cast<int*>(base[dev] + (size_t)DINFER_DECODE_STATIC_FLOATS * 4);
+  float* fl = reinterpret_cast<float*>(mine);
+  int* ct = reinterpret_cast<int*>(mine + (size_t)DINFER_DECODE_STATIC_FLOATS * 4);
   if (splits > 1) {                               // the counters must start at zero whatever the last call left
     e = cudaMemsetAsync(ct, 0, (size_t)counters * sizeof(int), stream);
     if (e != cudaSuccess) return refuse((int)e, "attention_decode_static: clearing the counters failed: %s", cudaGetErrorString(e));

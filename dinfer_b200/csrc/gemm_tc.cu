@@ -74,10 +74,10 @@ __device__ __forceinline__ uint64_t global_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: gives up after WAIT_LIMIT polls or about two seconds, whichever comes first.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Bounded wait: gives up after `limit` polls or about two seconds, whichever comes first.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = WAIT_LIMIT) {
   uint64_t start = 0;
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
@@ -705,6 +705,30 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
   return cuda_status("gemm_tc");
 }
 
+// What every bounded wait of this file does when it runs out, on its own: one CTA allocates tensor memory, waits
+// on an mbarrier that nobody arrives at (at most `polls` polls), records code 2, frees its tensor memory and
+// returns.  Launched by tests of the failure path only.
+__global__ void __launch_bounds__(64) wait_probe_kernel(int* status, uint32_t polls) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t s_tmem_base;
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(32) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  if (threadIdx.x == 0 && !mbar_wait(smem_u32(&bar), 0, polls)) atomicExch(status, 2);
+  __syncthreads();
+  if (warp == 1)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(s_tmem_base), "r"(32) : "memory");
+}
+
 int num_sms() {
   static int n = 0;
   if (!n) {
@@ -824,6 +848,15 @@ DINFER_API int dinfer_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t
                               cudaStream_t stream) {
   return dinfer_gemm_tc_fused(x, ldx, w, ldw, out, ldc, out_f32, tokens, N, K, splits, act, nullptr, 0, nullptr, 0,
                               nullptr, nullptr, 0, 0, 0.f, 0.f, status, stream);
+}
+
+// For tests of the failure path: a wait of at most `polls` polls (1..65536) that nothing ends; the kernel gives
+// up, sets *status = 2, frees its tensor memory and returns.
+DINFER_API int dinfer_gemm_tc_wait_probe(int* status, int polls, cudaStream_t stream) {
+  if (!status) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc_wait_probe: a status word is required");
+  if (polls < 1 || polls > 65536) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc_wait_probe: polls must be in 1..65536, got %d", polls);
+  wait_probe_kernel<<<1, 64, 0, stream>>>(status, (uint32_t)polls);
+  return cuda_status("gemm_tc_wait_probe");
 }
 
 // Parts of the sums of squares the residual epilogue writes for these sizes: 128-row tiles times effective K splits.

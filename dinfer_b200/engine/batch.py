@@ -48,10 +48,12 @@ class PlanBuilder:
 
     RING = 4
 
-    def __init__(self, manager: CacheManager, device, max_tokens: int, max_reqs: int, max_blocks: int):
+    def __init__(self, manager: CacheManager, device, max_tokens: int, max_reqs: int, max_blocks: int,
+                 max_positions: Optional[int] = None):
         self.manager = manager
         self.device = device
         self.max_blocks = max_blocks
+        self.max_positions = max_positions          # rows of the position table (None: not known here)
         self.max_tokens, self.max_reqs = max_tokens, max_reqs
         self.capacity = self.words(max_tokens, max_reqs, max_tokens, max_blocks)
         on_gpu = torch.device(device).type == "cuda"
@@ -81,9 +83,15 @@ class PlanBuilder:
 
     def _validate(self, T, B, cu, seq, pos, rows, tables, slot_maps) -> None:
         """What every kernel takes for granted about a plan (checked on the host when DINFER_VALIDATE_PLANS=1, as
-        the tests do: the device tools that would catch an access out of range are not at hand everywhere)."""
+        the tests do: the device tools that would catch an access out of range are not at hand everywhere).
+        Dummy requests are held to the same rules: a kernel walks their tables and looks their positions up too."""
         m = self.manager
         bs = m.block_size
+        if B and tables and int(seq.max()) > tables[0].shape[1] * bs:
+            raise AssertionError(f"plan: a request of {int(seq.max())} tokens is longer than its table of "
+                                 f"{tables[0].shape[1]} pages covers")
+        if T and self.max_positions is not None and int(pos.max()) >= self.max_positions:
+            raise AssertionError(f"plan: position {int(pos.max())} is outside the position table of {self.max_positions}")
         if int(cu[0]) != 0 or int(cu[-1]) != T or np.any(np.diff(cu) < 0):
             raise AssertionError("plan: request offsets must rise from 0 to the number of tokens")
         if rows.size and (rows.min() < 0 or rows.max() >= max(T, 1)):

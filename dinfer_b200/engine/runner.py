@@ -18,7 +18,7 @@ from __future__ import annotations
 
 import math
 import time
-from typing import Any, Dict, Hashable, List, Sequence
+from typing import Any, Dict, Hashable, List, Optional, Sequence
 
 import torch
 
@@ -36,14 +36,16 @@ _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
 def graph_shape(prompt_lens: Sequence[int], num_decodes: int, budget: int, buckets: Sequence[int],
-                place_counts: Sequence[int], small_max: int, padded_limit: int):
+                place_counts: Sequence[int], small_max: int, padded_limit: int, longest: Optional[int] = None):
     """The shape of the captured graph a step with prompt portions replays, as (prompt tokens after padding,
     prompt places, decode bucket), or None for a step that runs kernel by kernel.  ``prompt_lens``: the tokens of
     the step's prompt portions; ``place_counts``: the numbers of prompt places graphs are made with, rising (the
     padding takes a place too; a place without tokens still costs the attention kernel an empty CTA per head and
     row tile, hence more than one size); ``small_max``: up to so many prompt tokens are padded to a power of two
     (from 16); ``padded_limit``: up to so many are padded to a multiple of 128 (256 beyond 1024); portions that
-    fill ``budget`` exactly need no padding."""
+    fill ``budget`` exactly need no padding.  ``longest``: the most tokens one place may hold (the longest request
+    the cache tables and the position table are made for); a step whose dummy portion, or whose capture (dummy
+    portions only), would need a longer one runs kernel by kernel."""
     have = sum(prompt_lens)
     if not prompt_lens or any(n < 2 for n in prompt_lens):
         return None
@@ -65,7 +67,23 @@ def graph_shape(prompt_lens: Sequence[int], num_decodes: int, budget: int, bucke
     bucket = 0 if not num_decodes else next((b for b in buckets if b >= num_decodes), None)
     if places is None or bucket is None:
         return None
+    if longest is not None and (total - have > longest or capture_places(total, places, bucket, longest) is None):
+        return None
     return total, places, bucket
+
+
+def capture_places(total: int, n_places: int, bucket: int, longest: int):
+    """The dummy batch a graph of this shape is captured on, as (-1, tokens) per place: ``total`` prompt tokens
+    spread over the prompt places, none longer than ``longest``, then the bucket's one-token places.  None when
+    the places cannot hold them."""
+    places, rest = [], total
+    for _ in range(n_places):
+        n = min(rest, longest)
+        places.append((-1, n))
+        rest -= n
+    if rest > 0:
+        return None
+    return places + [(-1, 1)] * bucket
 
 
 class ModelRunner:
@@ -73,8 +91,6 @@ class ModelRunner:
     # padded up to a power of two to replay a graph (see graph_shape)
     PROMPT_PLACES = (4, 16)
     PADDED_PROMPT_TOKENS = 128
-    HOST_US_PER_LAYER = 120.0          # launching one layer's kernels one by one (measured, Python wrappers)
-    DEVICE_FLOPS = 1.2e15              # what a prompt-sized step reaches on the device, roughly
 
     def __init__(self, config_dict: Dict[str, Any], source: WeightSource, engine: EngineConfig):
         engine.check()
@@ -87,6 +103,9 @@ class ModelRunner:
         # true 32-bit means no reduced-precision matrix mode anywhere, library calls included
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
+        # the library's bfloat16 products fold their K splits in 32-bit, like the engine's own kernels do, so that
+        # the same tokens run in a large step and in a small one differ by one rounding only
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         self.act_dtype = _TORCH_DTYPE[engine.dtype]
         arch = resolve_architecture(config_dict)
         self.config = arch.parse_config(config_dict)
@@ -111,7 +130,7 @@ class ModelRunner:
         self.plan = PlanBuilder(self.manager, self.device,
                                 max_tokens=engine.max_num_batched_tokens + engine.max_num_seqs,
                                 max_reqs=engine.max_num_seqs + self.PROMPT_PLACES[-1],
-                                max_blocks=self.max_blocks_per_seq)
+                                max_blocks=self.max_blocks_per_seq, max_positions=self.spec.max_positions)
         # the tokens the last step sampled stay here (a fixed address, so that captured graphs can read it):
         # a step launched before the host has read them names them by row (see StepEntry.tokens)
         self.sampled = torch.zeros(max(1, engine.max_num_seqs), dtype=torch.int32, device=self.device)
@@ -203,10 +222,16 @@ class ModelRunner:
             if total > self.engine.max_model_len:
                 raise ValueError(f"request {e.req_id!r} would reach {total} tokens, max_model_len is "
                                  f"{self.engine.max_model_len}")
-            if not m.allocate(e.req_id, total):
-                raise OutOfPages(f"no pages for request {e.req_id!r} ({total} tokens; "
-                                 f"{[p.num_free for p in m.pools]} pages free)")
             starts.append(start)
+        # all or nothing: a step that does not fit leaves every table and state slot as it was
+        totals = [(e.req_id, s + len(e.tokens)) for e, s in zip(entries, starts)]
+        if not m.can_allocate_all(totals):
+            raise OutOfPages(f"no pages for this step of {len(entries)} requests growing to "
+                             f"{[t for _, t in totals]} tokens ({[p.num_free for p in m.pools]} pages free, "
+                             f"{m.state_slots.num_free} state slots free)")
+        for rid, total in totals:
+            if not m.allocate(rid, total):
+                raise RuntimeError(f"request {rid!r}: the cache manager refused pages it had promised")
         mixed = None
         if self._graph_ok and len(entries) <= self._buckets[-1] and all(len(e.tokens) == 1 for e in entries):
             logits = self._graph_step(entries, starts)
@@ -294,13 +319,13 @@ class ModelRunner:
         """The most prompt tokens of a step that is padded (up to a multiple of 128) to replay a graph: as long as
         launching the step kernel by kernel would keep the host busy for longer than the device needs for the
         padded step.  Both sides are estimates from the model's sizes, so the answer is the same in every run:
-        ``HOST_US_PER_LAYER`` for the host (measured: 120 us a layer through the Python wrappers, whatever the
-        rows), two flops per weight and token at ``DEVICE_FLOPS`` for the device."""
+        ``EngineConfig.graph_host_us_per_layer`` for the host, two flops per weight and token at
+        ``EngineConfig.graph_device_flops`` for the device."""
         table = (self.spec.vocab_size, self.spec.hidden_size)       # the table and the head do not see every row
         weights = sum(math.prod(d.shape) for d in self.model.declarations()
                       if len(d.shape) == 2 and tuple(d.shape) != table)
-        host_s = len(self.spec.schedule) * self.HOST_US_PER_LAYER * 1e-6
-        tokens = int(host_s * self.DEVICE_FLOPS / (2.0 * max(1, weights)))
+        host_s = len(self.spec.schedule) * self.engine.graph_host_us_per_layer * 1e-6
+        tokens = int(host_s * self.engine.graph_device_flops / (2.0 * max(1, weights)))
         return max(self.PADDED_PROMPT_TOKENS, tokens // 128 * 128)
 
     def _mixed_layout(self, entries: Sequence[StepEntry]):
@@ -322,7 +347,7 @@ class ModelRunner:
             return None                                      # only the last token's logits come out of a place
         shape = graph_shape([len(entries[i].tokens) for i in prompts], len(decodes),
                             self.engine.max_num_batched_tokens, self._buckets, self.PROMPT_PLACES,
-                            self.PADDED_PROMPT_TOKENS, self._padded_tokens)
+                            self.PADDED_PROMPT_TOKENS, self._padded_tokens, longest=self.engine.max_model_len)
         if shape is None:
             return None
         total, n_places, bucket = shape
@@ -345,8 +370,9 @@ class ModelRunner:
         width = self.max_blocks_per_seq
         B = n_places + bucket
         dev = torch.empty(self.plan.words(total + bucket, B, B, width), dtype=torch.int32, device=self.device)
-        # captured on a dummy batch of the same shape: one prompt place with all the tokens (no pages, no slots)
-        places = [(-1, total)] + [(-1, 0)] * (n_places - 1) + [(-1, 1)] * bucket
+        # captured on a dummy batch of the same shape (no pages, no slots): the prompt tokens in as few places as
+        # hold them without passing the longest request the tables and the position table are made for
+        places = capture_places(total, n_places, bucket, self.engine.max_model_len)
         ids, rows, ctx = self.plan.build([], [], table_width=width, dev=dev, slots=places)
         hkv = max([n.num_kv_heads for n in self.model.cache_needs() if isinstance(n, KvCacheNeed)] or [1])
         ctx.decode_splits = attention_ops.decode_splits(max(1, bucket), hkv, self.engine.max_model_len)
@@ -389,6 +415,11 @@ class ModelRunner:
         Reading the word synchronizes with the device."""
         from ..kernels import gemm_ops
         gemm_ops.check_status(self.device)
+
+    def reset_device_status(self) -> int:
+        """Clear the status word after a reported fault; returns the code it held."""
+        from ..kernels import gemm_ops
+        return gemm_ops.reset_status(self.device)
 
     def finish(self, req_id: Hashable) -> None:
         """The request is over: its pages and state slot go back to the pools."""

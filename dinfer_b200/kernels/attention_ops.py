@@ -6,10 +6,9 @@ from typing import Optional
 
 import torch
 
-from .lib import KernelError, check, ptr, require_cuda, stream_handle
+from .lib import KernelError, check, num_sms, ptr, require_cuda, stream_handle
 from .ops import _fn
 
-NUM_SMS = 148
 MAX_CLUSTER_SPLITS = 16         # key splits of the TMA decode kernel: one thread-block cluster
 
 
@@ -22,7 +21,7 @@ def decode_splits(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
     splits fill those slots in one wave; with as many pairs as slots or more, splitting only adds
     partial sums to fold, so there is none.  Never more than a quarter of the 64-key tiles, at
     most 16 (the largest cluster)."""
-    slots = 2 * NUM_SMS
+    slots = 2 * num_sms()
     base = max(1, num_reqs * num_kv_heads)
     want = slots // base if base <= slots else 1
     tiles = max(1, (max_seq_len + 63) // 64)

@@ -6,10 +6,9 @@ from typing import Optional
 
 import torch
 
-from .lib import KernelError, check, ptr, require_cuda, stream_handle
+from .lib import KernelError, check, num_sms, ptr, require_cuda, stream_handle
 from .ops import _fn
 
-NUM_SMS = 148
 DECODE_MAX_TOKENS = 64          # up to here the operands are swapped (weight rows fill the tile)
 MAX_SPLITS = 8                  # the portable cluster size
 
@@ -25,20 +24,69 @@ def _state(device):
     return st
 
 
-def device_status(device=None) -> int:
-    """The status word of the tcgen05 kernels (0 = fine).  Reading it synchronizes."""
-    device = torch.device(device or torch.cuda.current_device())
+def _device(device=None) -> torch.device:
+    device = torch.device(device if device is not None else torch.cuda.current_device())
     if device.type == "cuda" and device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
-    st = _STATE.get(device)
+    return device
+
+
+def device_status(device=None) -> int:
+    """The status word of the kernels with bounded waits (0 = fine).  Reading it synchronizes."""
+    st = _STATE.get(_device(device))
     return int(st["status"].item()) if st else 0
 
 
+# what a kernel was waiting for when it gave up (the code it left in the status word)
+STATUS_MEANING = {
+    1: "matrix product: the TMA producer waited for a free shared-memory stage",
+    2: "matrix product: the MMA thread waited for an operand tile (or a free accumulator)",
+    3: "matrix product: the epilogue warps waited for the accumulator",
+    11: "prompt attention: the TMA producer waited for a free K/V stage",
+    12: "prompt attention: the MMA thread waited for the Q or the first K tiles",
+    13: "prompt attention: the MMA thread waited for the softmax warps' P tile",
+    14: "prompt attention: the MMA thread waited for a K or V tile",
+    15: "prompt attention: the softmax warps waited for a score tile or for P V to finish",
+    16: "prompt attention: the softmax warps waited for the last P V before writing the output",
+    21: "decode attention: the TMA producer waited for a free stage",
+    22: "decode attention: the compute warps waited for a key/value tile",
+}
+
+
+def describe_status(code: int) -> str:
+    return STATUS_MEANING.get(int(code), "unknown code")
+
+
 def check_status(device=None) -> None:
+    """Raise if a kernel gave up one of its bounded waits.  The word stays set (every later check raises too)
+    until ``reset_status``: after such a fault the step's results are not to be trusted."""
     code = device_status(device)
     if code:
-        raise KernelError(f"a tcgen05 kernel gave up a bounded wait (status {code}: 1 = producer waiting for a free "
-                          f"stage, 2 = MMA waiting for a tile, 3 = epilogue waiting for the accumulator)")
+        raise KernelError(f"a kernel gave up a bounded wait and returned early (status {code}: "
+                          f"{describe_status(code)}); the results of that step are invalid")
+
+
+def reset_status(device=None) -> int:
+    """Clear the status word; returns the code it held."""
+    st = _STATE.get(_device(device))
+    if st is None:
+        return 0
+    code = int(st["status"].item())
+    st["status"].zero_()
+    return code
+
+
+def wait_probe(polls: int = 1000, device=None) -> int:
+    """Launch one CTA that allocates tensor memory and waits, with the products' own bounded wait cut down to
+    ``polls`` polls, on an mbarrier nobody arrives at; it must give up, record code 2 in the status word, free its
+    tensor memory and return.  Returns the status word after it (reading synchronizes).  For tests of the
+    failure path; nothing in the engine calls it."""
+    device = _device(device)
+    st = _state(device)
+    lib, f = _fn("gemm_tc", "dinfer_gemm_tc_wait_probe", [c_void_p, c_int, c_void_p])
+    with torch.cuda.device(device):
+        check(lib, f(ptr(st["status"]), int(polls), stream_handle()), "gemm_tc_wait_probe")
+    return device_status(device)
 
 
 def supported(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -55,7 +103,8 @@ def decode_splits(tokens: int, N: int, K: int) -> int:
     one thread-block cluster)."""
     tiles = (N + 127) // 128
     k_blocks = (K + 63) // 64
-    slots = 3 * NUM_SMS if tokens <= 16 else 2 * NUM_SMS - 16
+    sms = num_sms()
+    slots = 3 * sms if tokens <= 16 else 2 * sms - 16
     return max(1, min(slots // tiles, k_blocks // 8, MAX_SPLITS))
 
 

@@ -50,6 +50,21 @@ def preload(names) -> None:
             library(n)
 
 
+_SMS: Dict[int, int] = {}
+
+
+def num_sms(device=None) -> int:
+    """Streaming multiprocessors of the device (the current one by default), asked once per device; the split
+    heuristics size their grids by it.  148 (a whole B200) where no device can be asked."""
+    if not torch.cuda.is_available():
+        return 148
+    idx = torch.cuda.current_device() if device is None else (torch.device(device).index or torch.cuda.current_device())
+    n = _SMS.get(idx)
+    if n is None:
+        n = _SMS[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+    return n
+
+
 _launches = 0
 
 

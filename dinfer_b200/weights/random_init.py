@@ -61,14 +61,15 @@ def model_declarations(config_dict: Dict[str, Any]) -> List[TensorDecl]:
 
 
 def write_random_model(model_dir: str, config_dict: Dict[str, Any], seed: int, std: float = 0.02,
-                       norm_jitter: float = 0.0, dtype: torch.dtype = torch.bfloat16) -> str:
-    """Write ``config.json`` and ``model.safetensors`` into ``model_dir``."""
+                       norm_jitter: float = 0.0, dtype: torch.dtype = torch.bfloat16, device="cpu") -> str:
+    """Write ``config.json`` and ``model.safetensors`` into ``model_dir``.  ``device``: where the values are drawn
+    (a large model is made much faster on a CUDA device; the values depend on the kind of device)."""
     decls = model_declarations(config_dict)
     os.makedirs(model_dir, exist_ok=True)
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(config_dict, f, indent=1)
     write_safetensors(os.path.join(model_dir, "model.safetensors"),
-                      ((d.name, random_tensor(d, seed, std, norm_jitter, dtype)) for d in decls),
+                      ((d.name, random_tensor(d, seed, std, norm_jitter, dtype, device).cpu()) for d in decls),
                       metadata={"format": "pt", "seed": str(seed)})
     return model_dir
 

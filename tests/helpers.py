@@ -48,9 +48,9 @@ CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def make_model_dir(path: str, cfg: dict, seed: int, std: float, jitter: float,
-                   dtype: torch.dtype = torch.bfloat16) -> str:
+                   dtype: torch.dtype = torch.bfloat16, device: str = "cpu") -> str:
     from dinfer_b200.weights.random_init import write_random_model
-    return write_random_model(path, cfg, seed, std, jitter, dtype)
+    return write_random_model(path, cfg, seed, std, jitter, dtype, device=device)
 
 
 def load_plain_weights(model_dir: str) -> Dict[str, torch.Tensor]:
@@ -68,7 +68,7 @@ class PlainOracle:
 
     def __init__(self, model_dir: str):
         self.cfg = json.load(open(os.path.join(model_dir, "config.json")))
-        self.W = {k: v.to(torch.float64) for k, v in load_plain_weights(model_dir).items()}
+        self.W = load_plain_weights(model_dir)
         self._cache: Dict[Tuple[int, ...], np.ndarray] = {}
 
     def logits(self, ids: Sequence[int]) -> np.ndarray:
@@ -76,6 +76,25 @@ class PlainOracle:
         if key not in self._cache:
             self._cache[key] = plain_model.qwen3_logits(self.W, self.cfg, list(ids)).numpy()
         return self._cache[key]
+
+
+def check_greedy(oracle: "PlainOracle", prompt: Sequence[int], output_ids: Sequence[int], rel: float = 0.05) -> int:
+    """Every token of a greedy generation against the plain implementation run over the very sequence the engine
+    produced: the token is the plain logits' largest entry, or (reduced precision may leave the path at a
+    near-tie) lies within ``rel`` of the largest magnitude below it.  Returns how many were the largest."""
+    seq = list(prompt) + list(output_ids)
+    lg = oracle.logits(seq)
+    exact = 0
+    for i, t in enumerate(output_ids):
+        row = lg[len(prompt) - 1 + i]
+        top = int(row.argmax())
+        if t == top:
+            exact += 1
+            continue
+        gap = float(row[top] - row[t])
+        assert gap < rel * float(np.abs(row).max()), (f"token {i} of the output is {t}, the plain implementation "
+                                                      f"has {top}, {gap:.4f} above it (no near-tie)")
+    return exact
 
 
 class Replay:
@@ -163,6 +182,60 @@ def schedule_mixed(lengths: Dict[str, int], rng: random.Random, max_live: int = 
         if entries:
             steps.append((entries, end))
     return steps
+
+
+def schedule_mixed_large(lengths: Dict[str, int], rng: random.Random, portions=(40, 130, 512, 700),
+                         max_live: int = 4, decode_tail: int = 14, admit_every: int = 3):
+    """The steps a serving engine runs: up to ``max_live`` requests, prompts in LARGE portions (drawn from
+    ``portions``, so that a step's rows reach every product path: up to 32, 33..511, 512 and more) beside single
+    decoded tokens of the others; the last ``decode_tail`` tokens of every request come one by one.  A new request
+    is let in every ``admit_every`` steps at the earliest, so that its portions meet the others' decoded tokens;
+    a request may sit a step out; a finished one makes room, so pages are used again."""
+    waiting = list(lengths)
+    live: Dict[str, int] = {}
+    steps = []
+    since = admit_every
+    while waiting or live:
+        if waiting and len(live) < max_live and (since >= admit_every or not live):
+            live[waiting.pop(0)] = 0
+            since = 0
+        since += 1
+        entries, end = [], []
+        for r in list(live):
+            p, n = live[r], lengths[r]
+            left = n - p - decode_tail
+            if left <= 1 and len(live) > 1 and rng.random() < 0.15:
+                continue                                   # a decoding request sits this step out
+            c = 1 if left <= 1 else min(rng.choice(portions), left)
+            entries.append((r, p, p + c))
+            live[r] = p + c
+            if p + c == n:
+                end.append(r)
+                del live[r]
+        if entries:
+            steps.append((entries, end))
+    return steps
+
+
+def schedule_rolling(names: Sequence[str], portions: Sequence[int], n_decode: int, stagger: int = 1):
+    """Requests that are all alike, one starting every ``stagger`` steps: the prompt in ``portions`` (one a step),
+    then ``n_decode`` tokens one a step.  In the steady state every step has the same shape (the same portions
+    beside the same number of decoded tokens), which is what a captured graph of such a step needs to be replayed.
+    Returns (steps, lengths)."""
+    plan = list(portions) + [1] * n_decode
+    n_steps = (len(names) - 1) * stagger + len(plan)
+    steps = []
+    for t in range(n_steps):
+        entries, end = [], []
+        for i, r in enumerate(names):
+            k = t - i * stagger
+            if 0 <= k < len(plan):
+                lo = sum(plan[:k])
+                entries.append((r, lo, lo + plan[k]))
+                if k == len(plan) - 1:
+                    end.append(r)
+        steps.append((entries, end))
+    return steps, {r: sum(plan) for r in names}
 
 
 def max_live_tokens(steps, round_to: int = 64) -> int:

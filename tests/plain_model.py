@@ -130,20 +130,39 @@ def qwen3_logits(W: Dict[str, torch.Tensor], cfg: dict, ids: List[int],
     (models/qwen3/src/model.rs:821-853).  ``schedule`` lists the layers in the order they run
     (default: each once, in order).
     """
-    W = {k: v.to(dtype) for k, v in W.items()}
+    raw = W
+    W = _Converted(raw, dtype)                    # each tensor is widened when it is used (a large table never whole)
     ids_t = torch.as_tensor(ids, dtype=torch.long)
     positions = torch.arange(len(ids))
-    x = embedding(ids_t, W["model.embed_tokens.weight"])
+    x = embedding(ids_t, raw["model.embed_tokens.weight"]).to(dtype)
     order = list(range(cfg["num_hidden_layers"])) if schedule is None else schedule
     for l in order:
         x = decoder_layer(x, W, l, cfg, positions, window)
     x = rms_norm(x, W["model.norm.weight"], cfg["rms_norm_eps"])
-    if "lm_head.weight" in W:
-        head = W["lm_head.weight"]
+    if "lm_head.weight" in raw:
+        head = raw["lm_head.weight"]
     else:
         assert cfg.get("tie_word_embeddings", False), "no lm_head.weight and embeddings not tied"
-        head = W["model.embed_tokens.weight"]
-    return x @ head.T
+        head = raw["model.embed_tokens.weight"]
+    return lm_head(x, head)
+
+
+def lm_head(x: torch.Tensor, head: torch.Tensor, rows: int = 32768) -> torch.Tensor:
+    """``logits = x head^T`` (models/qwen3/src/model.rs:852-853), the table widened a slice of rows at a time."""
+    return torch.cat([x @ head[i:i + rows].to(x.dtype).T for i in range(0, head.shape[0], rows)], dim=1)
+
+
+class _Converted:
+    """``{name: tensor}`` whose tensors come out in ``dtype``."""
+
+    def __init__(self, raw: Dict[str, torch.Tensor], dtype: torch.dtype):
+        self.raw, self.dtype = raw, dtype
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        return self.raw[name].to(self.dtype)
+
+    def __contains__(self, name: str) -> bool:
+        return name in self.raw
 
 
 def greedy_generate(W, cfg, prompt: List[int], n: int, dtype=torch.float64) -> List[int]:

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 def run_tc(reqs, H, Hkv, D, bs, window, splits, seed):
     from dinfer_b200.kernels import attention_ops as A
     rng = random.Random(seed)
-    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, torch.bfloat16)
+    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, torch.bfloat16, window=window)
     seq = torch.tensor([h + n for h, n in reqs], dtype=torch.int32)
     scale = D ** -0.5
     # q as columns of a wider row, the way the engine passes the q part of the qkv rows
@@ -62,7 +62,7 @@ def test_decode_kernel(H, Hkv, D, bs, window, splits):
     from test_kernels_gpu import paged_case, plain_paged
     reqs = [(1000, 1), (63, 1), (0, 1), (129, 1), (40, 6), (2047, 1), (64, 1), (15, 1)]
     rng = random.Random(H * D + bs + splits)
-    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, torch.bfloat16)
+    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, torch.bfloat16, window=window)
     seq = torch.tensor([h + n for h, n in reqs], dtype=torch.int32)
     scale = D ** -0.5
     want = plain_paged(reqs, qs, ks, vs, scale, window).reshape(-1, H * D)
@@ -92,7 +92,7 @@ def test_far_key_and_window_edge():
     rng = random.Random(4)
     for hist, new, far, window in ((600, 1, 37, None), (300, 40, 5, None), (600, 1, 590, 11), (600, 1, 590, 10)):
         reqs = [(hist, new)]
-        q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, torch.bfloat16)
+        q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, torch.bfloat16, window=window)
         q[:] = 0
         q[:, :, 0] = 100.0
         cache[:, 0, :, :, 0] = 0

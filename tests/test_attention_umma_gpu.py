@@ -15,7 +15,7 @@ def run(reqs, H, Hkv, D, bs, window, seed):
     from dinfer_b200.kernels import attention_ops as A
     from dinfer_b200.kernels import gemm_ops as G
     rng = random.Random(seed)
-    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, torch.bfloat16)
+    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, torch.bfloat16, window=window)
     seq = torch.tensor([h + n for h, n in reqs], dtype=torch.int32)
     scale = D ** -0.5
     T = q.shape[0]
@@ -75,3 +75,44 @@ def test_far_key_wins():
     want = cache[blk, 1, :, far % bs].float().repeat_interleave(H // Hkv, 0)
     for t in (0, new // 2, new - 1):
         assert torch.allclose(out[t].float().reshape(H, D).cpu(), want, atol=2e-2)
+
+
+@pytest.mark.parametrize("window", [73, 70, 16, 130])
+@pytest.mark.parametrize("H,Hkv,D,bs", [(8, 2, 128, 16), (4, 2, 64, 8), (4, 1, 128, 32), (6, 3, 64, 4)])
+def test_window_edges_with_the_passed_pages_given_back(H, Hkv, D, bs, window):
+    """Every kernel that walks a block table, with the pages a window has passed given back (-1 in the table, NaN
+    wherever no request holds a page): the window's edge on a 64-key tile's edge (history 200, window 73: the
+    first key seen is 128), inside a page (window 70), nearer than a page ago (16), and inside a short portion
+    whose first rows still see keys the last rows do not."""
+    from dinfer_b200.kernels import attention_ops as A
+    from dinfer_b200.kernels import gemm_ops as G
+    reqs = [(200, 1), (200, 5), (300, 2), (129, 40), (0, 150), (1000, 1), (64, 1), (10, 1)]
+    rng = random.Random(window * 1000 + H * D + bs)
+    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, torch.bfloat16, window=window)
+    assert int((table[0] == -1).sum()) > (200 - window) // bs - 1          # pages really are gone
+    seq = torch.tensor([h + n for h, n in reqs], dtype=torch.int32)
+    scale = D ** -0.5
+    T = q.shape[0]
+    want = plain_paged(reqs, qs, ks, vs, scale, window).reshape(T, H * D)
+    dq, dc, dt, dcu, dseq = q.reshape(T, H * D).cuda(), cache.cuda(), table.cuda(), cu.cuda(), seq.cuda()
+    dec = [int(cu[i]) for i, (_, n) in enumerate(reqs) if n == 1]
+    pre = [r for i, (_, n) in enumerate(reqs) if n > 1 for r in range(int(cu[i]), int(cu[i + 1]))]
+    max_q = max(n for _, n in reqs)
+
+    def held(out, rows, what):
+        got = out.double().cpu()[rows]
+        assert torch.isfinite(got).all(), what
+        assert float((got - want[rows]).abs().max()) < 2e-2, what
+
+    for splits in (1, 4):
+        out = torch.full((T, H * D), 7.0, dtype=torch.bfloat16, device="cuda")
+        A.attention_decode(dq, out, dc, dt, dcu, dseq, H, Hkv, D, scale, window, splits)      # TMA, or cp.async at pages of 4
+        held(out, dec, f"decode kernel, {splits} splits")
+        out = torch.full((T, H * D), 7.0, dtype=torch.bfloat16, device="cuda")
+        A.attention_tc(dq, out, dc, dt, dcu, dseq, H, Hkv, D, scale, window, max_q, True, True, splits)
+        held(out, dec + pre, f"mma.sync kernel, {splits} splits")
+    if A.umma_supported(torch.bfloat16, D, H // Hkv, bs):
+        out = torch.full((T, H * D), 7.0, dtype=torch.bfloat16, device="cuda")
+        A.attention_umma(dq, out, dc, dt, dcu, dseq, H, Hkv, D, scale, window, max_q)
+        held(out, pre, "tcgen05 kernel")
+    G.check_status()

@@ -90,3 +90,35 @@ def test_which_steps_replay_a_graph():
     assert shape([4] * 15 + [3]) is None and shape([2] * 17) is None                 # 16 portions and padding; 17
     assert shape([40], budget=48) is None                                            # the padding would pass the budget
     assert shape([48], budget=48) == (48, 4, 0)
+
+
+def test_dummy_places_of_a_captured_graph_stay_inside_the_tables_and_the_position_table():
+    """A token budget above the longest request: the dummy portions a graph is captured on (and padded with) are
+    spread over places no longer than that, or the step runs kernel by kernel; a plan whose dummy request is
+    longer than its table covers, or whose positions leave the position table, does not pass the check."""
+    from dinfer_b200.engine import batch as B
+    from dinfer_b200.engine.runner import capture_places, graph_shape
+    buckets, places = [1, 2, 4], (4, 16)
+    # budget 512, longest request 96: a budget-filling step of 4 x 96 + 128 does not fit 4 or... it needs 16 places
+    assert graph_shape([96, 96, 96, 96, 96, 32], 1, 512, buckets, places, 128, 10**6, longest=96) == (512, 16, 1)
+    assert capture_places(512, 16, 1, 96) == [(-1, 96)] * 5 + [(-1, 32)] + [(-1, 0)] * 10 + [(-1, 1)]
+    assert capture_places(512, 4, 0, 96) is None
+    # 4 places of at most 96 cannot hold the 512 tokens of the capture: kernel by kernel
+    assert graph_shape([96, 96, 64], 0, 256, buckets, (4,), 128, 10**6, longest=60) is None
+    # a dummy portion longer than the longest request: kernel by kernel (130 tokens padded to 256 needs 126)
+    assert graph_shape([70, 60], 0, 512, buckets, places, 128, 10**6, longest=100) is None
+    assert graph_shape([70, 60], 0, 512, buckets, places, 128, 10**6, longest=128) == (256, 4, 0)
+    assert graph_shape([70, 60], 0, 512, buckets, places, 128, 10**6) == (256, 4, 0)
+
+    m = CacheManager([GroupSpec()], 4, 64, max_num_seqs=4)
+    builder = PlanBuilder(m, "cpu", max_tokens=256, max_reqs=8, max_blocks=6, max_positions=24)
+    old, B.VALIDATE_PLANS = B.VALIDATE_PLANS, True
+    try:
+        builder.build([], [], table_width=6, slots=capture_places(40, 4, 2, 24))          # 24 + 16 tokens: fine
+        with pytest.raises(AssertionError, match="longer than its table"):
+            builder.build([], [], table_width=6, slots=[(-1, 25), (-1, 1)])
+        wide = PlanBuilder(m, "cpu", max_tokens=256, max_reqs=8, max_blocks=16, max_positions=24)
+        with pytest.raises(AssertionError, match="position table"):
+            wide.build([], [], table_width=16, slots=[(-1, 25), (-1, 1)])
+    finally:
+        B.VALIDATE_PLANS = old

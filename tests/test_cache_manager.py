@@ -245,3 +245,16 @@ def test_tokens_that_are_not_known_yet():
     m.free("a")
     m.check_invariants()
     assert m.num_free_blocks() == 16
+
+
+def test_a_batch_is_asked_for_as_a_whole():
+    """``can_allocate_all`` answers for a step's whole batch and changes nothing."""
+    m = CacheManager([GroupSpec(), GroupSpec(window=8)], 4, [6, 6], max_num_seqs=2)
+    assert m.allocate("a", 9)                                   # 3 pages of each group
+    before = (m.num_free_blocks(0), m.num_free_blocks(1), m.state_slots.num_free)
+    assert m.can_allocate_all([("a", 12), ("b", 12)])            # 0 + 3 pages
+    assert not m.can_allocate_all([("a", 13), ("b", 12)])        # 1 + 3 pages of 3 free
+    assert not m.can_allocate_all([("a", 10), ("b", 1), ("c", 1)])   # one state slot free, two newcomers
+    assert (m.num_free_blocks(0), m.num_free_blocks(1), m.state_slots.num_free) == before
+    assert m.requests() == ["a"]
+    m.check_invariants()

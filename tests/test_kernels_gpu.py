@@ -145,13 +145,20 @@ def test_qk_post(dt, H, Hkv, D, rot, bs):
     assert torch.allclose(c, want_c, **tol(dt))
 
 
-def paged_case(rng, reqs, H, Hkv, D, bs, dt, extra_blocks=3):
-    """reqs = [(history, new)].  Returns the kernel's inputs and the plain answer [T, H, D]."""
+def paged_case(rng, reqs, H, Hkv, D, bs, dt, extra_blocks=3, window=None):
+    """reqs = [(history, new)].  Returns the kernel's inputs and the plain answer [T, H, D].
+
+    With ``window`` the pages that the window has passed before this step are gone, as the cache manager leaves
+    them: a page wholly below ``history - window + 1`` has the table entry -1 and its keys are nowhere; every page
+    no request holds (page 0 among them, where a kernel that mistook -1 for a page id might look) is NaN, so a
+    kernel that reads a key it must not see shows."""
     g = torch.Generator().manual_seed(rng.randrange(1 << 30))
     total_blocks = sum((h + n + bs - 1) // bs for h, n in reqs) + extra_blocks
-    perm = list(range(total_blocks))
+    perm = list(range(1 if window else 0, total_blocks))
     rng.shuffle(perm)
     cache = (torch.randn(total_blocks, 2, Hkv, bs, D, generator=g) * 50).to(dt)   # garbage where nothing is stored
+    if window:
+        cache[:] = float("nan")
     max_blocks = max((h + n + bs - 1) // bs for h, n in reqs) + 1
     table = torch.full((len(reqs), max_blocks), -1, dtype=torch.int32)
     qs, ks, vs, pos, cu = [], [], [], [], [0]
@@ -160,10 +167,12 @@ def paged_case(rng, reqs, H, Hkv, D, bs, dt, extra_blocks=3):
         k = torch.randn(L, Hkv, D, generator=g).to(dt)
         v = torch.randn(L, Hkv, D, generator=g).to(dt)
         q = torch.randn(new, H, D, generator=g).to(dt)
-        for i in range((L + bs - 1) // bs):
+        first = max(0, hist - window + 1) // bs if window else 0      # pages before it were given back
+        for i in range(first, (L + bs - 1) // bs):
             blk = perm.pop()
             table[b, i] = blk
             n = min(bs, L - i * bs)
+            cache[blk] = (torch.randn(2, Hkv, bs, D, generator=g) * 50).to(dt)    # what an earlier holder left
             cache[blk, 0, :, :n] = k[i * bs:i * bs + n].transpose(0, 1)
             cache[blk, 1, :, :n] = v[i * bs:i * bs + n].transpose(0, 1)
         qs.append(q); ks.append(k); vs.append(v)
@@ -188,7 +197,7 @@ def test_attention_generic(dt, H, Hkv, D, bs, window):
     from dinfer_b200.kernels import ops
     rng = random.Random(H * 1000 + D)
     reqs = [(40, 5), (70, 1), (0, 33), (130, 64), (0, 1), (7, 1)]        # portions with history beside decodes
-    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, dt)
+    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, reqs, H, Hkv, D, bs, dt, window=window)
     scale = D ** -0.5
     out = torch.empty(q.shape[0], H * D, dtype=dt, device="cuda")
     ops.attention_generic(dev(q).reshape(-1, H * D), out, dev(cache), dev(table), dev(cu), dev(pos), H, Hkv, D,
