@@ -83,7 +83,7 @@ def silu(x: torch.Tensor) -> torch.Tensor:
 def swiglu_mlp(x, w_gate, w_up, w_down):
     """``(silu(x Wg^T) * (x Wu^T)) Wd^T`` (crates/layers/src/nn.rs:373-381,
     crates/kernels/cuda/activation.cu:80-99)."""
-    return (silu(x @ w_gate.T) * (x @ w_up.T)) @ w_down.T
+    return gate(torch.cat([x @ w_gate.T, x @ w_up.T], dim=-1)) @ w_down.T
 
 
 def attention_block(x, W: Dict[str, torch.Tensor], prefix: str, cfg: dict, positions,
@@ -94,14 +94,13 @@ def attention_block(x, W: Dict[str, torch.Tensor], prefix: str, cfg: dict, posit
     T = x.shape[0]
     H, Hkv, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     eps = cfg["rms_norm_eps"]
-    q = (x @ W[prefix + "q_proj.weight"].T).reshape(T, H, D)
-    k = (x @ W[prefix + "k_proj.weight"].T).reshape(T, Hkv, D)
-    v = (x @ W[prefix + "v_proj.weight"].T).reshape(T, Hkv, D)
-    q = rms_norm(q, W[prefix + "q_norm.weight"], eps)
-    k = rms_norm(k, W[prefix + "k_norm.weight"], eps)
-    cos, sin = rope_cos_sin(positions, D, cfg["rope_theta"])
-    q = rope_neox(q, cos, sin)
-    k = rope_neox(k, cos, sin)
+    qkv = torch.cat([x @ W[prefix + "q_proj.weight"].T, x @ W[prefix + "k_proj.weight"].T,
+                     x @ W[prefix + "v_proj.weight"].T], dim=1)
+    rows, _ = qk_post(qkv, positions, H, Hkv, D, W[prefix + "q_norm.weight"], W[prefix + "k_norm.weight"], eps,
+                      cfg["rope_theta"])
+    q = rows[:, :H * D].reshape(T, H, D)
+    k = rows[:, H * D:(H + Hkv) * D].reshape(T, Hkv, D)
+    v = rows[:, (H + Hkv) * D:].reshape(T, Hkv, D)
     o = causal_gqa_attention(q, k, v, 1.0 / math.sqrt(D), window)
     return o.reshape(T, H * D) @ W[prefix + "o_proj.weight"].T
 
@@ -112,8 +111,8 @@ def decoder_layer(x, W, l: int, cfg: dict, positions, window: Optional[int] = No
     p = f"model.layers.{l}."
     eps = cfg["rms_norm_eps"]
     h = rms_norm(x, W[p + "input_layernorm.weight"], eps)
-    x = x + attention_block(h, W, p + "self_attn.", cfg, positions, window)
-    h = rms_norm(x, W[p + "post_attention_layernorm.weight"], eps)
+    x, h = add_and_norm(x, attention_block(h, W, p + "self_attn.", cfg, positions, window),
+                        W[p + "post_attention_layernorm.weight"], eps)
     x = x + swiglu_mlp(h, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"],
                        W[p + "mlp.down_proj.weight"])
     return x
@@ -196,15 +195,56 @@ def philox_uniform(seed: int, offset: int) -> float:
     return (c[0] >> 8) / 16777216.0
 
 
-def sample_token(logits: torch.Tensor, temperature: float, seed: int, offset: int,
-                 top_k: int = -1, top_p: float = 1.0, min_p: float = 0.0) -> int:
-    """temperature -> min_p -> top-k/top-p -> inverse CDF in vocabulary order
-    (crates/kernels/cuda/sampling.cu:196-283; models/qwen3/src/executor.rs:552-605).
-    Greedy when ``temperature <= 1e-5`` (crates/core/src/sample.rs:143-145)."""
-    x = logits.to(torch.float64)
-    if temperature <= 1e-5:
-        return int(torch.argmax(x))
-    x = x / temperature
+def add_and_norm(x: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float):
+    """The fused residual add and norm: ``x <- x + delta``, then ``rms_norm(x)``; returns both
+    (crates/kernels/cuda/norm.cu:60-95; scripts/verify/ops_parity_ref.py:70-76, where the sum is rounded to
+    the storage type before it is normed)."""
+    x = x + delta
+    return x, rms_norm(x, weight, eps)
+
+
+def qk_post(qkv: torch.Tensor, positions: torch.Tensor, H: int, Hkv: int, D: int, wq, wk, eps: float, theta: float):
+    """What happens to a step's q/k/v rows between the projection and attention: per-head RMSNorm of q and k,
+    THEN the rotation, v untouched; returns the rows ``[T, (H + 2 Hkv) D]`` and what goes into the cache per token,
+    ``[T, Hkv, 2 (k, v), D]`` (crates/kernels/cuda/qkv_post.cu:54-90; scripts/verify/ops_parity_ref.py:131-152)."""
+    T = qkv.shape[0]
+    q = qkv[:, :H * D].reshape(T, H, D)
+    k = qkv[:, H * D:(H + Hkv) * D].reshape(T, Hkv, D)
+    v = qkv[:, (H + Hkv) * D:].reshape(T, Hkv, D)
+    cos, sin = rope_cos_sin(positions, D, theta)
+    qn = rope_neox(rms_norm(q, wq, eps), cos, sin)
+    kn = rope_neox(rms_norm(k, wk, eps), cos, sin)
+    rows = torch.cat([qn.reshape(T, -1), kn.reshape(T, -1), v.reshape(T, -1)], dim=1)
+    return rows, torch.stack([kn, v], dim=2)
+
+
+def gate(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(first half) * second half`` of the fused gate/up product's rows: the gate comes first
+    (crates/kernels/cuda/activation.cu:80-99; scripts/verify/ops_parity_ref.py:84-89)."""
+    i = gate_up.shape[-1] // 2
+    return silu(gate_up[..., :i]) * gate_up[..., i:]
+
+
+def penalties(logits: torch.Tensor, prompt: List[int], output: List[int], repetition: float = 1.0,
+              frequency: float = 0.0, presence: float = 0.0) -> torch.Tensor:
+    """Every token of the prompt or the output, once: a positive logit is divided by the repetition penalty, any
+    other multiplied; tokens of the OUTPUT lose ``frequency * count + presence``
+    (crates/kernels/cuda/sampling.cu:322-349; scripts/verify/ops_parity_ref.py:285-299)."""
+    out = logits.clone()
+    for tok in set(prompt) | set(output):
+        x = float(out[tok])
+        if repetition != 1.0:
+            x = x / repetition if x > 0 else x * repetition
+        cnt = output.count(tok)
+        if cnt > 0:
+            x -= frequency * cnt + presence
+        out[tok] = x
+    return out
+
+
+def filter_logits(x: torch.Tensor, top_k: int = -1, top_p: float = 1.0, min_p: float = 0.0) -> torch.Tensor:
+    """min_p -> top-k -> top-p on the scaled logits: what is filtered out becomes -inf
+    (crates/kernels/cuda/sampling.cu:196-256,353-367; scripts/verify/ops_parity_ref.py:301-312,347-352)."""
     neg = torch.full_like(x, float("-inf"))
     if min_p > 0.0:
         probs = torch.softmax(x, dim=-1)
@@ -219,6 +259,18 @@ def sample_token(logits: torch.Tensor, temperature: float, seed: int, offset: in
         keep = torch.zeros_like(x, dtype=torch.bool)
         keep[si[before < top_p]] = True
         x = torch.where(keep, x, neg)
+    return x
+
+
+def sample_token(logits: torch.Tensor, temperature: float, seed: int, offset: int,
+                 top_k: int = -1, top_p: float = 1.0, min_p: float = 0.0) -> int:
+    """temperature -> min_p -> top-k/top-p -> inverse CDF in vocabulary order
+    (crates/kernels/cuda/sampling.cu:196-283; models/qwen3/src/executor.rs:552-605).
+    Greedy when ``temperature <= 1e-5`` (crates/core/src/sample.rs:143-145)."""
+    x = logits.to(torch.float64)
+    if temperature <= 1e-5:
+        return int(torch.argmax(x))
+    x = filter_logits(x / temperature, top_k, top_p, min_p)
     w = torch.exp(x - x.max())
     target = philox_uniform(seed, offset) * float(w.sum())
     cum = torch.cumsum(w, 0)

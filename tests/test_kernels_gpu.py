@@ -281,11 +281,9 @@ def test_penalties():
     rep, freq, pres = torch.tensor([1.5, 1.0]), torch.tensor([0.3, 0.0]), torch.tensor([0.2, 0.0])
     d = dev(logits.clone())
     S.apply_penalties(d, dev(ids), dev(offsets), dev(plen), dev(rep), dev(freq), dev(pres))
-    want = logits.clone()
-    for tok, cnt in ((3, 1), (40, 2), (7, 1)):
-        v = want[0, tok]
-        v = v / 1.5 if v > 0 else v * 1.5
-        want[0, tok] = v - 0.3 * cnt - 0.2
+    want = torch.stack([P.penalties(logits[0], [3, 40], [40, 7, 40, 3], 1.5, 0.3, 0.2),
+                        P.penalties(logits[1], [1, 2], [], 1.0, 0.0, 0.0)])
+    assert not torch.equal(want[0], logits[0]) and torch.equal(want[1], logits[1])
     assert torch.allclose(d.cpu(), want, atol=1e-6)
 
 

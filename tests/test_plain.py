@@ -31,6 +31,76 @@ def test_attention_matches_reference_formula():
     assert torch.allclose(o, t("attn_o"), atol=1e-5, rtol=1e-5)
 
 
+def bf(x):
+    return x.to(torch.bfloat16).float()
+
+
+def rounds_to(plain: torch.Tensor, want: torch.Tensor) -> bool:
+    """``want`` is a bfloat16 value of the reference; the plain result must round to it (a last place apart where
+    the unrounded values straddle a rounding boundary, in one entry in a hundred at most)."""
+    got = bf(plain.float())
+    exact = float((got == want).float().mean())
+    return exact >= 0.99 and torch.allclose(got, want, rtol=2.0 ** -7, atol=1e-6)
+
+
+def test_residual_add_and_norm_match_what_the_references_check_expects():
+    res, normed = P.add_and_norm(t("addnorm_res").double(), t("addnorm_x").double(), t("addnorm_w").double(), 1e-5)
+    assert rounds_to(res, t("addnorm_res_out"))
+    # the reference norms the ROUNDED sum (it keeps the residual in bfloat16); the plain sum is not rounded
+    assert torch.allclose(normed.float(), t("addnorm_out"), rtol=2.0 ** -6, atol=2e-3)
+    _, normed_r = P.add_and_norm(t("addnorm_res_out").double(), torch.zeros(1, dtype=torch.float64),
+                                 t("addnorm_w").double(), 1e-5)
+    assert rounds_to(normed_r, t("addnorm_out"))
+
+
+def test_gate_comes_first():
+    x = t("gate_x")
+    assert rounds_to(P.gate(x.double()), t("gate_out"))
+    i = x.shape[1] // 2
+    swapped = P.gate(torch.cat([x[:, i:], x[:, :i]], 1).double())
+    assert not torch.allclose(bf(swapped.float()), t("gate_out"), atol=1e-2)
+
+
+def test_head_norm_comes_before_the_rotation_and_the_cache_gets_rotated_keys():
+    H, HK, D = (int(v) for v in G["qkpost_dims"])
+    qkv, pos, theta = t("qkpost_qkv"), t("qkpost_pos"), float(G["qkpost_theta"])
+    rows, kv = P.qk_post(qkv.double(), pos, H, HK, D, t("qkpost_wq").double(), t("qkpost_wk").double(), 1e-5, theta)
+    assert rounds_to(rows, t("qkpost_rows"))
+    want_cache = t("qkpost_cache")                            # [slot, kv head, k|v, D], zero where nothing is written
+    cache = torch.zeros_like(want_cache)
+    for i, sl in enumerate(G["qkpost_slots"].tolist()):
+        if sl >= 0:
+            cache[sl] = bf(kv[i].float())
+    assert rounds_to(cache, want_cache)
+    assert float(want_cache.abs().sum(dim=(1, 2, 3)).gt(0).sum()) == 8          # the token without a slot wrote nothing
+    # the other order (rotation first) is not what the reference expects
+    T = qkv.shape[0]
+    cos, sin = P.rope_cos_sin(pos, D, theta)
+    q = qkv[:, :H * D].reshape(T, H, D).double()
+    wrong = P.rms_norm(P.rope_neox(q, cos, sin), t("qkpost_wq").double(), 1e-5).reshape(T, -1)
+    assert not torch.allclose(bf(wrong.float()), t("qkpost_rows")[:, :H * D], atol=5e-2)
+
+
+def test_penalties_match_the_reference_formula():
+    logits, ids = t("pen_logits"), G["pen_ids"].tolist()
+    offs, plen = G["pen_offsets"].tolist(), G["pen_prompt_len"].tolist()
+    for b in range(logits.shape[0]):
+        row = ids[offs[b]:offs[b + 1]]
+        got = P.penalties(logits[b], row[:plen[b]], row[plen[b]:], float(G["pen_rep"][b]), float(G["pen_freq"][b]),
+                          float(G["pen_pres"][b]))
+        assert torch.allclose(got, t("pen_out")[b], atol=1e-6)
+    assert not torch.equal(t("pen_out"), logits)
+
+
+def test_top_k_and_top_p_filters_match_the_reference_formula():
+    row = t("filter_row")
+    for (kk, pp), want in zip(G["filter_cases"].tolist(), t("filter_out")):
+        got = P.filter_logits(row.double(), top_k=int(kk) if kk else -1, top_p=float(pp))
+        assert torch.equal(torch.isinf(got), torch.isinf(want)), (kk, pp)
+        kept = ~torch.isinf(want)
+        assert torch.allclose(got[kept].float(), want[kept])
+
+
 def test_window_limits_the_keys():
     g = torch.Generator().manual_seed(0)
     q, k, v = (torch.randn(9, 2, 8, generator=g, dtype=torch.float64) for _ in range(3))
