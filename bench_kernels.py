@@ -9,9 +9,15 @@ graph's CUDA-event time divided by its launches.  Beside each time stands the ti
 
     python bench_kernels.py                     # all sections
     python bench_kernels.py --only gemm_decode --tokens 1 8 32
+    python bench_kernels.py --impl reference    # the reference's own kernels beside this package's (see below)
 
 Sections: gemm_decode (tcgen05 swapped-operand product per split count), gemm_prompt (tcgen05 product
 and the library's), attention_decode (per split count), attention_prompt, sampling.
+
+``--impl reference``: the same shapes and the same timing method for the reference's own CUDA kernels (norms, gate,
+q/k post-processing, prompt and decode attention, small-M products, sampling), compiled unmodified for sm_100a by
+``python baseline/build_ref_kernels.py /path/to/reference`` and called through their C ABI; one line per op with both
+times.  Prints an ``unavailable`` line when that library has not been built.
 """
 from __future__ import annotations
 
@@ -205,7 +211,10 @@ def sampling(vocab, rows_list):
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--only", choices=["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "sampling"])
+    ap.add_argument("--only", choices=["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "sampling",
+                                       "small_ops"])
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours",
+                    help="reference: time the reference's own kernels beside this package's")
     ap.add_argument("--tokens", type=int, nargs="*", default=[1, 8, 32], help="rows of the decode products")
     ap.add_argument("--batches", type=int, nargs="*", default=[1, 8, 64], help="requests of the decode attention")
     ap.add_argument("--contexts", type=int, nargs="*", default=[1024, 4096, 16384])
@@ -217,6 +226,10 @@ def main() -> int:
     hbm, tflops, source = peaks()
     print(f"# peaks ({source}): {hbm:.1f} GB/s, {tflops:.1f} TFLOP/s bf16; {torch.cuda.get_device_name(0)}")
     torch.manual_seed(0)
+    if a.impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import ref_kernels
+        return ref_kernels.run(sys.modules[__name__], a, hbm, tflops)
     todo = [a.only] if a.only else ["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "sampling"]
     if "gemm_decode" in todo:
         gemm_decode(SHAPE, a.tokens, hbm)
