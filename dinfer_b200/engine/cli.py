@@ -6,6 +6,7 @@ sub-commands, and for the engine options the reference's own flag names and defa
 place of ``serve``:
 
     dinfer generate --model DIR --prompt-ids 1,2,3 --prompt-ids 4,5 --max-tokens 16 --temperature 0
+    dinfer generate --random-weights config.json --weights-seed 0 --prompt-ids 1,2,3     (no files: weights made on the device)
     dinfer random-model --config config.json --out DIR --seed 0
     dinfer device-info
     dinfer replay --model DIR --dtype bfloat16 --out DIR --max-tokens N < steps.jsonl     (= bin/trace_run)
@@ -19,7 +20,17 @@ from typing import List
 
 
 def _engine_flags(p: argparse.ArgumentParser) -> None:
-    p.add_argument("--model", required=True, help="model folder (config.json + safetensors)")
+    src = p.add_mutually_exclusive_group(required=True)
+    src.add_argument("--model", help="model folder (config.json + safetensors)")
+    src.add_argument("--random-weights", metavar="CONFIG_JSON",
+                     help="no model folder: the architecture and every size from this config.json, the weights drawn "
+                          "on the device (see --weights-seed, --weights-std, --weights-norm-jitter)")
+    p.add_argument("--weights-seed", type=int, default=0, help="with --random-weights: the seed of the weights")
+    p.add_argument("--weights-std", type=float, default=0.02, help="with --random-weights: matrices are N(0, std)")
+    p.add_argument("--weights-norm-jitter", type=float, default=0.0,
+                   help="with --random-weights: norm weights are 1 + U(-jitter, jitter)")
+    p.add_argument("--allow-unused-tensors", action="store_true",
+                   help="tensors in the model's files that the model does not use are reported, not refused")
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--max-model-len", type=int, default=4096)
     p.add_argument("--max-num-seqs", type=int, default=16)
@@ -59,7 +70,16 @@ def cmd_generate(a) -> int:
     if not prompts:
         print("no prompt given (--prompt-ids or --prompt-file)", file=sys.stderr)
         return 2
-    llm = LLM(a.model, dtype=a.dtype, max_model_len=a.max_model_len, max_num_seqs=a.max_num_seqs,
+    source = {}
+    if a.random_weights:
+        import torch
+        from ..weights.random_init import RandomSource
+        with open(a.random_weights) as f:
+            cfg = json.load(f)
+        dt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[a.dtype]
+        source = dict(config=cfg, weights=RandomSource(cfg, a.weights_seed, a.weights_std, a.weights_norm_jitter, dt,
+                                                       device=f"cuda:{a.device}"))
+    llm = LLM(a.model, **source, allow_unused_tensors=a.allow_unused_tensors, dtype=a.dtype, max_model_len=a.max_model_len, max_num_seqs=a.max_num_seqs,
               max_num_batched_tokens=a.max_num_batched_tokens, num_blocks=a.num_blocks,
               block_size=a.block_size, gpu_memory_utilization=a.gpu_memory_utilization,
               decode_exempt_from_budget=not a.no_decode_exempt,

@@ -117,7 +117,13 @@ class ModelRunner:
         self.model = DecoderModel(self.spec, env)
         # where the start-up time goes, in seconds (the reference logs such phases: crates/layers/src/load.rs:35-136)
         t0 = time.perf_counter()
-        tensors = load_tensors(source, self.model.declarations(), self.act_dtype, self.device)
+        self.unused_tensors: List[str] = []
+        tensors = load_tensors(source, self.model.declarations(), self.act_dtype, self.device,
+                               allow_unexpected=engine.allow_unused_tensors, unused=self.unused_tensors)
+        if self.unused_tensors:
+            import sys
+            print(f"[dinfer_b200] {source.where}: {len(self.unused_tensors)} tensors the model does not use: "
+                  + ", ".join(self.unused_tensors), file=sys.stderr, flush=True)
         self.model.bind(tensors)
         del tensors
         torch.cuda.synchronize(self.device)

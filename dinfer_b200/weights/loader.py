@@ -106,7 +106,10 @@ _FLOATS = (torch.float32, torch.float64, torch.float16, torch.bfloat16)
 _INTS = (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8)
 
 
-def verify(source: WeightSource, decls: Sequence[TensorDecl]) -> None:
+def verify(source: WeightSource, decls: Sequence[TensorDecl], allow_unexpected: bool = False) -> List[str]:
+    """Hold what the source has against what the model declares; ONE error for everything that does not fit.
+    Returns the tensors the model does not use: an error like the rest by default; with ``allow_unexpected`` (a
+    checkpoint that carries buffers of its training code, say) they are only reported."""
     have = set(source.names())
     wanted = {}
     for d in decls:
@@ -126,8 +129,9 @@ def verify(source: WeightSource, decls: Sequence[TensorDecl]) -> None:
         if d.kind == "int" and dt not in _INTS:
             wrong_dtype.append((name, str(dt).replace("torch.", ""), "an integer type"))
     unexpected = sorted(have - set(wanted))
-    if missing or wrong_shape or wrong_dtype or unexpected:
+    if missing or wrong_shape or wrong_dtype or (unexpected and not allow_unexpected):
         raise WeightError(source.where, missing, unexpected, wrong_shape, wrong_dtype)
+    return unexpected
 
 
 def placed_dtype(stored: torch.dtype, kind: str, act_dtype: torch.dtype) -> torch.dtype:
@@ -141,9 +145,12 @@ def placed_dtype(stored: torch.dtype, kind: str, act_dtype: torch.dtype) -> torc
 
 
 def load_tensors(source: WeightSource, decls: Sequence[TensorDecl], act_dtype: torch.dtype,
-                 device) -> Dict[str, torch.Tensor]:
-    """Verify, then bring every declared tensor the source has to ``device`` in its placed dtype."""
-    verify(source, decls)
+                 device, allow_unexpected: bool = False, unused: List[str] | None = None) -> Dict[str, torch.Tensor]:
+    """Verify, then bring every declared tensor the source has to ``device`` in its placed dtype.  ``unused``:
+    a list that receives the names of tensors the model does not use (only reachable with ``allow_unexpected``)."""
+    extra = verify(source, decls, allow_unexpected)
+    if unused is not None:
+        unused.extend(extra)
     have = set(source.names())
     out: Dict[str, torch.Tensor] = {}
     for d in decls:

@@ -46,7 +46,8 @@ def test_random_model_writes_a_loadable_folder(tmp_path):
 
 
 def test_usage_errors():
-    assert run("generate").returncode != 0                      # --model is required
+    assert run("generate").returncode != 0                      # --model or --random-weights is required
+    assert run("generate", "--model", "x", "--random-weights", "y").returncode != 0     # not both
     assert run("no-such-command").returncode != 0
     r = run("generate", "--help")
     assert r.returncode == 0 and "--max-num-batched-tokens" in r.stdout and "--enable-prefix-caching" in r.stdout
@@ -66,3 +67,21 @@ def test_generate_gives_the_plain_tokens(tmp_path):
     for line, p in zip(lines, prompts):
         assert line["output_ids"] == P.greedy_generate(W, H.TINY_B, p, 7)
         assert line["finish_reason"] == "length"
+
+
+@pytest.mark.gpu
+def test_generate_with_random_weights_needs_no_files(tmp_path):
+    """``--random-weights config.json``: the weights are drawn on the device from the seed; the same seed gives the
+    same tokens, another seed other tokens."""
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(H.TINY_B))
+
+    def tokens(seed):
+        r = run("generate", "--random-weights", str(cfg_path), "--weights-seed", str(seed), "--weights-std", "0.03",
+                "--weights-norm-jitter", "0.2", "--dtype", "float32", "--max-model-len", "64", "--max-num-seqs", "2",
+                "--num-blocks", "16", "--prompt-ids", "5,17,3,9", "--max-tokens", "8", "--temperature", "0", "--ignore-eos")
+        assert r.returncode == 0, r.stderr
+        return [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")][0]["output_ids"]
+
+    a, b, c = tokens(1), tokens(1), tokens(2)
+    assert len(a) == 8 and a == b and a != c

@@ -124,3 +124,34 @@ def test_random_weights_follow_seed_and_rules(tmp_path):
     assert float(n.min()) >= 0.8 and float(n.max()) <= 1.2 and float(n.std()) > 0.05
     assert os.path.isfile(tmp_path / "a" / "config.json")
     assert set(a) == {d.name for d in model_declarations(H.TINY_B)}
+
+
+def test_unused_tensors_are_an_error_unless_allowed(tmp_path):
+    """A file with a tensor the model does not use: refused by default (listed in the one error); with
+    ``allow_unexpected`` the model loads and the name is reported.  Anything else that does not fit stays an error."""
+    import torch
+    from dinfer_b200.weights.loader import SafetensorsSource, WeightError, load_tensors
+    from dinfer_b200.weights.random_init import model_declarations, random_tensor
+    from dinfer_b200.weights.safetensors_io import write_safetensors
+    import helpers as H
+    decls = model_declarations(H.TINY_A)
+    d = tmp_path / "m"
+    d.mkdir()
+    tensors = [(x.name, random_tensor(x, 0, 0.02, 0.0, torch.float32)) for x in decls]
+    tensors.append(("model.layers.0.self_attn.rotary_emb.inv_freq", torch.ones(8)))
+    write_safetensors(str(d / "model.safetensors"), tensors)
+    src = SafetensorsSource(str(d))
+    try:
+        with pytest.raises(WeightError) as e:
+            load_tensors(src, decls, torch.float32, "cpu")
+        assert e.value.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"] and not e.value.missing
+        unused = []
+        got = load_tensors(src, decls, torch.float32, "cpu", allow_unexpected=True, unused=unused)
+        assert unused == ["model.layers.0.self_attn.rotary_emb.inv_freq"]
+        assert set(got) == {x.name for x in decls}
+        with pytest.raises(WeightError) as e:                       # a missing tensor is never tolerated
+            load_tensors(src, decls + [type(decls[0])("model.extra.weight", (3,))], torch.float32, "cpu",
+                         allow_unexpected=True)
+        assert e.value.missing == ["model.extra.weight"]
+    finally:
+        src.close()
