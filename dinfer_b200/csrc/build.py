@@ -37,7 +37,10 @@ LIBRARIES: Dict[str, tuple] = {
     "attention_decode": ("attention_decode.cu", []),
     "gemm_tc": ("gemm_tc.cu", []),
     "attention_umma": ("attention_umma.cu", []),
+    # host-side bookkeeping (page pools, cache manager, decode plans): plain C++, no CUDA
+    "host_core": ("host_core.cpp", []),
 }
+CXX_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
 
 
 class BuildError(RuntimeError):
@@ -70,7 +73,8 @@ def _stamp(source: str, extra: Iterable[str]) -> str:
         with open(os.path.join(CSRC, fn), "rb") as f:
             h.update(fn.encode())
             h.update(f.read())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + list(extra)).encode())
+    flags = CXX_FLAGS if source.endswith(".cpp") else ARCH_FLAGS + NVCC_FLAGS
+    h.update(" ".join(flags + list(extra)).encode())
     return h.hexdigest()[:12]
 
 
@@ -107,9 +111,14 @@ def _compile(name: str, verbose: bool) -> str:
     out = library_path(name)
     if os.path.isfile(out):
         return out
-    nvcc = find_nvcc()
     tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
-    cmd = [nvcc] + ARCH_FLAGS + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, os.path.join(CSRC, source)] + list(extra)
+    if source.endswith(".cpp"):
+        cxx = shutil.which(os.environ.get("CXX", "g++")) or shutil.which("c++")
+        if not cxx:
+            raise BuildError("no C++ compiler found (g++ or $CXX); the host core of dinfer_b200 cannot be built")
+        cmd = [cxx] + CXX_FLAGS + ["-I", CSRC, "-o", tmp, os.path.join(CSRC, source)] + list(extra)
+    else:
+        cmd = [find_nvcc()] + ARCH_FLAGS + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, os.path.join(CSRC, source)] + list(extra)
     t0 = time.time()
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
@@ -119,7 +128,7 @@ def _compile(name: str, verbose: bool) -> str:
             os.remove(tmp)
         except OSError:
             pass
-        raise BuildError(f"nvcc failed on {source}:\n{' '.join(cmd)}\n{proc.stdout}")
+        raise BuildError(f"the compiler failed on {source}:\n{' '.join(cmd)}\n{proc.stdout}")
     os.replace(tmp, out)
     # drop older builds of the same library
     prefix = f"libdinfer_{name}_"

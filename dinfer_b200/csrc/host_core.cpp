@@ -1,0 +1,467 @@
+// The engine's host-side bookkeeping in C++: the page pools, the cache manager, the scheduler's per-step
+// decisions and the packed plan of a decode step.  No CUDA here: plain C++17 behind a C ABI, loaded with ctypes
+// like the kernel libraries.  The Python classes of the same names (cache/block_pool.py, cache/manager.py,
+// engine/scheduler.py, engine/batch.py) define the behaviour; the CPU tests run against both.
+//
+// In the reference the same pieces are Rust: crates/core/src/kv/block_pool.rs (reference counts, a free list
+// in order of use, the hash index), kv/manager.rs (tables per request and group, all-or-nothing allocation),
+// sched/mod.rs (the scheduler) and runner.rs:745-876 (the flat batch plan), gated at under 200 us for scheduling
+// and updating 1024 decoding requests (crates/core/benches/scheduler.rs:1-5).
+//
+// Requests are named by 64-bit handles that the caller chooses (the Python side maps its request ids to them).
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#define DH_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+thread_local std::string g_error;
+int fail(const char* fmt, long long a = 0, long long b = 0, long long c = 0) {
+  char buf[256];
+  std::snprintf(buf, sizeof buf, fmt, a, b, c);
+  g_error = buf;
+  return -1;
+}
+
+// ---- content hashes of the prefix cache: 128 bits chained over a page's tokens and the page before it.
+// Two multiply-xorshift lanes with different constants; the lanes see each other's state every token.
+struct Hash128 {
+  uint64_t a = 0, b = 0;
+  bool operator==(const Hash128& o) const { return a == o.a && b == o.b; }
+};
+struct HashOf {
+  size_t operator()(const Hash128& h) const { return (size_t)(h.a ^ (h.b * 0x9E3779B97F4A7C15ull)); }
+};
+inline uint64_t stir(uint64_t z, uint64_t m1, uint64_t m2) {
+  z ^= z >> 31; z *= m1; z ^= z >> 29; z *= m2; z ^= z >> 32;
+  return z;
+}
+Hash128 chain_hash(const Hash128& parent, const int32_t* tokens, int n) {
+  Hash128 h{parent.a ^ 0x6A09E667F3BCC908ull, parent.b ^ 0xBB67AE8584CAA73Bull};
+  for (int i = 0; i < n; ++i) {
+    const uint64_t t = (uint64_t)(uint32_t)tokens[i] + ((uint64_t)(i + 1) << 40);
+    h.a = stir(h.a + t + (h.b << 7), 0xD6E8FEB86659FD93ull, 0xA0761D6478BD642Full);
+    h.b = stir(h.b ^ (t * 0x8EBC6AF09C88C6E3ull) ^ (h.a >> 9), 0xE7037ED1A0B428DBull, 0x589965CC75374CC3ull);
+  }
+  h.a = stir(h.a ^ (uint64_t)n, 0xD6E8FEB86659FD93ull, 0xA0761D6478BD642Full);
+  return h;
+}
+
+// ---- a pool of pages
+struct Pool {
+  int num_blocks = 0;
+  std::vector<int> refs, prev, next;
+  std::vector<char> on_free, hashed;
+  std::vector<Hash128> hash;
+  std::unordered_map<Hash128, int, HashOf> cached;
+  int head = -1, tail = -1, num_free = 0;
+  long long evictions = 0;
+
+  explicit Pool(int n) : num_blocks(n), refs(n, 0), prev(n, -1), next(n, -1), on_free(n, 0), hashed(n, 0), hash(n) {
+    for (int b = 0; b < n; ++b) push_tail(b);
+  }
+  void unlink(int b) {
+    if (prev[b] >= 0) next[prev[b]] = next[b]; else head = next[b];
+    if (next[b] >= 0) prev[next[b]] = prev[b]; else tail = prev[b];
+    prev[b] = next[b] = -1;
+    on_free[b] = 0;
+    --num_free;
+  }
+  void push_tail(int b) {
+    prev[b] = tail; next[b] = -1;
+    if (tail >= 0) next[tail] = b; else head = b;
+    tail = b;
+    on_free[b] = 1;
+    ++num_free;
+  }
+  void push_head(int b) {
+    next[b] = head; prev[b] = -1;
+    if (head >= 0) prev[head] = b; else tail = b;
+    head = b;
+    on_free[b] = 1;
+    ++num_free;
+  }
+  // the head of the free list; a page that carried a hash loses it (its old contents can no longer be found)
+  int take() {
+    const int b = head;
+    unlink(b);
+    if (hashed[b]) { cached.erase(hash[b]); hashed[b] = 0; ++evictions; }
+    refs[b] = 1;
+    return b;
+  }
+  // one holder lets go; a page without holders joins the free list: at its tail when it carries a hash (found
+  // again for as long as possible), at its head otherwise (used again at once)
+  int release(int b) {
+    if (b < 0 || b >= num_blocks) return fail("block %lld is not of this pool", b);
+    if (refs[b] <= 0) return fail("block %lld freed while not held", b);
+    if (--refs[b] == 0) { if (hashed[b]) push_tail(b); else push_head(b); }
+    return 0;
+  }
+  void touch(int b) {                     // one more holder of a page found through its hash (it may have been free)
+    if (refs[b] == 0) unlink(b);
+    ++refs[b];
+  }
+  bool set_hash(int b, const Hash128& h) {
+    if (hashed[b] || cached.count(h)) return false;
+    hashed[b] = 1; hash[b] = h; cached.emplace(h, b);
+    return true;
+  }
+  int lookup(const Hash128& h) const {
+    auto it = cached.find(h);
+    return it == cached.end() ? -1 : it->second;
+  }
+  int check() const {
+    int n = 0;
+    for (int b = head, p = -1; b >= 0; p = b, b = next[b], ++n) {
+      if (prev[b] != p || !on_free[b] || refs[b] != 0) return fail("page %lld: the free list is broken", b);
+      if (n > num_blocks) return fail("the free list has a loop");
+    }
+    if (n != num_free) return fail("the free list holds %lld pages, the count says %lld", n, num_free);
+    for (int b = 0; b < num_blocks; ++b) {
+      if ((refs[b] == 0) != (bool)on_free[b]) return fail("page %lld: %lld holders but its free-list mark disagrees", b, refs[b]);
+      if (hashed[b] && lookup(hash[b]) != b) return fail("page %lld has a hash the cache does not map to it", b);
+    }
+    for (auto& kv : cached)
+      if (!hashed[kv.second] || !(hash[kv.second] == kv.first)) return fail("the cache maps a hash to page %lld, which does not carry it", kv.second);
+    return 0;
+  }
+};
+
+struct Held {
+  std::vector<std::vector<int32_t>> tables;      // per group: page id per block index, -1 = given back
+  int num_tokens = 0, num_computed = 0, capacity = 0;
+  std::vector<int32_t> tokens;                   // prefix cache: ids of the computed tokens that are known
+  std::vector<Hash128> hashes;                   // prefix cache: chained hash per full page so far
+  int slot = -1;
+  bool fresh = false;
+};
+
+struct Manager {
+  std::vector<int> windows;                      // per group: 0 = every key is kept
+  int block_size = 1;
+  std::vector<Pool> pools;
+  bool prefix = false;
+  long long prefix_queries = 0, prefix_hits = 0;
+  std::vector<int> free_slots;
+  int max_slots = 0;
+  std::unordered_map<int64_t, Held> reqs;
+  std::vector<int64_t> order;                    // requests in the order they came (what requests() lists)
+
+  Held* find(int64_t r) {
+    auto it = reqs.find(r);
+    return it == reqs.end() ? nullptr : &it->second;
+  }
+  int first_needed_block(int g, int num_computed) const {
+    if (!windows[g]) return 0;
+    return std::max(0, num_computed - windows[g] + 1) / block_size;
+  }
+  int need(const Held* h, int g, int total) const {
+    const int want = (total + block_size - 1) / block_size;
+    const int have = h ? (int)h->tables[g].size() : 0;
+    return std::max(0, want - have);
+  }
+  bool can_allocate(int64_t r, int total) {
+    const Held* h = find(r);
+    if (!h && free_slots.empty()) return false;
+    for (size_t g = 0; g < pools.size(); ++g)
+      if (need(h, (int)g, total) > pools[g].num_free) return false;
+    return true;
+  }
+  bool allocate(int64_t r, int total) {
+    Held* h = find(r);
+    if (h && total <= h->capacity) {             // the usual decode step: room on the last page
+      if (total > h->num_tokens) h->num_tokens = total;
+      return true;
+    }
+    if (!can_allocate(r, total)) return false;
+    if (!h) {
+      Held fresh_one;
+      fresh_one.tables.resize(pools.size());
+      fresh_one.slot = free_slots.back();
+      free_slots.pop_back();
+      fresh_one.fresh = true;
+      h = &reqs.emplace(r, std::move(fresh_one)).first->second;
+      order.push_back(r);
+    }
+    int cap = 1 << 30;
+    for (size_t g = 0; g < pools.size(); ++g) {
+      for (int n = need(h, (int)g, total); n > 0; --n) h->tables[g].push_back(pools[g].take());
+      cap = std::min(cap, (int)h->tables[g].size());
+    }
+    h->capacity = cap * block_size;
+    h->num_tokens = std::max(h->num_tokens, total);
+    return true;
+  }
+  void hash_full_pages(Held& h) {
+    const int ready = std::min((int)h.tokens.size(), h.num_computed);
+    while (((int)h.hashes.size() + 1) * block_size <= ready) {
+      const int i = (int)h.hashes.size();
+      const Hash128 parent = i ? h.hashes.back() : Hash128{};
+      const Hash128 hh = chain_hash(parent, h.tokens.data() + (size_t)i * block_size, block_size);
+      h.hashes.push_back(hh);
+      for (size_t g = 0; g < pools.size(); ++g) pools[g].set_hash(h.tables[g][i], hh);
+    }
+  }
+  int release(int64_t r) {
+    auto it = reqs.find(r);
+    if (it == reqs.end()) return fail("request %lld holds nothing", r);
+    Held& h = it->second;
+    for (size_t g = 0; g < pools.size(); ++g)
+      for (auto p = h.tables[g].rbegin(); p != h.tables[g].rend(); ++p)
+        if (*p >= 0 && pools[g].release(*p)) return -1;
+    free_slots.push_back(h.slot);
+    reqs.erase(it);
+    order.erase(std::find(order.begin(), order.end(), r));
+    return 0;
+  }
+};
+
+}  // namespace
+
+DH_API const char* dh_last_error() { return g_error.c_str(); }
+
+// ---- cache manager
+DH_API void* dh_manager_new(int n_groups, const int* windows, int block_size, const int* num_blocks, int max_num_seqs,
+                            int prefix_caching) {
+  if (n_groups <= 0 || block_size <= 0 || max_num_seqs < 0) { fail("bad sizes"); return nullptr; }
+  auto* m = new Manager();
+  m->windows.assign(windows, windows + n_groups);
+  m->block_size = block_size;
+  for (int g = 0; g < n_groups; ++g) {
+    if (num_blocks[g] <= 0) { delete m; fail("a pool needs at least one block"); return nullptr; }
+    m->pools.emplace_back(num_blocks[g]);
+  }
+  m->prefix = prefix_caching != 0;
+  m->max_slots = max_num_seqs;
+  for (int s = max_num_seqs - 1; s >= 0; --s) m->free_slots.push_back(s);
+  return m;
+}
+DH_API void dh_manager_delete(void* m) { delete static_cast<Manager*>(m); }
+
+DH_API int dh_contains(void* m, int64_t r) { return static_cast<Manager*>(m)->find(r) != nullptr; }
+DH_API int dh_num_requests(void* m) { return (int)static_cast<Manager*>(m)->order.size(); }
+DH_API int dh_requests(void* m, int64_t* out, int cap) {
+  auto& o = static_cast<Manager*>(m)->order;
+  const int n = std::min(cap, (int)o.size());
+  std::copy(o.begin(), o.begin() + n, out);
+  return (int)o.size();
+}
+DH_API int dh_num_tokens(void* m, int64_t r) { Held* h = static_cast<Manager*>(m)->find(r); return h ? h->num_tokens : fail("request %lld holds nothing", r); }
+DH_API int dh_num_computed(void* m, int64_t r) { Held* h = static_cast<Manager*>(m)->find(r); return h ? h->num_computed : fail("request %lld holds nothing", r); }
+DH_API int dh_table_len(void* m, int64_t r, int g) { Held* h = static_cast<Manager*>(m)->find(r); return h ? (int)h->tables[g].size() : fail("request %lld holds nothing", r); }
+DH_API int dh_table(void* m, int64_t r, int g, int32_t* out, int cap) {
+  Held* h = static_cast<Manager*>(m)->find(r);
+  if (!h) return fail("request %lld holds nothing", r);
+  const auto& t = h->tables[g];
+  const int n = std::min(cap, (int)t.size());
+  std::copy(t.begin(), t.begin() + n, out);
+  return (int)t.size();
+}
+DH_API int dh_pool_free(void* m, int g) { return static_cast<Manager*>(m)->pools[g].num_free; }
+DH_API int dh_pool_blocks(void* m, int g) { return static_cast<Manager*>(m)->pools[g].num_blocks; }
+DH_API long long dh_pool_evictions(void* m, int g) { return static_cast<Manager*>(m)->pools[g].evictions; }
+DH_API int dh_pool_refcount(void* m, int g, int b) { return static_cast<Manager*>(m)->pools[g].refs[b]; }
+DH_API int dh_pool_check(void* m, int g) { return static_cast<Manager*>(m)->pools[g].check(); }
+DH_API long long dh_prefix_queries(void* m) { return static_cast<Manager*>(m)->prefix_queries; }
+DH_API long long dh_prefix_hits(void* m) { return static_cast<Manager*>(m)->prefix_hits; }
+DH_API int dh_slots_free(void* m) { return (int)static_cast<Manager*>(m)->free_slots.size(); }
+DH_API int dh_slot(void* m, int64_t r) { Held* h = static_cast<Manager*>(m)->find(r); return h ? h->slot : fail("request %lld holds no slot", r); }
+DH_API int dh_take_fresh(void* m, int64_t r) {
+  Held* h = static_cast<Manager*>(m)->find(r);
+  if (!h) return 0;
+  const bool f = h->fresh;
+  h->fresh = false;
+  return f;
+}
+
+DH_API int dh_can_allocate(void* m, int64_t r, int total) { return static_cast<Manager*>(m)->can_allocate(r, total); }
+// every (request, total) of a step's batch together; nothing changes
+DH_API int dh_can_allocate_all(void* mp, const int64_t* rs, const int* totals, int n) {
+  auto* m = static_cast<Manager*>(mp);
+  std::vector<int> need(m->pools.size(), 0);
+  int fresh = 0;
+  for (int i = 0; i < n; ++i) {
+    const Held* h = m->find(rs[i]);
+    fresh += h == nullptr;
+    if (h && totals[i] <= h->capacity) continue;
+    for (size_t g = 0; g < m->pools.size(); ++g) need[g] += m->need(h, (int)g, totals[i]);
+  }
+  if (fresh > (int)m->free_slots.size()) return 0;
+  for (size_t g = 0; g < m->pools.size(); ++g)
+    if (need[g] > m->pools[g].num_free) return 0;
+  return 1;
+}
+DH_API int dh_allocate(void* m, int64_t r, int total) { return static_cast<Manager*>(m)->allocate(r, total); }
+
+// A request enters with these tokens: take the pages of their longest cached beginning (whole pages, every group,
+// never the last token); returns the tokens they cover (0 without the prefix cache, for a request that holds pages
+// already, or when no state slot is free).
+DH_API int dh_begin(void* mp, int64_t r, const int32_t* tokens, int n) {
+  auto* m = static_cast<Manager*>(mp);
+  if (!m->prefix || m->find(r)) return 0;
+  const int bs = m->block_size;
+  const int limit = (n - 1) / bs;
+  m->prefix_queries += n;
+  std::vector<Hash128> chain;
+  std::vector<std::vector<int32_t>> found(m->pools.size());
+  Hash128 parent{};
+  for (int i = 0; i < limit; ++i) {
+    parent = chain_hash(parent, tokens + (size_t)i * bs, bs);
+    bool all = true;
+    std::vector<int> pages(m->pools.size());
+    for (size_t g = 0; g < m->pools.size(); ++g) { pages[g] = m->pools[g].lookup(parent); all = all && pages[g] >= 0; }
+    if (!all) break;
+    chain.push_back(parent);
+    for (size_t g = 0; g < m->pools.size(); ++g) found[g].push_back(pages[g]);
+  }
+  const int k = (int)chain.size();
+  if (k == 0 || m->free_slots.empty()) return 0;
+  Held h;
+  h.slot = m->free_slots.back();
+  m->free_slots.pop_back();
+  h.fresh = true;
+  for (size_t g = 0; g < m->pools.size(); ++g)
+    for (int b : found[g]) m->pools[g].touch(b);
+  h.tables = std::move(found);
+  h.num_tokens = h.num_computed = h.capacity = k * bs;
+  h.tokens.assign(tokens, tokens + (size_t)k * bs);
+  h.hashes = std::move(chain);
+  m->reqs.emplace(r, std::move(h));
+  m->order.push_back(r);
+  m->prefix_hits += (long long)k * bs;
+  return k * bs;
+}
+
+// The cache now holds the keys of the first `num_computed` tokens: pages every window has passed go back.  With the
+// prefix cache, `new_tokens` (n_new of them; null = not told) are the ids of the tokens computed since the last call;
+// ids not known yet (negative) may stand at their end.
+DH_API int dh_advance(void* mp, int64_t r, int num_computed, const int32_t* new_tokens, int n_new) {
+  auto* m = static_cast<Manager*>(mp);
+  Held* h = m->find(r);
+  if (!h) return fail("request %lld holds nothing", r);
+  if (num_computed > h->num_tokens) return fail("request %lld: %lld tokens computed but pages cover %lld", r, num_computed, h->num_tokens);
+  if (m->prefix && new_tokens) {
+    int known = n_new;
+    while (known > 0 && new_tokens[known - 1] < 0) --known;
+    for (int i = 0; i < known; ++i)
+      if (new_tokens[i] < 0) return fail("request %lld: an unknown token before a known one", r);
+    const int behind = (int)h->tokens.size() + n_new - num_computed;
+    if (behind > 0 || (behind < 0 && known > 0))
+      return fail("request %lld: %lld known + new tokens do not make %lld", r, (long long)h->tokens.size() + n_new, num_computed);
+    h->tokens.insert(h->tokens.end(), new_tokens, new_tokens + known);
+    h->num_computed = num_computed;
+    m->hash_full_pages(*h);
+  }
+  h->num_computed = num_computed;
+  for (size_t g = 0; g < m->pools.size(); ++g) {
+    if (!m->windows[g]) continue;
+    auto& t = h->tables[g];
+    const int stop = std::min(m->first_needed_block((int)g, num_computed), (int)t.size());
+    for (int i = 0; i < stop; ++i)
+      if (t[i] >= 0) { if (m->pools[g].release(t[i])) return -1; t[i] = -1; }
+  }
+  return 0;
+}
+DH_API int dh_resolve(void* mp, int64_t r, const int32_t* tokens, int n) {
+  auto* m = static_cast<Manager*>(mp);
+  Held* h = m->find(r);
+  if (!h || !m->prefix) return 0;
+  if ((int)h->tokens.size() + n > h->num_computed) return fail("request %lld: more tokens resolved than were computed", r);
+  h->tokens.insert(h->tokens.end(), tokens, tokens + n);
+  m->hash_full_pages(*h);
+  return 0;
+}
+DH_API int dh_free(void* m, int64_t r) { return static_cast<Manager*>(m)->release(r); }
+
+// No page lost or held twice: per group, held pages + free pages = the pool; shared pages carry a common hash.
+DH_API int dh_check_invariants(void* mp) {
+  auto* m = static_cast<Manager*>(mp);
+  for (size_t g = 0; g < m->pools.size(); ++g) {
+    Pool& pool = m->pools[g];
+    std::vector<int> holders(pool.num_blocks, 0);
+    for (auto& kv : m->reqs) {
+      const auto& t = kv.second.tables[g];
+      for (size_t i = 0; i < t.size(); ++i) {
+        const int b = t[i];
+        if (b < 0) continue;
+        if (holders[b] && !m->prefix) return fail("group %lld: page %lld held twice", (long long)g, b);
+        if (holders[b] && (i >= kv.second.hashes.size() || !pool.hashed[b] || !(pool.hash[b] == kv.second.hashes[i])))
+          return fail("group %lld: page %lld shared without a common hash", (long long)g, b);
+        if (pool.refs[b] <= 0) return fail("group %lld: page %lld of request %lld is marked free", (long long)g, b, kv.first);
+        ++holders[b];
+      }
+    }
+    int held = 0;
+    for (int b = 0; b < pool.num_blocks; ++b) {
+      if (holders[b] && pool.refs[b] != holders[b]) return fail("group %lld: page %lld has %lld references", (long long)g, b, pool.refs[b]);
+      held += holders[b] > 0;
+    }
+    if (held + pool.num_free != pool.num_blocks) return fail("group %lld: %lld held + free pages do not make the pool", (long long)g, held);
+    if (pool.check()) return -1;
+  }
+  std::vector<char> used(m->max_slots, 0);
+  for (auto& kv : m->reqs) {
+    const int s = kv.second.slot;
+    if (s < 0 || s >= m->max_slots || used[s]) return fail("a state slot is held twice or out of range");
+    used[s] = 1;
+  }
+  if ((int)m->reqs.size() + (int)m->free_slots.size() != m->max_slots) return fail("state slots and page holders differ");
+  return 0;
+}
+
+// ---- the packed plan of a decode-only step (the layout of engine/batch.py: PlanBuilder.layout for T = B = R =
+// bucket): ids, pos, rows, cu, seq, sslots, fresh, then per group slot and table, each aligned to 4 words.
+// `words` points at the plan's int32 words (pinned host memory), written whole: the live rows from the requests'
+// tables, the rest as dummy rows (token 0, position 0, no slot, no pages).
+DH_API int dh_decode_plan_fill(void* mp, int32_t* words, int bucket, int width, const int64_t* rs, const int32_t* tokens,
+                               const int32_t* starts, int n) {
+  auto* m = static_cast<Manager*>(mp);
+  if (n > bucket) return fail("more requests than the graph's bucket");
+  auto align = [](int x) { return (x + 3) / 4 * 4; };
+  const int ng = (int)m->pools.size(), bs = m->block_size;
+  int off = 0;
+  int32_t* ids = words + off; off = align(off + bucket);
+  int32_t* pos = words + off; off = align(off + bucket);
+  int32_t* rows = words + off; off = align(off + bucket);
+  int32_t* cu = words + off; off = align(off + bucket + 1);
+  int32_t* seq = words + off; off = align(off + bucket);
+  int32_t* sslots = words + off; off = align(off + bucket);
+  int32_t* fresh = words + off; off = align(off + bucket);
+  std::vector<int32_t*> slot(ng), tab(ng);
+  for (int g = 0; g < ng; ++g) {
+    slot[g] = words + off; off = align(off + bucket);
+    tab[g] = words + off; off = align(off + bucket * width);
+  }
+  for (int i = 0; i <= bucket; ++i) cu[i] = i;
+  for (int i = 0; i < bucket; ++i) rows[i] = i;
+  for (int i = 0; i < n; ++i) {
+    Held* h = m->find(rs[i]);
+    if (!h) return fail("request %lld holds nothing", rs[i]);
+    const int p = starts[i];
+    ids[i] = tokens[i]; pos[i] = p; seq[i] = p + 1;
+    sslots[i] = h->slot; fresh[i] = h->fresh; h->fresh = false;
+    for (int g = 0; g < ng; ++g) {
+      const auto& t = h->tables[g];
+      const int k = std::min((int)t.size(), width);
+      int32_t* row = tab[g] + (size_t)i * width;
+      std::copy(t.begin(), t.begin() + k, row);
+      std::fill(row + k, row + width, -1);
+      const int blk = p / bs < k ? t[p / bs] : -1;
+      slot[g][i] = blk >= 0 ? blk * bs + p % bs : -1;
+    }
+  }
+  for (int i = n; i < bucket; ++i) {
+    ids[i] = 0; pos[i] = 0; seq[i] = 1; sslots[i] = 0; fresh[i] = 0;
+    for (int g = 0; g < ng; ++g) {
+      slot[g][i] = -1;
+      std::fill(tab[g] + (size_t)i * width, tab[g] + (size_t)(i + 1) * width, -1);
+    }
+  }
+  return off;
+}

@@ -195,9 +195,10 @@ qk_post_lanes_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ p
 
 // Head size 128 in bfloat16, the rotation over the whole head: half a warp per head.  A lane owns four consecutive
 // elements of the head's first half and the four elements 64 further on, which are their rotation partners, so the
-// rotation needs no exchange between lanes (two 8-byte accesses a head).  A warp takes HALF_HP pairs of heads of one
+// rotation needs no exchange between lanes (two 8-byte accesses a head).  A warp takes HALF_HP pairs of heads (one
+// where the tokens are few: a decode step is a chain of latencies, more warps make it shorter) of one
 // token and requests all of them before it works on the first.  Value heads are only copied into the cache.
-constexpr int HALF_HP = 3;
+constexpr int FEW_TOKENS = 128;
 
 __device__ __forceinline__ void unpack4(const uint2& x, float (&v)[4]) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
@@ -212,27 +213,21 @@ __device__ __forceinline__ uint2 pack4(const float (&v)[4]) {
   return x;
 }
 
-template <typename TW>
+template <typename TW, int HALF_HP>
 __global__ void __launch_bounds__(WARPS * 32)
 qk_post_half_warp_kernel(__nv_bfloat16* __restrict__ qkv, int64_t ld, const int* __restrict__ positions,
                          const TW* __restrict__ q_weight, const TW* __restrict__ k_weight, float eps,
                          const float* __restrict__ cos_sin, __nv_bfloat16* __restrict__ cache,
                          const int* __restrict__ slots, int block_size, int H, int Hkv) {
   constexpr int D = 128;
-  pdl_enter();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int side = lane >> 4, l = lane & 15;
   const int head0 = (blockIdx.y * WARPS + warp) * 2 * HALF_HP + side;
   const int heads = H + 2 * Hkv;
-  __nv_bfloat16* row = qkv + (int64_t)t * ld + l * 4;          // this lane's elements of the first half
-  uint2 lo[HALF_HP], hi[HALF_HP];
-#pragma unroll
-  for (int u = 0; u < HALF_HP; ++u)
-    if (head0 + 2 * u < heads) {
-      lo[u] = *reinterpret_cast<const uint2*>(row + (int64_t)(head0 + 2 * u) * D);
-      hi[u] = *reinterpret_cast<const uint2*>(row + (int64_t)(head0 + 2 * u) * D + D / 2);
-    }
+  // What no kernel of the step writes (the token's position and slot, its row of the angle table, the norm weights)
+  // is fetched while the kernel before this one may still be running; the q/k/v rows only after it has completed.
+  pdl_launch_dependents();
   float4 c = make_float4(1.f, 1.f, 1.f, 1.f), sn = make_float4(0.f, 0.f, 0.f, 0.f);
   const bool has_table = cos_sin != nullptr;
   if (has_table) {
@@ -243,6 +238,31 @@ qk_post_half_warp_kernel(__nv_bfloat16* __restrict__ qkv, int64_t ld, const int*
   const float cv[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
   const int slot = cache ? slots[t] : -1;
   const int64_t blk = slot >= 0 ? slot / block_size : 0, off = slot >= 0 ? slot % block_size : 0;
+  float wq[2][4], wk[2][4];                                    // this lane's norm weights: [half of the head][element]
+  auto weights = [&](const TW* w, float (&dst)[2][4]) {
+    if (!w) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) dst[0][j] = dst[1][j] = 1.f;
+    } else if constexpr (sizeof(TW) == 2) {
+      unpack4(*reinterpret_cast<const uint2*>(w + l * 4), dst[0]);
+      unpack4(*reinterpret_cast<const uint2*>(w + D / 2 + l * 4), dst[1]);
+    } else {
+      const float4 x = *reinterpret_cast<const float4*>(w + l * 4), y = *reinterpret_cast<const float4*>(w + D / 2 + l * 4);
+      dst[0][0] = x.x; dst[0][1] = x.y; dst[0][2] = x.z; dst[0][3] = x.w;
+      dst[1][0] = y.x; dst[1][1] = y.y; dst[1][2] = y.z; dst[1][3] = y.w;
+    }
+  };
+  weights(q_weight, wq);
+  weights(k_weight, wk);
+  pdl_wait();
+  __nv_bfloat16* row = qkv + (int64_t)t * ld + l * 4;          // this lane's elements of the first half
+  uint2 lo[HALF_HP], hi[HALF_HP];
+#pragma unroll
+  for (int u = 0; u < HALF_HP; ++u)
+    if (head0 + 2 * u < heads) {
+      lo[u] = *reinterpret_cast<const uint2*>(row + (int64_t)(head0 + 2 * u) * D);
+      hi[u] = *reinterpret_cast<const uint2*>(row + (int64_t)(head0 + 2 * u) * D + D / 2);
+    }
 #pragma unroll
   for (int u = 0; u < HALF_HP; ++u) {
     const int head = head0 + 2 * u;
@@ -264,16 +284,11 @@ qk_post_half_warp_kernel(__nv_bfloat16* __restrict__ qkv, int64_t ld, const int*
     if (live && kind != 2) {
       if (w) {
         const float rinv = rsqrtf(ss / (float)D + eps);
-        float wa[4], wb[4];
-        if constexpr (sizeof(TW) == 2) {
-          unpack4(*reinterpret_cast<const uint2*>(w + l * 4), wa);
-          unpack4(*reinterpret_cast<const uint2*>(w + D / 2 + l * 4), wb);
-        } else {
-          const float4 x = *reinterpret_cast<const float4*>(w + l * 4), y = *reinterpret_cast<const float4*>(w + D / 2 + l * 4);
-          wa[0] = x.x; wa[1] = x.y; wa[2] = x.z; wa[3] = x.w; wb[0] = y.x; wb[1] = y.y; wb[2] = y.z; wb[3] = y.w;
-        }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { a[j] = a[j] * rinv * wa[j]; b[j] = b[j] * rinv * wb[j]; }
+        for (int j = 0; j < 4; ++j) {
+          a[j] = a[j] * rinv * (kind == 0 ? wq[0][j] : wk[0][j]);
+          b[j] = b[j] * rinv * (kind == 0 ? wq[1][j] : wk[1][j]);
+        }
       }
       if (rotate) {
 #pragma unroll
@@ -340,8 +355,10 @@ DINFER_API int dinfer_qk_post(void* qkv, int64_t ld, const int* positions, const
                            !(reinterpret_cast<uintptr_t>(k_weight) & 31) && !(reinterpret_cast<uintptr_t>(cos_sin) & 31);
       if constexpr (sizeof(TA) == 2) {
         if (aligned && (!cos_sin || rot == D) && D == 128) {
-          const dim3 half_grid(T, (heads + WARPS * 2 * HALF_HP - 1) / (WARPS * 2 * HALF_HP));
-          launch_pdl(qk_post_half_warp_kernel<TW>, half_grid, dim3(WARPS * 32), 0, stream, (__nv_bfloat16*)qkv, ld, positions,
+          const int hp = T <= FEW_TOKENS ? 1 : 3;
+          const dim3 half_grid(T, (heads + WARPS * 2 * hp - 1) / (WARPS * 2 * hp));
+          launch_pdl(hp == 1 ? qk_post_half_warp_kernel<TW, 1> : qk_post_half_warp_kernel<TW, 3>, half_grid, dim3(WARPS * 32), 0,
+                     stream, (__nv_bfloat16*)qkv, ld, positions,
                      (const TW*)q_weight, (const TW*)k_weight, eps, cos_sin, (__nv_bfloat16*)cache, slots, block_size, H, Hkv);
           return cuda_status("qk_post");
         }

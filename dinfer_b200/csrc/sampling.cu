@@ -32,6 +32,7 @@ constexpr int BLOCK = 1024;
 constexpr int ROW_CTAS = 8;                 // cluster size: CTAs that share a row
 constexpr int MAX_SLICE = 48 * 1024;        // floats of a row slice that shared memory holds (192 KB)
 constexpr int XCH = 16;                     // floats a CTA hands to the others per exchange
+constexpr int ARGMAX_MANY_ROWS = 40;        // from so many rows on the argmax runs a CTA per row
 
 // ---- cluster plumbing
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -412,6 +413,45 @@ argmax_kernel(const float* __restrict__ logits, int64_t ld, int* __restrict__ ou
   cluster_sync_all();                                    // nobody leaves while others may still write to it
 }
 
+// Many rows: a CTA per row (no cluster: with 8 CTAs a row, 64 rows are two waves of CTAs that mostly wait for each
+// other), four floats a load where the row allows.
+__global__ void __launch_bounds__(BLOCK)
+argmax_many_kernel(const float* __restrict__ logits, int64_t ld, int* __restrict__ out, int vocab) {
+  __shared__ float part_v[BLOCK / 32];
+  __shared__ int part_i[BLOCK / 32];
+  pdl_enter();
+  const int b = blockIdx.x;
+  const float* row = logits + (int64_t)b * ld;
+  ArgMax best{-INFINITY, 0x7fffffff};
+  if (!(reinterpret_cast<uintptr_t>(row) & 15)) {
+    const int n4 = vocab >> 2;
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    for (int i = threadIdx.x; i < n4; i += BLOCK) {
+      const float4 v = row4[i];
+      best = better(best, ArgMax{v.x, 4 * i});
+      best = better(best, ArgMax{v.y, 4 * i + 1});
+      best = better(best, ArgMax{v.z, 4 * i + 2});
+      best = better(best, ArgMax{v.w, 4 * i + 3});
+    }
+    for (int i = 4 * n4 + threadIdx.x; i < vocab; i += BLOCK) best = better(best, ArgMax{row[i], i});
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += BLOCK) best = better(best, ArgMax{row[i], i});
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    best = better(best, ArgMax{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)});
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { part_v[warp] = best.v; part_i[warp] = best.i; }
+  __syncthreads();
+  if (warp == 0) {
+    best = ArgMax{part_v[lane], part_i[lane]};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      best = better(best, ArgMax{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)});
+    if (lane == 0) out[b] = best.i == 0x7fffffff ? 0 : best.i;
+  }
+}
+
 __global__ void __launch_bounds__(BLOCK)
 sample_kernel(const float* __restrict__ logits, int64_t ld, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
@@ -720,6 +760,11 @@ DINFER_DEFINE_LAST_ERROR()
 DINFER_API int dinfer_argmax(const float* logits, int64_t ld, int* out, int rows, int vocab, cudaStream_t stream) {
   if (rows < 0 || vocab <= 0 || ld < vocab) return refuse(DINFER_BAD_ARGUMENT, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
   if (rows == 0) return 0;
+  if (rows >= ARGMAX_MANY_ROWS) {
+    cudaError_t e = launch_pdl(argmax_many_kernel, dim3(rows), dim3(BLOCK), 0, stream, logits, ld, out, vocab);
+    if (e != cudaSuccess) return refuse((int)e, "argmax: launch failed: %s", cudaGetErrorString(e));
+    return cuda_status("argmax");
+  }
   return launch_rows(argmax_kernel, rows, 0, stream, "argmax", logits, ld, out, vocab);
 }
 

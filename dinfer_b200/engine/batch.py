@@ -280,6 +280,16 @@ class DecodePlan:
         o, n = self.views[name]
         return self.shadow[o:o + n]
 
+    def _check(self) -> None:
+        """The plan in ``shadow`` names pages and slots of the pools only, and no slot twice."""
+        m = self.builder.manager
+        for g in range(self.ng):
+            n = m.pools[g].num_blocks
+            live = self._slot[g][self._slot[g] >= 0]
+            if self._tab[g].min() < -1 or self._tab[g].max() >= n or (live.size and live.max() >= n * m.block_size) \
+                    or live.size != np.unique(live).size:
+                raise AssertionError(f"decode plan: group {g}: a page or slot outside the pool, or a slot written twice")
+
     def fill(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> None:
         """Write the step of ``entries`` (one token each) into the plan and send it to the device."""
         b = self.builder
@@ -289,6 +299,16 @@ class DecodePlan:
         if n_real > self.bucket:
             raise ValueError("more requests than the graph's bucket")
         width = self.width
+        if hasattr(m, "fill_decode_plan"):
+            # the cache manager whose tables live in C++ writes the plan itself, straight into the pinned buffer
+            k = b._next_turn()
+            words = b._host[k].numpy()[:self.words]
+            m.fill_decode_plan(words, self.bucket, width, [e.req_id for e in entries], [e.tokens[0] for e in entries], starts)
+            if VALIDATE_PLANS:
+                self.shadow[:] = words
+                self._check()
+            b._send(k, self.words, self.dev)
+            return
         for i, e in enumerate(entries):
             p = starts[i]
             self._ids[i] = e.tokens[0]
@@ -324,12 +344,7 @@ class DecodePlan:
                 self._copied[i][g] = 0
         self._live = n_real
         if VALIDATE_PLANS:
-            for g in range(self.ng):
-                n = m.pools[g].num_blocks
-                live = self._slot[g][self._slot[g] >= 0]
-                if self._tab[g].min() < -1 or self._tab[g].max() >= n or (live.size and live.max() >= n * bs) \
-                        or live.size != np.unique(live).size:
-                    raise AssertionError(f"decode plan: group {g}: a page or slot outside the pool, or a slot written twice")
+            self._check()
         k = b._next_turn()
         b._host[k].numpy()[:self.words] = self.shadow
         b._send(k, self.words, self.dev)

@@ -92,7 +92,7 @@ class LLM:
                  decode_exempt_from_budget: bool = True, long_prefill_token_threshold: int = 0,
                  enable_cuda_graph: bool = True, enable_prefix_caching: bool = False,
                  split_norms: bool = False, async_scheduling: bool = True, mixed_cuda_graph: bool = True,
-                 allow_unused_tensors: bool = False, device: int = 0):
+                 allow_unused_tensors: bool = False, native_host: bool = True, device: int = 0):
         """``model``: a folder with config.json and *.safetensors; or ``config`` (the config.json
         dictionary) with ``weights`` (any WeightSource, e.g. ``RandomSource``)."""
         self.engine_config = EngineConfig(
@@ -103,7 +103,7 @@ class LLM:
             long_prefill_token_threshold=long_prefill_token_threshold,
             enable_cuda_graph=enable_cuda_graph, enable_prefix_caching=enable_prefix_caching,
             split_norms=split_norms, async_scheduling=async_scheduling, mixed_cuda_graph=mixed_cuda_graph,
-            allow_unused_tensors=allow_unused_tensors, dtype=dtype,
+            allow_unused_tensors=allow_unused_tensors, native_host=native_host, dtype=dtype,
             device=device)
         # what a request gets that brings no SamplingParams of its own: the model folder's generation_config.json
         # (temperature, top_p, top_k) over the built-in defaults

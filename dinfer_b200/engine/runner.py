@@ -188,8 +188,12 @@ class ModelRunner:
         if prefix and (any(g.window is not None for g in groups) or any(isinstance(n, StateNeed) for n in needs)):
             raise ValueError("enable_prefix_caching: this model has windowed layers or per-request state, "
                              "whose cache cannot be shared between requests")
-        self.manager = CacheManager(groups, bs, [self.num_blocks] * len(groups), e.max_num_seqs,
-                                    enable_prefix_caching=prefix)
+        if e.native_host:
+            from ..cache.native import NativeCacheManager as Manager
+        else:
+            Manager = CacheManager
+        self.manager = Manager(groups, bs, [self.num_blocks] * len(groups), e.max_num_seqs,
+                               enable_prefix_caching=prefix)
         self.bindings: List[CacheBinding] = []
         for i, (entry, n) in enumerate(zip(self.spec.schedule, needs)):
             if entry.cache_from is not None:

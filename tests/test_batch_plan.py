@@ -7,6 +7,7 @@ import pytest
 import torch
 
 from dinfer_b200.cache.manager import CacheManager, GroupSpec
+from dinfer_b200.cache.native import NativeCacheManager
 from dinfer_b200.engine.batch import DecodePlan, PlanBuilder, StepEntry
 
 
@@ -16,11 +17,13 @@ def packed(builder, entries, starts, bucket, width):
     return dev.numpy().copy()
 
 
+@pytest.mark.parametrize("manager", [CacheManager, NativeCacheManager])
 @pytest.mark.parametrize("groups", [[GroupSpec()], [GroupSpec(), GroupSpec(window=5)]])
-def test_decode_plan_matches_full_build(groups):
+def test_decode_plan_matches_full_build(groups, manager):
+    """(With the C++ cache manager the plan is written by the library from its own tables.)"""
     rng = random.Random(3)
     bs, width, bucket = 4, 12, 4
-    m = CacheManager(groups, bs, 64, max_num_seqs=bucket)
+    m = manager(groups, bs, 64, max_num_seqs=bucket)
     builder = PlanBuilder(m, "cpu", max_tokens=64, max_reqs=bucket, max_blocks=width)
     dev = torch.zeros(builder.words(bucket, bucket, bucket, width), dtype=torch.int32)
     plan = DecodePlan(builder, bucket, width, dev)

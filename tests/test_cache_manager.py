@@ -4,8 +4,22 @@ import random
 
 import pytest
 
+import sys
+
 from dinfer_b200.cache.block_pool import BlockPool, PoolError, StateSlots
 from dinfer_b200.cache.manager import CacheManager, GroupSpec
+from dinfer_b200.cache.native import NativeCacheManager
+
+PythonCacheManager = CacheManager
+
+
+@pytest.fixture(params=["python", "native"], autouse=True)
+def implementation(request, monkeypatch):
+    """Every test of this file runs twice: on the Python cache manager and on the one whose bookkeeping is C++."""
+    if request.param == "native":
+        monkeypatch.setattr(sys.modules[__name__], "CacheManager", NativeCacheManager)
+    return request.param
+
 
 
 def test_pool_reuses_freed_pages_first():
@@ -258,3 +272,54 @@ def test_a_batch_is_asked_for_as_a_whole():
     assert (m.num_free_blocks(0), m.num_free_blocks(1), m.state_slots.num_free) == before
     assert m.requests() == ["a"]
     m.check_invariants()
+
+
+def test_both_implementations_hand_out_the_same_pages_in_the_same_order():
+    """One random sequence of requests that come, grow, finish and repeat beginnings, driven through the Python and
+    the C++ cache manager side by side: the same answers, the same page ids in every table, the same free counts,
+    the same state slots, the same prefix hits and evictions (their page hashes differ, what they find does not)."""
+    rng = random.Random(2024)
+    for prefix, groups in ((False, [GroupSpec(), GroupSpec(window=9)]), (True, [GroupSpec(), GroupSpec()])):
+        a = PythonCacheManager(groups, 4, [30, 30], 5, enable_prefix_caching=prefix)
+        b = NativeCacheManager(groups, 4, [30, 30], 5, enable_prefix_caching=prefix)
+        stems = [[rng.randrange(40) for _ in range(rng.randrange(4, 40))] for _ in range(3)]
+        live = {}
+        for step in range(1500):
+            r = rng.random()
+            if live and r < 0.25:
+                rid = rng.choice(list(live))
+                assert (rid in a) == (rid in b)
+                if rid in a:
+                    a.free(rid); b.free(rid)
+                del live[rid]
+            elif r < 0.5:
+                rid = f"r{step}"
+                toks = list(rng.choice(stems)) + [rng.randrange(40) for _ in range(rng.randrange(1, 12))]
+                ha, hb = a.begin(rid, toks), b.begin(rid, toks)
+                assert ha == hb
+                live[rid] = (toks, ha)
+            elif live:
+                rid = rng.choice(list(live))
+                toks, done = live[rid]
+                n = min(rng.randrange(1, 9), len(toks) - done)
+                if n > 0:
+                    assert a.can_allocate(rid, done + n) == b.can_allocate(rid, done + n)
+                    oa, ob = a.allocate(rid, done + n), b.allocate(rid, done + n)
+                    assert oa == ob
+                    if oa:
+                        a.advance(rid, done + n, toks[done:done + n]); b.advance(rid, done + n, toks[done:done + n])
+                        live[rid] = (toks, done + n)
+                    elif rid not in a:
+                        del live[rid]
+            assert a.requests() == b.requests()
+            for rid in a.requests():
+                assert [a.block_table(rid, g) for g in range(2)] == [b.block_table(rid, g) for g in range(2)]
+                assert (a.num_tokens(rid), a.num_computed(rid)) == (b.num_tokens(rid), b.num_computed(rid))
+                assert a.state_slots.slot(rid) == b.state_slots.slot(rid)
+            assert [p.num_free for p in a.pools] == [p.num_free for p in b.pools]
+            assert [p.evictions for p in a.pools] == [p.evictions for p in b.pools]
+            assert a.state_slots.num_free == b.state_slots.num_free
+            assert (a.prefix_queries, a.prefix_hits) == (b.prefix_queries, b.prefix_hits)
+            if step % 50 == 0:
+                a.check_invariants(); b.check_invariants()
+        a.check_invariants(); b.check_invariants()

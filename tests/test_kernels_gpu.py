@@ -253,6 +253,24 @@ def test_argmax_and_sampling(V):
     assert agree >= total - 2, f"{agree}/{total}"
 
 
+@pytest.mark.parametrize("R,V,ld", [(64, 151936, 151936), (41, 517, 517), (100, 4099, 4104), (40, 1000, 1001)])
+def test_argmax_of_many_rows(R, V, ld):
+    """From 40 rows on the argmax runs a CTA per row: every row, ties to the lowest index, rows that start on no
+    16-byte boundary, a vocabulary that is no multiple of four, columns beyond the vocabulary ignored."""
+    from dinfer_b200.sampling import sampler as S
+    g = torch.Generator().manual_seed(R + V)
+    full = torch.randn(R, ld, generator=g) * 3
+    full[:, V:] = 1e9                                         # beyond the vocabulary: must not be looked at
+    logits = full[:, :V]
+    logits[3, 5] = logits[3, V - 1] = 60.0                    # a tie: the lower index wins
+    logits[7, V - 1] = 70.0                                   # the last column
+    logits[8, 0] = 70.0
+    got = S.argmax(dev(full)[:, :V]).cpu().tolist()
+    want = [int(torch.argmax(logits[i])) for i in range(R)]
+    want[3] = 5
+    assert got == want
+
+
 def test_sampling_distribution_and_batch_independence():
     from dinfer_b200.sampling import sampler as S
     logits = torch.tensor([[2.0, 1.0, 0.5, -1.0, 3.0, 0.0, -30.0]])
