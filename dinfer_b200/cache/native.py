@@ -38,7 +38,7 @@ def library() -> ctypes.CDLL:
             "dh_can_allocate": (I, [P, L, I]), "dh_can_allocate_all": (I, [P, P, P, I]), "dh_allocate": (I, [P, L, I]),
             "dh_begin": (I, [P, L, P, I]), "dh_advance": (I, [P, L, I, P, I]), "dh_resolve": (I, [P, L, P, I]),
             "dh_free": (I, [P, L]), "dh_check_invariants": (I, [P]),
-            "dh_decode_plan_fill": (I, [P, P, I, I, P, P, P, I]),
+            "dh_decode_plan_fill": (I, [P, P, I, I, P, P, P, I]), "dh_advance_many": (I, [P, P, P, I]),
         }
         for name, (res, args) in sig.items():
             f = getattr(lib, name)
@@ -226,6 +226,11 @@ class NativeCacheManager:
         else:
             rc = self._lib.dh_advance(self._h, rid, int(num_computed), None, 0)
         if rc:
+            raise PoolError(_error(self._lib))
+
+    def advance_many(self, handles: np.ndarray, computed: np.ndarray) -> None:
+        """``advance`` for a step's requests at once (int64 handles, int32 token counts; without the prefix cache)."""
+        if self._lib.dh_advance_many(self._h, handles.ctypes.data, computed.ctypes.data, len(handles)):
             raise PoolError(_error(self._lib))
 
     def resolve(self, req: Hashable, tokens: Sequence[int]) -> None:

@@ -465,3 +465,233 @@ DH_API int dh_decode_plan_fill(void* mp, int32_t* words, int bucket, int width, 
   }
   return off;
 }
+
+// ---- the scheduler: continuous batching above the step function (engine/scheduler.py defines the policy: running
+// requests first, then waiting ones while the token budget, max_num_seqs and the pages last; prompts cut into
+// portions; the LAST running request preempted when pages run out, never the one that asks while others run; a
+// request that alone does not fit finished with `length`; nothing admitted in a step that preempted; with
+// `lookahead` a request that samples counts as one token longer at once).  crates/core/src/sched/mod.rs:318-828.
+namespace {
+
+enum { ST_WAITING = 0, ST_RUNNING = 1, ST_FINISHED = 2 };
+enum { FIN_NONE = 0, FIN_STOP = 1, FIN_LENGTH = 2, FIN_ABORT = 3 };
+
+struct Rec {
+  int prompt_len = 0;
+  std::vector<int32_t> tokens;                   // prompt, then the output tokens the host knows
+  int num_computed = 0, placeholders = 0;
+  int max_tokens = 0, min_tokens = 0;
+  bool ignore_eos = false, every_prompt_row = false;
+  std::vector<int32_t> stop_ids;
+  int status = ST_WAITING, reason = FIN_NONE, preemptions = 0;
+  int n_out() const { return (int)tokens.size() - prompt_len; }
+};
+
+struct Sched {
+  Manager* m = nullptr;
+  int budget = 0, threshold = 0, max_model_len = 0, max_num_seqs = 0;
+  bool exempt = true;
+  std::vector<int32_t> eos;
+  std::unordered_map<int64_t, Rec> recs;
+  std::vector<int64_t> waiting, running;         // waiting[0] is the front of the queue
+  long long preemptions = 0;
+
+  void finish(int64_t id, Rec& r, int reason) {
+    r.status = ST_FINISHED;
+    r.reason = reason;
+    if (m->find(id)) m->release(id);
+  }
+  void preempt(int64_t id) {
+    Rec& r = recs[id];
+    if (m->find(id)) m->release(id);
+    r.num_computed = 0;
+    r.placeholders = 0;                          // a token in flight is still appended when it arrives (update)
+    r.status = ST_WAITING;
+    ++r.preemptions;
+    ++preemptions;
+    waiting.insert(waiting.begin(), id);
+  }
+  int check_stop(const Rec& r, int tok) const {
+    const int n_out = r.n_out();
+    if (n_out >= r.min_tokens) {
+      if (!r.ignore_eos && std::find(eos.begin(), eos.end(), tok) != eos.end()) return FIN_STOP;
+      if (std::find(r.stop_ids.begin(), r.stop_ids.end(), tok) != r.stop_ids.end()) return FIN_STOP;
+    }
+    if (n_out >= r.max_tokens || (int)r.tokens.size() >= max_model_len) return FIN_LENGTH;
+    return FIN_NONE;
+  }
+};
+
+}  // namespace
+
+DH_API void* dh_sched_new(void* manager, int max_num_batched_tokens, int long_prefill_token_threshold, int max_model_len,
+                          int max_num_seqs, int decode_exempt, const int32_t* eos, int n_eos) {
+  auto* s = new Sched();
+  s->m = static_cast<Manager*>(manager);
+  s->budget = max_num_batched_tokens; s->threshold = long_prefill_token_threshold; s->max_model_len = max_model_len;
+  s->max_num_seqs = max_num_seqs; s->exempt = decode_exempt != 0;
+  s->eos.assign(eos, eos + n_eos);
+  return s;
+}
+DH_API void dh_sched_delete(void* s) { delete static_cast<Sched*>(s); }
+
+DH_API int dh_sched_add(void* sp, int64_t id, const int32_t* prompt, int n, int max_tokens, int min_tokens, int ignore_eos,
+                        const int32_t* stop_ids, int n_stop, int every_prompt_row) {
+  auto* s = static_cast<Sched*>(sp);
+  if (s->recs.count(id)) return fail("request %lld is known already", id);
+  Rec r;
+  r.prompt_len = n;
+  r.tokens.assign(prompt, prompt + n);
+  r.max_tokens = max_tokens; r.min_tokens = min_tokens; r.ignore_eos = ignore_eos != 0;
+  r.every_prompt_row = every_prompt_row != 0;
+  r.stop_ids.assign(stop_ids, stop_ids + n_stop);
+  s->recs.emplace(id, std::move(r));
+  s->waiting.push_back(id);
+  return 0;
+}
+// a request that is over (finished or aborted) is forgotten
+DH_API void dh_sched_forget(void* sp, int64_t id) { static_cast<Sched*>(sp)->recs.erase(id); }
+DH_API int dh_sched_abort(void* sp, int64_t id) {
+  auto* s = static_cast<Sched*>(sp);
+  auto it = s->recs.find(id);
+  if (it == s->recs.end() || it->second.status == ST_FINISHED) return 0;
+  for (auto* q : {&s->running, &s->waiting}) {
+    auto p = std::find(q->begin(), q->end(), id);
+    if (p != q->end()) { q->erase(p); s->finish(id, it->second, FIN_ABORT); return 1; }
+  }
+  return 0;
+}
+DH_API int dh_sched_counts(void* sp, int* n_waiting, int* n_running) {
+  auto* s = static_cast<Sched*>(sp);
+  *n_waiting = (int)s->waiting.size(); *n_running = (int)s->running.size();
+  return 0;
+}
+DH_API int dh_sched_queue(void* sp, int which, int64_t* out, int cap) {
+  auto& q = which ? static_cast<Sched*>(sp)->running : static_cast<Sched*>(sp)->waiting;
+  const int n = std::min(cap, (int)q.size());
+  std::copy(q.begin(), q.begin() + n, out);
+  return (int)q.size();
+}
+DH_API long long dh_sched_preemptions(void* sp) { return static_cast<Sched*>(sp)->preemptions; }
+
+// One step's decisions.  Scheduled requests come back as columns (ids, start, num_tokens, samples, num_generated) of
+// at most `cap` entries, the preempted and the finished (no fit) as id lists of at most `cap`; counts[0..2] = how
+// many of each.  Returns 0, or -1 when `cap` is too small.
+DH_API int dh_sched_schedule(void* sp, int lookahead, int cap, int64_t* ids, int32_t* start, int32_t* num,
+                             int32_t* samples, int32_t* ngen, int64_t* preempted, int64_t* finished, int32_t* counts) {
+  auto* s = static_cast<Sched*>(sp);
+  Manager* m = s->m;
+  int n_s = 0, n_p = 0, n_f = 0;
+  int budget = s->budget;
+  auto emit = [&](int64_t id, int st, int n, bool smp, int gen) {
+    if (n_s >= cap) return false;
+    ids[n_s] = id; start[n_s] = st; num[n_s] = n; samples[n_s] = smp; ngen[n_s] = gen;
+    ++n_s;
+    return true;
+  };
+  size_t i = 0;
+  while (i < s->running.size()) {
+    const int64_t id = s->running[i];
+    Rec& r = s->recs[id];
+    const int ahead = r.placeholders, n_out = r.n_out();
+    const int known = (int)r.tokens.size() + ahead, computed = r.num_computed;
+    if (ahead && (n_out + ahead >= r.max_tokens || known >= s->max_model_len)) { ++i; continue; }
+    int num_new = known - computed;
+    const bool is_decode = num_new == 1 && computed > 0;
+    if (s->threshold > 0) num_new = std::min(num_new, s->threshold);
+    if (!(is_decode && s->exempt)) num_new = std::min(num_new, budget);
+    if (computed + num_new > s->max_model_len) num_new = s->max_model_len - computed;
+    if (num_new <= 0) { ++i; continue; }
+    bool placed = true, gone = false;
+    while (!m->allocate(id, computed + num_new)) {
+      const int64_t victim = s->running.back();
+      if (victim == id) {
+        if (s->running.size() > 1) {
+          placed = false;                        // others run: sit this step out, keep the pages
+        } else {
+          s->running.pop_back();                 // alone and still no fit: it can never finish
+          s->finish(id, r, FIN_LENGTH);
+          if (n_f >= cap) return fail("the result columns are too short");
+          finished[n_f++] = id;
+          placed = false; gone = true;
+        }
+        break;
+      }
+      s->running.pop_back();
+      s->preempt(victim);
+      if (n_p >= cap) return fail("the result columns are too short");
+      preempted[n_p++] = victim;
+    }
+    if (!placed) { if (!gone) ++i; continue; }
+    if (!emit(id, computed, num_new, computed + num_new == known, n_out + ahead)) return fail("the result columns are too short");
+    if (!(is_decode && s->exempt)) budget -= num_new;
+    ++i;
+  }
+  if (n_p == 0) {
+    while (!s->waiting.empty() && budget > 0 && (int)s->running.size() < s->max_num_seqs) {
+      const int64_t id = s->waiting.front();
+      Rec& r = s->recs[id];
+      bool began = false;
+      if (r.num_computed == 0 && m->prefix && !m->find(id) && !r.every_prompt_row) {
+        // pages of an earlier request with the same beginning: those tokens are not run again
+        r.num_computed = dh_begin(m, id, r.tokens.data(), (int)r.tokens.size());
+        began = r.num_computed > 0;
+      }
+      int num_new = (int)r.tokens.size() - r.num_computed;
+      if (s->threshold > 0) num_new = std::min(num_new, s->threshold);
+      num_new = std::min({num_new, budget, s->max_model_len - r.num_computed});
+      if (num_new <= 0 || !m->allocate(id, r.num_computed + num_new)) {
+        if (began) { m->release(id); r.num_computed = 0; }
+        break;
+      }
+      s->waiting.erase(s->waiting.begin());
+      r.status = ST_RUNNING;
+      s->running.push_back(id);
+      if (!emit(id, r.num_computed, num_new, r.num_computed + num_new == (int)r.tokens.size(), r.n_out()))
+        return fail("the result columns are too short");
+      budget -= num_new;
+    }
+  }
+  for (int k = 0; k < n_s; ++k) {                // the cache will hold these once the step has run
+    Rec& r = s->recs[ids[k]];
+    r.num_computed += num[k];
+    if (lookahead && samples[k]) ++r.placeholders;
+  }
+  counts[0] = n_s; counts[1] = n_p; counts[2] = n_f;
+  return 0;
+}
+
+// After the step: the sampled token of every scheduled request that samples (tokens[k] for entry k; ignored where
+// samples[k] is 0) is appended, the stop conditions are checked, what has finished is freed.  done_ids / reasons get
+// the requests that finished (at most n); returns how many.
+DH_API int dh_sched_update(void* sp, int n, const int64_t* ids, const int32_t* samples, const int32_t* tokens,
+                           int64_t* done_ids, int32_t* reasons) {
+  auto* s = static_cast<Sched*>(sp);
+  int n_done = 0;
+  for (int k = 0; k < n; ++k) {
+    if (!samples[k]) continue;
+    auto it = s->recs.find(ids[k]);
+    if (it == s->recs.end() || it->second.status == ST_FINISHED) continue;   // finished meanwhile: dropped
+    Rec& r = it->second;
+    r.tokens.push_back(tokens[k]);
+    const int reason = s->check_stop(r, tokens[k]);
+    if (r.status == ST_RUNNING) {
+      if (r.placeholders > 0) --r.placeholders;
+      if (reason) s->running.erase(std::find(s->running.begin(), s->running.end(), ids[k]));
+    } else if (reason) {                         // preempted while this token was in flight, and it ends the request
+      s->waiting.erase(std::find(s->waiting.begin(), s->waiting.end(), ids[k]));
+    }
+    if (reason) {
+      s->finish(ids[k], r, reason);
+      done_ids[n_done] = ids[k]; reasons[n_done] = reason; ++n_done;
+    }
+  }
+  return n_done;
+}
+
+// The same as dh_advance for every request of a step at once (no token ids: not for the prefix cache).
+DH_API int dh_advance_many(void* mp, const int64_t* rs, const int32_t* computed, int n) {
+  for (int i = 0; i < n; ++i)
+    if (dh_advance(mp, rs[i], computed[i], nullptr, 0)) return -1;
+  return 0;
+}

@@ -37,7 +37,7 @@ from ..weights.loader import WeightSource
 from .batch import StepEntry
 from .request import Request
 from .runner import ModelRunner
-from .scheduler import Scheduler
+from .scheduler import NativeScheduler, Scheduler
 
 
 @dataclass
@@ -114,7 +114,9 @@ class LLM:
             self.runner = ModelRunner(config, weights, self.engine_config)
         else:
             raise ValueError("give a model folder, or config and weights")
-        self.scheduler = Scheduler(self.engine_config, self.runner.manager, self.runner.spec.eos_token_ids)
+        native = hasattr(self.runner.manager, "fill_decode_plan")      # the C++ cache manager takes the C++ scheduler
+        self.scheduler = (NativeScheduler if native else Scheduler)(self.engine_config, self.runner.manager,
+                                                                    self.runner.spec.eos_token_ids)
         self.sampler = Sampler(self.runner.device)
         self.stats = EngineStats()
         self._next_id = 0

@@ -225,3 +225,195 @@ class Scheduler:
         if n_out >= p.max_tokens or req.num_tokens >= self.config.max_model_len:
             return FinishReason.LENGTH
         return None
+
+
+class NativeScheduler(Scheduler):
+    """The same scheduler with its decisions taken in C++ (``csrc/host_core.cpp``) over the C++ cache manager
+    (``cache.native.NativeCacheManager``): pages, queues, preemption and the stop check all live there; this class
+    keeps the ``Request`` objects of the Python interface in step with it.  ``schedule_columns`` / ``update_columns``
+    are the same calls without the objects (columns in, columns out), for callers that keep no ``Request``."""
+
+    _REASONS = {1: FinishReason.STOP, 2: FinishReason.LENGTH, 3: FinishReason.ABORT}
+
+    def __init__(self, config: EngineConfig, manager, eos_token_ids: Sequence[int] = ()):
+        import numpy as np
+        from ctypes import c_int, c_int32, c_int64, c_longlong, c_void_p
+        from ..cache.native import NativeCacheManager, library
+        if not isinstance(manager, NativeCacheManager):
+            raise TypeError("NativeScheduler works on a NativeCacheManager")
+        super().__init__(config, manager, eos_token_ids)
+        self._np = np
+        lib = self._lib = library()
+        P, I, L = c_void_p, c_int, c_int64
+        for name, res, args in (("dh_sched_new", P, [P, I, I, I, I, I, P, I]), ("dh_sched_delete", None, [P]),
+                                ("dh_sched_add", I, [P, L, P, I, I, I, I, P, I, I]), ("dh_sched_forget", None, [P, L]),
+                                ("dh_sched_abort", I, [P, L]), ("dh_sched_counts", I, [P, P, P]),
+                                ("dh_sched_queue", I, [P, I, P, I]), ("dh_sched_preemptions", c_longlong, [P]),
+                                ("dh_sched_schedule", I, [P, I, I, P, P, P, P, P, P, P, P]),
+                                ("dh_sched_update", I, [P, I, P, P, P, P, P])):
+            f = getattr(lib, name)
+            f.restype, f.argtypes = res, args
+        eos = np.asarray(sorted(self.eos), dtype=np.int32)
+        self._s = lib.dh_sched_new(manager._h, config.max_num_batched_tokens, config.long_prefill_token_threshold,
+                                   config.max_model_len, config.max_num_seqs, int(config.decode_exempt_from_budget),
+                                   eos.ctypes.data if eos.size else None, eos.size)
+        self._reqs: Dict[int, Request] = {}                  # handle -> request, while the request lives
+        cap = self._cap = max(16, 2 * config.max_num_seqs + 8)
+        self._ids, self._pre, self._fin = (np.zeros(cap, dtype=np.int64) for _ in range(3))
+        self._start, self._num, self._smp, self._gen = (np.zeros(cap, dtype=np.int32) for _ in range(4))
+        self._counts = np.zeros(4, dtype=np.int32)
+        self._tok, self._reason = np.zeros(cap, dtype=np.int32), np.zeros(cap, dtype=np.int32)
+        self._done = np.zeros(cap, dtype=np.int64)
+
+    def __del__(self):
+        s, self._s = getattr(self, "_s", None), None
+        if s:
+            self._lib.dh_sched_delete(s)
+
+    def _error(self) -> str:
+        msg = self._lib.dh_last_error()
+        return msg.decode("utf-8", "replace") if msg else "host core error"
+
+    # ---- the queues as the Python scheduler shows them
+    def _queue(self, which: int):
+        np = self._np
+        n = max(1, len(self._reqs))
+        buf = np.zeros(n, dtype=np.int64)
+        k = self._lib.dh_sched_queue(self._s, which, buf.ctypes.data, n)
+        return [self._reqs[int(h)] for h in buf[:k]]
+
+    @property
+    def waiting(self):
+        return deque(self._queue(0))
+
+    @waiting.setter
+    def waiting(self, value):            # (the base class's constructor sets empty queues)
+        pass
+
+    @property
+    def running(self):
+        return self._queue(1)
+
+    @running.setter
+    def running(self, value):
+        pass
+
+    @property
+    def num_preemptions(self) -> int:
+        return int(self._lib.dh_sched_preemptions(self._s)) if getattr(self, "_s", None) else 0
+
+    @num_preemptions.setter
+    def num_preemptions(self, value):
+        pass
+
+    def has_unfinished(self) -> bool:
+        np = self._np
+        w, r = np.zeros(1, dtype=np.int32), np.zeros(1, dtype=np.int32)
+        self._lib.dh_sched_counts(self._s, w.ctypes.data, r.ctypes.data)
+        return bool(w[0] or r[0])
+
+    # ---- queue
+    def add_request(self, req: Request) -> None:
+        np = self._np
+        req.params.validate()
+        if not req.prompt_ids:
+            raise ValueError(f"request {req.req_id!r}: empty prompt")
+        if len(req.prompt_ids) >= self.config.max_model_len:
+            raise ValueError(f"request {req.req_id!r}: prompt of {len(req.prompt_ids)} tokens leaves no room "
+                             f"under max_model_len {self.config.max_model_len}")
+        bs = self.manager.block_size
+        need = (len(req.prompt_ids) + 1 + bs - 1) // bs
+        if any(need > p.num_blocks for p in self.manager.pools):
+            raise ValueError(f"request {req.req_id!r}: needs {need} pages, the pool has "
+                             f"{min(p.num_blocks for p in self.manager.pools)}")
+        h = self.manager.handle(req.req_id)
+        prompt = np.ascontiguousarray(req.prompt_ids, dtype=np.int32)
+        stops = np.ascontiguousarray(sorted(req.params.stop_token_ids), dtype=np.int32)
+        p = req.params
+        if self._lib.dh_sched_add(self._s, h, prompt.ctypes.data, prompt.size, int(min(p.max_tokens, 2 ** 31 - 1)),
+                                  int(p.min_tokens), int(bool(p.ignore_eos)), stops.ctypes.data if stops.size else None,
+                                  stops.size, int(p.prompt_logprobs is not None)):
+            raise ValueError(self._error())
+        req.status = RequestStatus.WAITING
+        self._reqs[h] = req
+
+    def _drop(self, h: int) -> None:
+        req = self._reqs.pop(h, None)
+        self._lib.dh_sched_forget(self._s, h)
+        if req is not None:
+            self.manager._forget_if_gone(req.req_id)
+
+    def abort(self, req_id: Hashable) -> Optional[Request]:
+        h = self.manager._ids.get(req_id)
+        if h is None or h not in self._reqs or not self._lib.dh_sched_abort(self._s, h):
+            return None
+        req = self._reqs[h]
+        req.status, req.finish_reason = RequestStatus.FINISHED, FinishReason.ABORT
+        self._drop(h)
+        return req
+
+    # ---- one step's decisions
+    def schedule_columns(self, lookahead: bool = False):
+        """(handles, start, num_tokens, samples, num_generated, preempted handles, finished handles): views of
+        buffers that the next call overwrites."""
+        c = self._counts
+        if self._lib.dh_sched_schedule(self._s, int(lookahead), self._cap, self._ids.ctypes.data, self._start.ctypes.data,
+                                       self._num.ctypes.data, self._smp.ctypes.data, self._gen.ctypes.data,
+                                       self._pre.ctypes.data, self._fin.ctypes.data, c.ctypes.data):
+            raise RuntimeError(self._error())
+        n, p, f = int(c[0]), int(c[1]), int(c[2])
+        return (self._ids[:n], self._start[:n], self._num[:n], self._smp[:n], self._gen[:n], self._pre[:p], self._fin[:f])
+
+    def schedule(self, lookahead: bool = False) -> SchedulerOutput:
+        ids, start, num, smp, gen, pre, fin = self.schedule_columns(lookahead)
+        out = SchedulerOutput()
+        for h in pre.tolist():
+            r = self._reqs[h]
+            r.num_computed, r.num_placeholders, r.status = 0, 0, RequestStatus.WAITING
+            r.num_preemptions += 1
+            out.preempted.append(r)
+        for h in fin.tolist():
+            r = self._reqs[h]
+            r.status, r.finish_reason = RequestStatus.FINISHED, FinishReason.LENGTH
+            out.finished.append(r)
+            self._drop(h)
+        for h, s, n, m, g in zip(ids.tolist(), start.tolist(), num.tolist(), smp.tolist(), gen.tolist()):
+            r = self._reqs[h]
+            r.status = RequestStatus.RUNNING
+            r.num_computed = s + n
+            if lookahead and m:
+                r.num_placeholders += 1
+            out.scheduled.append(ScheduledRequest(r, s, n, bool(m), g))
+        return out
+
+    # ---- after the step
+    def update_columns(self, handles, samples, tokens):
+        """The sampled tokens of a step's scheduled requests (int32 columns as ``schedule_columns`` gave them, with
+        the tokens); returns (handles that finished, reasons 1 = stop, 2 = length)."""
+        n = len(handles)
+        k = self._lib.dh_sched_update(self._s, n, handles.ctypes.data, samples.ctypes.data, tokens.ctypes.data,
+                                      self._done.ctypes.data, self._reason.ctypes.data)
+        return self._done[:k], self._reason[:k]
+
+    def update(self, step: SchedulerOutput, sampled: Dict[Hashable, int]) -> List[Request]:
+        np = self._np
+        n = len(step.scheduled)
+        ids = np.zeros(max(1, n), dtype=np.int64)
+        smp = np.zeros(max(1, n), dtype=np.int32)
+        tok = np.zeros(max(1, n), dtype=np.int32)
+        for k, s in enumerate(step.scheduled):
+            req = s.request
+            ids[k] = self.manager._ids.get(req.req_id, -1) if not req.finished else -1
+            if s.samples and not req.finished:
+                smp[k], tok[k] = 1, int(sampled[req.req_id])
+                req.output_ids.append(int(tok[k]))
+                if req.status == RequestStatus.RUNNING and req.num_placeholders > 0:
+                    req.num_placeholders -= 1
+        done_h, reasons = self.update_columns(ids[:n], smp[:n], tok[:n])
+        done = []
+        for h, why in zip(done_h.tolist(), reasons.tolist()):
+            req = self._reqs[h]
+            req.status, req.finish_reason = RequestStatus.FINISHED, self._REASONS[why]
+            done.append(req)
+            self._drop(h)
+        return done

@@ -2,11 +2,24 @@
 in the manner of the reference's Echo executor (crates/core/src/runner.rs:888-905).  No GPU."""
 import pytest
 
+import sys
+
 from dinfer_b200.cache.manager import CacheManager, GroupSpec
+from dinfer_b200.cache.native import NativeCacheManager
 from dinfer_b200.config.engine_config import EngineConfig
 from dinfer_b200.engine.request import FinishReason, Request, RequestStatus
-from dinfer_b200.engine.scheduler import Scheduler
+from dinfer_b200.engine.scheduler import NativeScheduler, Scheduler
 from dinfer_b200.sampling.params import SamplingParams
+
+
+@pytest.fixture(params=["python", "native"], autouse=True)
+def implementation(request, monkeypatch):
+    """Every test of this file runs twice: on the Python scheduler and cache manager, and on the C++ ones."""
+    if request.param == "native":
+        monkeypatch.setattr(sys.modules[__name__], "CacheManager", NativeCacheManager)
+        monkeypatch.setattr(sys.modules[__name__], "Scheduler", NativeScheduler)
+    return request.param
+
 
 
 def make(num_blocks=64, block_size=4, **kw):
