@@ -38,7 +38,7 @@ def library() -> ctypes.CDLL:
             "dh_can_allocate": (I, [P, L, I]), "dh_can_allocate_all": (I, [P, P, P, I]), "dh_allocate": (I, [P, L, I]),
             "dh_begin": (I, [P, L, P, I]), "dh_advance": (I, [P, L, I, P, I]), "dh_resolve": (I, [P, L, P, I]),
             "dh_free": (I, [P, L]), "dh_check_invariants": (I, [P]),
-            "dh_decode_plan_fill": (I, [P, P, I, I, P, P, P, I]), "dh_advance_many": (I, [P, P, P, I]),
+            "dh_decode_plan_fill": (I, [P, P, I, I, P, P, P, I, I]), "dh_advance_many": (I, [P, P, P, I]),
         }
         for name, (res, args) in sig.items():
             f = getattr(lib, name)
@@ -250,7 +250,7 @@ class NativeCacheManager:
 
     # ---- the packed plan of a decode-only step, written by the library from its own tables
     def fill_decode_plan(self, words: np.ndarray, bucket: int, width: int, reqs: Sequence[Hashable],
-                         tokens: Sequence[int], starts: Sequence[int]) -> int:
+                         tokens: Sequence[int], starts: Sequence[int], spare_state_slot: int = 0) -> int:
         """``words``: the plan's int32 words (a view of pinned memory), in the layout of
         ``PlanBuilder.layout(bucket, bucket, bucket, width)``.  Returns the words written."""
         n = len(reqs)
@@ -258,7 +258,7 @@ class NativeCacheManager:
         tk = np.asarray(tokens, dtype=np.int32)
         st = np.asarray(starts, dtype=np.int32)
         used = self._lib.dh_decode_plan_fill(self._h, words.ctypes.data, bucket, width, rs.ctypes.data, tk.ctypes.data,
-                                             st.ctypes.data, n)
+                                             st.ctypes.data, n, int(spare_state_slot))
         if used < 0:
             raise PoolError(_error(self._lib))
         return used

@@ -153,8 +153,11 @@ def ensure_built(names: Iterable[str], verbose: bool = True) -> Dict[str, str]:
     missing = [n for n in names if not os.path.isfile(library_path(n))]
     if missing:
         if verbose:
-            print(f"[dinfer_b200] compiling CUDA kernels for sm_100a: {', '.join(missing)}",
-                  file=sys.stderr, flush=True)
+            cuda = [n for n in missing if not LIBRARIES[n][0].endswith(".cpp")]
+            host = [n for n in missing if LIBRARIES[n][0].endswith(".cpp")]
+            what = "; ".join(x for x in ((f"CUDA kernels for sm_100a: {', '.join(cuda)}" if cuda else ""),
+                                         (f"host code: {', '.join(host)}" if host else "")) if x)
+            print(f"[dinfer_b200] compiling {what}", file=sys.stderr, flush=True)
         t0 = time.time()
         with ThreadPoolExecutor(max_workers=min(len(missing), os.cpu_count() or 4)) as pool:
             futs = {n: pool.submit(_compile, n, verbose) for n in missing}

@@ -37,6 +37,16 @@ __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, in
   }
 }
 
+// out[t, n] += bias[n]: the bias of a linear part (none of the Qwen3 dense model's products has one; a mixer
+// or feed-forward of another architecture may), added in 32-bit with one rounding
+template <typename T, typename TB>
+__global__ void add_bias_kernel(T* __restrict__ out, int64_t ld, const TB* __restrict__ bias, int n) {
+  pdl_enter();
+  T* row = out + (int64_t)blockIdx.x * ld;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x)
+    row[i] = from_f32<T>(to_f32<T>(row[i]) + to_f32<TB>(bias[i]));
+}
+
 // bfloat16 in pairs: 16 inputs (two 16-byte loads) -> 8 outputs (one 16-byte store) per thread
 __global__ void silu_mul_pairs_bf16_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
                                            int inter8, int64_t ldx, int inter) {
@@ -153,6 +163,20 @@ DINFER_API int dinfer_cast(const void* src, void* dst, int64_t n, int src_dtype,
     DINFER_DISPATCH_DTYPE(dst_dtype, TD, {
       cast_kernel<TS, TD><<<(int)blocks, 256, 0, stream>>>((const TS*)src, (TD*)dst, n);
       return cuda_status("cast");
+    }));
+  return 0;
+}
+
+// out [T, N] (row stride ld, act dtype) += bias [N] (bias dtype)
+DINFER_API int dinfer_add_bias(void* out, int64_t ld, const void* bias, int T, int N, int act_dtype, int bias_dtype,
+                               cudaStream_t stream) {
+  if (T < 0 || N <= 0 || ld < N) return refuse(DINFER_BAD_ARGUMENT, "add_bias: bad sizes T=%d N=%d", T, N);
+  if (T == 0) return 0;
+  dim3 grid(T, (N + 1023) / 1024 > 64 ? 64 : (N + 1023) / 1024);
+  DINFER_DISPATCH_DTYPE(act_dtype, TA,
+    DINFER_DISPATCH_DTYPE(bias_dtype, TB, {
+      launch_pdl(add_bias_kernel<TA, TB>, grid, dim3(256), 0, stream, (TA*)out, ld, (const TB*)bias, N);
+      return cuda_status("add_bias");
     }));
   return 0;
 }

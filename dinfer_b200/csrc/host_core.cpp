@@ -418,9 +418,9 @@ DH_API int dh_check_invariants(void* mp) {
 // ---- the packed plan of a decode-only step (the layout of engine/batch.py: PlanBuilder.layout for T = B = R =
 // bucket): ids, pos, rows, cu, seq, sslots, fresh, then per group slot and table, each aligned to 4 words.
 // `words` points at the plan's int32 words (pinned host memory), written whole: the live rows from the requests'
-// tables, the rest as dummy rows (token 0, position 0, no slot, no pages).
+// tables, the rest as dummy rows (token 0, position 0, no slot, no pages, the spare state slot).
 DH_API int dh_decode_plan_fill(void* mp, int32_t* words, int bucket, int width, const int64_t* rs, const int32_t* tokens,
-                               const int32_t* starts, int n) {
+                               const int32_t* starts, int n, int spare_state_slot) {
   auto* m = static_cast<Manager*>(mp);
   if (n > bucket) return fail("more requests than the graph's bucket");
   auto align = [](int x) { return (x + 3) / 4 * 4; };
@@ -457,7 +457,7 @@ DH_API int dh_decode_plan_fill(void* mp, int32_t* words, int bucket, int width, 
     }
   }
   for (int i = n; i < bucket; ++i) {
-    ids[i] = 0; pos[i] = 0; seq[i] = 1; sslots[i] = 0; fresh[i] = 0;
+    ids[i] = 0; pos[i] = 0; seq[i] = 1; sslots[i] = spare_state_slot; fresh[i] = 0;
     for (int g = 0; g < ng; ++g) {
       slot[g][i] = -1;
       std::fill(tab[g] + (size_t)i * width, tab[g] + (size_t)(i + 1) * width, -1);

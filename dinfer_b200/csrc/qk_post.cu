@@ -45,7 +45,7 @@ template <typename TA, typename TW, bool VEC8>
 __global__ void __launch_bounds__(WARPS * 32)
 qk_post_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ positions,
                const TW* __restrict__ q_weight, const TW* __restrict__ k_weight, float eps,
-               const float* __restrict__ cos_sin, int rot,
+               const float* __restrict__ cos_sin, int rot, int interleaved,
                TA* __restrict__ cache, const int* __restrict__ slots, int block_size,
                int H, int Hkv, int D) {
   __shared__ __align__(16) float sm[WARPS][MAX_D];
@@ -103,8 +103,14 @@ qk_post_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ positio
       const int e = e0 + j;
       float v = xs[e];
       if (rotate && e < rot) {
-        if (e < half) v = v * cs[e] - xs[e + half] * cs[half + e];
-        else          v = v * cs[e - half] + xs[e - half] * cs[e];
+        if (interleaved) {                                    // pairs (2i, 2i + 1), angle i
+          const int i = e >> 1;
+          v = (e & 1) ? v * cs[i] + xs[e - 1] * cs[half + i] : v * cs[i] - xs[e + 1] * cs[half + i];
+        } else if (e < half) {                                // pairs (i, i + rot/2), angle i
+          v = v * cs[e] - xs[e + half] * cs[half + e];
+        } else {
+          v = v * cs[e - half] + xs[e - half] * cs[e];
+        }
       }
       r[j] = v;
     }
@@ -332,11 +338,12 @@ DINFER_DEFINE_LAST_ERROR()
 // qkv [T, >= (H+2Hkv)*D] act dtype with row stride ld, laid out q heads | k heads | v heads.
 // positions [T] int32; q_weight/k_weight [D] or null; cos_sin [max_pos, rot] f32 (cos | sin) or null;
 // cache (act dtype) or null; slots [T] int32 (negative = do not write).
-DINFER_API int dinfer_qk_post(void* qkv, int64_t ld, const int* positions, const void* q_weight,
-                              const void* k_weight, float eps, const float* cos_sin, int rot,
-                              void* cache, const int* slots, int block_size,
-                              int T, int H, int Hkv, int D, int act_dtype, int w_dtype,
-                              cudaStream_t stream) {
+// interleaved = 0: the rotation pairs element i with i + rot/2 (neox); 1: element 2i with 2i + 1.
+DINFER_API int dinfer_qk_post_styled(void* qkv, int64_t ld, const int* positions, const void* q_weight,
+                                     const void* k_weight, float eps, const float* cos_sin, int rot, int interleaved,
+                                     void* cache, const int* slots, int block_size,
+                                     int T, int H, int Hkv, int D, int act_dtype, int w_dtype,
+                                     cudaStream_t stream) {
   if (T < 0 || H <= 0 || Hkv < 0 || D <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "qk_post: bad sizes T=%d H=%d Hkv=%d D=%d", T, H, Hkv, D);
   if (D > MAX_D) return refuse(DINFER_BAD_ARGUMENT, "qk_post: head_dim %d above the limit %d", D, MAX_D);
@@ -354,7 +361,7 @@ DINFER_API int dinfer_qk_post(void* qkv, int64_t ld, const int* positions, const
                            !(reinterpret_cast<uintptr_t>(cache) & 31) && !(reinterpret_cast<uintptr_t>(q_weight) & 31) &&
                            !(reinterpret_cast<uintptr_t>(k_weight) & 31) && !(reinterpret_cast<uintptr_t>(cos_sin) & 31);
       if constexpr (sizeof(TA) == 2) {
-        if (aligned && (!cos_sin || rot == D) && D == 128) {
+        if (aligned && !interleaved && (!cos_sin || rot == D) && D == 128) {
           const int hp = T <= FEW_TOKENS ? 1 : 3;
           const dim3 half_grid(T, (heads + WARPS * 2 * hp - 1) / (WARPS * 2 * hp));
           launch_pdl(hp == 1 ? qk_post_half_warp_kernel<TW, 1> : qk_post_half_warp_kernel<TW, 3>, half_grid, dim3(WARPS * 32), 0,
@@ -363,7 +370,7 @@ DINFER_API int dinfer_qk_post(void* qkv, int64_t ld, const int* positions, const
           return cuda_status("qk_post");
         }
       }
-      if (aligned && (!cos_sin || rot == D) && (D == 32 || D == 64 || D == 128 || D == 256)) {
+      if (aligned && !interleaved && (!cos_sin || rot == D) && (D == 32 || D == 64 || D == 128 || D == 256)) {
         const dim3 lanes_grid(T, (heads + WARPS * HPW - 1) / (WARPS * HPW));
         launch_lanes<TA, TW>(lanes_grid, stream, (TA*)qkv, ld, positions, (const TW*)q_weight, (const TW*)k_weight, eps,
                              cos_sin, (TA*)cache, slots, block_size, H, Hkv, D);
@@ -374,13 +381,22 @@ DINFER_API int dinfer_qk_post(void* qkv, int64_t ld, const int* positions, const
                         !(reinterpret_cast<uintptr_t>(cache) & 31);
       if (vec8)
         qk_post_kernel<TA, TW, true><<<grid, WARPS * 32, 0, stream>>>(
-            (TA*)qkv, ld, positions, (const TW*)q_weight, (const TW*)k_weight, eps, cos_sin, rot,
+            (TA*)qkv, ld, positions, (const TW*)q_weight, (const TW*)k_weight, eps, cos_sin, rot, interleaved,
             (TA*)cache, slots, block_size, H, Hkv, D);
       else
         qk_post_kernel<TA, TW, false><<<grid, WARPS * 32, 0, stream>>>(
-            (TA*)qkv, ld, positions, (const TW*)q_weight, (const TW*)k_weight, eps, cos_sin, rot,
+            (TA*)qkv, ld, positions, (const TW*)q_weight, (const TW*)k_weight, eps, cos_sin, rot, interleaved,
             (TA*)cache, slots, block_size, H, Hkv, D);
       return cuda_status("qk_post");
     }));
   return 0;
+}
+
+DINFER_API int dinfer_qk_post(void* qkv, int64_t ld, const int* positions, const void* q_weight,
+                              const void* k_weight, float eps, const float* cos_sin, int rot,
+                              void* cache, const int* slots, int block_size,
+                              int T, int H, int Hkv, int D, int act_dtype, int w_dtype,
+                              cudaStream_t stream) {
+  return dinfer_qk_post_styled(qkv, ld, positions, q_weight, k_weight, eps, cos_sin, rot, 0, cache, slots, block_size, T, H,
+                               Hkv, D, act_dtype, w_dtype, stream);
 }

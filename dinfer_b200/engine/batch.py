@@ -49,11 +49,12 @@ class PlanBuilder:
     RING = 4
 
     def __init__(self, manager: CacheManager, device, max_tokens: int, max_reqs: int, max_blocks: int,
-                 max_positions: Optional[int] = None):
+                 max_positions: Optional[int] = None, spare_state_slot: int = 0):
         self.manager = manager
         self.device = device
         self.max_blocks = max_blocks
         self.max_positions = max_positions          # rows of the position table (None: not known here)
+        self.spare_state_slot = spare_state_slot    # the state slot of rows without a request (no request holds it)
         self.max_tokens, self.max_reqs = max_tokens, max_reqs
         self.capacity = self.words(max_tokens, max_reqs, max_tokens, max_blocks)
         on_gpu = torch.device(device).type == "cuda"
@@ -200,7 +201,7 @@ class PlanBuilder:
                 sl[cu[j]:cu[j + 1]] = np.where(blk >= 0, blk * bs + p % bs, -1)
             tables.append(tab)
             slot_maps.append(sl)
-        sslots = np.zeros(B, dtype=np.int32)
+        sslots = np.full(B, self.spare_state_slot, dtype=np.int32)
         fresh = np.zeros(B, dtype=np.int32)
         for j, (i, n) in enumerate(slots):
             if i >= 0:
@@ -263,6 +264,7 @@ class DecodePlan:
         f("rows")[:] = np.arange(bucket, dtype=np.int32)
         f("cu")[:] = np.arange(bucket + 1, dtype=np.int32)
         f("seq")[:] = 1
+        f("sslots")[:] = builder.spare_state_slot
         for g in range(self.ng):
             f(f"slot{g}")[:] = -1
             f(f"tab{g}")[:] = -1
@@ -303,7 +305,8 @@ class DecodePlan:
             # the cache manager whose tables live in C++ writes the plan itself, straight into the pinned buffer
             k = b._next_turn()
             words = b._host[k].numpy()[:self.words]
-            m.fill_decode_plan(words, self.bucket, width, [e.req_id for e in entries], [e.tokens[0] for e in entries], starts)
+            m.fill_decode_plan(words, self.bucket, width, [e.req_id for e in entries], [e.tokens[0] for e in entries], starts,
+                               b.spare_state_slot)
             if VALIDATE_PLANS:
                 self.shadow[:] = words
                 self._check()
@@ -335,7 +338,7 @@ class DecodePlan:
             self._ids[i] = 0
             self._pos[i] = 0
             self._seq[i] = 1
-            self._sslots[i] = 0
+            self._sslots[i] = b.spare_state_slot
             self._fresh[i] = 0
             for g in range(self.ng):
                 self._tab[g][i] = -1

@@ -136,7 +136,8 @@ class ModelRunner:
         self.plan = PlanBuilder(self.manager, self.device,
                                 max_tokens=engine.max_num_batched_tokens + engine.max_num_seqs,
                                 max_reqs=engine.max_num_seqs + self.PROMPT_PLACES[-1],
-                                max_blocks=self.max_blocks_per_seq, max_positions=self.spec.max_positions)
+                                max_blocks=self.max_blocks_per_seq, max_positions=self.spec.max_positions,
+                                spare_state_slot=engine.max_num_seqs)
         # the tokens the last step sampled stay here (a fixed address, so that captured graphs can read it):
         # a step launched before the host has read them names them by row (see StepEntry.tokens)
         self.sampled = torch.zeros(max(1, engine.max_num_seqs), dtype=torch.int32, device=self.device)
@@ -204,7 +205,8 @@ class ModelRunner:
                                  dtype=self.act_dtype, device=self.device)
                 self.bindings.append(CacheBinding(kv=kv, group=entry_group[i], write=True))
             elif isinstance(n, StateNeed):
-                st = torch.zeros((e.max_num_seqs,) + tuple(n.shape), dtype=n.dtype, device=self.device)
+                # one slot more than requests: the rows that pad a captured batch point at it
+                st = torch.zeros((e.max_num_seqs + 1,) + tuple(n.shape), dtype=n.dtype, device=self.device)
                 self.bindings.append(CacheBinding(state=st, group=-1, write=True))
             else:
                 self.bindings.append(CacheBinding())
@@ -261,11 +263,10 @@ class ModelRunner:
     def _init_graphs(self) -> None:
         """Decode-only steps (every request brings one token) run as a CUDA graph per batch-size
         bucket, the batch padded with dummy rows up to the bucket (models/qwen3/src/executor.rs:993-1023,
-        crates/layers/src/exec.rs:83-87).  Off for models with per-request state: a dummy row has no
-        state slot of its own."""
+        crates/layers/src/exec.rs:83-87).  A model with per-request state replays graphs too if every mixer with
+        state says its forward can be captured (``Mixer.graph_capturable``); the dummy rows share a spare state slot."""
         e = self.engine
-        has_state = any(isinstance(n, StateNeed) for n in self.model.cache_needs())
-        self._graph_ok = bool(e.enable_cuda_graph) and not has_state
+        self._graph_ok = bool(e.enable_cuda_graph) and self.model.graph_capturable()
         b, buckets = 1, []
         while b < e.max_num_seqs:
             buckets.append(b)

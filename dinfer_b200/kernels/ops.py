@@ -105,6 +105,18 @@ def silu_mul(x: torch.Tensor, out: torch.Tensor, pairs: bool = False) -> torch.T
     return out
 
 
+def add_bias(out: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """out[t, :] += bias, in place (a view with a row stride is fine)."""
+    require_cuda(out, bias)
+    _rows_contiguous(out, "add_bias")
+    if out.dim() != 2 or bias.dim() != 1 or bias.numel() != out.shape[1] or not bias.is_contiguous():
+        raise KernelError("add_bias: out [T, N], bias [N]")
+    lib, f = _fn("elementwise", "dinfer_add_bias", [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(out), out.stride(0), ptr(bias), out.shape[0], out.shape[1], dtype_code(out.dtype),
+                 dtype_code(bias.dtype), stream_handle()), "add_bias")
+    return out
+
+
 def cast(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
     require_cuda(src, dst)
     if not src.is_contiguous() or not dst.is_contiguous() or src.numel() != dst.numel():
@@ -137,8 +149,9 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tenso
 def qk_post(qkv: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
             eps: float, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
             cos_sin: Optional[torch.Tensor], cache: Optional[torch.Tensor],
-            slots: Optional[torch.Tensor], block_size: int) -> None:
-    """Per-head RMSNorm of q and k, neox rotation, write-back in place, k and v into the paged cache."""
+            slots: Optional[torch.Tensor], block_size: int, interleaved: bool = False) -> None:
+    """Per-head RMSNorm of q and k, rotation (element i with i + rot/2, or with ``interleaved`` element 2i with
+    2i + 1), write-back in place, k and v into the paged cache."""
     require_cuda(qkv, positions, q_weight, k_weight, cos_sin, cache, slots)
     _rows_contiguous(qkv, "qk_post")
     T = qkv.shape[0]
@@ -162,11 +175,11 @@ def qk_post(qkv: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_h
         if tuple(cache.shape[1:]) != (2, num_kv_heads, block_size, head_dim):
             raise KernelError(f"qk_post: cache shape {tuple(cache.shape)} is not [blocks, 2, {num_kv_heads}, "
                               f"{block_size}, {head_dim}]")
-    lib, f = _fn("qk_post", "dinfer_qk_post",
-                 [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p,
+    lib, f = _fn("qk_post", "dinfer_qk_post_styled",
+                 [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p,
                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     check(lib, f(ptr(qkv), qkv.stride(0), ptr(positions), ptr(q_weight), ptr(k_weight), float(eps),
-                 ptr(cos_sin), rot, ptr(cache), ptr(slots), block_size, T, num_heads, num_kv_heads,
+                 ptr(cos_sin), rot, int(bool(interleaved)), ptr(cache), ptr(slots), block_size, T, num_heads, num_kv_heads,
                  head_dim, dtype_code(qkv.dtype), dtype_code(w_dt), stream_handle()), "qk_post")
 
 

@@ -73,6 +73,12 @@ class DecoderModel:
             out.append(None if e.cache_from is not None else self.blocks[e.layer].mixer.cache_need())
         return out
 
+    def graph_capturable(self) -> bool:
+        """Whether a step of this model can be captured in a CUDA graph: every mixer that keeps per-request state
+        must say so (``Mixer.graph_capturable``); mixers without state always can."""
+        from ..parts.base import StateNeed
+        return all(not isinstance(b.mixer.cache_need(), StateNeed) or bool(b.mixer.graph_capturable) for b in self.blocks)
+
     def can_split_norms(self, rows: int) -> bool:
         """Whether some norm of the model can be taken apart for steps of this many rows."""
         from ..parts.block import norm_comes_apart

@@ -25,8 +25,9 @@ from .spec import PartSpec, TensorDecl
 @MIXERS.register("gqa_attention")
 class GQAttention(Mixer):
     """params: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``qk_norm`` (bool), ``eps``,
-    ``position`` (a PartSpec), optional ``window``, ``scale``, and the tensor names ``q_proj``,
-    ``k_proj``, ``v_proj``, ``o_proj``, ``q_norm``, ``k_norm`` (after the prefix)."""
+    ``position`` (a PartSpec), optional ``window``, ``scale``, ``bias`` (bool: the four projections have a bias,
+    named like their weights with ``.bias``), and the tensor names ``q_proj``, ``k_proj``, ``v_proj``, ``o_proj``,
+    ``q_norm``, ``k_norm`` (after the prefix)."""
 
     def __init__(self, params, env: BuildEnv, prefix=""):
         super().__init__(params, env, prefix)
@@ -41,6 +42,7 @@ class GQAttention(Mixer):
         self.eps = float(p.get("eps", 1e-6))
         self.window = p.get("window")
         self.scale = float(p.get("scale", 1.0 / math.sqrt(self.D)))
+        self.bias = bool(p.get("bias", False))
         pos: PartSpec = p.get("position") or PartSpec("none")
         self.position = build_part(POSITION_ENCODINGS, pos, env, prefix)
         n = lambda key, default: prefix + p.get(key, default)
@@ -59,14 +61,24 @@ class GQAttention(Mixer):
              TensorDecl(self.names["v"], (Hkv * D, h)), TensorDecl(self.names["o"], (h, H * D))]
         if self.qk_norm:
             d += [TensorDecl(self.names["qn"], (D,), init="ones"), TensorDecl(self.names["kn"], (D,), init="ones")]
+        if self.bias:
+            d += [TensorDecl(self._bias_name(x), (n,)) for x, n in (("q", H * D), ("k", Hkv * D), ("v", Hkv * D), ("o", h))]
         return d
+
+    def _bias_name(self, which: str) -> str:
+        name = self.names[which]
+        return (name[:-len(".weight")] if name.endswith(".weight") else name) + ".bias"
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         q, k, v = (tensors[self.names[x]] for x in ("q", "k", "v"))
         dt = torch.float32 if any(t.dtype == torch.float32 for t in (q, k, v)) else q.dtype
         # q, k, v rows stacked once at load into one [(H + 2 Hkv) D, h] matrix (model.rs:141-164)
-        self.qkv = Linear(torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0))
-        self.o = Linear(tensors[self.names["o"]])
+        qkv_bias = o_bias = None
+        if self.bias:
+            qkv_bias = torch.cat([tensors[self._bias_name(x)].to(dt) for x in ("q", "k", "v")])
+            o_bias = tensors[self._bias_name("o")]
+        self.qkv = Linear(torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0), qkv_bias)
+        self.o = Linear(tensors[self.names["o"]], o_bias)
         if self.qk_norm:
             self.q_norm_w = tensors[self.names["qn"]].contiguous()
             self.k_norm_w = tensors[self.names["kn"]].to(self.q_norm_w.dtype).contiguous()
@@ -96,7 +108,7 @@ class GQAttention(Mixer):
         table = self.position.fused_table()
         if self.position.fused:
             ops.qk_post(qkv, ctx.positions, H, Hkv, D, self.eps, self.q_norm_w, self.k_norm_w, table,
-                        kv, g.slot_mapping, g.block_size)
+                        kv, g.slot_mapping, g.block_size, interleaved=getattr(self.position, "interleaved", False))
         else:
             if self.qk_norm:
                 ops.qk_post(qkv, ctx.positions, H, Hkv, D, self.eps, self.q_norm_w, self.k_norm_w, None,

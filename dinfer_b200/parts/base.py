@@ -140,6 +140,13 @@ class Mixer(Part):
     norm))`` adds the part's output into the residual itself and returns the ``HalfNormed`` input of the
     next part instead of the output.  A part without them always gets and gives plain tensors."""
 
+    # A mixer with per-request state says here whether its forward can be captured in a CUDA graph: it must read the
+    # step's state slots and fresh flags from the device tensors of the context (``ctx.state_slots``,
+    # ``ctx.state_fresh``, ``ctx.cu_seqlens``), never from their host copies, and take rows without a request (the
+    # padding of a captured batch) in its stride: those carry the spare slot ``cache.state.shape[0] - 1``, which no
+    # request ever holds.  Mixers without state are always capturable.
+    graph_capturable = False
+
     def cache_need(self):
         return None
 

@@ -34,20 +34,25 @@ TC_MIN_GATED_PROMPT_TOKENS = 512
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor):
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        """``bias`` [out] is added behind the product by a kernel of its own (the Qwen3 dense model has none; with
+        one, the fused epilogues (gate, norm halves) step aside for the plain product)."""
         if weight.dim() != 2:
             raise ValueError("a linear weight is 2-D [out, in]")
         self.weight = weight.contiguous()
         self.out_features, self.in_features = weight.shape
+        if bias is not None and tuple(bias.shape) != (self.out_features,):
+            raise ValueError(f"a bias of {tuple(bias.shape)} does not fit {self.out_features} outputs")
+        self.bias = None if bias is None else bias.contiguous()
 
     def kernel_libraries(self):
-        return ["gemm_f32"] if self.weight.dtype == torch.float32 else ["gemm_tc"]
+        return (["gemm_f32"] if self.weight.dtype == torch.float32 else ["gemm_tc"]) + (["elementwise"] if self.bias is not None else [])
 
     def fuses_gate(self, x: torch.Tensor) -> bool:
         """Whether ``gated_pairs`` runs as one kernel for these rows: the tcgen05 product with the gate in its
         epilogue, for decode steps and for prompt portions that are long enough."""
         rows = x.shape[0]
-        return (x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16
+        return (self.bias is None and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16
                 and (rows <= TC_MAX_DECODE_TOKENS or rows >= TC_MIN_GATED_PROMPT_TOKENS)
                 and self.out_features % 2 == 0 and gemm_ops.supported(x, self.weight))
 
@@ -55,7 +60,7 @@ class Linear:
         """Whether this product can take one half of an RMSNorm for ``rows`` rows (the decode product with its
         residual or row-scale epilogue): bfloat16 throughout and rows that TMA can address."""
         w = self.weight
-        return (act_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < rows <= TC_MAX_DECODE_TOKENS
+        return (self.bias is None and act_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < rows <= TC_MAX_DECODE_TOKENS
                 and self.in_features % 8 == 0 and self.out_features % 8 == 0 and w.data_ptr() % 16 == 0)
 
     def gated_pairs(self, x) -> torch.Tensor:
@@ -85,6 +90,10 @@ class Linear:
             if out is None:
                 out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or x.xw.dtype, device=x.xw.device)
             return gemm_ops.gemm_tc(x.xw, self.weight, out, row_scale=(x.sums, x.parts, x.size, x.eps))
+        out = self._product(x, out_dtype, out)
+        return out if self.bias is None else ops.add_bias(out, self.bias)
+
+    def _product(self, x: torch.Tensor, out_dtype: Optional[torch.dtype], out: Optional[torch.Tensor]) -> torch.Tensor:
         out_dtype = out_dtype or x.dtype
         if out is None:
             out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype, device=x.device)

@@ -97,6 +97,73 @@ def test_attention_part_in_two_portions(dt, window):
     assert torch.allclose(got, want, **t)
 
 
+def plain_attention_general(x, W, p, Hq, Hkv, D, eps, theta, rot, style, factor, bias, qk_norm):
+    """The attention block of plain_model with the options Qwen3 does not use: biases on the four projections, a
+    rotation of the first ``rot`` elements only, in (2i, 2i + 1) pairs, at positions divided by ``factor``."""
+    T = x.shape[0]
+    lin = lambda name, v: v @ W[p + name + ".weight"].T + (W[p + name + ".bias"] if bias else 0.0)
+    q, k, v = lin("q_proj", x).reshape(T, Hq, D), lin("k_proj", x).reshape(T, Hkv, D), lin("v_proj", x).reshape(T, Hkv, D)
+    if qk_norm:
+        q, k = P.rms_norm(q, W[p + "q_norm.weight"], eps), P.rms_norm(k, W[p + "k_norm.weight"], eps)
+    cos, sin = P.rope_cos_sin(torch.arange(T, dtype=torch.float64) / factor, rot, theta)
+
+    def turn(t):
+        head, rest = t[..., :rot], t[..., rot:]
+        if style == "neox":
+            return torch.cat([P.rope_neox(head, cos, sin), rest], -1)
+        a, b = head[..., 0::2], head[..., 1::2]
+        c, s_ = cos[:, None, :], sin[:, None, :]
+        out = torch.stack([a * c - b * s_, b * c + a * s_], -1).flatten(-2)
+        return torch.cat([out, rest], -1)
+
+    o = P.causal_gqa_attention(turn(q), turn(k), v, D ** -0.5)
+    return lin("o_proj", o.reshape(T, Hq * D))
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("D,rot,style,factor,bias,qk_norm", [(16, 16, "interleaved", 1.0, False, True),
+                                                             (32, 16, "neox", 4.0, True, False),
+                                                             (64, 32, "interleaved", 2.0, True, True),
+                                                             (128, 128, "neox", 1.0, True, True)])
+def test_attention_part_with_biases_and_other_rotations(dt, D, rot, style, factor, bias, qk_norm):
+    """What the attention part takes beyond the Qwen3 dense model's use of it, all as parameters: a bias on the four
+    projections, no head norm, a rotation of a part of the head, in interleaved pairs, at scaled positions.  A
+    sequence in portions of 9 + 1 + 7 tokens against the plain formula over the whole of it."""
+    from dinfer_b200.cache.manager import CacheManager, GroupSpec
+    from dinfer_b200.engine.batch import PlanBuilder, StepEntry
+    from dinfer_b200.parts.base import MIXERS, CacheBinding
+    from dinfer_b200.parts.spec import PartSpec
+    import dinfer_b200.models.decoder  # noqa: F401
+    h, Hq, Hkv, bs = 80, 4, 2, 8
+    g = torch.Generator().manual_seed(D + rot)
+    pos = PartSpec("rope", {"head_dim": D, "rotary_dim": rot, "theta": 3000.0, "max_positions": 64, "style": style,
+                            "scaling_factor": factor})
+    mixer = MIXERS.get("gqa_attention")({"num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D, "qk_norm": qk_norm,
+                                         "eps": 1e-5, "bias": bias, "position": pos}, env(h, dt, 64), "a.")
+    names = [d.name for d in mixer.declare()]
+    assert ("a.q_proj.bias" in names) == bias and ("a.o_proj.bias" in names) == bias and ("a.q_norm.weight" in names) == qk_norm
+    W = {}
+    for d in mixer.declare():
+        W[d.name] = ((1 + 0.1 * torch.randn(d.shape, generator=g)) if d.init == "ones"
+                     else torch.randn(d.shape, generator=g) * (0.3 if d.name.endswith(".bias") else 0.12)).to(dt)
+    mixer.bind({k: v.cuda() for k, v in W.items()})
+    x = torch.randn(17, h, generator=g).to(dt)
+    kv = torch.zeros(8, 2, Hkv, bs, D, dtype=dt, device="cuda")
+    m = CacheManager([GroupSpec()], bs, 8, 2)
+    pb = PlanBuilder(m, "cuda", 64, 2, 8)
+    outs = []
+    for lo, hi in ((0, 9), (9, 10), (10, 17)):
+        assert m.allocate("r", hi)
+        _, _, ctx = pb.build([StepEntry("r", [0] * (hi - lo), [])], [lo])
+        outs.append(mixer.forward(x[lo:hi].cuda(), ctx, CacheBinding(kv=kv, group=0, write=True)))
+        m.advance("r", hi)
+    got = torch.cat(outs).double().cpu()
+    want = plain_attention_general(x.double(), {k: v.double() for k, v in W.items()}, "a.", Hq, Hkv, D, 1e-5, 3000.0,
+                                   rot, style, factor, bias, qk_norm)
+    t = dict(atol=2e-5, rtol=1e-4) if dt == torch.float32 else dict(atol=5e-2, rtol=5e-2)
+    assert torch.allclose(got, want, **t), float((got - want).abs().max())
+
+
 # ---------------------------------------------------------------- a toy architecture, defined here
 
 def register_toy():
@@ -384,3 +451,136 @@ def test_toy_routed_feed_forward_and_other_position_encoding(tmp_path):
         unregister_architecture("ToyRoutedForTest")
         FEED_FORWARDS.unregister("toy_routed")
         POSITION_ENCODINGS.unregister("toy_decay")
+
+
+# ------------------------------------------- a third toy: a mixer with state whose steps replay CUDA graphs
+
+def register_toy_state_graph():
+    from dinfer_b200.config.registry import register_architecture
+    from dinfer_b200.parts.base import MIXERS, Mixer, StateNeed
+    from dinfer_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorDecl
+
+    class RunningMeanOnDevice(Mixer):
+        """y_t = Wo mean_{j<=t}(Wi x_j) again, but driven by the context's DEVICE tensors only (request offsets, state
+        slots, fresh flags), so that a step can be captured once and replayed with other requests in its rows; rows
+        without a request carry the spare slot, which is read and written like any other and never looked at."""
+        graph_capturable = True
+
+        def __init__(self, params, env, prefix=""):
+            super().__init__(params, env, prefix)
+            self.d, self.h = int(params["state_size"]), env.hidden_size
+
+        def declare(self):
+            return [TensorDecl(self.prefix + "mix.in.weight", (self.d, self.h)),
+                    TensorDecl(self.prefix + "mix.out.weight", (self.h, self.d))]
+
+        def bind(self, tensors):
+            self.wi = tensors[self.prefix + "mix.in.weight"].float()
+            self.wo = tensors[self.prefix + "mix.out.weight"].float()
+
+        def cache_need(self):
+            return StateNeed((self.d + 1,), torch.float32)
+
+        def forward(self, x, ctx, cache):
+            T, B, d = x.shape[0], ctx.num_reqs, self.d
+            cu = ctx.cu_seqlens.long()
+            start, end = cu[:B], cu[1:B + 1]
+            slots = ctx.state_slots.long()
+            v = x.float() @ self.wi.T
+            tok = torch.arange(T, device=x.device)
+            req = torch.bucketize(tok, end, right=True).clamp(max=B - 1)         # the request of every token
+            c = torch.cumsum(v, 0)
+            before = torch.where((start > 0)[:, None], c[(start - 1).clamp(min=0)], torch.zeros_like(c[:1]))
+            st = cache.state.index_select(0, slots) * (1.0 - ctx.state_fresh.float())[:, None]
+            sums = c - before[req] + st[req, :d]
+            counts = st[req, d] + (tok - start[req] + 1).float()
+            out = ((sums / counts[:, None]) @ self.wo.T).to(x.dtype)
+            last = (end - 1).clamp(min=0)
+            new = torch.cat([sums[last], counts[last, None]], 1)
+            new = torch.where((end > start)[:, None], new, st)                      # a place without tokens keeps its state
+            cache.state.index_copy_(0, slots, new)
+            return out
+
+    MIXERS.register("toy_running_mean_device", RunningMeanOnDevice, replace=True)
+
+    def spec(c):
+        h, Hq, Hkv, D = c["hidden_size"], c["heads"], c["kv_heads"], c["head_dim"]
+        pos = PartSpec("rope", {"head_dim": D, "theta": c["theta"], "max_positions": c["max_positions"], "style": "interleaved"})
+        norm = lambda name: PartSpec("rmsnorm", {"size": h, "eps": c["eps"], "weight": name})
+        ffn = PartSpec("swiglu", {"intermediate_size": c["inter"]})
+        layers = (
+            LayerSpec("layers.0.", "prenorm_residual", PartSpec("toy_running_mean_device", {"state_size": c["state_size"]}),
+                      norm("n1.weight"), ffn, norm("n2.weight")),
+            LayerSpec("layers.1.", "prenorm_residual",
+                      PartSpec("gqa_attention", {"num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D, "qk_norm": True,
+                                                 "eps": c["eps"], "position": pos, "bias": True}),
+                      norm("n1.weight"), ffn, norm("n2.weight")),
+        )
+        return ModelSpec("ToyStateGraphForTest", h, c["vocab_size"], c["max_positions"], "embed.weight", layers,
+                         (ScheduleEntry(0), ScheduleEntry(1)), norm("final.weight"), "head.weight", False)
+
+    register_architecture("ToyStateGraphForTest", lambda d: dict(d), spec, replace=True)
+
+
+TOY_STATE = dict(architectures=["ToyStateGraphForTest"], vocab_size=111, hidden_size=48, heads=4, kv_heads=2, head_dim=16,
+                 inter=64, state_size=20, theta=9000.0, eps=1e-5, max_positions=128)
+
+
+def toy_state_plain_logits(W, c, ids):
+    W = {k: v.double() for k, v in W.items()}
+    T, Hq, Hkv, D = len(ids), c["heads"], c["kv_heads"], c["head_dim"]
+    x = W["embed.weight"][torch.tensor(ids)]
+    p = "layers.0."
+    hdn = P.rms_norm(x, W[p + "n1.weight"], c["eps"])
+    a = (torch.cumsum(hdn @ W[p + "mix.in.weight"].T, 0) / torch.arange(1, T + 1)[:, None]) @ W[p + "mix.out.weight"].T
+    x = x + a
+    x = x + P.swiglu_mlp(P.rms_norm(x, W[p + "n2.weight"], c["eps"]), W[p + "gate_proj.weight"], W[p + "up_proj.weight"],
+                         W[p + "down_proj.weight"])
+    p = "layers.1."
+    hdn = P.rms_norm(x, W[p + "n1.weight"], c["eps"])
+    x = x + plain_attention_general(hdn, W, p, Hq, Hkv, D, c["eps"], c["theta"], D, "interleaved", 1.0, True, True)
+    x = x + P.swiglu_mlp(P.rms_norm(x, W[p + "n2.weight"], c["eps"]), W[p + "gate_proj.weight"], W[p + "up_proj.weight"],
+                         W[p + "down_proj.weight"])
+    return P.rms_norm(x, W["final.weight"], c["eps"]) @ W["head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_replays_cuda_graphs(tmp_path, dtype):
+    """A model whose first mixer keeps per-request state (and says its forward can be captured), whose attention has
+    biases and an interleaved rotation: registered here, run with CUDA graphs ON.  Decode-only steps replay a graph
+    per bucket (dummy rows on the spare state slot), steps with prompt portions replay theirs; requests join, finish
+    and hand their state slots on; every last-token logit against the plain formula."""
+    from dinfer_b200.config.engine_config import EngineConfig
+    from dinfer_b200.engine.batch import StepEntry
+    from dinfer_b200.engine.runner import ModelRunner
+    register_toy_state_graph()
+    try:
+        tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+        d = H.make_model_dir(str(tmp_path / "toy"), TOY_STATE, 7, 0.08, 0.1, tdt)
+        W = H.load_plain_weights(d)
+        rng = random.Random(12)
+        names = [f"r{i}" for i in range(9)]
+        steps, lengths = H.schedule_rolling(names, [9, 6], 5)
+        tokens = {r: H.random_tokens(rng, n, TOY_STATE["vocab_size"]) for r, n in lengths.items()}
+        want = {r: toy_state_plain_logits(W, TOY_STATE, t).numpy() for r, t in tokens.items()}
+        r = ModelRunner.from_dir(d, EngineConfig(max_model_len=64, max_num_seqs=8, max_num_batched_tokens=16, num_blocks=40,
+                                                 block_size=4, dtype=dtype, enable_cuda_graph=True, mixed_cuda_graph=True))
+        assert r._graph_ok                                    # state, and still graphs
+        worst = 0.0
+        # after the rolling part: the survivors decode alone (decode-only buckets), with a newcomer now and then
+        for entries, end in steps:
+            out = r.step([StepEntry(q, tokens[q][lo:hi], [hi - lo - 1]) for q, lo, hi in entries]).cpu().numpy()
+            for i, (q, lo, hi) in enumerate(entries):
+                worst = max(worst, H.rel_err(out[i], want[q][hi - 1]))
+            for q in end:
+                r.finish(q)
+        assert any(isinstance(k, int) for k in r._graphs) and any(isinstance(k, tuple) for k in r._graphs), list(r._graphs)
+        r.manager.check_invariants()
+        assert r.manager.num_free_blocks() == 40
+        print("toy with state and graphs", dtype, worst, sorted(map(str, r._graphs)))
+        assert worst <= H.TOLERANCE[dtype], worst
+    finally:
+        from dinfer_b200.config.registry import unregister_architecture
+        from dinfer_b200.parts.base import MIXERS
+        unregister_architecture("ToyStateGraphForTest")
+        MIXERS.unregister("toy_running_mean_device")
