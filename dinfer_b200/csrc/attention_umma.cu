@@ -1,22 +1,25 @@
 // Paged causal attention for prompt portions on the 5th-generation tensor cores (tcgen05 + TMEM + TMA),
-// bfloat16, head size 64 or 128, group sizes that divide 128, pages of 8..64 tokens (power of two).
+// bfloat16, head size 64 or 128, group sizes that divide 128, pages of 8 tokens or more (a power of two).
 //
 // A CTA owns 2 x 128 rows of one (request, kv head); a row is a (token, query head of the group) pair, so
-// the heads of a group share every K/V tile.  Per 64-key tile and 128-row group:
-//     S[128, 64]  = Q K^T          tcgen05.mma, Q and K K-major in shared memory, S in tensor memory
-//     P = softmax step             one thread per row (= TMEM lane): tcgen05.ld, mask, exp2, P -> shared memory (bf16)
-//     O[128, D]  += P V            tcgen05.mma accumulating in tensor memory, V used as it lies in the cache
-//                                  ([key][d] = MN-major B operand); O is rescaled in place only when a row's
+// the heads of a group share every K/V tile.  Per 128-key tile and 128-row tile:
+//     S[128, 128] = Q K^T          tcgen05.mma, Q and K K-major in shared memory, S in tensor memory
+//     P = softmax step             two threads per row (= TMEM lane), 64 keys each: tcgen05.ld, mask, the row's
+//                                  maximum (the halves' maxima meet in shared memory), exp2; P goes back into
+//                                  tensor memory as bfloat16, over columns of S its thread has read (tcgen05.st)
+//     O[128, D]  += P V            tcgen05.mma with A = P from tensor memory and B = V as it lies in the cache
+//                                  ([key][d] = MN-major operand); O is rescaled in place only when a row's
 //                                  maximum grows by more than 2^8
-// Warp roles (352 threads): warp 0 = TMA producer (Q once through a 3-D map over [token][head][d]; K/V page
-// by page through a 2-D map over the layer's cache, looked up in the block table), warp 1 = TMEM
-// allocation + MMA issue for row tile A, warp 10 = MMA issue for row tile B (a tile's chain of products
-// hangs on one issuing thread; two threads keep the tiles from waiting for each other), warps 2..5 and
-// 6..9 = the softmax / output groups of the two row tiles.  K tiles
-// and V tiles ride a 3-stage mbarrier ring each (K runs two tiles ahead of V).  S is double-buffered in
-// tensor memory: the MMA thread issues Q K^T of tile j+2 right behind P V of tile j, so a group's softmax
-// of tile j+1 finds its S ready when it has handed P of tile j over, and the tensor core works for one
-// group while the other computes.  No cluster launch, no multicast.  Every mbarrier wait is bounded.
+// Tensor memory (512 columns): S of row tile A, S of row tile B, O of A, O of B, 128 columns each.
+// Warp roles (608 threads, at most 96 registers each): warp 0 = Q once (a 3-D map over [token][head][d]) and the K
+// tiles, warp 18 = the V tiles (page by page through a 2-D map over the layer's cache, looked up in the block
+// table; each on its own 2-stage mbarrier ring), warp 1 = TMEM allocation + MMA issue, warps 2..17 = softmax and
+// output: (row tile, half of the keys) by groups of four warps, TMEM lane quarter = warp index mod 4.
+// A row tile's chain is  Q K^T -> softmax -> P V, Q K^T of the next tile -> ...; the one issuing thread serves the two
+// row tiles strictly in turn and puts P V and the next Q K^T into the tensor pipe together, which runs them in order:
+// the next S overwrites P only after P V has read it, and the tensor core works for one row tile while the
+// other's softmax computes.  No cluster launch, no multicast.  Every mbarrier wait is bounded; the named barriers
+// between the two warps of a row are passed by both even after a wait has run out.
 //
 // Counterpart in the reference: gqa_fa_v5_kernel (crates/kernels/cuda/gqa.cu:167-369, mma.sync) for this
 // head size; its tcgen05 attention (crates/kernels/cuda/gqa_fa_sm100.cu) exists for D = 256 only and stages
@@ -29,8 +32,9 @@ using namespace dinfer;
 
 namespace {
 
-constexpr int BM = 128, BN = 64, STAGES = 3, NTHREADS = 352;   // BM rows per softmax group, two groups per CTA
-constexpr int MMA_WARP_B = 10;                                  // the second MMA issuer (the first is warp 1)
+constexpr int BM = 128, BN = 128, STAGES = 2, NTHREADS = 608;   // BM rows per row tile, two row tiles per CTA
+                                  // the second MMA issuer (the first is warp 1)
+constexpr int V_WARP = 18;                                     // the second producer warp
 constexpr int TABLE_SLOTS = 2048;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
@@ -73,6 +77,27 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
   return false;
 }
+// one look, no waiting
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// A wait as a tight loop of looks, for a thread with nothing else to do: it sees the barrier sooner than a
+// suspended wait wakes up.  Bounded like the other.
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity) {
+  uint64_t start = 0;
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if ((i & 255) == 255) {
+      const uint64_t now = global_ns();
+      if (start == 0) start = now;
+      else if (now - start > 2000000000ull) return false;
+    }
+  }
+  return false;
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
@@ -98,6 +123,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
                  "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]),
                  "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]),
                  "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&u)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
+                 "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
                : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -132,6 +163,18 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&r)[32]) 
                  "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
                : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&u)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+               "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]),
+                 "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15])
+               : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (rows = lanes, two bfloat16 per 32-bit column) from tensor memory
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -140,27 +183,27 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 template <int D> constexpr size_t smem_bytes() {
-  return (size_t)(2 * BM * D * 2 + 2 * STAGES * BN * D * 2 + 2 * BM * BN * 2) + 1024;
+  return (size_t)(2 * BM * D * 2 + 2 * STAGES * BN * D * 2) + 1024;      // Q of both row tiles, K and V stages
 }
 
-// Two row tiles (A, B) of 128 rows per CTA, each with its own softmax warpgroup; the MMA thread feeds
-// them alternately, so one group's softmax runs while the tensor core works for the other.
-// O accumulates in tensor memory across tiles; a row's reference maximum is only raised when it grows
-// by more than 2^8 (the accumulator and the running sum are then rescaled in place), so P stays below
-// 256 and the rescale is rare.
+// Two row tiles (A, B) of 128 rows per CTA, each with eight softmax warps.  O accumulates in tensor memory
+// across tiles; a row's reference maximum is only raised when it grows by more than 2^8 (the accumulator and
+// the running sums are then rescaled in place), so P stays below 256 and the rescale is rare.
 template <int D>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __maxnreg__(96)
 attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Params p) {
   constexpr int NH = D / 64;                          // 64-wide halves of the head
   constexpr uint32_t Q_HALF = BM * 128, KV_HALF = BN * 128;
-  constexpr uint32_t Q_BYTES = NH * Q_HALF, KV_BYTES = NH * KV_HALF, P_BYTES = BM * BN * 2;
-  constexpr int TMEM_COLS = 512, O_COL = 256;                  // S of (tile w, buffer b) at (2w + b) * 64; O_A 256, O_B 384
+  constexpr uint32_t Q_BYTES = NH * Q_HALF, KV_BYTES = NH * KV_HALF;
+  constexpr int TMEM_COLS = 512, O_COL = 256;                  // S (and P over it) of row tile w at w * 128; O_A 256, O_B 384
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES],
-      s_full[2][2], p_full[2], pv_done[2], o_full[2];
+      s_full[2], p_full[2], o_full[2];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_table[TABLE_SLOTS];
   __shared__ int s_abort;
+  __shared__ float s_sum[2][2][BM];                       // a row's running sum, by the halves of its keys
+  __shared__ float s_max[2][2][2][BM];                    // a tile's row maxima, by the halves of its keys
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z, hk = blockIdx.x;
   pdl_enter();
@@ -186,7 +229,7 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const int n_tiles_a = (hi_a + BN - 1) / BN - tile_begin;
 
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-  const uint32_t sQ = base, sK = sQ + 2 * Q_BYTES, sV = sK + STAGES * KV_BYTES, sP = sV + STAGES * KV_BYTES;
+  const uint32_t sQ = base, sK = sQ + 2 * Q_BYTES, sV = sK + STAGES * KV_BYTES;
 
   // page-table slice of this CTA's keys, and zeroed K/V stages (a page that is skipped leaves its slot as it
   // was: it must hold finite numbers, because a masked key still meets 0 * V)
@@ -202,14 +245,12 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
     mbar_init(smem_u32(&q_full), 1);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&k_full[s]), 1); mbar_init(smem_u32(&k_empty[s]), 2);       // empty: both MMA issuers
-      mbar_init(smem_u32(&v_full[s]), 1); mbar_init(smem_u32(&v_empty[s]), 2);
+      mbar_init(smem_u32(&k_full[s]), 1); mbar_init(smem_u32(&k_empty[s]), 1);
+      mbar_init(smem_u32(&v_full[s]), 1); mbar_init(smem_u32(&v_empty[s]), 1);
     }
     for (int w = 0; w < 2; ++w) {
-      mbar_init(smem_u32(&s_full[w][0]), 1);
-      mbar_init(smem_u32(&s_full[w][1]), 1);
-      mbar_init(smem_u32(&p_full[w]), 128);
-      mbar_init(smem_u32(&pv_done[w]), 1);
+      mbar_init(smem_u32(&s_full[w]), 1);
+      mbar_init(smem_u32(&p_full[w]), 256);
       mbar_init(smem_u32(&o_full[w]), 1);
     }
     s_abort = 0;
@@ -225,10 +266,12 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   tc_fence_after();
   const uint32_t tmem = s_tmem_base;
 
-  if (warp == 0) {
-    // ---- TMA producer: the whole warp.  Q once (lane 0); then per tile one copy per page, K / V and
-    // 64-wide half, spread over the lanes so that they are requested side by side.
-    if (lane == 0) {
+  if (warp == 0 || warp == V_WARP) {
+    // ---- TMA producers: warp 0 brings Q (once, lane 0) and the K tiles, another warp the V tiles, each walking
+    // its own ring; per tile one copy per page and 64-wide half, spread over the lanes.  (A copy of a page's
+    // 2 KB takes the issuing warp some 85 cycles: two warps issue side by side.)
+    const int kv = warp == 0 ? 0 : 1;
+    if (kv == 0 && lane == 0) {
       const uint32_t qb = smem_u32(&q_full);
       mbar_expect_tx(qb, (b_on ? 2 : 1) * Q_BYTES);
       for (int w = 0; w < (b_on ? 2 : 1); ++w)
@@ -237,12 +280,12 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
     const int br = min(p.block_size, BN);                          // rows of one K/V box
     const int boxes = BN / br;
-    const int n_ops = boxes * NH;                                  // copies of one of K / V of a tile, <= 16
+    const int n_ops = boxes * NH;                                  // copies of one of K / V of a tile, <= 32
     bool alive = true;
     for (int j = 0; j < n_tiles && alive; ++j) {
       const int s = j % STAGES;
       const int j0 = (tile_begin + j) * BN;
-      // this lane's copy: page x of the tile, 64-wide half h (the same for K and for V)
+      // this lane's copy: page x of the tile, 64-wide half h
       bool valid = false;
       int row_k = 0, col = 0; uint32_t off = 0;
       if (lane < n_ops) {
@@ -260,95 +303,106 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
       }
       const uint32_t bytes = __reduce_add_sync(0xffffffffu, valid ? (uint32_t)(br * 128) : 0u);
-#pragma unroll
-      for (int kv = 0; kv < 2; ++kv) {
-        bool ok = true;
-        if (lane == 0) ok = mbar_wait(smem_u32(kv == 0 ? &k_empty[s] : &v_empty[s]), ((j / STAGES) & 1) ^ 1);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) { if (lane == 0) { s_abort = 1; atomicExch(p.status, 11); } alive = false; break; }
-        const uint32_t bar = smem_u32(kv == 0 ? &k_full[s] : &v_full[s]);
-        if (lane == 0) {
-          if (bytes == 0) mbar_arrive(bar); else mbar_expect_tx(bar, bytes);
-        }
-        __syncwarp();
-        if (valid) tma_load_2d((kv == 0 ? sK : sV) + off, &map_kv, col, row_k + kv * p.Hkv * p.block_size, bar);
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(smem_u32(kv == 0 ? &k_empty[s] : &v_empty[s]), ((j / STAGES) & 1) ^ 1);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { if (lane == 0) { s_abort = 1; atomicExch(p.status, 11); } alive = false; break; }
+      const uint32_t bar = smem_u32(kv == 0 ? &k_full[s] : &v_full[s]);
+      if (lane == 0) {
+        if (bytes == 0) mbar_arrive(bar); else mbar_expect_tx(bar, bytes);
       }
+      __syncwarp();
+      if (valid) tma_load_2d((kv == 0 ? sK : sV) + off, &map_kv, col, row_k + kv * p.Hkv * p.block_size, bar);
     }
-  } else if (warp == 1 || warp == MMA_WARP_B) {
+  } else if (warp == 1) {
     if (lane == 0) {
-      // ---- MMA issue: one thread per row tile (warp 1: tile A, the last warp: tile B).  Each runs its tile's
-      // chain on its own, so neither waits for the other's softmax; the K and V stages go back to the producer
-      // when both have committed (or, past the end of its tile, plainly arrived on) their empty barriers.
-      const int w = warp == 1 ? 0 : 1;
-      const int n_w = w == 0 ? n_tiles_a : (b_on ? n_tiles : 0);
+      // ---- MMA issue: one thread, the two row tiles strictly in turn: P V of tile j and, right behind it, Q K^T
+      // of tile j + 1 for row tile A, then the same for row tile B.  The tensor pipe runs them in that order, so a
+      // row tile's next S overwrites its P only after P V has read it, and while the pipe works for one row tile
+      // the other's softmax computes: the turns keep the two a half step apart.
       constexpr uint32_t idesc_qk = idesc_bf16(BM, BN, 0), idesc_pv = idesc_bf16(BM, D, 1);
       // descriptors differ from these bases by constants (16-byte units in the low field)
-      const uint64_t dq = desc_k_major(sQ + w * Q_BYTES), dk = desc_k_major(sK);
-      const uint64_t dp = desc_k_major(sP + w * P_BYTES), dv = desc_mn_major(sV, KV_HALF);
-      const uint32_t o_tmem = tmem + O_COL + w * 128;
-      auto issue_qk = [&](int t) {                                  // S_w[t % 2] = Q_w K(t)^T
+      const uint64_t dq = desc_k_major(sQ), dk = desc_k_major(sK);
+      const uint64_t dv = desc_mn_major(sV, KV_HALF);
+      const int n_of[2] = {n_tiles_a, b_on ? n_tiles : 0};
+      auto issue_qk = [&](int w, int t) {                           // S_w = Q_w K(t)^T
+        const uint64_t dqs = dq + (uint64_t)(w * (Q_BYTES >> 4));
         const uint64_t dks = dk + (uint64_t)((t % STAGES) * (KV_BYTES >> 4));
-        const uint32_t s_tmem = tmem + (2 * w + (t & 1)) * BN;
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          tc_mma(s_tmem, dq + (uint64_t)(((k / 4) * Q_HALF + (k % 4) * 32) >> 4),
+        for (int k = 0; k < D / 16; ++k)
+          tc_mma(tmem + w * BN, dqs + (uint64_t)(((k / 4) * Q_HALF + (k % 4) * 32) >> 4),
                  dks + (uint64_t)(((k / 4) * KV_HALF + (k % 4) * 32) >> 4), idesc_qk, k > 0 ? 1u : 0u);
-        }
-        tc_commit(smem_u32(&s_full[w][t & 1]));
+        tc_commit(smem_u32(&s_full[w]));
       };
-      auto issue_pv = [&](int s, int j) {
+      auto issue_pv = [&](int w, int s, int j) {                    // O_w += P_w V(j), P from the columns of S_w
         const uint64_t dvs = dv + (uint64_t)(s * (KV_BYTES >> 4));
+        const uint32_t s_tmem = tmem + w * BN, o_tmem = tmem + O_COL + w * 128;
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k)
-          tc_mma(o_tmem, dp + (uint64_t)(k * 2), dvs + (uint64_t)((k * 16 * 128) >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+          tc_mma_ts(o_tmem, s_tmem + (k / 4) * 64 + (k % 4) * 8, dvs + (uint64_t)((k * 16 * 128) >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
       };
       bool ok = true;
-      if (n_w > 0 && !mbar_wait(smem_u32(&q_full), 0)) { s_abort = 1; atomicExch(p.status, 12); ok = false; }
-      // prologue: S of this row tile's first two key tiles
-      for (int t = 0; t < 2 && t < n_tiles && ok; ++t) {
-        if (t < n_w) {
-          if (!mbar_wait(smem_u32(&k_full[t % STAGES]), 0)) { s_abort = 1; atomicExch(p.status, 12); ok = false; break; }
+      if (!mbar_wait(smem_u32(&q_full), 0)) { s_abort = 1; atomicExch(p.status, 12); ok = false; }
+      if (ok && n_tiles > 0) {                                      // S of the first key tile, for both row tiles
+        if (!mbar_wait(smem_u32(&k_full[0]), 0)) { s_abort = 1; atomicExch(p.status, 12); ok = false; }
+        else {
           tc_fence_after();
-          issue_qk(t);
-          tc_commit(smem_u32(&k_empty[t % STAGES]));
-        } else {                                                   // not this tile's key tile: hand the stage back once it is full
-          if (!mbar_wait(smem_u32(&k_full[t % STAGES]), 0)) { s_abort = 1; atomicExch(p.status, 12); ok = false; break; }
-          mbar_arrive(smem_u32(&k_empty[t % STAGES]));
+          for (int w = 0; w < 2; ++w)
+            if (n_of[w] > 0) issue_qk(w, 0);
+          tc_commit(smem_u32(&k_empty[0]));
         }
       }
-      // Past the end of its own row tile an issuer still takes every stage in step (it waits for the stage
-      // to be full before it arrives on its empty barrier), so that a barrier never gets two arrivals of one
-      // issuer in one phase.
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % STAGES;
-        if (j < n_w) {
-          if (!mbar_wait(smem_u32(&p_full[w]), j & 1)) { s_abort = 1; atomicExch(p.status, 13); ok = false; break; }
-          if (!mbar_wait(smem_u32(&v_full[s]), (j / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); ok = false; break; }
-          tc_fence_after();
-          issue_pv(s, j);
-          tc_commit(smem_u32(&pv_done[w]));                         // P_w is free again, O_w is quiet until the next P V
-          if (j + 1 == n_w) tc_commit(smem_u32(&o_full[w]));         // this row tile's last P V
-          tc_commit(smem_u32(&v_empty[s]));
-        } else {
-          if (!mbar_wait(smem_u32(&v_full[s]), (j / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); ok = false; break; }
-          mbar_arrive(smem_u32(&v_empty[s]));
-        }
-        if (j + 2 < n_tiles) {
-          const int s2 = (j + 2) % STAGES;
-          if (j + 2 < n_w) {                                         // S of tile j + 2 into the buffer tile j just left
-            if (!mbar_wait(smem_u32(&k_full[s2]), ((j + 2) / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); ok = false; break; }
-            tc_fence_after();
-            issue_qk(j + 2);
-            tc_commit(smem_u32(&k_empty[s2]));
-          } else {
-            if (!mbar_wait(smem_u32(&k_full[s2]), ((j + 2) / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); ok = false; break; }
-            mbar_arrive(smem_u32(&k_empty[s2]));
+      // V of a tile and K of the next are there long before the tile's P.  The thread looks for them while it would
+      // wait anyway (between the two row tiles' turns of the step before), so that nothing but the issue itself
+      // stands between a row tile's P and its next S.
+      bool ahead = false;                                           // V(j) and K(j + 1) already seen
+      // The wait for a row tile's P is a tight loop of looks (this thread has nothing else to do, and a suspended
+      // wait wakes up late); between looks it sees to the next step's V and K.
+      auto wait_p = [&](int w, int j, uint32_t v_next, uint32_t v_par, uint32_t k_next, uint32_t k_par, bool look) {
+        const uint32_t bar = smem_u32(&p_full[w]);
+        uint64_t start = 0;
+        for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+          if (mbar_test(bar, j & 1)) return true;
+          if (look && !ahead) ahead = mbar_test(v_next, v_par) && (k_next == 0 || mbar_test(k_next, k_par));
+          if ((i & 255) == 255) {
+            const uint64_t now = global_ns();
+            if (start == 0) start = now;
+            else if (now - start > 2000000000ull) return false;
           }
         }
+        return false;
+      };
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % STAGES, s1 = (j + 1) % STAGES;
+        if (!ahead) {
+          if (!mbar_spin(smem_u32(&v_full[s]), (j / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); break; }
+          if (j + 1 < n_tiles && !mbar_spin(smem_u32(&k_full[s1]), ((j + 1) / STAGES) & 1)) { s_abort = 1; atomicExch(p.status, 14); break; }
+        }
+        ahead = false;
+        const bool look = j + 1 < n_tiles;                          // V(j + 1) and K(j + 2) went out a step ago
+        const uint32_t v_next = smem_u32(&v_full[s1]), v_par = ((j + 1) / STAGES) & 1;
+        const uint32_t k_next = j + 2 < n_tiles ? smem_u32(&k_full[s]) : 0u, k_par = ((j + 2) / STAGES) & 1;
+        for (int w = 0; w < 2 && ok; ++w) {
+          if (j < n_of[w]) {
+            if (!wait_p(w, j, v_next, v_par, k_next, k_par, look && w == 1)) { s_abort = 1; atomicExch(p.status, 13); ok = false; break; }
+            tc_fence_after();
+            issue_pv(w, s, j);
+            if (j + 1 == n_of[w]) tc_commit(smem_u32(&o_full[w]));   // this row tile's last P V
+          }
+          if (j + 1 < n_of[w]) issue_qk(w, j + 1);                   // the next S, queued right behind this P V
+        }
+        if (!ok) break;
+        // the stages go back when the products issued so far have read them
+        tc_commit(smem_u32(&v_empty[s]));
+        if (j + 1 < n_tiles) tc_commit(smem_u32(&k_empty[s1]));
       }
     }
-  } else {                                                          // ---- softmax and output: one thread per row
-    const int w = (warp - 2) >> 2;                                  // row tile A (warps 2..5) or B (warps 6..9)
+  } else {
+    // ---- softmax and output: two threads per row.  Both read the row's 128 scores for its maximum (so they
+    // agree on it without talking), then each takes the exponentials, the sum and the P columns of its own 64
+    // keys, and its own half of the columns of O when O is rescaled and when it is written.
+    const int idx = (warp - 2) >> 2;                                // 0..3: (row tile, half of the keys)
+    const int w = idx >> 1, h = idx & 1;
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const int row = row0 + w * BM + r;
@@ -357,95 +411,109 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int n_w = w == 0 ? n_tiles_a : (b_on ? n_tiles : 0);
     const int first_tok_w = (row0 + w * BM) / p.group;
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t s_addr = lane_addr + 2 * w * BN, o_addr = lane_addr + O_COL + w * 128;
-    unsigned char* prow = smem_dyn + (sP - smem_u32(smem_dyn)) + w * P_BYTES + r * 128;
-    float m_run = -INFINITY, l_run = 0.f;                           // reference maximum (scaled, log2 units), running sum
+    const uint32_t s_addr = lane_addr + w * BN, o_addr = lane_addr + O_COL + w * 128 + h * (D / 2);
+    const int pair_bar = 1 + w * 4 + quarter;                       // named barrier of the two warps on these 32 rows
+    float m_run = -INFINITY, l_run = 0.f;                           // reference maximum (scaled, log2 units), running sum of this half
     bool ok = true;
-    for (int j = 0; j < n_w && ok; ++j) {
-      if (!mbar_wait(smem_u32(&s_full[w][j & 1]), (j >> 1) & 1)) { s_abort = 1; atomicExch(p.status, 15); ok = false; break; }
+    // A warp that gives up a wait keeps walking the loop for the pair barriers alone, so that the warp it shares
+    // its rows with never waits for it in vain.
+    for (int j = 0; j < n_w; ++j) {
+      if (ok && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_full[w]), j & 1))) { s_abort = 1; atomicExch(p.status, 15); ok = false; }
       tc_fence_after();
-      float s0[32], s1[32];
-      tmem_ld32(s_addr + (j & 1) * BN, s0);
-      tmem_ld32(s_addr + (j & 1) * BN + 32, s1);
-      tmem_ld_wait();
       const int jbase = (tile_begin + j) * BN;
       const bool need_mask = (jbase + BN - 1 > hist + first_tok_w) || p.window > 0 || jbase < lo;
-      if (need_mask) {
+      // this thread's 64 scores; their maximum (raw: the scale is positive), as eight short chains
+      float v0[32], v1[32];
+      float mx = -INFINITY;
+      if (ok) {
+        tmem_ld32(s_addr + h * 64, v0);
+        tmem_ld32(s_addr + h * 64 + 32, v1);
+        tmem_ld_wait();
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int ja = jbase + i, jc = jbase + 32 + i;
-          if (!(ja <= pos && ja >= lo && (p.window <= 0 || ja > pos - p.window))) s0[i] = -INFINITY;
-          if (!(jc <= pos && jc >= lo && (p.window <= 0 || jc > pos - p.window))) s1[i] = -INFINITY;
+          for (int i = 0; i < 32; ++i) {
+            const int ja = jbase + h * 64 + i, jc = ja + 32;
+            if (!(ja <= pos && ja >= lo && (p.window <= 0 || ja > pos - p.window))) v0[i] = -INFINITY;
+            if (!(jc <= pos && jc >= lo && (p.window <= 0 || jc > pos - p.window))) v1[i] = -INFINITY;
+          }
         }
+        float mq[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mq[i] = fmaxf(v0[i], v1[i]);
+#pragma unroll
+        for (int i = 8; i < 32; ++i) mq[i & 7] = fmaxf(mq[i & 7], fmaxf(v0[i], v1[i]));
+        mx = fmaxf(fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])), fmaxf(fmaxf(mq[4], mq[5]), fmaxf(mq[6], mq[7])));
       }
-      // maximum of the raw scores (the scale is positive), as eight short chains instead of one long one
-      float mq[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) mq[i] = fmaxf(s0[i], s1[i]);
-#pragma unroll
-      for (int i = 8; i < 32; ++i) mq[i & 7] = fmaxf(mq[i & 7], fmaxf(s0[i], s1[i]));
-      float mx = fmaxf(fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])), fmaxf(fmaxf(mq[4], mq[5]), fmaxf(mq[6], mq[7])));
-      mx *= p.scale_log2;
+      // the row's maximum is the larger of its two halves': through shared memory (two slots in turn, so that a
+      // thread a tile ahead does not overwrite what its partner has yet to read)
+      s_max[j & 1][w][h][r] = mx;
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      if (!ok) continue;
+      mx = fmaxf(mx, s_max[j & 1][w][1 - h][r]) * p.scale_log2;
       // raise the reference maximum only when it grows by more than 8 (in log2 units)
       const bool raise = mx > m_run + 8.f;
-      bool pv_seen = j == 0;                                        // P V of tile j-1 known to be complete
       if (j > 0 && __any_sync(0xffffffffu, raise)) {
-        // O_w must be quiet: P V of tile j-1 complete (P V of tile j waits for our P)
-        if (!mbar_wait(smem_u32(&pv_done[w]), (j - 1) & 1)) { s_abort = 1; atomicExch(p.status, 15); ok = false; break; }
-        tc_fence_after();
-        pv_seen = true;
+        // O_w is quiet: the P V of tile j-1 went through the tensor pipe before the Q K^T that made this S
         const float alpha = raise ? fast_exp2(m_run - mx) : 1.f;     // m_run = -inf gives 0
         l_run *= alpha;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          float o[32];
-          tmem_ld32(o_addr + c * 32, o);
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {                           // 16 columns at a time: the scores stay in registers
+          uint32_t o[16];
+          tmem_ld16(o_addr + c * 16, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] *= alpha;
-          tmem_st32(o_addr + c * 32, o);
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st16(o_addr + c * 16, o);
         }
-        tmem_st_wait();
       }
       if (raise) m_run = mx;
       const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
-      float sq[8];                                                  // eight partial sums: short dependency chains
+      // P = 2^(s * scale - m) rounded to bfloat16, two keys to a column, over the first 32 columns of this
+      // thread's half of S
+      float sq[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) sq[i] = 0.f;
+      {
+        uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        s0[i] = fast_exp2(fmaf(s0[i], p.scale_log2, neg_m));         // masked: -inf stays -inf, 2^-inf = 0
-        s1[i] = fast_exp2(fmaf(s1[i], p.scale_log2, neg_m));
-        sq[i & 7] += s0[i] + s1[i];
+        for (int i = 0; i < 32; i += 2) {
+          const float e0 = fast_exp2(fmaf(v0[i], p.scale_log2, neg_m));         // masked: 2^-inf = 0
+          const float e1 = fast_exp2(fmaf(v0[i + 1], p.scale_log2, neg_m));
+          sq[(i >> 1) & 7] += e0 + e1;
+          pk[i >> 1] = pack_bf16(e0, e1);
+        }
+        tmem_st16(s_addr + h * 64, pk);
+      }
+      {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float e0 = fast_exp2(fmaf(v1[i], p.scale_log2, neg_m));
+          const float e1 = fast_exp2(fmaf(v1[i + 1], p.scale_log2, neg_m));
+          sq[(i >> 1) & 7] += e0 + e1;
+          pk[i >> 1] = pack_bf16(e0, e1);
+        }
+        tmem_st16(s_addr + h * 64 + 16, pk);
       }
       l_run += ((sq[0] + sq[1]) + (sq[2] + sq[3])) + ((sq[4] + sq[5]) + (sq[6] + sq[7]));
-      // the P V of tile j-1 must have read P before it is overwritten
-      if (!pv_seen) {
-        if (!mbar_wait(smem_u32(&pv_done[w]), (j - 1) & 1)) { s_abort = 1; atomicExch(p.status, 15); ok = false; break; }
-      }
-      // P row r: 64 keys = 8 chunks of 16 bytes, swizzled like a K-major tile with 128-byte rows
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const float* src = c < 4 ? s0 + c * 8 : s1 + (c - 4) * 8;
-        uint4 v;
-        v.x = pack_bf16(src[0], src[1]); v.y = pack_bf16(src[2], src[3]);
-        v.z = pack_bf16(src[4], src[5]); v.w = pack_bf16(src[6], src[7]);
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = v;
-      }
+      tmem_st_wait();
       tc_fence_before();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(smem_u32(&p_full[w]));
     }
     if (ok && n_w > 0) {
-      if (!mbar_wait(smem_u32(&o_full[w]), 0)) { s_abort = 1; atomicExch(p.status, 16); ok = false; }
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&o_full[w]), 0))) { s_abort = 1; atomicExch(p.status, 16); ok = false; }
       tc_fence_after();
     }
+    // the row's sum is the two halves' (the reference maximum is the same in both)
+    s_sum[w][h][r] = l_run;
+    asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
     if (ok && n_w > 0) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = row_ok ? p.out + (int64_t)(t0 + row / p.group) * p.ldo + (int64_t)(hk * p.group + row % p.group) * D
+      const float l_row = s_sum[w][0][r] + s_sum[w][1][r];
+      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+      __nv_bfloat16* dst = row_ok ? p.out + (int64_t)(t0 + row / p.group) * p.ldo + (int64_t)(hk * p.group + row % p.group) * D + h * (D / 2)
                                   : nullptr;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         float o[32];
         tmem_ld32(o_addr + c * 32, o);
         tmem_ld_wait();
