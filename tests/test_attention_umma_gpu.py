@@ -1,5 +1,5 @@
 """The tcgen05 / TMEM / TMA prompt attention against the plain formula: portions with and without
-history, several requests, both head sizes, group sizes that divide 128, page sizes 8..64, windows,
+history, several requests, both head sizes, group sizes that divide 128, page sizes 8..256, windows,
 decoded tokens in the batch left alone, garbage in unused cache slots, a decisive far key."""
 import random
 
@@ -37,7 +37,7 @@ def run(reqs, H, Hkv, D, bs, window, seed):
 
 
 @pytest.mark.parametrize("H,Hkv,D,bs", [(8, 2, 128, 16), (4, 4, 128, 8), (16, 1, 128, 64), (8, 4, 64, 16),
-                                        (2, 1, 64, 32), (32, 8, 128, 16)])
+                                        (2, 1, 64, 32), (32, 8, 128, 16), (8, 2, 128, 128), (4, 2, 64, 256)])
 @pytest.mark.parametrize("window", [None, 70])
 def test_mixed_portions(H, Hkv, D, bs, window):
     reqs = [(40, 5), (70, 1), (0, 33), (130, 64), (0, 1), (250, 17), (0, 2), (65, 130), (0, 300)]
