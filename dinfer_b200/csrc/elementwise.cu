@@ -12,7 +12,7 @@ namespace {
 
 template <typename TW>
 __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restrict__ prev, int prev_rows,
-                                 const TW* __restrict__ table, float* __restrict__ out, int h, int vocab) {
+                                 const TW* __restrict__ table, float* __restrict__ out, int h, int vocab, float scale) {
   pdl_enter();
   const int t = blockIdx.x;
   int id = ids[t];
@@ -20,7 +20,14 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restr
   if (id < 0 || id >= vocab) id = 0;
   const TW* row = table + (int64_t)id * h;
   float* o = out + (int64_t)t * h;
-  for (int i = threadIdx.x; i < h; i += blockDim.x) o[i] = to_f32<TW>(row[i]);
+  for (int i = threadIdx.x; i < h; i += blockDim.x) o[i] = to_f32<TW>(row[i]) * scale;
+}
+
+__global__ void softcap_kernel(float* __restrict__ x, int64_t n, float cap) {
+  pdl_enter();
+  const float inv = 1.f / cap;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] * inv);
 }
 
 // out[t, i] = silu(gate_i) * up_i; silu(g) = g / (1 + exp(-g)) in 32-bit, one rounding.  The row of x holds
@@ -107,14 +114,15 @@ __global__ void cast_kernel(const TS* __restrict__ src, TD* __restrict__ dst, in
 DINFER_DEFINE_LAST_ERROR()
 
 // ids [T] int32; table [vocab, h]; out [T, h] f32; prev [prev_rows] int32 or null (see the head of the file).
+// out[t] = table[ids[t]] * scale (scale 1 for a model that does not scale its embedding)
 DINFER_API int dinfer_embedding(const int* ids, const int* prev, int prev_rows, const void* table, float* out, int T,
-                                int h, int vocab, int table_dtype, cudaStream_t stream) {
+                                int h, int vocab, int table_dtype, float scale, cudaStream_t stream) {
   if (T < 0 || h <= 0 || vocab <= 0) return refuse(DINFER_BAD_ARGUMENT, "embedding: bad sizes T=%d h=%d vocab=%d", T, h, vocab);
   if (T == 0) return 0;
   int threads = (h + 31) / 32 * 32;
   if (threads > 256) threads = 256;
   DINFER_DISPATCH_DTYPE(table_dtype, TW, {
-    launch_pdl(embedding_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, prev, prev_rows, (const TW*)table, out, h, vocab);
+    launch_pdl(embedding_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, prev, prev_rows, (const TW*)table, out, h, vocab, scale);
     return cuda_status("embedding");
   });
   return 0;
@@ -165,6 +173,16 @@ DINFER_API int dinfer_cast(const void* src, void* dst, int64_t n, int src_dtype,
       return cuda_status("cast");
     }));
   return 0;
+}
+
+// x[i] = cap * tanh(x[i] / cap) in place over n 32-bit values (logits with a soft cap)
+DINFER_API int dinfer_softcap(float* x, int64_t n, float cap, cudaStream_t stream) {
+  if (n < 0 || !(cap > 0.f)) return refuse(DINFER_BAD_ARGUMENT, "softcap: n=%lld cap=%g", (long long)n, (double)cap);
+  if (n == 0) return 0;
+  int64_t blocks = (n + 1023) / 1024;
+  if (blocks > 4096) blocks = 4096;
+  launch_pdl(softcap_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, n, cap);
+  return cuda_status("softcap");
 }
 
 // out [T, N] (row stride ld, act dtype) += bias [N] (bias dtype)

@@ -31,8 +31,8 @@ def _rows_contiguous(t: torch.Tensor, what: str) -> None:
 
 
 def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
-              prev: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t, :] = table[ids[t], :] into the f32 residual stream.  With ``prev`` (int32 [rows], the tokens
+              prev: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """out[t, :] = table[ids[t], :] * scale into the f32 residual stream.  With ``prev`` (int32 [rows], the tokens
     the previous step sampled) an id -(r + 1) stands for prev[r]."""
     require_cuda(ids, table, out)
     T, h = out.shape
@@ -44,10 +44,21 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
         if prev.dtype != torch.int32 or prev.dim() != 1 or not prev.is_contiguous():
             raise KernelError("embedding: prev int32 [rows] contiguous")
     lib, f = _fn("elementwise", "dinfer_embedding",
-                 [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+                 [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
     check(lib, f(ptr(ids), ptr(prev) if prev is not None else None, prev.numel() if prev is not None else 0,
-                 ptr(table), ptr(out), T, h, table.shape[0], dtype_code(table.dtype), stream_handle()), "embedding")
+                 ptr(table), ptr(out), T, h, table.shape[0], dtype_code(table.dtype), float(scale), stream_handle()),
+          "embedding")
     return out
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x = cap * tanh(x / cap) in place (float32, contiguous): logits with a soft cap."""
+    require_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not cap > 0:
+        raise KernelError("softcap: contiguous float32 values and a positive cap")
+    lib, f = _fn("elementwise", "dinfer_softcap", [c_void_p, c_int64, c_float, c_void_p])
+    check(lib, f(ptr(x), x.numel(), float(cap), stream_handle()), "softcap")
+    return x
 
 
 def rmsnorm(residual: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,

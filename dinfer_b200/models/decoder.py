@@ -97,7 +97,7 @@ class DecoderModel:
         s = self.spec
         T = ids.numel()
         x = torch.empty((T, s.hidden_size), dtype=torch.float32, device=ids.device)
-        ops.embedding(ids, self.embedding, x, prev=ctx.prev_tokens)
+        ops.embedding(ids, self.embedding, x, prev=ctx.prev_tokens, scale=s.embedding_scale)
         stream = ResidualStream(x)
         order = [self.blocks[e.layer] for e in s.schedule]
         for i, (block, binding) in enumerate(zip(order, bindings)):
@@ -105,4 +105,7 @@ class DecoderModel:
         if logits_rows.numel() == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=ids.device)
         f = self.final_norm.forward(stream.x, delta=stream.pending, rows=logits_rows)
-        return self.lm_head(f, out_dtype=torch.float32)
+        logits = self.lm_head(f, out_dtype=torch.float32)
+        if s.logit_softcap > 0:
+            ops.softcap(logits, s.logit_softcap)
+        return logits

@@ -53,10 +53,14 @@ class ModelSpec:
     lm_head_tensor: str
     tie_word_embeddings: bool
     eos_token_ids: Tuple[int, ...] = ()
+    embedding_scale: float = 1.0        # the embedding rows are multiplied by this on their way into the residual stream
+    logit_softcap: float = 0.0          # > 0: logits = cap * tanh(logits / cap)
 
     def check(self) -> None:
         if not self.layers:
             raise ValueError("a model needs at least one layer")
+        if self.logit_softcap < 0 or not self.embedding_scale == self.embedding_scale:
+            raise ValueError("logit_softcap must not be negative and embedding_scale must be a number")
         for i, e in enumerate(self.schedule):
             if not (0 <= e.layer < len(self.layers)):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.layers)}")

@@ -61,6 +61,11 @@ def test_embedding_and_silu(dt):
     out = torch.empty(5, 72, dtype=torch.float32, device="cuda")
     ops.embedding(dev(ids), dev(table), out)
     assert torch.equal(out.cpu(), table.float()[ids.long()])
+    ops.embedding(dev(ids), dev(table), out, scale=8.48528137)    # a model that scales its embedding
+    assert torch.allclose(out.cpu(), table.float()[ids.long()] * 8.48528137, rtol=1e-6, atol=0)
+    logits = (torch.randn(3, 1001, generator=g) * 40).float()    # a soft cap on logits, in place
+    capped = ops.softcap(dev(logits).clone(), 30.0)
+    assert torch.allclose(capped.cpu().double(), 30.0 * torch.tanh(logits.double() / 30.0), rtol=1e-5, atol=1e-5)
     x = (torch.randn(9, 2 * 250, generator=g) * 4).to(dt)
     o = torch.empty(9, 250, dtype=dt, device="cuda")
     ops.silu_mul(dev(x), o)

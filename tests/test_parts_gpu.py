@@ -377,20 +377,22 @@ def register_toy_routed():
                       PartSpec("swiglu", {"intermediate_size": c["inter"]}), norm("n2.weight")),
         )
         return ModelSpec("ToyRoutedForTest", h, c["vocab_size"], c["max_positions"], "embed.weight", layers,
-                         (ScheduleEntry(0), ScheduleEntry(1)), norm("final.weight"), "head.weight", False)
+                         (ScheduleEntry(0), ScheduleEntry(1)), norm("final.weight"), "head.weight", False,
+                         embedding_scale=c["embedding_scale"], logit_softcap=c["logit_softcap"])
 
     register_architecture("ToyRoutedForTest", lambda d: dict(d), spec, replace=True)
 
 
 TOY_ROUTED = dict(architectures=["ToyRoutedForTest"], vocab_size=157, hidden_size=40, heads=6, kv_heads=3, head_dim=16,
-                  inter=48, experts=4, top_k=2, rate=0.03, theta=20000.0, eps=1e-6, max_positions=128)
+                  inter=48, experts=4, top_k=2, rate=0.03, theta=20000.0, eps=1e-6, max_positions=128,
+                  embedding_scale=6.3, logit_softcap=0.8)
 
 
 def toy_routed_plain_logits(W, c, ids):
     W = {k: v.double() for k, v in W.items()}
     T, H_, Hkv, D = len(ids), c["heads"], c["kv_heads"], c["head_dim"]
     pos = torch.arange(T)
-    x = W["embed.weight"][torch.tensor(ids)]
+    x = W["embed.weight"][torch.tensor(ids)] * float(torch.tensor(c["embedding_scale"], dtype=torch.float32))
     for layer in (0, 1):
         p = f"layers.{layer}."
         hdn = P.rms_norm(x, W[p + "n1.weight"], c["eps"])
@@ -419,13 +421,14 @@ def toy_routed_plain_logits(W, c, ids):
         else:
             y = P.swiglu_mlp(hdn, W[p + "gate_proj.weight"], W[p + "up_proj.weight"], W[p + "down_proj.weight"])
         x = x + y
-    return (P.rms_norm(x, W["final.weight"], c["eps"]) @ W["head.weight"].T).numpy()
+    logits = P.rms_norm(x, W["final.weight"], c["eps"]) @ W["head.weight"].T
+    return (c["logit_softcap"] * torch.tanh(logits / c["logit_softcap"])).numpy()
 
 
 def test_toy_routed_feed_forward_and_other_position_encoding(tmp_path):
-    """A feed-forward with routing and a position encoding that is no table rotation, both defined here,
-    registered, built from a model folder and stepped whole / in portions / mixed (32-bit: the routing
-    must pick the same experts as the plain implementation)."""
+    """A feed-forward with routing and a position encoding that is no table rotation, both defined here, in a model
+    that scales its embedding and caps its logits softly; registered, built from a model folder and stepped whole /
+    in portions / mixed (32-bit: the routing must pick the same experts as the plain implementation)."""
     register_toy_routed()
     try:
         d = H.make_model_dir(str(tmp_path / "toyr"), TOY_ROUTED, 5, 0.1, 0.1, torch.float32)
