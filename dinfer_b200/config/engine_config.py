@@ -28,6 +28,10 @@ class EngineConfig:
     long_prefill_token_threshold: int = 0
     # decode-only steps replay a captured CUDA graph
     enable_cuda_graph: bool = True
+    # the decode graphs of every batch-size bucket are captured when the engine starts, so that no request meets a
+    # capture (some tens of milliseconds, now and then hundreds) in the middle of its decoding; off: each bucket's
+    # graph is captured when a step first needs it
+    capture_graphs_at_start: bool = True
     # steps whose prompt portions fill the token budget exactly (the steady state while prompts are taken in) and
     # steps with at most 128 prompt tokens (padded up to a power of two) replay a captured graph as well, one per
     # shape and bucket of decoded tokens beside them; pays where launching a step's kernels one by one takes the

@@ -143,6 +143,9 @@ class ModelRunner:
         self.sampled = torch.zeros(max(1, engine.max_num_seqs), dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self._init_graphs()
+        if self._graph_ok and engine.capture_graphs_at_start:
+            for bucket in self._buckets:
+                self._capture(bucket)
 
     @classmethod
     def from_dir(cls, model_dir: str, engine: EngineConfig) -> "ModelRunner":
