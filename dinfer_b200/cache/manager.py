@@ -3,8 +3,9 @@
 Layers whose caches live and die together form a group: all full-attention layers one, all layers
 with the same window another.  Each group has pages of its own (its own pool); within a group one
 block table per request serves every layer, since each layer has its own device tensor indexed by
-the same page ids.  Entry ``i`` of a table covers the positions ``[i*block_size, (i+1)*block_size)``;
-a page a window has passed is given back at once and its entry becomes -1.
+the same page ids.  Entry ``i`` of a table covers the positions ``[i*block_size, (i+1)*block_size)``
+(a group may have a page size of its own, ``GroupSpec.block_size``); a page a window has passed is given back at
+once and its entry becomes -1.
 
 Allocation is all-or-nothing over the groups and leaves the state untouched when it fails, like
 the reference's ``allocate_slots`` (crates/core/src/kv/manager.rs:203-281); ``free`` gives
@@ -28,8 +29,10 @@ from .block_pool import BlockPool, PoolError, StateSlots
 
 @dataclass(frozen=True)
 class GroupSpec:
-    """``window`` None: every token's keys are kept; else the last ``window`` (the token itself counts)."""
+    """``window`` None: every token's keys are kept; else the last ``window`` (the token itself counts).
+    ``block_size`` None: the manager's page size; else this group's own."""
     window: Optional[int] = None
+    block_size: Optional[int] = None
 
 
 @dataclass
@@ -60,7 +63,12 @@ class CacheManager:
         self.prefix_caching = bool(enable_prefix_caching)
         self.prefix_queries = 0           # tokens asked for / found by begin()
         self.prefix_hits = 0
-        self.block_size = block_size
+        self.block_size = block_size                       # the default; ``block_sizes[g]`` is what group g uses
+        self.block_sizes = [int(g.block_size) if g.block_size else block_size for g in self.groups]
+        if any(b <= 0 for b in self.block_sizes):
+            raise ValueError("a group's block_size must be positive")
+        if enable_prefix_caching and len(set(self.block_sizes)) > 1:
+            raise ValueError("the prefix cache needs one page size for all groups (a page's hash names its tokens)")
         if isinstance(num_blocks, int):
             num_blocks = [num_blocks] * len(self.groups)
         if len(num_blocks) != len(self.groups):
@@ -93,16 +101,14 @@ class CacheManager:
         if w is None:
             return 0
         first_pos = max(0, num_computed - w + 1)      # oldest key a query at num_computed still sees
-        return first_pos // self.block_size
+        return first_pos // self.block_sizes[group]
 
     def _need(self, held: Optional[_Held], total_tokens: int) -> List[int]:
         """New pages each group needs so that the request covers ``total_tokens`` tokens."""
-        bs = self.block_size
-        want = (total_tokens + bs - 1) // bs
         need = []
-        for g in range(len(self.groups)):
+        for g, bs in enumerate(self.block_sizes):
             have = len(held.tables[g]) if held else 0
-            need.append(max(0, want - have))
+            need.append(max(0, (total_tokens + bs - 1) // bs - have))
         return need
 
     def can_allocate(self, req: Hashable, total_tokens: int) -> bool:
@@ -132,7 +138,7 @@ class CacheManager:
         the prefix cache, for a request that already holds pages, or when no state slot is free."""
         if not self.prefix_caching or req in self._reqs:
             return 0
-        bs = self.block_size
+        bs = self.block_sizes[0]                          # the same for all groups with the prefix cache on
         limit = (len(token_ids) - 1) // bs             # full pages that leave the last token out
         self.prefix_queries += len(token_ids)
         chain: List[bytes] = []
@@ -176,7 +182,7 @@ class CacheManager:
             self._reqs[req] = held
         for g, n in enumerate(self._need(held, total_tokens)):
             held.tables[g].extend(self.pools[g].allocate(n))
-        held.capacity = min(len(t) for t in held.tables) * self.block_size
+        held.capacity = min(len(t) * bs for t, bs in zip(held.tables, self.block_sizes))
         held.num_tokens = max(held.num_tokens, total_tokens)
         return True
 
@@ -224,7 +230,7 @@ class CacheManager:
 
     def _hash_full_pages(self, held: _Held) -> None:
         """Pages whose tokens are all computed and known get their hash (and become findable)."""
-        bs = self.block_size
+        bs = self.block_sizes[0]
         ready = min(len(held.tokens), held.num_computed)
         while (len(held.hashes) + 1) * bs <= ready:
             i = len(held.hashes)

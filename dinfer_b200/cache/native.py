@@ -28,7 +28,7 @@ def library() -> ctypes.CDLL:
         P, I, L = c_void_p, c_int, c_int64
         sig = {
             "dh_last_error": (ctypes.c_char_p, []),
-            "dh_manager_new": (P, [I, P, I, P, I, I]), "dh_manager_delete": (None, [P]),
+            "dh_manager_new": (P, [I, P, P, P, I, I]), "dh_manager_delete": (None, [P]),
             "dh_contains": (I, [P, L]), "dh_num_requests": (I, [P]), "dh_requests": (I, [P, P, I]),
             "dh_num_tokens": (I, [P, L]), "dh_num_computed": (I, [P, L]), "dh_table_len": (I, [P, L, I]),
             "dh_table": (I, [P, L, I, P, I]), "dh_pool_free": (I, [P, I]), "dh_pool_blocks": (I, [P, I]),
@@ -109,7 +109,12 @@ class NativeCacheManager:
         if enable_prefix_caching and any(g.window is not None for g in self.groups):
             raise ValueError("the prefix cache needs groups that keep every key (no window)")
         self.prefix_caching = bool(enable_prefix_caching)
-        self.block_size = block_size
+        self.block_size = block_size                       # the default; ``block_sizes[g]`` is what group g uses
+        self.block_sizes = [int(g.block_size) if g.block_size else block_size for g in self.groups]
+        if any(b <= 0 for b in self.block_sizes):
+            raise ValueError("a group's block_size must be positive")
+        if enable_prefix_caching and len(set(self.block_sizes)) > 1:
+            raise ValueError("the prefix cache needs one page size for all groups (a page's hash names its tokens)")
         if isinstance(num_blocks, int):
             num_blocks = [num_blocks] * len(self.groups)
         if len(num_blocks) != len(self.groups):
@@ -119,7 +124,8 @@ class NativeCacheManager:
         self._lib = library()
         windows = (c_int * len(self.groups))(*[int(g.window or 0) for g in self.groups])
         blocks = (c_int * len(self.groups))(*[int(n) for n in num_blocks])
-        self._h = self._lib.dh_manager_new(len(self.groups), windows, block_size, blocks, max_num_seqs,
+        sizes = (c_int * len(self.groups))(*self.block_sizes)
+        self._h = self._lib.dh_manager_new(len(self.groups), windows, sizes, blocks, max_num_seqs,
                                            int(self.prefix_caching))
         if not self._h:
             raise ValueError(_error(self._lib))

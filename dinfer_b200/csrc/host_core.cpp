@@ -144,7 +144,7 @@ struct Held {
 
 struct Manager {
   std::vector<int> windows;                      // per group: 0 = every key is kept
-  int block_size = 1;
+  std::vector<int> block_sizes;                  // per group: tokens a page holds (one size for all with the prefix cache on)
   std::vector<Pool> pools;
   bool prefix = false;
   long long prefix_queries = 0, prefix_hits = 0;
@@ -159,10 +159,10 @@ struct Manager {
   }
   int first_needed_block(int g, int num_computed) const {
     if (!windows[g]) return 0;
-    return std::max(0, num_computed - windows[g] + 1) / block_size;
+    return std::max(0, num_computed - windows[g] + 1) / block_sizes[g];
   }
   int need(const Held* h, int g, int total) const {
-    const int want = (total + block_size - 1) / block_size;
+    const int want = (total + block_sizes[g] - 1) / block_sizes[g];
     const int have = h ? (int)h->tables[g].size() : 0;
     return std::max(0, want - have);
   }
@@ -192,13 +192,14 @@ struct Manager {
     int cap = 1 << 30;
     for (size_t g = 0; g < pools.size(); ++g) {
       for (int n = need(h, (int)g, total); n > 0; --n) h->tables[g].push_back(pools[g].take());
-      cap = std::min(cap, (int)h->tables[g].size());
+      cap = std::min(cap, (int)h->tables[g].size() * block_sizes[g]);
     }
-    h->capacity = cap * block_size;
+    h->capacity = cap;
     h->num_tokens = std::max(h->num_tokens, total);
     return true;
   }
   void hash_full_pages(Held& h) {
+    const int block_size = block_sizes[0];         // the same for all groups with the prefix cache on
     const int ready = std::min((int)h.tokens.size(), h.num_computed);
     while (((int)h.hashes.size() + 1) * block_size <= ready) {
       const int i = (int)h.hashes.size();
@@ -227,12 +228,16 @@ struct Manager {
 DH_API const char* dh_last_error() { return g_error.c_str(); }
 
 // ---- cache manager
-DH_API void* dh_manager_new(int n_groups, const int* windows, int block_size, const int* num_blocks, int max_num_seqs,
+DH_API void* dh_manager_new(int n_groups, const int* windows, const int* block_sizes, const int* num_blocks, int max_num_seqs,
                             int prefix_caching) {
-  if (n_groups <= 0 || block_size <= 0 || max_num_seqs < 0) { fail("bad sizes"); return nullptr; }
+  if (n_groups <= 0 || max_num_seqs < 0) { fail("bad sizes"); return nullptr; }
+  for (int g = 0; g < n_groups; ++g) {
+    if (block_sizes[g] <= 0) { fail("a group's block size must be positive"); return nullptr; }
+    if (prefix_caching && block_sizes[g] != block_sizes[0]) { fail("the prefix cache needs one page size for all groups"); return nullptr; }
+  }
   auto* m = new Manager();
   m->windows.assign(windows, windows + n_groups);
-  m->block_size = block_size;
+  m->block_sizes.assign(block_sizes, block_sizes + n_groups);
   for (int g = 0; g < n_groups; ++g) {
     if (num_blocks[g] <= 0) { delete m; fail("a pool needs at least one block"); return nullptr; }
     m->pools.emplace_back(num_blocks[g]);
@@ -305,7 +310,7 @@ DH_API int dh_allocate(void* m, int64_t r, int total) { return static_cast<Manag
 DH_API int dh_begin(void* mp, int64_t r, const int32_t* tokens, int n) {
   auto* m = static_cast<Manager*>(mp);
   if (!m->prefix || m->find(r)) return 0;
-  const int bs = m->block_size;
+  const int bs = m->block_sizes[0];
   const int limit = (n - 1) / bs;
   m->prefix_queries += n;
   std::vector<Hash128> chain;
@@ -424,7 +429,7 @@ DH_API int dh_decode_plan_fill(void* mp, int32_t* words, int bucket, int width, 
   auto* m = static_cast<Manager*>(mp);
   if (n > bucket) return fail("more requests than the graph's bucket");
   auto align = [](int x) { return (x + 3) / 4 * 4; };
-  const int ng = (int)m->pools.size(), bs = m->block_size;
+  const int ng = (int)m->pools.size();
   int off = 0;
   int32_t* ids = words + off; off = align(off + bucket);
   int32_t* pos = words + off; off = align(off + bucket);
@@ -452,6 +457,7 @@ DH_API int dh_decode_plan_fill(void* mp, int32_t* words, int bucket, int width, 
       int32_t* row = tab[g] + (size_t)i * width;
       std::copy(t.begin(), t.begin() + k, row);
       std::fill(row + k, row + width, -1);
+      const int bs = m->block_sizes[g];
       const int blk = p / bs < k ? t[p / bs] : -1;
       slot[g][i] = blk >= 0 ? blk * bs + p % bs : -1;
     }

@@ -87,10 +87,10 @@ class PlanBuilder:
         the tests do: the device tools that would catch an access out of range are not at hand everywhere).
         Dummy requests are held to the same rules: a kernel walks their tables and looks their positions up too."""
         m = self.manager
-        bs = m.block_size
-        if B and tables and int(seq.max()) > tables[0].shape[1] * bs:
-            raise AssertionError(f"plan: a request of {int(seq.max())} tokens is longer than its table of "
-                                 f"{tables[0].shape[1]} pages covers")
+        for g, tab in enumerate(tables):
+            if B and int(seq.max()) > tab.shape[1] * m.block_sizes[g]:
+                raise AssertionError(f"plan: a request of {int(seq.max())} tokens is longer than its table of "
+                                     f"{tab.shape[1]} pages of group {g} covers")
         if T and self.max_positions is not None and int(pos.max()) >= self.max_positions:
             raise AssertionError(f"plan: position {int(pos.max())} is outside the position table of {self.max_positions}")
         if int(cu[0]) != 0 or int(cu[-1]) != T or np.any(np.diff(cu) < 0):
@@ -103,7 +103,7 @@ class PlanBuilder:
             n = m.pools[g].num_blocks
             if tab.min() < -1 or tab.max() >= n:
                 raise AssertionError(f"plan: group {g}: a page id outside the pool of {n}")
-            if T and (sl.min() < -1 or sl.max() >= n * bs):
+            if T and (sl.min() < -1 or sl.max() >= n * m.block_sizes[g]):
                 raise AssertionError(f"plan: group {g}: a slot outside the pool")
             live = sl[sl >= 0]
             if live.size != np.unique(live).size:
@@ -139,7 +139,6 @@ class PlanBuilder:
         without tokens).  ``dev``: the int32 device buffer to fill (default: the next one of the ring).
         Returns (ids, logits_rows, ctx)."""
         m = self.manager
-        bs = m.block_size
         if slots is None:
             n_pad = (pad_reqs - len(entries)) if pad_reqs is not None else 0
             if n_pad < 0:
@@ -183,11 +182,13 @@ class PlanBuilder:
         if table_width is not None:
             width = table_width
         else:
-            width = max(1, max((int(s_) + bs - 1) // bs for s_ in seq)) if B else 1
+            small = min(m.block_sizes)                       # one width for all groups: what the smallest pages need
+            width = max(1, max((int(s_) + small - 1) // small for s_ in seq)) if B else 1
         if width > self.max_blocks:
             raise ValueError(f"a request needs {width} pages, the plan buffers hold {self.max_blocks}")
         tables, slot_maps = [], []
         for g in range(len(m.groups)):
+            bs = m.block_sizes[g]
             tab = np.full((B, width), -1, dtype=np.int32)
             sl = np.full(T, -1, dtype=np.int32)
             for j, (i, n) in enumerate(slots):
@@ -233,7 +234,7 @@ class PlanBuilder:
             o, n = views[name]
             return dev[o:o + n]
 
-        groups = [CacheGroupView(bs, view(f"tab{g}").view(B, width), view(f"slot{g}"), m.groups[g].window)
+        groups = [CacheGroupView(m.block_sizes[g], view(f"tab{g}").view(B, width), view(f"slot{g}"), m.groups[g].window)
                   for g in range(len(m.groups))]
         ctx = StepContext(
             num_tokens=T, num_reqs=B, positions=view("pos"), cu_seqlens=view("cu"), seq_lens=view("seq"),
@@ -288,7 +289,7 @@ class DecodePlan:
         for g in range(self.ng):
             n = m.pools[g].num_blocks
             live = self._slot[g][self._slot[g] >= 0]
-            if self._tab[g].min() < -1 or self._tab[g].max() >= n or (live.size and live.max() >= n * m.block_size) \
+            if self._tab[g].min() < -1 or self._tab[g].max() >= n or (live.size and live.max() >= n * m.block_sizes[g]) \
                     or live.size != np.unique(live).size:
                 raise AssertionError(f"decode plan: group {g}: a page or slot outside the pool, or a slot written twice")
 
@@ -296,7 +297,6 @@ class DecodePlan:
         """Write the step of ``entries`` (one token each) into the plan and send it to the device."""
         b = self.builder
         m = b.manager
-        bs = m.block_size
         n_real = len(entries)
         if n_real > self.bucket:
             raise ValueError("more requests than the graph's bucket")
@@ -332,6 +332,7 @@ class DecodePlan:
                     if n > c:
                         row[c:n] = t[c:n]
                 self._copied[i][g] = n
+                bs = m.block_sizes[g]
                 blk = t[p // bs] if p // bs < n else -1
                 self._slot[g][i] = blk * bs + p % bs if blk >= 0 else -1
         for i in range(n_real, self._live):           # rows that fell out of use become dummy rows

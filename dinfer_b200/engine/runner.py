@@ -170,24 +170,30 @@ class ModelRunner:
                 entry_group.append(group_keys.index(key))
             else:
                 entry_group.append(-1)
-        groups = [GroupSpec(window=k[1]) for k in group_keys]
-        self.max_blocks_per_seq = (e.max_model_len + bs - 1) // bs
+        groups = [GroupSpec(window=k[1], block_size=k[2]) for k in group_keys]
+        sizes = [k[2] or bs for k in group_keys]             # tokens a page of each group holds
+        if any(b <= 0 for b in sizes):
+            raise ValueError("a cache group's block_size must be positive")
+        # one table width for all groups: what the group with the smallest pages needs
+        self.max_blocks_per_seq = max([(e.max_model_len + b - 1) // b for b in sizes] or [(e.max_model_len + bs - 1) // bs])
         elt = 4 if self.act_dtype == torch.float32 else 2
-        bytes_per_block = sum(2 * n.num_kv_heads * bs * n.head_dim * elt
-                              for n in needs if isinstance(n, KvCacheNeed))
+        bytes_per_token = sum(2 * n.num_kv_heads * n.head_dim * elt for n in needs if isinstance(n, KvCacheNeed))
+        # every group gets pages for the same number of tokens: ``num_blocks`` pages of the engine's page size
+        longest = (e.max_model_len + bs - 1) // bs
         if e.num_blocks is not None:
             num_blocks = e.num_blocks
         else:
             free, total = torch.cuda.mem_get_info(self.device)
             used = total - free
             budget = min(free, int(total * e.gpu_memory_utilization) - used) - (2 << 30)
-            num_blocks = max(0, budget // max(1, bytes_per_block * 1)) if bytes_per_block else 1
-            if num_blocks < self.max_blocks_per_seq:
+            num_blocks = max(0, budget // max(1, bytes_per_token * bs)) if bytes_per_token else 1
+            if num_blocks < longest:
                 raise RuntimeError(f"not enough device memory for the cache: room for {num_blocks} pages, "
-                                   f"one request of max_model_len needs {self.max_blocks_per_seq}")
+                                   f"one request of max_model_len needs {longest}")
             # never more than every sequence at full length could use
-            num_blocks = min(num_blocks, self.max_blocks_per_seq * e.max_num_seqs)
+            num_blocks = min(num_blocks, longest * e.max_num_seqs)
         self.num_blocks = int(num_blocks)
+        group_blocks = [max(1, self.num_blocks * bs // b) for b in sizes]
         prefix = bool(e.enable_prefix_caching)
         if prefix and (any(g.window is not None for g in groups) or any(isinstance(n, StateNeed) for n in needs)):
             raise ValueError("enable_prefix_caching: this model has windowed layers or per-request state, "
@@ -196,15 +202,15 @@ class ModelRunner:
             from ..cache.native import NativeCacheManager as Manager
         else:
             Manager = CacheManager
-        self.manager = Manager(groups, bs, [self.num_blocks] * len(groups), e.max_num_seqs,
-                               enable_prefix_caching=prefix)
+        self.manager = Manager(groups, bs, group_blocks, e.max_num_seqs, enable_prefix_caching=prefix)
         self.bindings: List[CacheBinding] = []
         for i, (entry, n) in enumerate(zip(self.spec.schedule, needs)):
             if entry.cache_from is not None:
                 src = self.bindings[entry.cache_from]
                 self.bindings.append(CacheBinding(kv=src.kv, group=src.group, write=False, state=src.state))
             elif isinstance(n, KvCacheNeed):
-                kv = torch.zeros((self.num_blocks, 2, n.num_kv_heads, bs, n.head_dim),
+                g = entry_group[i]
+                kv = torch.zeros((group_blocks[g], 2, n.num_kv_heads, sizes[g], n.head_dim),
                                  dtype=self.act_dtype, device=self.device)
                 self.bindings.append(CacheBinding(kv=kv, group=entry_group[i], write=True))
             elif isinstance(n, StateNeed):

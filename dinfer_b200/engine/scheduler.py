@@ -69,13 +69,17 @@ class Scheduler:
         if len(req.prompt_ids) >= self.config.max_model_len:
             raise ValueError(f"request {req.req_id!r}: prompt of {len(req.prompt_ids)} tokens leaves no room "
                              f"under max_model_len {self.config.max_model_len}")
-        bs = self.manager.block_size
-        need = (len(req.prompt_ids) + 1 + bs - 1) // bs
-        if any(need > p.num_blocks for p in self.manager.pools):
-            raise ValueError(f"request {req.req_id!r}: needs {need} pages, the pool has "
-                             f"{min(p.num_blocks for p in self.manager.pools)}")
+        self._check_fits(req)
         req.status = RequestStatus.WAITING
         self.waiting.append(req)
+
+    def _check_fits(self, req: Request) -> None:
+        """A prompt (and its first token) that no pool of the manager could ever hold is refused at the door."""
+        for g, pool in enumerate(self.manager.pools):
+            bs = self.manager.block_sizes[g]
+            need = (len(req.prompt_ids) + 1 + bs - 1) // bs
+            if need > pool.num_blocks:
+                raise ValueError(f"request {req.req_id!r}: needs {need} pages, the pool has {pool.num_blocks}")
 
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running)
@@ -321,11 +325,7 @@ class NativeScheduler(Scheduler):
         if len(req.prompt_ids) >= self.config.max_model_len:
             raise ValueError(f"request {req.req_id!r}: prompt of {len(req.prompt_ids)} tokens leaves no room "
                              f"under max_model_len {self.config.max_model_len}")
-        bs = self.manager.block_size
-        need = (len(req.prompt_ids) + 1 + bs - 1) // bs
-        if any(need > p.num_blocks for p in self.manager.pools):
-            raise ValueError(f"request {req.req_id!r}: needs {need} pages, the pool has "
-                             f"{min(p.num_blocks for p in self.manager.pools)}")
+        self._check_fits(req)
         h = self.manager.handle(req.req_id)
         prompt = np.ascontiguousarray(req.prompt_ids, dtype=np.int32)
         stops = np.ascontiguousarray(sorted(req.params.stop_token_ids), dtype=np.int32)

@@ -41,6 +41,7 @@ class GQAttention(Mixer):
         self.qk_norm = bool(p.get("qk_norm", False))
         self.eps = float(p.get("eps", 1e-6))
         self.window = p.get("window")
+        self.page_size = p.get("cache_block_size")           # None: the engine's page size
         self.scale = float(p.get("scale", 1.0 / math.sqrt(self.D)))
         self.bias = bool(p.get("bias", False))
         pos: PartSpec = p.get("position") or PartSpec("none")
@@ -84,7 +85,7 @@ class GQAttention(Mixer):
             self.k_norm_w = tensors[self.names["kn"]].to(self.q_norm_w.dtype).contiguous()
 
     def cache_need(self):
-        return KvCacheNeed(self.Hkv, self.D, self.window)
+        return KvCacheNeed(self.Hkv, self.D, self.window, int(self.page_size) if self.page_size else None)
 
     def kernel_libraries(self):
         att = ["attention_generic"]

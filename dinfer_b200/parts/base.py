@@ -24,14 +24,16 @@ from .spec import PartSpec, TensorDecl
 
 @dataclass(frozen=True)
 class KvCacheNeed:
-    """Keys and values of every token (``window`` None) or of the last ``window`` tokens."""
+    """Keys and values of every token (``window`` None) or of the last ``window`` tokens, in pages of
+    ``block_size`` tokens (None: the engine's page size)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    block_size: Optional[int] = None
 
     def group_key(self):
-        # layers whose pages live and die together: same span of tokens
-        return ("kv", self.window)
+        # layers whose pages live and die together: same span of tokens, same page size
+        return ("kv", self.window, self.block_size)
 
 
 @dataclass(frozen=True)

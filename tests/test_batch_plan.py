@@ -18,7 +18,8 @@ def packed(builder, entries, starts, bucket, width):
 
 
 @pytest.mark.parametrize("manager", [CacheManager, NativeCacheManager])
-@pytest.mark.parametrize("groups", [[GroupSpec()], [GroupSpec(), GroupSpec(window=5)]])
+@pytest.mark.parametrize("groups", [[GroupSpec()], [GroupSpec(), GroupSpec(window=5)],
+                                    [GroupSpec(block_size=8), GroupSpec(window=5, block_size=2)]])
 def test_decode_plan_matches_full_build(groups, manager):
     """(With the C++ cache manager the plan is written by the library from its own tables.)"""
     rng = random.Random(3)
@@ -46,7 +47,7 @@ def test_decode_plan_matches_full_build(groups, manager):
             m.free(rid)
             assert m.allocate(rid, n0)
             m.advance(rid, n0)
-        for rid in [r for r, n in live.items() if n + 1 > bs * width]:
+        for rid in [r for r, n in live.items() if n + 1 > min(m.block_sizes) * width]:
             m.free(rid)
             del live[rid]
         order = list(live)
@@ -125,3 +126,20 @@ def test_dummy_places_of_a_captured_graph_stay_inside_the_tables_and_the_positio
             wide.build([], [], table_width=16, slots=[(-1, 25), (-1, 1)])
     finally:
         B.VALIDATE_PLANS = old
+
+
+def test_slots_and_tables_of_groups_with_page_sizes_of_their_own():
+    """A token's slot in a group is page * (the group's page size) + offset, and every group's table is as wide as
+    the plan says (the unused entries -1)."""
+    m = CacheManager([GroupSpec(), GroupSpec(block_size=2)], 8, [16, 64], max_num_seqs=2)
+    builder = PlanBuilder(m, "cpu", max_tokens=32, max_reqs=2, max_blocks=16)
+    assert m.allocate("a", 13)
+    ids, rows, ctx = builder.build([StepEntry("a", list(range(13)), [12])], [0])
+    big, small = m.block_table("a", 0), m.block_table("a", 1)
+    assert (len(big), len(small)) == (2, 7)
+    g0, g1 = ctx.groups
+    assert (g0.block_size, g1.block_size) == (8, 2)
+    assert g0.block_table.shape == g1.block_table.shape == (1, 7)              # one width: what the small pages need
+    assert g0.block_table[0].tolist() == big + [-1] * 5 and g1.block_table[0].tolist() == small
+    assert g0.slot_mapping.tolist() == [big[p // 8] * 8 + p % 8 for p in range(13)]
+    assert g1.slot_mapping.tolist() == [small[p // 2] * 2 + p % 2 for p in range(13)]

@@ -93,9 +93,12 @@ def test_state_slots():
 @pytest.mark.parametrize("seed", range(6))
 def test_random_orders(seed):
     rng = random.Random(seed)
-    groups = [GroupSpec(), GroupSpec(window=rng.choice([3, 7, 16]))] if seed % 2 else [GroupSpec()]
     bs = rng.choice([1, 4, 16])
+    own = rng.choice([2, 8]) if seed % 3 == 1 else None          # a page size of the second group's own
+    groups = [GroupSpec(), GroupSpec(window=rng.choice([3, 7, 16]), block_size=own)] if seed % 2 else [GroupSpec()]
+    sizes = [g.block_size or bs for g in groups]
     m = CacheManager(groups, bs, [rng.randrange(8, 40) for _ in groups], max_num_seqs=5)
+    assert m.block_sizes == sizes
     live = {}
     next_id = 0
     for _ in range(600):
@@ -115,7 +118,8 @@ def test_random_orders(seed):
                     t = m.block_table(r, g)
                     w = groups[g].window
                     first = 0 if w is None else max(0, live[r] - w + 1)
-                    assert all(t[p // bs] >= 0 for p in range(first, live[r]))
+                    assert all(t[p // sizes[g]] >= 0 for p in range(first, live[r]))
+                    assert len(t) == (live[r] + sizes[g] - 1) // sizes[g] or len(t) * sizes[g] >= live[r]
             else:
                 assert [m.num_free_blocks(g) for g in range(len(groups))] == before
                 if r not in m:
@@ -279,7 +283,8 @@ def test_both_implementations_hand_out_the_same_pages_in_the_same_order():
     the C++ cache manager side by side: the same answers, the same page ids in every table, the same free counts,
     the same state slots, the same prefix hits and evictions (their page hashes differ, what they find does not)."""
     rng = random.Random(2024)
-    for prefix, groups in ((False, [GroupSpec(), GroupSpec(window=9)]), (True, [GroupSpec(), GroupSpec()])):
+    for prefix, groups in ((False, [GroupSpec(), GroupSpec(window=9)]), (True, [GroupSpec(), GroupSpec()]),
+                           (False, [GroupSpec(block_size=16), GroupSpec(window=9, block_size=2)])):
         a = PythonCacheManager(groups, 4, [30, 30], 5, enable_prefix_caching=prefix)
         b = NativeCacheManager(groups, 4, [30, 30], 5, enable_prefix_caching=prefix)
         stems = [[rng.randrange(40) for _ in range(rng.randrange(4, 40))] for _ in range(3)]
@@ -323,3 +328,22 @@ def test_both_implementations_hand_out_the_same_pages_in_the_same_order():
             if step % 50 == 0:
                 a.check_invariants(); b.check_invariants()
         a.check_invariants(); b.check_invariants()
+
+
+def test_groups_with_page_sizes_of_their_own():
+    """A group may have its own page size: its table is as long as its pages need, a window gives back what its own
+    pages have passed, and the prefix cache, whose hashes name the tokens of a page, wants one size for all."""
+    m = CacheManager([GroupSpec(), GroupSpec(window=6, block_size=2), GroupSpec(block_size=16)], block_size=4,
+                     num_blocks=[8, 16, 2], max_num_seqs=2)
+    assert m.block_sizes == [4, 2, 16]
+    assert m.allocate("a", 11)
+    assert [len(m.block_table("a", g)) for g in range(3)] == [3, 6, 1]
+    m.advance("a", 11)
+    assert m.block_table("a", 1)[:3] == [-1, -1, -1] and all(b >= 0 for b in m.block_table("a", 1)[3:])   # keys 6.. stay
+    assert m.allocate("a", 32) and not m.can_allocate("a", 33)      # the third group's two pages of 16 are the limit
+    assert [len(m.block_table("a", g)) for g in range(3)] == [8, 16, 2]
+    m.free("a")
+    m.check_invariants()
+    assert [m.num_free_blocks(g) for g in range(3)] == [8, 16, 2]
+    with pytest.raises(ValueError):
+        CacheManager([GroupSpec(), GroupSpec(block_size=8)], 4, 8, 2, enable_prefix_caching=True)

@@ -217,8 +217,10 @@ def register_toy():
         ffn = PartSpec("swiglu", {"intermediate_size": c["inter"]})
 
         def attn(window):
+            # the windowed layer keeps its keys in pages of its own size, smaller than the engine's
             return PartSpec("gqa_attention", {"num_heads": Hq, "num_kv_heads": Hkv, "head_dim": D, "qk_norm": True,
-                                              "eps": c["eps"], "position": pos, "window": window})
+                                              "eps": c["eps"], "position": pos, "window": window,
+                                              "cache_block_size": c["window_page"] if window else None})
         layers = (
             LayerSpec("layers.0.", "prenorm_residual", PartSpec("toy_running_mean", {"state_size": c["state_size"]}),
                       norm("n1.weight"), ffn, norm("n2.weight")),
@@ -234,7 +236,7 @@ def register_toy():
 
 
 TOY = dict(architectures=["ToyMixedForTest"], vocab_size=203, hidden_size=56, heads=4, kv_heads=2, head_dim=16,
-           inter=72, state_size=24, window=9, theta=5000.0, eps=1e-5, max_positions=128)
+           inter=72, state_size=24, window=9, window_page=4, theta=5000.0, eps=1e-5, max_positions=128)
 
 
 def toy_plain_logits(W, c, ids):
@@ -286,6 +288,7 @@ def test_toy_architecture_registered_in_the_test(tmp_path, dtype):
         want = {r: toy_plain_logits(W, TOY, t) for r, t in tokens.items()}
         lengths = {r: len(t) for r, t in tokens.items()}
         rp = H.LocalReplay(d, dtype, 256, block_size=8)
+        assert rp.runner.manager.block_sizes == [4, 8]             # the windowed group's own page size, the engine's
         worst = {}
         try:
             for name, steps in (("whole", H.schedule_whole(lengths)), ("chunks", H.schedule_chunks(lengths, rng)),
