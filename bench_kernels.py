@@ -182,6 +182,27 @@ def attention_prompt(s, tokens_list, tflops):
         print(f"tokens {T:5d} | tcgen05 {t_umma:7.1f} us {flops / t_umma * 1e-6:6.1f} TFLOP/s"
               f" | mma.sync {t_tc:7.1f} us {flops / t_tc * 1e-6:6.1f} TFLOP/s | at peak {flops / tflops * 1e-6:6.1f} us", flush=True)
         del caches
+    print("# attention_prompt, a portion behind a history: us per launch by the CTAs that share a row-tile pair's keys;"
+          " 'auto' is the engine's choice")
+    for P, C in ((512, 4096), (512, 16384), (256, 8192), (128, 4096), (1024, 8192)):
+        caches, table = paged_cache(1, C, Hkv, D, bs, 4)
+        cu = torch.tensor([0, P], dtype=torch.int32, device="cuda")
+        seq = torch.tensor([C], dtype=torch.int32, device="cuda")
+        qkv = torch.randn(P, (H + 2 * Hkv) * D, device="cuda").to(torch.bfloat16)
+        q = qkv[:, :H * D]
+        out = torch.empty(P, H * D, dtype=torch.bfloat16, device="cuda")
+        flops = 4.0 * (P * (C - P) + P * (P + 1) / 2) * D * H
+        auto = A.umma_key_splits([P], H // Hkv, Hkv, D, C)
+        cells = []
+        for ks in (1, 2, 4, 8):
+            t = graph_time_us(lambda i: A.attention_umma(q, out, caches[i % 4], table, cu, seq, H, Hkv, D, D ** -0.5,
+                                                         0, P, ks), 8)
+            cells.append(f"s{ks} {t:6.1f}")
+            if ks == auto:
+                t_auto = t
+        print(f"portion {P:5d} context {C:6d} | {' '.join(cells)} | auto s{auto} {t_auto:6.1f} us "
+              f"{flops / t_auto * 1e-6:6.1f} TFLOP/s | at peak {flops / tflops * 1e-6:6.1f} us", flush=True)
+        del caches
     G.check_status()
 
 

@@ -43,6 +43,7 @@ struct Params {
   const int* block_table; int max_blocks;
   const int* cu_seqlens; const int* seq_lens;
   int H, Hkv, group, block_size, bs_log2, window;
+  int ksplit;                          // CTAs of a cluster that share a row-tile pair's keys (1, 2, 4 or 8)
   float scale_log2;
   int* status;
 };
@@ -105,6 +106,29 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The cluster's barrier counts warps: a warp whose lanes went different ways comes together first, so that
+// it arrives once.
+__device__ __forceinline__ void cluster_sync_all() {
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -194,8 +218,11 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   __shared__ int s_abort;
   __shared__ float s_sum[2][2][BM];                       // a row's running sum, by the halves of its keys
   __shared__ float s_max[2][2][2][BM];                    // a tile's row maxima, by the halves of its keys
+  __shared__ float x_max[2 * BM], x_sum[2 * BM];          // what the other CTAs of a cluster found for the rows this one writes
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, hk = blockIdx.x;
+  const int ks = p.ksplit;
+  const int rank = ks > 1 ? (int)cluster_ctarank() : 0;   // the cluster spans ks neighbours of the grid's x
+  const int b = blockIdx.z, hk = blockIdx.x / ks;
   pdl_enter();
   const int t0 = p.cu_seqlens[b];
   const int q_len = p.cu_seqlens[b + 1] - t0;
@@ -214,9 +241,14 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const int hi = hist + last_tok + 1;
   const int hi_a = hist + last_tok_a + 1;
   const int lo = p.window > 0 ? max(0, hist + first_tok - p.window + 1) : 0;
-  const int tile_begin = lo / BN, tile_end = (hi + BN - 1) / BN;
-  const int n_tiles = tile_end - tile_begin;           // tiles of B (or of A when B does not exist)
-  const int n_tiles_a = (hi_a + BN - 1) / BN - tile_begin;
+  // the key tiles of the pair, dealt out to the cluster's CTAs in runs of `per` (a CTA may get none)
+  const int tile_first = lo / BN;
+  const int n_all = (hi + BN - 1) / BN - tile_first;   // tiles of B (or of A when B does not exist)
+  const int n_all_a = (hi_a + BN - 1) / BN - tile_first;
+  const int per = (n_all + ks - 1) / ks;
+  const int tile_begin = tile_first + rank * per;
+  const int n_tiles = max(0, min(per, n_all - rank * per));
+  const int n_tiles_a = max(0, min(per, n_all_a - rank * per));
 
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   const uint32_t sQ = base, sK = sQ + 2 * Q_BYTES, sV = sK + STAGES * KV_BYTES;
@@ -225,7 +257,7 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   // was: it must hold finite numbers, because a masked key still meets 0 * V)
   const int table_first = (tile_begin * BN) >> p.bs_log2;
   {
-    const int last = (min(tile_end * BN, hi) - 1) >> p.bs_log2;
+    const int last = (min((tile_begin + n_tiles) * BN, hi) - 1) >> p.bs_log2;
     for (int i = threadIdx.x; i < TABLE_SLOTS && table_first + i <= last; i += NTHREADS) s_table[i] = table[table_first + i];
     uint4* z = reinterpret_cast<uint4*>(smem_dyn + (sK - smem_u32(smem_dyn)));
     for (int i = threadIdx.x; i < (int)(2 * STAGES * KV_BYTES / 16); i += NTHREADS) z[i] = make_uint4(0, 0, 0, 0);
@@ -497,27 +529,113 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     // the row's sum is the two halves' (the reference maximum is the same in both)
     s_sum[w][h][r] = l_run;
     asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-    if (ok && n_w > 0) {
-      const float l_row = s_sum[w][0][r] + s_sum[w][1][r];
-      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-      __nv_bfloat16* dst = row_ok ? p.out + (int64_t)(t0 + row / p.group) * p.ldo + (int64_t)(hk * p.group + row % p.group) * D + h * (D / 2)
-                                  : nullptr;
+    const float l_own = n_w > 0 ? s_sum[w][0][r] + s_sum[w][1][r] : 0.f;
+    __nv_bfloat16* dst = row_ok ? p.out + (int64_t)(t0 + row / p.group) * p.ldo + (int64_t)(hk * p.group + row % p.group) * D + h * (D / 2)
+                                : nullptr;
+    if (ks == 1) {
+      if (ok && n_w > 0) {
+        const float inv = l_own > 0.f ? 1.f / l_own : 0.f;
 #pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        float o[32];
-        tmem_ld32(o_addr + c * 32, o);
-        tmem_ld_wait();
-        if (row_ok) {
+        for (int c = 0; c < D / 64; ++c) {
+          float o[32];
+          tmem_ld32(o_addr + c * 32, o);
+          tmem_ld_wait();
+          if (row_ok) {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 v;
-            v.x = pack_bf16(o[q4 * 8] * inv, o[q4 * 8 + 1] * inv); v.y = pack_bf16(o[q4 * 8 + 2] * inv, o[q4 * 8 + 3] * inv);
-            v.z = pack_bf16(o[q4 * 8 + 4] * inv, o[q4 * 8 + 5] * inv); v.w = pack_bf16(o[q4 * 8 + 6] * inv, o[q4 * 8 + 7] * inv);
-            reinterpret_cast<uint4*>(dst + c * 32)[q4] = v;
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 v;
+              v.x = pack_bf16(o[q4 * 8] * inv, o[q4 * 8 + 1] * inv); v.y = pack_bf16(o[q4 * 8 + 2] * inv, o[q4 * 8 + 3] * inv);
+              v.z = pack_bf16(o[q4 * 8 + 4] * inv, o[q4 * 8 + 5] * inv); v.w = pack_bf16(o[q4 * 8 + 6] * inv, o[q4 * 8 + 7] * inv);
+              reinterpret_cast<uint4*>(dst + c * 32)[q4] = v;
+            }
+          }
+        }
+      }
+    } else {
+      // ---- the cluster's CTAs hold partial results of the same rows over different keys.  The 256 rows are dealt
+      // out in runs of 32 (one warp's): CTA `dest` writes the run out, the others send it their unnormalised O, their
+      // reference maximum and their sum through distributed shared memory, into the K/V stages, which are free once
+      // every CTA's products have completed (the first cluster barrier).  Layout of what a CTA receives:
+      // [sender][4-column group][row of the CTA's runs] float4, so that a warp's stores and loads are contiguous.
+      constexpr int C4 = D / 4;
+      const int run = w * 4 + quarter;
+      const int runs_per = 8 / ks;
+      const int dest = run / runs_per;
+      const int rows_r = runs_per * 32;
+      const int rloc = (run % runs_per) * 32 + lane;
+      const bool mine = ok && n_w > 0;                              // O_w of this CTA holds something
+      cluster_sync_all();
+      if (dest != rank) {
+        const int slot = rank < dest ? rank : rank - 1;
+        if (mine) {
+          const uint32_t remote = map_to_rank(sK, (uint32_t)dest) + (uint32_t)(((slot * C4 + h * (C4 / 2)) * rows_r + rloc) * 16);
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) {
+            float o[32];
+            tmem_ld32(o_addr + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4)
+              st_cluster_f32x4(remote + (uint32_t)((c * 8 + q4) * rows_r * 16), o[q4 * 4], o[q4 * 4 + 1], o[q4 * 4 + 2], o[q4 * 4 + 3]);
+          }
+        }
+        if (h == 0) {
+          st_cluster_f32(map_to_rank(smem_u32(&x_max[slot * rows_r + rloc]), (uint32_t)dest), mine ? m_run : -INFINITY);
+          st_cluster_f32(map_to_rank(smem_u32(&x_sum[slot * rows_r + rloc]), (uint32_t)dest), mine ? l_own : 0.f);
+        }
+      }
+      cluster_sync_all();
+      if (dest == rank && ok) {
+        float m_all = mine ? m_run : -INFINITY;
+        for (int sl = 0; sl < ks - 1; ++sl) m_all = fmaxf(m_all, x_max[sl * rows_r + rloc]);
+        const float a_own = (mine && m_run > -INFINITY) ? fast_exp2(m_run - m_all) : 0.f;
+        float l_all = l_own * a_own;
+        for (int sl = 0; sl < ks - 1; ++sl) {
+          const float l_p = x_sum[sl * rows_r + rloc];
+          if (l_p > 0.f) l_all += l_p * fast_exp2(x_max[sl * rows_r + rloc] - m_all);
+        }
+        const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+        const float4* recv = reinterpret_cast<const float4*>(smem_dyn + (sK - smem_u32(smem_dyn)));
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          float o[32];
+          if (mine) {                                               // the whole warp or none of it: tcgen05.ld is a warp's instruction
+            tmem_ld32(o_addr + c * 32, o);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = a_own != 0.f ? o[i] * a_own : 0.f;   // a row without a key holds anything
+          for (int sl = 0; sl < ks - 1; ++sl) {
+            const float l_p = x_sum[sl * rows_r + rloc];
+            if (l_p > 0.f) {
+              const float a_p = fast_exp2(x_max[sl * rows_r + rloc] - m_all);
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4) {
+                const float4 v = recv[(sl * C4 + h * (C4 / 2) + c * 8 + q4) * rows_r + rloc];
+                o[q4 * 4] = fmaf(a_p, v.x, o[q4 * 4]); o[q4 * 4 + 1] = fmaf(a_p, v.y, o[q4 * 4 + 1]);
+                o[q4 * 4 + 2] = fmaf(a_p, v.z, o[q4 * 4 + 2]); o[q4 * 4 + 3] = fmaf(a_p, v.w, o[q4 * 4 + 3]);
+              }
+            }
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 v;
+              v.x = pack_bf16(o[q4 * 8] * inv, o[q4 * 8 + 1] * inv); v.y = pack_bf16(o[q4 * 8 + 2] * inv, o[q4 * 8 + 3] * inv);
+              v.z = pack_bf16(o[q4 * 8 + 4] * inv, o[q4 * 8 + 5] * inv); v.w = pack_bf16(o[q4 * 8 + 6] * inv, o[q4 * 8 + 7] * inv);
+              reinterpret_cast<uint4*>(dst + c * 32)[q4] = v;
+            }
           }
         }
       }
     }
+  }
+  if (ks > 1 && (warp < 2 || warp == V_WARP)) {             // the other warps pass the cluster's two barriers too
+    cluster_sync_all();
+    cluster_sync_all();
   }
 
   tc_fence_before();
@@ -547,6 +665,7 @@ EncodeTiledFn encode_fn() {
 
 template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const Params& p, dim3 grid, cudaStream_t stream) {
+  static_assert((size_t)2 * STAGES * BN * D * 2 >= (size_t)7 * 32 * D * 4, "the K/V stages hold what seven senders bring");
   auto k = attention_umma_kernel<D>;
   constexpr size_t sm = smem_bytes<D>();
   static bool opted = false;
@@ -555,13 +674,38 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const Params& p, dim3 
     if (e != cudaSuccess) return refuse((int)e, "attention_umma: shared memory opt-in failed: %s", cudaGetErrorString(e));
     opted = true;
   }
-  launch_pdl(k, grid, dim3(NTHREADS), sm, stream, mq, mkv, p);
+  launch_pdl_cluster(k, grid, dim3(NTHREADS), dim3(p.ksplit, 1, 1), sm, stream, mq, mkv, p);
   return cuda_status("attention_umma");
+}
+
+template <int D>
+int max_clusters(int key_splits) {
+  auto k = attention_umma_kernel<D>;
+  constexpr size_t sm = smem_bytes<D>();
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  if (e != cudaSuccess) return -refuse((int)e, "attention_umma: shared memory opt-in failed: %s", cudaGetErrorString(e));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(key_splits * 64, 1, 1); cfg.blockDim = dim3(NTHREADS); cfg.dynamicSmemBytes = sm;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = key_splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  int n = 0;
+  e = cudaOccupancyMaxActiveClusters(&n, k, &cfg);
+  if (e != cudaSuccess) return -refuse((int)e, "attention_umma: cluster occupancy query failed: %s", cudaGetErrorString(e));
+  return n;
 }
 
 }  // namespace
 
 DINFER_DEFINE_LAST_ERROR()
+
+// How many clusters of key_splits CTAs of this kernel the device runs at a time (negative: an error code).
+DINFER_API int dinfer_attention_umma_max_clusters(int D, int key_splits) {
+  if ((D != 64 && D != 128) || (key_splits != 1 && key_splits != 2 && key_splits != 4 && key_splits != 8))
+    return -refuse(DINFER_BAD_ARGUMENT, "attention_umma: no such kernel (head_dim %d, key_splits %d)", D, key_splits);
+  return D == 64 ? max_clusters<64>(key_splits) : max_clusters<128>(key_splits);
+}
 
 DINFER_API int dinfer_attention_umma_supports(int D, int group, int block_size) {
   return (D == 64 || D == 128) && group >= 1 && group <= 128 && (128 % group) == 0 && block_size >= 8 &&
@@ -569,12 +713,14 @@ DINFER_API int dinfer_attention_umma_supports(int D, int group, int block_size) 
 }
 
 // Prompt portions (q_len > 1) only; requests that bring one token are skipped.
+// key_splits (1, 2, 4 or 8): that many CTAs of a cluster share the keys of a row-tile pair and fold their results
+// through distributed shared memory; for steps with fewer row tiles than the device has SMs.
 // q: [T, ...] rows of stride ldq with head h at h*D (all H heads); cache [num_blocks, 2, Hkv, block, D] bf16.
 DINFER_API int dinfer_attention_umma(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
                                      int64_t num_blocks, const int* block_table, int max_blocks,
                                      const int* cu_seqlens, const int* seq_lens, int T, int B, int H, int Hkv, int D,
-                                     int block_size, float scale, int window, int max_q_len, int* status,
-                                     cudaStream_t stream) {
+                                     int block_size, float scale, int window, int max_q_len, int key_splits,
+                                     int* status, cudaStream_t stream) {
   if (T <= 0 || B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || max_blocks <= 0 || num_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_umma: bad sizes T=%d B=%d H=%d Hkv=%d", T, B, H, Hkv);
   const int group = H / Hkv;
@@ -586,6 +732,8 @@ DINFER_API int dinfer_attention_umma(const void* q, int64_t ldq, void* out, int6
       (reinterpret_cast<uintptr_t>(cache) & 15))
     return refuse(DINFER_BAD_ARGUMENT, "attention_umma: rows and bases must be 16-byte aligned");
   if (!status) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: a status word is required");
+  if (key_splits != 1 && key_splits != 2 && key_splits != 4 && key_splits != 8)
+    return refuse(DINFER_BAD_ARGUMENT, "attention_umma: key_splits must be 1, 2, 4 or 8, got %d", key_splits);
   if (Hkv > 65535 || B > 65535) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: too many heads or requests for the grid");
   const int64_t cache_rows = num_blocks * 2 * Hkv * block_size;
   if (cache_rows > 0x7fffffffLL) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: the cache has too many rows for a tensor map coordinate");
@@ -619,6 +767,7 @@ DINFER_API int dinfer_attention_umma(const void* q, int64_t ldq, void* out, int6
   p.bs_log2 = 0;
   while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
   p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-  dim3 grid(Hkv, ((int64_t)max_q_len * group + 2 * BM - 1) / (2 * BM), B);
+  p.ksplit = key_splits;
+  dim3 grid(Hkv * key_splits, ((int64_t)max_q_len * group + 2 * BM - 1) / (2 * BM), B);
   return D == 64 ? launch<64>(mq, mkv, p, grid, stream) : launch<128>(mq, mkv, p, grid, stream);
 }

@@ -102,12 +102,46 @@ def umma_supported(dtype: torch.dtype, head_dim: int, group: int, block_size: in
             and block_size >= 8 and block_size & (block_size - 1) == 0)
 
 
+_UMMA_CLUSTERS = {}
+
+
+def umma_max_clusters(head_dim: int, key_splits: int) -> int:
+    """Clusters of ``key_splits`` CTAs of the prompt attention that the device runs at a time (asked once)."""
+    key = (torch.cuda.current_device(), head_dim, key_splits)
+    if key not in _UMMA_CLUSTERS:
+        lib, f = _fn("attention_umma", "dinfer_attention_umma_max_clusters", [c_int, c_int])
+        n = f(head_dim, key_splits)
+        if n < 0:
+            msg = lib.dinfer_last_error()
+            raise KernelError(f"attention_umma_max_clusters failed (code {-n}): {msg.decode('utf-8', 'replace') if msg else ''}")
+        _UMMA_CLUSTERS[key] = n
+    return _UMMA_CLUSTERS[key]
+
+
+def umma_key_splits(portion_lens, group: int, num_kv_heads: int, head_dim: int, max_seq_len: int) -> int:
+    """How many CTAs share the keys of one 256-row tile pair of the prompt attention.  A CTA walks its
+    128-key tiles one after the other, so a step with fewer tile pairs than SMs (one portion of 512
+    tokens behind a long history: 64 pairs at 8 kv heads) leaves SMs idle while the others run long
+    chains.  The keys are split as far as all clusters still run at the same time (a second wave
+    would cost more than the shorter chains save), each CTA keeping at least four tiles of the
+    longest request; at most 8 ways (the portable cluster size).
+    ``portion_lens``: tokens each request brings in this step (those with one token do not count)."""
+    pairs = sum((n * group + 255) // 256 for n in portion_lens if n > 1) * num_kv_heads
+    if pairs <= 0:
+        return 1
+    tiles = (max_seq_len + 127) // 128
+    splits = 1
+    while splits < 8 and tiles >= splits * 2 * 4 and pairs <= umma_max_clusters(head_dim, splits * 2):
+        splits *= 2
+    return splits
+
+
 def attention_umma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                    cu_seqlens: torch.Tensor, seq_lens: torch.Tensor, num_heads: int, num_kv_heads: int,
-                   head_dim: int, scale: float, window: int, max_q_len: int) -> torch.Tensor:
+                   head_dim: int, scale: float, window: int, max_q_len: int, key_splits: int = 1) -> torch.Tensor:
     """Attention of the prompt portions of the batch (requests with more than one token; the others
     are skipped) on tcgen05 / TMEM / TMA.  ``q``: the [T, H*D] columns of the step's rows (a view with a
-    row stride is fine)."""
+    row stride is fine).  ``key_splits``: see ``umma_key_splits``."""
     from . import gemm_ops
     require_cuda(q, out, cache, block_table, cu_seqlens, seq_lens)
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
@@ -123,10 +157,11 @@ def attention_umma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
     status = gemm_ops._state(q.device)["status"]
     lib, f = _fn("attention_umma", "dinfer_attention_umma",
                  [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
-                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p])
     check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), cache.shape[0], ptr(block_table),
                  block_table.shape[1], ptr(cu_seqlens), ptr(seq_lens), q.shape[0], B, num_heads, num_kv_heads,
-                 head_dim, cache.shape[3], float(scale), int(window), int(max_q_len), ptr(status), stream_handle()),
+                 head_dim, cache.shape[3], float(scale), int(window), int(max_q_len), int(key_splits), ptr(status),
+                 stream_handle()),
           "attention_umma")
     return out
 

@@ -141,8 +141,15 @@ class GQAttention(Mixer):
             tc_prefill = ctx.any_prefill
             if ctx.any_prefill and attention_ops.umma_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size):
                 # prompt portions: tcgen05 / TMEM / TMA
+                key = ("umma_key_splits", self.H, self.Hkv)
+                key_splits = ctx.derived.get(key)
+                if key_splits is None:
+                    cu = ctx.cu_seqlens_host
+                    lens = [cu[i + 1] - cu[i] for i in range(len(cu) - 1)] or [ctx.max_q_len]
+                    key_splits = ctx.derived[key] = attention_ops.umma_key_splits(
+                        lens, self.H // self.Hkv, self.Hkv, self.D, ctx.max_seq_len)
                 attention_ops.attention_umma(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
-                                             self.Hkv, self.D, self.scale, window, ctx.max_q_len)
+                                             self.Hkv, self.D, self.scale, window, ctx.max_q_len, key_splits)
                 tc_prefill = False
             if tc_decode or tc_prefill:
                 attention_ops.attention_tc(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,

@@ -12,7 +12,7 @@ No part knows which model it is in.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
@@ -78,6 +78,8 @@ class StepContext:
     seq_lens_host: Sequence[int] = ()
     state_slots_host: Sequence[int] = ()
     state_fresh_host: Sequence[int] = ()
+    # numbers a part derives from the host copies once per step and shares between its layers
+    derived: Dict[Any, Any] = field(default_factory=dict)
 
 
 @dataclass

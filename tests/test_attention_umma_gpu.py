@@ -11,7 +11,7 @@ from test_kernels_gpu import paged_case, plain_paged
 pytestmark = pytest.mark.gpu
 
 
-def run(reqs, H, Hkv, D, bs, window, seed):
+def run(reqs, H, Hkv, D, bs, window, seed, key_splits=1):
     from dinfer_b200.kernels import attention_ops as A
     from dinfer_b200.kernels import gemm_ops as G
     rng = random.Random(seed)
@@ -23,7 +23,7 @@ def run(reqs, H, Hkv, D, bs, window, seed):
     wide[:, :H * D] = q.reshape(T, H * D).cuda()
     out = torch.full((T, H * D), 7.0, dtype=torch.bfloat16, device="cuda")
     A.attention_umma(wide[:, :H * D], out, cache.cuda(), table.cuda(), cu.cuda(), seq.cuda(), H, Hkv, D, scale,
-                     window or 0, max(n for _, n in reqs))
+                     window or 0, max(n for _, n in reqs), key_splits)
     G.check_status()
     want = plain_paged(reqs, qs, ks, vs, scale, window).reshape(T, H * D)
     got = out.double().cpu()
@@ -48,6 +48,57 @@ def test_long_prompt_and_history():
     run([(0, 1100)], 8, 2, 128, 16, None, seed=1)
     run([(1500, 700), (3, 129)], 8, 2, 128, 16, None, seed=2)
     run([(900, 260)], 4, 1, 64, 16, 333, seed=3)
+
+
+@pytest.mark.parametrize("key_splits", [2, 4, 8])
+@pytest.mark.parametrize("H,Hkv,D,bs,window", [(8, 2, 128, 16, None), (4, 4, 128, 8, 300), (8, 4, 64, 16, None),
+                                               (2, 1, 64, 32, 70), (16, 1, 128, 64, None)])
+def test_keys_split_over_the_ctas_of_a_cluster(H, Hkv, D, bs, window, key_splits):
+    """The keys of a row-tile pair dealt out to 2, 4 or 8 CTAs that fold their results through distributed shared
+    memory: requests with fewer key tiles than CTAs (some CTAs hold nothing, and for the earliest rows of a prompt
+    without history only the first does), a second row tile that does not exist or has a tile less, a window that
+    cuts the early tiles away, long histories, decoded tokens left alone."""
+    reqs = [(1500, 300), (0, 1), (0, 40), (900, 33), (0, 600), (127, 2), (260, 64), (3000, 1), (640, 129)]
+    run(reqs, H, Hkv, D, bs, window, seed=key_splits * 1000 + H * D + bs, key_splits=key_splits)
+
+
+def test_keys_split_and_a_far_key_in_another_cta():
+    """One key decides every row and lies in the first CTA's share; the rows are written by all four CTAs."""
+    from dinfer_b200.kernels import attention_ops as A
+    from dinfer_b200.kernels import gemm_ops as G
+    H, Hkv, D, bs = 4, 2, 128, 16
+    rng = random.Random(14)
+    hist, new, far = 2000, 128, 37
+    q, cache, table, cu, pos, qs, ks, vs = paged_case(rng, [(hist, new)], H, Hkv, D, bs, torch.bfloat16)
+    q[:] = 0
+    q[:, :, 0] = 100.0
+    cache[:, 0, :, :, 0] = 0
+    blk = int(table[0, far // bs])
+    cache[blk, 0, :, far % bs, 0] = 10.0
+    seq = torch.tensor([hist + new], dtype=torch.int32)
+    for key_splits in (2, 4, 8):
+        out = torch.empty(new, H * D, dtype=torch.bfloat16, device="cuda")
+        A.attention_umma(q.reshape(new, H * D).cuda(), out, cache.cuda(), table.cuda(), cu.cuda(), seq.cuda(), H, Hkv, D,
+                         1.0, 0, new, key_splits)
+        G.check_status()
+        want = cache[blk, 1, :, far % bs].float().repeat_interleave(H // Hkv, 0)
+        for t in (0, new // 2, new - 1):
+            assert torch.allclose(out[t].float().reshape(H, D).cpu(), want, atol=2e-2), (key_splits, t)
+
+
+def test_key_split_choice():
+    """As many ways as keep every cluster running at once and leave a CTA four key tiles."""
+    from dinfer_b200.kernels import attention_ops as A
+    assert A.umma_key_splits([1, 1, 1], 4, 8, 128, 4096) == 1              # no portion
+    assert A.umma_key_splits([2048], 4, 8, 128, 2048) == 1                 # 256 tile pairs: more than SMs
+    assert A.umma_key_splits([64], 4, 8, 128, 256) == 1                    # two tiles: nothing to share
+    for lens, seq in (([512, 1, 1], 4096), ([64], 100000), ([256, 300], 8192)):
+        got = A.umma_key_splits(lens, 4, 8, 128, seq)
+        pairs = sum((n * 4 + 255) // 256 for n in lens if n > 1) * 8
+        assert got in (1, 2, 4, 8)
+        assert got == 1 or (pairs <= A.umma_max_clusters(128, got) and (seq + 127) // 128 >= got * 4)
+        assert got == 8 or (seq + 127) // 128 < got * 8 or pairs > A.umma_max_clusters(128, got * 2)
+    assert A.umma_max_clusters(128, 1) >= A.umma_max_clusters(128, 2) * 2 - 2 > 0
 
 
 def test_more_pages_than_the_shared_memory_table_holds():
