@@ -18,8 +18,11 @@
 // A row tile's chain is  Q K^T -> softmax -> P V, Q K^T of the next tile -> ...; the one issuing thread serves the two
 // row tiles strictly in turn and puts P V and the next Q K^T into the tensor pipe together, which runs them in order:
 // the next S overwrites P only after P V has read it, and the tensor core works for one row tile while the
-// other's softmax computes.  No cluster launch, no multicast.  Every mbarrier wait is bounded; the named barriers
-// between the two warps of a row are passed by both even after a wait has run out.
+// other's softmax computes.  Every mbarrier wait is bounded; the named barriers between the two warps of a row
+// are passed by both even after a wait has run out.
+// With key_splits > 1 the launch is a cluster of that many CTAs on one row-tile pair: each takes a run of the
+// pair's key tiles, and the partial results (O, reference maximum, sum) are folded through distributed shared
+// memory behind two cluster barriers, each CTA writing out a share of the 256 rows.  No multicast.
 //
 // Counterpart in the reference: gqa_fa_v5_kernel (crates/kernels/cuda/gqa.cu:167-369, mma.sync) for this
 // head size; its tcgen05 attention (crates/kernels/cuda/gqa_fa_sm100.cu) exists for D = 256 only and stages

@@ -141,7 +141,7 @@ class GQAttention(Mixer):
             tc_prefill = ctx.any_prefill
             if ctx.any_prefill and attention_ops.umma_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size):
                 # prompt portions: tcgen05 / TMEM / TMA
-                key = ("umma_key_splits", self.H, self.Hkv)
+                key = ("umma_key_splits", self.H, self.Hkv, self.D)
                 key_splits = ctx.derived.get(key)
                 if key_splits is None:
                     cu = ctx.cu_seqlens_host
