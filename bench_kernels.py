@@ -12,7 +12,8 @@ graph's CUDA-event time divided by its launches.  Beside each time stands the ti
     python bench_kernels.py --impl reference    # the reference's own kernels beside this package's (see below)
 
 Sections: gemm_decode (tcgen05 swapped-operand product per split count), gemm_prompt (tcgen05 product
-and the library's), attention_decode (per split count), attention_prompt, sampling.
+and the library's), attention_decode (per split count), attention_prompt, attention_portion (a portion of a
+long prompt, per key split), sampling.
 
 ``--impl reference``: the same shapes and the same timing method for the reference's own CUDA kernels (norms, gate,
 q/k post-processing, prompt and decode attention, small-M products, sampling), compiled unmodified for sm_100a by
@@ -182,7 +183,15 @@ def attention_prompt(s, tokens_list, tflops):
         print(f"tokens {T:5d} | tcgen05 {t_umma:7.1f} us {flops / t_umma * 1e-6:6.1f} TFLOP/s"
               f" | mma.sync {t_tc:7.1f} us {flops / t_tc * 1e-6:6.1f} TFLOP/s | at peak {flops / tflops * 1e-6:6.1f} us", flush=True)
         del caches
-    print("# attention_prompt, a portion behind a history: us per launch by the CTAs that share a row-tile pair's keys;"
+    G.check_status()
+
+
+def attention_portion(s, tflops):
+    """The tcgen05 prompt attention on one portion of a long prompt (chunked prefill): few row tiles, long histories."""
+    from dinfer_b200.kernels import attention_ops as A
+    from dinfer_b200.kernels import gemm_ops as G
+    H, Hkv, D, bs = s["heads"], s["kv_heads"], s["head_dim"], s["block_size"]
+    print("# attention_portion: a portion behind a history, us per launch by the CTAs that share a row-tile pair's keys;"
           " 'auto' is the engine's choice")
     for P, C in ((512, 4096), (512, 16384), (256, 8192), (128, 4096), (1024, 8192)):
         caches, table = paged_cache(1, C, Hkv, D, bs, 4)
@@ -232,7 +241,7 @@ def sampling(vocab, rows_list):
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--only", choices=["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "sampling",
+    ap.add_argument("--only", choices=["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "attention_portion", "sampling",
                                        "small_ops"])
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours",
                     help="reference: time the reference's own kernels beside this package's")
@@ -251,7 +260,7 @@ def main() -> int:
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
         import ref_kernels
         return ref_kernels.run(sys.modules[__name__], a, hbm, tflops)
-    todo = [a.only] if a.only else ["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "sampling"]
+    todo = [a.only] if a.only else ["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "attention_portion", "sampling"]
     if "gemm_decode" in todo:
         gemm_decode(SHAPE, a.tokens, hbm)
     if "gemm_prompt" in todo:
@@ -260,6 +269,8 @@ def main() -> int:
         attention_decode(SHAPE, a.batches, a.contexts, hbm)
     if "attention_prompt" in todo:
         attention_prompt(SHAPE, a.prompt_tokens, tflops)
+    if "attention_portion" in todo:
+        attention_portion(SHAPE, tflops)
     if "sampling" in todo:
         sampling(151936, a.batches)
     return 0
