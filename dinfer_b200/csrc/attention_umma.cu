@@ -223,9 +223,8 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   __shared__ float s_max[2][2][2][BM];                    // a tile's row maxima, by the halves of its keys
   __shared__ float x_max[2 * BM], x_sum[2 * BM];          // what the other CTAs of a cluster found for the rows this one writes
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int ks = p.ksplit;
-  const int rank = ks > 1 ? (int)cluster_ctarank() : 0;   // the cluster spans ks neighbours of the grid's x
-  const int b = blockIdx.z, hk = blockIdx.x / ks;
+  const int rank = p.ksplit > 1 ? (int)cluster_ctarank() : 0;   // the cluster spans ksplit neighbours of the grid's x
+  const int b = blockIdx.z, hk = blockIdx.x / p.ksplit;
   pdl_enter();
   const int t0 = p.cu_seqlens[b];
   const int q_len = p.cu_seqlens[b + 1] - t0;
@@ -248,6 +247,11 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const int tile_first = lo / BN;
   const int n_all = (hi + BN - 1) / BN - tile_first;   // tiles of B (or of A when B does not exist)
   const int n_all_a = (hi_a + BN - 1) / BN - tile_first;
+  // The launch's split is an upper bound (a graph is captured for the longest request there may be): a pair is
+  // shared by as many CTAs as leave each at least four tiles; the cluster's other CTAs have nothing to do with it.
+  int ks = p.ksplit;
+  while (ks > 1 && n_all < 4 * ks) ks >>= 1;
+  if (rank >= ks) return;
   const int per = (n_all + ks - 1) / ks;
   const int tile_begin = tile_first + rank * per;
   const int n_tiles = max(0, min(per, n_all - rank * per));

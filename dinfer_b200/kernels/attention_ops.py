@@ -124,7 +124,9 @@ def umma_key_splits(portion_lens, group: int, num_kv_heads: int, head_dim: int, 
     tokens behind a long history: 64 pairs at 8 kv heads) leaves SMs idle while the others run long
     chains.  The keys are split as far as all clusters still run at the same time (a second wave
     would cost more than the shorter chains save), each CTA keeping at least four tiles of the
-    longest request; at most 8 ways (the portable cluster size).
+    longest request; at most 8 ways (the portable cluster size).  The count is an upper bound: in the
+    kernel a pair with fewer key tiles is shared by fewer CTAs and the rest of its cluster leaves at
+    once, so a graph captured for the longest request there may be costs a short one nothing.
     ``portion_lens``: tokens each request brings in this step (those with one token do not count)."""
     pairs = sum((n * group + 255) // 256 for n in portion_lens if n > 1) * num_kv_heads
     if pairs <= 0:
