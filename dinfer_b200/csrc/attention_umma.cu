@@ -45,7 +45,7 @@ struct Params {
   __nv_bfloat16* out; int64_t ldo;
   const int* block_table; int max_blocks;
   const int* cu_seqlens; const int* seq_lens;
-  int H, Hkv, group, block_size, bs_log2, window;
+  int B, H, Hkv, group, block_size, bs_log2, window;
   int ksplit;                          // CTAs of a cluster that share a row-tile pair's keys (1, 2, 4 or 8)
   float scale_log2;
   int* status;
@@ -224,16 +224,47 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   __shared__ float x_max[2 * BM], x_sum[2 * BM];          // what the other CTAs of a cluster found for the rows this one writes
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = p.ksplit > 1 ? (int)cluster_ctarank() : 0;   // the cluster spans ksplit neighbours of the grid's x
-  const int b = blockIdx.z, hk = blockIdx.x / p.ksplit;
+  const int hk = blockIdx.x / p.ksplit;
   pdl_enter();
+  // The grid's y counts the row-tile pairs of the whole batch (an upper bound of them): which request's pair this
+  // is comes from the portions' lengths, summed by every warp for itself.  Requests that bring one token have no
+  // pair (they belong to the decode kernel), so a step with many of them launches no CTAs for them.
+  int b = -1, pair = 0, pairs_b = 0;
+  {
+    const int y = blockIdx.y;
+    int before = 0;
+    for (int i0 = 0; i0 < p.B; i0 += 32) {
+      const int i = i0 + lane;
+      int n = 0;
+      if (i < p.B) {
+        const int ql = p.cu_seqlens[i + 1] - p.cu_seqlens[i];
+        n = ql > 1 ? (ql * p.group + 2 * BM - 1) / (2 * BM) : 0;
+      }
+      int incl = n;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += v;
+      }
+      const int chunk = __shfl_sync(0xffffffffu, incl, 31);
+      if (y < before + chunk) {
+        const unsigned hit = __ballot_sync(0xffffffffu, y >= before + incl - n && y < before + incl);
+        const int src = __ffs(hit) - 1;
+        b = i0 + src;
+        pair = y - before - __shfl_sync(0xffffffffu, incl - n, src);
+        pairs_b = __shfl_sync(0xffffffffu, n, src);
+        break;
+      }
+      before += chunk;
+    }
+  }
+  if (b < 0) return;                                   // beyond the batch's pairs
   const int t0 = p.cu_seqlens[b];
   const int q_len = p.cu_seqlens[b + 1] - t0;
-  if (q_len <= 1) return;                              // decoded tokens belong to the decode kernel
   const int rows_total = q_len * p.group;
-  // CTAs start in the order of blockIdx (x fastest): every kv head of the longest (latest) row tile first,
-  // so that the long CTAs do not start last and leave the other SMs idle at the end
-  const int row0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * 2 * BM;
-  if (row0 >= rows_total) return;
+  // CTAs start in the order of blockIdx (x fastest): every kv head of a request's longest (latest) row tile
+  // first, so that the long CTAs do not start last and leave the other SMs idle at the end
+  const int row0 = (pairs_b - 1 - pair) * 2 * BM;
   const int hist = p.seq_lens[b] - q_len;
   const int* table = p.block_table + (int64_t)b * p.max_blocks;
   const bool b_on = row0 + BM < rows_total;            // the second row tile exists
@@ -720,14 +751,16 @@ DINFER_API int dinfer_attention_umma_supports(int D, int group, int block_size) 
 }
 
 // Prompt portions (q_len > 1) only; requests that bring one token are skipped.
+// pair_bound: an upper bound of the batch's row-tile pairs, sum over the portions of ceil(tokens * group / 256)
+// (0: B times the longest portion's); CTAs beyond the pairs there are return at once.
 // key_splits (1, 2, 4 or 8): that many CTAs of a cluster share the keys of a row-tile pair and fold their results
 // through distributed shared memory; for steps with fewer row tiles than the device has SMs.
 // q: [T, ...] rows of stride ldq with head h at h*D (all H heads); cache [num_blocks, 2, Hkv, block, D] bf16.
 DINFER_API int dinfer_attention_umma(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
                                      int64_t num_blocks, const int* block_table, int max_blocks,
                                      const int* cu_seqlens, const int* seq_lens, int T, int B, int H, int Hkv, int D,
-                                     int block_size, float scale, int window, int max_q_len, int key_splits,
-                                     int* status, cudaStream_t stream) {
+                                     int block_size, float scale, int window, int max_q_len, int pair_bound,
+                                     int key_splits, int* status, cudaStream_t stream) {
   if (T <= 0 || B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || max_blocks <= 0 || num_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_umma: bad sizes T=%d B=%d H=%d Hkv=%d", T, B, H, Hkv);
   const int group = H / Hkv;
@@ -741,7 +774,7 @@ DINFER_API int dinfer_attention_umma(const void* q, int64_t ldq, void* out, int6
   if (!status) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: a status word is required");
   if (key_splits != 1 && key_splits != 2 && key_splits != 4 && key_splits != 8)
     return refuse(DINFER_BAD_ARGUMENT, "attention_umma: key_splits must be 1, 2, 4 or 8, got %d", key_splits);
-  if (Hkv > 65535 || B > 65535) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: too many heads or requests for the grid");
+  if ((int64_t)Hkv * key_splits > 0x7fffffffLL) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: too many heads for the grid");
   const int64_t cache_rows = num_blocks * 2 * Hkv * block_size;
   if (cache_rows > 0x7fffffffLL) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: the cache has too many rows for a tensor map coordinate");
   EncodeTiledFn fn = encode_fn();
@@ -774,7 +807,10 @@ DINFER_API int dinfer_attention_umma(const void* q, int64_t ldq, void* out, int6
   p.bs_log2 = 0;
   while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
   p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-  p.ksplit = key_splits;
-  dim3 grid(Hkv * key_splits, ((int64_t)max_q_len * group + 2 * BM - 1) / (2 * BM), B);
+  p.ksplit = key_splits; p.B = B;
+  // pairs of 128-row tiles in the batch: the caller's bound, or every request taken for the longest
+  int64_t pairs = pair_bound > 0 ? pair_bound : (int64_t)B * (((int64_t)max_q_len * group + 2 * BM - 1) / (2 * BM));
+  if (pairs > 65535) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: %lld row-tile pairs are too many for the grid", (long long)pairs);
+  dim3 grid(Hkv * key_splits, (unsigned)pairs, 1);
   return D == 64 ? launch<64>(mq, mkv, p, grid, stream) : launch<128>(mq, mkv, p, grid, stream);
 }

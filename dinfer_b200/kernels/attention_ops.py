@@ -118,6 +118,16 @@ def umma_max_clusters(head_dim: int, key_splits: int) -> int:
     return _UMMA_CLUSTERS[key]
 
 
+def umma_pair_bound(portion_lens, group: int) -> int:
+    """An upper bound of the 256-row tile pairs of a step's prompt portions, which the kernel's grid counts.  It
+    holds for every way of spreading the same prompt tokens over the same places (a captured graph is replayed
+    on portions of other lengths): places without tokens count as places, requests that bring one token (they
+    belong to the decode kernel) do not."""
+    tokens = sum(n for n in portion_lens if n != 1)
+    places = sum(1 for n in portion_lens if n != 1)
+    return max(1, (tokens * group + 255 * places) // 256)
+
+
 def umma_key_splits(portion_lens, group: int, num_kv_heads: int, head_dim: int, max_seq_len: int) -> int:
     """How many CTAs share the keys of one 256-row tile pair of the prompt attention.  A CTA walks its
     128-key tiles one after the other, so a step with fewer tile pairs than SMs (one portion of 512
@@ -140,10 +150,12 @@ def umma_key_splits(portion_lens, group: int, num_kv_heads: int, head_dim: int, 
 
 def attention_umma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                    cu_seqlens: torch.Tensor, seq_lens: torch.Tensor, num_heads: int, num_kv_heads: int,
-                   head_dim: int, scale: float, window: int, max_q_len: int, key_splits: int = 1) -> torch.Tensor:
+                   head_dim: int, scale: float, window: int, max_q_len: int, key_splits: int = 1,
+                   pair_bound: int = 0) -> torch.Tensor:
     """Attention of the prompt portions of the batch (requests with more than one token; the others
     are skipped) on tcgen05 / TMEM / TMA.  ``q``: the [T, H*D] columns of the step's rows (a view with a
-    row stride is fine).  ``key_splits``: see ``umma_key_splits``."""
+    row stride is fine).  ``key_splits``: see ``umma_key_splits``; ``pair_bound``: see ``umma_pair_bound``
+    (0: every request is taken for the longest portion)."""
     from . import gemm_ops
     require_cuda(q, out, cache, block_table, cu_seqlens, seq_lens)
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
@@ -159,10 +171,10 @@ def attention_umma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
     status = gemm_ops._state(q.device)["status"]
     lib, f = _fn("attention_umma", "dinfer_attention_umma",
                  [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
-                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p])
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), cache.shape[0], ptr(block_table),
                  block_table.shape[1], ptr(cu_seqlens), ptr(seq_lens), q.shape[0], B, num_heads, num_kv_heads,
-                 head_dim, cache.shape[3], float(scale), int(window), int(max_q_len), int(key_splits), ptr(status),
+                 head_dim, cache.shape[3], float(scale), int(window), int(max_q_len), int(pair_bound), int(key_splits), ptr(status),
                  stream_handle()),
           "attention_umma")
     return out

@@ -141,15 +141,17 @@ class GQAttention(Mixer):
             tc_prefill = ctx.any_prefill
             if ctx.any_prefill and attention_ops.umma_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size):
                 # prompt portions: tcgen05 / TMEM / TMA
-                key = ("umma_key_splits", self.H, self.Hkv, self.D)
-                key_splits = ctx.derived.get(key)
-                if key_splits is None:
+                key = ("attention_umma", self.H, self.Hkv, self.D)
+                shape = ctx.derived.get(key)
+                if shape is None:
                     cu = ctx.cu_seqlens_host
-                    lens = [cu[i + 1] - cu[i] for i in range(len(cu) - 1)] or [ctx.max_q_len]
-                    key_splits = ctx.derived[key] = attention_ops.umma_key_splits(
-                        lens, self.H // self.Hkv, self.Hkv, self.D, ctx.max_seq_len)
+                    lens = [cu[i + 1] - cu[i] for i in range(len(cu) - 1)]
+                    group = self.H // self.Hkv
+                    shape = ctx.derived[key] = (
+                        attention_ops.umma_key_splits(lens or [ctx.max_q_len], group, self.Hkv, self.D, ctx.max_seq_len),
+                        attention_ops.umma_pair_bound(lens, group) if lens else 0)
                 attention_ops.attention_umma(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
-                                             self.Hkv, self.D, self.scale, window, ctx.max_q_len, key_splits)
+                                             self.Hkv, self.D, self.scale, window, ctx.max_q_len, shape[0], shape[1])
                 tc_prefill = False
             if tc_decode or tc_prefill:
                 attention_ops.attention_tc(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,

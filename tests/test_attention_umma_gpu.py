@@ -23,7 +23,8 @@ def run(reqs, H, Hkv, D, bs, window, seed, key_splits=1):
     wide[:, :H * D] = q.reshape(T, H * D).cuda()
     out = torch.full((T, H * D), 7.0, dtype=torch.bfloat16, device="cuda")
     A.attention_umma(wide[:, :H * D], out, cache.cuda(), table.cuda(), cu.cuda(), seq.cuda(), H, Hkv, D, scale,
-                     window or 0, max(n for _, n in reqs), key_splits)
+                     window or 0, max(n for _, n in reqs), key_splits,
+                     A.umma_pair_bound([n for _, n in reqs], H // Hkv) if seed % 2 else 0)   # the step's own bound, or none
     G.check_status()
     want = plain_paged(reqs, qs, ks, vs, scale, window).reshape(T, H * D)
     got = out.double().cpu()
@@ -84,6 +85,14 @@ def test_keys_split_and_a_far_key_in_another_cta():
         want = cache[blk, 1, :, far % bs].float().repeat_interleave(H // Hkv, 0)
         for t in (0, new // 2, new - 1):
             assert torch.allclose(out[t].float().reshape(H, D).cpu(), want, atol=2e-2), (key_splits, t)
+
+
+def test_many_decoding_requests_beside_a_portion():
+    """The grid counts the batch's row-tile pairs, not requests: 300 requests that bring one token each, before,
+    between and behind three portions."""
+    reqs = [(50 + i, 1) for i in range(120)] + [(700, 200)] + [(9, 1)] * 100 + [(0, 300), (128, 2)] + [(77, 1)] * 80
+    run(reqs, 8, 2, 128, 16, None, seed=21, key_splits=2)
+    run(reqs, 4, 4, 64, 8, 90, seed=22)
 
 
 def test_key_split_choice():

@@ -143,3 +143,21 @@ def test_slots_and_tables_of_groups_with_page_sizes_of_their_own():
     assert g0.block_table[0].tolist() == big + [-1] * 5 and g1.block_table[0].tolist() == small
     assert g0.slot_mapping.tolist() == [big[p // 8] * 8 + p % 8 for p in range(13)]
     assert g1.slot_mapping.tolist() == [small[p // 2] * 2 + p % 2 for p in range(13)]
+
+
+def test_pair_bound_of_the_prompt_attention_holds_for_every_spread_of_the_tokens():
+    """A graph is captured with all prompt tokens in one place and replayed with them spread over the places: the
+    bound made at capture covers every such spread, and requests with one token add nothing."""
+    import random
+    from dinfer_b200.kernels.attention_ops import umma_pair_bound
+    rng = random.Random(5)
+    for _ in range(300):
+        group = rng.choice([1, 2, 4, 8, 16])
+        places = rng.choice([1, 4, 16])
+        total = rng.randint(2, 3000)
+        decodes = [1] * rng.randint(0, 70)
+        bound = umma_pair_bound([total] + [0] * (places - 1) + decodes, group)
+        cuts = sorted(rng.randint(0, total) for _ in range(places - 1))
+        lens = [b - a for a, b in zip([0] + cuts, cuts + [total])]
+        pairs = sum((n * group + 255) // 256 for n in lens if n > 1)
+        assert pairs <= bound <= (total * group) // 256 + places, (lens, group, bound)
