@@ -12,8 +12,8 @@ graph's CUDA-event time divided by its launches.  Beside each time stands the ti
     python bench_kernels.py --impl reference    # the reference's own kernels beside this package's (see below)
 
 Sections: gemm_decode (tcgen05 swapped-operand product per split count), gemm_prompt (tcgen05 product
-and the library's), attention_decode (per split count), attention_prompt, attention_portion (a portion of a
-long prompt, per key split), sampling.
+and the library's), attention_decode (per split count), attention_prompt, attention_short (short whole prompts, the two
+tcgen05 kernels), attention_portion (a portion of a long prompt, per key split), sampling.
 
 ``--impl reference``: the same shapes and the same timing method for the reference's own CUDA kernels (norms, gate,
 q/k post-processing, prompt and decode attention, small-M products, sampling), compiled unmodified for sm_100a by
@@ -186,6 +186,31 @@ def attention_prompt(s, tokens_list, tflops):
     G.check_status()
 
 
+def attention_short(s):
+    """Whole short prompts, as a serving step takes them in: the two tcgen05 kernels beside each other."""
+    from dinfer_b200.kernels import attention_ops as A
+    from dinfer_b200.kernels import gemm_ops as G
+    H, Hkv, D, bs = s["heads"], s["kv_heads"], s["head_dim"], s["block_size"]
+    print(f"# attention_short: B whole prompts of P tokens in one step, us per launch; the engine takes the 64-key kernel up to "
+          f"{A.UMMA_SHORT_CONTEXT} tokens")
+    for B, P in ((1, 32), (1, 128), (8, 128), (32, 128), (1, 512), (4, 512), (1, 1024)):
+        caches, table = paged_cache(B, P, Hkv, D, bs, 4)
+        cu = torch.arange(0, (B + 1) * P, P, dtype=torch.int32, device="cuda")
+        seq = torch.full((B,), P, dtype=torch.int32, device="cuda")
+        qkv = torch.randn(B * P, (H + 2 * Hkv) * D, device="cuda").to(torch.bfloat16)
+        q = qkv[:, :H * D]
+        out = torch.empty(B * P, H * D, dtype=torch.bfloat16, device="cuda")
+        bound = A.umma_pair_bound([P] * B, H // Hkv)
+        ks = A.umma_key_splits([P] * B, H // Hkv, Hkv, D, P)
+        t128 = graph_time_us(lambda i: A.attention_umma(q, out, caches[i % 4], table, cu, seq, H, Hkv, D, D ** -0.5,
+                                                        0, P, ks, bound), 8)
+        t64 = graph_time_us(lambda i: A.attention_umma64(q, out, caches[i % 4], table, cu, seq, H, Hkv, D, D ** -0.5,
+                                                         0, P, bound), 8)
+        print(f"prompts {B:3d} tokens {P:5d} | 64-key tiles {t64:6.1f} us | 128-key tiles {t128:6.1f} us", flush=True)
+        del caches
+    G.check_status()
+
+
 def attention_portion(s, tflops):
     """The tcgen05 prompt attention on one portion of a long prompt (chunked prefill): few row tiles, long histories."""
     from dinfer_b200.kernels import attention_ops as A
@@ -241,7 +266,7 @@ def sampling(vocab, rows_list):
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--only", choices=["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "attention_portion", "sampling",
+    ap.add_argument("--only", choices=["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "attention_short", "attention_portion", "sampling",
                                        "small_ops"])
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours",
                     help="reference: time the reference's own kernels beside this package's")
@@ -260,7 +285,7 @@ def main() -> int:
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
         import ref_kernels
         return ref_kernels.run(sys.modules[__name__], a, hbm, tflops)
-    todo = [a.only] if a.only else ["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "attention_portion", "sampling"]
+    todo = [a.only] if a.only else ["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "attention_short", "attention_portion", "sampling"]
     if "gemm_decode" in todo:
         gemm_decode(SHAPE, a.tokens, hbm)
     if "gemm_prompt" in todo:
@@ -269,6 +294,8 @@ def main() -> int:
         attention_decode(SHAPE, a.batches, a.contexts, hbm)
     if "attention_prompt" in todo:
         attention_prompt(SHAPE, a.prompt_tokens, tflops)
+    if "attention_short" in todo:
+        attention_short(SHAPE)
     if "attention_portion" in todo:
         attention_portion(SHAPE, tflops)
     if "sampling" in todo:

@@ -37,6 +37,7 @@ LIBRARIES: Dict[str, tuple] = {
     "attention_decode": ("attention_decode.cu", []),
     "gemm_tc": ("gemm_tc.cu", []),
     "attention_umma": ("attention_umma.cu", []),
+    "attention_umma64": ("attention_umma64.cu", []),
     # host-side bookkeeping (page pools, cache manager, decode plans): plain C++, no CUDA
     "host_core": ("host_core.cpp", []),
 }

@@ -240,6 +240,7 @@ class PlanBuilder:
             num_tokens=T, num_reqs=B, positions=view("pos"), cu_seqlens=view("cu"), seq_lens=view("seq"),
             groups=groups, state_slots=view("sslots"), state_fresh=view("fresh"),
             max_q_len=max(lens) if lens else 0, max_seq_len=int(seq.max()) if B else 0,
+            max_prefill_seq_len=max([int(seq[i]) for i, n in enumerate(lens) if n > 1] or [0]),
             all_decode=all(n == 1 for n in lens),
             any_decode=any(n == 1 for n in lens), any_prefill=any(n > 1 for n in lens),
             cu_seqlens_host=cu.tolist(), seq_lens_host=seq.tolist(),

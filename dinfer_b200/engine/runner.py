@@ -91,6 +91,9 @@ class ModelRunner:
     # padded up to a power of two to replay a graph (see graph_shape)
     PROMPT_PLACES = (4, 16)
     PADDED_PROMPT_TOKENS = 128
+    # mixed steps whose prompt requests all stay within this many tokens replay graphs of their own, captured with
+    # that bound in the step context, so that a part may choose its kernel for short contexts there
+    SHORT_CONTEXT = 512
 
     def __init__(self, config_dict: Dict[str, Any], source: WeightSource, engine: EngineConfig):
         engine.check()
@@ -256,7 +259,7 @@ class ModelRunner:
         mixed = None
         if self._graph_ok and len(entries) <= self._buckets[-1] and all(len(e.tokens) == 1 for e in entries):
             logits = self._graph_step(entries, starts)
-        elif self._graph_ok and (mixed := self._mixed_layout(entries)) is not None:
+        elif self._graph_ok and (mixed := self._mixed_layout(entries, starts)) is not None:
             logits = self._mixed_graph_step(entries, starts, *mixed)
         else:
             ids, rows, ctx = self.plan.build(entries, starts)
@@ -348,7 +351,7 @@ class ModelRunner:
         tokens = int(host_s * self.engine.graph_device_flops / (2.0 * max(1, weights)))
         return max(self.PADDED_PROMPT_TOKENS, tokens // 128 * 128)
 
-    def _mixed_layout(self, entries: Sequence[StepEntry]):
+    def _mixed_layout(self, entries: Sequence[StepEntry], starts: Sequence[int]):
         """Steps with prompt portions whose shape comes again replay a graph per (prompt tokens, decode bucket), laid
         out as ``PROMPT_PLACES`` prompt places (a dummy portion that pads the prompt tokens in one of them, the
         unused ones without tokens) followed by the bucket's one-token places (the unused ones dummy rows):
@@ -372,7 +375,8 @@ class ModelRunner:
             return None
         total, n_places, bucket = shape
         have = sum(len(entries[i].tokens) for i in prompts)
-        key = ("mixed", total, n_places, bucket)
+        short = all(starts[i] + len(entries[i].tokens) <= self.SHORT_CONTEXT for i in prompts)
+        key = ("mixed", total, n_places, bucket, short)
         if key not in self._graphs:
             self._mixed_seen[key] = self._mixed_seen.get(key, 0) + 1
             if self._mixed_seen[key] < 2:
@@ -386,7 +390,7 @@ class ModelRunner:
 
     def _capture_mixed(self, key):
         from ..kernels import attention_ops
-        _, total, n_places, bucket = key
+        _, total, n_places, bucket, short = key
         width = self.max_blocks_per_seq
         B = n_places + bucket
         dev = torch.empty(self.plan.words(total + bucket, B, B, width), dtype=torch.int32, device=self.device)
@@ -397,6 +401,7 @@ class ModelRunner:
         hkv = max([n.num_kv_heads for n in self.model.cache_needs() if isinstance(n, KvCacheNeed)] or [1])
         ctx.decode_splits = attention_ops.decode_splits(max(1, bucket), hkv, self.engine.max_model_len)
         ctx.max_seq_len = self.engine.max_model_len
+        ctx.max_prefill_seq_len = min(self.SHORT_CONTEXT, self.engine.max_model_len) if short else self.engine.max_model_len
         ctx.split_norms = False
         ctx.prev_tokens = self.sampled
         rec = self._capture_one(ids, rows, ctx)

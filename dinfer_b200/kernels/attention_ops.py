@@ -10,6 +10,10 @@ from .lib import KernelError, check, num_sms, ptr, require_cuda, stream_handle
 from .ops import _fn
 
 MAX_CLUSTER_SPLITS = 16         # key splits of the TMA decode kernel: one thread-block cluster
+# The prompt attention has a kernel with 64-key tiles beside the one with 128-key tiles: steps whose longest
+# request stays within this many tokens run the first (measured: it wins up to about 512 keys a row, at 1024
+# the two meet, beyond that and behind long histories the second wins)
+UMMA_SHORT_CONTEXT = 512
 
 
 def tc_supported(dtype: torch.dtype, head_dim: int, group: int) -> bool:
@@ -118,6 +122,11 @@ def umma_max_clusters(head_dim: int, key_splits: int) -> int:
     return _UMMA_CLUSTERS[key]
 
 
+def umma64_supported(dtype: torch.dtype, head_dim: int, group: int, block_size: int) -> bool:
+    """The 64-key-tile prompt attention: as ``umma_supported``, with pages of at most 64 tokens."""
+    return umma_supported(dtype, head_dim, group, block_size) and block_size <= 64
+
+
 def umma_pair_bound(portion_lens, group: int) -> int:
     """An upper bound of the 256-row tile pairs of a step's prompt portions, which the kernel's grid counts.  It
     holds for every way of spreading the same prompt tokens over the same places (a captured graph is replayed
@@ -156,6 +165,22 @@ def attention_umma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
     are skipped) on tcgen05 / TMEM / TMA.  ``q``: the [T, H*D] columns of the step's rows (a view with a
     row stride is fine).  ``key_splits``: see ``umma_key_splits``; ``pair_bound``: see ``umma_pair_bound``
     (0: every request is taken for the longest portion)."""
+    _umma_launch(False, q, out, cache, block_table, cu_seqlens, seq_lens, num_heads, num_kv_heads, head_dim, scale,
+                 window, max_q_len, key_splits, pair_bound)
+    return out
+
+
+def attention_umma64(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                     cu_seqlens: torch.Tensor, seq_lens: torch.Tensor, num_heads: int, num_kv_heads: int,
+                     head_dim: int, scale: float, window: int, max_q_len: int, pair_bound: int = 0) -> torch.Tensor:
+    """The same attention through the kernel with 64-key tiles (``UMMA_SHORT_CONTEXT``); no key split."""
+    _umma_launch(True, q, out, cache, block_table, cu_seqlens, seq_lens, num_heads, num_kv_heads, head_dim, scale,
+                 window, max_q_len, 1, pair_bound)
+    return out
+
+
+def _umma_launch(short, q, out, cache, block_table, cu_seqlens, seq_lens, num_heads, num_kv_heads, head_dim, scale,
+                 window, max_q_len, key_splits, pair_bound) -> None:
     from . import gemm_ops
     require_cuda(q, out, cache, block_table, cu_seqlens, seq_lens)
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
@@ -169,15 +194,17 @@ def attention_umma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
     if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
         raise KernelError(f"attention_umma: cache shape {tuple(cache.shape)} is not [blocks, 2, Hkv, block, D]")
     status = gemm_ops._state(q.device)["status"]
-    lib, f = _fn("attention_umma", "dinfer_attention_umma",
-                 [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
-                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), cache.shape[0], ptr(block_table),
-                 block_table.shape[1], ptr(cu_seqlens), ptr(seq_lens), q.shape[0], B, num_heads, num_kv_heads,
-                 head_dim, cache.shape[3], float(scale), int(window), int(max_q_len), int(pair_bound), int(key_splits), ptr(status),
-                 stream_handle()),
-          "attention_umma")
-    return out
+    head = (ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), cache.shape[0], ptr(block_table),
+            block_table.shape[1], ptr(cu_seqlens), ptr(seq_lens), q.shape[0], B, num_heads, num_kv_heads,
+            head_dim, cache.shape[3], float(scale), int(window), int(max_q_len), int(pair_bound))
+    types = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int]
+    if short:
+        lib, f = _fn("attention_umma64", "dinfer_attention_umma64", types + [c_void_p, c_void_p])
+        check(lib, f(*head, ptr(status), stream_handle()), "attention_umma64")
+    else:
+        lib, f = _fn("attention_umma", "dinfer_attention_umma", types + [c_int, c_void_p, c_void_p])
+        check(lib, f(*head, int(key_splits), ptr(status), stream_handle()), "attention_umma")
 
 
 def attention_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,

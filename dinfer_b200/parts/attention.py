@@ -92,7 +92,7 @@ class GQAttention(Mixer):
         if attention_ops.tc_supported(self.env.act_dtype, self.D, self.H // self.Hkv):
             att = ["attention_tc"]
             if self.D in (64, 128):
-                att += ["attention_decode", "attention_umma"]
+                att += ["attention_decode", "attention_umma", "attention_umma64"]
         return ["qk_post"] + att + self.qkv.kernel_libraries() + self.o.kernel_libraries()
 
     def takes_half_normed(self, rows: int) -> bool:
@@ -150,8 +150,13 @@ class GQAttention(Mixer):
                     shape = ctx.derived[key] = (
                         attention_ops.umma_key_splits(lens or [ctx.max_q_len], group, self.Hkv, self.D, ctx.max_seq_len),
                         attention_ops.umma_pair_bound(lens, group) if lens else 0)
-                attention_ops.attention_umma(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
-                                             self.Hkv, self.D, self.scale, window, ctx.max_q_len, shape[0], shape[1])
+                if ((ctx.max_prefill_seq_len or ctx.max_seq_len) <= attention_ops.UMMA_SHORT_CONTEXT
+                        and attention_ops.umma64_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size)):
+                    attention_ops.attention_umma64(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
+                                                   self.Hkv, self.D, self.scale, window, ctx.max_q_len, shape[1])
+                else:
+                    attention_ops.attention_umma(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
+                                                 self.Hkv, self.D, self.scale, window, ctx.max_q_len, shape[0], shape[1])
                 tc_prefill = False
             if tc_decode or tc_prefill:
                 attention_ops.attention_tc(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,

@@ -71,6 +71,8 @@ class StepContext:
     any_decode: bool = True            # some request brings exactly one token
     any_prefill: bool = True           # some request brings more than one
     decode_splits: int = 0             # > 0: the decode attention uses this many key splits (CUDA graphs)
+    max_prefill_seq_len: int = 0       # longest request among those that bring more than one token (0: not known,
+                                       # take max_seq_len); inside a captured graph a bound for all its replays
     split_norms: bool = False          # norms between two products may be taken apart (see HalfNormed)
     prev_tokens: Optional[torch.Tensor] = None   # int32 [rows]: a token id -(r + 1) stands for prev_tokens[r]
     # host copies for parts written in plain torch (tests, toy parts)

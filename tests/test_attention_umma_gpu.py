@@ -1,4 +1,5 @@
-"""The tcgen05 / TMEM / TMA prompt attention against the plain formula: portions with and without
+"""The tcgen05 / TMEM / TMA prompt attention (the kernel with 128-key tiles and the one with 64-key tiles for
+short contexts) against the plain formula: portions with and without
 history, several requests, both head sizes, group sizes that divide 128, page sizes 8..256, windows,
 decoded tokens in the batch left alone, garbage in unused cache slots, a decisive far key."""
 import random
@@ -11,7 +12,7 @@ from test_kernels_gpu import paged_case, plain_paged
 pytestmark = pytest.mark.gpu
 
 
-def run(reqs, H, Hkv, D, bs, window, seed, key_splits=1):
+def run(reqs, H, Hkv, D, bs, window, seed, key_splits=1, short=False):
     from dinfer_b200.kernels import attention_ops as A
     from dinfer_b200.kernels import gemm_ops as G
     rng = random.Random(seed)
@@ -22,9 +23,14 @@ def run(reqs, H, Hkv, D, bs, window, seed, key_splits=1):
     wide = torch.zeros(T, (H + 2 * Hkv) * D, dtype=torch.bfloat16, device="cuda")    # q as columns of the qkv rows
     wide[:, :H * D] = q.reshape(T, H * D).cuda()
     out = torch.full((T, H * D), 7.0, dtype=torch.bfloat16, device="cuda")
-    A.attention_umma(wide[:, :H * D], out, cache.cuda(), table.cuda(), cu.cuda(), seq.cuda(), H, Hkv, D, scale,
-                     window or 0, max(n for _, n in reqs), key_splits,
-                     A.umma_pair_bound([n for _, n in reqs], H // Hkv) if seed % 2 else 0)   # the step's own bound, or none
+    bound = A.umma_pair_bound([n for _, n in reqs], H // Hkv) if seed % 2 else 0       # the step's own bound, or none
+    if short:
+        assert A.umma64_supported(torch.bfloat16, D, H // Hkv, bs)
+        A.attention_umma64(wide[:, :H * D], out, cache.cuda(), table.cuda(), cu.cuda(), seq.cuda(), H, Hkv, D, scale,
+                           window or 0, max(n for _, n in reqs), bound)
+    else:
+        A.attention_umma(wide[:, :H * D], out, cache.cuda(), table.cuda(), cu.cuda(), seq.cuda(), H, Hkv, D, scale,
+                         window or 0, max(n for _, n in reqs), key_splits, bound)
     G.check_status()
     want = plain_paged(reqs, qs, ks, vs, scale, window).reshape(T, H * D)
     got = out.double().cpu()
@@ -43,12 +49,15 @@ def run(reqs, H, Hkv, D, bs, window, seed, key_splits=1):
 def test_mixed_portions(H, Hkv, D, bs, window):
     reqs = [(40, 5), (70, 1), (0, 33), (130, 64), (0, 1), (250, 17), (0, 2), (65, 130), (0, 300)]
     run(reqs, H, Hkv, D, bs, window, seed=H * D + bs)
+    if bs <= 64:
+        run(reqs, H, Hkv, D, bs, window, seed=H * D + bs + 1, short=True)
 
 
-def test_long_prompt_and_history():
-    run([(0, 1100)], 8, 2, 128, 16, None, seed=1)
-    run([(1500, 700), (3, 129)], 8, 2, 128, 16, None, seed=2)
-    run([(900, 260)], 4, 1, 64, 16, 333, seed=3)
+@pytest.mark.parametrize("short", [False, True])
+def test_long_prompt_and_history(short):
+    run([(0, 1100)], 8, 2, 128, 16, None, seed=1, short=short)
+    run([(1500, 700), (3, 129)], 8, 2, 128, 16, None, seed=2, short=short)
+    run([(900, 260)], 4, 1, 64, 16, 333, seed=3, short=short)
 
 
 @pytest.mark.parametrize("key_splits", [2, 4, 8])
@@ -93,6 +102,8 @@ def test_many_decoding_requests_beside_a_portion():
     reqs = [(50 + i, 1) for i in range(120)] + [(700, 200)] + [(9, 1)] * 100 + [(0, 300), (128, 2)] + [(77, 1)] * 80
     run(reqs, 8, 2, 128, 16, None, seed=21, key_splits=2)
     run(reqs, 4, 4, 64, 8, 90, seed=22)
+    run(reqs, 8, 2, 128, 16, None, seed=23, short=True)
+    run(reqs, 4, 4, 64, 8, 90, seed=24, short=True)
 
 
 def test_key_split_choice():
@@ -110,11 +121,12 @@ def test_key_split_choice():
     assert A.umma_max_clusters(128, 1) >= A.umma_max_clusters(128, 2) * 2 - 2 > 0
 
 
-def test_more_pages_than_the_shared_memory_table_holds():
+@pytest.mark.parametrize("short", [False, True])
+def test_more_pages_than_the_shared_memory_table_holds(short):
     """Block tables longer than the slice a CTA keeps in shared memory (2048 entries): the entries
     beyond it are read from the table in memory."""
-    run([(17000, 40)], 4, 2, 128, 8, None, seed=5)
-    run([(16500, 300)], 4, 1, 64, 8, 9000, seed=6)
+    run([(17000, 40)], 4, 2, 128, 8, None, seed=5, short=short)
+    run([(16500, 300)], 4, 1, 64, 8, 9000, seed=6, short=short)
 
 
 def test_far_key_wins():
@@ -175,4 +187,7 @@ def test_window_edges_with_the_passed_pages_given_back(H, Hkv, D, bs, window):
         out = torch.full((T, H * D), 7.0, dtype=torch.bfloat16, device="cuda")
         A.attention_umma(dq, out, dc, dt, dcu, dseq, H, Hkv, D, scale, window, max_q)
         held(out, pre, "tcgen05 kernel")
+        out = torch.full((T, H * D), 7.0, dtype=torch.bfloat16, device="cuda")
+        A.attention_umma64(dq, out, dc, dt, dcu, dseq, H, Hkv, D, scale, window, max_q)
+        held(out, pre, "tcgen05 kernel with 64-key tiles")
     G.check_status()

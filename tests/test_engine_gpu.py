@@ -491,7 +491,7 @@ def test_a_long_prompt_whole_and_in_portions(tmp_path, dtype):
             got.append(r.step([StepEntry("a", [t], [0])])[0].float().cpu())
             places.append(n0 + i)
         if budget == 512:
-            assert ("mixed", 512, 4, 0) in r._graphs
+            assert ("mixed", 512, 4, 0, False) in r._graphs          # the graph of portions beyond the short contexts
         r.finish("a")
         r.check_device_status()
         err = H.rel_err(torch.stack(got).numpy(), want[places])
