@@ -120,7 +120,7 @@ def make_llm(cfg, layers, max_seqs, context, seed=42, **engine):
     blocks = max_seqs * ((context + 64 + 15) // 16) + (PREFILL_TOKENS + 64) // 16 + 64
     return LLM(config=c, weights=RandomSource(c, seed, std=0.02, norm_jitter=0.0), dtype="bfloat16",
                max_model_len=max(context, PREFILL_TOKENS) + 64, max_num_seqs=max(max_seqs, 1), max_num_batched_tokens=2048,
-               num_blocks=blocks, block_size=16, enable_cuda_graph=True, **engine)
+               num_blocks=blocks, block_size=16, enable_cuda_graph=True, **{"split_norms": "auto", **engine})
 
 
 def count_launches(fn):
@@ -293,7 +293,7 @@ def closed_loop_run(shape: str, clients: int, prompt_len: int, output_len: int, 
     name, cfg = SHAPES[shape]
     llm = LLM(config=cfg, weights=RandomSource(cfg, 3, std=0.02, norm_jitter=0.0), dtype="bfloat16",
               max_model_len=max(2048, prompt_len + output_len + 64), max_num_seqs=max(16, clients),
-              max_num_batched_tokens=2048, block_size=16)
+              max_num_batched_tokens=2048, block_size=16, split_norms="auto")
     rng = random.Random(11)
     sp = SamplingParams(temperature=0.0, max_tokens=output_len, ignore_eos=True)
 
@@ -402,7 +402,9 @@ def main() -> int:
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
                    "vocab": cfg["vocab_size"], "global_batch": a.batch, "seq_len": a.context, "mean_context_timed": round(ctx_mid, 1),
                    "block_size": 16, "parallelism": "single GPU", "prefill_tokens": PREFILL_TOKENS,
-                   "l2": "inputs larger than L2 (weights + cache read per step)", "peaks": pk["source"]},
+                   "l2": "inputs larger than L2 (weights + cache read per step)", "peaks": pk["source"],
+                   # the engine option this run sets: each decode graph in the faster of its two forms, measured at start
+                   "split_norms": "auto: norms taken apart at batch sizes " + (",".join(map(str, llm.runner.split_norms_buckets())) or "none")},
         "e2e": {"value": round(a.batch * 1e3 / main_run["e2e_ms_per_step"], 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": main_run["h2d_bytes_per_step"],
                 "d2h_bytes_per_step": main_run["d2h_bytes_per_step"],

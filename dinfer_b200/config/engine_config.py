@@ -4,7 +4,7 @@
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
+from typing import Any, Optional
 
 
 @dataclass
@@ -48,9 +48,13 @@ class EngineConfig:
     enable_prefix_caching: bool = False
     # RMSNorms between two decode products (steps of at most 32 rows, bfloat16): True = taken apart into the
     # products' epilogues wherever the parts can (two launches per layer less), False = kernels of their own.
-    # Off by default: it pays where a step is bound by launch latency (small models, +4..9 % at the 0.6B shape
-    # up to batch 8) and costs where the products' longer tails show (-6 % at the 8B shape at batch 1).
-    split_norms: bool = False
+    # Off by default: it pays here and costs there with no rule to it (closed loops of 128 + 128 tokens: +8 % at
+    # the 0.6B shape with one client, -8 % with 32; -8 % at the 8B shape with one client, +3 % with 8).
+    # "auto" = measured: every decode graph is captured in both forms when it is made, each is replayed a few
+    # times between CUDA events, and the form taken apart is kept where it is faster by 2 % or more.  Steps that
+    # run kernel by kernel keep the norms whole.  The two forms differ by roundings, so with "auto" the same seed
+    # may give another text after a restart should a measurement fall the other way; hence not the default.
+    split_norms: Any = False
     # the next step is scheduled and launched while the last one still runs; the host reads a step's tokens one
     # step late (the reference's ASYNC_SCHED, on by default there too: crates/core/src/engine.rs:153,822).
     # Steps with penalties or log-probabilities (which need the last tokens on the host) run one at a time
@@ -81,5 +85,7 @@ class EngineConfig:
             raise ValueError("gpu_memory_utilization must be in (0, 1]")
         if self.graph_host_us_per_layer < 0 or self.graph_device_flops <= 0:
             raise ValueError("graph_host_us_per_layer must not be negative and graph_device_flops must be positive")
+        if self.split_norms not in (False, True, "auto"):
+            raise ValueError(f'split_norms must be False, True or "auto", got {self.split_norms!r}')
         if self.num_blocks is not None and self.num_blocks <= 0:
             raise ValueError("num_blocks must be positive")

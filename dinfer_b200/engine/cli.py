@@ -44,9 +44,9 @@ def _engine_flags(p: argparse.ArgumentParser) -> None:
     p.add_argument("--no-cuda-graph", action="store_true")
     p.add_argument("--enable-prefix-caching", action="store_true",
                    help="share the cached pages of equal prompt beginnings between requests")
-    p.add_argument("--split-norms", action="store_true",
-                   help="decode steps: take the RMSNorms between two products apart into the products' epilogues "
-                        "(pays for small models, see EngineConfig.split_norms)")
+    p.add_argument("--split-norms", nargs="?", const="on", default="off", choices=["on", "off", "auto"],
+                   help="decode steps: take the RMSNorms between two products apart into the products' epilogues; "
+                        "auto = measured per batch-size bucket when its graph is captured (see EngineConfig.split_norms)")
     p.add_argument("--no-mixed-cuda-graph", action="store_true",
                    help="steps with prompt portions always launch their kernels one by one")
     p.add_argument("--no-async-scheduling", action="store_true",
@@ -84,7 +84,7 @@ def cmd_generate(a) -> int:
               block_size=a.block_size, gpu_memory_utilization=a.gpu_memory_utilization,
               decode_exempt_from_budget=not a.no_decode_exempt,
               long_prefill_token_threshold=a.long_prefill_token_threshold,
-              enable_cuda_graph=not a.no_cuda_graph, enable_prefix_caching=a.enable_prefix_caching, split_norms=a.split_norms,
+              enable_cuda_graph=not a.no_cuda_graph, enable_prefix_caching=a.enable_prefix_caching, split_norms={"on": True, "off": False, "auto": "auto"}[a.split_norms],
               async_scheduling=not a.no_async_scheduling, mixed_cuda_graph=not a.no_mixed_cuda_graph,
               device=a.device)
     su = llm.runner.startup_seconds

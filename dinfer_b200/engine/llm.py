@@ -91,7 +91,7 @@ class LLM:
                  block_size: int = 16, gpu_memory_utilization: float = 0.9,
                  decode_exempt_from_budget: bool = True, long_prefill_token_threshold: int = 0,
                  enable_cuda_graph: bool = True, enable_prefix_caching: bool = False,
-                 split_norms: bool = False, async_scheduling: bool = True, mixed_cuda_graph: bool = True,
+                 split_norms: Any = False, async_scheduling: bool = True, mixed_cuda_graph: bool = True,
                  allow_unused_tensors: bool = False, native_host: bool = True, device: int = 0):
         """``model``: a folder with config.json and *.safetensors; or ``config`` (the config.json
         dictionary) with ``weights`` (any WeightSource, e.g. ``RandomSource``)."""

@@ -16,6 +16,7 @@ CUDA graph per batch bucket, steps with prompt portions replay one where their s
 """
 from __future__ import annotations
 
+import dataclasses
 import math
 import time
 from typing import Any, Dict, Hashable, List, Optional, Sequence
@@ -263,7 +264,7 @@ class ModelRunner:
             logits = self._mixed_graph_step(entries, starts, *mixed)
         else:
             ids, rows, ctx = self.plan.build(entries, starts)
-            ctx.split_norms = bool(self.engine.split_norms)
+            ctx.split_norms = self.engine.split_norms is True
             ctx.prev_tokens = self.sampled
             logits = self.model.forward(ids, ctx, self.bindings, rows)
         for e, s in zip(entries, starts):
@@ -298,12 +299,41 @@ class ModelRunner:
         # the split count is part of the captured launch: fixed per bucket, for the longest context
         hkv = max([n.num_kv_heads for n in self.model.cache_needs() if isinstance(n, KvCacheNeed)] or [1])
         ctx.decode_splits = attention_ops.decode_splits(bucket, hkv, self.engine.max_model_len)
-        ctx.split_norms = bool(self.engine.split_norms)
+        ctx.split_norms = self.engine.split_norms is True
         ctx.prev_tokens = self.sampled
         rec = self._capture_one(ids, rows, ctx)
+        rec["split_norms"] = ctx.split_norms
+        if self.engine.split_norms == "auto" and self.model.can_split_norms(bucket):
+            # both forms of the step, measured on this device: the one with the norms taken apart where it is faster
+            apart = self._capture_one(ids, rows, dataclasses.replace(ctx, split_norms=True, derived={}))
+            t_whole, t_apart = self._graph_time(rec["graph"]), self._graph_time(apart["graph"])
+            if t_apart <= 0.98 * t_whole:
+                rec = apart
+                rec["split_norms"] = True
+            rec["times_ms"] = (t_whole, t_apart)
         rec.update(dev=dev, splits=ctx.decode_splits, width=width, plan=DecodePlan(self.plan, bucket, width, dev))
         self._graphs[bucket] = rec
         return rec
+
+    @staticmethod
+    def _graph_time(graph, replays: int = 8, rounds: int = 3) -> float:
+        """Milliseconds per replay: the best of a few rounds of back-to-back replays between CUDA events."""
+        graph.replay()
+        best = None
+        for _ in range(rounds):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(replays):
+                graph.replay()
+            e1.record()
+            e1.synchronize()
+            ms = e0.elapsed_time(e1) / replays
+            best = ms if best is None else min(best, ms)
+        return best
+
+    def split_norms_buckets(self) -> List[int]:
+        """The decode buckets captured so far whose graph runs with the norms taken apart."""
+        return sorted(k for k, r in self._graphs.items() if isinstance(k, int) and r.get("split_norms"))
 
     def _capture_one(self, ids, rows, ctx):
         cur = torch.cuda.current_stream()

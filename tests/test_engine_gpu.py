@@ -578,3 +578,43 @@ def test_prompt_logprobs(dirs):
                 assert rec.rank == int((want[i - 1] > want[i - 1, p[i]]).sum())
                 assert rec.top_ids == torch.topk(want[i - 1], k).indices.tolist() if k else rec.top_ids == []
     llm.runner.manager.check_invariants()
+
+
+def test_decode_graphs_in_the_measured_form(tmp_path):
+    """split_norms = "auto": every decode bucket's graph is captured with the norms whole and taken apart, both are
+    timed, one is kept; whichever it is, the decoded tokens' logits are the plain model's."""
+    from dinfer_b200.config.engine_config import EngineConfig
+    from dinfer_b200.engine.batch import StepEntry
+    from dinfer_b200.engine.runner import ModelRunner
+    cfg = H.TINY_D
+    rng = random.Random(12)
+    toks = {r: H.random_tokens(rng, n, cfg["vocab_size"]) for r, n in {"a": 30, "b": 21, "c": 26}.items()}
+    d = H.make_model_dir(str(tmp_path / "d"), cfg, *H.INIT["D"], torch.bfloat16)
+    oracle = H.PlainOracle(d)
+    r = ModelRunner.from_dir(d, EngineConfig(max_model_len=64, max_num_seqs=4, max_num_batched_tokens=64,
+                                                     num_blocks=16, block_size=16, dtype="bfloat16", split_norms="auto"))
+    assert r.model.can_split_norms(4)
+    buckets = [k for k in r._graphs if isinstance(k, int)]
+    assert buckets == [1, 2, 4]                                      # captured when the engine starts
+    for k in buckets:
+        t_whole, t_apart = r._graphs[k]["times_ms"]
+        assert t_whole > 0 and t_apart > 0
+        assert r._graphs[k]["split_norms"] == (t_apart <= 0.98 * t_whole)
+    assert r.split_norms_buckets() == [k for k in buckets if r._graphs[k]["split_norms"]]
+    got = {k: [] for k in toks}
+    out = r.step([StepEntry(k, t[:6], [5]) for k, t in toks.items()])
+    for i, k in enumerate(toks):
+        got[k].append(out[i].float().cpu())
+    p = 6
+    while any(len(t) > p for t in toks.values()):
+        live = [k for k, t in toks.items() if len(t) > p]
+        out = r.step([StepEntry(k, [toks[k][p]], [0]) for k in live])
+        for j, k in enumerate(live):
+            got[k].append(out[j].float().cpu())
+            if len(toks[k]) == p + 1:
+                r.finish(k)
+        p += 1
+    r.check_device_status()
+    for k, t in toks.items():
+        err = H.rel_err(torch.stack(got[k]).numpy(), oracle.logits(t)[5:])
+        assert err <= H.TOLERANCE["bfloat16"], (k, err)
