@@ -51,6 +51,7 @@ def test_usage_errors():
     assert run("no-such-command").returncode != 0
     r = run("generate", "--help")
     assert r.returncode == 0 and "--max-num-batched-tokens" in r.stdout and "--enable-prefix-caching" in r.stdout
+    assert run("generate", "--model", "x", "--split-norms", "sometimes").returncode != 0     # on, off or auto
 
 
 @pytest.mark.gpu
@@ -85,3 +86,17 @@ def test_generate_with_random_weights_needs_no_files(tmp_path):
 
     a, b, c = tokens(1), tokens(1), tokens(2)
     assert len(a) == 8 and a == b and a != c
+
+
+@pytest.mark.gpu
+def test_generate_with_the_norms_taken_apart_where_measured_faster(tmp_path):
+    """``--split-norms auto`` (and plain ``--split-norms`` = on) in bfloat16: the run goes through and gives as many
+    tokens as asked, ids within the vocabulary."""
+    d = H.make_model_dir(str(tmp_path / "d"), H.TINY_D, *H.INIT["D"], torch.bfloat16)
+    for flag in (["--split-norms", "auto"], ["--split-norms"]):
+        r = run("generate", "--model", d, "--dtype", "bfloat16", "--max-model-len", "64", "--max-num-seqs", "2",
+                "--num-blocks", "16", "--prompt-ids", "5,17,3,9", "--max-tokens", "6", "--temperature", "0",
+                "--ignore-eos", *flag)
+        assert r.returncode == 0, r.stderr
+        line = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")][0]
+        assert len(line["output_ids"]) == 6 and all(0 <= t < H.TINY_D["vocab_size"] for t in line["output_ids"])
