@@ -41,8 +41,8 @@ def graph_shape(prompt_lens: Sequence[int], num_decodes: int, budget: int, bucke
     """The shape of the captured graph a step with prompt portions replays, as (prompt tokens after padding,
     prompt places, decode bucket), or None for a step that runs kernel by kernel.  ``prompt_lens``: the tokens of
     the step's prompt portions; ``place_counts``: the numbers of prompt places graphs are made with, rising (the
-    padding takes a place too; a place without tokens still costs the attention kernel an empty CTA per head and
-    row tile, hence more than one size); ``small_max``: up to so many prompt tokens are padded to a power of two
+    padding takes a place too; a place without tokens still counts one row-tile pair per head in the bound the
+    attention kernel's grid is made from, hence more than one size); ``small_max``: up to so many prompt tokens are padded to a power of two
     (from 16); ``padded_limit``: up to so many are padded to a multiple of 128 (256 beyond 1024); portions that
     fill ``budget`` exactly need no padding.  ``longest``: the most tokens one place may hold (the longest request
     the cache tables and the position table are made for); a step whose dummy portion, or whose capture (dummy
