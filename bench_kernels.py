@@ -274,6 +274,8 @@ def main() -> int:
     ap.add_argument("--batches", type=int, nargs="*", default=[1, 8, 64], help="requests of the decode attention")
     ap.add_argument("--contexts", type=int, nargs="*", default=[1024, 4096, 16384])
     ap.add_argument("--prompt-tokens", type=int, nargs="*", default=[2048, 8192])
+    ap.add_argument("--heads", type=int, nargs=3, metavar=("H", "HKV", "D"), default=None,
+                    help="attention sections: other head counts and head size than the Qwen3-8B shape's 32 8 128")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         print("bench_kernels.py needs a GPU", file=sys.stderr)
@@ -285,6 +287,9 @@ def main() -> int:
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
         import ref_kernels
         return ref_kernels.run(sys.modules[__name__], a, hbm, tflops)
+    if a.heads:
+        SHAPE.update(heads=a.heads[0], kv_heads=a.heads[1], head_dim=a.heads[2])
+        print(f"# heads {a.heads[0]}, kv heads {a.heads[1]}, head size {a.heads[2]}")
     todo = [a.only] if a.only else ["gemm_decode", "gemm_prompt", "attention_decode", "attention_prompt", "attention_short", "attention_portion", "sampling"]
     if "gemm_decode" in todo:
         gemm_decode(SHAPE, a.tokens, hbm)
