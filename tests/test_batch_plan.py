@@ -161,3 +161,18 @@ def test_pair_bound_of_the_prompt_attention_holds_for_every_spread_of_the_tokens
         lens = [b - a for a, b in zip([0] + cuts, cuts + [total])]
         pairs = sum((n * group + 255) // 256 for n in lens if n > 1)
         assert pairs <= bound <= (total * group) // 256 + places, (lens, group, bound)
+
+
+def test_the_longest_prompt_request_of_a_step_is_told_apart_from_the_longest_request():
+    """``max_prefill_seq_len`` counts only requests that bring more than one token: a short new prompt beside a
+    long decoding request still counts as a short context for the parts that choose by it."""
+    m = CacheManager([GroupSpec()], 8, [64], max_num_seqs=4)
+    builder = PlanBuilder(m, "cpu", max_tokens=64, max_reqs=4, max_blocks=32)
+    assert m.allocate("old", 200) and m.allocate("new", 9) and m.allocate("more", 40)
+    m.advance("old", 199)
+    m.advance("more", 30)
+    entries = [StepEntry("old", [5], [0]), StepEntry("new", list(range(9)), [8]), StepEntry("more", list(range(10)), [])]
+    ids, rows, ctx = builder.build(entries, [199, 0, 30])
+    assert ctx.max_seq_len == 200 and ctx.max_prefill_seq_len == 40 and ctx.max_q_len == 10
+    ids, rows, ctx = builder.build(entries[:1], [199])
+    assert ctx.max_prefill_seq_len == 0 and ctx.all_decode
