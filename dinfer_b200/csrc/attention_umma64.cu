@@ -59,7 +59,7 @@ template <int D> constexpr size_t smem_bytes() {
 // 256 and the rescale is rare.
 template <int D>
 __global__ void __launch_bounds__(NTHREADS, 1)
-attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Params p) {
+attention_umma64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Params p) {
   constexpr int NH = D / 64;                          // 64-wide halves of the head
   constexpr uint32_t Q_HALF = BM * 128, KV_HALF = BN * 128;
   constexpr uint32_t Q_BYTES = NH * Q_HALF, KV_BYTES = NH * KV_HALF, P_BYTES = BM * BN * 2;
@@ -429,7 +429,7 @@ EncodeTiledFn encode_fn() {
 
 template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const Params& p, dim3 grid, cudaStream_t stream) {
-  auto k = attention_umma_kernel<D>;
+  auto k = attention_umma64_kernel<D>;
   constexpr size_t sm = smem_bytes<D>();
   static bool opted = false;
   if (!opted) {
